@@ -1,0 +1,409 @@
+"""CPU oracle for the quantized-inference operator family (TEST INFRASTRUCTURE ONLY).
+
+This module is a checker, not a product path: only the test-suite, the smoke
+check and the CPU-baseline leg of the benchmark may import it.  It restates, on
+the host CPU with torch float8 dtypes, the semantics that the reference fixes
+for ``torch.ops.hpu.{cast_to_fp8_v2, cast_from_fp8, fp8_gemm_v2,
+convert_from_int4, convert_from_uint4}``.  The reference itself holds no
+arithmetic for these operators (each one only appends a node to a graph that a
+closed kernel library executes), so every function below follows the argument
+plumbing of the reference's C++ and the CPU emulation that the reference's own
+tests compare the device against:
+
+* ``hpu_ops/backend/fp8_ops.cpp:29-53``   scale / scale_shape validation
+* ``hpu_ops/backend/fp8_ops.cpp:63-96``   scale tensor reshape, scalar and list scales
+* ``hpu_ops/backend/fp8_ops.cpp:105-119`` rounding-mode choice (RNE / stochastic)
+* ``hpu_ops/backend/fp8_ops.cpp:170-258`` cast_to_fp8_v2 (dtype checks, amax shape)
+* ``hpu_ops/backend/fp8_ops.cpp:262-308`` cast_from_fp8
+* ``hpu_ops/backend/fp8_ops.cpp:370-496`` fp8_gemm_v2 (operand order, accumulate check)
+* ``hpu_ops/common/batched_matmul_output_shape.cpp:34-88`` matmul output shape rules
+* ``hpu_ops/backend/int4_ops.cpp:22-56``  convert_from_{int4,uint4}
+* ``tests/pytest_working/any_mode/test_hpu_fp8_ops_any_mode.py:85-87`` expected value of a
+  cast: ``simulateFp8Precision(input * scale.to(dtype))`` -- the product is
+  formed and rounded in the INPUT dtype before the fp8 rounding
+* ``tests/pytest_working/any_mode/test_hpu_fp8_ops_any_mode.py:220-243`` saturation to +-max
+* ``tests/pytest_working/any_mode/test_hpu_convert_from_int4.py:41-71,119-132`` nibble order
+  (LSB first), packed / unpacked zero points
+
+Pinning: the RNE cast is checked against golden vectors produced by the
+reference's own ``tests/pytest_working/fp8_utils.py::simulateFp8Precision``
+(imported from the reference tree by ``tests/golden/make_golden.py``; the
+vectors are committed under ``tests/golden/``).  Stochastic-rounding bit
+patterns, NaN/Inf handling and the GEMM summation order are pinned by no
+reference test; for those the definitions in this file are the contract.
+"""
+from __future__ import annotations
+
+import math
+from typing import Optional, Sequence, Union
+
+import numpy as np
+import torch
+
+FP8_DTYPES = (torch.float8_e5m2, torch.float8_e4m3fn)
+FP8_MAX = {torch.float8_e4m3fn: 448.0, torch.float8_e5m2: 57344.0}
+# (mantissa bits, biased fp32 exponent of the smallest normal, log2 of the subnormal quantum)
+_FP8_FMT = {torch.float8_e4m3fn: (3, 127 - 6, -9), torch.float8_e5m2: (2, 127 - 14, -16)}
+
+ScaleArg = Union[None, float, Sequence[float], torch.Tensor]
+
+
+def dtype_name(dt: torch.dtype) -> str:
+    """c10 spelling of a dtype as it appears in the reference's error strings."""
+    return {
+        torch.float8_e5m2: "Float8_e5m2",
+        torch.float8_e4m3fn: "Float8_e4m3fn",
+        torch.float32: "Float",
+        torch.bfloat16: "BFloat16",
+    }.get(dt, str(dt))
+
+
+# --------------------------------------------------------------------------- scales
+def validate_scale_shape(scale: ScaleArg, scale_shape) -> None:
+    """fp8_ops.cpp:29-53 -- element-count check, skipped for None / float scales."""
+    if scale is None or isinstance(scale, (float, int)) or scale_shape is None:
+        return
+    n = scale.numel() if isinstance(scale, torch.Tensor) else len(scale)
+    m = 1
+    for d in scale_shape:
+        m *= int(d)
+    if n != m:
+        raise RuntimeError(
+            f"Number of scale elements ({n}) is not equal to number of scale_shape elements ({m})."
+        )
+
+
+def resolve_scale(scale: ScaleArg, scale_shape=None) -> Optional[torch.Tensor]:
+    """Return the scale as a tensor ready to broadcast, or None.
+
+    fp8_ops.cpp:63-74: a tensor with more than one element is reshaped to
+    scale_shape when the two differ.  fp8_ops.cpp:85-96: a float becomes a
+    constant, a float list becomes a constant tensor of shape scale_shape.
+    """
+    validate_scale_shape(scale, scale_shape)
+    if scale is None:
+        return None
+    if isinstance(scale, (float, int)):
+        return torch.tensor(float(scale), dtype=torch.float32)
+    if isinstance(scale, torch.Tensor):
+        s = scale.detach().cpu()
+        if s.numel() > 1 and scale_shape is not None and list(s.shape) != list(scale_shape):
+            s = s.reshape(list(scale_shape))
+        return s
+    s = torch.tensor([float(v) for v in scale], dtype=torch.float32)
+    if scale_shape is not None:
+        s = s.reshape(list(scale_shape))
+    return s
+
+
+# --------------------------------------------------------------------------- Philox + SR
+_PHILOX_M0 = np.uint64(0xD2511F53)
+_PHILOX_M1 = np.uint64(0xCD9E8D57)
+_PHILOX_W0 = 0x9E3779B9
+_PHILOX_W1 = 0xBB67AE85
+_U32 = np.uint64(0xFFFFFFFF)
+
+
+def philox4x32_10(counter_lo: np.ndarray, seed: int, offset: int = 0) -> np.ndarray:
+    """Philox4x32-10.  counter = (c & 2^32-1, c >> 32, offset lo, offset hi), key = seed.
+
+    counter_lo: uint64 array of 64-bit block counters.  Returns uint32 [n, 4].
+    """
+    c = counter_lo.astype(np.uint64)
+    c0 = c & _U32
+    c1 = c >> np.uint64(32)
+    c2 = np.full_like(c0, np.uint64(offset & 0xFFFFFFFF))
+    c3 = np.full_like(c0, np.uint64((offset >> 32) & 0xFFFFFFFF))
+    k0 = seed & 0xFFFFFFFF
+    k1 = (seed >> 32) & 0xFFFFFFFF
+    for r in range(10):
+        p0 = _PHILOX_M0 * c0
+        p1 = _PHILOX_M1 * c2
+        hi0, lo0 = p0 >> np.uint64(32), p0 & _U32
+        hi1, lo1 = p1 >> np.uint64(32), p1 & _U32
+        c0, c1, c2, c3 = (hi1 ^ c1 ^ np.uint64(k0)), lo1, (hi0 ^ c3 ^ np.uint64(k1)), lo0
+        k0 = (k0 + _PHILOX_W0) & 0xFFFFFFFF
+        k1 = (k1 + _PHILOX_W1) & 0xFFFFFFFF
+    return np.stack([c0, c1, c2, c3], axis=1).astype(np.uint32)
+
+
+def philox_words(n: int, seed: int, offset: int = 0, first_index: int = 0) -> np.ndarray:
+    """One 32-bit word per element: element i uses word (i % 4) of block (i // 4)."""
+    idx = np.arange(first_index, first_index + n, dtype=np.uint64)
+    blocks = idx >> np.uint64(2)
+    ub, inv = np.unique(blocks, return_inverse=True)
+    w = philox4x32_10(ub, seed, offset)
+    return w[inv, (idx & np.uint64(3)).astype(np.int64)]
+
+
+def stochastic_round_to_fp8(v32: torch.Tensor, dtype: torch.dtype, seed: int, offset: int = 0,
+                            first_index: int = 0) -> torch.Tensor:
+    """Stochastic rounding of an fp32 tensor (already scaled and clamped) to fp8.
+
+    |v| is rounded to one of its two fp8 neighbours; it moves away from zero
+    with probability (|v| - lo) / (hi - lo).  Bit-level definition, for an
+    element whose flat index is i and random word r = philox(seed, i):
+    let E be the biased fp32 exponent of |v| (0 counts as 1), Emin that of the
+    smallest normal fp8 value and d = 23 - mantissa bits.
+      E >= Emin : bits = (bits + (r & (2^d - 1))) with the low d bits cleared;
+      E <  Emin : s = d + Emin - E; with the 24-bit significand m (for s > 32
+                  first m >>= s - 32 and s = 32): t = (m + (r & (2^s - 1))) >> s,
+                  result = t * 2^(log2 of the subnormal quantum).
+    The result is clamped to +-max.  Values between 0 and the smallest
+    subnormal therefore also round stochastically (the reference's default
+    "SFTZ" behaviour, scripts/env_flags.yaml:753-758).  NaN stays NaN.
+    """
+    mbits, emin, qlog2 = _FP8_FMT[dtype]
+    d = 23 - mbits
+    flat = v32.detach().to(torch.float32).contiguous().reshape(-1)
+    n = flat.numel()
+    bits = flat.numpy().view(np.uint32).astype(np.uint64)
+    sign = bits & np.uint64(0x80000000)
+    mag = bits & np.uint64(0x7FFFFFFF)
+    r = philox_words(n, seed, offset, first_index).astype(np.uint64)
+    isnan = mag > np.uint64(0x7F800000)
+    E = (mag >> np.uint64(23)).astype(np.int64)
+    # normal range of the target
+    nmag = (mag + (r & np.uint64((1 << d) - 1))) & ~np.uint64((1 << d) - 1)
+    nval = (nmag & _U32).astype(np.uint32).view(np.float32)
+    # subnormal range of the target
+    Eeff = np.maximum(E, 1)
+    m = np.where(E > 0, (mag & np.uint64(0x7FFFFF)) | np.uint64(0x800000), mag & np.uint64(0x7FFFFF))
+    s = d + (emin - Eeff)
+    s = np.maximum(s, 0)
+    extra = np.clip(s - 32, 0, 63).astype(np.uint64)
+    m2 = m >> extra
+    s2 = np.minimum(s, 32).astype(np.uint64)
+    mask = (np.uint64(1) << s2) - np.uint64(1)
+    t = (m2 + (r & mask)) >> s2
+    sval = (t.astype(np.float64) * (2.0 ** qlog2)).astype(np.float32)
+    val = np.where(E >= emin, nval, sval)
+    val = np.minimum(val, np.float32(FP8_MAX[dtype]))
+    out = torch.from_numpy(val.copy())
+    out = torch.where(torch.from_numpy((sign != 0).copy()), -out, out)
+    out8 = out.to(dtype)  # exact: every value is representable
+    if isnan.any():
+        nanbyte = torch.from_numpy(((sign >> np.uint64(24)) | np.uint64(0x7F)).astype(np.uint8))
+        out8 = torch.where(torch.from_numpy(isnan.copy()), nanbyte, out8.view(torch.uint8)).view(dtype)
+    return out8.reshape(v32.shape)
+
+
+# --------------------------------------------------------------------------- casts
+def _rne_to_fp8(v32: torch.Tensor, dtype: torch.dtype) -> torch.Tensor:
+    """Saturating round-half-to-even: clamp to +-max in fp32, then convert.
+    NaN -> 0x7F | sign (torch's own conversion); never inf."""
+    mx = FP8_MAX[dtype]
+    return v32.clamp(-mx, mx).to(dtype)
+
+
+def cast_to_fp8_v2(input: torch.Tensor, scale: ScaleArg = None, stochastic_rounding: bool = False,
+                   is_amax: bool = False, dtype: torch.dtype = None, scale_shape=None, *,
+                   mul_in_fp32: bool = False, seed: int = 1234, offset: int = 0, first_index: int = 0):
+    """(out, amax) = cast_to_fp8_v2(...)   -- fp8_ops.cpp:192-258.
+
+    out  = fp8(input * scale), same shape as input.
+    amax = max|input| of the unscaled input as a 0-dim fp32 tensor when is_amax,
+           else an empty fp32 tensor of shape [0] (fp8_ops.cpp:170-178).
+    The product is formed in the input dtype (scale cast to it first) unless
+    mul_in_fp32 is set, in which case it is formed in fp32 with the fp32 scale.
+    """
+    if dtype is None:
+        raise RuntimeError("cast_to_fp8_v2: dtype is required")
+    x = input.detach().cpu()
+    is_fp8_in = x.dtype in FP8_DTYPES
+    if not (is_fp8_in or x.dtype in (torch.float32, torch.bfloat16)):
+        raise RuntimeError(
+            "CastToFp8V2 input dtype must be one of [float, bfloat16, float8_e5m2, float8_e4m3fn].")
+    if is_fp8_in:
+        if is_amax:
+            raise RuntimeError("CastToFp8V2 must have no amax for float8.")
+        if x.dtype != dtype:
+            raise RuntimeError(
+                "CastToFp8V2 input and output must have the same dtype for float8, but are "
+                f"{dtype_name(x.dtype)} and {dtype_name(dtype)}")
+    s = resolve_scale(scale, scale_shape)
+    amax = x.float().abs().max().to(torch.float32) if (is_amax and x.numel()) else (
+        torch.zeros((), dtype=torch.float32) if is_amax else torch.empty(0, dtype=torch.float32))
+    if is_fp8_in:
+        return x.clone(), amax
+    if s is None:
+        y32 = x.float()
+    elif mul_in_fp32:
+        y32 = x.float() * s.float()
+    else:
+        y32 = (x * s.to(x.dtype)).float()
+    mx = FP8_MAX[dtype]
+    if stochastic_rounding:
+        out = stochastic_round_to_fp8(y32.clamp(-mx, mx), dtype, seed, offset, first_index)
+    else:
+        out = _rne_to_fp8(y32, dtype)
+    return out, amax
+
+
+def cast_from_fp8(input: torch.Tensor, scale: ScaleArg, out_dtype: torch.dtype, scale_shape=None):
+    """out = T(input) * scale.to(T), rounded once in T  -- fp8_ops.cpp:265-308 and
+    test_hpu_fp8_ops_any_mode.py:85-87."""
+    if out_dtype not in (torch.float32, torch.bfloat16):
+        raise RuntimeError("CastFromFp8 output dtype must be equal to float or bfloat16.")
+    s = resolve_scale(scale, scale_shape)
+    y = input.detach().cpu().to(out_dtype)
+    return y if s is None else y * s.to(out_dtype)
+
+
+# --------------------------------------------------------------------------- gemm
+def matmul_out_shape(shape_a, shape_b, trans_a: bool, trans_b: bool):
+    """batched_matmul_output_shape.cpp:34-88 (torch.matmul rules with transposes)."""
+    ra, rb = len(shape_a), len(shape_b)
+    out = []
+    ca = cb = 0
+    if rb > 1:
+        out.append(shape_b[rb - 2 if trans_b else rb - 1])
+        cb = rb - 1 if trans_b else rb - 2
+    if ra > 1:
+        out.append(shape_a[ra - 1 if trans_a else ra - 2])
+        ca = ra - 2 if trans_a else ra - 1
+    if shape_a[ca] != shape_b[cb]:
+        raise RuntimeError(
+            f"Common dimension sizes of matmul inputs should be the same. Got {shape_a[ca]} and {shape_b[cb]}")
+    mr = max(ra, rb)
+    for i in range(3, mr + 1):
+        da = 1 if i > ra else shape_a[ra - i]
+        db = 1 if i > rb else shape_b[rb - i]
+        if da != db and da != 1 and db != 1:
+            raise RuntimeError(
+                f"Batch dimension {mr - i} of matmul inputs should be the same or at least one of them "
+                f"should be equal to 1. Got {da} and {db}")
+        out.append(da if da == db else da * db)
+    return list(reversed(out))
+
+
+def fp8_gemm_v2(A, trans_A, B, trans_B, D, out_dtype, A_scale_inv: ScaleArg = None,
+                B_scale_inv: ScaleArg = None, bias=None, accumulate: bool = False, B_scale_shape=None):
+    """out = (op(A) @ op(B)) * A_scale_inv * B_scale_inv [+ bias] [+ D]  -- fp8_ops.cpp:403-496.
+    fp32 accumulation; scales, bias and D applied in fp32; one rounding to out_dtype."""
+    if accumulate and D is None:
+        raise RuntimeError(
+            "Accumulation tensor must be provided at index 4 for Fp8GemmV2, when accumulate is true")
+    matmul_out_shape(list(A.shape), list(B.shape), trans_A, trans_B)
+    a = A.detach().cpu().float()
+    b = B.detach().cpu().float()
+    if trans_A and a.dim() >= 2:
+        a = a.transpose(-2, -1)
+    if trans_B and b.dim() >= 2:
+        b = b.transpose(-2, -1)
+    acc = torch.matmul(a, b)
+    sa = resolve_scale(A_scale_inv, None)
+    sb = resolve_scale(B_scale_inv, B_scale_shape)
+    if sa is not None:
+        acc = acc * sa.float()
+    if sb is not None:
+        acc = acc * sb.float()
+    if bias is not None:
+        acc = acc + bias.detach().cpu().float()
+    if accumulate:
+        acc = acc + D.detach().cpu().float()
+    return acc.to(out_dtype)
+
+
+# --------------------------------------------------------------------------- int4
+def pack_nibbles(values: torch.Tensor) -> torch.Tensor:
+    """Pack 4-bit values (any integer tensor, last dim a multiple of 8) into int32,
+    element 8p+i of the last dim -> bits [4i, 4i+4) of word p (LSB first), the
+    format of test_hpu_convert_from_int4.py:41-71."""
+    v = (values.to(torch.int64) & 0xF).reshape(*values.shape[:-1], values.shape[-1] // 8, 8)
+    sh = torch.arange(8, dtype=torch.int64) * 4
+    w = (v << sh).sum(-1)
+    w = torch.where(w >= 2 ** 31, w - 2 ** 32, w)
+    return w.to(torch.int32)
+
+
+def unpack_nibbles(packed: torch.Tensor, signed: bool) -> torch.Tensor:
+    w = packed.detach().cpu().to(torch.int64) & 0xFFFFFFFF
+    sh = torch.arange(8, dtype=torch.int64) * 4
+    v = (w.unsqueeze(-1) >> sh) & 0xF
+    if signed:
+        v = torch.where(v > 7, v - 16, v)
+    return v.reshape(*packed.shape[:-1], packed.shape[-1] * 8)
+
+
+def _expand_groups(t: torch.Tensor, out_shape) -> torch.Tensor:
+    """[.., K/g, N] -> [.., K, N] by repeating each row g times (grouped GPTQ scales)."""
+    if list(t.shape) == list(out_shape):
+        return t
+    if t.dim() >= 2 and t.dim() == len(out_shape) and t.shape[-1] == out_shape[-1] \
+            and out_shape[-2] % t.shape[-2] == 0 and list(t.shape[:-2]) == list(out_shape[:-2]):
+        return t.repeat_interleave(out_shape[-2] // t.shape[-2], dim=-2)
+    return t.expand(out_shape)
+
+
+def convert_from_4bit(input, scale, zero_point, out_dtype, signed: bool):
+    """out = (q - zero_point) * scale   -- int4_ops.cpp:22-56.
+    Packed int32 zero points are unpacked like the input and subtracted exactly as
+    integers; float zero points are subtracted in out_dtype.  Every float
+    operation is rounded in out_dtype (test_hpu_convert_from_int4.py:128-132)."""
+    if out_dtype not in (torch.float32, torch.bfloat16):
+        raise RuntimeError("convert_from_int4 output dtype must be float or bfloat16.")
+    q = unpack_nibbles(input, signed)
+    oshape = list(q.shape)
+    s = _expand_groups(scale.detach().cpu().to(out_dtype), oshape)
+    if zero_point is None:
+        sub = q.to(out_dtype)
+    elif zero_point.dtype == torch.int32:
+        zp = _expand_groups(unpack_nibbles(zero_point, signed), oshape)
+        sub = (q - zp).to(out_dtype)
+    else:
+        zp = _expand_groups(zero_point.detach().cpu().to(out_dtype), oshape)
+        sub = q.to(out_dtype) - zp
+    return sub * s
+
+
+def convert_from_int4(input, scale, zero_point, out_dtype):
+    return convert_from_4bit(input, scale, zero_point, out_dtype, True)
+
+
+def convert_from_uint4(input, scale, zero_point, out_dtype):
+    return convert_from_4bit(input, scale, zero_point, out_dtype, False)
+
+
+def dequant_kpacked(qweight, scales, qzeros, out_dtype=torch.bfloat16):
+    """Dequantise weights packed along K (AutoGPTQ layout): qweight int32 [K/8, N], row
+    8p+i of W = nibble i of qweight[p]; scales [K/g, N]; qzeros int32 [K/g, N/8]
+    packed along N (or None)."""
+    w = unpack_nibbles(qweight.t().contiguous(), False).t().contiguous()  # [K, N]
+    K, N = w.shape
+    s = _expand_groups(scales.detach().cpu().to(out_dtype), [K, N])
+    if qzeros is None:
+        return w.to(out_dtype) * s
+    zp = _expand_groups(unpack_nibbles(qzeros, False), [K, N])
+    return (w - zp).to(out_dtype) * s
+
+
+def w4a16_gemm(x, qweight, scales, qzeros, out_dtype=torch.bfloat16, k_packed=False):
+    """x @ W with W = convert_from_uint4(...) rounded to bf16; fp32 accumulation.
+    Contract by composition (the reference fuses the two nodes in its graph compiler)."""
+    if k_packed:
+        w = dequant_kpacked(qweight, scales, qzeros, torch.bfloat16)
+    else:
+        w = convert_from_uint4(qweight, scales, qzeros, torch.bfloat16)
+    return torch.matmul(x.detach().cpu().float(), w.float()).to(out_dtype)
+
+
+# --------------------------------------------------------------------------- TP MLP
+def fp8_swiglu_mlp(x_bf16, wg8, wu8, wd8, sg_inv, su_inv, sd_inv, x_scale, act_scale):
+    """FP8 SwiGLU MLP on one device: the composition the tensor-parallel path must match.
+    x_bf16 [T, d]; w*8 e4m3 [out, in]; s*_inv per-output-channel fp32; x_scale / act_scale
+    per-tensor fp32 scalars."""
+    x8, _ = cast_to_fp8_v2(x_bf16, x_scale, False, False, torch.float8_e4m3fn)
+    xs_inv = 1.0 / float(x_scale)
+    g = fp8_gemm_v2(x8, False, wg8, True, None, torch.bfloat16, xs_inv, sg_inv, None, False, [1, sg_inv.numel()])
+    u = fp8_gemm_v2(x8, False, wu8, True, None, torch.bfloat16, xs_inv, su_inv, None, False, [1, su_inv.numel()])
+    h = (torch.nn.functional.silu(g.float()) * u.float()).to(torch.bfloat16)
+    h8, _ = cast_to_fp8_v2(h, act_scale, False, False, torch.float8_e4m3fn)
+    return fp8_gemm_v2(h8, False, wd8, True, None, torch.bfloat16, 1.0 / float(act_scale), sd_inv, None, False,
+                       [1, sd_inv.numel()])
+
+
+def rel_frobenius(a: torch.Tensor, b: torch.Tensor) -> float:
+    a = a.detach().cpu().double()
+    b = b.detach().cpu().double()
+    return float((a - b).norm() / max(b.norm(), 1e-30))
