@@ -1,0 +1,168 @@
+"""ctypes binding of the C ABI in include/b200q.h (the drop-in boundary), used by the
+benchmarks and by tests that want to call the kernels without the torch dispatcher."""
+import ctypes as C
+import os
+
+import torch
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+_LIB_PATH = os.path.join(os.path.dirname(_HERE), "lib", "libb200q.so")
+
+F32, BF16, E4M3, E5M2 = 0, 1, 2, 3
+BCAST_NONE, BCAST_SCALAR_HOST, BCAST_SCALAR_DEV, BCAST_PER_COL, BCAST_PER_ROW, BCAST_FULL = range(6)
+ROUND_RNE, ROUND_STOCHASTIC = 0, 1
+ZP_NONE, ZP_PACKED, ZP_FLOAT = 0, 1, 2
+CAST_MUL_IN_FP32 = 1
+
+EXPORTS = [
+    "b200q_strerror", "b200q_last_cuda_error", "b200q_device_status", "b200q_launch_count",
+    "b200q_cast_to_fp8", "b200q_cast_from_fp8", "b200q_dequant_int4", "b200q_fp8_gemm",
+    "b200q_w4a16_gemm", "b200q_swiglu_cast_fp8",
+]
+
+DTYPE = {torch.float32: F32, torch.bfloat16: BF16, torch.float8_e4m3fn: E4M3, torch.float8_e5m2: E5M2}
+
+
+class GemmArgs(C.Structure):
+    _fields_ = [
+        ("A", C.c_void_p), ("B", C.c_void_p), ("a_dtype", C.c_int), ("b_dtype", C.c_int),
+        ("trans_a", C.c_int), ("trans_b", C.c_int),
+        ("M", C.c_int64), ("N", C.c_int64), ("K", C.c_int64), ("lda", C.c_int64), ("ldb", C.c_int64),
+        ("batch", C.c_int64), ("a_batch_stride", C.c_int64), ("b_batch_stride", C.c_int64),
+        ("out_batch_stride", C.c_int64),
+        ("out", C.c_void_p), ("out_dtype", C.c_int), ("ldo", C.c_int64),
+        ("a_scale", C.c_void_p), ("a_scale_host", C.c_float), ("a_scale_mode", C.c_int),
+        ("b_scale", C.c_void_p), ("b_scale_host", C.c_float), ("b_scale_mode", C.c_int),
+        ("bias", C.c_void_p), ("bias_dtype", C.c_int), ("bias_mode", C.c_int),
+        ("bias_ld", C.c_int64), ("bias_batch_stride", C.c_int64),
+        ("D", C.c_void_p), ("d_dtype", C.c_int), ("ldd", C.c_int64), ("d_batch_stride", C.c_int64),
+        ("force_generic", C.c_int), ("stream", C.c_void_p),
+    ]
+
+
+def _bind():
+    lib = C.CDLL(_LIB_PATH, mode=C.RTLD_GLOBAL)
+    lib.b200q_strerror.restype = C.c_char_p
+    lib.b200q_strerror.argtypes = [C.c_int]
+    lib.b200q_last_cuda_error.restype = C.c_char_p
+    lib.b200q_device_status.argtypes = [C.POINTER(C.c_int)]
+    lib.b200q_launch_count.restype = C.c_uint64
+    lib.b200q_cast_to_fp8.argtypes = [C.c_void_p, C.c_int, C.c_void_p, C.c_int, C.c_void_p, C.c_float, C.c_int,
+                                      C.c_int64, C.c_int64, C.c_void_p, C.c_int, C.c_uint64, C.c_uint64, C.c_uint64,
+                                      C.c_int, C.c_void_p]
+    lib.b200q_cast_from_fp8.argtypes = [C.c_void_p, C.c_int, C.c_void_p, C.c_int, C.c_void_p, C.c_float, C.c_int,
+                                        C.c_int64, C.c_int64, C.c_void_p]
+    lib.b200q_dequant_int4.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p,
+                                       C.c_int64, C.c_int64, C.c_int64, C.c_int, C.c_void_p]
+    lib.b200q_fp8_gemm.argtypes = [C.POINTER(GemmArgs)]
+    lib.b200q_w4a16_gemm.argtypes = [C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int,
+                                     C.c_int64, C.c_int64, C.c_int64, C.c_int64, C.c_void_p, C.c_int, C.c_int64,
+                                     C.c_void_p]
+    lib.b200q_swiglu_cast_fp8.argtypes = [C.c_void_p, C.c_int64, C.c_void_p, C.c_int64, C.c_void_p, C.c_float,
+                                          C.c_int64, C.c_int64, C.c_void_p, C.c_void_p]
+    return lib
+
+
+lib = _bind()
+
+
+class B200QError(RuntimeError):
+    pass
+
+
+def check(rc: int, what: str = "b200q") -> None:
+    if rc != 0:
+        msg = lib.b200q_strerror(rc).decode()
+        if rc == -3:
+            msg += " -- " + lib.b200q_last_cuda_error().decode()
+        raise B200QError(f"{what}: {msg} ({rc})")
+
+
+def ptr(t):
+    return None if t is None else C.c_void_p(t.data_ptr())
+
+
+def stream_ptr():
+    return C.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def launch_count() -> int:
+    return int(lib.b200q_launch_count())
+
+
+def device_status() -> int:
+    """Synchronise and return the device status word (0 = every bounded wait completed)."""
+    code = C.c_int(0)
+    rc = lib.b200q_device_status(C.byref(code))
+    if rc not in (0, -5):
+        check(rc, "b200q_device_status")
+    return code.value
+
+
+def cast_to_fp8(x, out_dtype, scale=None, scale_mode=None, amax=False, stochastic=False, seed=1234, offset=0,
+                first_index=0, mul_in_fp32=False, rows=None, cols=None):
+    """Direct C-ABI call.  scale: None | float | fp32 CUDA tensor (mode inferred: 1 element ->
+    SCALAR_DEV, else `scale_mode` must be given).  Returns (out, amax or None)."""
+    assert x.is_cuda and x.is_contiguous()
+    out = torch.empty(x.shape, dtype=out_dtype, device=x.device)
+    am = torch.empty((), dtype=torch.float32, device=x.device) if amax else None
+    sdev, shost, mode = None, 1.0, BCAST_NONE
+    if isinstance(scale, (int, float)):
+        shost, mode = float(scale), BCAST_SCALAR_HOST
+    elif scale is not None:
+        sdev = scale
+        mode = scale_mode if scale_mode is not None else BCAST_SCALAR_DEV
+    if rows is None:
+        rows, cols = 1, x.numel()
+    check(lib.b200q_cast_to_fp8(ptr(x), DTYPE[x.dtype], ptr(out), DTYPE[out_dtype], ptr(sdev), shost, mode, rows, cols,
+                                ptr(am), ROUND_STOCHASTIC if stochastic else ROUND_RNE, seed, offset, first_index,
+                                CAST_MUL_IN_FP32 if mul_in_fp32 else 0, stream_ptr()), "b200q_cast_to_fp8")
+    return out, am
+
+
+def cast_from_fp8(x8, out_dtype, scale=None, scale_mode=None, rows=None, cols=None):
+    assert x8.is_cuda and x8.is_contiguous()
+    out = torch.empty(x8.shape, dtype=out_dtype, device=x8.device)
+    sdev, shost, mode = None, 1.0, BCAST_NONE
+    if isinstance(scale, (int, float)):
+        shost, mode = float(scale), BCAST_SCALAR_HOST
+    elif scale is not None:
+        sdev = scale
+        mode = scale_mode if scale_mode is not None else BCAST_SCALAR_DEV
+    if rows is None:
+        rows, cols = 1, x8.numel()
+    check(lib.b200q_cast_from_fp8(ptr(x8), DTYPE[x8.dtype], ptr(out), DTYPE[out_dtype], ptr(sdev), shost, mode, rows,
+                                  cols, stream_ptr()), "b200q_cast_from_fp8")
+    return out
+
+
+def fp8_gemm_nt(a8, b8, out_dtype=torch.bfloat16, a_scale=None, b_scale=None, bias=None, out=None,
+                force_generic=False):
+    """out[M][N] = a8[M][K] . b8[N][K]^T with scalar (float) a_scale, per-column fp32 CUDA b_scale [N]
+    (or float), optional per-column bias [N]: the projection-GEMM form, straight through the C ABI."""
+    M, K = a8.shape
+    N = b8.shape[0]
+    if out is None:
+        out = torch.empty((M, N), dtype=out_dtype, device=a8.device)
+    g = GemmArgs()
+    g.A, g.B = a8.data_ptr(), b8.data_ptr()
+    g.a_dtype, g.b_dtype = DTYPE[a8.dtype], DTYPE[b8.dtype]
+    g.trans_a, g.trans_b = 0, 1
+    g.M, g.N, g.K, g.lda, g.ldb = M, N, K, a8.stride(0), b8.stride(0)
+    g.batch = 1
+    g.out, g.out_dtype, g.ldo = out.data_ptr(), DTYPE[out.dtype], out.stride(0)
+    for name, s in (("a", a_scale), ("b", b_scale)):
+        if s is None:
+            setattr(g, name + "_scale_mode", BCAST_NONE)
+        elif isinstance(s, (int, float)):
+            setattr(g, name + "_scale_mode", BCAST_SCALAR_HOST)
+            setattr(g, name + "_scale_host", float(s))
+        else:
+            setattr(g, name + "_scale", s.data_ptr())
+            setattr(g, name + "_scale_mode", BCAST_SCALAR_DEV if s.numel() == 1 else BCAST_PER_COL)
+    if bias is not None:
+        g.bias, g.bias_dtype, g.bias_mode = bias.data_ptr(), DTYPE[bias.dtype], BCAST_PER_COL
+    g.force_generic = 1 if force_generic else 0
+    g.stream = torch.cuda.current_stream().cuda_stream
+    check(lib.b200q_fp8_gemm(C.byref(g)), "b200q_fp8_gemm")
+    return out

@@ -1,0 +1,177 @@
+// extern "C" entry points of libb200q: argument validation, dispatch, status reporting.
+#include <stdio.h>
+#include <string.h>
+
+#include "common.cuh"
+#include "gemm_common.cuh"
+
+namespace b200q {
+
+std::atomic<uint64_t> g_launches{0};
+static thread_local char t_cuda_error[256] = "";
+
+__device__ int g_device_status = 0;
+
+int record_cuda_error(cudaError_t e, const char* where) {
+  snprintf(t_cuda_error, sizeof(t_cuda_error), "%s: %s (%s)", where, cudaGetErrorName(e), cudaGetErrorString(e));
+  return B200Q_ERR_CUDA;
+}
+
+// The status word is a __device__ variable: in host code its name is only a handle, so the
+// device address is looked up once per device (with that device current) and cached.
+int* device_status_ptr() {
+  constexpr int kMaxDev = 64;
+  static std::atomic<int*> cache[kMaxDev];
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDev) return nullptr;
+  int* p = cache[dev].load(std::memory_order_acquire);
+  if (p) return p;
+  void* addr = nullptr;
+  cudaError_t e = cudaGetSymbolAddress(&addr, g_device_status);
+  if (e != cudaSuccess) {
+    record_cuda_error(e, "cudaGetSymbolAddress(g_device_status)");
+    return nullptr;
+  }
+  cache[dev].store(static_cast<int*>(addr), std::memory_order_release);
+  return static_cast<int*>(addr);
+}
+
+int cast_to_fp8_impl(const void*, int, void*, int, const float*, float, int, int64_t, int64_t, float*, int, uint64_t,
+                     uint64_t, uint64_t, int, cudaStream_t);
+int cast_from_fp8_impl(const void*, int, void*, int, const float*, float, int, int64_t, int64_t, cudaStream_t);
+int swiglu_cast_impl(const void*, int64_t, const void*, int64_t, void*, float, int64_t, int64_t, float*, cudaStream_t);
+int dequant_int4_impl(const int32_t*, const void*, const void*, int, int, int, void*, int64_t, int64_t, int64_t, int,
+                      cudaStream_t);
+int w4a16_gemm_impl(const void*, int64_t, const int32_t*, const void*, const int32_t*, int, int, int64_t, int64_t,
+                    int64_t, int64_t, void*, int, int64_t, cudaStream_t);
+
+static bool is_fp8(int d) { return d == B200Q_E4M3 || d == B200Q_E5M2; }
+static bool is_wide(int d) { return d == B200Q_F32 || d == B200Q_BF16; }
+static bool scale_args_ok(const float* dev, int mode) {
+  if (mode < B200Q_BCAST_NONE || mode > B200Q_BCAST_FULL) return false;
+  if (mode >= B200Q_BCAST_SCALAR_DEV && !dev) return false;
+  return true;
+}
+
+}  // namespace b200q
+
+using namespace b200q;
+
+extern "C" {
+
+const char* b200q_strerror(int status) {
+  switch (status) {
+    case B200Q_OK: return "ok";
+    case B200Q_ERR_BAD_ARGUMENT: return "bad argument (null pointer, negative size or unknown enum value)";
+    case B200Q_ERR_UNSUPPORTED: return "argument combination not supported by this build";
+    case B200Q_ERR_CUDA: return "CUDA call failed (see b200q_last_cuda_error)";
+    case B200Q_ERR_TOO_LARGE: return "size beyond the documented maximum";
+    case B200Q_ERR_DEVICE_TIMEOUT: return "a bounded wait inside a kernel ran out";
+    default: return "unknown b200q status";
+  }
+}
+
+const char* b200q_last_cuda_error(void) { return t_cuda_error; }
+
+uint64_t b200q_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
+
+int b200q_device_status(int* code_out) {
+  int* p = device_status_ptr();
+  if (!p) return B200Q_ERR_CUDA;
+  B200Q_CUDA_OK(cudaDeviceSynchronize());
+  int code = 0;
+  B200Q_CUDA_OK(cudaMemcpy(&code, p, sizeof(int), cudaMemcpyDeviceToHost));
+  if (code != 0) {
+    int zero = 0;
+    B200Q_CUDA_OK(cudaMemcpy(p, &zero, sizeof(int), cudaMemcpyHostToDevice));
+  }
+  if (code_out) *code_out = code;
+  return code == 0 ? B200Q_OK : B200Q_ERR_DEVICE_TIMEOUT;
+}
+
+int b200q_cast_to_fp8(const void* in, int in_dtype, void* out, int out_dtype, const float* scale, float scale_host,
+                      int scale_mode, int64_t rows, int64_t cols, float* amax, int rounding, uint64_t seed,
+                      uint64_t offset, uint64_t first_index, int flags, void* stream) {
+  if (rows < 0 || cols < 0) return B200Q_ERR_BAD_ARGUMENT;
+  if (rows * cols > 0 && (!in || !out)) return B200Q_ERR_BAD_ARGUMENT;
+  if (!is_fp8(out_dtype) || !(is_wide(in_dtype) || is_fp8(in_dtype))) return B200Q_ERR_BAD_ARGUMENT;
+  if (!scale_args_ok(scale, scale_mode)) return B200Q_ERR_BAD_ARGUMENT;
+  if (rounding != B200Q_ROUND_RNE && rounding != B200Q_ROUND_STOCHASTIC) return B200Q_ERR_BAD_ARGUMENT;
+  return cast_to_fp8_impl(in, in_dtype, out, out_dtype, scale, scale_host, scale_mode, rows, cols, amax, rounding,
+                          seed, offset, first_index, flags, static_cast<cudaStream_t>(stream));
+}
+
+int b200q_cast_from_fp8(const void* in, int in_dtype, void* out, int out_dtype, const float* scale, float scale_host,
+                        int scale_mode, int64_t rows, int64_t cols, void* stream) {
+  if (rows < 0 || cols < 0) return B200Q_ERR_BAD_ARGUMENT;
+  if (rows * cols > 0 && (!in || !out)) return B200Q_ERR_BAD_ARGUMENT;
+  if (!is_fp8(in_dtype) || !is_wide(out_dtype)) return B200Q_ERR_BAD_ARGUMENT;
+  if (!scale_args_ok(scale, scale_mode)) return B200Q_ERR_BAD_ARGUMENT;
+  return cast_from_fp8_impl(in, in_dtype, out, out_dtype, scale, scale_host, scale_mode, rows, cols,
+                            static_cast<cudaStream_t>(stream));
+}
+
+int b200q_swiglu_cast_fp8(const void* gate, int64_t ld_gate, const void* up, int64_t ld_up, void* out,
+                          float scale_host, int64_t rows, int64_t cols, float* amax, void* stream) {
+  if (rows < 0 || cols < 0 || ld_gate < cols || ld_up < cols) return B200Q_ERR_BAD_ARGUMENT;
+  if (rows * cols > 0 && (!gate || !up || !out)) return B200Q_ERR_BAD_ARGUMENT;
+  return swiglu_cast_impl(gate, ld_gate, up, ld_up, out, scale_host, rows, cols, amax,
+                          static_cast<cudaStream_t>(stream));
+}
+
+int b200q_dequant_int4(const int32_t* packed, const void* scale, const void* zp, int zp_kind, int is_signed,
+                       int out_dtype, void* out, int64_t rows, int64_t cols_packed, int64_t scale_rows, int k_packed,
+                       void* stream) {
+  if (rows < 0 || cols_packed < 0) return B200Q_ERR_BAD_ARGUMENT;
+  if (rows * cols_packed > 0 && (!packed || !scale || !out)) return B200Q_ERR_BAD_ARGUMENT;
+  if (!is_wide(out_dtype)) return B200Q_ERR_BAD_ARGUMENT;
+  if (zp_kind < B200Q_ZP_NONE || zp_kind > B200Q_ZP_FLOAT) return B200Q_ERR_BAD_ARGUMENT;
+  if (zp_kind != B200Q_ZP_NONE && !zp && rows * cols_packed > 0) return B200Q_ERR_BAD_ARGUMENT;
+  return dequant_int4_impl(packed, scale, zp, zp_kind, is_signed, out_dtype, out, rows, cols_packed, scale_rows,
+                           k_packed, static_cast<cudaStream_t>(stream));
+}
+
+int b200q_fp8_gemm(const b200q_gemm_args* a) {
+  if (!a) return B200Q_ERR_BAD_ARGUMENT;
+  if (a->M < 0 || a->N < 0 || a->K < 0 || a->batch < 0) return B200Q_ERR_BAD_ARGUMENT;
+  if (!is_fp8(a->a_dtype) || !is_fp8(a->b_dtype) || !is_wide(a->out_dtype)) return B200Q_ERR_BAD_ARGUMENT;
+  if (!scale_args_ok(a->a_scale, a->a_scale_mode) || !scale_args_ok(a->b_scale, a->b_scale_mode))
+    return B200Q_ERR_BAD_ARGUMENT;
+  if (a->bias_mode < B200Q_BCAST_NONE || a->bias_mode > B200Q_BCAST_FULL || a->bias_mode == B200Q_BCAST_SCALAR_HOST)
+    return B200Q_ERR_BAD_ARGUMENT;
+  if (a->bias_mode != B200Q_BCAST_NONE && (!a->bias || !is_wide(a->bias_dtype))) return B200Q_ERR_BAD_ARGUMENT;
+  if (a->D && !is_wide(a->d_dtype)) return B200Q_ERR_BAD_ARGUMENT;
+  const int64_t work = a->M * a->N * a->batch;
+  if (work == 0) return B200Q_OK;
+  if (!a->out || (a->K > 0 && (!a->A || !a->B))) return B200Q_ERR_BAD_ARGUMENT;
+  GemmParams g;
+  g.A = a->A; g.B = a->B; g.a_dtype = a->a_dtype; g.b_dtype = a->b_dtype; g.trans_a = a->trans_a; g.trans_b = a->trans_b;
+  g.M = a->M; g.N = a->N; g.K = a->K; g.lda = a->lda; g.ldb = a->ldb;
+  g.batch = a->batch; g.a_batch_stride = a->a_batch_stride; g.b_batch_stride = a->b_batch_stride;
+  g.out_batch_stride = a->out_batch_stride; g.out = a->out; g.out_dtype = a->out_dtype; g.ldo = a->ldo;
+  g.a_scale = a->a_scale; g.a_scale_host = a->a_scale_host; g.a_scale_mode = a->a_scale_mode;
+  g.b_scale = a->b_scale; g.b_scale_host = a->b_scale_host; g.b_scale_mode = a->b_scale_mode;
+  g.bias = a->bias; g.bias_dtype = a->bias_dtype; g.bias_mode = a->bias_mode; g.bias_ld = a->bias_ld;
+  g.bias_batch_stride = a->bias_batch_stride; g.D = a->D; g.d_dtype = a->d_dtype; g.ldd = a->ldd;
+  g.d_batch_stride = a->d_batch_stride;
+  cudaStream_t st = static_cast<cudaStream_t>(a->stream);
+  if (!a->force_generic) {
+    int rc = gemm_tcgen05_launch(g, st);
+    if (rc != B200Q_ERR_UNSUPPORTED) return rc;
+  }
+  return gemm_generic_launch(g, st);
+}
+
+int b200q_w4a16_gemm(const void* x, int64_t ldx, const int32_t* qweight, const void* scale, const int32_t* zp,
+                     int zp_kind, int k_packed, int64_t M, int64_t N, int64_t K, int64_t group, void* out,
+                     int out_dtype, int64_t ldo, void* stream) {
+  if (M < 0 || N < 0 || K < 0 || group <= 0) return B200Q_ERR_BAD_ARGUMENT;
+  if (M * N == 0) return B200Q_OK;
+  if (!x || !qweight || !scale || !out || !is_wide(out_dtype)) return B200Q_ERR_BAD_ARGUMENT;
+  if (zp_kind != B200Q_ZP_NONE && zp_kind != B200Q_ZP_PACKED) return B200Q_ERR_UNSUPPORTED;
+  if (zp_kind == B200Q_ZP_PACKED && !zp) return B200Q_ERR_BAD_ARGUMENT;
+  return w4a16_gemm_impl(x, ldx, qweight, scale, zp, zp_kind, k_packed, M, N, K, group, out, out_dtype, ldo,
+                         static_cast<cudaStream_t>(stream));
+}
+
+}  // extern "C"

@@ -1,0 +1,433 @@
+// cast_to_fp8 / cast_from_fp8 / swiglu_cast_fp8: single-pass, HBM-bound kernels.
+//
+// Each thread moves 16 elements per step with 128-bit loads and stores; the amax of
+// the unscaled input is folded into the same pass (integer max on the |x| bit pattern,
+// warp shuffle, shared memory, one atomicMax per block).
+#include "common.cuh"
+
+namespace b200q {
+
+enum ScaleClass { SC_ONE = 0, SC_COL = 1, SC_ROW = 2, SC_FULL = 3 };
+
+struct CastParams {
+  const void* in;
+  void* out;
+  const float* scale;  // device scale (SCALAR_DEV / PER_COL / PER_ROW / FULL) or null
+  float scale_host;
+  int has_scale;       // 0: no multiply at all
+  int scale_from_dev;  // SC_ONE only: read scale[0]
+  int64_t n, cols;
+  float* amax;
+  uint64_t seed, offset, first_index;
+  int mul_fp32;
+};
+
+template <typename T>
+struct InTraits;
+template <>
+struct InTraits<float> {
+  static constexpr bool kIsBf16 = false;
+};
+template <>
+struct InTraits<__nv_bfloat16> {
+  static constexpr bool kIsBf16 = true;
+};
+
+// Product in the input dtype (bf16: scale and product both rounded to bf16) or in fp32.
+template <bool BF16>
+__device__ __forceinline__ float scaled(float x, float s, float s_in_dtype, int mul_fp32) {
+  if (BF16 && !mul_fp32) return round_to_bf16(x * s_in_dtype);
+  return x * s;
+}
+
+template <int FMT>
+__device__ __forceinline__ float clampf(float v) {
+  // fminf/fmaxf drop NaN; NaN bytes are patched by the caller from the unclamped value.
+  return fminf(fmaxf(v, -Fp8Fmt<FMT>::kMax), Fp8Fmt<FMT>::kMax);
+}
+
+// Every NaN becomes the canonical byte 0x7F in both formats (the sign of a NaN that went
+// through a multiply differs between CPUs and GPUs, so it is not carried).
+template <int FMT>
+__device__ __forceinline__ uint32_t nan_byte(float) {
+  return 0x7Fu;
+}
+
+template <typename InT, int FMT, bool SR, int SC>
+__global__ void __launch_bounds__(256) cast_to_fp8_kernel(CastParams p) {
+  constexpr bool BF16 = InTraits<InT>::kIsBf16;
+  const InT* __restrict__ in = static_cast<const InT*>(p.in);
+  uint8_t* __restrict__ out = static_cast<uint8_t*>(p.out);
+  const int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const int64_t nthreads = (int64_t)gridDim.x * blockDim.x;
+
+  float s_one = 1.f;
+  if (SC == SC_ONE && p.has_scale) s_one = p.scale_from_dev ? __ldg(p.scale) : p.scale_host;
+  const float s_one_in = BF16 ? round_to_bf16(s_one) : s_one;
+  const bool aligned = ((reinterpret_cast<uintptr_t>(in) | reinterpret_cast<uintptr_t>(out)) & 15) == 0 &&
+                       ((SC != SC_FULL && SC != SC_COL) || (reinterpret_cast<uintptr_t>(p.scale) & 15) == 0);
+  const bool col_vec = (SC != SC_COL && SC != SC_ROW) || (p.cols % 16 == 0);
+  const int64_t nvec = (aligned && col_vec) ? p.n / 16 : 0;
+  uint32_t amax_bits = 0;
+
+  for (int64_t v = tid; v < nvec; v += nthreads) {
+    const int64_t base = v * 16;
+    float x[16];
+    if (BF16) {
+      const uint4* src = reinterpret_cast<const uint4*>(in + base);
+      uint4 a = __ldcs(src), b = __ldcs(src + 1);
+      uint32_t w[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        x[2 * i] = __uint_as_float(w[i] << 16);
+        x[2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u);
+      }
+    } else {
+      const float4* src = reinterpret_cast<const float4*>(in + base);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        float4 f = __ldcs(src + i);
+        x[4 * i] = f.x; x[4 * i + 1] = f.y; x[4 * i + 2] = f.z; x[4 * i + 3] = f.w;
+      }
+    }
+    if (p.amax) {
+#pragma unroll
+      for (int i = 0; i < 16; ++i) amax_bits = max(amax_bits, __float_as_uint(x[i]) & 0x7FFFFFFFu);
+    }
+    float s[16];
+    if (SC == SC_COL) {
+      const float4* sp = reinterpret_cast<const float4*>(p.scale + (base % p.cols));
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        float4 f = __ldg(sp + i);
+        s[4 * i] = f.x; s[4 * i + 1] = f.y; s[4 * i + 2] = f.z; s[4 * i + 3] = f.w;
+      }
+    } else if (SC == SC_FULL) {
+      const float4* sp = reinterpret_cast<const float4*>(p.scale + base);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        float4 f = __ldcs(sp + i);
+        s[4 * i] = f.x; s[4 * i + 1] = f.y; s[4 * i + 2] = f.z; s[4 * i + 3] = f.w;
+      }
+    } else {
+      float sv = (SC == SC_ROW) ? __ldg(p.scale + base / p.cols) : s_one;
+#pragma unroll
+      for (int i = 0; i < 16; ++i) s[i] = sv;
+    }
+    float y[16];
+    bool any_nan = false;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      float si = (SC == SC_ONE) ? s_one_in : (BF16 ? round_to_bf16(s[i]) : s[i]);
+      y[i] = p.has_scale ? scaled<BF16>(x[i], s[i], si, p.mul_fp32) : x[i];
+      any_nan |= (y[i] != y[i]);
+    }
+    uint32_t o[4];
+    if (SR) {
+      const uint64_t g = p.first_index + (uint64_t)base;  // multiple of 4 only if first_index is
+      float z[16];
+      if ((p.first_index & 3) == 0) {
+#pragma unroll
+        for (int q = 0; q < 4; ++q) {
+          uint4 r = philox4x32_10((g >> 2) + q, p.seed, p.offset);
+          z[4 * q + 0] = sr_round<FMT>(clampf<FMT>(y[4 * q + 0]), r.x);
+          z[4 * q + 1] = sr_round<FMT>(clampf<FMT>(y[4 * q + 1]), r.y);
+          z[4 * q + 2] = sr_round<FMT>(clampf<FMT>(y[4 * q + 2]), r.z);
+          z[4 * q + 3] = sr_round<FMT>(clampf<FMT>(y[4 * q + 3]), r.w);
+        }
+      } else {
+#pragma unroll 1
+        for (int i = 0; i < 16; ++i) {
+          uint64_t gi = g + i;
+          uint4 r = philox4x32_10(gi >> 2, p.seed, p.offset);
+          uint32_t rr = (gi & 3) == 0 ? r.x : (gi & 3) == 1 ? r.y : (gi & 3) == 2 ? r.z : r.w;
+          z[i] = sr_round<FMT>(clampf<FMT>(y[i]), rr);
+        }
+      }
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+        o[i] = cvt_fp8x2<FMT>(z[4 * i], z[4 * i + 1]) | (cvt_fp8x2<FMT>(z[4 * i + 2], z[4 * i + 3]) << 16);
+    } else {
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+        o[i] = cvt_fp8x2<FMT>(clampf<FMT>(y[4 * i]), clampf<FMT>(y[4 * i + 1])) |
+               (cvt_fp8x2<FMT>(clampf<FMT>(y[4 * i + 2]), clampf<FMT>(y[4 * i + 3])) << 16);
+    }
+    if (any_nan) {
+#pragma unroll
+      for (int i = 0; i < 16; ++i)
+        if (y[i] != y[i]) {
+          uint32_t sh = (i & 3) * 8;
+          o[i >> 2] = (o[i >> 2] & ~(0xFFu << sh)) | (nan_byte<FMT>(y[i]) << sh);
+        }
+    }
+    __stcs(reinterpret_cast<uint4*>(out + base), make_uint4(o[0], o[1], o[2], o[3]));
+  }
+
+  // scalar path: the tail, or everything when the fast path's alignment rules do not hold
+  for (int64_t i = nvec * 16 + tid; i < p.n; i += nthreads) {
+    float x = BF16 ? __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(in)[i])
+                   : reinterpret_cast<const float*>(in)[i];
+    if (p.amax) amax_bits = max(amax_bits, __float_as_uint(x) & 0x7FFFFFFFu);
+    float y = x;
+    if (p.has_scale) {
+      float s = SC == SC_ONE ? s_one : SC == SC_COL ? p.scale[i % p.cols] : SC == SC_ROW ? p.scale[i / p.cols]
+                                                                                       : p.scale[i];
+      y = scaled<BF16>(x, s, BF16 ? round_to_bf16(s) : s, p.mul_fp32);
+    }
+    float z = clampf<FMT>(y);
+    if (SR) {
+      uint64_t gi = p.first_index + (uint64_t)i;
+      uint4 r = philox4x32_10(gi >> 2, p.seed, p.offset);
+      uint32_t rr = (gi & 3) == 0 ? r.x : (gi & 3) == 1 ? r.y : (gi & 3) == 2 ? r.z : r.w;
+      z = sr_round<FMT>(z, rr);
+    }
+    uint32_t b = cvt_fp8x2<FMT>(z, 0.f) & 0xFFu;
+    if (y != y) b = nan_byte<FMT>(y);
+    out[i] = (uint8_t)b;
+  }
+
+  if (p.amax) block_amax_to_global(amax_bits, p.amax);
+}
+
+// ------------------------------------------------------------------ cast_from_fp8
+struct UncastParams {
+  const uint8_t* in;
+  void* out;
+  const float* scale;
+  float scale_host;
+  int has_scale, scale_from_dev;
+  int64_t n, cols;
+};
+
+template <typename OutT, int FMT, int SC>
+__global__ void __launch_bounds__(256) cast_from_fp8_kernel(UncastParams p) {
+  constexpr bool BF16 = InTraits<OutT>::kIsBf16;
+  const int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const int64_t nthreads = (int64_t)gridDim.x * blockDim.x;
+  OutT* __restrict__ out = static_cast<OutT*>(p.out);
+  float s_one = 1.f;
+  if (SC == SC_ONE && p.has_scale) s_one = p.scale_from_dev ? __ldg(p.scale) : p.scale_host;
+  if (BF16) s_one = round_to_bf16(s_one);
+  const bool aligned = ((reinterpret_cast<uintptr_t>(p.in) | reinterpret_cast<uintptr_t>(out)) & 15) == 0 &&
+                       ((SC != SC_FULL && SC != SC_COL) || (reinterpret_cast<uintptr_t>(p.scale) & 15) == 0);
+  const bool col_vec = (SC != SC_COL && SC != SC_ROW) || (p.cols % 16 == 0);
+  const int64_t nvec = (aligned && col_vec) ? p.n / 16 : 0;
+
+  for (int64_t v = tid; v < nvec; v += nthreads) {
+    const int64_t base = v * 16;
+    uint4 raw = __ldcs(reinterpret_cast<const uint4*>(p.in + base));
+    uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+    float y[16];
+#pragma unroll
+    for (int i = 0; i < 16; ++i) y[i] = fp8_to_float<FMT>((w[i >> 2] >> ((i & 3) * 8)) & 0xFFu);
+    if (p.has_scale) {
+      if (SC == SC_COL || SC == SC_FULL) {
+        const float4* sp = reinterpret_cast<const float4*>(p.scale + (SC == SC_COL ? base % p.cols : base));
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          float4 f = __ldg(sp + i);
+          float s4[4] = {f.x, f.y, f.z, f.w};
+#pragma unroll
+          for (int j = 0; j < 4; ++j) y[4 * i + j] *= BF16 ? round_to_bf16(s4[j]) : s4[j];
+        }
+      } else {
+        float sv = s_one;
+        if (SC == SC_ROW) {
+          sv = __ldg(p.scale + base / p.cols);
+          if (BF16) sv = round_to_bf16(sv);
+        }
+#pragma unroll
+        for (int i = 0; i < 16; ++i) y[i] *= sv;
+      }
+    }
+    if (BF16) {
+      uint4 o0 = make_uint4(pack_bf16x2(y[0], y[1]), pack_bf16x2(y[2], y[3]), pack_bf16x2(y[4], y[5]),
+                            pack_bf16x2(y[6], y[7]));
+      uint4 o1 = make_uint4(pack_bf16x2(y[8], y[9]), pack_bf16x2(y[10], y[11]), pack_bf16x2(y[12], y[13]),
+                            pack_bf16x2(y[14], y[15]));
+      uint4* dst = reinterpret_cast<uint4*>(out + base);
+      __stcs(dst, o0);
+      __stcs(dst + 1, o1);
+    } else {
+      float4* dst = reinterpret_cast<float4*>(out + base);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) __stcs(dst + i, make_float4(y[4 * i], y[4 * i + 1], y[4 * i + 2], y[4 * i + 3]));
+    }
+  }
+  for (int64_t i = nvec * 16 + tid; i < p.n; i += nthreads) {
+    float y = fp8_to_float<FMT>(p.in[i]);
+    if (p.has_scale) {
+      float s = SC == SC_ONE ? s_one : SC == SC_COL ? p.scale[i % p.cols] : SC == SC_ROW ? p.scale[i / p.cols]
+                                                                                       : p.scale[i];
+      if (BF16 && SC != SC_ONE) s = round_to_bf16(s);
+      y *= s;
+    }
+    if (BF16) reinterpret_cast<__nv_bfloat16*>(out)[i] = __float2bfloat16_rn(y);
+    else reinterpret_cast<float*>(out)[i] = y;
+  }
+}
+
+// ------------------------------------------------------------------ swiglu + cast
+struct SwigluParams {
+  const __nv_bfloat16* gate;
+  const __nv_bfloat16* up;
+  uint8_t* out;
+  int64_t ld_gate, ld_up, rows, cols;
+  float scale;
+  float* amax;
+};
+
+__device__ __forceinline__ float silu_mul_bf16(float g, float u) {
+  // silu in fp32, product rounded once to bf16 (the dtype the unfused graph would hold)
+  float s = g / (1.f + expf(-g));
+  return round_to_bf16(s * u);
+}
+
+__global__ void __launch_bounds__(256) swiglu_cast_kernel(SwigluParams p) {
+  const int64_t vec_per_row = p.cols / 16;
+  const int64_t nvec = p.rows * vec_per_row;
+  const int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const int64_t nthreads = (int64_t)gridDim.x * blockDim.x;
+  const float s_in = round_to_bf16(p.scale);
+  uint32_t amax_bits = 0;
+  for (int64_t v = tid; v < nvec; v += nthreads) {
+    const int64_t r = v / vec_per_row, c = (v % vec_per_row) * 16;
+    const uint4* gp = reinterpret_cast<const uint4*>(p.gate + r * p.ld_gate + c);
+    const uint4* upp = reinterpret_cast<const uint4*>(p.up + r * p.ld_up + c);
+    uint4 g0 = __ldcs(gp), g1 = __ldcs(gp + 1), u0 = __ldcs(upp), u1 = __ldcs(upp + 1);
+    uint32_t gw[8] = {g0.x, g0.y, g0.z, g0.w, g1.x, g1.y, g1.z, g1.w};
+    uint32_t uw[8] = {u0.x, u0.y, u0.z, u0.w, u1.x, u1.y, u1.z, u1.w};
+    float y[16];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      float h0 = silu_mul_bf16(__uint_as_float(gw[i] << 16), __uint_as_float(uw[i] << 16));
+      float h1 = silu_mul_bf16(__uint_as_float(gw[i] & 0xFFFF0000u), __uint_as_float(uw[i] & 0xFFFF0000u));
+      amax_bits = max(amax_bits, max(__float_as_uint(h0), __float_as_uint(h1)) & 0x7FFFFFFFu);
+      y[2 * i] = round_to_bf16(h0 * s_in);
+      y[2 * i + 1] = round_to_bf16(h1 * s_in);
+    }
+    uint32_t o[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i)
+      o[i] = cvt_fp8x2<B200Q_E4M3>(clampf<B200Q_E4M3>(y[4 * i]), clampf<B200Q_E4M3>(y[4 * i + 1])) |
+             (cvt_fp8x2<B200Q_E4M3>(clampf<B200Q_E4M3>(y[4 * i + 2]), clampf<B200Q_E4M3>(y[4 * i + 3])) << 16);
+    __stcs(reinterpret_cast<uint4*>(p.out + r * p.cols + c), make_uint4(o[0], o[1], o[2], o[3]));
+  }
+  if (p.amax) block_amax_to_global(amax_bits, p.amax);
+}
+
+// ------------------------------------------------------------------ host launchers
+static int grid_for(int64_t n_items) {
+  int64_t blocks = (n_items + 255) / 256;
+  int64_t cap = (int64_t)kNumSMs * 8;  // 2048 resident threads per SM
+  if (blocks > cap) blocks = cap;
+  if (blocks < 1) blocks = 1;
+  return (int)blocks;
+}
+
+template <typename InT, int FMT, bool SR>
+static void launch_cast_sc(int sc, int grid, cudaStream_t st, const CastParams& p) {
+  switch (sc) {
+    case SC_ONE: cast_to_fp8_kernel<InT, FMT, SR, SC_ONE><<<grid, 256, 0, st>>>(p); break;
+    case SC_COL: cast_to_fp8_kernel<InT, FMT, SR, SC_COL><<<grid, 256, 0, st>>>(p); break;
+    case SC_ROW: cast_to_fp8_kernel<InT, FMT, SR, SC_ROW><<<grid, 256, 0, st>>>(p); break;
+    default: cast_to_fp8_kernel<InT, FMT, SR, SC_FULL><<<grid, 256, 0, st>>>(p); break;
+  }
+}
+
+template <typename InT, int FMT>
+static void launch_cast_sr(bool sr, int sc, int grid, cudaStream_t st, const CastParams& p) {
+  if (sr) launch_cast_sc<InT, FMT, true>(sc, grid, st, p);
+  else launch_cast_sc<InT, FMT, false>(sc, grid, st, p);
+}
+
+static int scale_class(int mode) {
+  switch (mode) {
+    case B200Q_BCAST_PER_COL: return SC_COL;
+    case B200Q_BCAST_PER_ROW: return SC_ROW;
+    case B200Q_BCAST_FULL: return SC_FULL;
+    default: return SC_ONE;
+  }
+}
+
+int cast_to_fp8_impl(const void* in, int in_dtype, void* out, int out_dtype, const float* scale,
+                     float scale_host, int scale_mode, int64_t rows, int64_t cols, float* amax, int rounding,
+                     uint64_t seed, uint64_t offset, uint64_t first_index, int flags, cudaStream_t st) {
+  const int64_t n = rows * cols;
+  if (in_dtype == B200Q_E4M3 || in_dtype == B200Q_E5M2) {
+    if (out_dtype != in_dtype || amax) return B200Q_ERR_BAD_ARGUMENT;
+    if (n) B200Q_CUDA_OK(cudaMemcpyAsync(out, in, (size_t)n, cudaMemcpyDeviceToDevice, st));
+    return B200Q_OK;
+  }
+  if (amax) B200Q_CUDA_OK(cudaMemsetAsync(amax, 0, sizeof(float), st));
+  if (n == 0) return B200Q_OK;
+  CastParams p;
+  p.in = in; p.out = out; p.scale = scale; p.scale_host = scale_host;
+  p.has_scale = scale_mode != B200Q_BCAST_NONE;
+  p.scale_from_dev = scale_mode == B200Q_BCAST_SCALAR_DEV;
+  p.n = n; p.cols = cols; p.amax = amax; p.seed = seed; p.offset = offset; p.first_index = first_index;
+  p.mul_fp32 = (flags & B200Q_CAST_MUL_IN_FP32) ? 1 : 0;
+  const int sc = scale_class(scale_mode);
+  const int grid = grid_for((n + 15) / 16);
+  const bool sr = rounding == B200Q_ROUND_STOCHASTIC;
+  if (in_dtype == B200Q_BF16) {
+    if (out_dtype == B200Q_E4M3) launch_cast_sr<__nv_bfloat16, B200Q_E4M3>(sr, sc, grid, st, p);
+    else launch_cast_sr<__nv_bfloat16, B200Q_E5M2>(sr, sc, grid, st, p);
+  } else {
+    if (out_dtype == B200Q_E4M3) launch_cast_sr<float, B200Q_E4M3>(sr, sc, grid, st, p);
+    else launch_cast_sr<float, B200Q_E5M2>(sr, sc, grid, st, p);
+  }
+  B200Q_LAUNCH_CHECK();
+  return B200Q_OK;
+}
+
+template <typename OutT, int FMT>
+static void launch_uncast_sc(int sc, int grid, cudaStream_t st, const UncastParams& p) {
+  switch (sc) {
+    case SC_ONE: cast_from_fp8_kernel<OutT, FMT, SC_ONE><<<grid, 256, 0, st>>>(p); break;
+    case SC_COL: cast_from_fp8_kernel<OutT, FMT, SC_COL><<<grid, 256, 0, st>>>(p); break;
+    case SC_ROW: cast_from_fp8_kernel<OutT, FMT, SC_ROW><<<grid, 256, 0, st>>>(p); break;
+    default: cast_from_fp8_kernel<OutT, FMT, SC_FULL><<<grid, 256, 0, st>>>(p); break;
+  }
+}
+
+int cast_from_fp8_impl(const void* in, int in_dtype, void* out, int out_dtype, const float* scale,
+                       float scale_host, int scale_mode, int64_t rows, int64_t cols, cudaStream_t st) {
+  const int64_t n = rows * cols;
+  if (n == 0) return B200Q_OK;
+  UncastParams p;
+  p.in = static_cast<const uint8_t*>(in); p.out = out; p.scale = scale; p.scale_host = scale_host;
+  p.has_scale = scale_mode != B200Q_BCAST_NONE;
+  p.scale_from_dev = scale_mode == B200Q_BCAST_SCALAR_DEV;
+  p.n = n; p.cols = cols;
+  const int sc = scale_class(scale_mode);
+  const int grid = grid_for((n + 15) / 16);
+  if (out_dtype == B200Q_BF16) {
+    if (in_dtype == B200Q_E4M3) launch_uncast_sc<__nv_bfloat16, B200Q_E4M3>(sc, grid, st, p);
+    else launch_uncast_sc<__nv_bfloat16, B200Q_E5M2>(sc, grid, st, p);
+  } else {
+    if (in_dtype == B200Q_E4M3) launch_uncast_sc<float, B200Q_E4M3>(sc, grid, st, p);
+    else launch_uncast_sc<float, B200Q_E5M2>(sc, grid, st, p);
+  }
+  B200Q_LAUNCH_CHECK();
+  return B200Q_OK;
+}
+
+int swiglu_cast_impl(const void* gate, int64_t ld_gate, const void* up, int64_t ld_up, void* out, float scale,
+                     int64_t rows, int64_t cols, float* amax, cudaStream_t st) {
+  if (cols % 16 || ld_gate % 8 || ld_up % 8) return B200Q_ERR_UNSUPPORTED;
+  if (((reinterpret_cast<uintptr_t>(gate) | reinterpret_cast<uintptr_t>(up) | reinterpret_cast<uintptr_t>(out)) & 15))
+    return B200Q_ERR_UNSUPPORTED;
+  if (amax) B200Q_CUDA_OK(cudaMemsetAsync(amax, 0, sizeof(float), st));
+  if (rows * cols == 0) return B200Q_OK;
+  SwigluParams p;
+  p.gate = static_cast<const __nv_bfloat16*>(gate); p.up = static_cast<const __nv_bfloat16*>(up);
+  p.out = static_cast<uint8_t*>(out); p.ld_gate = ld_gate; p.ld_up = ld_up; p.rows = rows; p.cols = cols;
+  p.scale = scale; p.amax = amax;
+  swiglu_cast_kernel<<<grid_for(rows * cols / 16), 256, 0, st>>>(p);
+  B200Q_LAUNCH_CHECK();
+  return B200Q_OK;
+}
+
+}  // namespace b200q

@@ -1,0 +1,148 @@
+// Shared device/host helpers for the b200q kernels (sm_100a only).
+#pragma once
+
+#include <cuda_bf16.h>
+#include <cuda_fp8.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <atomic>
+
+#include "b200q.h"
+
+namespace b200q {
+
+constexpr int kNumSMs = 148;  // B200
+
+// ---- host-side bookkeeping (abi.cu owns the storage) ----
+extern std::atomic<uint64_t> g_launches;
+int record_cuda_error(cudaError_t e, const char* where);
+inline void count_launch() { g_launches.fetch_add(1, std::memory_order_relaxed); }
+
+#define B200Q_CUDA_OK(expr)                                                   \
+  do {                                                                        \
+    cudaError_t e__ = (expr);                                                 \
+    if (e__ != cudaSuccess) return ::b200q::record_cuda_error(e__, #expr);    \
+  } while (0)
+
+#define B200Q_LAUNCH_CHECK()                                                  \
+  do {                                                                        \
+    ::b200q::count_launch();                                                  \
+    cudaError_t e__ = cudaGetLastError();                                     \
+    if (e__ != cudaSuccess) return ::b200q::record_cuda_error(e__, "launch"); \
+  } while (0)
+
+// Device status word of the current device: 0 = fine; kernels with bounded waits write a
+// code here.  Returns null if its address cannot be obtained.
+int* device_status_ptr();
+
+// ---- small device helpers ----
+__device__ __forceinline__ float bf16_bits_to_float(uint32_t b16) { return __uint_as_float(b16 << 16); }
+
+__device__ __forceinline__ float round_to_bf16(float v) {
+  return __bfloat162float(__float2bfloat16_rn(v));
+}
+
+__device__ __forceinline__ uint32_t pack_bf16x2(float lo, float hi) {
+  __nv_bfloat162 p = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&p);
+}
+
+template <int FMT>
+struct Fp8Fmt;
+template <>
+struct Fp8Fmt<B200Q_E4M3> {
+  static constexpr float kMax = 448.f;
+  static constexpr int kMant = 3;
+  static constexpr int kEmin = 127 - 6;  // biased fp32 exponent of the smallest normal
+  static constexpr float kQuantum = 0.001953125f;  // 2^-9
+  static constexpr __nv_fp8_interpretation_t kInterp = __NV_E4M3;
+};
+template <>
+struct Fp8Fmt<B200Q_E5M2> {
+  static constexpr float kMax = 57344.f;
+  static constexpr int kMant = 2;
+  static constexpr int kEmin = 127 - 14;
+  static constexpr float kQuantum = 1.52587890625e-05f;  // 2^-16
+  static constexpr __nv_fp8_interpretation_t kInterp = __NV_E5M2;
+};
+
+// Two floats -> two fp8 bytes (a in the low byte), round half to even, saturating.
+template <int FMT>
+__device__ __forceinline__ uint32_t cvt_fp8x2(float a, float b) {
+  return (uint32_t)__nv_cvt_float2_to_fp8x2(make_float2(a, b), __NV_SATFINITE, Fp8Fmt<FMT>::kInterp);
+}
+
+template <int FMT>
+__device__ __forceinline__ float fp8_to_float(uint32_t byte) {
+  __half_raw h = __nv_cvt_fp8_to_halfraw((__nv_fp8_storage_t)byte, Fp8Fmt<FMT>::kInterp);
+  return __half2float(*reinterpret_cast<__half*>(&h));
+}
+
+// Philox4x32-10; counter = (block lo, block hi, offset lo, offset hi), key = seed.
+__device__ __forceinline__ uint4 philox4x32_10(uint64_t block, uint64_t seed, uint64_t offset) {
+  uint32_t c0 = (uint32_t)block, c1 = (uint32_t)(block >> 32);
+  uint32_t c2 = (uint32_t)offset, c3 = (uint32_t)(offset >> 32);
+  uint32_t k0 = (uint32_t)seed, k1 = (uint32_t)(seed >> 32);
+#pragma unroll
+  for (int r = 0; r < 10; ++r) {
+    uint32_t hi0 = __umulhi(0xD2511F53u, c0), lo0 = 0xD2511F53u * c0;
+    uint32_t hi1 = __umulhi(0xCD9E8D57u, c2), lo1 = 0xCD9E8D57u * c2;
+    uint32_t n0 = hi1 ^ c1 ^ k0, n2 = hi0 ^ c3 ^ k1;
+    c0 = n0; c1 = lo1; c2 = n2; c3 = lo0;
+    k0 += 0x9E3779B9u; k1 += 0xBB67AE85u;
+  }
+  return make_uint4(c0, c1, c2, c3);
+}
+
+// Stochastic rounding of an fp32 value (already clamped to +-max) to a float that the fp8
+// format represents exactly.  r is the element's 32-bit random word.
+template <int FMT>
+__device__ __forceinline__ float sr_round(float v, uint32_t r) {
+  constexpr int d = 23 - Fp8Fmt<FMT>::kMant;
+  uint32_t bits = __float_as_uint(v);
+  uint32_t sign = bits & 0x80000000u, mag = bits & 0x7FFFFFFFu;
+  int E = (int)(mag >> 23);
+  float res;
+  if (E >= Fp8Fmt<FMT>::kEmin) {
+    uint32_t m = (mag + (r & ((1u << d) - 1u))) & ~((1u << d) - 1u);
+    res = fminf(__uint_as_float(m), Fp8Fmt<FMT>::kMax);
+    if (mag > 0x7F800000u) res = __uint_as_float(mag);  // NaN stays NaN
+  } else {
+    int Ee = E > 0 ? E : 1;
+    uint32_t m = E > 0 ? ((mag & 0x7FFFFFu) | 0x800000u) : (mag & 0x7FFFFFu);
+    int s = d + (Fp8Fmt<FMT>::kEmin - Ee);
+    int extra = s > 32 ? s - 32 : 0;
+    if (extra > 31) { m = 0; extra = 0; }
+    m >>= extra;
+    int s2 = s > 32 ? 32 : s;
+    uint64_t mask = (s2 >= 32) ? 0xFFFFFFFFull : ((1ull << s2) - 1ull);
+    uint64_t t = ((uint64_t)m + ((uint64_t)r & mask)) >> s2;
+    res = (float)(uint32_t)t * Fp8Fmt<FMT>::kQuantum;
+  }
+  return __uint_as_float(__float_as_uint(res) | sign);
+}
+
+__device__ __forceinline__ uint32_t warp_max_u32(uint32_t v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = max(v, __shfl_xor_sync(0xFFFFFFFFu, v, o));
+  return v;
+}
+
+// Block-wide max of a non-negative float's bit pattern, then one atomicMax per block.
+// Works on bit patterns so that NaN (pattern above +inf) wins and is propagated.
+__device__ __forceinline__ void block_amax_to_global(uint32_t local_bits, float* amax) {
+  __shared__ uint32_t s_warp[32];
+  uint32_t w = warp_max_u32(local_bits);
+  int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+  if (lane == 0) s_warp[wid] = w;
+  __syncthreads();
+  if (wid == 0) {
+    int nw = (blockDim.x + 31) >> 5;
+    uint32_t v = lane < nw ? s_warp[lane] : 0u;
+    v = warp_max_u32(v);
+    if (lane == 0 && v != 0u) atomicMax(reinterpret_cast<unsigned int*>(amax), v);
+  }
+}
+
+}  // namespace b200q

@@ -1,0 +1,393 @@
+// FP8 GEMM on the 5th-generation tensor cores: out = (A[M][K] . B[N][K]^T) * scales + bias (+ D).
+//
+// Persistent, warp-specialised kernel, one CTA per SM:
+//   warp 0    TMA producer: 128-byte-swizzled K-major tiles of both operands into a
+//             shared-memory ring (no multicast), completion on "full" mbarriers
+//   warp 1    TMEM owner and MMA issuer: one thread issues tcgen05.mma.kind::f8f6f4
+//             (128 x BN x 32 per instruction), tcgen05.commit releases ring stages
+//             and publishes finished accumulators
+//   warps 2-5 epilogue: tcgen05.ld the fp32 accumulator (each warp its 32 TMEM lanes),
+//             apply (acc * sa) * sb + bias + D, round once, store
+// The accumulator is double-buffered in TMEM (2 x BN columns) so the epilogue of tile i
+// overlaps the main loop of tile i+1.
+//
+// SWAP = false: lanes <- rows of A (tokens), columns <- rows of B (output channels).
+// SWAP = true : lanes <- rows of B, columns <- rows of A: the small-M ("decode") form where
+//               the weight stream fills the 128-lane dimension and the few tokens ride N.
+#include <cuda.h>
+
+#include "common.cuh"
+#include "gemm_common.cuh"
+#include "tcgen05_ptx.cuh"
+
+namespace b200q {
+
+using namespace ptx;
+
+constexpr int kBlockX = 128;  // rows of the lane-side operand per tile (UMMA M)
+constexpr int kBlockK = 128;  // bytes (= fp8 elements) of K per ring stage: one swizzle row
+constexpr int kUmmaK = 32;
+constexpr int kThreads = 192;
+constexpr int kEpiThreads = 128;
+
+enum { kErrProducer = 101, kErrMma = 102, kErrMmaTmem = 103, kErrEpilogue = 104 };
+
+struct TcGemmParams {
+  GemmParams g;
+  int64_t x_rows, y_rows;  // extents of the lane-side / column-side operands
+  int x_tiles, y_tiles, num_kb;
+  int a_fmt_bits, b_fmt_bits;  // 0 = e4m3, 1 = e5m2 (lane-side, column-side)
+  int* status;                 // device status word (bounded waits report here)
+};
+
+template <int BN, int STAGES>
+struct SmemLayout {
+  static constexpr int kXBytes = kBlockX * kBlockK;
+  static constexpr int kYBytes = BN * kBlockK;
+  static constexpr int kStageBytes = kXBytes + kYBytes;
+  static constexpr int kRing = STAGES * kStageBytes;
+  static constexpr int kEpiFloats = 2 * 3 * BN;  // per accumulator: col scale A, col scale B, col bias
+  static constexpr int kBarOffset = kRing + kEpiFloats * 4;
+  static constexpr int kNumBars = 2 * STAGES + 4;
+  static constexpr int kTotal = kBarOffset + kNumBars * 8 + 16;
+};
+
+template <int BN, int STAGES, bool SWAP>
+__global__ void __launch_bounds__(kThreads, 1)
+gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_y,
+                    const TcGemmParams p) {
+  using L = SmemLayout<BN, STAGES>;
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  // dynamic shared memory is only guaranteed 16-byte aligned: round up to the swizzle atom
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  float* epi_f = reinterpret_cast<float*>(smem + L::kRing);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::kBarOffset);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + L::kNumBars);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  volatile int* epi_stop = reinterpret_cast<volatile int*>(tmem_slot + 2);
+
+  const uint32_t smem_base = smem_u32(smem);
+  const uint32_t bar_full = smem_u32(bars), bar_empty = bar_full + 8 * STAGES;
+  const uint32_t bar_tfull = bar_empty + 8 * STAGES, bar_tempty = bar_tfull + 16;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  constexpr uint32_t kTmemCols = (2 * BN) < 32 ? 32 : 2 * BN;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(bar_full + 8 * s, 1);
+      mbar_init(bar_empty + 8 * s, 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(bar_tfull + 8 * a, 1);
+      mbar_init(bar_tempty + 8 * a, kEpiThreads);
+    }
+    *abort_flag = 0;
+    *epi_stop = 0;
+    fence_barrier_init();
+    tma_prefetch_desc(&map_x);
+    tma_prefetch_desc(&map_y);
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(tmem_slot), kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const int num_tiles = p.x_tiles * p.y_tiles;
+  const int num_kb = p.num_kb;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      uint32_t stage = 0, phase = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        const int xt = tile % p.x_tiles, yt = tile / p.x_tiles;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(bar_empty + 8 * stage, phase ^ 1, abort_flag, p.status, kErrProducer)) {
+            ok = false;
+            break;
+          }
+          const uint32_t full = bar_full + 8 * stage;
+          mbar_arrive_expect_tx(full, L::kStageBytes);
+          tma_load_2d(smem_base + stage * L::kStageBytes, &map_x, full, kb * kBlockK, xt * kBlockX);
+          tma_load_2d(smem_base + stage * L::kStageBytes + L::kXBytes, &map_y, full, kb * kBlockK, yt * BN);
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      const uint32_t idesc = umma_idesc(p.a_fmt_bits, p.b_fmt_bits, kBlockX, BN);
+      uint32_t stage = 0, phase = 0;
+      int it = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++it) {
+        const uint32_t acc = it & 1, acc_phase = (it >> 1) & 1;
+        if (!mbar_wait(bar_tempty + 8 * acc, acc_phase ^ 1, abort_flag, p.status, kErrMmaTmem)) break;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(bar_full + 8 * stage, phase, abort_flag, p.status, kErrMma)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t xs = smem_base + stage * L::kStageBytes, ys = xs + L::kXBytes;
+#pragma unroll
+          for (int k = 0; k < kBlockK / kUmmaK; ++k) {
+            umma_f8(d_tmem, smem_desc_k_sw128(xs + k * kUmmaK), smem_desc_k_sw128(ys + k * kUmmaK), idesc,
+                    (kb | k) != 0);
+          }
+          umma_commit(bar_empty + 8 * stage);  // stage reusable once these MMAs have read it
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+        if (ok) umma_commit(bar_tfull + 8 * acc);  // accumulator complete
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue (warps 2..5)
+    const GemmParams& g = p.g;
+    const int q = warp & 3;              // TMEM lane quarter this warp may read
+    const int et = threadIdx.x - 64;     // 0..127
+    int it = 0;
+    for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++it) {
+      const int xt = tile % p.x_tiles, yt = tile / p.x_tiles;
+      const uint32_t acc = it & 1, acc_phase = (it >> 1) & 1;
+      const int64_t x0 = (int64_t)xt * kBlockX, y0 = (int64_t)yt * BN;
+      // column-side (per-y) epilogue operands for this tile -> shared memory
+      float* cA = epi_f + acc * 3 * BN;
+      float* cB = cA + BN;
+      float* cBias = cB + BN;
+      // which output dimension the columns are: n (normal) or m (swapped)
+      const int col_mode = SWAP ? B200Q_BCAST_PER_ROW : B200Q_BCAST_PER_COL;
+      const int row_mode = SWAP ? B200Q_BCAST_PER_COL : B200Q_BCAST_PER_ROW;
+      for (int c = et; c < BN; c += kEpiThreads) {
+        const int64_t y = y0 + c;
+        const bool in = y < p.y_rows;
+        cA[c] = (g.a_scale_mode == col_mode && in) ? __ldg(g.a_scale + y) : 1.f;
+        cB[c] = (g.b_scale_mode == col_mode && in) ? __ldg(g.b_scale + y) : 1.f;
+        cBias[c] = (g.bias_mode == col_mode && in) ? ld_out_typed(g.bias, g.bias_dtype, y) : 0.f;
+      }
+      const int64_t x = x0 + q * 32 + lane;  // this thread's lane-side index
+      const bool x_in = x < p.x_rows;
+      float rA = 1.f, rB = 1.f, rBias = 0.f;
+      if (g.a_scale_mode == B200Q_BCAST_SCALAR_HOST) rA = g.a_scale_host;
+      else if (g.a_scale_mode == B200Q_BCAST_SCALAR_DEV) rA = __ldg(g.a_scale);
+      else if (g.a_scale_mode == row_mode && x_in) rA = __ldg(g.a_scale + x);
+      if (g.b_scale_mode == B200Q_BCAST_SCALAR_HOST) rB = g.b_scale_host;
+      else if (g.b_scale_mode == B200Q_BCAST_SCALAR_DEV) rB = __ldg(g.b_scale);
+      else if (g.b_scale_mode == row_mode && x_in) rB = __ldg(g.b_scale + x);
+      if (g.bias_mode == row_mode && x_in) rBias = ld_out_typed(g.bias, g.bias_dtype, x);
+      // The wait can give up for some threads only; the decision to stop must be the same for
+      // all 128 epilogue threads because they meet at named barriers: one thread samples the
+      // abort flag between two barriers and everybody follows that sample.
+      mbar_wait(bar_tfull + 8 * acc, acc_phase, abort_flag, p.status, kErrEpilogue);
+      named_bar_sync(1, kEpiThreads);
+      if (et == 0) *epi_stop = *abort_flag;
+      named_bar_sync(1, kEpiThreads);
+      if (*epi_stop) break;
+      tc_fence_after();
+      const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16) + acc * BN;
+      const bool full_extra = g.bias_mode == B200Q_BCAST_FULL || g.D != nullptr;
+
+#pragma unroll 1
+      for (int c0 = 0; c0 < BN; c0 += 32) {
+        uint32_t r[32];
+        if (BN % 32 == 0) {
+          tmem_ld_32x32(t_row + c0, r);
+        } else {
+          tmem_ld_32x16(t_row + c0, r);  // BN == 16
+        }
+        tmem_ld_wait();
+        constexpr int CW = (BN % 32 == 0) ? 32 : 16;
+        float v[CW];
+#pragma unroll
+        for (int j = 0; j < CW; ++j) {
+          float a = __uint_as_float(r[j]);
+          a = a * (rA * cA[c0 + j]);
+          a = a * (rB * cB[c0 + j]);
+          v[j] = a + (rBias + cBias[c0 + j]);
+        }
+        if (!SWAP) {
+          // thread = output row m, registers = CW consecutive output columns n
+          const int64_t m = x, n0 = y0 + c0;
+          if (x_in) {
+            if (full_extra) {
+#pragma unroll
+              for (int j = 0; j < CW; ++j) {
+                const int64_t n = n0 + j;
+                if (n < g.N) {
+                  if (g.bias_mode == B200Q_BCAST_FULL) v[j] += ld_out_typed(g.bias, g.bias_dtype, m * g.bias_ld + n);
+                  if (g.D) v[j] += ld_out_typed(g.D, g.d_dtype, m * g.ldd + n);
+                }
+              }
+            }
+            if (g.out_dtype == B200Q_BF16) {
+              __nv_bfloat16* o = static_cast<__nv_bfloat16*>(g.out) + m * g.ldo + n0;
+              if (n0 + CW <= g.N && (reinterpret_cast<uintptr_t>(o) & 15) == 0) {
+#pragma unroll
+                for (int j = 0; j < CW; j += 8)
+                  *reinterpret_cast<uint4*>(o + j) =
+                      make_uint4(pack_bf16x2(v[j], v[j + 1]), pack_bf16x2(v[j + 2], v[j + 3]),
+                                 pack_bf16x2(v[j + 4], v[j + 5]), pack_bf16x2(v[j + 6], v[j + 7]));
+              } else {
+#pragma unroll
+                for (int j = 0; j < CW; ++j)
+                  if (n0 + j < g.N) o[j] = __float2bfloat16_rn(v[j]);
+              }
+            } else {
+              float* o = static_cast<float*>(g.out) + m * g.ldo + n0;
+              if (n0 + CW <= g.N && (reinterpret_cast<uintptr_t>(o) & 15) == 0) {
+#pragma unroll
+                for (int j = 0; j < CW; j += 4)
+                  *reinterpret_cast<float4*>(o + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+              } else {
+#pragma unroll
+                for (int j = 0; j < CW; ++j)
+                  if (n0 + j < g.N) o[j] = v[j];
+              }
+            }
+          }
+        } else {
+          // thread = output column n (weight row), registers = CW consecutive tokens m
+          const int64_t n = x;
+          if (x_in) {
+#pragma unroll
+            for (int j = 0; j < CW; ++j) {
+              const int64_t m = y0 + c0 + j;
+              if (m < g.M) {
+                float o = v[j];
+                if (g.bias_mode == B200Q_BCAST_FULL) o += ld_out_typed(g.bias, g.bias_dtype, m * g.bias_ld + n);
+                if (g.D) o += ld_out_typed(g.D, g.d_dtype, m * g.ldd + n);
+                if (g.out_dtype == B200Q_BF16) static_cast<__nv_bfloat16*>(g.out)[m * g.ldo + n] = __float2bfloat16_rn(o);
+                else static_cast<float*>(g.out)[m * g.ldo + n] = o;
+              }
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      mbar_arrive(bar_tempty + 8 * acc);
+    }
+  }
+
+  // ---------------------------------------------------------------- teardown
+  __syncwarp();  // lanes 1..31 of the single-thread roles rejoin lane 0 here
+  tc_fence_before();
+  __syncthreads();
+  if (*abort_flag) {
+    // a bounded wait ran out: give copies that are still in flight time to land before the
+    // shared memory and TMEM are released
+    for (int i = 0; i < 200; ++i) __nanosleep(1000);
+    __syncthreads();
+  }
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+// ------------------------------------------------------------------------ host side
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::atomic<int> tried{0};
+  if (!tried.load(std::memory_order_acquire)) {
+    void* sym = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(sym);
+    tried.store(1, std::memory_order_release);
+  }
+  return fn;
+}
+
+// 2-D map over a row-major byte matrix [rows][kbytes] with row stride ld bytes; box = 128 bytes x box_rows.
+int make_operand_map(CUtensorMap* map, const void* base, int64_t rows, int64_t kbytes, int64_t ld_bytes,
+                     int box_rows) {
+  EncodeTiledFn enc = get_encode_fn();
+  if (!enc) return B200Q_ERR_CUDA;
+  cuuint64_t dims[2] = {(cuuint64_t)kbytes, (cuuint64_t)rows};
+  cuuint64_t strides[1] = {(cuuint64_t)ld_bytes};
+  cuuint32_t box[2] = {(cuuint32_t)kBlockK, (cuuint32_t)box_rows};
+  cuuint32_t estr[2] = {1, 1};
+  CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? B200Q_OK : B200Q_ERR_CUDA;
+}
+
+template <int BN, int STAGES, bool SWAP>
+static int launch_cfg(const CUtensorMap& mx, const CUtensorMap& my, const TcGemmParams& tp, cudaStream_t st) {
+  using L = SmemLayout<BN, STAGES>;
+  constexpr int smem = L::kTotal + 1024;  // slack for the manual 1024-byte alignment
+  static_assert(smem <= 227 * 1024, "shared memory budget");
+  static_assert(smem > 116 * 1024, "one CTA per SM: two CTAs must never contend for TMEM");
+  auto kern = gemm_tcgen05_kernel<BN, STAGES, SWAP>;
+  B200Q_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+  int tiles = tp.x_tiles * tp.y_tiles;
+  int grid = tiles < kNumSMs ? tiles : kNumSMs;
+  kern<<<grid, kThreads, smem, st>>>(mx, my, tp);
+  B200Q_LAUNCH_CHECK();
+  return B200Q_OK;
+}
+
+static inline int fmt_bits(int dtype) { return dtype == B200Q_E5M2 ? 1 : 0; }
+
+int gemm_tcgen05_launch(const GemmParams& g, cudaStream_t st) {
+  // eligibility: both operands K-major, TMA-compatible strides and bases, one problem per launch
+  if (g.trans_a || !g.trans_b) return B200Q_ERR_UNSUPPORTED;
+  if (g.batch != 1 || g.K < 16 || (g.K % 16) || (g.lda % 16) || (g.ldb % 16)) return B200Q_ERR_UNSUPPORTED;
+  if ((reinterpret_cast<uintptr_t>(g.A) | reinterpret_cast<uintptr_t>(g.B)) & 15) return B200Q_ERR_UNSUPPORTED;
+  if (g.a_scale_mode == B200Q_BCAST_FULL || g.b_scale_mode == B200Q_BCAST_FULL) return B200Q_ERR_UNSUPPORTED;
+  if (g.M <= 0 || g.N <= 0) return B200Q_ERR_UNSUPPORTED;
+  if (g.M > (1ll << 30) || g.N > (1ll << 30) || g.K > (1ll << 30)) return B200Q_ERR_UNSUPPORTED;
+
+  TcGemmParams tp;
+  tp.g = g;
+  tp.status = device_status_ptr();
+  if (!tp.status) return B200Q_ERR_CUDA;
+  tp.num_kb = (int)((g.K + kBlockK - 1) / kBlockK);
+  const bool swap = g.M <= 128 && g.N >= 128;
+  CUtensorMap mx, my;
+  if (!swap) {
+    tp.x_rows = g.M; tp.y_rows = g.N;
+    tp.a_fmt_bits = fmt_bits(g.a_dtype); tp.b_fmt_bits = fmt_bits(g.b_dtype);
+    tp.x_tiles = (int)((g.M + kBlockX - 1) / kBlockX);
+    const int bn = g.N > 128 ? 256 : 128;
+    tp.y_tiles = (int)((g.N + bn - 1) / bn);
+    int rc = make_operand_map(&mx, g.A, g.M, g.K, g.lda, kBlockX);
+    if (rc) return rc;
+    rc = make_operand_map(&my, g.B, g.N, g.K, g.ldb, bn);
+    if (rc) return rc;
+    if (bn == 256) return launch_cfg<256, 4, false>(mx, my, tp, st);
+    return launch_cfg<128, 6, false>(mx, my, tp, st);
+  }
+  // small M: weights on the lanes, tokens on the columns
+  tp.x_rows = g.N; tp.y_rows = g.M;
+  tp.a_fmt_bits = fmt_bits(g.b_dtype); tp.b_fmt_bits = fmt_bits(g.a_dtype);
+  tp.x_tiles = (int)((g.N + kBlockX - 1) / kBlockX);
+  const int bn = g.M <= 16 ? 16 : g.M <= 32 ? 32 : g.M <= 64 ? 64 : 128;
+  tp.y_tiles = (int)((g.M + bn - 1) / bn);
+  int rc = make_operand_map(&mx, g.B, g.N, g.K, g.ldb, kBlockX);
+  if (rc) return rc;
+  rc = make_operand_map(&my, g.A, g.M, g.K, g.lda, bn);
+  if (rc) return rc;
+  switch (bn) {
+    case 16: return launch_cfg<16, 10, true>(mx, my, tp, st);
+    case 32: return launch_cfg<32, 9, true>(mx, my, tp, st);
+    case 64: return launch_cfg<64, 8, true>(mx, my, tp, st);
+    default: return launch_cfg<128, 6, true>(mx, my, tp, st);
+  }
+}
+
+}  // namespace b200q

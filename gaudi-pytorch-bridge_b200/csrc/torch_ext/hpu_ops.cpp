@@ -1,0 +1,728 @@
+// torch.ops.hpu.* for CUDA tensors on B200: the operator schemas of the reference
+// (habana_kernels/kernels_register.cpp:2427-2451, identical in
+// habana_eager/eager_custom_op_register.cpp:2146-2171) registered verbatim, with CUDA and
+// Meta implementations.  Argument checks and error strings follow
+// hpu_ops/backend/fp8_ops.cpp and hpu_ops/common/batched_matmul_output_shape.cpp; the
+// wrappers mirror habana_eager/eager_custom_op_register.cpp:59-322,1272-1306.  All device
+// work goes through the C ABI in b200q.h on the current CUDA stream; there is no fallback.
+#include <ATen/ATen.h>
+#include <c10/cuda/CUDAGuard.h>
+#include <c10/cuda/CUDAStream.h>
+#include <torch/library.h>
+
+#include <atomic>
+#include <cstdlib>
+#include <sstream>
+#include <variant>
+
+#include "b200q.h"
+
+namespace {
+
+using OptTensor = c10::optional<at::Tensor>;
+using OptShape = at::OptionalIntArrayRef;
+using ScaleArg = std::variant<std::monostate, at::Tensor, double, std::vector<double>>;
+
+// ---- process-wide knobs (out-of-band: the operator schemas have no argument for them) ----
+std::atomic<int64_t> g_sr_seed{[] {
+  const char* e = std::getenv("B200Q_SR_SEED");
+  return e ? std::atoll(e) : 1234ll;
+}()};
+std::atomic<int64_t> g_sr_offset{0};
+std::atomic<bool> g_mul_in_fp32{[] {
+  const char* e = std::getenv("B200Q_CAST_MUL_IN_FP32");
+  return e && e[0] == '1';
+}()};
+
+void check_status(int rc, const char* op) {
+  if (rc == B200Q_OK) return;
+  TORCH_CHECK(false, op, ": ", b200q_strerror(rc), rc == B200Q_ERR_CUDA ? std::string(" -- ") + b200q_last_cuda_error()
+                                                                        : std::string());
+}
+
+int to_b200q_dtype(at::ScalarType t) {
+  switch (t) {
+    case at::kFloat: return B200Q_F32;
+    case at::kBFloat16: return B200Q_BF16;
+    case at::kFloat8_e4m3fn: return B200Q_E4M3;
+    case at::kFloat8_e5m2: return B200Q_E5M2;
+    default: TORCH_CHECK(false, "unsupported dtype ", t); return -1;
+  }
+}
+bool is_fp8(at::ScalarType t) { return t == at::kFloat8_e5m2 || t == at::kFloat8_e4m3fn; }
+
+void* current_stream() { return static_cast<void*>(c10::cuda::getCurrentCUDAStream().stream()); }
+
+int64_t numel_of(c10::IntArrayRef s) {
+  int64_t n = 1;
+  for (auto d : s) n *= d;
+  return n;
+}
+
+// hpu_ops/backend/fp8_ops.cpp:29-53
+void validate_scale_shape(const ScaleArg& scale, OptShape scale_shape) {
+  if (!scale_shape.has_value()) return;
+  int64_t n = 0;
+  if (auto t = std::get_if<at::Tensor>(&scale)) n = t->numel();
+  else if (auto l = std::get_if<std::vector<double>>(&scale)) n = (int64_t)l->size();
+  else return;
+  int64_t m = numel_of(*scale_shape);
+  TORCH_CHECK(n == m, "Number of scale elements (", n, ") is not equal to number of scale_shape elements (", m, ").");
+}
+
+// A scale resolved against a [rows, cols] problem.
+struct ResolvedScale {
+  int mode = B200Q_BCAST_NONE;
+  float host = 1.f;
+  at::Tensor dev;  // fp32, contiguous, on the problem's device (keeps the storage alive)
+  const float* ptr() const { return dev.defined() ? dev.data_ptr<float>() : nullptr; }
+};
+
+// Scale as an fp32 tensor of its final shape (fp8_ops.cpp:63-96), or undefined for None/float.
+at::Tensor scale_tensor(const ScaleArg& scale, OptShape scale_shape, const at::Device& dev) {
+  if (auto t = std::get_if<at::Tensor>(&scale)) {
+    at::Tensor s = t->to(dev, at::kFloat);
+    if (s.numel() > 1 && scale_shape.has_value() && s.sizes() != *scale_shape) s = s.reshape(*scale_shape);
+    return s;
+  }
+  if (auto l = std::get_if<std::vector<double>>(&scale)) {
+    at::Tensor s = at::tensor(*l, at::TensorOptions().dtype(at::kDouble)).to(at::kFloat);
+    if (scale_shape.has_value()) s = s.reshape(*scale_shape);
+    return s.to(dev);
+  }
+  return at::Tensor();
+}
+
+// Classify how `s` (already of its final shape) broadcasts against `shape`; on return rows*cols ==
+// numel(shape) and the mode says how s lines up with that 2-D view.
+ResolvedScale classify_against(const at::Tensor& s_in, c10::IntArrayRef shape, int64_t* rows, int64_t* cols,
+                               const char* what) {
+  ResolvedScale r;
+  const int64_t n = numel_of(shape);
+  *rows = 1;
+  *cols = n;
+  at::Tensor s = s_in;
+  if (s.numel() == 1) {
+    r.mode = B200Q_BCAST_SCALAR_DEV;
+    r.dev = s.reshape({1}).contiguous();
+    return r;
+  }
+  const int64_t rank = (int64_t)shape.size();
+  TORCH_CHECK(s.dim() <= rank, what, " of shape ", s.sizes(), " does not broadcast against ", shape);
+  std::vector<int64_t> ss(rank, 1);
+  for (int64_t i = 0; i < s.dim(); ++i) ss[rank - s.dim() + i] = s.size(i);
+  for (int64_t i = 0; i < rank; ++i)
+    TORCH_CHECK(ss[i] == 1 || ss[i] == shape[i], what, " of shape ", s.sizes(), " does not broadcast against ", shape);
+  int64_t first_full = rank, last_full = -1;
+  bool all_full = true;
+  for (int64_t i = 0; i < rank; ++i) {
+    bool full = ss[i] == shape[i] && shape[i] != 1;
+    bool one = ss[i] == 1 && shape[i] != 1;
+    if (full) { first_full = std::min(first_full, i); last_full = std::max(last_full, i); }
+    if (one) all_full = false;
+  }
+  if (all_full) {
+    r.mode = B200Q_BCAST_FULL;
+    r.dev = s.contiguous();
+    return r;
+  }
+  // trailing block: ones before first_full, matches from first_full to the end
+  bool trailing = true, leading = true;
+  for (int64_t i = 0; i < rank; ++i) {
+    if (shape[i] == 1) continue;
+    bool full = ss[i] == shape[i];
+    if (i >= first_full && !full) trailing = false;
+    if (i <= last_full && !full) leading = false;
+  }
+  if (trailing && first_full < rank) {
+    *cols = 1;
+    for (int64_t i = first_full; i < rank; ++i) *cols *= shape[i];
+    *rows = n / *cols;
+    r.mode = B200Q_BCAST_PER_COL;
+    r.dev = s.contiguous().reshape({*cols});
+    return r;
+  }
+  if (leading && last_full >= 0) {
+    *rows = 1;
+    for (int64_t i = 0; i <= last_full; ++i) *rows *= shape[i];
+    *cols = n / *rows;
+    r.mode = B200Q_BCAST_PER_ROW;
+    r.dev = s.contiguous().reshape({*rows});
+    return r;
+  }
+  r.mode = B200Q_BCAST_FULL;  // mixed pattern: materialise
+  r.dev = s.reshape(ss).expand(shape).contiguous();
+  return r;
+}
+
+ResolvedScale resolve_cast_scale(const ScaleArg& scale, OptShape scale_shape, const at::Tensor& input, int64_t* rows,
+                                 int64_t* cols) {
+  validate_scale_shape(scale, scale_shape);
+  *rows = 1;
+  *cols = input.numel();
+  ResolvedScale r;
+  if (std::holds_alternative<std::monostate>(scale)) return r;
+  if (auto d = std::get_if<double>(&scale)) {
+    r.mode = B200Q_BCAST_SCALAR_HOST;
+    r.host = (float)*d;
+    return r;
+  }
+  return classify_against(scale_tensor(scale, scale_shape, input.device()), input.sizes(), rows, cols, "scale");
+}
+
+// ------------------------------------------------------------------ cast_to_fp8_v2
+std::tuple<at::Tensor, at::Tensor> cast_to_fp8_v2_common(const at::Tensor& input, const ScaleArg& scale,
+                                                         bool stochastic_rounding, bool is_amax, at::ScalarType dtype,
+                                                         OptShape scale_shape) {
+  const auto src = input.scalar_type();
+  const bool fp8_in = is_fp8(src);
+  TORCH_CHECK(fp8_in || src == at::kFloat || src == at::kBFloat16,
+              "CastToFp8V2 input dtype must be one of [float, bfloat16, float8_e5m2, float8_e4m3fn].");
+  if (fp8_in) {
+    TORCH_CHECK(!is_amax, "CastToFp8V2 must have no amax for float8.");
+    TORCH_CHECK(src == dtype, "CastToFp8V2 input and output must have the same dtype for float8, but are ", src,
+                " and ", dtype);
+  }
+  TORCH_CHECK(is_fp8(dtype), "CastToFp8V2 output dtype must be float8_e5m2 or float8_e4m3fn, got ", dtype);
+  c10::cuda::CUDAGuard guard(input.device());
+  at::Tensor in = input.contiguous();
+  int64_t rows, cols;
+  ResolvedScale s = resolve_cast_scale(scale, scale_shape, in, &rows, &cols);
+  at::Tensor out = at::empty(in.sizes(), in.options().dtype(dtype));
+  at::Tensor amax = is_amax ? at::empty({}, in.options().dtype(at::kFloat)) : at::empty({0}, in.options().dtype(at::kFloat));
+  uint64_t seed = (uint64_t)g_sr_seed.load(), offset = 0;
+  if (stochastic_rounding && !fp8_in) offset = (uint64_t)g_sr_offset.fetch_add(1);
+  int flags = g_mul_in_fp32.load() ? B200Q_CAST_MUL_IN_FP32 : 0;
+  check_status(b200q_cast_to_fp8(in.data_ptr(), to_b200q_dtype(src), out.data_ptr(), to_b200q_dtype(dtype), s.ptr(),
+                                 s.host, fp8_in ? B200Q_BCAST_NONE : s.mode, rows, cols,
+                                 is_amax ? amax.data_ptr<float>() : nullptr,
+                                 stochastic_rounding ? B200Q_ROUND_STOCHASTIC : B200Q_ROUND_RNE, seed, offset, 0, flags,
+                                 current_stream()),
+               "cast_to_fp8_v2");
+  return {out, amax};
+}
+
+std::tuple<at::Tensor, at::Tensor> cast_to_fp8_v2(const at::Tensor& input, const OptTensor& scale,
+                                                  bool stochastic_rounding, bool is_amax, at::ScalarType dtype,
+                                                  OptShape scale_shape) {
+  ScaleArg s;
+  if (scale.has_value() && scale->defined()) s = *scale;
+  return cast_to_fp8_v2_common(input, s, stochastic_rounding, is_amax, dtype, scale_shape);
+}
+std::tuple<at::Tensor, at::Tensor> cast_to_fp8_v2_scalar(const at::Tensor& input, double scale,
+                                                         bool stochastic_rounding, bool is_amax, at::ScalarType dtype,
+                                                         OptShape) {
+  return cast_to_fp8_v2_common(input, ScaleArg(scale), stochastic_rounding, is_amax, dtype, c10::nullopt);
+}
+std::tuple<at::Tensor, at::Tensor> cast_to_fp8_v2_scalar_list(const at::Tensor& input, c10::ArrayRef<double> scale,
+                                                              bool stochastic_rounding, bool is_amax,
+                                                              at::ScalarType dtype, OptShape scale_shape) {
+  return cast_to_fp8_v2_common(input, ScaleArg(scale.vec()), stochastic_rounding, is_amax, dtype, scale_shape);
+}
+
+// legacy out-variant (kernels_register.cpp:2427; fp8_ops.cpp:123-166)
+std::tuple<at::Tensor&, at::Tensor&> cast_to_fp8(const at::Tensor& input, const OptTensor& scale,
+                                                 bool stochastic_rounding, at::Tensor& out, at::Tensor& amax) {
+  const auto src = input.scalar_type();
+  TORCH_CHECK(src == at::kFloat || src == at::kBFloat16, "CastToFp8 input must be of float or bfloat16 dtype.");
+  TORCH_CHECK(input.sizes() == out.sizes(), "Input and output must have the same shape");
+  TORCH_CHECK(out.is_contiguous() && is_fp8(out.scalar_type()), "CastToFp8 out must be a contiguous float8 tensor");
+  auto r = cast_to_fp8_v2(input, scale, stochastic_rounding, amax.numel() != 0, out.scalar_type(), c10::nullopt);
+  out.copy_(std::get<0>(r));
+  if (amax.numel() != 0) amax.copy_(std::get<1>(r).reshape(amax.sizes()));
+  return {out, amax};
+}
+
+// ------------------------------------------------------------------ cast_from_fp8
+at::Tensor cast_from_fp8_common(const at::Tensor& input, const ScaleArg& scale, at::ScalarType out_dtype,
+                                OptShape scale_shape) {
+  validate_scale_shape(scale, scale_shape);
+  TORCH_CHECK(out_dtype == at::kFloat || out_dtype == at::kBFloat16,
+              "CastFromFp8 output dtype must be equal to float or bfloat16.");
+  TORCH_CHECK(is_fp8(input.scalar_type()), "CastFromFp8 input must be float8_e5m2 or float8_e4m3fn, got ",
+              input.scalar_type());
+  c10::cuda::CUDAGuard guard(input.device());
+  at::Tensor in = input.contiguous();
+  int64_t rows, cols;
+  ResolvedScale s = resolve_cast_scale(scale, scale_shape, in, &rows, &cols);
+  at::Tensor out = at::empty(in.sizes(), in.options().dtype(out_dtype));
+  check_status(b200q_cast_from_fp8(in.data_ptr(), to_b200q_dtype(in.scalar_type()), out.data_ptr(),
+                                   to_b200q_dtype(out_dtype), s.ptr(), s.host, s.mode, rows, cols, current_stream()),
+               "cast_from_fp8");
+  return out;
+}
+at::Tensor cast_from_fp8(const at::Tensor& input, const OptTensor& scale, at::ScalarType out_dtype,
+                         OptShape scale_shape) {
+  ScaleArg s;
+  if (scale.has_value() && scale->defined()) s = *scale;
+  return cast_from_fp8_common(input, s, out_dtype, scale_shape);
+}
+at::Tensor cast_from_fp8_scalar(const at::Tensor& input, double scale, at::ScalarType out_dtype, OptShape) {
+  return cast_from_fp8_common(input, ScaleArg(scale), out_dtype, c10::nullopt);
+}
+at::Tensor cast_from_fp8_scalar_list(const at::Tensor& input, c10::ArrayRef<double> scale, at::ScalarType out_dtype,
+                                     OptShape scale_shape) {
+  return cast_from_fp8_common(input, ScaleArg(scale.vec()), out_dtype, scale_shape);
+}
+
+// ------------------------------------------------------------------ convert_from_{int4,uint4}
+at::Tensor convert_from_4bit(const at::Tensor& input, const at::Tensor& scale, const OptTensor& zero_point,
+                             at::ScalarType out_dtype, bool is_signed) {
+  TORCH_CHECK(input.scalar_type() == at::kInt, "convert_from_int4 input must be int32 (8 packed nibbles per element)");
+  TORCH_CHECK(out_dtype == at::kFloat || out_dtype == at::kBFloat16,
+              "convert_from_int4 output dtype must be float or bfloat16, got ", out_dtype);
+  TORCH_CHECK(input.dim() >= 1, "convert_from_int4 input must have at least one dimension");
+  c10::cuda::CUDAGuard guard(input.device());
+  at::Tensor in = input.contiguous();
+  auto out_shape = in.sizes().vec();
+  out_shape.back() *= 8;
+  const int64_t cols_packed = in.size(-1), cols = cols_packed * 8;
+  const int64_t rows = cols_packed ? in.numel() / cols_packed : 0;
+  // scale: out_dtype, either the full output shape or [..., K/g, N]
+  at::Tensor sc = scale.to(in.device(), out_dtype).contiguous();
+  int64_t scale_rows = rows;
+  if (sc.sizes() != c10::IntArrayRef(out_shape)) {
+    bool grouped = sc.dim() == (int64_t)out_shape.size() && sc.dim() >= 2 && sc.size(-1) == cols &&
+                   sc.size(-2) > 0 && out_shape[out_shape.size() - 2] % sc.size(-2) == 0;
+    for (int64_t i = 0; grouped && i < sc.dim() - 2; ++i) grouped = sc.size(i) == out_shape[i];
+    if (grouped) scale_rows = sc.numel() / cols;
+    else {
+      sc = sc.expand(out_shape).contiguous();
+    }
+  }
+  int zp_kind = B200Q_ZP_NONE;
+  at::Tensor zp;
+  if (zero_point.has_value() && zero_point->defined()) {
+    if (zero_point->scalar_type() == at::kInt) {
+      zp_kind = B200Q_ZP_PACKED;
+      zp = zero_point->to(in.device()).contiguous();
+      TORCH_CHECK(zp.numel() == scale_rows * cols_packed, "packed zero_point must have the scale's shape with the last "
+                  "dimension divided by 8, got ", zp.sizes(), " for scale ", sc.sizes());
+    } else {
+      zp_kind = B200Q_ZP_FLOAT;
+      zp = zero_point->to(in.device(), out_dtype);
+      if (zp.numel() != scale_rows * cols) zp = zp.expand(sc.sizes());
+      zp = zp.contiguous();
+    }
+  }
+  at::Tensor out = at::empty(out_shape, in.options().dtype(out_dtype));
+  check_status(b200q_dequant_int4(in.data_ptr<int32_t>(), sc.data_ptr(), zp.defined() ? zp.data_ptr() : nullptr, zp_kind,
+                                  is_signed ? 1 : 0, to_b200q_dtype(out_dtype), out.data_ptr(), rows, cols_packed,
+                                  scale_rows, 0, current_stream()),
+               "convert_from_int4");
+  return out;
+}
+at::Tensor convert_from_int4(const at::Tensor& input, const at::Tensor& scale, const OptTensor& zp, at::ScalarType dt) {
+  return convert_from_4bit(input, scale, zp, dt, true);
+}
+at::Tensor convert_from_uint4(const at::Tensor& input, const at::Tensor& scale, const OptTensor& zp,
+                              at::ScalarType dt) {
+  return convert_from_4bit(input, scale, zp, dt, false);
+}
+
+// AutoGPTQ layout (packed along K) -> [K, N]; b200q namespace: not a reference operator.
+at::Tensor dequant_kpacked(const at::Tensor& qweight, const at::Tensor& scales, const OptTensor& qzeros,
+                           at::ScalarType out_dtype) {
+  TORCH_CHECK(qweight.dim() == 2 && qweight.scalar_type() == at::kInt, "qweight must be int32 [K/8, N]");
+  c10::cuda::CUDAGuard guard(qweight.device());
+  at::Tensor q = qweight.contiguous();
+  const int64_t K = q.size(0) * 8, N = q.size(1);
+  at::Tensor sc = scales.to(q.device(), out_dtype).contiguous();
+  TORCH_CHECK(sc.dim() == 2 && sc.size(1) == N && K % sc.size(0) == 0, "scales must be [K/g, N]");
+  at::Tensor zp;
+  int zp_kind = B200Q_ZP_NONE;
+  if (qzeros.has_value() && qzeros->defined()) {
+    zp = qzeros->contiguous();
+    TORCH_CHECK(zp.scalar_type() == at::kInt && zp.numel() == sc.size(0) * (N / 8), "qzeros must be int32 [K/g, N/8]");
+    zp_kind = B200Q_ZP_PACKED;
+  }
+  at::Tensor out = at::empty({K, N}, q.options().dtype(out_dtype));
+  check_status(b200q_dequant_int4(q.data_ptr<int32_t>(), sc.data_ptr(), zp.defined() ? zp.data_ptr() : nullptr, zp_kind, 0,
+                                  to_b200q_dtype(out_dtype), out.data_ptr(), K, N, sc.size(0), 1, current_stream()),
+               "dequant_kpacked");
+  return out;
+}
+
+// ------------------------------------------------------------------ fp8_gemm_v2
+// hpu_ops/common/batched_matmul_output_shape.cpp:34-88
+std::vector<int64_t> matmul_out_shape(c10::IntArrayRef a, c10::IntArrayRef b, bool ta, bool tb) {
+  std::vector<int64_t> out;
+  const size_t ra = a.size(), rb = b.size();
+  TORCH_CHECK(ra >= 1 && rb >= 1, "matmul inputs must have at least one dimension");
+  size_t ca = 0, cb = 0;
+  if (rb > 1) {
+    out.push_back(b[tb ? rb - 2 : rb - 1]);
+    cb = tb ? rb - 1 : rb - 2;
+  }
+  if (ra > 1) {
+    out.push_back(a[ta ? ra - 1 : ra - 2]);
+    ca = ta ? ra - 2 : ra - 1;
+  }
+  TORCH_CHECK(a[ca] == b[cb], "Common dimension sizes of matmul inputs should be the same. Got ", a[ca], " and ", b[cb]);
+  const size_t mr = std::max(ra, rb);
+  for (size_t i = 3; i <= mr; ++i) {
+    int64_t da = i > ra ? 1 : a[ra - i], db = i > rb ? 1 : b[rb - i];
+    TORCH_CHECK(da == db || da == 1 || db == 1, "Batch dimension ", mr - i,
+                " of matmul inputs should be the same or at least one of them should be equal to 1. Got ", da, " and ",
+                db);
+    out.push_back(da == db ? da : da * db);
+  }
+  std::reverse(out.begin(), out.end());
+  return out;
+}
+
+struct EpiOperand {
+  int mode = B200Q_BCAST_NONE;
+  float host = 1.f;
+  at::Tensor t;
+  int64_t ld = 0, batch_stride = 0;
+};
+
+// Line a scale / bias tensor up with the output, seen canonically as bshape + [M, N]
+// (has_m / has_n say whether the output really has those dimensions: 1-D operands drop them).
+EpiOperand classify_epi(const at::Tensor& t_in, c10::IntArrayRef bshape, int64_t M, int64_t N, bool has_m, bool has_n,
+                        c10::IntArrayRef out_shape, bool want_float, const char* what) {
+  EpiOperand e;
+  at::Tensor t = want_float ? t_in.to(at::kFloat) : t_in;
+  if (t.numel() == 1) {
+    e.mode = B200Q_BCAST_SCALAR_DEV;
+    e.t = t.reshape({1}).contiguous();
+    return e;
+  }
+  const int64_t orank = (int64_t)out_shape.size();
+  TORCH_CHECK(t.dim() <= orank, what, " of shape ", t.sizes(), " does not broadcast against the output ", out_shape);
+  // right-align with the output, then insert the dropped M / N dimensions as size 1
+  std::vector<int64_t> ts(orank, 1);
+  for (int64_t i = 0; i < t.dim(); ++i) ts[orank - t.dim() + i] = t.size(i);
+  for (int64_t i = 0; i < orank; ++i)
+    TORCH_CHECK(ts[i] == 1 || ts[i] == out_shape[i], what, " of shape ", t.sizes(),
+                " does not broadcast against the output ", out_shape);
+  std::vector<int64_t> can(ts.begin(), ts.begin() + (int64_t)bshape.size());
+  int64_t pos = (int64_t)bshape.size();
+  can.push_back(has_m ? ts[pos++] : 1);
+  can.push_back(has_n ? ts[pos++] : 1);
+  bool batch_ones = true;
+  for (size_t i = 0; i < bshape.size(); ++i) batch_ones = batch_ones && can[i] == 1;
+  const int64_t tm = can[can.size() - 2], tn = can[can.size() - 1];
+  if (batch_ones && tm == 1 && tn == N) {
+    e.mode = B200Q_BCAST_PER_COL;
+    e.t = t.reshape({N}).contiguous();
+    return e;
+  }
+  if (batch_ones && tn == 1 && tm == M) {
+    e.mode = B200Q_BCAST_PER_ROW;
+    e.t = t.reshape({M}).contiguous();
+    return e;
+  }
+  std::vector<int64_t> full(bshape.begin(), bshape.end());
+  full.push_back(M);
+  full.push_back(N);
+  int64_t batch = numel_of(bshape);
+  e.mode = B200Q_BCAST_FULL;
+  e.t = t.reshape(can).expand(full).contiguous().reshape({batch, M, N});
+  e.ld = N;
+  e.batch_stride = M * N;
+  return e;
+}
+
+ScaleArg to_scale_arg(const OptTensor& t) {
+  ScaleArg s;
+  if (t.has_value() && t->defined()) s = *t;
+  return s;
+}
+
+at::Tensor fp8_gemm_v2_common(const at::Tensor& A, bool trans_A, const at::Tensor& B, bool trans_B, const OptTensor& D,
+                              at::ScalarType out_dtype, const ScaleArg& A_scale_inv, const ScaleArg& B_scale_inv,
+                              const OptTensor& bias, bool accumulate, OptShape B_scale_shape) {
+  TORCH_CHECK(is_fp8(A.scalar_type()) && is_fp8(B.scalar_type()), "fp8_gemm_v2 inputs must be float8 tensors, got ",
+              A.scalar_type(), " and ", B.scalar_type());
+  TORCH_CHECK(out_dtype == at::kFloat || out_dtype == at::kBFloat16,
+              "fp8_gemm_v2 output dtype must be float or bfloat16, got ", out_dtype);
+  validate_scale_shape(B_scale_inv, B_scale_shape);
+  const bool has_D = D.has_value() && D->defined();
+  TORCH_CHECK(!accumulate || has_D,
+              "Accumulation tensor must be provided at index 4 for Fp8GemmV2, when accumulate is true");
+  const std::vector<int64_t> out_shape = matmul_out_shape(A.sizes(), B.sizes(), trans_A, trans_B);
+  c10::cuda::CUDAGuard guard(A.device());
+
+  // 2-D (or batched 3-D) operand views; 1-D operands become a row / a column
+  at::Tensor a = A, b = B;
+  bool ta = trans_A, tb = trans_B;
+  const bool has_m = A.dim() > 1, has_n = B.dim() > 1;
+  if (a.dim() == 1) { a = a.unsqueeze(0); ta = false; }
+  if (b.dim() == 1) { b = b.unsqueeze(1); tb = false; }
+  const int64_t M = ta ? a.size(-1) : a.size(-2), K = ta ? a.size(-2) : a.size(-1);
+  const int64_t N = tb ? b.size(-2) : b.size(-1);
+  // batch dims
+  std::vector<int64_t> bshape;
+  {
+    auto ab = a.sizes().slice(0, a.dim() - 2), bb = b.sizes().slice(0, b.dim() - 2);
+    bshape = at::infer_size(ab, bb);
+  }
+  int64_t batch = numel_of(bshape);
+  at::Tensor out = at::empty(out_shape, A.options().dtype(out_dtype));
+  if (out.numel() == 0) return out;
+
+  b200q_gemm_args g{};
+  int64_t Mk = M;  // M as the kernel sees it (batch may be folded in)
+  bool folded = false;
+  if (batch > 1 && b.dim() == 2 && !ta) {
+    // [.., M, K] x [K, N]: fold the batch into M
+    a = a.contiguous().reshape({batch * M, K});
+    Mk = batch * M;
+    folded = true;
+  } else if (batch > 1 || a.dim() > 2 || b.dim() > 2) {
+    std::vector<int64_t> as = bshape, bs = bshape;
+    as.push_back(a.size(-2)); as.push_back(a.size(-1));
+    bs.push_back(b.size(-2)); bs.push_back(b.size(-1));
+    a = a.expand(as).contiguous().reshape({batch, a.size(-2), a.size(-1)});
+    b = b.expand(bs).contiguous().reshape({batch, b.size(-2), b.size(-1)});
+  }
+  auto as_matrix = [](at::Tensor& t) {
+    // row-major with unit inner stride (a transposed view counts as a copy here)
+    if (t.stride(-1) != 1 || (t.dim() >= 2 && t.size(-2) > 1 && t.stride(-2) < t.size(-1))) t = t.contiguous();
+  };
+  as_matrix(a);
+  as_matrix(b);
+  const int64_t kbatch = folded ? 1 : batch;
+  g.A = a.data_ptr(); g.B = b.data_ptr();
+  g.a_dtype = to_b200q_dtype(a.scalar_type()); g.b_dtype = to_b200q_dtype(b.scalar_type());
+  g.trans_a = ta; g.trans_b = tb; g.M = Mk; g.N = N; g.K = K;
+  g.lda = a.size(-2) > 1 ? a.stride(-2) : a.size(-1);
+  g.ldb = b.size(-2) > 1 ? b.stride(-2) : b.size(-1);
+  g.batch = kbatch;
+  g.a_batch_stride = a.dim() == 3 ? a.stride(0) : 0;
+  g.b_batch_stride = b.dim() == 3 ? b.stride(0) : 0;
+  g.out_batch_stride = M * N;
+  g.out = out.data_ptr(); g.out_dtype = to_b200q_dtype(out_dtype); g.ldo = N;
+
+  // epilogue operands are classified against the un-folded output, then adapted if folded
+  std::vector<at::Tensor> keep;
+  auto setup_scale = [&](const ScaleArg& s, OptShape shape, const float** dev, float* host, int* mode) {
+    *mode = B200Q_BCAST_NONE; *dev = nullptr; *host = 1.f;
+    if (std::holds_alternative<std::monostate>(s)) return;
+    if (auto d = std::get_if<double>(&s)) { *mode = B200Q_BCAST_SCALAR_HOST; *host = (float)*d; return; }
+    at::Tensor t = scale_tensor(s, shape, A.device());
+    EpiOperand e = classify_epi(t, bshape, M, N, has_m, has_n, out_shape, true, "scale");
+    if (folded && e.mode == B200Q_BCAST_PER_ROW) e.t = e.t.repeat({batch});
+    if (e.mode == B200Q_BCAST_FULL) {
+      TORCH_CHECK(folded || batch == 1, "fp8_gemm_v2: an element-wise scale with batched operands is not supported");
+    }
+    keep.push_back(e.t);
+    *dev = e.t.data_ptr<float>(); *mode = e.mode;
+  };
+  setup_scale(A_scale_inv, c10::nullopt, &g.a_scale, &g.a_scale_host, &g.a_scale_mode);
+  setup_scale(B_scale_inv, B_scale_shape, &g.b_scale, &g.b_scale_host, &g.b_scale_mode);
+  if (bias.has_value() && bias->defined()) {
+    at::Tensor bt = bias->to(A.device());
+    if (bt.scalar_type() != at::kFloat && bt.scalar_type() != at::kBFloat16) bt = bt.to(at::kFloat);
+    EpiOperand e = classify_epi(bt, bshape, M, N, has_m, has_n, out_shape, false, "bias");
+    if (e.mode == B200Q_BCAST_SCALAR_DEV) {  // one value: treat as a per-column vector
+      e.t = e.t.expand({N}).contiguous();
+      e.mode = B200Q_BCAST_PER_COL;
+    }
+    if (folded && e.mode == B200Q_BCAST_PER_ROW) e.t = e.t.repeat({batch});
+    keep.push_back(e.t);
+    g.bias = e.t.data_ptr(); g.bias_dtype = to_b200q_dtype(e.t.scalar_type()); g.bias_mode = e.mode;
+    g.bias_ld = N; g.bias_batch_stride = folded ? 0 : M * N;
+  }
+  if (accumulate) {
+    at::Tensor d = D->to(A.device());
+    if (d.scalar_type() != at::kFloat && d.scalar_type() != at::kBFloat16) d = d.to(at::kFloat);
+    d = d.expand(out_shape).contiguous();
+    keep.push_back(d);
+    g.D = d.data_ptr(); g.d_dtype = to_b200q_dtype(d.scalar_type()); g.ldd = N; g.d_batch_stride = folded ? 0 : M * N;
+  }
+  g.stream = current_stream();
+  check_status(b200q_fp8_gemm(&g), "fp8_gemm_v2");
+  return out;
+}
+
+at::Tensor fp8_gemm_v2(const at::Tensor& A, bool trans_A, const at::Tensor& B, bool trans_B, const OptTensor& D,
+                       at::ScalarType out_dtype, const OptTensor& A_scale_inv, const OptTensor& B_scale_inv,
+                       const OptTensor& bias, bool accumulate, OptShape B_scale_shape) {
+  return fp8_gemm_v2_common(A, trans_A, B, trans_B, D, out_dtype, to_scale_arg(A_scale_inv), to_scale_arg(B_scale_inv),
+                            bias, accumulate, B_scale_shape);
+}
+at::Tensor fp8_gemm_v2_scalar(const at::Tensor& A, bool trans_A, const at::Tensor& B, bool trans_B, const OptTensor& D,
+                              at::ScalarType out_dtype, double A_scale_inv, double B_scale_inv, const OptTensor& bias,
+                              bool accumulate, OptShape) {
+  return fp8_gemm_v2_common(A, trans_A, B, trans_B, D, out_dtype, ScaleArg(A_scale_inv), ScaleArg(B_scale_inv), bias,
+                            accumulate, c10::nullopt);
+}
+at::Tensor fp8_gemm_v2_scalar_list(const at::Tensor& A, bool trans_A, const at::Tensor& B, bool trans_B,
+                                   const OptTensor& D, at::ScalarType out_dtype, c10::ArrayRef<double> A_scale_inv,
+                                   c10::ArrayRef<double> B_scale_inv, const OptTensor& bias, bool accumulate,
+                                   OptShape B_scale_shape) {
+  return fp8_gemm_v2_common(A, trans_A, B, trans_B, D, out_dtype, ScaleArg(A_scale_inv.vec()),
+                            ScaleArg(B_scale_inv.vec()), bias, accumulate, B_scale_shape);
+}
+
+// legacy out-variant (kernels_register.cpp:2445; fp8_ops.cpp:312-366)
+at::Tensor& fp8_gemm(const at::Tensor& A, bool trans_A, const at::Tensor& B, bool trans_B, const at::Tensor& D,
+                     at::ScalarType out_dtype, const OptTensor& A_scale_inv, const OptTensor& B_scale_inv,
+                     const OptTensor& bias, bool accumulate, at::Tensor& out) {
+  at::Tensor r = fp8_gemm_v2(A, trans_A, B, trans_B, D, out_dtype, A_scale_inv, B_scale_inv, bias, accumulate,
+                             c10::nullopt);
+  out.copy_(r);
+  return out;
+}
+
+// ------------------------------------------------------------------ b200q:: extras
+at::Tensor w4a16_gemm(const at::Tensor& x, const at::Tensor& qweight, const at::Tensor& scales, const OptTensor& qzeros,
+                      int64_t group_size, bool k_packed, at::ScalarType out_dtype) {
+  TORCH_CHECK(x.scalar_type() == at::kBFloat16 && x.dim() == 2, "w4a16_gemm: x must be bf16 [M, K]");
+  TORCH_CHECK(qweight.scalar_type() == at::kInt && qweight.dim() == 2, "w4a16_gemm: qweight must be int32 2-D");
+  c10::cuda::CUDAGuard guard(x.device());
+  at::Tensor xc = x.contiguous(), q = qweight.contiguous(), sc = scales.to(at::kBFloat16).contiguous();
+  const int64_t M = xc.size(0), K = xc.size(1);
+  const int64_t N = k_packed ? q.size(1) : q.size(1) * 8;
+  TORCH_CHECK((k_packed ? q.size(0) * 8 : q.size(0)) == K, "w4a16_gemm: qweight does not match K = ", K);
+  TORCH_CHECK(group_size > 0 && K % group_size == 0 && sc.dim() == 2 && sc.size(0) == K / group_size && sc.size(1) == N,
+              "w4a16_gemm: scales must be [K/group, N]");
+  at::Tensor zp;
+  int zp_kind = B200Q_ZP_NONE;
+  if (qzeros.has_value() && qzeros->defined()) {
+    zp = qzeros->contiguous();
+    TORCH_CHECK(zp.scalar_type() == at::kInt && zp.numel() == sc.size(0) * (N / 8), "w4a16_gemm: qzeros must be int32 [K/group, N/8]");
+    zp_kind = B200Q_ZP_PACKED;
+  }
+  at::Tensor out = at::empty({M, N}, xc.options().dtype(out_dtype));
+  check_status(b200q_w4a16_gemm(xc.data_ptr(), K, q.data_ptr<int32_t>(), sc.data_ptr(),
+                                zp.defined() ? zp.data_ptr<int32_t>() : nullptr, zp_kind, k_packed ? 1 : 0, M, N, K,
+                                group_size, out.data_ptr(), to_b200q_dtype(out_dtype), N, current_stream()),
+               "w4a16_gemm");
+  return out;
+}
+
+std::tuple<at::Tensor, at::Tensor> swiglu_cast_fp8(const at::Tensor& gate, const at::Tensor& up, double scale,
+                                                   bool is_amax) {
+  TORCH_CHECK(gate.scalar_type() == at::kBFloat16 && up.scalar_type() == at::kBFloat16 && gate.dim() == 2 &&
+                  gate.sizes() == up.sizes() && gate.stride(1) == 1 && up.stride(1) == 1,
+              "swiglu_cast_fp8: gate/up must be bf16 [rows, cols] with unit inner stride");
+  c10::cuda::CUDAGuard guard(gate.device());
+  at::Tensor out = at::empty(gate.sizes(), gate.options().dtype(at::kFloat8_e4m3fn));
+  at::Tensor amax = is_amax ? at::empty({}, gate.options().dtype(at::kFloat)) : at::empty({0}, gate.options().dtype(at::kFloat));
+  check_status(b200q_swiglu_cast_fp8(gate.data_ptr(), gate.stride(0), up.data_ptr(), up.stride(0), out.data_ptr(),
+                                     (float)scale, gate.size(0), gate.size(1),
+                                     is_amax ? amax.data_ptr<float>() : nullptr, current_stream()),
+               "swiglu_cast_fp8");
+  return {out, amax};
+}
+
+void set_sr_seed(int64_t seed) {
+  g_sr_seed.store(seed);
+  g_sr_offset.store(0);
+}
+void set_cast_mul_in_fp32(bool on) { g_mul_in_fp32.store(on); }
+int64_t launch_count() { return (int64_t)b200q_launch_count(); }
+int64_t device_status() {
+  int code = 0;
+  int rc = b200q_device_status(&code);
+  TORCH_CHECK(rc == B200Q_OK || rc == B200Q_ERR_DEVICE_TIMEOUT, "device_status: ", b200q_strerror(rc), " ",
+              b200q_last_cuda_error());
+  return code;
+}
+
+// ------------------------------------------------------------------ Meta
+// python_packages/habana_frameworks/torch/dynamo/_custom_op_meta_registrations.py:56-217
+std::tuple<at::Tensor, at::Tensor> meta_cast_to(const at::Tensor& input, bool is_amax, at::ScalarType dtype) {
+  at::Tensor out = at::empty(input.sizes(), input.options().dtype(dtype));
+  at::Tensor amax = is_amax ? at::empty({}, input.options().dtype(at::kFloat)) : at::empty({0}, input.options().dtype(at::kFloat));
+  return {out, amax};
+}
+std::tuple<at::Tensor, at::Tensor> meta_cast_to_fp8_v2(const at::Tensor& i, const OptTensor&, bool, bool a,
+                                                       at::ScalarType d, OptShape) { return meta_cast_to(i, a, d); }
+std::tuple<at::Tensor, at::Tensor> meta_cast_to_fp8_v2_scalar(const at::Tensor& i, double, bool, bool a,
+                                                              at::ScalarType d, OptShape) { return meta_cast_to(i, a, d); }
+std::tuple<at::Tensor, at::Tensor> meta_cast_to_fp8_v2_list(const at::Tensor& i, c10::ArrayRef<double>, bool, bool a,
+                                                            at::ScalarType d, OptShape) { return meta_cast_to(i, a, d); }
+at::Tensor meta_cast_from(const at::Tensor& i, at::ScalarType d) { return at::empty(i.sizes(), i.options().dtype(d)); }
+at::Tensor meta_cast_from_fp8(const at::Tensor& i, const OptTensor&, at::ScalarType d, OptShape) { return meta_cast_from(i, d); }
+at::Tensor meta_cast_from_fp8_scalar(const at::Tensor& i, double, at::ScalarType d, OptShape) { return meta_cast_from(i, d); }
+at::Tensor meta_cast_from_fp8_list(const at::Tensor& i, c10::ArrayRef<double>, at::ScalarType d, OptShape) { return meta_cast_from(i, d); }
+at::Tensor meta_convert_from_4bit(const at::Tensor& i, const at::Tensor&, const OptTensor&, at::ScalarType d) {
+  auto s = i.sizes().vec();
+  s.back() *= 8;
+  return at::empty(s, i.options().dtype(d));
+}
+at::Tensor meta_gemm(const at::Tensor& A, bool ta, const at::Tensor& B, bool tb, at::ScalarType d) {
+  return at::empty(matmul_out_shape(A.sizes(), B.sizes(), ta, tb), A.options().dtype(d));
+}
+at::Tensor meta_fp8_gemm_v2(const at::Tensor& A, bool ta, const at::Tensor& B, bool tb, const OptTensor&,
+                            at::ScalarType d, const OptTensor&, const OptTensor&, const OptTensor&, bool, OptShape) {
+  return meta_gemm(A, ta, B, tb, d);
+}
+at::Tensor meta_fp8_gemm_v2_scalar(const at::Tensor& A, bool ta, const at::Tensor& B, bool tb, const OptTensor&,
+                                   at::ScalarType d, double, double, const OptTensor&, bool, OptShape) {
+  return meta_gemm(A, ta, B, tb, d);
+}
+at::Tensor meta_fp8_gemm_v2_list(const at::Tensor& A, bool ta, const at::Tensor& B, bool tb, const OptTensor&,
+                                 at::ScalarType d, c10::ArrayRef<double>, c10::ArrayRef<double>, const OptTensor&, bool,
+                                 OptShape) {
+  return meta_gemm(A, ta, B, tb, d);
+}
+
+}  // namespace
+
+TORCH_LIBRARY(hpu, m) {
+  m.def("cast_to_fp8(Tensor input, Tensor? scale, bool stochastic_rounding, Tensor(a!) out, Tensor(b!) amax) -> (Tensor(a!), Tensor(b!))");
+  m.def("cast_to_fp8_v2(Tensor input, Tensor? scale=None, bool stochastic_rounding=False, bool is_amax=False, ScalarType dtype=None, int[]? scale_shape=None) -> (Tensor, Tensor)");
+  m.def("cast_to_fp8_v2.scalar(Tensor input, float scale, bool stochastic_rounding=False, bool is_amax=False, ScalarType dtype=None, int[]? scale_shape=None) -> (Tensor, Tensor)");
+  m.def("cast_to_fp8_v2.scalar_list(Tensor input, float[] scale, bool stochastic_rounding=False, bool is_amax=False, ScalarType dtype=None, int[]? scale_shape=None) -> (Tensor, Tensor)");
+  m.def("convert_from_int4(Tensor input, Tensor scale, Tensor? zero_point, ScalarType out_dtype) -> Tensor");
+  m.def("convert_from_uint4(Tensor input, Tensor scale, Tensor? zero_point, ScalarType out_dtype) -> Tensor");
+  m.def("cast_from_fp8(Tensor input, Tensor? scale, ScalarType out_dtype, int[]? scale_shape=None) -> Tensor");
+  m.def("cast_from_fp8.scalar(Tensor input, float scale, ScalarType out_dtype, int[]? scale_shape=None) -> Tensor");
+  m.def("cast_from_fp8.scalar_list(Tensor input, float[] scale, ScalarType out_dtype, int[]? scale_shape=None) -> Tensor");
+  m.def("fp8_gemm(Tensor A, bool trans_A, Tensor B, bool trans_B, Tensor D, ScalarType out_dtype, Tensor? A_scale_inv, Tensor? B_scale_inv, Tensor? bias, bool accumulate, Tensor(a!) out) -> Tensor(a!)");
+  m.def("fp8_gemm_v2(Tensor A, bool trans_A, Tensor B, bool trans_B, Tensor? D, ScalarType out_dtype, Tensor? A_scale_inv=None, Tensor? B_scale_inv=None, Tensor? bias=None, bool accumulate=False, int[]? B_scale_shape=None) -> Tensor");
+  m.def("fp8_gemm_v2.scalar(Tensor A, bool trans_A, Tensor B, bool trans_B, Tensor? D, ScalarType out_dtype, float A_scale_inv, float B_scale_inv, Tensor? bias=None, bool accumulate=False, int[]? B_scale_shape=None) -> Tensor");
+  m.def("fp8_gemm_v2.scalar_list(Tensor A, bool trans_A, Tensor B, bool trans_B, Tensor? D, ScalarType out_dtype, float[] A_scale_inv, float[] B_scale_inv, Tensor? bias=None, bool accumulate=False, int[]? B_scale_shape=None) -> Tensor");
+}
+
+TORCH_LIBRARY_IMPL(hpu, CUDA, m) {
+  m.impl("cast_to_fp8", cast_to_fp8);
+  m.impl("cast_to_fp8_v2", cast_to_fp8_v2);
+  m.impl("cast_to_fp8_v2.scalar", cast_to_fp8_v2_scalar);
+  m.impl("cast_to_fp8_v2.scalar_list", cast_to_fp8_v2_scalar_list);
+  m.impl("convert_from_int4", convert_from_int4);
+  m.impl("convert_from_uint4", convert_from_uint4);
+  m.impl("cast_from_fp8", cast_from_fp8);
+  m.impl("cast_from_fp8.scalar", cast_from_fp8_scalar);
+  m.impl("cast_from_fp8.scalar_list", cast_from_fp8_scalar_list);
+  m.impl("fp8_gemm", fp8_gemm);
+  m.impl("fp8_gemm_v2", fp8_gemm_v2);
+  m.impl("fp8_gemm_v2.scalar", fp8_gemm_v2_scalar);
+  m.impl("fp8_gemm_v2.scalar_list", fp8_gemm_v2_scalar_list);
+}
+
+TORCH_LIBRARY_IMPL(hpu, Meta, m) {
+  m.impl("cast_to_fp8_v2", meta_cast_to_fp8_v2);
+  m.impl("cast_to_fp8_v2.scalar", meta_cast_to_fp8_v2_scalar);
+  m.impl("cast_to_fp8_v2.scalar_list", meta_cast_to_fp8_v2_list);
+  m.impl("convert_from_int4", meta_convert_from_4bit);
+  m.impl("convert_from_uint4", meta_convert_from_4bit);
+  m.impl("cast_from_fp8", meta_cast_from_fp8);
+  m.impl("cast_from_fp8.scalar", meta_cast_from_fp8_scalar);
+  m.impl("cast_from_fp8.scalar_list", meta_cast_from_fp8_list);
+  m.impl("fp8_gemm_v2", meta_fp8_gemm_v2);
+  m.impl("fp8_gemm_v2.scalar", meta_fp8_gemm_v2_scalar);
+  m.impl("fp8_gemm_v2.scalar_list", meta_fp8_gemm_v2_list);
+}
+
+TORCH_LIBRARY(b200q, m) {
+  m.def("w4a16_gemm(Tensor x, Tensor qweight, Tensor scales, Tensor? qzeros, int group_size, bool k_packed, ScalarType out_dtype) -> Tensor");
+  m.def("dequant_kpacked(Tensor qweight, Tensor scales, Tensor? qzeros, ScalarType out_dtype) -> Tensor");
+  m.def("swiglu_cast_fp8(Tensor gate, Tensor up, float scale, bool is_amax) -> (Tensor, Tensor)");
+  m.def("set_sr_seed(int seed) -> ()", set_sr_seed);
+  m.def("set_cast_mul_in_fp32(bool on) -> ()", set_cast_mul_in_fp32);
+  m.def("launch_count() -> int", launch_count);
+  m.def("device_status() -> int", device_status);
+}
+
+TORCH_LIBRARY_IMPL(b200q, CUDA, m) {
+  m.impl("w4a16_gemm", w4a16_gemm);
+  m.impl("dequant_kpacked", dequant_kpacked);
+  m.impl("swiglu_cast_fp8", swiglu_cast_fp8);
+}

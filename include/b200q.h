@@ -1,0 +1,198 @@
+/*
+ * b200q -- C ABI of the B200 (sm_100a) kernels behind the quantized-inference
+ * operator family torch.ops.hpu.{cast_to_fp8_v2, cast_from_fp8, fp8_gemm_v2,
+ * convert_from_int4, convert_from_uint4} plus the fused W4A16 GEMM.
+ *
+ * Conventions
+ *  - every pointer is a caller-owned DEVICE pointer unless its name ends in _host;
+ *  - `stream` is a cudaStream_t passed as void* (NULL = the legacy default stream);
+ *  - nothing here allocates, synchronises or throws; a call validates its
+ *    arguments on the host, enqueues kernels on `stream` and returns;
+ *  - the return value is B200Q_OK (0) or a negative B200Q_ERR_* code, and
+ *    b200q_strerror() turns it into text;
+ *  - kernels that wait on barriers bound every wait; a wait that runs out sets a
+ *    device status word that b200q_device_status() reads back (it synchronises).
+ *
+ * Each entry point names the reference interface it replaces, by the file's
+ * path inside the reference project.
+ */
+#ifndef B200Q_H_
+#define B200Q_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+enum b200q_status {
+  B200Q_OK = 0,
+  B200Q_ERR_BAD_ARGUMENT = -1,  /* null pointer, negative size, unknown enum value */
+  B200Q_ERR_UNSUPPORTED = -2,   /* a combination this build has no kernel for */
+  B200Q_ERR_CUDA = -3,          /* a CUDA runtime / driver call failed; see b200q_last_cuda_error() */
+  B200Q_ERR_TOO_LARGE = -4,     /* size beyond a documented maximum */
+  B200Q_ERR_DEVICE_TIMEOUT = -5 /* a bounded wait inside a kernel ran out (b200q_device_status) */
+};
+
+enum b200q_dtype {
+  B200Q_F32 = 0,
+  B200Q_BF16 = 1,
+  B200Q_E4M3 = 2, /* float8_e4m3fn: no inf, max 448 */
+  B200Q_E5M2 = 3  /* float8_e5m2: max finite 57344 */
+};
+
+/* How a scale (or bias) operand lines up with the [rows, cols] problem. */
+enum b200q_bcast {
+  B200Q_BCAST_NONE = 0,        /* operand absent */
+  B200Q_BCAST_SCALAR_HOST = 1, /* one value, passed by value in the *_host field */
+  B200Q_BCAST_SCALAR_DEV = 2,  /* one value in device memory */
+  B200Q_BCAST_PER_COL = 3,     /* cols values: operand[c] applies to column c */
+  B200Q_BCAST_PER_ROW = 4,     /* rows values: operand[r] applies to row r */
+  B200Q_BCAST_FULL = 5         /* rows x cols values */
+};
+
+enum b200q_rounding {
+  B200Q_ROUND_RNE = 0,       /* round half to nearest even, saturating */
+  B200Q_ROUND_STOCHASTIC = 1 /* Philox4x32-10 keyed by (seed, element index), saturating */
+};
+
+/* flag bits of b200q_cast_to_fp8 */
+#define B200Q_CAST_MUL_IN_FP32 1 /* form input*scale in fp32 instead of in the input dtype */
+
+const char* b200q_strerror(int status);
+/* Text of the last CUDA error a b200q call saw on this thread ("" if none). */
+const char* b200q_last_cuda_error(void);
+/* Synchronises the current device, reads and clears the device status word.
+ * 0 = every bounded wait completed; otherwise a kernel-specific code. */
+int b200q_device_status(int* code_out);
+/* Number of kernels this library has launched in this process (all threads). */
+uint64_t b200q_launch_count(void);
+
+/*
+ * cast_to_fp8: out = fp8(in * scale), optional amax = max|in| (of the unscaled input).
+ * Replaces the node `convert_to_fp8_{f32,bf16}` emitted by CastToFp8V2::AddNode,
+ * hpu_ops/backend/fp8_ops.cpp:192-258 (rounding choice :105-119, scales :63-96).
+ *
+ * in        [rows*cols] contiguous, in_dtype F32 or BF16 (E4M3/E5M2 input = byte copy,
+ *           out_dtype must equal in_dtype, amax must be NULL)
+ * out       [rows*cols] bytes, out_dtype E4M3 or E5M2
+ * scale     per b200q_bcast, fp32; the product is formed in the input dtype (the scale
+ *           is first rounded to it) unless B200Q_CAST_MUL_IN_FP32 is set
+ * amax      NULL or one fp32; written by the call (zeroed on `stream` first)
+ * rounding  b200q_rounding; for STOCHASTIC element i uses 32-bit word (first_index+i)%4 of
+ *           Philox block (first_index+i)/4 with key = seed and counter words 2,3 = offset
+ */
+int b200q_cast_to_fp8(const void* in, int in_dtype, void* out, int out_dtype,
+                      const float* scale, float scale_host, int scale_mode,
+                      int64_t rows, int64_t cols, float* amax, int rounding,
+                      uint64_t seed, uint64_t offset, uint64_t first_index, int flags,
+                      void* stream);
+
+/*
+ * cast_from_fp8: out = T(in) * T(scale), rounded once in T = out_dtype (F32 or BF16).
+ * Replaces `convert_from_fp8_{f32,bf16}`, CastFromFp8::AddNode,
+ * hpu_ops/backend/fp8_ops.cpp:265-308.
+ */
+int b200q_cast_from_fp8(const void* in, int in_dtype, void* out, int out_dtype,
+                        const float* scale, float scale_host, int scale_mode,
+                        int64_t rows, int64_t cols, void* stream);
+
+/* zero-point kinds of b200q_dequant_int4 / b200q_w4a16_gemm */
+enum b200q_zp_kind {
+  B200Q_ZP_NONE = 0,
+  B200Q_ZP_PACKED = 1, /* int32 words, 8 nibbles each, same nibble order and signedness as the input */
+  B200Q_ZP_FLOAT = 2   /* out_dtype values, subtracted in out_dtype */
+};
+
+/*
+ * dequant_int4: out[r][8p+i] = (nibble_i(packed[r][p]) - zp) * scale, nibble i = bits [4i,4i+4).
+ * Replaces `dequantize_4_bit_{bf16,f32}`, Int4BaseOp::AddNode,
+ * hpu_ops/backend/int4_ops.cpp:40-56 (int4/uint4 typing backend/habana_operator.cpp:376-386).
+ *
+ * packed      int32 [rows][cols_packed]
+ * out         out_dtype (F32/BF16) [rows][8*cols_packed]
+ * scale       out_dtype [scale_rows][8*cols_packed]; scale_rows divides rows and row r uses
+ *             scale row r / (rows/scale_rows)   (scale_rows == rows: one scale per element)
+ * zp          per zp_kind; PACKED: int32 [scale_rows][cols_packed]; FLOAT: like scale
+ * is_signed   1 = int4 (nibbles above 7 are negative), 0 = uint4
+ * k_packed    0 = the operator's layout above.  1 = AutoGPTQ layout: packed is
+ *             [rows/8][cols] with the 8 nibbles of a word going down 8 consecutive ROWS,
+ *             out is [rows][cols], scale [scale_rows][cols], PACKED zp [scale_rows][cols/8]
+ *             (packed along columns); `cols_packed` then carries cols.
+ */
+int b200q_dequant_int4(const int32_t* packed, const void* scale, const void* zp, int zp_kind,
+                       int is_signed, int out_dtype, void* out, int64_t rows, int64_t cols_packed,
+                       int64_t scale_rows, int k_packed, void* stream);
+
+/*
+ * fp8_gemm: out = (op(A) @ op(B)) * a_scale * b_scale [+ bias] [+ D], fp32 accumulation.
+ * Replaces `fp8_gemm_{f32,bf16}`, Fp8GemmV2::AddNode, hpu_ops/backend/fp8_ops.cpp:403-496
+ * (node inputs [A, B, A_scale_inv, B_scale_inv, bias, D]).
+ *
+ * op(A) is M x K: A is stored [M][K] (trans_a = 0) or [K][M] (trans_a = 1), row stride lda.
+ * op(B) is K x N: B is stored [K][N] (trans_b = 0) or [N][K] (trans_b = 1), row stride ldb.
+ * Scales and bias line up with the M x N output per b200q_bcast (rows = M, cols = N).
+ * `batch` independent problems are `*_batch_stride` elements apart (0 = shared operand).
+ * The tcgen05 path needs both operands K-major (trans_a = 0, trans_b = 1), K % 16 == 0
+ * and 16-byte aligned bases and row strides; everything else runs a generic CUDA kernel.
+ */
+typedef struct b200q_gemm_args {
+  const void* A;
+  const void* B;
+  int a_dtype, b_dtype; /* E4M3 / E5M2, may differ */
+  int trans_a, trans_b;
+  int64_t M, N, K;
+  int64_t lda, ldb;
+  int64_t batch, a_batch_stride, b_batch_stride, out_batch_stride;
+  void* out;
+  int out_dtype; /* F32 / BF16 */
+  int64_t ldo;
+  const float* a_scale;
+  float a_scale_host;
+  int a_scale_mode;
+  const float* b_scale;
+  float b_scale_host;
+  int b_scale_mode;
+  const void* bias; /* bias_dtype F32 / BF16 */
+  int bias_dtype, bias_mode;
+  int64_t bias_ld, bias_batch_stride; /* bias_ld: row stride when bias_mode == FULL */
+  const void* D; /* NULL = no accumulate */
+  int d_dtype;
+  int64_t ldd, d_batch_stride;
+  int force_generic; /* 1 = skip the tcgen05 path (testing) */
+  void* stream;
+} b200q_gemm_args;
+
+int b200q_fp8_gemm(const b200q_gemm_args* args);
+
+/*
+ * w4a16_gemm: out[M][N] = x[M][K] @ W[K][N], W = (nibble - zp) * scale rounded to bf16 exactly
+ * as b200q_dequant_int4 would produce it, bf16 tensor-core product, fp32 accumulation.
+ * No counterpart node in the reference: there `dequantize_4_bit` -> `gemm` are two nodes
+ * that the graph compiler fuses (hpu_ops/backend/int4_ops.cpp:48-53); the contract is the
+ * composition matmul(x, convert_from_uint4(...)).
+ *
+ * x        bf16 [M][K], row stride ldx
+ * qweight  k_packed = 0: int32 [K][N/8] (operator layout); 1: int32 [K/8][N] (AutoGPTQ)
+ * scale    bf16 [K/group][N];  zp: NONE or PACKED int32 [K/group][N/8]
+ * out      out_dtype F32/BF16 [M][N], row stride ldo
+ */
+int b200q_w4a16_gemm(const void* x, int64_t ldx, const int32_t* qweight, const void* scale,
+                     const int32_t* zp, int zp_kind, int k_packed, int64_t M, int64_t N, int64_t K,
+                     int64_t group, void* out, int out_dtype, int64_t ldo, void* stream);
+
+/*
+ * swiglu_cast_fp8: out8 = e4m3(bf16(silu(gate) * up) * scale), the activation step between the
+ * column-parallel and the row-parallel GEMMs of an FP8 MLP, in one pass.
+ * No single counterpart in the reference (silu, mul and CastToFp8V2 are separate nodes there,
+ * fused by its graph compiler; cast semantics as b200q_cast_to_fp8 with RNE).
+ * gate/up bf16 [rows][cols] with row strides ld_gate / ld_up; out e4m3 [rows][cols] contiguous.
+ */
+int b200q_swiglu_cast_fp8(const void* gate, int64_t ld_gate, const void* up, int64_t ld_up,
+                          void* out, float scale_host, int64_t rows, int64_t cols, float* amax,
+                          void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* B200Q_H_ */

@@ -149,9 +149,9 @@ def stochastic_round_to_fp8(v32: torch.Tensor, dtype: torch.dtype, seed: int, of
       E <  Emin : s = d + Emin - E; with the 24-bit significand m (for s > 32
                   first m >>= s - 32 and s = 32): t = (m + (r & (2^s - 1))) >> s,
                   result = t * 2^(log2 of the subnormal quantum).
-    The result is clamped to +-max.  Values between 0 and the smallest
+    The result is clamped to +-max; NaN becomes the byte 0x7F.  Values between 0 and the smallest
     subnormal therefore also round stochastically (the reference's default
-    "SFTZ" behaviour, scripts/env_flags.yaml:753-758).  NaN stays NaN.
+    "SFTZ" behaviour, scripts/env_flags.yaml:753-758).
     """
     mbits, emin, qlog2 = _FP8_FMT[dtype]
     d = 23 - mbits
@@ -183,17 +183,22 @@ def stochastic_round_to_fp8(v32: torch.Tensor, dtype: torch.dtype, seed: int, of
     out = torch.where(torch.from_numpy((sign != 0).copy()), -out, out)
     out8 = out.to(dtype)  # exact: every value is representable
     if isnan.any():
-        nanbyte = torch.from_numpy(((sign >> np.uint64(24)) | np.uint64(0x7F)).astype(np.uint8))
+        nanbyte = torch.full((n,), 0x7F, dtype=torch.uint8)
         out8 = torch.where(torch.from_numpy(isnan.copy()), nanbyte, out8.view(torch.uint8)).view(dtype)
     return out8.reshape(v32.shape)
 
 
 # --------------------------------------------------------------------------- casts
 def _rne_to_fp8(v32: torch.Tensor, dtype: torch.dtype) -> torch.Tensor:
-    """Saturating round-half-to-even: clamp to +-max in fp32, then convert.
-    NaN -> 0x7F | sign (torch's own conversion); never inf."""
+    """Saturating round-half-to-even: clamp to +-max in fp32, then convert; never inf.
+    Every NaN becomes the byte 0x7F (sign and payload dropped: CPUs and GPUs do not agree on
+    the sign of a NaN that went through a multiply, so the contract is the canonical NaN)."""
     mx = FP8_MAX[dtype]
-    return v32.clamp(-mx, mx).to(dtype)
+    out = v32.clamp(-mx, mx).to(dtype)
+    nan = torch.isnan(v32)
+    if nan.any():
+        out = torch.where(nan, torch.full_like(out.view(torch.uint8), 0x7F), out.view(torch.uint8)).view(dtype)
+    return out
 
 
 def cast_to_fp8_v2(input: torch.Tensor, scale: ScaleArg = None, stochastic_rounding: bool = False,

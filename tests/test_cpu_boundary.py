@@ -1,0 +1,106 @@
+"""CPU-only checks of the drop-in boundary: the C-ABI library loads and exports every symbol
+that include/b200q.h declares, the hpu::* schemas are registered verbatim, Meta kernels give the
+reference's shapes/dtypes, and CPU tensors are refused (there is no fallback)."""
+import ctypes
+import os
+import re
+
+import pytest
+import torch
+
+from conftest import ROOT
+
+import b200_hpu_ops
+from b200_hpu_ops import abi
+
+
+def test_header_symbols_are_exported():
+    hdr = open(os.path.join(ROOT, "include", "b200q.h")).read()
+    declared = set(re.findall(r"^(?:int|const char\*|uint64_t)\s+(b200q_[a-z0-9_]+)\s*\(", hdr, re.M))
+    assert declared, "no declarations found"
+    lib = ctypes.CDLL(b200_hpu_ops.KERNEL_LIB)
+    for name in sorted(declared):
+        assert hasattr(lib, name), f"{name} declared in b200q.h but not exported"
+    assert declared == set(abi.EXPORTS)
+    assert abi.lib.b200q_strerror(0) == b"ok"
+    assert b"bad argument" in abi.lib.b200q_strerror(-1)
+
+
+SCHEMAS = {
+    "cast_to_fp8_v2": "hpu::cast_to_fp8_v2(Tensor input, Tensor? scale=None, bool stochastic_rounding=False, bool is_amax=False, ScalarType dtype=None, int[]? scale_shape=None) -> (Tensor, Tensor)",
+    "cast_to_fp8_v2.scalar": "hpu::cast_to_fp8_v2.scalar(Tensor input, float scale, bool stochastic_rounding=False, bool is_amax=False, ScalarType dtype=None, int[]? scale_shape=None) -> (Tensor, Tensor)",
+    "cast_to_fp8_v2.scalar_list": "hpu::cast_to_fp8_v2.scalar_list(Tensor input, float[] scale, bool stochastic_rounding=False, bool is_amax=False, ScalarType dtype=None, int[]? scale_shape=None) -> (Tensor, Tensor)",
+    "convert_from_int4": "hpu::convert_from_int4(Tensor input, Tensor scale, Tensor? zero_point, ScalarType out_dtype) -> Tensor",
+    "convert_from_uint4": "hpu::convert_from_uint4(Tensor input, Tensor scale, Tensor? zero_point, ScalarType out_dtype) -> Tensor",
+    "cast_from_fp8": "hpu::cast_from_fp8(Tensor input, Tensor? scale, ScalarType out_dtype, int[]? scale_shape=None) -> Tensor",
+    "cast_from_fp8.scalar": "hpu::cast_from_fp8.scalar(Tensor input, float scale, ScalarType out_dtype, int[]? scale_shape=None) -> Tensor",
+    "cast_from_fp8.scalar_list": "hpu::cast_from_fp8.scalar_list(Tensor input, float[] scale, ScalarType out_dtype, int[]? scale_shape=None) -> Tensor",
+    "fp8_gemm_v2": "hpu::fp8_gemm_v2(Tensor A, bool trans_A, Tensor B, bool trans_B, Tensor? D, ScalarType out_dtype, Tensor? A_scale_inv=None, Tensor? B_scale_inv=None, Tensor? bias=None, bool accumulate=False, int[]? B_scale_shape=None) -> Tensor",
+    "fp8_gemm_v2.scalar": "hpu::fp8_gemm_v2.scalar(Tensor A, bool trans_A, Tensor B, bool trans_B, Tensor? D, ScalarType out_dtype, float A_scale_inv, float B_scale_inv, Tensor? bias=None, bool accumulate=False, int[]? B_scale_shape=None) -> Tensor",
+    "fp8_gemm_v2.scalar_list": "hpu::fp8_gemm_v2.scalar_list(Tensor A, bool trans_A, Tensor B, bool trans_B, Tensor? D, ScalarType out_dtype, float[] A_scale_inv, float[] B_scale_inv, Tensor? bias=None, bool accumulate=False, int[]? B_scale_shape=None) -> Tensor",
+}
+
+
+@pytest.mark.parametrize("name", sorted(SCHEMAS))
+def test_schema_strings_match_reference(name):
+    # habana_kernels/kernels_register.cpp:2429-2451
+    base, _, overload = name.partition(".")
+    op = getattr(getattr(torch.ops.hpu, base), overload or "default")
+    assert str(op._schema) == SCHEMAS[name]
+
+
+def test_meta_shapes_follow_reference():
+    # python_packages/habana_frameworks/torch/dynamo/_custom_op_meta_registrations.py:56-217
+    x = torch.empty(6, 10, device="meta", dtype=torch.bfloat16)
+    for is_amax in (False, True):
+        o, a = torch.ops.hpu.cast_to_fp8_v2(x, None, False, is_amax, torch.float8_e5m2)
+        assert o.shape == x.shape and o.dtype == torch.float8_e5m2
+        assert a.dtype == torch.float32 and tuple(a.shape) == (() if is_amax else (0,))
+    o, _ = torch.ops.hpu.cast_to_fp8_v2(x, 2.0, False, False, torch.float8_e4m3fn)
+    assert o.dtype == torch.float8_e4m3fn
+    o, _ = torch.ops.hpu.cast_to_fp8_v2(x, [1.0] * 10, False, False, torch.float8_e4m3fn, [1, 10])
+    assert o.shape == x.shape
+    r = torch.ops.hpu.cast_from_fp8(o, None, torch.bfloat16)
+    assert r.dtype == torch.bfloat16 and r.shape == x.shape
+    q = torch.empty(4, 6, 4, device="meta", dtype=torch.int32)
+    for fn in (torch.ops.hpu.convert_from_int4, torch.ops.hpu.convert_from_uint4):
+        assert tuple(fn(q, x, None, torch.float32).shape) == (4, 6, 32)
+    f8 = torch.float8_e4m3fn
+    cases = [((2, 1, 4, 2), (1, 3, 4, 8), True, False, (2, 3, 2, 8)), ((4, 2), (3, 4, 8), True, False, (3, 2, 8)),
+             ((10,), (10,), False, False, ()), ((2, 10), (10,), False, False, (2,)),
+             ((8,), (2, 4, 8, 16), False, False, (2, 4, 16)), ((4096, 4096), (14336, 4096), False, True, (4096, 14336))]
+    for sa, sb, ta, tb, so in cases:
+        A = torch.empty(sa, device="meta", dtype=f8)
+        B = torch.empty(sb, device="meta", dtype=f8)
+        assert tuple(torch.ops.hpu.fp8_gemm_v2(A, ta, B, tb, None, torch.bfloat16).shape) == so
+        assert tuple(torch.ops.hpu.fp8_gemm_v2(A, ta, B, tb, None, torch.float32, 1.0, 1.0).shape) == so
+    with pytest.raises(RuntimeError, match="Common dimension sizes of matmul inputs should be the same. Got 5 and 4"):
+        torch.ops.hpu.fp8_gemm_v2(torch.empty(3, 5, device="meta", dtype=f8), False,
+                                  torch.empty(4, 6, device="meta", dtype=f8), False, None, torch.bfloat16)
+    with pytest.raises(RuntimeError, match="Batch dimension 0 of matmul inputs should be the same"):
+        torch.ops.hpu.fp8_gemm_v2(torch.empty(2, 3, 5, device="meta", dtype=f8), False,
+                                  torch.empty(3, 5, 6, device="meta", dtype=f8), False, None, torch.bfloat16)
+
+
+def test_cpu_tensors_are_refused():
+    with pytest.raises(NotImplementedError):
+        torch.ops.hpu.cast_to_fp8_v2(torch.zeros(4), None, False, False, torch.float8_e4m3fn)
+
+
+def test_abi_rejects_bad_arguments_without_a_gpu():
+    # validation happens before any CUDA call
+    assert abi.lib.b200q_cast_to_fp8(None, abi.BF16, None, abi.E4M3, None, 1.0, abi.BCAST_NONE, 4, 4, None, 0, 0, 0, 0,
+                                     0, None) == -1
+    assert abi.lib.b200q_cast_to_fp8(None, abi.BF16, None, abi.BF16, None, 1.0, abi.BCAST_NONE, 0, 0, None, 0, 0, 0, 0,
+                                     0, None) == -1
+    assert abi.lib.b200q_cast_from_fp8(None, abi.BF16, None, abi.BF16, None, 1.0, abi.BCAST_NONE, 0, 0, None) == -1
+    assert abi.lib.b200q_fp8_gemm(None) == -1
+    g = abi.GemmArgs()
+    g.M = g.N = g.K = 4
+    g.batch = 1
+    g.a_dtype = g.b_dtype = abi.E4M3
+    g.out_dtype = abi.BF16
+    assert abi.lib.b200q_fp8_gemm(ctypes.byref(g)) == -1  # null operands
+    g.a_dtype = abi.F32
+    assert abi.lib.b200q_fp8_gemm(ctypes.byref(g)) == -1
+    assert abi.lib.b200q_dequant_int4(None, None, None, 7, 0, abi.BF16, None, 1, 1, 1, 0, None) == -1

@@ -1,0 +1,121 @@
+"""convert_from_int4 / convert_from_uint4 on the GPU: bit-exact against the oracle and the golden
+vectors made from the reference's own pack / GPTQ helpers
+(tests/pytest_working/any_mode/test_hpu_convert_from_int4.py)."""
+import os
+
+import numpy as np
+import pytest
+import torch
+
+from conftest import GOLDEN
+from oracle import hpu_oracle as O
+
+pytestmark = pytest.mark.gpu
+_DT = {"torch.float32": torch.float32, "torch.bfloat16": torch.bfloat16}
+
+
+@pytest.fixture(scope="module")
+def ops():
+    import b200_hpu_ops
+    return b200_hpu_ops
+
+
+def _eq(a, b):
+    a, b = a.cpu(), b.cpu()
+    return a.dtype == b.dtype and a.shape == b.shape and torch.equal(a.float(), b.float())
+
+
+def test_golden_unit_and_gptq(ops):
+    z = np.load(os.path.join(GOLDEN, "int4.npz"))
+    for i in range(int(z["n_unit"])):
+        k = f"u{i}"
+        variant, zp_kind, od = z[k + "_meta"]
+        od = _DT[od]
+        packed = torch.from_numpy(z[k + "_packed"]).cuda()
+        scale = torch.from_numpy(z[k + "_scale"]).to(od).cuda()
+        zp = None
+        if zp_kind == "packed":
+            zp = torch.from_numpy(z[k + "_zp"]).cuda()
+        elif zp_kind == "unpacked":
+            zp = torch.from_numpy(z[k + "_zp"]).to(od).cuda()
+        fn = torch.ops.hpu.convert_from_int4 if variant == "int4" else torch.ops.hpu.convert_from_uint4
+        r = fn(packed, scale, zp, od)
+        assert r.dtype == od
+        assert torch.equal(r.cpu().float(), torch.from_numpy(z[k + "_ref"])), (k, variant, zp_kind, od)
+    for i in range(int(z["n_gptq"])):
+        k = f"a{i}"
+        od = _DT[z[k + "_meta"][0]]
+        is_zp = z[k + "_meta"][1] == "True"
+        qw = torch.from_numpy(z[k + "_qweight"]).cuda()
+        qz = torch.from_numpy(z[k + "_qzeros"]).cuda()
+        sc = torch.from_numpy(z[k + "_scale"]).to(od).cuda()
+        ref = torch.from_numpy(z[k + "_ref"])
+        r = torch.ops.hpu.convert_from_uint4(qw, sc, qz if is_zp else None, od)
+        assert torch.equal(r.cpu().float(), ref), (k, list(z[k + "_meta"]))
+
+
+@pytest.mark.parametrize("od", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("signed", [True, False])
+@pytest.mark.parametrize("shape,group", [((10,), None), ((4, 6, 4), None), ((256, 64), 32), ((3, 64, 24), 16),
+                                         ((130, 7), None), ((1024, 512), 128)])
+def test_against_oracle(ops, od, signed, shape, group):
+    g = torch.Generator().manual_seed(hash((shape, signed)) % 1000)
+    real = list(shape)
+    real[-1] *= 8
+    q = torch.randint(0, 16, real, generator=g)
+    packed = O.pack_nibbles(q)
+    if group is None:
+        sshape = real
+    else:
+        sshape = real[:-2] + [real[-2] // group, real[-1]]
+    scale = (torch.rand(sshape, generator=g) * 0.015 + 0.005).to(od)
+    zq = torch.randint(0, 16, sshape, generator=g)
+    zpacked = O.pack_nibbles(zq)
+    zfloat = (torch.randn(sshape, generator=g) * 5).to(od)
+    fn = torch.ops.hpu.convert_from_int4 if signed else torch.ops.hpu.convert_from_uint4
+    ofn = O.convert_from_int4 if signed else O.convert_from_uint4
+    for zp in (None, zpacked, zfloat):
+        r = fn(packed.cuda(), scale.cuda(), None if zp is None else zp.cuda(), od)
+        assert _eq(r, ofn(packed, scale, zp, od)), (shape, group, None if zp is None else zp.dtype)
+
+
+def test_kpacked_layout_matches_repacked_operator_layout(ops):
+    """AutoGPTQ packs along K; the reference repacks on the host to the operator's layout
+    (test_hpu_convert_from_int4.py:380-395).  The K-packed kernel must give the same matrix."""
+    g = torch.Generator().manual_seed(3)
+    K, N, group = 512, 256, 128
+    w = torch.randint(0, 16, (K, N), generator=g)
+    zq = torch.randint(0, 16, (K // group, N), generator=g)
+    scale = (torch.rand(K // group, N, generator=g) * 0.015 + 0.005).to(torch.bfloat16)
+    q_op = O.pack_nibbles(w)                                   # [K, N/8]
+    q_k = O.pack_nibbles(w.t().contiguous()).t().contiguous()  # [K/8, N]
+    z_op = O.pack_nibbles(zq)
+    ref = O.convert_from_uint4(q_op, scale, z_op, torch.bfloat16)
+    assert _eq(O.dequant_kpacked(q_k, scale, z_op), ref)
+    a = torch.ops.hpu.convert_from_uint4(q_op.cuda(), scale.cuda(), z_op.cuda(), torch.bfloat16)
+    b = torch.ops.b200q.dequant_kpacked(q_k.cuda(), scale.cuda(), z_op.cuda(), torch.bfloat16)
+    assert _eq(a, ref) and _eq(b, ref)
+    b0 = torch.ops.b200q.dequant_kpacked(q_k.cuda(), scale.cuda(), None, torch.float32)
+    assert _eq(b0, O.dequant_kpacked(q_k, scale, None, torch.float32))
+
+
+def test_full_size_weight_matrix(ops):
+    """K = N = 8192, group 128 (the benchmark's shape): sampled rows bit-exact against the oracle,
+    and a checksum identity: sum over the dequantised matrix of rows of one group equals
+    scale * sum(q - zp) computed from integer sums."""
+    g = torch.Generator(device="cuda").manual_seed(0)
+    K = N = 8192
+    packed = torch.randint(-2 ** 31, 2 ** 31 - 1, (K, N // 8), device="cuda", dtype=torch.int32, generator=g)
+    scale = (torch.rand(K // 128, N, device="cuda", generator=g) * 0.015 + 0.005).to(torch.bfloat16)
+    zp = torch.randint(-2 ** 31, 2 ** 31 - 1, (K // 128, N // 8), device="cuda", dtype=torch.int32, generator=g)
+    out = torch.ops.hpu.convert_from_uint4(packed, scale, zp, torch.bfloat16)
+    assert out.shape == (K, N) and out.dtype == torch.bfloat16
+    rows = torch.tensor([0, 1, 127, 128, 129, 4095, 4096, 8191])
+    for r in rows.tolist():
+        grp = r // 128
+        ref = O.convert_from_uint4(packed[r:r + 1].cpu(), scale[grp:grp + 1].cpu(), zp[grp:grp + 1].cpu(),
+                                   torch.bfloat16)
+        assert torch.equal(out[r:r + 1].cpu().float(), ref.float()), r
+    # every value is (integer in [-15, 15]) * scale: dividing by the scale gives integers back
+    ratio = out[:128].float() / scale[0].float()
+    assert torch.all((ratio - ratio.round()).abs() < 0.26)  # bf16 rounding of the product: < 2^-8 * 15 * ...
