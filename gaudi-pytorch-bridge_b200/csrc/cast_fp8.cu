@@ -303,7 +303,7 @@ __global__ void __launch_bounds__(256) swiglu_cast_kernel(SwigluParams p) {
     for (int i = 0; i < 8; ++i) {
       float h0 = silu_mul_bf16(__uint_as_float(gw[i] << 16), __uint_as_float(uw[i] << 16));
       float h1 = silu_mul_bf16(__uint_as_float(gw[i] & 0xFFFF0000u), __uint_as_float(uw[i] & 0xFFFF0000u));
-      amax_bits = max(amax_bits, max(__float_as_uint(h0), __float_as_uint(h1)) & 0x7FFFFFFFu);
+      amax_bits = max(amax_bits, max(__float_as_uint(h0) & 0x7FFFFFFFu, __float_as_uint(h1) & 0x7FFFFFFFu));
       y[2 * i] = round_to_bf16(h0 * s_in);
       y[2 * i + 1] = round_to_bf16(h1 * s_in);
     }

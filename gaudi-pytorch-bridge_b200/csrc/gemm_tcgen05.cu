@@ -84,6 +84,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
     *abort_flag = 0;
     *epi_stop = 0;
     fence_barrier_init();
+    fence_proxy_async_smem();
     tma_prefetch_desc(&map_x);
     tma_prefetch_desc(&map_y);
   }

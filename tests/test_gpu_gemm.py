@@ -84,7 +84,7 @@ def test_transposes_and_odd_sizes(ops, tA, tB, fa, fb, M, N, K):
     D = torch.randn(M, N, generator=g)
     for od in (torch.bfloat16, torch.float32):
         _check(A, tA, B, tB, None, od)
-        _check(A, tA, B, tB, D, od, 0.25, sB, bias, True, [1, N])
+        _check(A, tA, B, tB, D, od, torch.tensor(0.25), sB, bias, True, [1, N])
 
 
 @pytest.mark.parametrize("shapeA,shapeB", [((2, 1, 4, 2), (1, 3, 4, 8)), ((2, 1, 4, 2), (4, 8)), ((4, 2), (3, 4, 8))])
@@ -243,7 +243,7 @@ def test_tcgen05_batch_folds_into_m(ops):
     A = _rand_fp8((3, 5, 64, 128), torch.float8_e4m3fn, g)
     B = _rand_fp8((256, 128), torch.float8_e4m3fn, g)
     bias = torch.randn(256, generator=g)
-    _check(A, False, B, True, None, torch.bfloat16, 0.5, torch.rand(256, generator=g) + 0.5, bias, False, [1, 256])
+    _check(A, False, B, True, None, torch.bfloat16, torch.tensor(0.5), torch.rand(256, generator=g) + 0.5, bias, False, [1, 256])
     _check(A, False, B, True, None, torch.float32, torch.rand(64, 1, generator=g) + 0.5, None, None, False, None, 1e-5)
 
 
@@ -256,17 +256,18 @@ def test_tcgen05_full_size_properties(ops):
     B8 = torch.randn(N, K, device="cuda", generator=g).clamp(-3, 3).mul(100).to(torch.float8_e4m3fn)
     sb = torch.rand(N, device="cuda", generator=g) * 1e-4 + 1e-4
     bias = (torch.randn(N, device="cuda", generator=g) * 0.01).to(torch.bfloat16)
-    r1 = torch.ops.hpu.fp8_gemm_v2(A8, False, B8, True, None, torch.bfloat16, 1e-2, sb, bias, False, [1, N])
-    r2 = torch.ops.hpu.fp8_gemm_v2(A8, False, B8, True, None, torch.bfloat16, 1e-2, sb, bias, False, [1, N])
+    sa = torch.tensor(1e-2, device="cuda")
+    r1 = torch.ops.hpu.fp8_gemm_v2(A8, False, B8, True, None, torch.bfloat16, sa, sb, bias, False, [1, N])
+    r2 = torch.ops.hpu.fp8_gemm_v2(A8, False, B8, True, None, torch.bfloat16, sa, sb, bias, False, [1, N])
     assert torch.equal(r1, r2)
     rows = torch.tensor([0, 1, 127, 128, 2047, 4095])
-    e = O.fp8_gemm_v2(A8[rows].cpu(), False, B8.cpu(), True, None, torch.bfloat16, 1e-2, sb.cpu(), bias.cpu(), False, [1, N])
+    e = O.fp8_gemm_v2(A8[rows].cpu(), False, B8.cpu(), True, None, torch.bfloat16, sa.cpu(), sb.cpu(), bias.cpu(), False, [1, N])
     assert O.rel_frobenius(r1[rows], e) <= TOL
     cols = torch.tensor([0, 255, 256, 7000, 14335])
-    e = O.fp8_gemm_v2(A8.cpu(), False, B8[cols].cpu(), True, None, torch.bfloat16, 1e-2, sb[cols].cpu(), bias[cols].cpu(),
+    e = O.fp8_gemm_v2(A8.cpu(), False, B8[cols].cpu(), True, None, torch.bfloat16, sa.cpu(), sb[cols].cpu(), bias[cols].cpu(),
                       False, [1, len(cols)])
     assert O.rel_frobenius(r1[:, cols], e) <= TOL
     # linearity: doubling the A scale doubles (out - bias)
-    r3 = torch.ops.hpu.fp8_gemm_v2(A8, False, B8, True, None, torch.float32, 2e-2, sb, None, False, [1, N])
-    r4 = torch.ops.hpu.fp8_gemm_v2(A8, False, B8, True, None, torch.float32, 1e-2, sb, None, False, [1, N])
+    r3 = torch.ops.hpu.fp8_gemm_v2(A8, False, B8, True, None, torch.float32, 2 * sa, sb, None, False, [1, N])
+    r4 = torch.ops.hpu.fp8_gemm_v2(A8, False, B8, True, None, torch.float32, sa, sb, None, False, [1, N])
     assert torch.equal(r3, 2 * r4)
