@@ -190,6 +190,107 @@ __global__ void __launch_bounds__(256) cast_to_fp8_kernel(CastParams p) {
   if (p.amax) block_amax_to_global(amax_bits, p.amax);
 }
 
+
+// ------------------------------------------------------------------ bf16 -> fp8, RNE, fast path
+// One scale for the whole chunk (per tensor or per row) and the product formed in bf16: the
+// multiply is one packed bf16x2 instruction per two elements (exact product, one rounding to
+// bf16 -- the same value as an fp32 multiply followed by a rounding to bf16), amax is a packed
+// NaN-propagating max, and the saturating conversion instruction takes care of +-inf and of
+// values beyond the format's maximum.  NaN bytes are made canonical on the packed output.
+__device__ __forceinline__ uint32_t bf16x2_mul(uint32_t a, uint32_t b) {
+  __nv_bfloat162 r = __hmul2(*reinterpret_cast<__nv_bfloat162*>(&a), *reinterpret_cast<__nv_bfloat162*>(&b));
+  return *reinterpret_cast<uint32_t*>(&r);
+}
+__device__ __forceinline__ uint32_t bf16x2_max_nan(uint32_t a, uint32_t b) {
+  __nv_bfloat162 r = __hmax2_nan(*reinterpret_cast<__nv_bfloat162*>(&a), *reinterpret_cast<__nv_bfloat162*>(&b));
+  return *reinterpret_cast<uint32_t*>(&r);
+}
+
+// Replace every NaN code in four packed fp8 bytes by 0x7F.
+template <int FMT>
+__device__ __forceinline__ uint32_t canonical_nan_bytes(uint32_t w) {
+  const uint32_t t = w & 0x7F7F7F7Fu;
+  // e4m3: NaN is 0x7F; e5m2: NaN is 0x7D..0x7F (0x7C, inf, cannot come out of a saturating convert)
+  const uint32_t hit = (t + (FMT == B200Q_E4M3 ? 0x01010101u : 0x03030303u)) & 0x80808080u;
+  if (hit == 0u) return w;
+  const uint32_t bytes = (hit >> 7) * 0xFFu;  // 0xFF in every NaN byte
+  return (w & ~bytes) | (bytes & 0x7F7F7F7Fu);
+}
+
+template <int FMT>
+__device__ __forceinline__ uint4 cast16_bf16_rne(const uint4 a, const uint4 b, uint32_t s2, bool has_scale,
+                                                 uint32_t& amax2) {
+  uint32_t w[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+  uint32_t o[4];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) amax2 = bf16x2_max_nan(amax2, w[i] & 0x7FFF7FFFu);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    uint32_t y0 = has_scale ? bf16x2_mul(w[2 * i], s2) : w[2 * i];
+    uint32_t y1 = has_scale ? bf16x2_mul(w[2 * i + 1], s2) : w[2 * i + 1];
+    uint32_t lo = cvt_fp8x2<FMT>(__uint_as_float(y0 << 16), __uint_as_float(y0 & 0xFFFF0000u));
+    uint32_t hi = cvt_fp8x2<FMT>(__uint_as_float(y1 << 16), __uint_as_float(y1 & 0xFFFF0000u));
+    o[i] = canonical_nan_bytes<FMT>(lo | (hi << 16));
+  }
+  return make_uint4(o[0], o[1], o[2], o[3]);
+}
+
+template <int FMT, bool PER_ROW>
+__global__ void __launch_bounds__(256) cast_bf16_rne_fast_kernel(CastParams p) {
+  const __nv_bfloat16* __restrict__ in = static_cast<const __nv_bfloat16*>(p.in);
+  uint8_t* __restrict__ out = static_cast<uint8_t*>(p.out);
+  const int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const int64_t nthreads = (int64_t)gridDim.x * blockDim.x;
+  const int64_t nvec = p.n / 16;
+  uint32_t s2 = 0;
+  if (!PER_ROW && p.has_scale) {
+    float s = p.scale_from_dev ? __ldg(p.scale) : p.scale_host;
+    s2 = pack_bf16x2(s, s);
+  }
+  uint32_t amax2 = 0;
+  int64_t v = tid;
+  for (; v + nthreads < nvec; v += 2 * nthreads) {  // two independent chunks in flight per thread
+    const int64_t b0 = v * 16, b1 = (v + nthreads) * 16;
+    const uint4* s0 = reinterpret_cast<const uint4*>(in + b0);
+    const uint4* s1 = reinterpret_cast<const uint4*>(in + b1);
+    uint4 a0 = __ldcs(s0), a1 = __ldcs(s0 + 1), c0 = __ldcs(s1), c1 = __ldcs(s1 + 1);
+    uint32_t sa = s2, sc = s2;
+    if (PER_ROW) {
+      float f0 = __ldg(p.scale + b0 / p.cols), f1 = __ldg(p.scale + b1 / p.cols);
+      sa = pack_bf16x2(f0, f0);
+      sc = pack_bf16x2(f1, f1);
+    }
+    __stcs(reinterpret_cast<uint4*>(out + b0), cast16_bf16_rne<FMT>(a0, a1, sa, p.has_scale, amax2));
+    __stcs(reinterpret_cast<uint4*>(out + b1), cast16_bf16_rne<FMT>(c0, c1, sc, p.has_scale, amax2));
+  }
+  for (; v < nvec; v += nthreads) {
+    const int64_t b0 = v * 16;
+    const uint4* s0 = reinterpret_cast<const uint4*>(in + b0);
+    uint4 a0 = __ldcs(s0), a1 = __ldcs(s0 + 1);
+    uint32_t sa = s2;
+    if (PER_ROW) {
+      float f0 = __ldg(p.scale + b0 / p.cols);
+      sa = pack_bf16x2(f0, f0);
+    }
+    __stcs(reinterpret_cast<uint4*>(out + b0), cast16_bf16_rne<FMT>(a0, a1, sa, p.has_scale, amax2));
+  }
+  // tail (fewer than 16 elements)
+  uint32_t amax_bits = max(amax2 << 16, amax2 & 0xFFFF0000u);
+  for (int64_t i = nvec * 16 + tid; i < p.n; i += nthreads) {
+    float x = __bfloat162float(in[i]);
+    amax_bits = max(amax_bits, __float_as_uint(x) & 0x7FFFFFFFu);
+    float y = x;
+    if (p.has_scale) {
+      float s = PER_ROW ? p.scale[i / p.cols] : (p.scale_from_dev ? __ldg(p.scale) : p.scale_host);
+      y = round_to_bf16(x * round_to_bf16(s));
+    }
+    uint32_t b = cvt_fp8x2<FMT>(y, 0.f) & 0xFFu;
+    if (y != y) b = 0x7Fu;
+    out[i] = (uint8_t)b;
+  }
+  if (p.amax) block_amax_to_global(amax_bits, p.amax);
+}
+
 // ------------------------------------------------------------------ cast_from_fp8
 struct UncastParams {
   const uint8_t* in;
@@ -199,6 +300,55 @@ struct UncastParams {
   int has_scale, scale_from_dev;
   int64_t n, cols;
 };
+
+// 8 fp8 bytes -> 8 values of OutT, scaled.  A thread loads 8 bytes and stores 16 (bf16) or 32
+// (fp32) bytes, so that both the loads and the stores of a warp are contiguous.
+template <typename OutT, int FMT, int SC>
+__device__ __forceinline__ void uncast8(const UncastParams& p, OutT* __restrict__ out, int64_t base, uint2 raw,
+                                        float s_one) {
+  constexpr bool BF16 = InTraits<OutT>::kIsBf16;
+  uint32_t w[2] = {raw.x, raw.y};
+  float y[8];
+#pragma unroll
+  for (int i = 0; i < 2; ++i) {
+    // two bytes -> f16x2 in one conversion, then widen
+    __half2_raw h0 = __nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)(w[i] & 0xFFFFu), Fp8Fmt<FMT>::kInterp);
+    __half2_raw h1 = __nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)(w[i] >> 16), Fp8Fmt<FMT>::kInterp);
+    float2 f0 = __half22float2(*reinterpret_cast<__half2*>(&h0));
+    float2 f1 = __half22float2(*reinterpret_cast<__half2*>(&h1));
+    y[4 * i] = f0.x; y[4 * i + 1] = f0.y; y[4 * i + 2] = f1.x; y[4 * i + 3] = f1.y;
+  }
+  if (p.has_scale) {
+    if (SC == SC_COL || SC == SC_FULL) {
+      const float4* sp = reinterpret_cast<const float4*>(p.scale + (SC == SC_COL ? base % p.cols : base));
+#pragma unroll
+      for (int i = 0; i < 2; ++i) {
+        float4 f = __ldg(sp + i);
+        float s4[4] = {f.x, f.y, f.z, f.w};
+#pragma unroll
+        for (int j = 0; j < 4; ++j) y[4 * i + j] *= BF16 ? round_to_bf16(s4[j]) : s4[j];
+      }
+    } else {
+      float sv = s_one;
+      if (SC == SC_ROW) {
+        sv = __ldg(p.scale + base / p.cols);
+        if (BF16) sv = round_to_bf16(sv);
+      }
+#pragma unroll
+      for (int i = 0; i < 8; ++i) y[i] *= sv;
+    }
+  }
+  if (BF16) {
+    __stcs(reinterpret_cast<uint4*>(out + base), make_uint4(pack_bf16x2(y[0], y[1]), pack_bf16x2(y[2], y[3]),
+                                                             pack_bf16x2(y[4], y[5]), pack_bf16x2(y[6], y[7])));
+  } else {
+    float4* dst = reinterpret_cast<float4*>(out + base);
+    __stcs(dst, make_float4(y[0], y[1], y[2], y[3]));
+    __stcs(dst + 1, make_float4(y[4], y[5], y[6], y[7]));
+  }
+}
+
+constexpr int kUncastUnroll = 8;
 
 template <typename OutT, int FMT, int SC>
 __global__ void __launch_bounds__(256) cast_from_fp8_kernel(UncastParams p) {
@@ -211,51 +361,25 @@ __global__ void __launch_bounds__(256) cast_from_fp8_kernel(UncastParams p) {
   if (BF16) s_one = round_to_bf16(s_one);
   const bool aligned = ((reinterpret_cast<uintptr_t>(p.in) | reinterpret_cast<uintptr_t>(out)) & 15) == 0 &&
                        ((SC != SC_FULL && SC != SC_COL) || (reinterpret_cast<uintptr_t>(p.scale) & 15) == 0);
-  const bool col_vec = (SC != SC_COL && SC != SC_ROW) || (p.cols % 16 == 0);
-  const int64_t nvec = (aligned && col_vec) ? p.n / 16 : 0;
+  const bool col_vec = (SC != SC_COL && SC != SC_ROW) || (p.cols % 8 == 0);
+  const int64_t nvec = (aligned && col_vec) ? p.n / 8 : 0;
 
-  for (int64_t v = tid; v < nvec; v += nthreads) {
-    const int64_t base = v * 16;
-    uint4 raw = __ldcs(reinterpret_cast<const uint4*>(p.in + base));
-    uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
-    float y[16];
+  // a block owns kUncastUnroll consecutive runs of 256 x 8 bytes; all loads are issued first
+  const int64_t per_block = (int64_t)blockDim.x * kUncastUnroll;
+  for (int64_t b0 = (int64_t)blockIdx.x * per_block; b0 < nvec; b0 += (int64_t)gridDim.x * per_block) {
+    uint2 r[kUncastUnroll];
 #pragma unroll
-    for (int i = 0; i < 16; ++i) y[i] = fp8_to_float<FMT>((w[i >> 2] >> ((i & 3) * 8)) & 0xFFu);
-    if (p.has_scale) {
-      if (SC == SC_COL || SC == SC_FULL) {
-        const float4* sp = reinterpret_cast<const float4*>(p.scale + (SC == SC_COL ? base % p.cols : base));
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          float4 f = __ldg(sp + i);
-          float s4[4] = {f.x, f.y, f.z, f.w};
-#pragma unroll
-          for (int j = 0; j < 4; ++j) y[4 * i + j] *= BF16 ? round_to_bf16(s4[j]) : s4[j];
-        }
-      } else {
-        float sv = s_one;
-        if (SC == SC_ROW) {
-          sv = __ldg(p.scale + base / p.cols);
-          if (BF16) sv = round_to_bf16(sv);
-        }
-#pragma unroll
-        for (int i = 0; i < 16; ++i) y[i] *= sv;
-      }
+    for (int u = 0; u < kUncastUnroll; ++u) {
+      const int64_t v = b0 + (int64_t)u * blockDim.x + threadIdx.x;
+      r[u] = v < nvec ? __ldcs(reinterpret_cast<const uint2*>(p.in + v * 8)) : make_uint2(0u, 0u);
     }
-    if (BF16) {
-      uint4 o0 = make_uint4(pack_bf16x2(y[0], y[1]), pack_bf16x2(y[2], y[3]), pack_bf16x2(y[4], y[5]),
-                            pack_bf16x2(y[6], y[7]));
-      uint4 o1 = make_uint4(pack_bf16x2(y[8], y[9]), pack_bf16x2(y[10], y[11]), pack_bf16x2(y[12], y[13]),
-                            pack_bf16x2(y[14], y[15]));
-      uint4* dst = reinterpret_cast<uint4*>(out + base);
-      __stcs(dst, o0);
-      __stcs(dst + 1, o1);
-    } else {
-      float4* dst = reinterpret_cast<float4*>(out + base);
 #pragma unroll
-      for (int i = 0; i < 4; ++i) __stcs(dst + i, make_float4(y[4 * i], y[4 * i + 1], y[4 * i + 2], y[4 * i + 3]));
+    for (int u = 0; u < kUncastUnroll; ++u) {
+      const int64_t v = b0 + (int64_t)u * blockDim.x + threadIdx.x;
+      if (v < nvec) uncast8<OutT, FMT, SC>(p, out, v * 8, r[u], s_one);
     }
   }
-  for (int64_t i = nvec * 16 + tid; i < p.n; i += nthreads) {
+  for (int64_t i = nvec * 8 + tid; i < p.n; i += nthreads) {
     float y = fp8_to_float<FMT>(p.in[i]);
     if (p.has_scale) {
       float s = SC == SC_ONE ? s_one : SC == SC_COL ? p.scale[i % p.cols] : SC == SC_ROW ? p.scale[i / p.cols]
@@ -318,28 +442,39 @@ __global__ void __launch_bounds__(256) swiglu_cast_kernel(SwigluParams p) {
 }
 
 // ------------------------------------------------------------------ host launchers
-static int grid_for(int64_t n_items) {
+// Grid for the grid-stride kernels: one block per 256 work items up to 16 times the number of
+// blocks that are resident at once, so that the block scheduler balances the SMs to within a
+// sixteenth of a wave whatever the size.
+template <typename Kernel>
+static int grid_for(Kernel kernel, int64_t n_items) {
+  int per_sm = 0;
+  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, 256, 0) != cudaSuccess || per_sm < 1) per_sm = 4;
   int64_t blocks = (n_items + 255) / 256;
-  int64_t cap = (int64_t)kNumSMs * 8;  // 2048 resident threads per SM
+  int64_t cap = (int64_t)kNumSMs * per_sm * 16;
   if (blocks > cap) blocks = cap;
   if (blocks < 1) blocks = 1;
   return (int)blocks;
 }
 
+template <typename Kernel, typename Params>
+static void launch_persistent(Kernel kernel, int64_t items, cudaStream_t st, const Params& p) {
+  kernel<<<grid_for(kernel, items), 256, 0, st>>>(p);
+}
+
 template <typename InT, int FMT, bool SR>
-static void launch_cast_sc(int sc, int grid, cudaStream_t st, const CastParams& p) {
+static void launch_cast_sc(int sc, int64_t items, cudaStream_t st, const CastParams& p) {
   switch (sc) {
-    case SC_ONE: cast_to_fp8_kernel<InT, FMT, SR, SC_ONE><<<grid, 256, 0, st>>>(p); break;
-    case SC_COL: cast_to_fp8_kernel<InT, FMT, SR, SC_COL><<<grid, 256, 0, st>>>(p); break;
-    case SC_ROW: cast_to_fp8_kernel<InT, FMT, SR, SC_ROW><<<grid, 256, 0, st>>>(p); break;
-    default: cast_to_fp8_kernel<InT, FMT, SR, SC_FULL><<<grid, 256, 0, st>>>(p); break;
+    case SC_ONE: launch_persistent(cast_to_fp8_kernel<InT, FMT, SR, SC_ONE>, items, st, p); break;
+    case SC_COL: launch_persistent(cast_to_fp8_kernel<InT, FMT, SR, SC_COL>, items, st, p); break;
+    case SC_ROW: launch_persistent(cast_to_fp8_kernel<InT, FMT, SR, SC_ROW>, items, st, p); break;
+    default: launch_persistent(cast_to_fp8_kernel<InT, FMT, SR, SC_FULL>, items, st, p); break;
   }
 }
 
 template <typename InT, int FMT>
-static void launch_cast_sr(bool sr, int sc, int grid, cudaStream_t st, const CastParams& p) {
-  if (sr) launch_cast_sc<InT, FMT, true>(sc, grid, st, p);
-  else launch_cast_sc<InT, FMT, false>(sc, grid, st, p);
+static void launch_cast_sr(bool sr, int sc, int64_t items, cudaStream_t st, const CastParams& p) {
+  if (sr) launch_cast_sc<InT, FMT, true>(sc, items, st, p);
+  else launch_cast_sc<InT, FMT, false>(sc, items, st, p);
 }
 
 static int scale_class(int mode) {
@@ -369,26 +504,39 @@ int cast_to_fp8_impl(const void* in, int in_dtype, void* out, int out_dtype, con
   p.n = n; p.cols = cols; p.amax = amax; p.seed = seed; p.offset = offset; p.first_index = first_index;
   p.mul_fp32 = (flags & B200Q_CAST_MUL_IN_FP32) ? 1 : 0;
   const int sc = scale_class(scale_mode);
-  const int grid = grid_for((n + 15) / 16);
+  const int64_t items = (n + 15) / 16;
   const bool sr = rounding == B200Q_ROUND_STOCHASTIC;
-  if (in_dtype == B200Q_BF16) {
-    if (out_dtype == B200Q_E4M3) launch_cast_sr<__nv_bfloat16, B200Q_E4M3>(sr, sc, grid, st, p);
-    else launch_cast_sr<__nv_bfloat16, B200Q_E5M2>(sr, sc, grid, st, p);
+  // fast path: bf16 input, RNE, product in bf16, one scale per 16-element chunk, aligned pointers
+  const bool aligned = ((reinterpret_cast<uintptr_t>(in) | reinterpret_cast<uintptr_t>(out)) & 15) == 0;
+  const bool fast = in_dtype == B200Q_BF16 && !sr && !p.mul_fp32 && aligned &&
+                    (sc == SC_ONE || (sc == SC_ROW && cols % 16 == 0));
+  if (fast) {
+    const int64_t half = (items + 1) / 2;  // two chunks per thread and step
+    if (out_dtype == B200Q_E4M3) {
+      if (sc == SC_ROW) launch_persistent(cast_bf16_rne_fast_kernel<B200Q_E4M3, true>, half, st, p);
+      else launch_persistent(cast_bf16_rne_fast_kernel<B200Q_E4M3, false>, half, st, p);
+    } else {
+      if (sc == SC_ROW) launch_persistent(cast_bf16_rne_fast_kernel<B200Q_E5M2, true>, half, st, p);
+      else launch_persistent(cast_bf16_rne_fast_kernel<B200Q_E5M2, false>, half, st, p);
+    }
+  } else if (in_dtype == B200Q_BF16) {
+    if (out_dtype == B200Q_E4M3) launch_cast_sr<__nv_bfloat16, B200Q_E4M3>(sr, sc, items, st, p);
+    else launch_cast_sr<__nv_bfloat16, B200Q_E5M2>(sr, sc, items, st, p);
   } else {
-    if (out_dtype == B200Q_E4M3) launch_cast_sr<float, B200Q_E4M3>(sr, sc, grid, st, p);
-    else launch_cast_sr<float, B200Q_E5M2>(sr, sc, grid, st, p);
+    if (out_dtype == B200Q_E4M3) launch_cast_sr<float, B200Q_E4M3>(sr, sc, items, st, p);
+    else launch_cast_sr<float, B200Q_E5M2>(sr, sc, items, st, p);
   }
   B200Q_LAUNCH_CHECK();
   return B200Q_OK;
 }
 
 template <typename OutT, int FMT>
-static void launch_uncast_sc(int sc, int grid, cudaStream_t st, const UncastParams& p) {
+static void launch_uncast_sc(int sc, int64_t items, cudaStream_t st, const UncastParams& p) {
   switch (sc) {
-    case SC_ONE: cast_from_fp8_kernel<OutT, FMT, SC_ONE><<<grid, 256, 0, st>>>(p); break;
-    case SC_COL: cast_from_fp8_kernel<OutT, FMT, SC_COL><<<grid, 256, 0, st>>>(p); break;
-    case SC_ROW: cast_from_fp8_kernel<OutT, FMT, SC_ROW><<<grid, 256, 0, st>>>(p); break;
-    default: cast_from_fp8_kernel<OutT, FMT, SC_FULL><<<grid, 256, 0, st>>>(p); break;
+    case SC_ONE: launch_persistent(cast_from_fp8_kernel<OutT, FMT, SC_ONE>, items, st, p); break;
+    case SC_COL: launch_persistent(cast_from_fp8_kernel<OutT, FMT, SC_COL>, items, st, p); break;
+    case SC_ROW: launch_persistent(cast_from_fp8_kernel<OutT, FMT, SC_ROW>, items, st, p); break;
+    default: launch_persistent(cast_from_fp8_kernel<OutT, FMT, SC_FULL>, items, st, p); break;
   }
 }
 
@@ -402,13 +550,13 @@ int cast_from_fp8_impl(const void* in, int in_dtype, void* out, int out_dtype, c
   p.scale_from_dev = scale_mode == B200Q_BCAST_SCALAR_DEV;
   p.n = n; p.cols = cols;
   const int sc = scale_class(scale_mode);
-  const int grid = grid_for((n + 15) / 16);
+  const int64_t items = ((n + 7) / 8 + kUncastUnroll - 1) / kUncastUnroll;  // 8-byte items, kUncastUnroll per thread and step
   if (out_dtype == B200Q_BF16) {
-    if (in_dtype == B200Q_E4M3) launch_uncast_sc<__nv_bfloat16, B200Q_E4M3>(sc, grid, st, p);
-    else launch_uncast_sc<__nv_bfloat16, B200Q_E5M2>(sc, grid, st, p);
+    if (in_dtype == B200Q_E4M3) launch_uncast_sc<__nv_bfloat16, B200Q_E4M3>(sc, items, st, p);
+    else launch_uncast_sc<__nv_bfloat16, B200Q_E5M2>(sc, items, st, p);
   } else {
-    if (in_dtype == B200Q_E4M3) launch_uncast_sc<float, B200Q_E4M3>(sc, grid, st, p);
-    else launch_uncast_sc<float, B200Q_E5M2>(sc, grid, st, p);
+    if (in_dtype == B200Q_E4M3) launch_uncast_sc<float, B200Q_E4M3>(sc, items, st, p);
+    else launch_uncast_sc<float, B200Q_E5M2>(sc, items, st, p);
   }
   B200Q_LAUNCH_CHECK();
   return B200Q_OK;
@@ -425,7 +573,7 @@ int swiglu_cast_impl(const void* gate, int64_t ld_gate, const void* up, int64_t 
   p.gate = static_cast<const __nv_bfloat16*>(gate); p.up = static_cast<const __nv_bfloat16*>(up);
   p.out = static_cast<uint8_t*>(out); p.ld_gate = ld_gate; p.ld_up = ld_up; p.rows = rows; p.cols = cols;
   p.scale = scale; p.amax = amax;
-  swiglu_cast_kernel<<<grid_for(rows * cols / 16), 256, 0, st>>>(p);
+  swiglu_cast_kernel<<<grid_for(swiglu_cast_kernel, rows * cols / 16), 256, 0, st>>>(p);
   B200Q_LAUNCH_CHECK();
   return B200Q_OK;
 }

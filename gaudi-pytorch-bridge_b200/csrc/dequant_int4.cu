@@ -105,6 +105,89 @@ __device__ __forceinline__ void expand_word(uint32_t w, const float* s, int zp_k
   }
 }
 
+
+// ---- packed bf16x2 expansion (bf16 output, packed or no zero point) --------------------------
+// A nibble q OR-ed into the mantissa of the bf16 constant 128.0 (0x4300) is exactly 128 + q, so
+// two nibbles become a bf16x2 with one shift and one logic op, (128+q) - (128+z) is exact, and
+// the product with the bf16 scale is a single bf16x2 multiply with one rounding: the same value
+// as (q - z) converted to bf16 and multiplied by the scale in bf16.
+// Pair i of a word holds nibbles i and i+4 (low / high half).
+template <bool SIGNED>
+__device__ __forceinline__ uint32_t nib_pair(uint32_t w, int i) {
+  // signed: (q ^ 8) is q + 8 for the two's-complement nibble, and 0x4308 is 128 + 8
+  return SIGNED ? (((w >> (4 * i)) & 0x000F000Fu) ^ 0x43084308u) : (((w >> (4 * i)) & 0x000F000Fu) | 0x43004300u);
+}
+__device__ __forceinline__ uint32_t bf2_sub(uint32_t a, uint32_t b) {
+  __nv_bfloat162 r = __hsub2(*reinterpret_cast<__nv_bfloat162*>(&a), *reinterpret_cast<__nv_bfloat162*>(&b));
+  return *reinterpret_cast<uint32_t*>(&r);
+}
+__device__ __forceinline__ uint32_t bf2_mul(uint32_t a, uint32_t b) {
+  __nv_bfloat162 r = __hmul2(*reinterpret_cast<__nv_bfloat162*>(&a), *reinterpret_cast<__nv_bfloat162*>(&b));
+  return *reinterpret_cast<uint32_t*>(&r);
+}
+
+// Scales / zero references of one group, re-paired to (i, i+4) order once per group.
+struct GroupBf2 {
+  uint32_t sp[4];  // {s_i, s_{i+4}}
+  uint32_t zr[4];  // {128 + z_i, 128 + z_{i+4}} (or the plain offset when there is no zero point)
+};
+
+template <bool SIGNED>
+__device__ __forceinline__ void load_group_bf2(GroupBf2& g, const __nv_bfloat16* scale8, bool has_zp, uint32_t zw) {
+  uint4 s = __ldg(reinterpret_cast<const uint4*>(scale8));  // s0..s7 in natural order
+  g.sp[0] = __byte_perm(s.x, s.z, 0x5410);  // {s0, s4}
+  g.sp[1] = __byte_perm(s.x, s.z, 0x7632);  // {s1, s5}
+  g.sp[2] = __byte_perm(s.y, s.w, 0x5410);  // {s2, s6}
+  g.sp[3] = __byte_perm(s.y, s.w, 0x7632);  // {s3, s7}
+#pragma unroll
+  for (int i = 0; i < 4; ++i) g.zr[i] = has_zp ? nib_pair<SIGNED>(zw, i) : (SIGNED ? 0x43084308u : 0x43004300u);
+}
+
+template <bool SIGNED>
+__device__ __forceinline__ uint4 expand_word_bf2(uint32_t w, const GroupBf2& g) {
+  uint32_t o[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) o[i] = bf2_mul(bf2_sub(nib_pair<SIGNED>(w, i), g.zr[i]), g.sp[i]);  // {o_i, o_{i+4}}
+  return make_uint4(__byte_perm(o[0], o[1], 0x5410), __byte_perm(o[2], o[3], 0x5410),   // o0 o1 | o2 o3
+                    __byte_perm(o[0], o[1], 0x7632), __byte_perm(o[2], o[3], 0x7632));  // o4 o5 | o6 o7
+}
+
+constexpr int kFastRows = 16;
+
+// bf16 output, operator layout, 16-byte aligned everything: one thread expands one packed word
+// of each of kFastRows consecutive rows (all loads issued before the first use).
+template <bool SIGNED>
+__global__ void __launch_bounds__(256) dequant_rowpacked_bf16_kernel(DequantParams p) {
+  const int64_t bx = blockIdx.x % p.col_blocks, by = blockIdx.x / p.col_blocks;
+  const int64_t cp = bx * blockDim.x + threadIdx.x;
+  if (cp >= p.cols_packed) return;
+  const int64_t cols = p.cols_packed * 8;
+  const __nv_bfloat16* scale = static_cast<const __nv_bfloat16*>(p.scale);
+  __nv_bfloat16* out = static_cast<__nv_bfloat16*>(p.out);
+  const int64_t r0 = by * kFastRows;
+  uint32_t w[kFastRows];
+#pragma unroll
+  for (int j = 0; j < kFastRows; ++j) {
+    int64_t r = r0 + j;
+    w[j] = r < p.rows ? (uint32_t)__ldcs(p.packed + r * p.cols_packed + cp) : 0u;
+  }
+  int64_t last_sr = -1;
+  GroupBf2 g;
+#pragma unroll
+  for (int j = 0; j < kFastRows; ++j) {
+    int64_t r = r0 + j;
+    if (r >= p.rows) break;
+    int64_t sr = r / p.group_rows;
+    if (sr != last_sr) {
+      uint32_t zw = 0;
+      if (p.zp_kind == B200Q_ZP_PACKED) zw = (uint32_t)__ldg(static_cast<const int32_t*>(p.zp) + sr * p.cols_packed + cp);
+      load_group_bf2<SIGNED>(g, scale + sr * cols + cp * 8, p.zp_kind == B200Q_ZP_PACKED, zw);
+      last_sr = sr;
+    }
+    __stcs(reinterpret_cast<uint4*>(out + r * cols + cp * 8), expand_word_bf2<SIGNED>(w[j], g));
+  }
+}
+
 constexpr int kRowsPerBlock = 8;
 
 // Operator layout: packed [rows][cols_packed] -> out [rows][8*cols_packed].
@@ -195,7 +278,15 @@ int dequant_int4_impl(const int32_t* packed, const void* scale, const void* zp, 
   DequantParams p;
   p.packed = packed; p.scale = scale; p.zp = zp; p.out = out; p.rows = rows; p.cols_packed = cols_packed;
   p.scale_rows = scale_rows; p.group_rows = rows / scale_rows; p.zp_kind = zp_kind; p.is_signed = is_signed;
-  if (!k_packed) {
+  const bool all_aligned = ((reinterpret_cast<uintptr_t>(out) | reinterpret_cast<uintptr_t>(scale) |
+                              reinterpret_cast<uintptr_t>(packed)) & 15) == 0;
+  if (!k_packed && out_dtype == B200Q_BF16 && zp_kind != B200Q_ZP_FLOAT && all_aligned) {
+    p.col_blocks = (cols_packed + 255) / 256;
+    const int64_t nblk = p.col_blocks * ((rows + kFastRows - 1) / kFastRows);
+    if (nblk > 0x7FFFFFFFll) return B200Q_ERR_TOO_LARGE;
+    if (is_signed) dequant_rowpacked_bf16_kernel<true><<<(unsigned)nblk, 256, 0, st>>>(p);
+    else dequant_rowpacked_bf16_kernel<false><<<(unsigned)nblk, 256, 0, st>>>(p);
+  } else if (!k_packed) {
     p.col_blocks = (cols_packed + 255) / 256;
     const int64_t nblk = p.col_blocks * ((rows + kRowsPerBlock - 1) / kRowsPerBlock);
     if (nblk > 0x7FFFFFFFll) return B200Q_ERR_TOO_LARGE;
