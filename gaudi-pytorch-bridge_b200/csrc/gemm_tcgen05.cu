@@ -19,6 +19,7 @@
 #include "common.cuh"
 #include "gemm_common.cuh"
 #include "tcgen05_ptx.cuh"
+#include "tma_host.cuh"
 
 namespace b200q {
 
@@ -294,37 +295,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
 }
 
 // ------------------------------------------------------------------------ host side
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-static EncodeTiledFn get_encode_fn() {
-  static EncodeTiledFn fn = nullptr;
-  static std::atomic<int> tried{0};
-  if (!tried.load(std::memory_order_acquire)) {
-    void* sym = nullptr;
-    cudaDriverEntryPointQueryResult qres;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &qres) == cudaSuccess &&
-        qres == cudaDriverEntryPointSuccess)
-      fn = reinterpret_cast<EncodeTiledFn>(sym);
-    tried.store(1, std::memory_order_release);
-  }
-  return fn;
-}
-
 // 2-D map over a row-major byte matrix [rows][kbytes] with row stride ld bytes; box = 128 bytes x box_rows.
 int make_operand_map(CUtensorMap* map, const void* base, int64_t rows, int64_t kbytes, int64_t ld_bytes,
                      int box_rows) {
-  EncodeTiledFn enc = get_encode_fn();
-  if (!enc) return B200Q_ERR_CUDA;
-  cuuint64_t dims[2] = {(cuuint64_t)kbytes, (cuuint64_t)rows};
-  cuuint64_t strides[1] = {(cuuint64_t)ld_bytes};
-  cuuint32_t box[2] = {(cuuint32_t)kBlockK, (cuuint32_t)box_rows};
-  cuuint32_t estr[2] = {1, 1};
-  CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, estr,
-                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  return r == CUDA_SUCCESS ? B200Q_OK : B200Q_ERR_CUDA;
+  return make_tma_map_2d(map, base, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, kbytes, rows, ld_bytes, kBlockK, box_rows,
+                         CU_TENSOR_MAP_SWIZZLE_128B);
 }
 
 template <int BN, int STAGES, bool SWAP>

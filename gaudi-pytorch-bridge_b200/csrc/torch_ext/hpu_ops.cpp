@@ -588,9 +588,13 @@ at::Tensor w4a16_gemm(const at::Tensor& x, const at::Tensor& qweight, const at::
     zp_kind = B200Q_ZP_PACKED;
   }
   at::Tensor out = at::empty({M, N}, xc.options().dtype(out_dtype));
+  const size_t ws_bytes = b200q_w4a16_workspace_bytes(M, N, K);
+  at::Tensor ws;
+  if (ws_bytes) ws = at::empty({(int64_t)ws_bytes}, xc.options().dtype(at::kByte));
   check_status(b200q_w4a16_gemm(xc.data_ptr(), K, q.data_ptr<int32_t>(), sc.data_ptr(),
                                 zp.defined() ? zp.data_ptr<int32_t>() : nullptr, zp_kind, k_packed ? 1 : 0, M, N, K,
-                                group_size, out.data_ptr(), to_b200q_dtype(out_dtype), N, current_stream()),
+                                group_size, out.data_ptr(), to_b200q_dtype(out_dtype), N,
+                                ws_bytes ? ws.data_ptr() : nullptr, ws_bytes, current_stream()),
                "w4a16_gemm");
   return out;
 }

@@ -1,9 +1,516 @@
-// W4A16 GEMM (placeholder until the fused kernel lands in this file).
+// W4A16 GEMM: out[M][N] = x[M][K] (bf16) . W[K][N], W = (nibble - zero_point) * scale held as
+// packed 4-bit words [K][N/8] with group scales -- the dequantisation is fused into the staging
+// of the weight operand, so the bf16 weights never exist in global memory.
+//
+// Warp-specialised, persistent:
+//   warp 0        TMA producer: activation tile (bf16, 128-byte swizzle) and the raw packed-weight
+//                 tile into a shared-memory ring.  The weight tile is fetched through a 3-D
+//                 tensor map that views K as (k / 8, k % 8) and lands in shared memory as
+//                 row (k % 8) * 8 + k / 8 with the hardware swizzle on, which is what lets the
+//                 expanders read it without bank conflicts (see the expander section)
+//   warps 6..     expanders (4 warps per 128 weight columns): read packed words from the ring,
+//                 expand with packed bf16x2 arithmetic ((128+q)-(128+z) exact, one rounding in the
+//                 multiply by the scale: bit-identical to the stand-alone dequant kernel), transpose
+//                 8x8 in registers and write K-major, 128-byte-swizzled bf16 tiles, then
+//                 fence.proxy.async + mbarrier arrive
+//   warp 1        MMA issuer: tcgen05.mma.kind::f16 (bf16 x bf16 -> fp32 in TMEM)
+//   warps 2..5    epilogue: tcgen05.ld, convert, store (or fp32 partials for split-K)
+//
+// SWAP = false (large M): lanes <- 128 tokens, columns <- BN weight columns.
+// SWAP = true  (small M): lanes <- 128 weight columns, columns <- BN tokens; K is split over
+//              several CTAs per tile so that every SM streams weights, and the fp32 partial
+//              tiles are summed by a second kernel (deterministic: no atomics).
+#include <cuda.h>
+
 #include "common.cuh"
+#include "tcgen05_ptx.cuh"
+#include "tma_host.cuh"
 
 namespace b200q {
-int w4a16_gemm_impl(const void*, int64_t, const int32_t*, const void*, const int32_t*, int, int, int64_t, int64_t,
-                    int64_t, int64_t, void*, int, int64_t, cudaStream_t) {
-  return B200Q_ERR_UNSUPPORTED;
+
+using namespace ptx;
+
+namespace w4 {
+
+constexpr int kK = 64;               // k per ring stage: 64 bf16 = one 128-byte swizzle row
+constexpr int kUmmaKBytes = 32;      // 16 bf16 per tcgen05.mma.kind::f16
+constexpr int kUnit = 128;           // weight columns expanded by one 4-warp group per stage
+constexpr int kRawUnit = kK * 64;    // packed words of one unit and stage: 64 k-rows x 16 words
+constexpr int kEpiThreads = 128;
+
+enum { kErrProducer = 201, kErrMma = 202, kErrMmaTmem = 203, kErrEpilogue = 204, kErrExpand = 205 };
+
+struct Params {
+  const __nv_bfloat16* scale;  // [K/group][N]
+  const int32_t* zp;           // [K/group][N/8] or null
+  void* out;                   // [M][N] out_dtype (splits == 1)
+  float* partial;              // [splits][M][N] fp32 (splits > 1)
+  int64_t M, N, K, ldo;
+  int group, out_dtype;
+  int x_tiles, y_tiles, num_kb, splits, kb_per_split;
+  int* status;
+};
+
+template <int BN, bool SWAP, int STAGES, int NWBUF>
+struct Cfg {
+  static constexpr int kUnits = SWAP ? 1 : BN / kUnit;
+  static constexpr int kActRows = SWAP ? BN : 128;
+  static constexpr int kActBytes = kActRows * 128;
+  static constexpr int kRawBytes = kUnits * kRawUnit;
+  static constexpr int kStageBytes = ((kActBytes + kRawBytes + 1023) / 1024) * 1024;
+  static constexpr int kTxBytes = kActBytes + kRawBytes;
+  static constexpr int kRawRowBytes = kUnits * 64;  // 64 (64-byte swizzle) or 128 (128-byte swizzle)
+  static constexpr int kWBufBytes = kUnits * kUnit * 128;
+  static constexpr int kRing = STAGES * kStageBytes;
+  static constexpr int kWOffset = kRing;
+  static constexpr int kBarOffset = kWOffset + NWBUF * kWBufBytes;
+  static constexpr int kNumBars = 2 * STAGES + 2 * NWBUF + 4;
+  static constexpr int kTotal = kBarOffset + kNumBars * 8 + 16;
+  static constexpr int kExpandWarps = 4 * kUnits;
+  static constexpr int kThreads = 32 * (6 + kExpandWarps);
+  static constexpr uint32_t kTmemCols = (2 * BN) < 32 ? 32 : 2 * BN;
+};
+
+__device__ __forceinline__ uint32_t lds32(uint32_t addr) {
+  uint32_t v;
+  asm volatile("ld.shared.b32 %0, [%1];" : "=r"(v) : "r"(addr));
+  return v;
 }
+__device__ __forceinline__ void sts128(uint32_t addr, uint32_t a, uint32_t b, uint32_t c, uint32_t d) {
+  asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(addr), "r"(a), "r"(b), "r"(c), "r"(d) : "memory");
+}
+__device__ __forceinline__ uint32_t bf2_sub(uint32_t a, uint32_t b) {
+  __nv_bfloat162 r = __hsub2(*reinterpret_cast<__nv_bfloat162*>(&a), *reinterpret_cast<__nv_bfloat162*>(&b));
+  return *reinterpret_cast<uint32_t*>(&r);
+}
+__device__ __forceinline__ uint32_t bf2_mul(uint32_t a, uint32_t b) {
+  __nv_bfloat162 r = __hmul2(*reinterpret_cast<__nv_bfloat162*>(&a), *reinterpret_cast<__nv_bfloat162*>(&b));
+  return *reinterpret_cast<uint32_t*>(&r);
+}
+// nibbles i and i+4 of a word as the bf16x2 {128 + q_i, 128 + q_{i+4}}
+__device__ __forceinline__ uint32_t nib_pair(uint32_t w, int i) {
+  return ((w >> (4 * i)) & 0x000F000Fu) | 0x43004300u;
+}
+
+struct GroupRegs {
+  uint32_t sp[4];  // {s_i, s_{i+4}}
+  uint32_t zr[4];  // {128 + z_i, 128 + z_{i+4}}
+};
+__device__ __forceinline__ void make_group(GroupRegs& g, uint4 s, uint32_t zw, bool has_zp) {
+  g.sp[0] = __byte_perm(s.x, s.z, 0x5410);
+  g.sp[1] = __byte_perm(s.x, s.z, 0x7632);
+  g.sp[2] = __byte_perm(s.y, s.w, 0x5410);
+  g.sp[3] = __byte_perm(s.y, s.w, 0x7632);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) g.zr[i] = has_zp ? nib_pair(zw, i) : 0x43004300u;
+}
+
+template <int BN, bool SWAP, int STAGES, int NWBUF>
+__global__ void __launch_bounds__((Cfg<BN, SWAP, STAGES, NWBUF>::kThreads), 1)
+w4a16_kernel(const __grid_constant__ CUtensorMap map_act, const __grid_constant__ CUtensorMap map_raw, const Params p) {
+  using C = Cfg<BN, SWAP, STAGES, NWBUF>;
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::kBarOffset);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + C::kNumBars);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  volatile int* epi_stop = reinterpret_cast<volatile int*>(tmem_slot + 2);
+
+  const uint32_t smem_base = smem_u32(smem);
+  const uint32_t wbuf_base = smem_base + C::kWOffset;
+  const uint32_t bar_full = smem_u32(bars), bar_empty = bar_full + 8 * STAGES;
+  const uint32_t bar_wready = bar_empty + 8 * STAGES, bar_wfree = bar_wready + 8 * NWBUF;
+  const uint32_t bar_tfull = bar_wfree + 8 * NWBUF, bar_tempty = bar_tfull + 16;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(bar_full + 8 * s, 1);
+      mbar_init(bar_empty + 8 * s, 1);
+    }
+    for (int b = 0; b < NWBUF; ++b) {
+      mbar_init(bar_wready + 8 * b, C::kExpandWarps * 32);
+      mbar_init(bar_wfree + 8 * b, 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(bar_tfull + 8 * a, 1);
+      mbar_init(bar_tempty + 8 * a, kEpiThreads);
+    }
+    *abort_flag = 0;
+    *epi_stop = 0;
+    fence_barrier_init();
+    fence_proxy_async_smem();
+    tma_prefetch_desc(&map_act);
+    tma_prefetch_desc(&map_raw);
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(tmem_slot), C::kTmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const int num_work = p.x_tiles * p.y_tiles * p.splits;
+  // work item -> (lane-side tile, column-side tile, k range); consecutive items share a tile
+  auto decode = [&](int w, int& xt, int& yt, int& kb0, int& kb1, int& split) {
+    split = w % p.splits;
+    const int tile = w / p.splits;
+    xt = tile % p.x_tiles;
+    yt = tile / p.x_tiles;
+    kb0 = split * p.kb_per_split;
+    kb1 = min(p.num_kb, kb0 + p.kb_per_split);
+  };
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
+    if (lane == 0) {
+      uint32_t stage = 0, phase = 0;
+      bool ok = true;
+      for (int w = blockIdx.x; w < num_work && ok; w += gridDim.x) {
+        int xt, yt, kb0, kb1, split;
+        decode(w, xt, yt, kb0, kb1, split);
+        const int act_row0 = (SWAP ? yt * BN : xt * 128);
+        const int n0 = (SWAP ? xt * 128 : yt * BN);
+        for (int kb = kb0; kb < kb1; ++kb) {
+          if (!mbar_wait(bar_empty + 8 * stage, phase ^ 1, abort_flag, p.status, kErrProducer)) {
+            ok = false;
+            break;
+          }
+          const uint32_t full = bar_full + 8 * stage;
+          const uint32_t sbase = smem_base + stage * C::kStageBytes;
+          mbar_arrive_expect_tx(full, C::kTxBytes);
+          tma_load_2d(sbase, &map_act, full, kb * kK, act_row0);
+          tma_load_3d(sbase + C::kActBytes, &map_raw, full, n0 / 8, kb * (kK / 8), 0);
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer
+    if (lane == 0) {
+      const uint32_t idesc = umma_idesc(1u, 1u, 128, BN);  // bf16 x bf16
+      uint32_t stage = 0, phase = 0, wb = 0, wphase = 0;
+      int it = 0;
+      bool ok = true;
+      for (int w = blockIdx.x; w < num_work && ok; w += gridDim.x, ++it) {
+        int xt, yt, kb0, kb1, split;
+        decode(w, xt, yt, kb0, kb1, split);
+        const uint32_t acc = it & 1, acc_phase = (it >> 1) & 1;
+        if (!mbar_wait(bar_tempty + 8 * acc, acc_phase ^ 1, abort_flag, p.status, kErrMmaTmem)) break;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = kb0; kb < kb1; ++kb) {
+          if (!mbar_wait(bar_full + 8 * stage, phase, abort_flag, p.status, kErrMma) ||
+              !mbar_wait(bar_wready + 8 * wb, wphase, abort_flag, p.status, kErrMma)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t act = smem_base + stage * C::kStageBytes, wt = wbuf_base + wb * C::kWBufBytes;
+          const uint32_t xs = SWAP ? wt : act, ys = SWAP ? act : wt;
+#pragma unroll
+          for (int k = 0; k < 128 / kUmmaKBytes; ++k)
+            umma_f16(d_tmem, smem_desc_k_sw128(xs + k * kUmmaKBytes), smem_desc_k_sw128(ys + k * kUmmaKBytes), idesc,
+                     (kb != kb0 || k != 0) ? 1u : 0u);
+          umma_commit(bar_empty + 8 * stage);
+          umma_commit(bar_wfree + 8 * wb);
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+          if (++wb == NWBUF) { wb = 0; wphase ^= 1; }
+        }
+        if (ok) umma_commit(bar_tfull + 8 * acc);
+      }
+    }
+  } else if (warp < 6) {
+    // ------------------------------------------------------------ epilogue (warps 2..5)
+    const int q = warp & 3;
+    const int et = threadIdx.x - 64;
+    int it = 0;
+    for (int w = blockIdx.x; w < num_work; w += gridDim.x, ++it) {
+      int xt, yt, kb0, kb1, split;
+      decode(w, xt, yt, kb0, kb1, split);
+      const uint32_t acc = it & 1, acc_phase = (it >> 1) & 1;
+      mbar_wait(bar_tfull + 8 * acc, acc_phase, abort_flag, p.status, kErrEpilogue);
+      named_bar_sync(1, kEpiThreads);
+      if (et == 0) *epi_stop = *abort_flag;
+      named_bar_sync(1, kEpiThreads);
+      if (*epi_stop) break;
+      tc_fence_after();
+      const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16) + acc * BN;
+      const int64_t x = (int64_t)xt * 128 + q * 32 + lane;  // lane-side index: token (normal) or column n (swap)
+      const int64_t y0 = (int64_t)yt * BN;
+      constexpr int CW = (BN % 32 == 0) ? 32 : 16;
+#pragma unroll 1
+      for (int c0 = 0; c0 < BN; c0 += 32) {
+        uint32_t r[32];
+        if (BN % 32 == 0) tmem_ld_32x32(t_row + c0, r);
+        else tmem_ld_32x16(t_row + c0, r);
+        tmem_ld_wait();
+        if (!SWAP) {
+          const int64_t m = x, n0 = y0 + c0;
+          if (m < p.M) {
+            if (p.splits > 1) {
+              float* o = p.partial + ((int64_t)split * p.M + m) * p.N + n0;
+#pragma unroll
+              for (int j = 0; j < CW; ++j)
+                if (n0 + j < p.N) o[j] = __uint_as_float(r[j]);
+            } else if (p.out_dtype == B200Q_BF16) {
+              __nv_bfloat16* o = static_cast<__nv_bfloat16*>(p.out) + m * p.ldo + n0;
+              if (n0 + CW <= p.N && (reinterpret_cast<uintptr_t>(o) & 15) == 0) {
+#pragma unroll
+                for (int j = 0; j < CW; j += 8)
+                  *reinterpret_cast<uint4*>(o + j) = make_uint4(
+                      pack_bf16x2(__uint_as_float(r[j]), __uint_as_float(r[j + 1])),
+                      pack_bf16x2(__uint_as_float(r[j + 2]), __uint_as_float(r[j + 3])),
+                      pack_bf16x2(__uint_as_float(r[j + 4]), __uint_as_float(r[j + 5])),
+                      pack_bf16x2(__uint_as_float(r[j + 6]), __uint_as_float(r[j + 7])));
+              } else {
+#pragma unroll
+                for (int j = 0; j < CW; ++j)
+                  if (n0 + j < p.N) o[j] = __float2bfloat16_rn(__uint_as_float(r[j]));
+              }
+            } else {
+              float* o = static_cast<float*>(p.out) + m * p.ldo + n0;
+#pragma unroll
+              for (int j = 0; j < CW; ++j)
+                if (n0 + j < p.N) o[j] = __uint_as_float(r[j]);
+            }
+          }
+        } else {
+          const int64_t n = x;
+          if (n < p.N) {
+#pragma unroll
+            for (int j = 0; j < CW; ++j) {
+              const int64_t m = y0 + c0 + j;
+              if (m < p.M) {
+                const float v = __uint_as_float(r[j]);
+                if (p.splits > 1) p.partial[((int64_t)split * p.M + m) * p.N + n] = v;
+                else if (p.out_dtype == B200Q_BF16) static_cast<__nv_bfloat16*>(p.out)[m * p.ldo + n] = __float2bfloat16_rn(v);
+                else static_cast<float*>(p.out)[m * p.ldo + n] = v;
+              }
+            }
+          }
+        }
+      }
+      tc_fence_before();
+      mbar_arrive(bar_tempty + 8 * acc);
+    }
+  } else {
+    // ------------------------------------------------------------ expanders (warps 6..)
+    const int et = threadIdx.x - 192;          // 0 .. 128*kUnits-1
+    const int u = et >> 7;                     // unit (128 weight columns)
+    const int d = et & 127;
+    const int kg = d & 7;                      // k-octet inside the stage
+    const int ng = d >> 3;                     // group of 8 weight columns inside the unit
+    const bool has_zp = p.zp != nullptr;
+    uint32_t stage = 0, phase = 0, wb = 0, wphase = 0;
+    bool ok = true;
+    for (int w = blockIdx.x; w < num_work && ok; w += gridDim.x) {
+      int xt, yt, kb0, kb1, split;
+      decode(w, xt, yt, kb0, kb1, split);
+      const int64_t n8 = (int64_t)(SWAP ? xt * 128 : yt * BN) + u * kUnit + 8 * ng;  // first of this thread's 8 columns
+      const bool n_in = n8 < p.N;  // N is a multiple of 8
+      GroupRegs g;
+      int g_cur = -1;
+      uint4 s_next = make_uint4(0, 0, 0, 0);
+      uint32_t z_next = 0;
+      int g_next = kb0 < kb1 ? (kb0 * kK) / p.group : -1;
+      if (n_in && g_next >= 0) {
+        s_next = __ldg(reinterpret_cast<const uint4*>(p.scale + (int64_t)g_next * p.N + n8));
+        if (has_zp) z_next = (uint32_t)__ldg(p.zp + (int64_t)g_next * (p.N / 8) + n8 / 8);
+      }
+      for (int kb = kb0; kb < kb1; ++kb) {
+        if (g_next != g_cur) {
+          make_group(g, s_next, z_next, has_zp);
+          g_cur = g_next;
+        }
+        // prefetch the next stage's group parameters when the group changes
+        if (kb + 1 < kb1) {
+          const int gn = ((kb + 1) * kK) / p.group;
+          if (gn != g_cur) {
+            g_next = gn;
+            if (n_in) {
+              s_next = __ldg(reinterpret_cast<const uint4*>(p.scale + (int64_t)gn * p.N + n8));
+              if (has_zp) z_next = (uint32_t)__ldg(p.zp + (int64_t)gn * (p.N / 8) + n8 / 8);
+            }
+          }
+        }
+        if (!mbar_wait(bar_full + 8 * stage, phase, abort_flag, p.status, kErrExpand) ||
+            !mbar_wait(bar_wfree + 8 * wb, wphase ^ 1, abort_flag, p.status, kErrExpand)) {
+          ok = false;
+          break;
+        }
+        // Packed word of k-row 8*kg + j and column group ng.  Shared-memory row = j * 8 + kg;
+        // inside a row the 16-byte chunks are XOR-swizzled by the hardware with the row's low
+        // bits, which here are kg: the 8 lanes that share ng but differ in kg hit 8 different
+        // chunks, and the 4 values of ng % 4 in a warp fill the banks inside a chunk.
+        const int ngl = u * 16 + ng;  // column group inside the stage's tile
+        const uint32_t chunk = (C::kRawRowBytes == 128) ? (uint32_t)((ngl >> 2) ^ kg)
+                                                        : (uint32_t)((ngl >> 2) ^ ((kg >> 1) & 3));
+        const uint32_t raw = smem_base + stage * C::kStageBytes + C::kActBytes + kg * C::kRawRowBytes + (chunk << 4) +
+                             (ngl & 3) * 4;
+        uint32_t t[8][4];  // t[j][i] = {W[k_j][n_i], W[k_j][n_{i+4}]}
+#pragma unroll
+        for (int j = 0; j < 8; ++j) {
+          const uint32_t wv = lds32(raw + j * 8 * C::kRawRowBytes);
+#pragma unroll
+          for (int i = 0; i < 4; ++i) t[j][i] = bf2_mul(bf2_sub(nib_pair(wv, i), g.zr[i]), g.sp[i]);
+        }
+        // 8x8 transpose in registers: row n_i gets its eight k values as four bf16x2
+        const uint32_t wt = wbuf_base + wb * C::kWBufBytes + (u * kUnit + 8 * ng) * 128;
+#pragma unroll
+        for (int i = 0; i < 4; ++i) {
+          sts128(wt + i * 128 + ((kg ^ i) << 4), __byte_perm(t[0][i], t[1][i], 0x5410),
+                 __byte_perm(t[2][i], t[3][i], 0x5410), __byte_perm(t[4][i], t[5][i], 0x5410),
+                 __byte_perm(t[6][i], t[7][i], 0x5410));
+          sts128(wt + (i + 4) * 128 + ((kg ^ (i + 4)) << 4), __byte_perm(t[0][i], t[1][i], 0x7632),
+                 __byte_perm(t[2][i], t[3][i], 0x7632), __byte_perm(t[4][i], t[5][i], 0x7632),
+                 __byte_perm(t[6][i], t[7][i], 0x7632));
+        }
+        fence_proxy_async_smem();  // generic-proxy writes -> visible to the tensor core's async proxy
+        mbar_arrive(bar_wready + 8 * wb);
+        if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        if (++wb == NWBUF) { wb = 0; wphase ^= 1; }
+      }
+    }
+  }
+
+  // ---------------------------------------------------------------- teardown
+  __syncwarp();
+  tc_fence_before();
+  __syncthreads();
+  if (*abort_flag) {
+    for (int i = 0; i < 200; ++i) __nanosleep(1000);
+    __syncthreads();
+  }
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, C::kTmemCols);
+  }
+}
+
+// Sum the fp32 partial tiles of a split-K run and round once to the output dtype.
+__global__ void __launch_bounds__(256) splitk_reduce_kernel(const float* __restrict__ partial, void* out, int out_dtype,
+                                                            int64_t M, int64_t N, int64_t ldo, int splits) {
+  const int64_t total = M * N;
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
+    float v = 0.f;
+    for (int s = 0; s < splits; ++s) v += partial[(int64_t)s * total + i];
+    const int64_t m = i / N, n = i % N;
+    if (out_dtype == B200Q_BF16) static_cast<__nv_bfloat16*>(out)[m * ldo + n] = __float2bfloat16_rn(v);
+    else static_cast<float*>(out)[m * ldo + n] = v;
+  }
+}
+
+template <int BN, bool SWAP, int STAGES, int NWBUF>
+static int launch(const CUtensorMap& ma, const CUtensorMap& mr, const Params& p, cudaStream_t st) {
+  using C = Cfg<BN, SWAP, STAGES, NWBUF>;
+  constexpr int smem = C::kTotal + 1024;
+  static_assert(smem <= 227 * 1024, "shared memory budget");
+  // TMEM: CTAs that share an SM must never ask for more than 512 columns together
+  static_assert(C::kTmemCols * (227 * 1024 / smem) <= 512, "TMEM over-subscription");
+  auto kern = w4a16_kernel<BN, SWAP, STAGES, NWBUF>;
+  B200Q_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+  int work = p.x_tiles * p.y_tiles * p.splits;
+  int per_sm = 227 * 1024 / smem;
+  int grid = work < kNumSMs * per_sm ? work : kNumSMs * per_sm;
+  kern<<<grid, C::kThreads, smem, st>>>(ma, mr, p);
+  B200Q_LAUNCH_CHECK();
+  return B200Q_OK;
+}
+
+}  // namespace w4
+
+// Packed weights [K][N/8] int32 seen as {words, k / 8, k % 8}; a box of {box_words, 8, 8} lands in
+// shared memory as rows (k % 8) * 8 + k / 8 of box_words words, swizzled over the row width.
+static int make_tma_map_raw_w4(CUtensorMap* map, const int32_t* qweight, int64_t N, int64_t K, int box_words) {
+  EncodeTiledFn enc = get_encode_fn();
+  if (!enc) return B200Q_ERR_CUDA;
+  const cuuint64_t row_bytes = (cuuint64_t)(N / 8) * 4;
+  cuuint64_t dims[3] = {(cuuint64_t)(N / 8), (cuuint64_t)(K / 8), 8};
+  cuuint64_t strides[2] = {8 * row_bytes, row_bytes};
+  cuuint32_t box[3] = {(cuuint32_t)box_words, 8, 8};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_INT32, 3, const_cast<int32_t*>(qweight), dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, box_words == 32 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B,
+                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? B200Q_OK : B200Q_ERR_CUDA;
+}
+
+// Number of K splits the small-M path uses, and the fp32 workspace it needs.
+static int w4a16_splits(int64_t M, int64_t N, int64_t K) {
+  if (M > 128) return 1;
+  const int64_t tiles = ((N + 127) / 128) * ((M + 127) / 128);
+  const int64_t num_kb = K / w4::kK;
+  int s = 1;
+  while (tiles * s < 2 * kNumSMs && s * 2 <= num_kb / 4 && s < 16) s *= 2;  // >= 4 stages of k per split
+  return s;
+}
+
+size_t w4a16_workspace_bytes_impl(int64_t M, int64_t N, int64_t K) {
+  const int s = w4a16_splits(M, N, K);
+  return s > 1 ? (size_t)s * (size_t)M * (size_t)N * sizeof(float) : 0;
+}
+
+int w4a16_gemm_impl(const void* x, int64_t ldx, const int32_t* qweight, const void* scale, const int32_t* zp,
+                    int zp_kind, int k_packed, int64_t M, int64_t N, int64_t K, int64_t group, void* out,
+                    int out_dtype, int64_t ldo, void* workspace, size_t workspace_bytes, cudaStream_t st) {
+  if (k_packed) return B200Q_ERR_UNSUPPORTED;  // the fused kernel takes the operator layout [K][N/8]
+  if (K % w4::kK || group % w4::kK || K % group || N % 32 || ldx % 8) return B200Q_ERR_UNSUPPORTED;
+  if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(qweight) | reinterpret_cast<uintptr_t>(scale)) & 15)
+    return B200Q_ERR_UNSUPPORTED;
+  if (M > (1ll << 30) || N > (1ll << 30) || K > (1ll << 30)) return B200Q_ERR_TOO_LARGE;
+  w4::Params p;
+  p.scale = static_cast<const __nv_bfloat16*>(scale);
+  p.zp = zp_kind == B200Q_ZP_PACKED ? zp : nullptr;
+  p.out = out; p.partial = nullptr; p.M = M; p.N = N; p.K = K; p.ldo = ldo; p.group = (int)group;
+  p.out_dtype = out_dtype; p.num_kb = (int)(K / w4::kK);
+  p.status = device_status_ptr();
+  if (!p.status) return B200Q_ERR_CUDA;
+  const bool swap = M <= 128;
+  p.splits = swap ? w4a16_splits(M, N, K) : 1;
+  p.kb_per_split = (p.num_kb + p.splits - 1) / p.splits;
+  if (p.splits > 1) {
+    const size_t need = (size_t)p.splits * (size_t)M * (size_t)N * sizeof(float);
+    if (!workspace || workspace_bytes < need) return B200Q_ERR_BAD_ARGUMENT;
+    p.partial = static_cast<float*>(workspace);
+  }
+  CUtensorMap ma, mr;
+  int rc = 0;
+  const int bn_w = (!swap && N > 128) ? 256 : 128;  // weight columns per stage tile
+  rc = make_tma_map_raw_w4(&mr, qweight, N, K, bn_w / 8);
+  if (rc) return rc;
+  if (!swap) {
+    p.x_tiles = (int)((M + 127) / 128);
+    const int bn = bn_w;
+    p.y_tiles = (int)((N + bn - 1) / bn);
+    rc = make_tma_map_2d(&ma, x, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, K, M, ldx * 2, w4::kK, 128, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc) return rc;
+    if (bn == 256) rc = w4::launch<256, false, 4, 3>(ma, mr, p, st);
+    else rc = w4::launch<128, false, 5, 4>(ma, mr, p, st);
+  } else {
+    p.x_tiles = (int)((N + 127) / 128);
+    const int bn = M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : 128;
+    p.y_tiles = (int)((M + bn - 1) / bn);
+    rc = make_tma_map_2d(&ma, x, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, K, M, ldx * 2, w4::kK, bn, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc) return rc;
+    switch (bn) {
+      case 16: rc = w4::launch<16, true, 6, 3>(ma, mr, p, st); break;
+      case 32: rc = w4::launch<32, true, 6, 3>(ma, mr, p, st); break;
+      case 64: rc = w4::launch<64, true, 6, 3>(ma, mr, p, st); break;
+      default: rc = w4::launch<128, true, 5, 3>(ma, mr, p, st); break;
+    }
+  }
+  if (rc) return rc;
+  if (p.splits > 1) {
+    const int64_t total = M * N;
+    int grid = (int)((total + 255) / 256);
+    if (grid > kNumSMs * 8) grid = kNumSMs * 8;
+    w4::splitk_reduce_kernel<<<grid, 256, 0, st>>>(p.partial, out, out_dtype, M, N, ldo, p.splits);
+    B200Q_LAUNCH_CHECK();
+  }
+  return B200Q_OK;
+}
+
 }  // namespace b200q

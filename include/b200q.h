@@ -19,6 +19,7 @@
 #ifndef B200Q_H_
 #define B200Q_H_
 
+#include <stddef.h>
 #include <stdint.h>
 
 #ifdef __cplusplus
@@ -176,10 +177,18 @@ int b200q_fp8_gemm(const b200q_gemm_args* args);
  * qweight  k_packed = 0: int32 [K][N/8] (operator layout); 1: int32 [K/8][N] (AutoGPTQ)
  * scale    bf16 [K/group][N];  zp: NONE or PACKED int32 [K/group][N/8]
  * out      out_dtype F32/BF16 [M][N], row stride ldo
+ * workspace  caller-owned device scratch of at least b200q_w4a16_workspace_bytes(M, N, K) bytes
+ *            (0 for M > 128): for small M the K dimension is split over several CTAs per
+ *            output tile and the fp32 partial tiles are summed by a second kernel.  May be
+ *            NULL when the required size is 0.  Needs 16-byte alignment; contents are scratch.
+ * The fused kernel takes k_packed = 0 with K % 64 == 0, group % 64 == 0, K % group == 0,
+ * N % 32 == 0 and 16-byte aligned bases; other cases return B200Q_ERR_UNSUPPORTED.
  */
+size_t b200q_w4a16_workspace_bytes(int64_t M, int64_t N, int64_t K);
 int b200q_w4a16_gemm(const void* x, int64_t ldx, const int32_t* qweight, const void* scale,
                      const int32_t* zp, int zp_kind, int k_packed, int64_t M, int64_t N, int64_t K,
-                     int64_t group, void* out, int out_dtype, int64_t ldo, void* stream);
+                     int64_t group, void* out, int out_dtype, int64_t ldo, void* workspace,
+                     size_t workspace_bytes, void* stream);
 
 /*
  * swiglu_cast_fp8: out8 = e4m3(bf16(silu(gate) * up) * scale), the activation step between the

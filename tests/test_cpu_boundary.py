@@ -16,7 +16,7 @@ from b200_hpu_ops import abi
 
 def test_header_symbols_are_exported():
     hdr = open(os.path.join(ROOT, "include", "b200q.h")).read()
-    declared = set(re.findall(r"^(?:int|const char\*|uint64_t)\s+(b200q_[a-z0-9_]+)\s*\(", hdr, re.M))
+    declared = set(re.findall(r"^(?:int|const char\*|uint64_t|size_t)\s+(b200q_[a-z0-9_]+)\s*\(", hdr, re.M))
     assert declared, "no declarations found"
     lib = ctypes.CDLL(b200_hpu_ops.KERNEL_LIB)
     for name in sorted(declared):

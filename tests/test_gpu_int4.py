@@ -119,3 +119,71 @@ def test_full_size_weight_matrix(ops):
     # every value is (integer in [-15, 15]) * scale: dividing by the scale gives integers back
     ratio = out[:128].float() / scale[0].float()
     assert torch.all((ratio - ratio.round()).abs() < 0.26)  # bf16 rounding of the product: < 2^-8 * 15 * ...
+
+
+# ---------------------------------------------------------------- fused W4A16 GEMM
+def _w4_case(M, N, K, group, g, with_zp=True):
+    w = torch.randint(0, 16, (K, N), generator=g)
+    qw = O.pack_nibbles(w)
+    scale = (torch.rand(K // group, N, generator=g) * 0.015 + 0.005).to(torch.bfloat16)
+    zp = O.pack_nibbles(torch.randint(0, 16, (K // group, N), generator=g)) if with_zp else None
+    x = torch.randn(M, K, generator=g).to(torch.bfloat16)
+    return x, qw, scale, zp
+
+
+@pytest.mark.parametrize("M", [1, 16, 17, 64, 128, 130, 384])
+@pytest.mark.parametrize("N,K,group", [(256, 256, 128), (384, 512, 64), (1024, 2048, 128)])
+def test_w4a16_matches_composition(ops, M, N, K, group):
+    """out = x @ convert_from_uint4(...): the fused kernel against the oracle's composition, and
+    (in fp32 output, where no output rounding hides anything) against the unfused GPU path."""
+    g = torch.Generator().manual_seed(M * 31 + N)
+    for with_zp in (True, False):
+        x, qw, scale, zp = _w4_case(M, N, K, group, g, with_zp)
+        zc = None if zp is None else zp.cuda()
+        r = torch.ops.b200q.w4a16_gemm(x.cuda(), qw.cuda(), scale.cuda(), zc, group, False, torch.bfloat16)
+        e = O.w4a16_gemm(x, qw, scale, zp, torch.bfloat16)
+        assert r.dtype == torch.bfloat16 and r.shape == (M, N)
+        assert O.rel_frobenius(r, e) <= 1e-2
+        r32 = torch.ops.b200q.w4a16_gemm(x.cuda(), qw.cuda(), scale.cuda(), zc, group, False, torch.float32)
+        wdq = torch.ops.hpu.convert_from_uint4(qw.cuda(), scale.cuda(), zc, torch.bfloat16)
+        e32 = x.cuda().float() @ wdq.float()
+        assert O.rel_frobenius(r32, e32) <= 2e-5
+    assert ops.device_status() == 0
+
+
+def test_w4a16_weight_layout_probe(ops):
+    """One-hot activations read single rows of the dequantised weight matrix back through the
+    tensor cores: any mistake in the 8x8 register transpose or the swizzled tile layout shows up
+    as a wrong element, not as noise."""
+    g = torch.Generator().manual_seed(5)
+    N, K, group = 512, 512, 128
+    _, qw, scale, zp = _w4_case(1, N, K, group, g)
+    wdq = O.convert_from_uint4(qw, scale, zp, torch.bfloat16).float()
+    for M in (16, 256):
+        rows = (torch.arange(M) * 37) % K
+        x = torch.zeros(M, K)
+        x[torch.arange(M), rows] = 1.0
+        r = torch.ops.b200q.w4a16_gemm(x.to(torch.bfloat16).cuda(), qw.cuda(), scale.cuda(), zp.cuda(), group, False,
+                                       torch.float32)
+        assert torch.equal(r.cpu(), wdq[rows]), M
+    assert ops.device_status() == 0
+
+
+def test_w4a16_full_size(ops):
+    """K = N = 8192, group 128 (the benchmark's weight): M = 16 and M = 2048 against the unfused
+    GPU composition on sampled rows, and two runs agree bit for bit (the split-K sum is ordered)."""
+    g = torch.Generator(device="cuda").manual_seed(0)
+    K = N = 8192
+    qw = torch.randint(-2 ** 31, 2 ** 31 - 1, (K, N // 8), device="cuda", dtype=torch.int32, generator=g)
+    scale = (torch.rand(K // 128, N, device="cuda", generator=g) * 0.015 + 0.005).to(torch.bfloat16)
+    zp = torch.randint(-2 ** 31, 2 ** 31 - 1, (K // 128, N // 8), device="cuda", dtype=torch.int32, generator=g)
+    wdq = torch.ops.hpu.convert_from_uint4(qw, scale, zp, torch.bfloat16)
+    for M in (16, 2048):
+        x = torch.randn(M, K, device="cuda", generator=g).to(torch.bfloat16)
+        r1 = torch.ops.b200q.w4a16_gemm(x, qw, scale, zp, 128, False, torch.bfloat16)
+        r2 = torch.ops.b200q.w4a16_gemm(x, qw, scale, zp, 128, False, torch.bfloat16)
+        assert torch.equal(r1, r2)
+        rows = torch.tensor([0, 1, M // 2, M - 1], device="cuda")
+        e = (x[rows].double() @ wdq.double()).float()
+        assert O.rel_frobenius(r1[rows], e) <= 1e-2
+    assert ops.device_status() == 0
