@@ -9,7 +9,8 @@ rank per GPU) every rank owns one 14336-column shard of a [14336*N, 4096] weight
 (column-parallel, no data-path collective): per-GPU work is fixed, scaling is "weak".
 
 --workload selects other members of the operator family for the same JSON contract:
-  gemm (default) | gemm_m1 | gemm_m16 | gemm_m128 | cast_rne | cast_sr | uncast | dequant | w4a16_m2048 | w4a16_m16
+  gemm (default) | gemm_m1 | gemm_m16 | gemm_m128 | cast_rne | cast_sr | uncast | dequant | w4a16_m2048 | w4a16_m16 |
+  mlp (tensor-parallel FP8 SwiGLU MLP, strong scaling over the ranks)
 --impl reference times the CPU restatement of the reference semantics (the oracle; the
 reference itself has no arithmetic for these operators) on the host cores.
 """
@@ -145,6 +146,7 @@ def run_ours(args):
     peaks = measured_peaks()
     wl = args.workload
     steps, warmup = args.steps, max(args.warmup, 3)
+    scaling = "weak"
 
     # ------------------------------------------------------------------ build the step function
     if wl.startswith("gemm"):
@@ -280,6 +282,45 @@ def run_ours(args):
         dtype = "u4 x bf16 (fp32 accumulate)"
         l2 = "3 rotating operand sets"
         e2e_setup = None
+    elif wl == "mlp":
+        from b200_hpu_ops import tp_mlp
+        T, d, f = args.tokens, 8192, 28672
+        lo, hi = tp_mlp.shard_bounds(f, world, rank)
+        fl = hi - lo
+        g = torch.Generator(device=dev).manual_seed(17)  # same seed on every rank: x is replicated
+
+        def rand_e4m3(rows, cols, seed):
+            gg = torch.Generator(device=dev).manual_seed(seed)
+            w = torch.empty(rows, cols, device=dev, dtype=torch.float8_e4m3fn)
+            blk = 4096
+            for r0 in range(0, rows, blk):
+                r1 = min(rows, r0 + blk)
+                t = (torch.randn(r1 - r0, cols, device=dev, generator=gg, dtype=torch.float32) * 100).to(torch.bfloat16)
+                w[r0:r1] = torch.ops.hpu.cast_to_fp8_v2(t, None, False, False, torch.float8_e4m3fn)[0]
+            return w
+
+        wgu = rand_e4m3(2 * fl, d, 100 + rank)
+        wd = rand_e4m3(d, fl, 200 + rank)
+        sgu = torch.full((2 * fl,), 0.02 / 100 / (448.0 / 5.0) * 448.0 / 5.0, device=dev)
+        sdn = torch.full((d,), 0.02 / 100, device=dev)
+        shard = tp_mlp.MlpShard(wgu, sgu, wd, sdn, fl)
+        mlp = tp_mlp.TpFp8Mlp(shard, 448.0 / 5.0, 448.0 / 8.0, row_blocks=args.row_blocks)
+        xs = [torch.randn(T, d, device=dev, generator=g, dtype=torch.float32).to(torch.bfloat16) for _ in range(2)]
+
+        def step(i):
+            mlp(xs[i % 2])
+        launches_per_step = 4 if world == 1 else 3 + args.row_blocks
+        flops = tp_mlp.mlp_flops(T, d, f)
+        algo_bytes = 3 * d * fl + 2 * T * d * 2 + T * d + 3 * T * fl * 2 + T * fl
+        bound, unit_per_step, unit = "tensor", flops / 1e12 / world, "TFLOP/s"   # per-rank share; value sums ranks
+        peak = 2.0 * peaks["bf16_tflops"]
+        peak_note = "2 x measured cuBLAS bf16 burst; the step also holds casts, SwiGLU and (tp>1) the all-reduce"
+        metric = "tensor-parallel FP8 SwiGLU MLP TFLOP/s (whole job)"
+        workload = f"Llama-3-70B-shaped MLP d=8192 ffn=28672 tokens={T}, tp={world}: gate/up column-parallel, down row-parallel + bf16 all-reduce"
+        dtype = "fp8_e4m3 (fp32 accumulate), bf16 activations"
+        l2 = "2 rotating activation tensors; weights (705 MB / tp) exceed L2"
+        scaling = "strong"
+        e2e_setup = None
     else:
         raise SystemExit(f"unknown workload {wl}")
 
@@ -357,9 +398,10 @@ def run_ours(args):
     if rank == 0:
         line = {
             "metric": metric, "value": value, "unit": unit, "n_gpus": world, "steps": steps, "warmup": warmup,
-            "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "ms_per_step": ms_step, "higher_is_better": True, "scaling": scaling, "vs_baseline": None,
             "dtype": dtype, "data": "synthetic (seeded normal activations/weights, random-init; no dataset involved)",
-            "config": {"workload": workload, "l2": l2, "parallelism": f"column-parallel over {world} rank(s), no collective"},
+            "config": {"workload": workload, "l2": l2, "parallelism": (f"column-parallel over {world} rank(s), no collective" if wl != "mlp"
+                                       else f"tp{world}: column-parallel gate/up, row-parallel down, NCCL all-reduce in {args.row_blocks} row blocks")},
             "roofline": {"bound": bound, "achieved": kernel_rate, "peak": peak, "unit": unit, "frac": kernel_rate / peak,
                          "traffic": traffic, "peak_source": peaks["which"] + ": " + peak_note,
                          "algorithmic_bytes_per_launch": algo_bytes},
@@ -460,6 +502,8 @@ def main():
     ap.add_argument("--workload", default="gemm")
     ap.add_argument("--elems", type=int, default=1 << 26)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--tokens", type=int, default=8192)
+    ap.add_argument("--row-blocks", type=int, default=4)
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

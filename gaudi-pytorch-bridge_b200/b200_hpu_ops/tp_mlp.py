@@ -1,0 +1,133 @@
+"""Tensor-parallel FP8 SwiGLU MLP built from the hpu::* operators.
+
+    y = down( fp8( silu(x8 @ Wg^T) * (x8 @ Wu^T) ) )          x8 = fp8(x * x_scale)
+
+Sharding over `tp` ranks (one process per GPU):
+* gate and up projections are column-parallel: rank r holds rows [r*f/tp, (r+1)*f/tp) of
+  W_gate and W_up ([ffn, d_model], K-major) with their per-output-channel scale_inv slices; the
+  activations are replicated; no collective.  The two shards are stacked into one [2f/tp, d]
+  weight so that gate and up come out of a single fp8_gemm_v2 call.
+* the down projection is row-parallel: rank r holds columns [r*f/tp, (r+1)*f/tp) of W_down
+  ([d_model, ffn]) -- a [d, f/tp] K-major shard -- and produces a full-size [tokens, d] partial
+  sum; one SUM all-reduce over the ranks finishes it.  The all-reduce is issued per block of
+  token rows so that the reduction of block i overlaps the GEMM of block i+1 (the
+  reference's collective is a chunked hcclAllReduce on a network stream,
+  python_packages/habana_frameworks/torch/distributed/hccl/process_group_hccl_base.cpp:412-497).
+* activation scales are per tensor and static (given), so no amax exchange sits on the path.
+
+The operator namespace is a constructor argument so that the partitioning and the collective
+can be exercised on CPU ranks (gloo) with a stand-in for the operators; the default is the
+CUDA implementation registered by this package, and nothing here falls back to anything else.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import List, Optional
+
+import torch
+
+E4M3 = torch.float8_e4m3fn
+
+
+@dataclass
+class MlpShard:
+    """One rank's weights.  w_gate_up: e4m3 [2*f_local, d]; w_down: e4m3 [d, f_local]."""
+    w_gate_up: torch.Tensor
+    s_gate_up_inv: torch.Tensor  # fp32 [2*f_local]
+    w_down: torch.Tensor
+    s_down_inv: torch.Tensor     # fp32 [d]
+    f_local: int
+
+
+def shard_bounds(n: int, tp: int, rank: int):
+    """Contiguous, equal shards; n must divide evenly (28672 / 8 = 3584 = 14 x 256 stays tile-aligned)."""
+    if n % tp:
+        raise ValueError(f"dimension {n} does not divide over {tp} ranks")
+    step = n // tp
+    return rank * step, (rank + 1) * step
+
+
+def shard_mlp(w_gate8, w_up8, w_down8, s_gate_inv, s_up_inv, s_down_inv, tp: int, rank: int) -> MlpShard:
+    """Slice full e4m3 weights ([f, d], [f, d], [d, f]) and their scale_inv vectors for one rank."""
+    f = w_gate8.shape[0]
+    lo, hi = shard_bounds(f, tp, rank)
+    gu = torch.cat([w_gate8[lo:hi].view(torch.uint8), w_up8[lo:hi].view(torch.uint8)], dim=0).view(E4M3).contiguous()
+    sgu = torch.cat([s_gate_inv[lo:hi], s_up_inv[lo:hi]]).float().contiguous()
+    wd = w_down8.view(torch.uint8)[:, lo:hi].contiguous().view(E4M3)
+    return MlpShard(gu, sgu, wd, s_down_inv.float().contiguous(), hi - lo)
+
+
+class TpFp8Mlp:
+    def __init__(self, shard: MlpShard, x_scale: float, act_scale: float, group=None, row_blocks: int = 4,
+                 ops=None, fused_swiglu: bool = True):
+        self.s = shard
+        self.x_scale = float(x_scale)
+        self.act_scale = float(act_scale)
+        self.group = group
+        self.row_blocks = int(row_blocks)
+        self.ops = ops if ops is not None else torch.ops.hpu
+        self.fused_swiglu = fused_swiglu and ops is None
+        dev = shard.w_gate_up.device
+        self._xs_inv = torch.tensor(1.0 / self.x_scale, dtype=torch.float32, device=dev)
+        self._as_inv = torch.tensor(1.0 / self.act_scale, dtype=torch.float32, device=dev)
+
+    # -- the three local stages ------------------------------------------------------------
+    def gate_up(self, x: torch.Tensor) -> torch.Tensor:
+        x8, _ = self.ops.cast_to_fp8_v2(x, self.x_scale, False, False, E4M3)
+        n = self.s.w_gate_up.shape[0]
+        return self.ops.fp8_gemm_v2(x8, False, self.s.w_gate_up, True, None, torch.bfloat16, self._xs_inv,
+                                    self.s.s_gate_up_inv, None, False, [1, n])
+
+    def activation(self, gu: torch.Tensor) -> torch.Tensor:
+        f = self.s.f_local
+        if self.fused_swiglu:
+            h8, _ = torch.ops.b200q.swiglu_cast_fp8(gu[:, :f], gu[:, f:], self.act_scale, False)
+            return h8
+        h = (torch.nn.functional.silu(gu[:, :f].float()) * gu[:, f:].float()).to(torch.bfloat16)
+        h8, _ = self.ops.cast_to_fp8_v2(h, self.act_scale, False, False, E4M3)
+        return h8
+
+    def down_partial(self, h8: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        d = self.s.w_down.shape[0]
+        if out is not None and self.ops is torch.ops.hpu:
+            # write straight into the caller's row block (the operator itself always allocates)
+            from . import abi
+            return abi.fp8_gemm_nt(h8, self.s.w_down, torch.bfloat16, 1.0 / self.act_scale, self.s.s_down_inv, None, out=out)
+        r = self.ops.fp8_gemm_v2(h8, False, self.s.w_down, True, None, torch.bfloat16, self._as_inv, self.s.s_down_inv,
+                                 None, False, [1, d])
+        if out is not None:
+            out.copy_(r)
+            return out
+        return r
+
+    # -- forward -----------------------------------------------------------------------------
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        import torch.distributed as dist
+
+        h8 = self.activation(self.gate_up(x))
+        tp = dist.get_world_size(self.group) if (dist.is_available() and dist.is_initialized()) else 1
+        if tp == 1:
+            return self.down_partial(h8)
+        rows = h8.shape[0]
+        nblk = max(1, min(self.row_blocks, rows))
+        step = (rows + nblk - 1) // nblk
+        out = torch.empty(rows, self.s.w_down.shape[0], dtype=torch.bfloat16, device=h8.device)
+        works: List = []
+        for b in range(nblk):
+            lo, hi = b * step, min(rows, (b + 1) * step)
+            if lo >= hi:
+                break
+            self.down_partial(h8[lo:hi], out[lo:hi])
+            # the collective of this block runs on the communicator's stream while the next
+            # block's GEMM runs on the compute stream
+            works.append(dist.all_reduce(out[lo:hi], op=dist.ReduceOp.SUM, group=self.group, async_op=True))
+        for w in works:
+            w.wait()
+        return out
+
+    __call__ = forward
+
+
+def mlp_flops(tokens: int, d_model: int, ffn: int) -> float:
+    """2*T*d*f for each of gate, up and down."""
+    return 3 * 2.0 * tokens * d_model * ffn

@@ -1,0 +1,91 @@
+"""The FP8 SwiGLU MLP on the GPU: single device against the oracle, and (when the box has two or
+more GPUs) tensor-parallel over NCCL ranks against the same oracle."""
+import os
+import socket
+import sys
+
+import pytest
+import torch
+
+from conftest import ROOT
+from oracle import hpu_oracle as O
+
+pytestmark = pytest.mark.gpu
+
+
+def _problem(T, d, f, seed=0):
+    g = torch.Generator().manual_seed(seed)
+    x = torch.randn(T, d, generator=g).to(torch.bfloat16)
+
+    def q(w):
+        s = 448.0 / w.abs().amax(dim=1, keepdim=True)
+        w8, _ = O.cast_to_fp8_v2(w.to(torch.bfloat16), s, False, False, torch.float8_e4m3fn, list(s.shape))
+        return w8, (1.0 / s).reshape(-1).float()
+
+    wg8, sg = q(torch.randn(f, d, generator=g) * 0.05)
+    wu8, su = q(torch.randn(f, d, generator=g) * 0.05)
+    wd8, sd = q(torch.randn(d, f, generator=g) * 0.05)
+    return x, wg8, wu8, wd8, sg, su, sd, 448.0 / 5.0, 448.0 / 2.0
+
+
+def test_mlp_single_device_matches_oracle():
+    import b200_hpu_ops
+    from b200_hpu_ops import tp_mlp
+    x, wg8, wu8, wd8, sg, su, sd, xs, acs = _problem(256, 512, 1024)
+    shard = tp_mlp.shard_mlp(wg8.cuda(), wu8.cuda(), wd8.cuda(), sg.cuda(), su.cuda(), sd.cuda(), 1, 0)
+    ref = O.fp8_swiglu_mlp(x, wg8, wu8, wd8, sg, su, sd, xs, acs)
+    for fused in (True, False):
+        y = tp_mlp.TpFp8Mlp(shard, xs, acs, fused_swiglu=fused)(x.cuda())
+        assert y.shape == ref.shape and y.dtype == torch.bfloat16
+        assert O.rel_frobenius(y, ref) <= 1e-2
+    assert b200_hpu_ops.device_status() == 0
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    p = s.getsockname()[1]
+    s.close()
+    return p
+
+
+def _worker(rank, world, port, q):
+    sys.path.insert(0, ROOT)
+    sys.path.insert(0, os.path.join(ROOT, "gaudi-pytorch-bridge_b200"))
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    import torch.distributed as dist
+    torch.cuda.set_device(rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    try:
+        import b200_hpu_ops
+        from b200_hpu_ops import tp_mlp
+        x, wg8, wu8, wd8, sg, su, sd, xs, acs = _problem(512, 512, 2048)
+        dev = torch.device("cuda", rank)
+        shard = tp_mlp.shard_mlp(wg8.to(dev), wu8.to(dev), wd8.to(dev), sg.to(dev), su.to(dev), sd.to(dev), world, rank)
+        y = tp_mlp.TpFp8Mlp(shard, xs, acs, row_blocks=4)(x.to(dev))
+        torch.cuda.synchronize()
+        ref = O.fp8_swiglu_mlp(x, wg8, wu8, wd8, sg, su, sd, xs, acs)
+        q.put((rank, O.rel_frobenius(y, ref), b200_hpu_ops.device_status()))
+    finally:
+        dist.destroy_process_group()
+
+
+@pytest.mark.parametrize("world", [2, 4, 8])
+def test_mlp_tensor_parallel_nccl(world):
+    if torch.cuda.device_count() < world:
+        pytest.skip(f"needs {world} GPUs")
+    import torch.multiprocessing as mp
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_worker, args=(r, world, port, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    res = [q.get(timeout=300) for _ in range(world)]
+    for p in procs:
+        p.join(timeout=120)
+        assert p.exitcode == 0
+    for rank, err, status in res:
+        assert status == 0
+        assert err <= 1e-2, (rank, err)
