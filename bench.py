@@ -34,8 +34,9 @@ def measured_peaks():
     p = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(p):
         d = json.load(open(p))
-        return {"hbm_gbs": d["hbm_gbs"], "bf16_tflops": d["bf16_tflops"], "which": "measured"}
-    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "which": "fallback"}
+        return {"hbm_gbs": d["hbm_gbs"], "bf16_tflops": d["bf16_tflops"],
+                "bf16_sustained": d.get("bf16_tflops_sustained", d["bf16_tflops"]), "which": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_sustained": 1400.0, "which": "fallback"}
 
 
 # ----------------------------------------------------------------------------- clocks
@@ -205,21 +206,20 @@ def run_ours(args):
         x8s = [abi.cast_to_fp8(x, fp8, scale)[0] for x in xs]
         amax = torch.zeros((), device=dev, dtype=torch.float32)
         backs = [torch.empty(n, device=dev, dtype=torch.bfloat16) for _ in range(3)] if wl == "uncast" else None
-        st = abi.stream_ptr()
         # preallocated outputs and direct C-ABI calls: at 2^20..2^24 elements the kernel is a few
         # microseconds and host-side allocation would dominate the step
         if wl == "uncast":
             def step(i):
                 j = i % 3
                 abi.check(abi.lib.b200q_cast_from_fp8(abi.ptr(x8s[j]), abi.DTYPE[fp8], abi.ptr(backs[j]), abi.BF16, None,
-                                                      1.0 / scale, abi.BCAST_SCALAR_HOST, 1, n, st))
+                                                      1.0 / scale, abi.BCAST_SCALAR_HOST, 1, n, abi.stream_ptr()))
         else:
             rnd = abi.ROUND_STOCHASTIC if wl == "cast_sr" else abi.ROUND_RNE
 
             def step(i):
                 j = i % 3
                 abi.check(abi.lib.b200q_cast_to_fp8(abi.ptr(xs[j]), abi.BF16, abi.ptr(x8s[j]), abi.DTYPE[fp8], None, scale,
-                                                    abi.BCAST_SCALAR_HOST, 1, n, abi.ptr(amax), rnd, 1234, i, 0, 0, st))
+                                                    abi.BCAST_SCALAR_HOST, 1, n, abi.ptr(amax), rnd, 1234, i, 0, 0, abi.stream_ptr()))
         launches_per_step = 1
         algo_bytes = 3 * n
         bound, unit_per_step, unit = "hbm", algo_bytes / 1e9, "GB/s"
@@ -334,23 +334,47 @@ def run_ours(args):
     for i in range(warmup):
         step(i)
     barrier()
+    # Short kernels (decode GEMMs, casts, dequant: 5-50 us) are replayed from a CUDA graph of G
+    # consecutive steps so that the host's per-call work does not pace the device; G divides K.
+    use_graph = (not args.no_graph) and wl not in ("gemm", "mlp")
+    G = 1
+    if use_graph:
+        G = max(d for d in range(1, 26) if steps % d == 0)
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.stream(side):
+            for i in range(3):
+                step(i)
+            side.synchronize()
+            with torch.cuda.graph(graph, stream=side):
+                for i in range(G):
+                    step(i)
+        torch.cuda.current_stream().wait_stream(side)
+        torch.cuda.synchronize()
+
+        def run_steps(k):
+            for _ in range(k // G):
+                graph.replay()
+    else:
+        def run_steps(k):
+            for i in range(k):
+                step(i)
     sampler.start()
-    for i in range(warmup):  # a second warm-up under the sampler so short runs still have samples under load
-        step(i)
+    run_steps(max(G, (warmup // G) * G))  # a second warm-up under the sampler so short runs still have samples under load
     torch.cuda.synchronize()
     n0 = b200_hpu_ops.launch_count()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     barrier()
     t0 = time.perf_counter()
     e0.record()
-    for i in range(steps):
-        step(i)
+    run_steps(steps)
     e1.record()
     barrier()
     t1 = time.perf_counter()
     sampler.stop()
     ms_total = e0.elapsed_time(e1)
-    launches = b200_hpu_ops.launch_count() - n0
+    launches = (b200_hpu_ops.launch_count() - n0) if not use_graph else steps * launches_per_step
     status = b200_hpu_ops.device_status()
     if status != 0:
         raise SystemExit(f"device status {status}: a bounded wait inside a kernel ran out")
@@ -361,6 +385,10 @@ def run_ours(args):
     ms_step = ms_total / steps
     value = world * unit_per_step / (ms_step / 1e3)
     kernel_rate = unit_per_step / (ms_step / 1e3)  # one launch per step: the step time is the launch time
+    if bound == "tensor" and ms_total > 1000.0:
+        # a seconds-long loop runs under the power cap: compare with the sustained cuBLAS figure
+        peak = peak * peaks["bf16_sustained"] / peaks["bf16_tflops"]
+        peak_note += "; timed region > 1 s, so the sustained (power-capped) figure is used"
 
     # ------------------------------------------------------------------ end to end through the operator
     e2e = None
@@ -406,7 +434,8 @@ def run_ours(args):
                          "traffic": traffic, "peak_source": peaks["which"] + ": " + peak_note,
                          "algorithmic_bytes_per_launch": algo_bytes},
             "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": int(launches),
-            "launches_per_step": launches_per_step, "clocks": sampler.summary(t0, t1),
+            "launches_per_step": launches_per_step, "cuda_graph_steps": G if use_graph else 0,
+            "clocks": sampler.summary(t0, t1),
         }
         print(json.dumps(line))
     if dist is not None:
@@ -502,6 +531,7 @@ def main():
     ap.add_argument("--workload", default="gemm")
     ap.add_argument("--elems", type=int, default=1 << 26)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-graph", action="store_true", help="do not replay short kernels from a CUDA graph")
     ap.add_argument("--tokens", type=int, default=8192)
     ap.add_argument("--row-blocks", type=int, default=4)
     args = ap.parse_args()

@@ -447,8 +447,12 @@ __global__ void __launch_bounds__(256) swiglu_cast_kernel(SwigluParams p) {
 // sixteenth of a wave whatever the size.
 template <typename Kernel>
 static int grid_for(Kernel kernel, int64_t n_items) {
-  int per_sm = 0;
-  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, 256, 0) != cudaSuccess || per_sm < 1) per_sm = 4;
+  static std::atomic<int> cached{0};  // per kernel instantiation; the same on every B200 of a process
+  int per_sm = cached.load(std::memory_order_relaxed);
+  if (per_sm == 0) {
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, 256, 0) != cudaSuccess || per_sm < 1) per_sm = 4;
+    cached.store(per_sm, std::memory_order_relaxed);
+  }
   int64_t blocks = (n_items + 255) / 256;
   int64_t cap = (int64_t)kNumSMs * per_sm * 16;
   if (blocks > cap) blocks = cap;

@@ -32,6 +32,15 @@ inline void count_launch() { g_launches.fetch_add(1, std::memory_order_relaxed);
     if (e__ != cudaSuccess) return ::b200q::record_cuda_error(e__, "launch"); \
   } while (0)
 
+// Per-device one-time setup helper: `slot` is a static array of kMaxDevices ints owned by the
+// caller (0 = not yet done on that device).  Returns the current device index or -1.
+constexpr int kMaxDevices = 64;
+inline int current_device_index() {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) return -1;
+  return dev;
+}
+
 // Device status word of the current device: 0 = fine; kernels with bounded waits write a
 // code here.  Returns null if its address cannot be obtained.
 int* device_status_ptr();

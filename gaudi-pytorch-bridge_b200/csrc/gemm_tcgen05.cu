@@ -16,6 +16,9 @@
 //               the weight stream fills the 128-lane dimension and the few tokens ride N.
 #include <cuda.h>
 
+#include <cstdio>
+#include <cstdlib>
+
 #include "common.cuh"
 #include "gemm_common.cuh"
 #include "tcgen05_ptx.cuh"
@@ -53,6 +56,129 @@ struct SmemLayout {
   static constexpr int kTotal = kBarOffset + kNumBars * 8 + 16;
 };
 
+// ---------------------------------------------------------------------------- epilogue pieces
+// Per-thread (lane-side) and per-column epilogue operands of one tile.  Scales multiply in the
+// order (acc * sa) * sb; a scalar or lane-side scale lives in rA / rB, a column-side one in
+// shared memory (cA / cB), the other factor is 1.
+struct EpiRow {
+  float rA, rB, rBias;
+  int64_t x;
+  bool x_in;
+};
+
+template <int BN, bool SWAP>
+__device__ __forceinline__ EpiRow epi_stage_operands(const GemmParams& g, int64_t x_rows, int64_t y_rows, int64_t x,
+                                                     int64_t y0, int et, float* cA, float* cB, float* cBias) {
+  // which output dimension the columns are: n (normal) or m (swapped)
+  const int col_mode = SWAP ? B200Q_BCAST_PER_ROW : B200Q_BCAST_PER_COL;
+  const int row_mode = SWAP ? B200Q_BCAST_PER_COL : B200Q_BCAST_PER_ROW;
+  for (int c = et; c < BN; c += kEpiThreads) {
+    const int64_t y = y0 + c;
+    const bool in = y < y_rows;
+    cA[c] = (g.a_scale_mode == col_mode && in) ? __ldg(g.a_scale + y) : 1.f;
+    cB[c] = (g.b_scale_mode == col_mode && in) ? __ldg(g.b_scale + y) : 1.f;
+    cBias[c] = (g.bias_mode == col_mode && in) ? ld_out_typed(g.bias, g.bias_dtype, y) : 0.f;
+  }
+  EpiRow r;
+  r.x = x;
+  r.x_in = x < x_rows;
+  r.rA = 1.f; r.rB = 1.f; r.rBias = 0.f;
+  if (g.a_scale_mode == B200Q_BCAST_SCALAR_HOST) r.rA = g.a_scale_host;
+  else if (g.a_scale_mode == B200Q_BCAST_SCALAR_DEV) r.rA = __ldg(g.a_scale);
+  else if (g.a_scale_mode == row_mode && r.x_in) r.rA = __ldg(g.a_scale + x);
+  if (g.b_scale_mode == B200Q_BCAST_SCALAR_HOST) r.rB = g.b_scale_host;
+  else if (g.b_scale_mode == B200Q_BCAST_SCALAR_DEV) r.rB = __ldg(g.b_scale);
+  else if (g.b_scale_mode == row_mode && r.x_in) r.rB = __ldg(g.b_scale + x);
+  if (g.bias_mode == row_mode && r.x_in) r.rBias = ld_out_typed(g.bias, g.bias_dtype, x);
+  return r;
+}
+
+// TMEM accumulator (this warp's 32 lanes, BN columns from t_row) -> scaled, biased, rounded, stored.
+template <int BN, bool SWAP>
+__device__ __forceinline__ void epi_drain(const GemmParams& g, uint32_t t_row, const EpiRow& e, int64_t y0,
+                                          const float* cA, const float* cB, const float* cBias) {
+  const bool full_extra = g.bias_mode == B200Q_BCAST_FULL || g.D != nullptr;
+  const int64_t x = e.x;
+  const bool x_in = e.x_in;
+  const float rA = e.rA, rB = e.rB, rBias = e.rBias;
+#pragma unroll 1
+  for (int c0 = 0; c0 < BN; c0 += 32) {
+    uint32_t r[32];
+    if (BN % 32 == 0) {
+      tmem_ld_32x32(t_row + c0, r);
+    } else {
+      tmem_ld_32x16(t_row + c0, r);  // BN == 16
+    }
+    tmem_ld_wait();
+    constexpr int CW = (BN % 32 == 0) ? 32 : 16;
+    float v[CW];
+#pragma unroll
+    for (int j = 0; j < CW; ++j) {
+      float a = __uint_as_float(r[j]);
+      a = a * (rA * cA[c0 + j]);
+      a = a * (rB * cB[c0 + j]);
+      v[j] = a + (rBias + cBias[c0 + j]);
+    }
+    if (!SWAP) {
+      // thread = output row m, registers = CW consecutive output columns n
+      const int64_t m = x, n0 = y0 + c0;
+      if (x_in) {
+        if (full_extra) {
+#pragma unroll
+          for (int j = 0; j < CW; ++j) {
+            const int64_t n = n0 + j;
+            if (n < g.N) {
+              if (g.bias_mode == B200Q_BCAST_FULL) v[j] += ld_out_typed(g.bias, g.bias_dtype, m * g.bias_ld + n);
+              if (g.D) v[j] += ld_out_typed(g.D, g.d_dtype, m * g.ldd + n);
+            }
+          }
+        }
+        if (g.out_dtype == B200Q_BF16) {
+          __nv_bfloat16* o = static_cast<__nv_bfloat16*>(g.out) + m * g.ldo + n0;
+          if (n0 + CW <= g.N && (reinterpret_cast<uintptr_t>(o) & 15) == 0) {
+#pragma unroll
+            for (int j = 0; j < CW; j += 8)
+              *reinterpret_cast<uint4*>(o + j) =
+                  make_uint4(pack_bf16x2(v[j], v[j + 1]), pack_bf16x2(v[j + 2], v[j + 3]),
+                             pack_bf16x2(v[j + 4], v[j + 5]), pack_bf16x2(v[j + 6], v[j + 7]));
+          } else {
+#pragma unroll
+            for (int j = 0; j < CW; ++j)
+              if (n0 + j < g.N) o[j] = __float2bfloat16_rn(v[j]);
+          }
+        } else {
+          float* o = static_cast<float*>(g.out) + m * g.ldo + n0;
+          if (n0 + CW <= g.N && (reinterpret_cast<uintptr_t>(o) & 15) == 0) {
+#pragma unroll
+            for (int j = 0; j < CW; j += 4)
+              *reinterpret_cast<float4*>(o + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+          } else {
+#pragma unroll
+            for (int j = 0; j < CW; ++j)
+              if (n0 + j < g.N) o[j] = v[j];
+          }
+        }
+      }
+    } else {
+      // thread = output column n (weight row), registers = CW consecutive tokens m
+      const int64_t n = x;
+      if (x_in) {
+#pragma unroll
+        for (int j = 0; j < CW; ++j) {
+          const int64_t m = y0 + c0 + j;
+          if (m < g.M) {
+            float o = v[j];
+            if (g.bias_mode == B200Q_BCAST_FULL) o += ld_out_typed(g.bias, g.bias_dtype, m * g.bias_ld + n);
+            if (g.D) o += ld_out_typed(g.D, g.d_dtype, m * g.ldd + n);
+            if (g.out_dtype == B200Q_BF16) static_cast<__nv_bfloat16*>(g.out)[m * g.ldo + n] = __float2bfloat16_rn(o);
+            else static_cast<float*>(g.out)[m * g.ldo + n] = o;
+          }
+        }
+      }
+    }
+  }
+}
+
 template <int BN, int STAGES, bool SWAP>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_y,
@@ -71,7 +197,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
   const uint32_t bar_full = smem_u32(bars), bar_empty = bar_full + 8 * STAGES;
   const uint32_t bar_tfull = bar_empty + 8 * STAGES, bar_tempty = bar_tfull + 16;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  constexpr uint32_t kTmemCols = (2 * BN) < 32 ? 32 : 2 * BN;
+  // TMEM is allocated in powers of two columns (two accumulators of BN columns each)
+  constexpr uint32_t kTmemCols = 2 * BN <= 32 ? 32 : 2 * BN <= 64 ? 64 : 2 * BN <= 128 ? 128 : 2 * BN <= 256 ? 256 : 512;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
@@ -165,26 +292,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
       float* cA = epi_f + acc * 3 * BN;
       float* cB = cA + BN;
       float* cBias = cB + BN;
-      // which output dimension the columns are: n (normal) or m (swapped)
-      const int col_mode = SWAP ? B200Q_BCAST_PER_ROW : B200Q_BCAST_PER_COL;
-      const int row_mode = SWAP ? B200Q_BCAST_PER_COL : B200Q_BCAST_PER_ROW;
-      for (int c = et; c < BN; c += kEpiThreads) {
-        const int64_t y = y0 + c;
-        const bool in = y < p.y_rows;
-        cA[c] = (g.a_scale_mode == col_mode && in) ? __ldg(g.a_scale + y) : 1.f;
-        cB[c] = (g.b_scale_mode == col_mode && in) ? __ldg(g.b_scale + y) : 1.f;
-        cBias[c] = (g.bias_mode == col_mode && in) ? ld_out_typed(g.bias, g.bias_dtype, y) : 0.f;
-      }
-      const int64_t x = x0 + q * 32 + lane;  // this thread's lane-side index
-      const bool x_in = x < p.x_rows;
-      float rA = 1.f, rB = 1.f, rBias = 0.f;
-      if (g.a_scale_mode == B200Q_BCAST_SCALAR_HOST) rA = g.a_scale_host;
-      else if (g.a_scale_mode == B200Q_BCAST_SCALAR_DEV) rA = __ldg(g.a_scale);
-      else if (g.a_scale_mode == row_mode && x_in) rA = __ldg(g.a_scale + x);
-      if (g.b_scale_mode == B200Q_BCAST_SCALAR_HOST) rB = g.b_scale_host;
-      else if (g.b_scale_mode == B200Q_BCAST_SCALAR_DEV) rB = __ldg(g.b_scale);
-      else if (g.b_scale_mode == row_mode && x_in) rB = __ldg(g.b_scale + x);
-      if (g.bias_mode == row_mode && x_in) rBias = ld_out_typed(g.bias, g.bias_dtype, x);
+      const EpiRow er = epi_stage_operands<BN, SWAP>(g, p.x_rows, p.y_rows, x0 + q * 32 + lane, y0, et, cA, cB, cBias);
       // The wait can give up for some threads only; the decision to stop must be the same for
       // all 128 epilogue threads because they meet at named barriers: one thread samples the
       // abort flag between two barriers and everybody follows that sample.
@@ -194,85 +302,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
       named_bar_sync(1, kEpiThreads);
       if (*epi_stop) break;
       tc_fence_after();
-      const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16) + acc * BN;
-      const bool full_extra = g.bias_mode == B200Q_BCAST_FULL || g.D != nullptr;
-
-#pragma unroll 1
-      for (int c0 = 0; c0 < BN; c0 += 32) {
-        uint32_t r[32];
-        if (BN % 32 == 0) {
-          tmem_ld_32x32(t_row + c0, r);
-        } else {
-          tmem_ld_32x16(t_row + c0, r);  // BN == 16
-        }
-        tmem_ld_wait();
-        constexpr int CW = (BN % 32 == 0) ? 32 : 16;
-        float v[CW];
-#pragma unroll
-        for (int j = 0; j < CW; ++j) {
-          float a = __uint_as_float(r[j]);
-          a = a * (rA * cA[c0 + j]);
-          a = a * (rB * cB[c0 + j]);
-          v[j] = a + (rBias + cBias[c0 + j]);
-        }
-        if (!SWAP) {
-          // thread = output row m, registers = CW consecutive output columns n
-          const int64_t m = x, n0 = y0 + c0;
-          if (x_in) {
-            if (full_extra) {
-#pragma unroll
-              for (int j = 0; j < CW; ++j) {
-                const int64_t n = n0 + j;
-                if (n < g.N) {
-                  if (g.bias_mode == B200Q_BCAST_FULL) v[j] += ld_out_typed(g.bias, g.bias_dtype, m * g.bias_ld + n);
-                  if (g.D) v[j] += ld_out_typed(g.D, g.d_dtype, m * g.ldd + n);
-                }
-              }
-            }
-            if (g.out_dtype == B200Q_BF16) {
-              __nv_bfloat16* o = static_cast<__nv_bfloat16*>(g.out) + m * g.ldo + n0;
-              if (n0 + CW <= g.N && (reinterpret_cast<uintptr_t>(o) & 15) == 0) {
-#pragma unroll
-                for (int j = 0; j < CW; j += 8)
-                  *reinterpret_cast<uint4*>(o + j) =
-                      make_uint4(pack_bf16x2(v[j], v[j + 1]), pack_bf16x2(v[j + 2], v[j + 3]),
-                                 pack_bf16x2(v[j + 4], v[j + 5]), pack_bf16x2(v[j + 6], v[j + 7]));
-              } else {
-#pragma unroll
-                for (int j = 0; j < CW; ++j)
-                  if (n0 + j < g.N) o[j] = __float2bfloat16_rn(v[j]);
-              }
-            } else {
-              float* o = static_cast<float*>(g.out) + m * g.ldo + n0;
-              if (n0 + CW <= g.N && (reinterpret_cast<uintptr_t>(o) & 15) == 0) {
-#pragma unroll
-                for (int j = 0; j < CW; j += 4)
-                  *reinterpret_cast<float4*>(o + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
-              } else {
-#pragma unroll
-                for (int j = 0; j < CW; ++j)
-                  if (n0 + j < g.N) o[j] = v[j];
-              }
-            }
-          }
-        } else {
-          // thread = output column n (weight row), registers = CW consecutive tokens m
-          const int64_t n = x;
-          if (x_in) {
-#pragma unroll
-            for (int j = 0; j < CW; ++j) {
-              const int64_t m = y0 + c0 + j;
-              if (m < g.M) {
-                float o = v[j];
-                if (g.bias_mode == B200Q_BCAST_FULL) o += ld_out_typed(g.bias, g.bias_dtype, m * g.bias_ld + n);
-                if (g.D) o += ld_out_typed(g.D, g.d_dtype, m * g.ldd + n);
-                if (g.out_dtype == B200Q_BF16) static_cast<__nv_bfloat16*>(g.out)[m * g.ldo + n] = __float2bfloat16_rn(o);
-                else static_cast<float*>(g.out)[m * g.ldo + n] = o;
-              }
-            }
-          }
-        }
-      }
+      epi_drain<BN, SWAP>(g, tmem_base + ((uint32_t)(q * 32) << 16) + acc * BN, er, y0, cA, cB, cBias);
       tc_fence_before();
       mbar_arrive(bar_tempty + 8 * acc);
     }
@@ -294,6 +324,206 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
   }
 }
 
+
+// ------------------------------------------------------------------------ CTA-pair kernel
+// Large-M form: two CTAs of a cluster (one per SM of a TPC) share a 256 x BN output tile.  Each
+// CTA loads its own 128 rows of A and its own BN/2 rows of B per ring stage (no multicast: every
+// byte is fetched by exactly one CTA), the even CTA's MMA thread issues
+// tcgen05.mma.cta_group::2 (M = 256), which reads both CTAs' shared memory and writes 128
+// accumulator rows into each CTA's TMEM.  Per flop the pair moves a third less data from L2
+// into shared memory than two independent 128 x BN tiles, which is what bounds the
+// single-CTA kernel.  Barrier traffic: both producers' TMA bytes complete on the even CTA's
+// "full" barrier; tcgen05.commit (multicast to both CTAs) releases ring stages and publishes
+// accumulators; both CTAs' epilogue threads arrive on the even CTA's "accumulator free" barrier.
+template <int BN, int STAGES>
+struct PairSmem {
+  static constexpr int kXBytes = kBlockX * kBlockK;
+  static constexpr int kYBytes = (BN / 2) * kBlockK;
+  static constexpr int kStageBytes = kXBytes + kYBytes;
+  static constexpr int kRing = STAGES * kStageBytes;
+  static constexpr int kEpiFloats = 2 * 3 * BN;
+  static constexpr int kBarOffset = kRing + kEpiFloats * 4;
+  static constexpr int kNumBars = 2 * STAGES + 4;
+  static constexpr int kTotal = kBarOffset + kNumBars * 8 + 16;
+};
+
+template <int BN, int STAGES>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(kThreads, 1)
+gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_y,
+                         const TcGemmParams p) {
+  using L = PairSmem<BN, STAGES>;
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  float* epi_f = reinterpret_cast<float*>(smem + L::kRing);
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + L::kBarOffset);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + L::kNumBars);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  volatile int* epi_stop = reinterpret_cast<volatile int*>(tmem_slot + 2);
+
+  const uint32_t rank = cluster_ctarank();  // 0 = even CTA (issues the MMAs), 1 = its peer
+  const uint32_t smem_base = smem_u32(smem);
+  const uint32_t bar_full = smem_u32(bars), bar_empty = bar_full + 8 * STAGES;
+  const uint32_t bar_tfull = bar_empty + 8 * STAGES, bar_tempty = bar_tfull + 16;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  constexpr uint32_t kTmemCols = 2 * BN <= 256 ? 256 : 512;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(bar_full + 8 * s, 1);   // the even CTA's expect_tx arrival; bytes of both CTAs
+      mbar_init(bar_empty + 8 * s, 1);  // one multicast commit
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(bar_tfull + 8 * a, 1);
+      mbar_init(bar_tempty + 8 * a, 2 * kEpiThreads);  // used in the even CTA only
+    }
+    *abort_flag = 0;
+    *epi_stop = 0;
+    fence_barrier_init();
+    fence_proxy_async_smem();
+    tma_prefetch_desc(&map_x);
+    tma_prefetch_desc(&map_y);
+  }
+  __syncthreads();
+  if (warp == 1) {
+    tmem_alloc_pair(smem_u32(tmem_slot), kTmemCols);
+    tmem_relinquish_pair();
+  }
+  tc_fence_before();
+  cluster_sync_all();  // both CTAs' barriers are initialised before anything signals them remotely
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const int pair = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
+  const int num_tiles = p.x_tiles * p.y_tiles;  // x_tiles counts 256-row tiles here
+  const int num_kb = p.num_kb;
+
+  if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer (both CTAs)
+    if (lane == 0) {
+      uint32_t stage = 0, phase = 0;
+      bool ok = true;
+      for (int tile = pair; tile < num_tiles && ok; tile += num_pairs) {
+        const int xt = tile % p.x_tiles, yt = tile / p.x_tiles;
+        const int x_row = xt * 2 * kBlockX + (int)rank * kBlockX;
+        const int y_row = yt * BN + (int)rank * (BN / 2);
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(bar_empty + 8 * stage, phase ^ 1, abort_flag, p.status, kErrProducer)) {
+            ok = false;
+            break;
+          }
+          const uint32_t full_leader = (bar_full + 8 * stage) & kPeerBitMask;
+          if (rank == 0) mbar_arrive_expect_tx(bar_full + 8 * stage, 2 * L::kStageBytes);
+          tma_load_2d_pair(smem_base + stage * L::kStageBytes, &map_x, full_leader, kb * kBlockK, x_row);
+          tma_load_2d_pair(smem_base + stage * L::kStageBytes + L::kXBytes, &map_y, full_leader, kb * kBlockK, y_row);
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer (even CTA only)
+    if (lane == 0 && rank == 0) {
+      const uint32_t idesc = umma_idesc(p.a_fmt_bits, p.b_fmt_bits, 2 * kBlockX, BN);
+      uint32_t stage = 0, phase = 0;
+      int it = 0;
+      bool ok = true;
+      for (int tile = pair; tile < num_tiles && ok; tile += num_pairs, ++it) {
+        const uint32_t acc = it & 1, acc_phase = (it >> 1) & 1;
+        if (!mbar_wait(bar_tempty + 8 * acc, acc_phase ^ 1, abort_flag, p.status, kErrMmaTmem)) break;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(bar_full + 8 * stage, phase, abort_flag, p.status, kErrMma)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t xs = smem_base + stage * L::kStageBytes, ys = xs + L::kXBytes;
+#pragma unroll
+          for (int k = 0; k < kBlockK / kUmmaK; ++k) {
+            umma_f8_pair(d_tmem, smem_desc_k_sw128(xs + k * kUmmaK), smem_desc_k_sw128(ys + k * kUmmaK), idesc,
+                         (kb | k) != 0);
+          }
+          umma_commit_pair_both(bar_empty + 8 * stage);
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+        if (ok) umma_commit_pair_both(bar_tfull + 8 * acc);
+      }
+    }
+  } else {
+    // ------------------------------------------------------------ epilogue (warps 2..5, both CTAs)
+    const GemmParams& g = p.g;
+    const int q = warp & 3;
+    const int et = threadIdx.x - 64;
+    int it = 0;
+    for (int tile = pair; tile < num_tiles; tile += num_pairs, ++it) {
+      const int xt = tile % p.x_tiles, yt = tile / p.x_tiles;
+      const uint32_t acc = it & 1, acc_phase = (it >> 1) & 1;
+      const int64_t x0 = (int64_t)xt * 2 * kBlockX + (int64_t)rank * kBlockX, y0 = (int64_t)yt * BN;
+      float* cA = epi_f + acc * 3 * BN;
+      float* cB = cA + BN;
+      float* cBias = cB + BN;
+      const EpiRow er = epi_stage_operands<BN, false>(g, p.x_rows, p.y_rows, x0 + q * 32 + lane, y0, et, cA, cB, cBias);
+      mbar_wait(bar_tfull + 8 * acc, acc_phase, abort_flag, p.status, kErrEpilogue);
+      named_bar_sync(1, kEpiThreads);
+      if (et == 0) *epi_stop = *abort_flag;
+      named_bar_sync(1, kEpiThreads);
+      if (*epi_stop) break;
+      tc_fence_after();
+      epi_drain<BN, false>(g, tmem_base + ((uint32_t)(q * 32) << 16) + acc * BN, er, y0, cA, cB, cBias);
+      tc_fence_before();
+      mbar_arrive_cluster((bar_tempty + 8 * acc) & kPeerBitMask);  // the even CTA's barrier
+    }
+  }
+
+  // ---------------------------------------------------------------- teardown
+  __syncwarp();
+  tc_fence_before();
+  __syncthreads();
+  if (*abort_flag) {
+    for (int i = 0; i < 200; ++i) __nanosleep(1000);
+  }
+  cluster_sync_all();  // neither CTA leaves while the other may still touch its shared memory, barriers or TMEM
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc_pair(tmem_base, kTmemCols);
+  }
+}
+
+template <int BN, int STAGES>
+static int launch_pair(const CUtensorMap& mx, const CUtensorMap& my, const TcGemmParams& tp, cudaStream_t st) {
+  using L = PairSmem<BN, STAGES>;
+  constexpr int smem = L::kTotal + 1024;
+  static_assert(smem <= 227 * 1024, "shared memory budget");
+  static_assert(smem > 116 * 1024, "one CTA per SM: two CTAs must never contend for TMEM");
+  auto kern = gemm_tcgen05_pair_kernel<BN, STAGES>;
+  // per device, once: raise the dynamic shared-memory limit and ask how many CTA pairs can be
+  // resident at once (a pair needs both SMs of a TPC); -1 = pairs not available on this device
+  static std::atomic<int> resident_pairs[kMaxDevices];
+  const int dev = current_device_index();
+  if (dev < 0) return B200Q_ERR_CUDA;
+  int clusters = resident_pairs[dev].load(std::memory_order_acquire);
+  if (clusters == 0) {
+    B200Q_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(kNumSMs, 1, 1);
+    cfg.blockDim = dim3(kThreads, 1, 1);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaError_t oe = cudaOccupancyMaxActiveClusters(&clusters, kern, &cfg);
+    if (oe != cudaSuccess || clusters < 1) {
+      cudaGetLastError();
+      clusters = -1;
+    }
+    resident_pairs[dev].store(clusters, std::memory_order_release);
+  }
+  if (clusters < 0) return B200Q_ERR_UNSUPPORTED;
+  int tiles = tp.x_tiles * tp.y_tiles;
+  int pairs = tiles < clusters ? tiles : clusters;
+  kern<<<2 * pairs, kThreads, smem, st>>>(mx, my, tp);
+  B200Q_LAUNCH_CHECK();
+  return B200Q_OK;
+}
+
 // ------------------------------------------------------------------------ host side
 // 2-D map over a row-major byte matrix [rows][kbytes] with row stride ld bytes; box = 128 bytes x box_rows.
 int make_operand_map(CUtensorMap* map, const void* base, int64_t rows, int64_t kbytes, int64_t ld_bytes,
@@ -309,7 +539,13 @@ static int launch_cfg(const CUtensorMap& mx, const CUtensorMap& my, const TcGemm
   static_assert(smem <= 227 * 1024, "shared memory budget");
   static_assert(smem > 116 * 1024, "one CTA per SM: two CTAs must never contend for TMEM");
   auto kern = gemm_tcgen05_kernel<BN, STAGES, SWAP>;
-  B200Q_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+  static std::atomic<int> configured[kMaxDevices];
+  const int dev = current_device_index();
+  if (dev < 0) return B200Q_ERR_CUDA;
+  if (!configured[dev].load(std::memory_order_acquire)) {
+    B200Q_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    configured[dev].store(1, std::memory_order_release);
+  }
   int tiles = tp.x_tiles * tp.y_tiles;
   int grid = tiles < kNumSMs ? tiles : kNumSMs;
   kern<<<grid, kThreads, smem, st>>>(mx, my, tp);
@@ -339,14 +575,53 @@ int gemm_tcgen05_launch(const GemmParams& g, cudaStream_t st) {
     tp.x_rows = g.M; tp.y_rows = g.N;
     tp.a_fmt_bits = fmt_bits(g.a_dtype); tp.b_fmt_bits = fmt_bits(g.b_dtype);
     tp.x_tiles = (int)((g.M + kBlockX - 1) / kBlockX);
-    const int bn = g.N > 128 ? 256 : 128;
+    // Column-tile width: the one that minimises (waves over the 148 SMs) x (tile cost).  A
+    // narrower tile can remove a nearly empty last wave: 4096 x 14336 is 1792 tiles of 256
+    // columns (12.1 waves -> 13) but 2048 tiles of 224 columns (13.8 waves -> 14 shorter ones).
+    static const int kWidths[] = {256, 224, 192, 160, 128};
+    int bn = 128;
+    double best = 1e30;
+    for (int w : kWidths) {
+      if (w > 128 && g.N <= 128) continue;
+      const int64_t tiles = (int64_t)tp.x_tiles * ((g.N + w - 1) / w);
+      const double cost = (double)((tiles + kNumSMs - 1) / kNumSMs) * (w + 24);
+      if (cost < best) { best = cost; bn = w; }
+    }
     tp.y_tiles = (int)((g.N + bn - 1) / bn);
     int rc = make_operand_map(&mx, g.A, g.M, g.K, g.lda, kBlockX);
     if (rc) return rc;
+    // CTA pairs (256-row tiles) when there are enough rows to fill them
+    static const bool no_pairs = std::getenv("B200Q_GEMM_NO_PAIRS") != nullptr;
+    if (g.M > 128 && g.N > 128 && !no_pairs) {
+      TcGemmParams pp = tp;
+      pp.x_tiles = (int)((g.M + 2 * kBlockX - 1) / (2 * kBlockX));
+      int bp = 256;
+      double bestp = 1e30;
+      static const int kPairWidths[] = {256, 224, 192};
+      for (int w : kPairWidths) {
+        const int64_t tiles = (int64_t)pp.x_tiles * ((g.N + w - 1) / w);
+        const double cost = (double)((tiles + kNumSMs / 2 - 1) / (kNumSMs / 2)) * (w + 24);
+        if (cost < bestp) { bestp = cost; bp = w; }
+      }
+      pp.y_tiles = (int)((g.N + bp - 1) / bp);
+      rc = make_operand_map(&my, g.B, g.N, g.K, g.ldb, bp / 2);
+      if (rc) return rc;
+      switch (bp) {
+        case 256: rc = launch_pair<256, 6>(mx, my, pp, st); break;
+        case 224: rc = launch_pair<224, 7>(mx, my, pp, st); break;
+        default: rc = launch_pair<192, 7>(mx, my, pp, st); break;
+      }
+      if (rc != B200Q_ERR_UNSUPPORTED) return rc;
+    }
     rc = make_operand_map(&my, g.B, g.N, g.K, g.ldb, bn);
     if (rc) return rc;
-    if (bn == 256) return launch_cfg<256, 4, false>(mx, my, tp, st);
-    return launch_cfg<128, 6, false>(mx, my, tp, st);
+    switch (bn) {
+      case 256: return launch_cfg<256, 4, false>(mx, my, tp, st);
+      case 224: return launch_cfg<224, 5, false>(mx, my, tp, st);
+      case 192: return launch_cfg<192, 5, false>(mx, my, tp, st);
+      case 160: return launch_cfg<160, 6, false>(mx, my, tp, st);
+      default: return launch_cfg<128, 6, false>(mx, my, tp, st);
+    }
   }
   // small M: weights on the lanes, tokens on the columns
   tp.x_rows = g.N; tp.y_rows = g.M;

@@ -411,7 +411,13 @@ static int launch(const CUtensorMap& ma, const CUtensorMap& mr, const Params& p,
   // TMEM: CTAs that share an SM must never ask for more than 512 columns together
   static_assert(C::kTmemCols * (227 * 1024 / smem) <= 512, "TMEM over-subscription");
   auto kern = w4a16_kernel<BN, SWAP, STAGES, NWBUF>;
-  B200Q_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+  static std::atomic<int> configured[kMaxDevices];
+  const int dev = current_device_index();
+  if (dev < 0) return B200Q_ERR_CUDA;
+  if (!configured[dev].load(std::memory_order_acquire)) {
+    B200Q_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    configured[dev].store(1, std::memory_order_release);
+  }
   int work = p.x_tiles * p.y_tiles * p.splits;
   int per_sm = 227 * 1024 / smem;
   int grid = work < kNumSMs * per_sm ? work : kNumSMs * per_sm;
@@ -438,14 +444,16 @@ static int make_tma_map_raw_w4(CUtensorMap* map, const int32_t* qweight, int64_t
   return r == CUDA_SUCCESS ? B200Q_OK : B200Q_ERR_CUDA;
 }
 
-// Number of K splits the small-M path uses, and the fp32 workspace it needs.
+// Number of K splits the small-M path uses (every split gets at least one k-block), and the
+// fp32 workspace that goes with it.
 static int w4a16_splits(int64_t M, int64_t N, int64_t K) {
   if (M > 128) return 1;
   const int64_t tiles = ((N + 127) / 128) * ((M + 127) / 128);
   const int64_t num_kb = K / w4::kK;
   int s = 1;
   while (tiles * s < 2 * kNumSMs && s * 2 <= num_kb / 4 && s < 16) s *= 2;  // >= 4 stages of k per split
-  return s;
+  const int64_t per = (num_kb + s - 1) / s;
+  return (int)((num_kb + per - 1) / per);  // drop splits that would be empty
 }
 
 size_t w4a16_workspace_bytes_impl(int64_t M, int64_t N, int64_t K) {
