@@ -45,6 +45,8 @@ int dequant_int4_impl(const int32_t*, const void*, const void*, int, int, int, v
 int w4a16_gemm_impl(const void*, int64_t, const int32_t*, const void*, const int32_t*, int, int, int64_t, int64_t,
                     int64_t, int64_t, void*, int, int64_t, void*, size_t, cudaStream_t);
 size_t w4a16_workspace_bytes_impl(int64_t, int64_t, int64_t);
+int w4a16_gemm_noalloc_impl(const void*, int64_t, const int32_t*, const void*, const int32_t*, int, int, int64_t, int64_t,
+                            int64_t, int64_t, void*, int, int64_t, cudaStream_t);
 
 static bool is_fp8(int d) { return d == B200Q_E4M3 || d == B200Q_E5M2; }
 static bool is_wide(int d) { return d == B200Q_F32 || d == B200Q_BF16; }
@@ -178,6 +180,18 @@ int b200q_w4a16_gemm(const void* x, int64_t ldx, const int32_t* qweight, const v
   if (zp_kind == B200Q_ZP_PACKED && !zp) return B200Q_ERR_BAD_ARGUMENT;
   return w4a16_gemm_impl(x, ldx, qweight, scale, zp, zp_kind, k_packed, M, N, K, group, out, out_dtype, ldo, workspace,
                          workspace_bytes, static_cast<cudaStream_t>(stream));
+}
+
+int b200q_w4a16_gemm_noalloc(const void* x, int64_t ldx, const int32_t* qweight, const void* scale, const int32_t* zp,
+                             int zp_kind, int k_packed, int64_t M, int64_t N, int64_t K, int64_t group, void* out,
+                             int out_dtype, int64_t ldo, void* stream) {
+  if (M < 0 || N < 0 || K < 0 || group <= 0) return B200Q_ERR_BAD_ARGUMENT;
+  if (M * N == 0) return B200Q_OK;
+  if (!x || !qweight || !scale || !out || !is_wide(out_dtype)) return B200Q_ERR_BAD_ARGUMENT;
+  if (zp_kind != B200Q_ZP_NONE && zp_kind != B200Q_ZP_PACKED) return B200Q_ERR_UNSUPPORTED;
+  if (zp_kind == B200Q_ZP_PACKED && !zp) return B200Q_ERR_BAD_ARGUMENT;
+  return w4a16_gemm_noalloc_impl(x, ldx, qweight, scale, zp, zp_kind, k_packed, M, N, K, group, out, out_dtype, ldo,
+                                 static_cast<cudaStream_t>(stream));
 }
 
 }  // extern "C"

@@ -521,4 +521,46 @@ int w4a16_gemm_impl(const void* x, int64_t ldx, const int32_t* qweight, const vo
   return B200Q_OK;
 }
 
+// ------------------------------------------------------------------------ allocation-free variant
+// Scratch for b200q_w4a16_gemm_noalloc: it lives in the library image, so every GPU that loads
+// the library carries these 8 MiB until the process exits, and the caller never has to hand in
+// (or allocate) a workspace.  Only device code may use the name directly; host code must ask the
+// runtime for the device address (below).
+constexpr size_t kStaticScratchBytes = size_t(8) << 20;
+static __device__ __align__(256) float g_w4a16_static_scratch[kStaticScratchBytes / sizeof(float)];
+
+// Device address of the static scratch on the current device.  In host code the array's name
+// is only a stand-in for the symbol, not a pointer the GPU can follow, so the address is
+// looked up with cudaGetSymbolAddress -- once per device, with that device current -- and kept.
+static int static_scratch_ptr(float** out) {
+  static std::atomic<float*> cache[kMaxDevices];
+  const int dev = current_device_index();
+  if (dev < 0) return B200Q_ERR_CUDA;
+  float* p = cache[dev].load(std::memory_order_acquire);
+  if (!p) {
+    void* addr = nullptr;
+    B200Q_CUDA_OK(cudaGetSymbolAddress(&addr, g_w4a16_static_scratch));
+    p = static_cast<float*>(addr);
+    cache[dev].store(p, std::memory_order_release);
+  }
+  *out = p;
+  return B200Q_OK;
+}
+
+int w4a16_gemm_noalloc_impl(const void* x, int64_t ldx, const int32_t* qweight, const void* scale, const int32_t* zp,
+                            int zp_kind, int k_packed, int64_t M, int64_t N, int64_t K, int64_t group, void* out,
+                            int out_dtype, int64_t ldo, cudaStream_t st) {
+  const size_t need = w4a16_workspace_bytes_impl(M, N, K);
+  if (need > kStaticScratchBytes) return B200Q_ERR_TOO_LARGE;
+  float* scratch = nullptr;
+  int rc = static_scratch_ptr(&scratch);
+  if (rc) return rc;
+  // Nothing in the scratch has to start at zero: every (split, row, column) cell that the
+  // reduction reads is written by exactly one CTA of this call first.
+  return w4a16_gemm_impl(x, ldx, qweight, scale, zp, zp_kind, k_packed, M, N, K, group, out, out_dtype, ldo, scratch,
+                         kStaticScratchBytes, st);
+}
+
+size_t w4a16_noalloc_max_bytes_impl() { return kStaticScratchBytes; }
+
 }  // namespace b200q

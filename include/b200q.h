@@ -191,6 +191,34 @@ int b200q_w4a16_gemm(const void* x, int64_t ldx, const int32_t* qweight, const v
                      size_t workspace_bytes, void* stream);
 
 /*
+ * w4a16_gemm_noalloc: b200q_w4a16_gemm for callers that cannot supply a workspace.
+ * It has no counterpart in the reference.
+ *
+ * Who needs it: code that runs where device memory must not be requested -- a serving loop
+ * whose memory plan was frozen at start-up (all of HBM already handed to weights and KV
+ * cache, so a cudaMalloc could fail or stall the device while it synchronises), a plug-in
+ * called from inside another framework's stream callback or memory-pool critical section,
+ * or a host language binding that owns no allocator at all.  Such callers pass only their
+ * inputs and the output; the split-K scratch that the small-M path needs sits in an 8 MiB
+ * array that is part of the library image (every GPU that loads the library keeps it until
+ * the process exits).
+ *
+ * Same arguments and results as b200q_w4a16_gemm without the workspace pair.  Limits and rules:
+ *  - the call fails with B200Q_ERR_TOO_LARGE when b200q_w4a16_workspace_bytes(M, N, K) exceeds
+ *    8 MiB (for K = N = 8192 that admits M <= 32; M > 128 needs no scratch and always fits);
+ *  - it calls no cudaMalloc / cudaFree and no allocating library routine;
+ *  - the first call on a device looks up the array's device address (cudaGetSymbolAddress, with
+ *    that device current) and keeps it; make that first call before any stream capture;
+ *  - all calls share the one array and it keeps the previous call's contents (nothing in it
+ *    needs clearing: each cell is written before it is read within a call), so two calls
+ *    that overlap on the GPU -- different streams, or different threads -- race.  Serialise them.
+ */
+int b200q_w4a16_gemm_noalloc(const void* x, int64_t ldx, const int32_t* qweight, const void* scale,
+                             const int32_t* zp, int zp_kind, int k_packed, int64_t M, int64_t N,
+                             int64_t K, int64_t group, void* out, int out_dtype, int64_t ldo,
+                             void* stream);
+
+/*
  * swiglu_cast_fp8: out8 = e4m3(bf16(silu(gate) * up) * scale), the activation step between the
  * column-parallel and the row-parallel GEMMs of an FP8 MLP, in one pass.
  * No single counterpart in the reference (silu, mul and CastToFp8V2 are separate nodes there,
