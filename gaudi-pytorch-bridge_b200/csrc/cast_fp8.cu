@@ -124,25 +124,30 @@ __global__ void __launch_bounds__(256) cast_to_fp8_kernel(CastParams p) {
     }
     uint32_t o[4];
     if (SR) {
-      const uint64_t g = p.first_index + (uint64_t)base;  // multiple of 4 only if first_index is
+      // bf16 product: 8 random bits per element (one Philox block per 16 elements); otherwise 16
+      const uint64_t g = p.first_index + (uint64_t)base;
       float z[16];
-      if ((p.first_index & 3) == 0) {
+      const bool rb8 = BF16 && !p.mul_fp32;
+      if ((p.first_index & 15) == 0) {
+        if (rb8) {
+          const uint4 r = philox4x32_10(g >> 4, p.seed, p.offset);
+          const uint32_t rw[4] = {r.x, r.y, r.z, r.w};
 #pragma unroll
-        for (int q = 0; q < 4; ++q) {
-          uint4 r = philox4x32_10((g >> 2) + q, p.seed, p.offset);
-          z[4 * q + 0] = sr_round<FMT>(clampf<FMT>(y[4 * q + 0]), r.x);
-          z[4 * q + 1] = sr_round<FMT>(clampf<FMT>(y[4 * q + 1]), r.y);
-          z[4 * q + 2] = sr_round<FMT>(clampf<FMT>(y[4 * q + 2]), r.z);
-          z[4 * q + 3] = sr_round<FMT>(clampf<FMT>(y[4 * q + 3]), r.w);
+          for (int i = 0; i < 16; ++i) z[i] = sr_round<FMT, 8>(y[i], (rw[i >> 2] >> ((i & 3) * 8)) & 0xFFu);
+        } else {
+#pragma unroll
+          for (int h = 0; h < 2; ++h) {
+            const uint4 r = philox4x32_10((g >> 3) + h, p.seed, p.offset);
+            const uint32_t rw[4] = {r.x, r.y, r.z, r.w};
+#pragma unroll
+            for (int i = 0; i < 8; ++i) z[8 * h + i] = sr_round<FMT, 16>(y[8 * h + i], (rw[i >> 1] >> ((i & 1) * 16)) & 0xFFFFu);
+          }
         }
       } else {
 #pragma unroll 1
-        for (int i = 0; i < 16; ++i) {
-          uint64_t gi = g + i;
-          uint4 r = philox4x32_10(gi >> 2, p.seed, p.offset);
-          uint32_t rr = (gi & 3) == 0 ? r.x : (gi & 3) == 1 ? r.y : (gi & 3) == 2 ? r.z : r.w;
-          z[i] = sr_round<FMT>(clampf<FMT>(y[i]), rr);
-        }
+        for (int i = 0; i < 16; ++i)
+          z[i] = rb8 ? sr_round<FMT, 8>(y[i], sr_random_bits<8>(g + i, p.seed, p.offset))
+                     : sr_round<FMT, 16>(y[i], sr_random_bits<16>(g + i, p.seed, p.offset));
       }
 #pragma unroll
       for (int i = 0; i < 4; ++i)
@@ -177,10 +182,9 @@ __global__ void __launch_bounds__(256) cast_to_fp8_kernel(CastParams p) {
     }
     float z = clampf<FMT>(y);
     if (SR) {
-      uint64_t gi = p.first_index + (uint64_t)i;
-      uint4 r = philox4x32_10(gi >> 2, p.seed, p.offset);
-      uint32_t rr = (gi & 3) == 0 ? r.x : (gi & 3) == 1 ? r.y : (gi & 3) == 2 ? r.z : r.w;
-      z = sr_round<FMT>(z, rr);
+      const uint64_t gi = p.first_index + (uint64_t)i;
+      z = (BF16 && !p.mul_fp32) ? sr_round<FMT, 8>(y, sr_random_bits<8>(gi, p.seed, p.offset))
+                                : sr_round<FMT, 16>(y, sr_random_bits<16>(gi, p.seed, p.offset));
     }
     uint32_t b = cvt_fp8x2<FMT>(z, 0.f) & 0xFFu;
     if (y != y) b = nan_byte<FMT>(y);
@@ -285,6 +289,123 @@ __global__ void __launch_bounds__(256) cast_bf16_rne_fast_kernel(CastParams p) {
       y = round_to_bf16(x * round_to_bf16(s));
     }
     uint32_t b = cvt_fp8x2<FMT>(y, 0.f) & 0xFFu;
+    if (y != y) b = 0x7Fu;
+    out[i] = (uint8_t)b;
+  }
+  if (p.amax) block_amax_to_global(amax_bits, p.amax);
+}
+
+// ------------------------------------------------------------------ bf16 -> fp8, stochastic, fast path
+// Same frame as the RNE fast path.  In the normal range a bf16 product needs only its low
+// g = 4 (e4m3) or 5 (e5m2) mantissa bits resolved, so stochastic rounding is a packed integer
+// add of g random bits to both halves of a bf16x2 word followed by a mask; one Philox block
+// (16 random bytes) serves a 16-element chunk.  Chunks that hold a value below the smallest
+// normal, an infinity or a NaN take the general per-element routine instead (same definition).
+template <int FMT>
+__device__ __forceinline__ uint4 cast16_bf16_sr(const uint4 a, const uint4 b, uint32_t s2, bool has_scale,
+                                                uint32_t& amax2, uint64_t gi, uint64_t seed, uint64_t offset) {
+  constexpr int g = (23 - Fp8Fmt<FMT>::kMant) - 16;
+  constexpr uint32_t kLow = (1u << g) - 1u;
+  constexpr uint32_t kMinNormalBf16 = (uint32_t)Fp8Fmt<FMT>::kEmin << 7;  // bf16 bits of 2^Emin
+  uint32_t w[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+  uint32_t y[8];
+  uint32_t lo_mag = 0xFFFFFFFFu, hi_mag = 0;  // min / max of the 15-bit magnitudes in the chunk
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    amax2 = bf16x2_max_nan(amax2, w[i] & 0x7FFF7FFFu);
+    y[i] = has_scale ? bf16x2_mul(w[i], s2) : w[i];
+    const uint32_t m = y[i] & 0x7FFF7FFFu;
+    lo_mag = min(lo_mag, min(m & 0xFFFFu, m >> 16));
+    hi_mag = max(hi_mag, max(m & 0xFFFFu, m >> 16));
+  }
+  const uint4 r = philox4x32_10(gi >> 4, seed, offset);
+  const uint32_t rw[4] = {r.x, r.y, r.z, r.w};
+  uint32_t o[4];
+  if (lo_mag >= kMinNormalBf16 && hi_mag < 0x7F80u) {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      // bytes 2*(i%2), 2*(i%2)+1 of word i/2 -> low bytes of the two halves, top g bits kept
+      const uint32_t rr = (__byte_perm(rw[i >> 1], 0u, (i & 1) ? 0x4342 : 0x4140) >> (8 - g)) & (kLow | (kLow << 16));
+      y[i] = (y[i] + rr) & ~(kLow | (kLow << 16));
+    }
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const uint32_t l = cvt_fp8x2<FMT>(__uint_as_float(y[2 * i] << 16), __uint_as_float(y[2 * i] & 0xFFFF0000u));
+      const uint32_t h = cvt_fp8x2<FMT>(__uint_as_float(y[2 * i + 1] << 16), __uint_as_float(y[2 * i + 1] & 0xFFFF0000u));
+      o[i] = l | (h << 16);
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      uint32_t word = 0;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int e = 4 * i + j;
+        const float v = __uint_as_float((e & 1) ? (y[e >> 1] & 0xFFFF0000u) : (y[e >> 1] << 16));
+        const float z = sr_round<FMT, 8>(v, (rw[e >> 2] >> ((e & 3) * 8)) & 0xFFu);
+        uint32_t byte = cvt_fp8x2<FMT>(z, 0.f) & 0xFFu;
+        if (v != v) byte = 0x7Fu;
+        word |= byte << (8 * j);
+      }
+      o[i] = word;
+    }
+  }
+  return make_uint4(o[0], o[1], o[2], o[3]);
+}
+
+template <int FMT, bool PER_ROW>
+__global__ void __launch_bounds__(256) cast_bf16_sr_fast_kernel(CastParams p) {
+  const __nv_bfloat16* __restrict__ in = static_cast<const __nv_bfloat16*>(p.in);
+  uint8_t* __restrict__ out = static_cast<uint8_t*>(p.out);
+  const int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const int64_t nthreads = (int64_t)gridDim.x * blockDim.x;
+  const int64_t nvec = p.n / 16;
+  uint32_t s2 = 0;
+  if (!PER_ROW && p.has_scale) {
+    float s = p.scale_from_dev ? __ldg(p.scale) : p.scale_host;
+    s2 = pack_bf16x2(s, s);
+  }
+  uint32_t amax2 = 0;
+  int64_t v = tid;
+  for (; v + nthreads < nvec; v += 2 * nthreads) {
+    const int64_t b0 = v * 16, b1 = (v + nthreads) * 16;
+    const uint4* s0 = reinterpret_cast<const uint4*>(in + b0);
+    const uint4* s1 = reinterpret_cast<const uint4*>(in + b1);
+    uint4 a0 = __ldcs(s0), a1 = __ldcs(s0 + 1), c0 = __ldcs(s1), c1 = __ldcs(s1 + 1);
+    uint32_t sa = s2, sc = s2;
+    if (PER_ROW) {
+      float f0 = __ldg(p.scale + b0 / p.cols), f1 = __ldg(p.scale + b1 / p.cols);
+      sa = pack_bf16x2(f0, f0);
+      sc = pack_bf16x2(f1, f1);
+    }
+    __stcs(reinterpret_cast<uint4*>(out + b0),
+           cast16_bf16_sr<FMT>(a0, a1, sa, p.has_scale, amax2, p.first_index + (uint64_t)b0, p.seed, p.offset));
+    __stcs(reinterpret_cast<uint4*>(out + b1),
+           cast16_bf16_sr<FMT>(c0, c1, sc, p.has_scale, amax2, p.first_index + (uint64_t)b1, p.seed, p.offset));
+  }
+  for (; v < nvec; v += nthreads) {
+    const int64_t b0 = v * 16;
+    const uint4* s0 = reinterpret_cast<const uint4*>(in + b0);
+    uint4 a0 = __ldcs(s0), a1 = __ldcs(s0 + 1);
+    uint32_t sa = s2;
+    if (PER_ROW) {
+      float f0 = __ldg(p.scale + b0 / p.cols);
+      sa = pack_bf16x2(f0, f0);
+    }
+    __stcs(reinterpret_cast<uint4*>(out + b0),
+           cast16_bf16_sr<FMT>(a0, a1, sa, p.has_scale, amax2, p.first_index + (uint64_t)b0, p.seed, p.offset));
+  }
+  uint32_t amax_bits = max(amax2 << 16, amax2 & 0xFFFF0000u);
+  for (int64_t i = nvec * 16 + tid; i < p.n; i += nthreads) {
+    float x = __bfloat162float(in[i]);
+    amax_bits = max(amax_bits, __float_as_uint(x) & 0x7FFFFFFFu);
+    float y = x;
+    if (p.has_scale) {
+      float s = PER_ROW ? p.scale[i / p.cols] : (p.scale_from_dev ? __ldg(p.scale) : p.scale_host);
+      y = round_to_bf16(x * round_to_bf16(s));
+    }
+    const float z = sr_round<FMT, 8>(y, sr_random_bits<8>(p.first_index + (uint64_t)i, p.seed, p.offset));
+    uint32_t b = cvt_fp8x2<FMT>(z, 0.f) & 0xFFu;
     if (y != y) b = 0x7Fu;
     out[i] = (uint8_t)b;
   }
@@ -512,9 +633,18 @@ int cast_to_fp8_impl(const void* in, int in_dtype, void* out, int out_dtype, con
   const bool sr = rounding == B200Q_ROUND_STOCHASTIC;
   // fast path: bf16 input, RNE, product in bf16, one scale per 16-element chunk, aligned pointers
   const bool aligned = ((reinterpret_cast<uintptr_t>(in) | reinterpret_cast<uintptr_t>(out)) & 15) == 0;
-  const bool fast = in_dtype == B200Q_BF16 && !sr && !p.mul_fp32 && aligned &&
-                    (sc == SC_ONE || (sc == SC_ROW && cols % 16 == 0));
-  if (fast) {
+  const bool fast = in_dtype == B200Q_BF16 && !p.mul_fp32 && aligned &&
+                    (sc == SC_ONE || (sc == SC_ROW && cols % 16 == 0)) && (!sr || (first_index & 15) == 0);
+  if (fast && sr) {
+    const int64_t half = (items + 1) / 2;
+    if (out_dtype == B200Q_E4M3) {
+      if (sc == SC_ROW) launch_persistent(cast_bf16_sr_fast_kernel<B200Q_E4M3, true>, half, st, p);
+      else launch_persistent(cast_bf16_sr_fast_kernel<B200Q_E4M3, false>, half, st, p);
+    } else {
+      if (sc == SC_ROW) launch_persistent(cast_bf16_sr_fast_kernel<B200Q_E5M2, true>, half, st, p);
+      else launch_persistent(cast_bf16_sr_fast_kernel<B200Q_E5M2, false>, half, st, p);
+    }
+  } else if (fast) {
     const int64_t half = (items + 1) / 2;  // two chunks per thread and step
     if (out_dtype == B200Q_E4M3) {
       if (sc == SC_ROW) launch_persistent(cast_bf16_rne_fast_kernel<B200Q_E4M3, true>, half, st, p);

@@ -104,32 +104,43 @@ __device__ __forceinline__ uint4 philox4x32_10(uint64_t block, uint64_t seed, ui
   return make_uint4(c0, c1, c2, c3);
 }
 
-// Stochastic rounding of an fp32 value (already clamped to +-max) to a float that the fp8
-// format represents exactly.  r is the element's 32-bit random word.
-template <int FMT>
+// Stochastic rounding of the fp32 product v to a float that the fp8 format represents exactly
+// (NaN passes through; the caller writes the NaN byte).  r holds RB random bits (8 when v is a
+// bf16 value, 16 otherwise).  With d = 23 - mantissa bits and g = d - 16:
+//   a = min(|v|, max); below the smallest normal the value is first lifted by that amount so
+//   that the dropped bits sit at the same place (u = a + 2^Emin, an fp32 addition);
+//   r_d = (r >> (8 - g)) << 16 for RB == 8 in the normal range (the top g bits are all that a
+//   bf16 value can need), otherwise (r << (d - RB)) + (1 << (d - RB - 1));
+//   bits(u) += r_d, low d bits cleared, the lift removed, clamped to max, sign restored.
+template <int FMT, int RB>
 __device__ __forceinline__ float sr_round(float v, uint32_t r) {
   constexpr int d = 23 - Fp8Fmt<FMT>::kMant;
-  uint32_t bits = __float_as_uint(v);
-  uint32_t sign = bits & 0x80000000u, mag = bits & 0x7FFFFFFFu;
-  int E = (int)(mag >> 23);
-  float res;
-  if (E >= Fp8Fmt<FMT>::kEmin) {
-    uint32_t m = (mag + (r & ((1u << d) - 1u))) & ~((1u << d) - 1u);
-    res = fminf(__uint_as_float(m), Fp8Fmt<FMT>::kMax);
-    if (mag > 0x7F800000u) res = __uint_as_float(mag);  // NaN stays NaN
-  } else {
-    int Ee = E > 0 ? E : 1;
-    uint32_t m = E > 0 ? ((mag & 0x7FFFFFu) | 0x800000u) : (mag & 0x7FFFFFu);
-    int s = d + (Fp8Fmt<FMT>::kEmin - Ee);
-    int extra = s > 32 ? s - 32 : 0;
-    if (extra > 31) { m = 0; extra = 0; }
-    m >>= extra;
-    int s2 = s > 32 ? 32 : s;
-    uint64_t mask = (s2 >= 32) ? 0xFFFFFFFFull : ((1ull << s2) - 1ull);
-    uint64_t t = ((uint64_t)m + ((uint64_t)r & mask)) >> s2;
-    res = (float)(uint32_t)t * Fp8Fmt<FMT>::kQuantum;
-  }
+  constexpr int g = d - 16;
+  const float min_normal = __uint_as_float((uint32_t)Fp8Fmt<FMT>::kEmin << 23);
+  const uint32_t sign = __float_as_uint(v) & 0x80000000u;
+  if (v != v) return v;
+  const float a = fminf(fabsf(v), Fp8Fmt<FMT>::kMax);
+  const bool sub = a < min_normal;
+  const float u = sub ? a + min_normal : a;
+  uint32_t r_d = (r << (d - RB)) + (1u << (d - RB - 1));
+  if (RB == 8 && !sub) r_d = (r >> (8 - g)) << 16;
+  const uint32_t b = (__float_as_uint(u) + r_d) & ~((1u << d) - 1u);
+  float res = __uint_as_float(b);
+  if (sub) res -= min_normal;
+  res = fminf(res, Fp8Fmt<FMT>::kMax);
   return __uint_as_float(__float_as_uint(res) | sign);
+}
+
+// The RB random bits of global element index gi (see philox4x32_10): block gi / (128 / RB),
+// consecutive bytes (RB = 8) or halves (RB = 16) of the block's four words.
+template <int RB>
+__device__ __forceinline__ uint32_t sr_random_bits(uint64_t gi, uint64_t seed, uint64_t offset) {
+  constexpr int per = 128 / RB, per_word = 32 / RB;
+  const uint4 r = philox4x32_10(gi / per, seed, offset);
+  const int e = (int)(gi % per);
+  const int w = e / per_word;
+  const uint32_t word = w == 0 ? r.x : w == 1 ? r.y : w == 2 ? r.z : r.w;
+  return (word >> ((e % per_word) * RB)) & ((1u << RB) - 1u);
 }
 
 __device__ __forceinline__ uint32_t warp_max_u32(uint32_t v) {

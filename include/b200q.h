@@ -80,8 +80,10 @@ uint64_t b200q_launch_count(void);
  * scale     per b200q_bcast, fp32; the product is formed in the input dtype (the scale
  *           is first rounded to it) unless B200Q_CAST_MUL_IN_FP32 is set
  * amax      NULL or one fp32; written by the call (zeroed on `stream` first)
- * rounding  b200q_rounding; for STOCHASTIC element i uses 32-bit word (first_index+i)%4 of
- *           Philox block (first_index+i)/4 with key = seed and counter words 2,3 = offset
+ * rounding  b200q_rounding; for STOCHASTIC, element i draws from Philox4x32-10 (key = seed,
+ *           counter = (block, offset)) at global index first_index + i: 8 random bits per
+ *           element, 16 elements per block, when the product is a bf16 value (bf16 input and
+ *           no B200Q_CAST_MUL_IN_FP32), else 16 bits per element, 8 elements per block
  */
 int b200q_cast_to_fp8(const void* in, int in_dtype, void* out, int out_dtype,
                       const float* scale, float scale_host, int scale_mode,
