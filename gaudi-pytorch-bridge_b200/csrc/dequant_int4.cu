@@ -171,20 +171,30 @@ __global__ void __launch_bounds__(256) dequant_rowpacked_bf16_kernel(DequantPara
     int64_t r = r0 + j;
     w[j] = r < p.rows ? (uint32_t)__ldcs(p.packed + r * p.cols_packed + cp) : 0u;
   }
-  int64_t last_sr = -1;
+  // group index of the first row by one division, then by counting (a 64-bit division per row
+  // would cost more than the expansion itself)
+  int64_t sr = r0 / p.group_rows;
+  int64_t left = (sr + 1) * p.group_rows - r0;  // rows of this block that still belong to group sr
+  bool fresh = true;
   GroupBf2 g;
+  __nv_bfloat16* orow = out + r0 * cols + cp * 8;
 #pragma unroll
   for (int j = 0; j < kFastRows; ++j) {
-    int64_t r = r0 + j;
-    if (r >= p.rows) break;
-    int64_t sr = r / p.group_rows;
-    if (sr != last_sr) {
+    if (r0 + j >= p.rows) break;
+    if (left == 0) {
+      ++sr;
+      left = p.group_rows;
+      fresh = true;
+    }
+    if (fresh) {
       uint32_t zw = 0;
       if (p.zp_kind == B200Q_ZP_PACKED) zw = (uint32_t)__ldg(static_cast<const int32_t*>(p.zp) + sr * p.cols_packed + cp);
       load_group_bf2<SIGNED>(g, scale + sr * cols + cp * 8, p.zp_kind == B200Q_ZP_PACKED, zw);
-      last_sr = sr;
+      fresh = false;
     }
-    __stcs(reinterpret_cast<uint4*>(out + r * cols + cp * 8), expand_word_bf2<SIGNED>(w[j], g));
+    --left;
+    __stcs(reinterpret_cast<uint4*>(orow), expand_word_bf2<SIGNED>(w[j], g));
+    orow += cols;
   }
 }
 

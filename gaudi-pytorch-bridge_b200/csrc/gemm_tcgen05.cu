@@ -296,7 +296,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
       // The wait can give up for some threads only; the decision to stop must be the same for
       // all 128 epilogue threads because they meet at named barriers: one thread samples the
       // abort flag between two barriers and everybody follows that sample.
-      mbar_wait(bar_tfull + 8 * acc, acc_phase, abort_flag, p.status, kErrEpilogue);
+      mbar_wait(bar_tfull + 8 * acc, acc_phase, abort_flag, p.status, kErrEpilogue, 128);
       named_bar_sync(1, kEpiThreads);
       if (et == 0) *epi_stop = *abort_flag;
       named_bar_sync(1, kEpiThreads);
@@ -463,7 +463,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
       float* cB = cA + BN;
       float* cBias = cB + BN;
       const EpiRow er = epi_stage_operands<BN, false>(g, p.x_rows, p.y_rows, x0 + q * 32 + lane, y0, et, cA, cB, cBias);
-      mbar_wait(bar_tfull + 8 * acc, acc_phase, abort_flag, p.status, kErrEpilogue);
+      mbar_wait(bar_tfull + 8 * acc, acc_phase, abort_flag, p.status, kErrEpilogue, 128);
       named_bar_sync(1, kEpiThreads);
       if (et == 0) *epi_stop = *abort_flag;
       named_bar_sync(1, kEpiThreads);

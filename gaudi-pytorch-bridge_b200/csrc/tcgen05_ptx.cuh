@@ -44,11 +44,15 @@ __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity)
 
 // Bounded wait.  `abort_flag` is a shared-memory word any role may set; the wait gives up
 // when it is set or after kWaitLimit polls (seconds of wall time), and then sets it itself.
+// `backoff_ns` > 0 makes a waiter that is not on the critical path (an epilogue warp waiting
+// for the whole main loop of its tile) sleep between polls, so that it does not take issue
+// slots from the warps that feed the tensor core.
 constexpr uint32_t kWaitLimit = 1u << 24;
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status,
-                                          int code) {
+                                          int code, uint32_t backoff_ns = 0) {
   for (uint32_t i = 0; i < kWaitLimit; ++i) {
     if (mbar_try_wait(bar, parity)) return true;
+    if (backoff_ns) __nanosleep(backoff_ns);
     if ((i & 255u) == 255u) {
       if (*abort_flag) return false;
       if (i > 4096u) __nanosleep(64);

@@ -231,7 +231,7 @@ w4a16_kernel(const __grid_constant__ CUtensorMap map_act, const __grid_constant_
       int xt, yt, kb0, kb1, split;
       decode(w, xt, yt, kb0, kb1, split);
       const uint32_t acc = it & 1, acc_phase = (it >> 1) & 1;
-      mbar_wait(bar_tfull + 8 * acc, acc_phase, abort_flag, p.status, kErrEpilogue);
+      mbar_wait(bar_tfull + 8 * acc, acc_phase, abort_flag, p.status, kErrEpilogue, 128);
       named_bar_sync(1, kEpiThreads);
       if (et == 0) *epi_stop = *abort_flag;
       named_bar_sync(1, kEpiThreads);
