@@ -28,6 +28,20 @@ __device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t byt
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
+// Non-blocking probe of a phase (test_wait never suspends the thread).
+__device__ __forceinline__ uint32_t mbar_test_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n"
+      "selp.u32 %0, 1, 0, p;\n"
+      "}\n"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok;
+}
 __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(
@@ -51,7 +65,11 @@ constexpr uint32_t kWaitLimit = 1u << 24;
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status,
                                           int code, uint32_t backoff_ns = 0) {
   for (uint32_t i = 0; i < kWaitLimit; ++i) {
+#ifdef B200Q_SPIN_TEST_WAIT
+    if (mbar_test_wait(bar, parity)) return true;
+#else
     if (mbar_try_wait(bar, parity)) return true;
+#endif
     if (backoff_ns) __nanosleep(backoff_ns);
     if ((i & 255u) == 255u) {
       if (*abort_flag) return false;
@@ -225,10 +243,28 @@ __device__ __forceinline__ uint64_t smem_desc_k_sw128(uint32_t saddr) {
   return d;
 }
 
+// MN-major operand (the M or N index is contiguous in memory), 128-byte swizzle: 64 bf16 along
+// MN form a 128-byte row, 8 consecutive k form a 1024-byte atom; `lbo` is the byte distance
+// between 64-element MN blocks and `sbo` the distance between 8-k groups.
+__device__ __forceinline__ uint64_t smem_desc_mn_sw128(uint32_t saddr, uint32_t lbo, uint32_t sbo) {
+  uint64_t d = 0;
+  d |= (uint64_t)((saddr & 0x3FFFFu) >> 4);
+  d |= (uint64_t)((lbo >> 4) & 0x3FFFu) << 16;
+  d |= (uint64_t)((sbo >> 4) & 0x3FFFu) << 32;
+  d |= (uint64_t)1 << 46;
+  d |= (uint64_t)2 << 61;
+  return d;
+}
+
 // Instruction descriptor (dense, fp32 accumulate, both operands K-major).
 // fmt for kind::f8f6f4: 0 = e4m3, 1 = e5m2; for kind::f16: 0 = f16, 1 = bf16.
 __host__ __device__ constexpr uint32_t umma_idesc(uint32_t a_fmt, uint32_t b_fmt, uint32_t m, uint32_t n) {
   return (1u << 4) | (a_fmt << 7) | (b_fmt << 10) | ((n >> 3) << 17) | ((m >> 4) << 24);
+}
+// Same with the operands' major-ness: bit 15 = A is MN-major, bit 16 = B is MN-major.
+__host__ __device__ constexpr uint32_t umma_idesc_major(uint32_t a_fmt, uint32_t b_fmt, uint32_t m, uint32_t n,
+                                                        uint32_t a_mn, uint32_t b_mn) {
+  return umma_idesc(a_fmt, b_fmt, m, n) | (a_mn << 15) | (b_mn << 16);
 }
 
 }  // namespace ptx

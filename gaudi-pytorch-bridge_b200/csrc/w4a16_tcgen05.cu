@@ -3,16 +3,17 @@
 // of the weight operand, so the bf16 weights never exist in global memory.
 //
 // Warp-specialised, persistent:
-//   warp 0        TMA producer: activation tile (bf16, 128-byte swizzle) and the raw packed-weight
-//                 tile into a shared-memory ring.  The weight tile is fetched through a 3-D
-//                 tensor map that views K as (k / 8, k % 8) and lands in shared memory as
-//                 row (k % 8) * 8 + k / 8 with the hardware swizzle on, which is what lets the
-//                 expanders read it without bank conflicts (see the expander section)
-//   warps 6..     expanders (4 warps per 128 weight columns): read packed words from the ring,
-//                 expand with packed bf16x2 arithmetic ((128+q)-(128+z) exact, one rounding in the
-//                 multiply by the scale: bit-identical to the stand-alone dequant kernel), transpose
-//                 8x8 in registers and write K-major, 128-byte-swizzled bf16 tiles, then
-//                 fence.proxy.async + mbarrier arrive
+//   warp 0        TMA producer: per ring stage the activation tile (bf16, K-major, 128-byte
+//                 swizzle), the raw packed-weight tile [64 k][W words], and the k-group's scales
+//                 and packed zero points
+//   warps 6..     expanders: each thread takes packed words (k, column group) from the ring and
+//                 expands them with packed bf16x2 arithmetic ((128+q)-(128+z) exact, one rounding
+//                 in the multiply by the scale: bit-identical to the stand-alone dequant kernel).
+//                 A word is eight neighbouring COLUMNS of one k, so the expanded tile is written
+//                 MN-major (columns contiguous, 64 per 128-byte row, 8 k per swizzle atom) and the
+//                 tensor core reads it through an MN-major descriptor: no transpose.  The nibble
+//                 pairs come out as columns (i, i+4); they are stored in that order and the
+//                 epilogue undoes the permutation when it writes the output columns.
 //   warp 1        MMA issuer: tcgen05.mma.kind::f16 (bf16 x bf16 -> fp32 in TMEM)
 //   warps 2..5    epilogue: tcgen05.ld, convert, store (or fp32 partials for split-K)
 //
@@ -57,16 +58,25 @@ struct Cfg {
   static constexpr int kActRows = SWAP ? BN : 128;
   static constexpr int kActBytes = kActRows * 128;
   static constexpr int kRawBytes = kUnits * kRawUnit;
-  static constexpr int kStageBytes = ((kActBytes + kRawBytes + 1023) / 1024) * 1024;
-  static constexpr int kTxBytes = kActBytes + kRawBytes;
-  static constexpr int kRawRowBytes = kUnits * 64;  // 64 (64-byte swizzle) or 128 (128-byte swizzle)
+  // group scales (bf16) and packed zero points of the stage's k-group ride in the same ring:
+  // fetched from global memory by the expanders they would put a DRAM/L2 latency on every
+  // group change, in the ring they are covered by the pipeline depth like everything else
+  static constexpr int kWCols = kUnits * kUnit;
+  static constexpr int kMetaOffset = kActBytes + kRawBytes;
+  static constexpr int kScaleBytes = kWCols * 2, kZpBytes = kWCols / 2;
+  static constexpr int kZpOffset = kMetaOffset + 512;
+  static constexpr int kStageBytes = ((kMetaOffset + 1024 + 1023) / 1024) * 1024;
+  static constexpr int kTxBytes = kActBytes + kRawBytes + kScaleBytes;  // + kZpBytes when there are zero points
+  static constexpr int kRawRowWords = kUnits * 16;  // packed words per k-row of the stage's tile
   static constexpr int kWBufBytes = kUnits * kUnit * 128;
   static constexpr int kRing = STAGES * kStageBytes;
   static constexpr int kWOffset = kRing;
   static constexpr int kBarOffset = kWOffset + NWBUF * kWBufBytes;
   static constexpr int kNumBars = 2 * STAGES + 2 * NWBUF + 4;
   static constexpr int kTotal = kBarOffset + kNumBars * 8 + 16;
-  static constexpr int kExpandWarps = 4 * kUnits;
+  // 8 expander warps per 128 weight columns: each thread expands 4 packed words per stage
+  static constexpr int kSplit = 2;
+  static constexpr int kExpandWarps = 4 * kUnits * kSplit;
   static constexpr int kThreads = 32 * (6 + kExpandWarps);
   static constexpr uint32_t kTmemCols = (2 * BN) < 32 ? 32 : 2 * BN;
 };
@@ -107,7 +117,8 @@ __device__ __forceinline__ void make_group(GroupRegs& g, uint4 s, uint32_t zw, b
 
 template <int BN, bool SWAP, int STAGES, int NWBUF>
 __global__ void __launch_bounds__((Cfg<BN, SWAP, STAGES, NWBUF>::kThreads), 1)
-w4a16_kernel(const __grid_constant__ CUtensorMap map_act, const __grid_constant__ CUtensorMap map_raw, const Params p) {
+w4a16_kernel(const __grid_constant__ CUtensorMap map_act, const __grid_constant__ CUtensorMap map_raw,
+             const __grid_constant__ CUtensorMap map_scale, const __grid_constant__ CUtensorMap map_zp, const Params p) {
   using C = Cfg<BN, SWAP, STAGES, NWBUF>;
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -142,6 +153,8 @@ w4a16_kernel(const __grid_constant__ CUtensorMap map_act, const __grid_constant_
     fence_proxy_async_smem();
     tma_prefetch_desc(&map_act);
     tma_prefetch_desc(&map_raw);
+    tma_prefetch_desc(&map_scale);
+    if (p.zp) tma_prefetch_desc(&map_zp);
   }
   if (warp == 1) {
     tmem_alloc(smem_u32(tmem_slot), C::kTmemCols);
@@ -180,9 +193,12 @@ w4a16_kernel(const __grid_constant__ CUtensorMap map_act, const __grid_constant_
           }
           const uint32_t full = bar_full + 8 * stage;
           const uint32_t sbase = smem_base + stage * C::kStageBytes;
-          mbar_arrive_expect_tx(full, C::kTxBytes);
+          mbar_arrive_expect_tx(full, C::kTxBytes + (p.zp ? C::kZpBytes : 0));
           tma_load_2d(sbase, &map_act, full, kb * kK, act_row0);
-          tma_load_3d(sbase + C::kActBytes, &map_raw, full, n0 / 8, kb * (kK / 8), 0);
+          tma_load_2d(sbase + C::kActBytes, &map_raw, full, n0 / 8, kb * kK);
+          const int grp = (kb * kK) / p.group;
+          tma_load_2d(sbase + C::kMetaOffset, &map_scale, full, n0, grp);
+          if (p.zp) tma_load_2d(sbase + C::kZpOffset, &map_zp, full, n0 / 8, grp);
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
       }
@@ -190,7 +206,8 @@ w4a16_kernel(const __grid_constant__ CUtensorMap map_act, const __grid_constant_
   } else if (warp == 1) {
     // ------------------------------------------------------------ MMA issuer
     if (lane == 0) {
-      const uint32_t idesc = umma_idesc(1u, 1u, 128, BN);  // bf16 x bf16
+      // bf16 x bf16; the expanded weights are the MN-major operand (A when swapped, else B)
+      const uint32_t idesc = umma_idesc_major(1u, 1u, 128, BN, SWAP ? 1u : 0u, SWAP ? 0u : 1u);
       uint32_t stage = 0, phase = 0, wb = 0, wphase = 0;
       int it = 0;
       bool ok = true;
@@ -209,11 +226,14 @@ w4a16_kernel(const __grid_constant__ CUtensorMap map_act, const __grid_constant_
           }
           tc_fence_after();
           const uint32_t act = smem_base + stage * C::kStageBytes, wt = wbuf_base + wb * C::kWBufBytes;
-          const uint32_t xs = SWAP ? wt : act, ys = SWAP ? act : wt;
 #pragma unroll
-          for (int k = 0; k < 128 / kUmmaKBytes; ++k)
-            umma_f16(d_tmem, smem_desc_k_sw128(xs + k * kUmmaKBytes), smem_desc_k_sw128(ys + k * kUmmaKBytes), idesc,
-                     (kb != kb0 || k != 0) ? 1u : 0u);
+          for (int k = 0; k < kK / 16; ++k) {
+            // activations: K-major, 32 bytes per k-step inside the 128-byte row; weights: MN-major,
+            // two 8-k atoms (2048 bytes) per k-step, column blocks 8 atoms apart
+            const uint64_t da = smem_desc_k_sw128(act + k * kUmmaKBytes);
+            const uint64_t dw = smem_desc_mn_sw128(wt + k * 2048, (kK / 8) * 1024, 1024);
+            umma_f16(d_tmem, SWAP ? dw : da, SWAP ? da : dw, idesc, (kb != kb0 || k != 0) ? 1u : 0u);
+          }
           umma_commit(bar_empty + 8 * stage);
           umma_commit(bar_wfree + 8 * wb);
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
@@ -238,7 +258,11 @@ w4a16_kernel(const __grid_constant__ CUtensorMap map_act, const __grid_constant_
       if (*epi_stop) break;
       tc_fence_after();
       const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16) + acc * BN;
-      const int64_t x = (int64_t)xt * 128 + q * 32 + lane;  // lane-side index: token (normal) or column n (swap)
+      // The weight columns inside every group of 8 sit at tile positions (0,4,1,5,2,6,3,7) (the
+      // order the nibble pairs were stored in): position p holds column (p >> 1) + 4 * (p & 1).
+      const int pos = q * 32 + lane;
+      const int64_t x = (int64_t)xt * 128 +
+                        (SWAP ? (pos & ~7) + ((pos & 7) >> 1) + 4 * (pos & 1) : pos);  // token, or weight column n
       const int64_t y0 = (int64_t)yt * BN;
       constexpr int CW = (BN % 32 == 0) ? 32 : 16;
 #pragma unroll 1
@@ -248,6 +272,14 @@ w4a16_kernel(const __grid_constant__ CUtensorMap map_act, const __grid_constant_
         else tmem_ld_32x16(t_row + c0, r);
         tmem_ld_wait();
         if (!SWAP) {
+          // registers are in tile-position order: rename them into column order (free: all static)
+          {
+            uint32_t t[32];
+#pragma unroll
+            for (int j = 0; j < CW; ++j) t[(j & ~7) + ((j & 7) >> 1) + 4 * (j & 1)] = r[j];
+#pragma unroll
+            for (int j = 0; j < CW; ++j) r[j] = t[j];
+          }
           const int64_t m = x, n0 = y0 + c0;
           if (m < p.M) {
             if (p.splits > 1) {
@@ -298,75 +330,55 @@ w4a16_kernel(const __grid_constant__ CUtensorMap map_act, const __grid_constant_
     }
   } else {
     // ------------------------------------------------------------ expanders (warps 6..)
-    const int et = threadIdx.x - 192;          // 0 .. 128*kUnits-1
-    const int u = et >> 7;                     // unit (128 weight columns)
-    const int d = et & 127;
-    const int kg = d & 7;                      // k-octet inside the stage
-    const int ng = d >> 3;                     // group of 8 weight columns inside the unit
+    const int et = threadIdx.x - 192;           // 0 .. kExpandWarps*32-1
+    constexpr int W = C::kRawRowWords;          // packed words per k-row (16 per 128 columns)
+    constexpr int kRowsPerPass = C::kExpandWarps * 32 / W;  // k-rows covered by all threads at once (8 * kSplit)
+    constexpr int kPasses = kK / kRowsPerPass;
+    const int ngl = et % W;                     // column group (8 columns) inside the stage's tile
+    const int kr = et / W;                      // first k-row of this thread; then every kRowsPerPass
     const bool has_zp = p.zp != nullptr;
     uint32_t stage = 0, phase = 0, wb = 0, wphase = 0;
     bool ok = true;
     for (int w = blockIdx.x; w < num_work && ok; w += gridDim.x) {
       int xt, yt, kb0, kb1, split;
       decode(w, xt, yt, kb0, kb1, split);
-      const int64_t n8 = (int64_t)(SWAP ? xt * 128 : yt * BN) + u * kUnit + 8 * ng;  // first of this thread's 8 columns
-      const bool n_in = n8 < p.N;  // N is a multiple of 8
       GroupRegs g;
       int g_cur = -1;
-      uint4 s_next = make_uint4(0, 0, 0, 0);
-      uint32_t z_next = 0;
-      int g_next = kb0 < kb1 ? (kb0 * kK) / p.group : -1;
-      if (n_in && g_next >= 0) {
-        s_next = __ldg(reinterpret_cast<const uint4*>(p.scale + (int64_t)g_next * p.N + n8));
-        if (has_zp) z_next = (uint32_t)__ldg(p.zp + (int64_t)g_next * (p.N / 8) + n8 / 8);
-      }
       for (int kb = kb0; kb < kb1; ++kb) {
-        if (g_next != g_cur) {
-          make_group(g, s_next, z_next, has_zp);
-          g_cur = g_next;
-        }
-        // prefetch the next stage's group parameters when the group changes
-        if (kb + 1 < kb1) {
-          const int gn = ((kb + 1) * kK) / p.group;
-          if (gn != g_cur) {
-            g_next = gn;
-            if (n_in) {
-              s_next = __ldg(reinterpret_cast<const uint4*>(p.scale + (int64_t)gn * p.N + n8));
-              if (has_zp) z_next = (uint32_t)__ldg(p.zp + (int64_t)gn * (p.N / 8) + n8 / 8);
-            }
-          }
-        }
         if (!mbar_wait(bar_full + 8 * stage, phase, abort_flag, p.status, kErrExpand) ||
             !mbar_wait(bar_wfree + 8 * wb, wphase ^ 1, abort_flag, p.status, kErrExpand)) {
           ok = false;
           break;
         }
-        // Packed word of k-row 8*kg + j and column group ng.  Shared-memory row = j * 8 + kg;
-        // inside a row the 16-byte chunks are XOR-swizzled by the hardware with the row's low
-        // bits, which here are kg: the 8 lanes that share ng but differ in kg hit 8 different
-        // chunks, and the 4 values of ng % 4 in a warp fill the banks inside a chunk.
-        const int ngl = u * 16 + ng;  // column group inside the stage's tile
-        const uint32_t chunk = (C::kRawRowBytes == 128) ? (uint32_t)((ngl >> 2) ^ kg)
-                                                        : (uint32_t)((ngl >> 2) ^ ((kg >> 1) & 3));
-        const uint32_t raw = smem_base + stage * C::kStageBytes + C::kActBytes + kg * C::kRawRowBytes + (chunk << 4) +
-                             (ngl & 3) * 4;
-        uint32_t t[8][4];  // t[j][i] = {W[k_j][n_i], W[k_j][n_{i+4}]}
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          const uint32_t wv = lds32(raw + j * 8 * C::kRawRowBytes);
-#pragma unroll
-          for (int i = 0; i < 4; ++i) t[j][i] = bf2_mul(bf2_sub(nib_pair(wv, i), g.zr[i]), g.sp[i]);
+        const uint32_t sbase = smem_base + stage * C::kStageBytes;
+        const int grp = (kb * kK) / p.group;
+        if (grp != g_cur) {  // this stage's ring slot holds the group's scales / zero points
+          uint4 sv;
+          asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
+                       : "=r"(sv.x), "=r"(sv.y), "=r"(sv.z), "=r"(sv.w)
+                       : "r"(sbase + C::kMetaOffset + ngl * 16));
+          const uint32_t zw = has_zp ? lds32(sbase + C::kZpOffset + ngl * 4) : 0u;
+          make_group(g, sv, zw, has_zp);
+          g_cur = grp;
         }
-        // 8x8 transpose in registers: row n_i gets its eight k values as four bf16x2
-        const uint32_t wt = wbuf_base + wb * C::kWBufBytes + (u * kUnit + 8 * ng) * 128;
+        // Raw tile: row k holds W consecutive words, so a warp reads 32 consecutive words.
+        // Expanded tile: column block b = ngl / 8 (64 columns), 16-byte chunk c = ngl % 8 of the
+        // 128-byte row k % 8 of atom (b, k / 8), chunk XOR-swizzled with the row: the 8 lanes of
+        // a quarter warp write the 8 chunks of one row.
+        const uint32_t raw = sbase + C::kActBytes + (kr * W + ngl) * 4;
+        const uint32_t krow = kr & 7;
+        const uint32_t wt = wbuf_base + wb * C::kWBufBytes + ((ngl >> 3) * (kK / 8) + (kr >> 3)) * 1024 + krow * 128 +
+                            (((ngl & 7) ^ krow) << 4);
+        uint32_t wv[kPasses];
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          sts128(wt + i * 128 + ((kg ^ i) << 4), __byte_perm(t[0][i], t[1][i], 0x5410),
-                 __byte_perm(t[2][i], t[3][i], 0x5410), __byte_perm(t[4][i], t[5][i], 0x5410),
-                 __byte_perm(t[6][i], t[7][i], 0x5410));
-          sts128(wt + (i + 4) * 128 + ((kg ^ (i + 4)) << 4), __byte_perm(t[0][i], t[1][i], 0x7632),
-                 __byte_perm(t[2][i], t[3][i], 0x7632), __byte_perm(t[4][i], t[5][i], 0x7632),
-                 __byte_perm(t[6][i], t[7][i], 0x7632));
+        for (int j = 0; j < kPasses; ++j) wv[j] = lds32(raw + j * kRowsPerPass * W * 4);
+#pragma unroll
+        for (int j = 0; j < kPasses; ++j) {
+          // pair i = columns (i, i+4): stored in that order, the epilogue restores the column order
+          sts128(wt + j * (kRowsPerPass / 8) * 1024, bf2_mul(bf2_sub(nib_pair(wv[j], 0), g.zr[0]), g.sp[0]),
+                 bf2_mul(bf2_sub(nib_pair(wv[j], 1), g.zr[1]), g.sp[1]),
+                 bf2_mul(bf2_sub(nib_pair(wv[j], 2), g.zr[2]), g.sp[2]),
+                 bf2_mul(bf2_sub(nib_pair(wv[j], 3), g.zr[3]), g.sp[3]));
         }
         fence_proxy_async_smem();  // generic-proxy writes -> visible to the tensor core's async proxy
         mbar_arrive(bar_wready + 8 * wb);
@@ -404,7 +416,8 @@ __global__ void __launch_bounds__(256) splitk_reduce_kernel(const float* __restr
 }
 
 template <int BN, bool SWAP, int STAGES, int NWBUF>
-static int launch(const CUtensorMap& ma, const CUtensorMap& mr, const Params& p, cudaStream_t st) {
+static int launch(const CUtensorMap& ma, const CUtensorMap& mr, const CUtensorMap& ms, const CUtensorMap& mz, const Params& p,
+                  cudaStream_t st) {
   using C = Cfg<BN, SWAP, STAGES, NWBUF>;
   constexpr int smem = C::kTotal + 1024;
   static_assert(smem <= 227 * 1024, "shared memory budget");
@@ -421,28 +434,12 @@ static int launch(const CUtensorMap& ma, const CUtensorMap& mr, const Params& p,
   int work = p.x_tiles * p.y_tiles * p.splits;
   int per_sm = 227 * 1024 / smem;
   int grid = work < kNumSMs * per_sm ? work : kNumSMs * per_sm;
-  kern<<<grid, C::kThreads, smem, st>>>(ma, mr, p);
+  kern<<<grid, C::kThreads, smem, st>>>(ma, mr, ms, mz, p);
   B200Q_LAUNCH_CHECK();
   return B200Q_OK;
 }
 
 }  // namespace w4
-
-// Packed weights [K][N/8] int32 seen as {words, k / 8, k % 8}; a box of {box_words, 8, 8} lands in
-// shared memory as rows (k % 8) * 8 + k / 8 of box_words words, swizzled over the row width.
-static int make_tma_map_raw_w4(CUtensorMap* map, const int32_t* qweight, int64_t N, int64_t K, int box_words) {
-  EncodeTiledFn enc = get_encode_fn();
-  if (!enc) return B200Q_ERR_CUDA;
-  const cuuint64_t row_bytes = (cuuint64_t)(N / 8) * 4;
-  cuuint64_t dims[3] = {(cuuint64_t)(N / 8), (cuuint64_t)(K / 8), 8};
-  cuuint64_t strides[2] = {8 * row_bytes, row_bytes};
-  cuuint32_t box[3] = {(cuuint32_t)box_words, 8, 8};
-  cuuint32_t estr[3] = {1, 1, 1};
-  CUresult r = enc(map, CU_TENSOR_MAP_DATA_TYPE_INT32, 3, const_cast<int32_t*>(qweight), dims, strides, box, estr,
-                   CU_TENSOR_MAP_INTERLEAVE_NONE, box_words == 32 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B,
-                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  return r == CUDA_SUCCESS ? B200Q_OK : B200Q_ERR_CUDA;
-}
 
 // Number of K splits the small-M path uses (every split gets at least one k-block), and the
 // fp32 workspace that goes with it.
@@ -487,16 +484,28 @@ int w4a16_gemm_impl(const void* x, int64_t ldx, const int32_t* qweight, const vo
   CUtensorMap ma, mr;
   int rc = 0;
   const int bn_w = (!swap && N > 128) ? 256 : 128;  // weight columns per stage tile
-  rc = make_tma_map_raw_w4(&mr, qweight, N, K, bn_w / 8);
+  rc = make_tma_map_2d(&mr, qweight, CU_TENSOR_MAP_DATA_TYPE_INT32, 4, N / 8, K, (N / 8) * 4, bn_w / 8, w4::kK,
+                       CU_TENSOR_MAP_SWIZZLE_NONE);
   if (rc) return rc;
+  CUtensorMap ms, mz;
+  rc = make_tma_map_2d(&ms, scale, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, N, K / group, N * 2, bn_w, 1, CU_TENSOR_MAP_SWIZZLE_NONE);
+  if (rc) return rc;
+  if (p.zp) {
+    if (reinterpret_cast<uintptr_t>(p.zp) & 15) return B200Q_ERR_UNSUPPORTED;
+    rc = make_tma_map_2d(&mz, p.zp, CU_TENSOR_MAP_DATA_TYPE_INT32, 4, N / 8, K / group, (N / 8) * 4, bn_w / 8, 1,
+                         CU_TENSOR_MAP_SWIZZLE_NONE);
+    if (rc) return rc;
+  } else {
+    mz = ms;  // never dereferenced
+  }
   if (!swap) {
     p.x_tiles = (int)((M + 127) / 128);
     const int bn = bn_w;
     p.y_tiles = (int)((N + bn - 1) / bn);
     rc = make_tma_map_2d(&ma, x, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, K, M, ldx * 2, w4::kK, 128, CU_TENSOR_MAP_SWIZZLE_128B);
     if (rc) return rc;
-    if (bn == 256) rc = w4::launch<256, false, 4, 3>(ma, mr, p, st);
-    else rc = w4::launch<128, false, 5, 4>(ma, mr, p, st);
+    if (bn == 256) rc = w4::launch<256, false, 4, 3>(ma, mr, ms, mz, p, st);
+    else rc = w4::launch<128, false, 5, 4>(ma, mr, ms, mz, p, st);
   } else {
     p.x_tiles = (int)((N + 127) / 128);
     const int bn = M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : 128;
@@ -504,10 +513,10 @@ int w4a16_gemm_impl(const void* x, int64_t ldx, const int32_t* qweight, const vo
     rc = make_tma_map_2d(&ma, x, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, K, M, ldx * 2, w4::kK, bn, CU_TENSOR_MAP_SWIZZLE_128B);
     if (rc) return rc;
     switch (bn) {
-      case 16: rc = w4::launch<16, true, 6, 3>(ma, mr, p, st); break;
-      case 32: rc = w4::launch<32, true, 6, 3>(ma, mr, p, st); break;
-      case 64: rc = w4::launch<64, true, 6, 3>(ma, mr, p, st); break;
-      default: rc = w4::launch<128, true, 5, 3>(ma, mr, p, st); break;
+      case 16: rc = w4::launch<16, true, 6, 3>(ma, mr, ms, mz, p, st); break;
+      case 32: rc = w4::launch<32, true, 6, 3>(ma, mr, ms, mz, p, st); break;
+      case 64: rc = w4::launch<64, true, 6, 3>(ma, mr, ms, mz, p, st); break;
+      default: rc = w4::launch<128, true, 5, 3>(ma, mr, ms, mz, p, st); break;
     }
   }
   if (rc) return rc;
