@@ -166,10 +166,13 @@ w4a16_kernel(const __grid_constant__ CUtensorMap map_act, const __grid_constant_
   const uint32_t tmem_base = *tmem_slot;
 
   const int num_work = p.x_tiles * p.y_tiles * p.splits;
-  // work item -> (lane-side tile, column-side tile, k range); consecutive items share a tile
+  // work item -> (lane-side tile, column-side tile, k range).  Consecutive items (CTAs that run
+  // at the same time) are neighbouring tiles of the same k range: together they read whole rows
+  // of the packed weight matrix, which keeps the DRAM pages they open fully used.
   auto decode = [&](int w, int& xt, int& yt, int& kb0, int& kb1, int& split) {
-    split = w % p.splits;
-    const int tile = w / p.splits;
+    const int tiles = p.x_tiles * p.y_tiles;
+    split = w / tiles;
+    const int tile = w % tiles;
     xt = tile % p.x_tiles;
     yt = tile / p.x_tiles;
     kb0 = split * p.kb_per_split;
