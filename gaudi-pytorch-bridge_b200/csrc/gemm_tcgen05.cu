@@ -41,6 +41,7 @@ struct TcGemmParams {
   int64_t x_rows, y_rows;  // extents of the lane-side / column-side operands
   int x_tiles, y_tiles, num_kb;
   int a_fmt_bits, b_fmt_bits;  // 0 = e4m3, 1 = e5m2 (lane-side, column-side)
+  int x_mn, y_mn;              // 1 = that operand is stored MN-major ([K][rows], rows contiguous)
   int* status;                 // device status word (bounded waits report here)
 };
 
@@ -242,8 +243,19 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
           }
           const uint32_t full = bar_full + 8 * stage;
           mbar_arrive_expect_tx(full, L::kStageBytes);
-          tma_load_2d(smem_base + stage * L::kStageBytes, &map_x, full, kb * kBlockK, xt * kBlockX);
-          tma_load_2d(smem_base + stage * L::kStageBytes + L::kXBytes, &map_y, full, kb * kBlockK, yt * BN);
+          // K-major operand: box = 128 bytes of k x rows.  MN-major operand (stored [K][rows]):
+          // box = 128 rows (bytes) x 128 k, one box per 128-row block; either way a 128-byte-
+          // swizzled tile of the same size lands in the stage.
+          const uint32_t xs = smem_base + stage * L::kStageBytes, ys = xs + L::kXBytes;
+          if (!p.x_mn) tma_load_2d(xs, &map_x, full, kb * kBlockK, xt * kBlockX);
+          else tma_load_2d(xs, &map_x, full, xt * kBlockX, kb * kBlockK);
+          if (!p.y_mn) {
+            tma_load_2d(ys, &map_y, full, kb * kBlockK, yt * BN);
+          } else {
+#pragma unroll
+            for (int b = 0; b < BN / 128; ++b)
+              tma_load_2d(ys + b * (kBlockK * 128), &map_y, full, yt * BN + b * 128, kb * kBlockK);
+          }
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
       }
@@ -251,7 +263,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
   } else if (warp == 1) {
     // ------------------------------------------------------------ MMA issuer
     if (lane == 0) {
-      const uint32_t idesc = umma_idesc(p.a_fmt_bits, p.b_fmt_bits, kBlockX, BN);
+      const uint32_t idesc = umma_idesc_major(p.a_fmt_bits, p.b_fmt_bits, kBlockX, BN, p.x_mn, p.y_mn);
       uint32_t stage = 0, phase = 0;
       int it = 0;
       bool ok = true;
@@ -269,8 +281,13 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
           const uint32_t xs = smem_base + stage * L::kStageBytes, ys = xs + L::kXBytes;
 #pragma unroll
           for (int k = 0; k < kBlockK / kUmmaK; ++k) {
-            umma_f8(d_tmem, smem_desc_k_sw128(xs + k * kUmmaK), smem_desc_k_sw128(ys + k * kUmmaK), idesc,
-                    (kb | k) != 0);
+            // K-major: 32 bytes per k-step inside the 128-byte row.  MN-major: a k-step is four
+            // 8-k atoms (4096 bytes); 128-row blocks are a whole k-block (16 KB) apart.
+            const uint64_t dx = p.x_mn ? smem_desc_mn_sw128(xs + k * 4096, kBlockK * 128, 1024)
+                                       : smem_desc_k_sw128(xs + k * kUmmaK);
+            const uint64_t dy = p.y_mn ? smem_desc_mn_sw128(ys + k * 4096, kBlockK * 128, 1024)
+                                       : smem_desc_k_sw128(ys + k * kUmmaK);
+            umma_f8(d_tmem, dx, dy, idesc, (kb | k) != 0);
           }
           umma_commit(bar_empty + 8 * stage);  // stage reusable once these MMAs have read it
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
@@ -555,10 +572,20 @@ static int launch_cfg(const CUtensorMap& mx, const CUtensorMap& my, const TcGemm
 
 static inline int fmt_bits(int dtype) { return dtype == B200Q_E5M2 ? 1 : 0; }
 
+// Operand map: K-major = row-major [rows][K] (box 128 k-bytes x box_rows); MN-major = row-major
+// [K][rows] (box 128 row-bytes x 128 k).
+static int make_map(CUtensorMap* map, const void* base, int64_t rows, int64_t K, int64_t ld, bool mn, int box_rows) {
+  if (!mn) return make_operand_map(map, base, rows, K, ld, box_rows);
+  return make_tma_map_2d(map, base, CU_TENSOR_MAP_DATA_TYPE_UINT8, 1, rows, K, ld, 128, kBlockK, CU_TENSOR_MAP_SWIZZLE_128B);
+}
+
 int gemm_tcgen05_launch(const GemmParams& g, cudaStream_t st) {
-  // eligibility: both operands K-major, TMA-compatible strides and bases, one problem per launch
-  if (g.trans_a || !g.trans_b) return B200Q_ERR_UNSUPPORTED;
-  if (g.batch != 1 || g.K < 16 || (g.K % 16) || (g.lda % 16) || (g.ldb % 16)) return B200Q_ERR_UNSUPPORTED;
+  // eligibility: TMA-compatible strides and bases, one problem per launch.  A is K-major when
+  // stored [M][K] (trans_a = 0), B when stored [N][K] (trans_b = 1); the other storage orders
+  // are MN-major operands, which the tensor core reads through MN-major descriptors.
+  const bool a_mn = g.trans_a != 0, b_mn = g.trans_b == 0;
+  if (g.batch != 1 || g.K < 1 || (g.lda % 16) || (g.ldb % 16)) return B200Q_ERR_UNSUPPORTED;
+  if ((!a_mn || !b_mn) && (g.K % 16)) return B200Q_ERR_UNSUPPORTED;  // a K-major row must be 16-byte granular
   if ((reinterpret_cast<uintptr_t>(g.A) | reinterpret_cast<uintptr_t>(g.B)) & 15) return B200Q_ERR_UNSUPPORTED;
   if (g.a_scale_mode == B200Q_BCAST_FULL || g.b_scale_mode == B200Q_BCAST_FULL) return B200Q_ERR_UNSUPPORTED;
   if (g.M <= 0 || g.N <= 0) return B200Q_ERR_UNSUPPORTED;
@@ -569,30 +596,35 @@ int gemm_tcgen05_launch(const GemmParams& g, cudaStream_t st) {
   tp.status = device_status_ptr();
   if (!tp.status) return B200Q_ERR_CUDA;
   tp.num_kb = (int)((g.K + kBlockK - 1) / kBlockK);
-  const bool swap = g.M <= 128 && g.N >= 128;
+  // small M: weights on the lanes, tokens on the columns -- unless the tokens are MN-major (their
+  // column tile would be narrower than the 128-byte MN-major row)
+  const bool swap = g.M <= 128 && g.N >= 128 && !a_mn;
   CUtensorMap mx, my;
   if (!swap) {
     tp.x_rows = g.M; tp.y_rows = g.N;
     tp.a_fmt_bits = fmt_bits(g.a_dtype); tp.b_fmt_bits = fmt_bits(g.b_dtype);
+    tp.x_mn = a_mn; tp.y_mn = b_mn;
     tp.x_tiles = (int)((g.M + kBlockX - 1) / kBlockX);
     // Column-tile width: the one that minimises (waves over the 148 SMs) x (tile cost).  A
     // narrower tile can remove a nearly empty last wave: 4096 x 14336 is 1792 tiles of 256
     // columns (12.1 waves -> 13) but 2048 tiles of 224 columns (13.8 waves -> 14 shorter ones).
+    // An MN-major B operand comes in 128-column blocks: 256 or 128 only.
     static const int kWidths[] = {256, 224, 192, 160, 128};
     int bn = 128;
     double best = 1e30;
     for (int w : kWidths) {
       if (w > 128 && g.N <= 128) continue;
+      if (b_mn && (w % 128)) continue;
       const int64_t tiles = (int64_t)tp.x_tiles * ((g.N + w - 1) / w);
       const double cost = (double)((tiles + kNumSMs - 1) / kNumSMs) * (w + 24);
       if (cost < best) { best = cost; bn = w; }
     }
     tp.y_tiles = (int)((g.N + bn - 1) / bn);
-    int rc = make_operand_map(&mx, g.A, g.M, g.K, g.lda, kBlockX);
+    int rc = make_map(&mx, g.A, g.M, g.K, g.lda, a_mn, kBlockX);
     if (rc) return rc;
-    // CTA pairs (256-row tiles) when there are enough rows to fill them
+    // CTA pairs (256-row tiles) when there are enough rows to fill them (K-major operands)
     static const bool no_pairs = std::getenv("B200Q_GEMM_NO_PAIRS") != nullptr;
-    if (g.M > 128 && g.N > 128 && !no_pairs) {
+    if (g.M > 128 && g.N > 128 && !no_pairs && !a_mn && !b_mn) {
       TcGemmParams pp = tp;
       pp.x_tiles = (int)((g.M + 2 * kBlockX - 1) / (2 * kBlockX));
       int bp = 256;
@@ -613,7 +645,7 @@ int gemm_tcgen05_launch(const GemmParams& g, cudaStream_t st) {
       }
       if (rc != B200Q_ERR_UNSUPPORTED) return rc;
     }
-    rc = make_operand_map(&my, g.B, g.N, g.K, g.ldb, bn);
+    rc = make_map(&my, g.B, g.N, g.K, g.ldb, b_mn, bn);
     if (rc) return rc;
     switch (bn) {
       case 256: return launch_cfg<256, 4, false>(mx, my, tp, st);
@@ -623,13 +655,13 @@ int gemm_tcgen05_launch(const GemmParams& g, cudaStream_t st) {
       default: return launch_cfg<128, 6, false>(mx, my, tp, st);
     }
   }
-  // small M: weights on the lanes, tokens on the columns
   tp.x_rows = g.N; tp.y_rows = g.M;
   tp.a_fmt_bits = fmt_bits(g.b_dtype); tp.b_fmt_bits = fmt_bits(g.a_dtype);
+  tp.x_mn = b_mn; tp.y_mn = 0;
   tp.x_tiles = (int)((g.N + kBlockX - 1) / kBlockX);
   const int bn = g.M <= 16 ? 16 : g.M <= 32 ? 32 : g.M <= 64 ? 64 : 128;
   tp.y_tiles = (int)((g.M + bn - 1) / bn);
-  int rc = make_operand_map(&mx, g.B, g.N, g.K, g.ldb, kBlockX);
+  int rc = make_map(&mx, g.B, g.N, g.K, g.ldb, b_mn, kBlockX);
   if (rc) return rc;
   rc = make_operand_map(&my, g.A, g.M, g.K, g.lda, bn);
   if (rc) return rc;

@@ -136,8 +136,10 @@ int b200q_dequant_int4(const int32_t* packed, const void* scale, const void* zp,
  * op(B) is K x N: B is stored [K][N] (trans_b = 0) or [N][K] (trans_b = 1), row stride ldb.
  * Scales and bias line up with the M x N output per b200q_bcast (rows = M, cols = N).
  * `batch` independent problems are `*_batch_stride` elements apart (0 = shared operand).
- * The tcgen05 path needs both operands K-major (trans_a = 0, trans_b = 1), K % 16 == 0
- * and 16-byte aligned bases and row strides; everything else runs a generic CUDA kernel.
+ * The tcgen05 path takes all four storage orders (a transposed operand is read through an
+ * MN-major shared-memory descriptor); it needs batch == 1, 16-byte aligned bases and row
+ * strides, and K % 16 == 0 unless both operands are stored [K][rows]; everything else runs a
+ * generic CUDA kernel.
  */
 typedef struct b200q_gemm_args {
   const void* A;

@@ -271,3 +271,32 @@ def test_tcgen05_full_size_properties(ops):
     r3 = torch.ops.hpu.fp8_gemm_v2(A8, False, B8, True, None, torch.float32, 2 * sa, sb, None, False, [1, N])
     r4 = torch.ops.hpu.fp8_gemm_v2(A8, False, B8, True, None, torch.float32, sa, sb, None, False, [1, N])
     assert torch.equal(r3, 2 * r4)
+
+
+@pytest.mark.parametrize("tA,tB", [(True, False), (True, True), (False, False)])
+@pytest.mark.parametrize("M,N,K", [(384, 512, 320), (208, 1008, 144), (4096, 256, 512), (48, 640, 1024)])
+def test_tcgen05_mn_major_operands(ops, tA, tB, M, N, K):
+    """Transposed storage orders go to the tensor cores through MN-major descriptors: compare with
+    the oracle, with the generic kernel, and exactly on small-integer operands."""
+    from b200_hpu_ops import abi
+    g = torch.Generator().manual_seed(M + 3 * N + K)
+    A = _rand_fp8((K, M) if tA else (M, K), torch.float8_e4m3fn, g)
+    B = _rand_fp8((N, K) if tB else (K, N), torch.float8_e5m2, g)
+    sB = torch.rand(N, generator=g) + 0.5
+    bias = torch.randn(N, generator=g).to(torch.bfloat16)
+    _check(A, tA, B, tB, None, torch.bfloat16, torch.tensor(0.5), sB, bias, False, [1, N])
+    # exact: small integers, fp32 output, no scales
+    Ai = torch.randint(-4, 5, A.shape, generator=g).float()
+    Bi = torch.randint(-4, 5, B.shape, generator=g).float()
+    r = torch.ops.hpu.fp8_gemm_v2(Ai.to(torch.float8_e4m3fn).cuda(), tA, Bi.to(torch.float8_e4m3fn).cuda(), tB, None,
+                                  torch.float32)
+    ref = (Ai.t() if tA else Ai) @ (Bi.t() if tB else Bi)
+    assert torch.equal(r.cpu(), ref)
+
+
+def test_tcgen05_mn_major_k_not_multiple_of_16(ops):
+    g = torch.Generator().manual_seed(77)
+    M, N, K = 256, 384, 200   # both operands MN-major: K needs no alignment
+    A = _rand_fp8((K, M), torch.float8_e4m3fn, g)
+    B = _rand_fp8((K, N), torch.float8_e4m3fn, g)
+    _check(A, True, B, False, None, torch.float32, None, None, None, False, None, tol=1e-5)
