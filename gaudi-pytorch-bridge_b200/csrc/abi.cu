@@ -159,8 +159,27 @@ int b200q_fp8_gemm(const b200q_gemm_args* a) {
   g.d_batch_stride = a->d_batch_stride;
   cudaStream_t st = static_cast<cudaStream_t>(a->stream);
   if (!a->force_generic) {
-    int rc = gemm_tcgen05_launch(g, st);
-    if (rc != B200Q_ERR_UNSUPPORTED) return rc;
+    if (g.batch == 1) {
+      int rc = gemm_tcgen05_launch(g, st);
+      if (rc != B200Q_ERR_UNSUPPORTED) return rc;
+    } else if (g.batch <= 1024) {
+      // batched problems: one tensor-core launch per batch item (same eligibility for all of them)
+      auto elem = [](int dtype) { return dtype == B200Q_BF16 ? 2 : 4; };
+      for (int64_t b = 0; b < g.batch; ++b) {
+        GemmParams gb = g;
+        gb.batch = 1;
+        gb.A = static_cast<const uint8_t*>(g.A) + b * g.a_batch_stride;
+        gb.B = static_cast<const uint8_t*>(g.B) + b * g.b_batch_stride;
+        gb.out = static_cast<uint8_t*>(g.out) + b * g.out_batch_stride * elem(g.out_dtype);
+        if (g.bias_mode == B200Q_BCAST_FULL)
+          gb.bias = static_cast<const uint8_t*>(g.bias) + b * g.bias_batch_stride * elem(g.bias_dtype);
+        if (g.D) gb.D = static_cast<const uint8_t*>(g.D) + b * g.d_batch_stride * elem(g.d_dtype);
+        int rc = gemm_tcgen05_launch(gb, st);
+        if (rc == B200Q_ERR_UNSUPPORTED && b == 0) break;  // not eligible: the generic kernel takes the whole batch
+        if (rc != B200Q_OK) return rc;
+        if (b == g.batch - 1) return B200Q_OK;
+      }
+    }
   }
   return gemm_generic_launch(g, st);
 }

@@ -33,6 +33,7 @@ constexpr int kBlockK = 128;  // bytes (= fp8 elements) of K per ring stage: one
 constexpr int kUmmaK = 32;
 constexpr int kThreads = 192;
 constexpr int kEpiThreads = 128;
+constexpr int kTileOverheadCols = 590;  // width-independent part of a tile's cost, in columns (see the width choice)
 
 enum { kErrProducer = 101, kErrMma = 102, kErrMmaTmem = 103, kErrEpilogue = 104 };
 
@@ -264,6 +265,16 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
     // ------------------------------------------------------------ MMA issuer
     if (lane == 0) {
       const uint32_t idesc = umma_idesc_major(p.a_fmt_bits, p.b_fmt_bits, kBlockX, BN, p.x_mn, p.y_mn);
+      // The issuing thread is a single dependent instruction stream: everything that does not
+      // change per MMA is hoisted.  Descriptors of stage 0 are built once; a stage adds
+      // kStageBytes >> 4 to the address field and a k-step adds 2 (K-major: 32 bytes inside the
+      // 128-byte row) or 256 (MN-major: four 8-k atoms of 1024 bytes; 128-row blocks are a whole
+      // k-block, 16 KB, apart).  The address field is 14 bits of (address >> 4), so the sums
+      // never carry out of it.
+      const uint64_t xd0 = p.x_mn ? smem_desc_mn_sw128(smem_base, kBlockK * 128, 1024) : smem_desc_k_sw128(smem_base);
+      const uint64_t yd0 = p.y_mn ? smem_desc_mn_sw128(smem_base + L::kXBytes, kBlockK * 128, 1024)
+                                  : smem_desc_k_sw128(smem_base + L::kXBytes);
+      const uint32_t xstep = p.x_mn ? (4096u >> 4) : (kUmmaK >> 4), ystep = p.y_mn ? (4096u >> 4) : (kUmmaK >> 4);
       uint32_t stage = 0, phase = 0;
       int it = 0;
       bool ok = true;
@@ -278,17 +289,11 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
             break;
           }
           tc_fence_after();
-          const uint32_t xs = smem_base + stage * L::kStageBytes, ys = xs + L::kXBytes;
+          const uint64_t xd = xd0 + (uint64_t)(stage * (uint32_t)(L::kStageBytes >> 4));
+          const uint64_t yd = yd0 + (uint64_t)(stage * (uint32_t)(L::kStageBytes >> 4));
+          umma_f8(d_tmem, xd, yd, idesc, kb != 0);
 #pragma unroll
-          for (int k = 0; k < kBlockK / kUmmaK; ++k) {
-            // K-major: 32 bytes per k-step inside the 128-byte row.  MN-major: a k-step is four
-            // 8-k atoms (4096 bytes); 128-row blocks are a whole k-block (16 KB) apart.
-            const uint64_t dx = p.x_mn ? smem_desc_mn_sw128(xs + k * 4096, kBlockK * 128, 1024)
-                                       : smem_desc_k_sw128(xs + k * kUmmaK);
-            const uint64_t dy = p.y_mn ? smem_desc_mn_sw128(ys + k * 4096, kBlockK * 128, 1024)
-                                       : smem_desc_k_sw128(ys + k * kUmmaK);
-            umma_f8(d_tmem, dx, dy, idesc, (kb | k) != 0);
-          }
+          for (int k = 1; k < kBlockK / kUmmaK; ++k) umma_f8(d_tmem, xd + k * xstep, yd + k * ystep, idesc, 1u);
           umma_commit(bar_empty + 8 * stage);  // stage reusable once these MMAs have read it
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
@@ -440,6 +445,8 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
     // ------------------------------------------------------------ MMA issuer (even CTA only)
     if (lane == 0 && rank == 0) {
       const uint32_t idesc = umma_idesc(p.a_fmt_bits, p.b_fmt_bits, 2 * kBlockX, BN);
+      // hoisted descriptors: see the single-CTA kernel
+      const uint64_t xd0 = smem_desc_k_sw128(smem_base), yd0 = smem_desc_k_sw128(smem_base + L::kXBytes);
       uint32_t stage = 0, phase = 0;
       int it = 0;
       bool ok = true;
@@ -454,12 +461,12 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
             break;
           }
           tc_fence_after();
-          const uint32_t xs = smem_base + stage * L::kStageBytes, ys = xs + L::kXBytes;
+          const uint64_t xd = xd0 + (uint64_t)(stage * (uint32_t)(L::kStageBytes >> 4));
+          const uint64_t yd = yd0 + (uint64_t)(stage * (uint32_t)(L::kStageBytes >> 4));
+          umma_f8_pair(d_tmem, xd, yd, idesc, kb != 0);
 #pragma unroll
-          for (int k = 0; k < kBlockK / kUmmaK; ++k) {
-            umma_f8_pair(d_tmem, smem_desc_k_sw128(xs + k * kUmmaK), smem_desc_k_sw128(ys + k * kUmmaK), idesc,
-                         (kb | k) != 0);
-          }
+          for (int k = 1; k < kBlockK / kUmmaK; ++k)
+            umma_f8_pair(d_tmem, xd + k * (kUmmaK >> 4), yd + k * (kUmmaK >> 4), idesc, 1u);
           umma_commit_pair_both(bar_empty + 8 * stage);
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
@@ -605,9 +612,11 @@ int gemm_tcgen05_launch(const GemmParams& g, cudaStream_t st) {
     tp.a_fmt_bits = fmt_bits(g.a_dtype); tp.b_fmt_bits = fmt_bits(g.b_dtype);
     tp.x_mn = a_mn; tp.y_mn = b_mn;
     tp.x_tiles = (int)((g.M + kBlockX - 1) / kBlockX);
-    // Column-tile width: the one that minimises (waves over the 148 SMs) x (tile cost).  A
-    // narrower tile can remove a nearly empty last wave: 4096 x 14336 is 1792 tiles of 256
-    // columns (12.1 waves -> 13) but 2048 tiles of 224 columns (13.8 waves -> 14 shorter ones).
+    // Column-tile width: the one that minimises (waves over the 148 SMs) x (tile cost).  Measured
+    // on 4096 x 14336 x 4096: a wave of 224-column tiles takes 96 % of the time of a wave of
+    // 256-column tiles (the k-block time is dominated by operand traffic that does not shrink with
+    // the width), i.e. a tile costs about (width + 590) units; narrower tiles only win when they
+    // remove a whole wave.
     // An MN-major B operand comes in 128-column blocks: 256 or 128 only.
     static const int kWidths[] = {256, 224, 192, 160, 128};
     int bn = 128;
@@ -616,7 +625,7 @@ int gemm_tcgen05_launch(const GemmParams& g, cudaStream_t st) {
       if (w > 128 && g.N <= 128) continue;
       if (b_mn && (w % 128)) continue;
       const int64_t tiles = (int64_t)tp.x_tiles * ((g.N + w - 1) / w);
-      const double cost = (double)((tiles + kNumSMs - 1) / kNumSMs) * (w + 24);
+      const double cost = (double)((tiles + kNumSMs - 1) / kNumSMs) * (w + kTileOverheadCols);
       if (cost < best) { best = cost; bn = w; }
     }
     tp.y_tiles = (int)((g.N + bn - 1) / bn);
@@ -632,9 +641,11 @@ int gemm_tcgen05_launch(const GemmParams& g, cudaStream_t st) {
       static const int kPairWidths[] = {256, 224, 192};
       for (int w : kPairWidths) {
         const int64_t tiles = (int64_t)pp.x_tiles * ((g.N + w - 1) / w);
-        const double cost = (double)((tiles + kNumSMs / 2 - 1) / (kNumSMs / 2)) * (w + 24);
+        const double cost = (double)((tiles + kNumSMs / 2 - 1) / (kNumSMs / 2)) * (w + kTileOverheadCols);
         if (cost < bestp) { bestp = cost; bp = w; }
       }
+      static const int forced = std::getenv("B200Q_GEMM_PAIR_BN") ? std::atoi(std::getenv("B200Q_GEMM_PAIR_BN")) : 0;
+      if (forced == 256 || forced == 224 || forced == 192) bp = forced;
       pp.y_tiles = (int)((g.N + bp - 1) / bp);
       rc = make_operand_map(&my, g.B, g.N, g.K, g.ldb, bp / 2);
       if (rc) return rc;

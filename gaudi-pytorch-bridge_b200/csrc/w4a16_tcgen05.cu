@@ -211,6 +211,8 @@ w4a16_kernel(const __grid_constant__ CUtensorMap map_act, const __grid_constant_
     if (lane == 0) {
       // bf16 x bf16; the expanded weights are the MN-major operand (A when swapped, else B)
       const uint32_t idesc = umma_idesc_major(1u, 1u, 128, BN, SWAP ? 1u : 0u, SWAP ? 0u : 1u);
+      const uint64_t da0 = smem_desc_k_sw128(smem_base);
+      const uint64_t dw0 = smem_desc_mn_sw128(wbuf_base, (kK / 8) * 1024, 1024);
       uint32_t stage = 0, phase = 0, wb = 0, wphase = 0;
       int it = 0;
       bool ok = true;
@@ -228,14 +230,16 @@ w4a16_kernel(const __grid_constant__ CUtensorMap map_act, const __grid_constant_
             break;
           }
           tc_fence_after();
-          const uint32_t act = smem_base + stage * C::kStageBytes, wt = wbuf_base + wb * C::kWBufBytes;
+          // activations: K-major, 32 bytes per k-step inside the 128-byte row; weights: MN-major,
+          // two 8-k atoms (2048 bytes) per k-step, column blocks 8 atoms apart (descriptors of
+          // stage 0 / buffer 0 are hoisted out of the loop)
+          const uint64_t da = da0 + (uint64_t)(stage * (uint32_t)(C::kStageBytes >> 4));
+          const uint64_t dw = dw0 + (uint64_t)(wb * (uint32_t)(C::kWBufBytes >> 4));
+          umma_f16(d_tmem, SWAP ? dw : da, SWAP ? da : dw, idesc, kb != kb0);
 #pragma unroll
-          for (int k = 0; k < kK / 16; ++k) {
-            // activations: K-major, 32 bytes per k-step inside the 128-byte row; weights: MN-major,
-            // two 8-k atoms (2048 bytes) per k-step, column blocks 8 atoms apart
-            const uint64_t da = smem_desc_k_sw128(act + k * kUmmaKBytes);
-            const uint64_t dw = smem_desc_mn_sw128(wt + k * 2048, (kK / 8) * 1024, 1024);
-            umma_f16(d_tmem, SWAP ? dw : da, SWAP ? da : dw, idesc, (kb != kb0 || k != 0) ? 1u : 0u);
+          for (int k = 1; k < kK / 16; ++k) {
+            const uint64_t a = da + k * (kUmmaKBytes >> 4), w2 = dw + k * (2048 >> 4);
+            umma_f16(d_tmem, SWAP ? w2 : a, SWAP ? a : w2, idesc, 1u);
           }
           umma_commit(bar_empty + 8 * stage);
           umma_commit(bar_wfree + 8 * wb);

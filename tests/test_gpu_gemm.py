@@ -300,3 +300,17 @@ def test_tcgen05_mn_major_k_not_multiple_of_16(ops):
     A = _rand_fp8((K, M), torch.float8_e4m3fn, g)
     B = _rand_fp8((K, N), torch.float8_e4m3fn, g)
     _check(A, True, B, False, None, torch.float32, None, None, None, False, None, tol=1e-5)
+
+
+def test_tcgen05_batched(ops):
+    """Batched operands (both with batch dimensions, or a broadcast one) run one tensor-core launch
+    per batch item."""
+    g = torch.Generator().manual_seed(91)
+    A = _rand_fp8((3, 2, 144, 256), torch.float8_e4m3fn, g)
+    B = _rand_fp8((3, 1, 320, 256), torch.float8_e4m3fn, g)
+    bias = torch.randn(3, 2, 144, 320, generator=g)
+    D = torch.randn(3, 2, 144, 320, generator=g)
+    _check(A, False, B, True, D, torch.float32, torch.tensor(0.5), torch.rand(320, generator=g) + 0.5, bias, True,
+           [1, 320], tol=1e-5)
+    Bt = _rand_fp8((2, 256, 320), torch.float8_e5m2, g)   # [K][N] storage, batch broadcast against A's
+    _check(A, False, Bt, False, None, torch.bfloat16)
