@@ -206,6 +206,28 @@ def run_ours(args):
 
             return e2e_step, host_a.numel(), host_out.numel() * 2
 
+    elif wl == "cast_hybrid":
+        n = args.elems
+        g = torch.Generator(device=dev).manual_seed(7 + rank)
+        xs = [torch.randn(n, device=dev, generator=g, dtype=torch.float32).to(torch.bfloat16) for _ in range(3)]
+        o5 = [torch.empty(n, device=dev, dtype=torch.float8_e5m2) for _ in range(3)]
+        o4 = [torch.empty(n, device=dev, dtype=torch.float8_e4m3fn) for _ in range(3)]
+        amax = torch.zeros((), device=dev, dtype=torch.float32)
+
+        def step(i):
+            j = i % 3
+            abi.check(abi.lib.b200q_cast_to_fp8_hybrid(abi.ptr(xs[j]), abi.BF16, abi.ptr(o5[j]), abi.ptr(o4[j]), None, 1000.0,
+                                                       abi.BCAST_SCALAR_HOST, None, 8.0, abi.BCAST_SCALAR_HOST, n, abi.ptr(amax),
+                                                       abi.ROUND_RNE, 1234, 0, 0, 0, abi.stream_ptr()))
+        launches_per_step = 1
+        algo_bytes = 4 * n
+        bound, unit_per_step, unit = "hbm", algo_bytes / 1e9, "GB/s"
+        peak, peak_note = peaks["hbm_gbs"], "measured copy bandwidth"
+        metric = "cast_to_fp8_hybrid (e5m2 + e4m3, RNE, amax) GB/s"
+        workload = f"cast_to_fp8_hybrid on {n} bf16 elements ~N(0,1)"
+        dtype = "bf16->e5m2+e4m3"
+        l2 = "3 rotating tensors"
+        e2e_setup = None
     elif wl in ("cast_rne", "cast_sr", "uncast"):
         n = args.elems
         g = torch.Generator(device=dev).manual_seed(7 + rank)

@@ -38,6 +38,8 @@ int* device_status_ptr() {
 
 int cast_to_fp8_impl(const void*, int, void*, int, const float*, float, int, int64_t, int64_t, float*, int, uint64_t,
                      uint64_t, uint64_t, int, cudaStream_t);
+int cast_hybrid_impl(const void*, int, void*, void*, const float*, float, int, const float*, float, int, int64_t, float*, int,
+                     uint64_t, uint64_t, uint64_t, int, cudaStream_t);
 int cast_from_fp8_impl(const void*, int, void*, int, const float*, float, int, int64_t, int64_t, cudaStream_t);
 int swiglu_cast_impl(const void*, int64_t, const void*, int64_t, void*, float, int64_t, int64_t, float*, cudaStream_t);
 int dequant_int4_impl(const int32_t*, const void*, const void*, int, int, int, void*, int64_t, int64_t, int64_t, int,
@@ -102,6 +104,22 @@ int b200q_cast_to_fp8(const void* in, int in_dtype, void* out, int out_dtype, co
   if (rounding != B200Q_ROUND_RNE && rounding != B200Q_ROUND_STOCHASTIC) return B200Q_ERR_BAD_ARGUMENT;
   return cast_to_fp8_impl(in, in_dtype, out, out_dtype, scale, scale_host, scale_mode, rows, cols, amax, rounding,
                           seed, offset, first_index, flags, static_cast<cudaStream_t>(stream));
+}
+
+int b200q_cast_to_fp8_hybrid(const void* in, int in_dtype, void* out_e5m2, void* out_e4m3, const float* scale_e5m2,
+                             float scale_e5m2_host, int scale_e5m2_mode, const float* scale_e4m3, float scale_e4m3_host,
+                             int scale_e4m3_mode, int64_t n, float* amax, int rounding_e5m2, uint64_t seed,
+                             uint64_t offset, uint64_t first_index, int flags, void* stream) {
+  if (n < 0 || (n > 0 && (!in || !out_e5m2 || !out_e4m3))) return B200Q_ERR_BAD_ARGUMENT;
+  if (!is_wide(in_dtype)) return B200Q_ERR_BAD_ARGUMENT;
+  for (int m : {scale_e5m2_mode, scale_e4m3_mode})
+    if (m != B200Q_BCAST_NONE && m != B200Q_BCAST_SCALAR_HOST && m != B200Q_BCAST_SCALAR_DEV) return B200Q_ERR_UNSUPPORTED;
+  if ((scale_e5m2_mode == B200Q_BCAST_SCALAR_DEV && !scale_e5m2) || (scale_e4m3_mode == B200Q_BCAST_SCALAR_DEV && !scale_e4m3))
+    return B200Q_ERR_BAD_ARGUMENT;
+  if (rounding_e5m2 != B200Q_ROUND_RNE && rounding_e5m2 != B200Q_ROUND_STOCHASTIC) return B200Q_ERR_BAD_ARGUMENT;
+  return cast_hybrid_impl(in, in_dtype, out_e5m2, out_e4m3, scale_e5m2, scale_e5m2_host, scale_e5m2_mode, scale_e4m3,
+                          scale_e4m3_host, scale_e4m3_mode, n, amax, rounding_e5m2, seed, offset, first_index, flags,
+                          static_cast<cudaStream_t>(stream));
 }
 
 int b200q_cast_from_fp8(const void* in, int in_dtype, void* out, int out_dtype, const float* scale, float scale_host,

@@ -412,6 +412,117 @@ __global__ void __launch_bounds__(256) cast_bf16_sr_fast_kernel(CastParams p) {
   if (p.amax) block_amax_to_global(amax_bits, p.amax);
 }
 
+// ------------------------------------------------------------------ hybrid cast (e5m2 + e4m3 in one pass)
+struct HybridParams {
+  const void* in;
+  uint8_t* out152;
+  uint8_t* out143;
+  const float* s152;
+  const float* s143;
+  float s152_host, s143_host;
+  int has152, has143, dev152, dev143;
+  int64_t n;
+  float* amax;
+  uint64_t seed, offset, first_index;
+  int mul_fp32;
+};
+
+// One read of the input, two fp8 outputs: e5m2 (RNE or stochastic) with its own per-tensor scale
+// and e4m3 (always RNE) with its own.  4 bytes per bf16 element instead of 6 for two casts.
+template <typename InT, bool SR>
+__global__ void __launch_bounds__(256) cast_hybrid_kernel(HybridParams p) {
+  constexpr bool BF16 = InTraits<InT>::kIsBf16;
+  const InT* __restrict__ in = static_cast<const InT*>(p.in);
+  const int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const int64_t nthreads = (int64_t)gridDim.x * blockDim.x;
+  float s5 = 1.f, s4 = 1.f;
+  if (p.has152) s5 = p.dev152 ? __ldg(p.s152) : p.s152_host;
+  if (p.has143) s4 = p.dev143 ? __ldg(p.s143) : p.s143_host;
+  const float s5i = BF16 ? round_to_bf16(s5) : s5, s4i = BF16 ? round_to_bf16(s4) : s4;
+  const bool aligned = ((reinterpret_cast<uintptr_t>(in) | reinterpret_cast<uintptr_t>(p.out152) |
+                         reinterpret_cast<uintptr_t>(p.out143)) & 15) == 0 && (p.first_index & 15) == 0;
+  const int64_t nvec = aligned ? p.n / 16 : 0;
+  const bool rb8 = BF16 && !p.mul_fp32;
+  uint32_t amax_bits = 0;
+  for (int64_t v = tid; v < nvec; v += nthreads) {
+    const int64_t base = v * 16;
+    float x[16];
+    if (BF16) {
+      const uint4* src = reinterpret_cast<const uint4*>(in + base);
+      uint4 a = __ldcs(src), b = __ldcs(src + 1);
+      uint32_t w[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        x[2 * i] = __uint_as_float(w[i] << 16);
+        x[2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u);
+      }
+    } else {
+      const float4* src = reinterpret_cast<const float4*>(in + base);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        float4 f = __ldcs(src + i);
+        x[4 * i] = f.x; x[4 * i + 1] = f.y; x[4 * i + 2] = f.z; x[4 * i + 3] = f.w;
+      }
+    }
+    float y5[16], y4[16];
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      amax_bits = max(amax_bits, __float_as_uint(x[i]) & 0x7FFFFFFFu);
+      y5[i] = p.has152 ? scaled<BF16>(x[i], s5, s5i, p.mul_fp32) : x[i];
+      y4[i] = p.has143 ? scaled<BF16>(x[i], s4, s4i, p.mul_fp32) : x[i];
+    }
+    if (SR) {
+      const uint64_t g = p.first_index + (uint64_t)base;
+      if (rb8) {
+        const uint4 r = philox4x32_10(g >> 4, p.seed, p.offset);
+        const uint32_t rw[4] = {r.x, r.y, r.z, r.w};
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          const float z = sr_round<B200Q_E5M2, 8>(y5[i], (rw[i >> 2] >> ((i & 3) * 8)) & 0xFFu);
+          y5[i] = z;
+        }
+      } else {
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+          const uint4 r = philox4x32_10((g >> 3) + h, p.seed, p.offset);
+          const uint32_t rw[4] = {r.x, r.y, r.z, r.w};
+#pragma unroll
+          for (int i = 0; i < 8; ++i)
+            y5[8 * h + i] = sr_round<B200Q_E5M2, 16>(y5[8 * h + i], (rw[i >> 1] >> ((i & 1) * 16)) & 0xFFFFu);
+        }
+      }
+    }
+    uint32_t o5[4], o4[4];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      o5[i] = canonical_nan_bytes<B200Q_E5M2>(cvt_fp8x2<B200Q_E5M2>(y5[4 * i], y5[4 * i + 1]) |
+                                              (cvt_fp8x2<B200Q_E5M2>(y5[4 * i + 2], y5[4 * i + 3]) << 16));
+      o4[i] = canonical_nan_bytes<B200Q_E4M3>(cvt_fp8x2<B200Q_E4M3>(y4[4 * i], y4[4 * i + 1]) |
+                                              (cvt_fp8x2<B200Q_E4M3>(y4[4 * i + 2], y4[4 * i + 3]) << 16));
+    }
+    __stcs(reinterpret_cast<uint4*>(p.out152 + base), make_uint4(o5[0], o5[1], o5[2], o5[3]));
+    __stcs(reinterpret_cast<uint4*>(p.out143 + base), make_uint4(o4[0], o4[1], o4[2], o4[3]));
+  }
+  for (int64_t i = nvec * 16 + tid; i < p.n; i += nthreads) {
+    float x = BF16 ? __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(in)[i]) : reinterpret_cast<const float*>(in)[i];
+    amax_bits = max(amax_bits, __float_as_uint(x) & 0x7FFFFFFFu);
+    float y5 = p.has152 ? scaled<BF16>(x, s5, s5i, p.mul_fp32) : x;
+    float y4 = p.has143 ? scaled<BF16>(x, s4, s4i, p.mul_fp32) : x;
+    float z5 = y5;
+    if (SR) {
+      const uint64_t gi = p.first_index + (uint64_t)i;
+      z5 = rb8 ? sr_round<B200Q_E5M2, 8>(y5, sr_random_bits<8>(gi, p.seed, p.offset))
+               : sr_round<B200Q_E5M2, 16>(y5, sr_random_bits<16>(gi, p.seed, p.offset));
+    }
+    uint32_t b5 = cvt_fp8x2<B200Q_E5M2>(z5, 0.f) & 0xFFu, b4 = cvt_fp8x2<B200Q_E4M3>(y4, 0.f) & 0xFFu;
+    if (y5 != y5) b5 = 0x7Fu;
+    if (y4 != y4) b4 = 0x7Fu;
+    p.out152[i] = (uint8_t)b5;
+    p.out143[i] = (uint8_t)b4;
+  }
+  if (p.amax) block_amax_to_global(amax_bits, p.amax);
+}
+
 // ------------------------------------------------------------------ cast_from_fp8
 struct UncastParams {
   const uint8_t* in;
@@ -708,6 +819,31 @@ int swiglu_cast_impl(const void* gate, int64_t ld_gate, const void* up, int64_t 
   p.out = static_cast<uint8_t*>(out); p.ld_gate = ld_gate; p.ld_up = ld_up; p.rows = rows; p.cols = cols;
   p.scale = scale; p.amax = amax;
   swiglu_cast_kernel<<<grid_for(swiglu_cast_kernel, rows * cols / 16), 256, 0, st>>>(p);
+  B200Q_LAUNCH_CHECK();
+  return B200Q_OK;
+}
+
+int cast_hybrid_impl(const void* in, int in_dtype, void* out152, void* out143, const float* s152, float s152_host,
+                     int mode152, const float* s143, float s143_host, int mode143, int64_t n, float* amax, int rounding,
+                     uint64_t seed, uint64_t offset, uint64_t first_index, int flags, cudaStream_t st) {
+  if (amax) B200Q_CUDA_OK(cudaMemsetAsync(amax, 0, sizeof(float), st));
+  if (n == 0) return B200Q_OK;
+  HybridParams p;
+  p.in = in; p.out152 = static_cast<uint8_t*>(out152); p.out143 = static_cast<uint8_t*>(out143);
+  p.s152 = s152; p.s143 = s143; p.s152_host = s152_host; p.s143_host = s143_host;
+  p.has152 = mode152 != B200Q_BCAST_NONE; p.has143 = mode143 != B200Q_BCAST_NONE;
+  p.dev152 = mode152 == B200Q_BCAST_SCALAR_DEV; p.dev143 = mode143 == B200Q_BCAST_SCALAR_DEV;
+  p.n = n; p.amax = amax; p.seed = seed; p.offset = offset; p.first_index = first_index;
+  p.mul_fp32 = (flags & B200Q_CAST_MUL_IN_FP32) ? 1 : 0;
+  const int64_t items = (n + 15) / 16;
+  const bool sr = rounding == B200Q_ROUND_STOCHASTIC;
+  if (in_dtype == B200Q_BF16) {
+    if (sr) launch_persistent(cast_hybrid_kernel<__nv_bfloat16, true>, items, st, p);
+    else launch_persistent(cast_hybrid_kernel<__nv_bfloat16, false>, items, st, p);
+  } else {
+    if (sr) launch_persistent(cast_hybrid_kernel<float, true>, items, st, p);
+    else launch_persistent(cast_hybrid_kernel<float, false>, items, st, p);
+  }
   B200Q_LAUNCH_CHECK();
   return B200Q_OK;
 }

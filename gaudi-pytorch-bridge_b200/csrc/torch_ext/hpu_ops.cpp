@@ -233,6 +233,40 @@ std::tuple<at::Tensor&, at::Tensor&> cast_to_fp8(const at::Tensor& input, const 
   return {out, amax};
 }
 
+// ------------------------------------------------------------------ cast_to_fp8_hybrid
+// scripts/hpu_op.yaml:7365-7366, hpu_ops/backend/cast_to_fp8_hybrid_gen.cpp:39-100
+std::tuple<at::Tensor, at::Tensor, at::Tensor> cast_to_fp8_hybrid(const at::Tensor& input, const OptTensor& scale_152,
+                                                                  const OptTensor& scale_143, bool stochastic_rounding,
+                                                                  bool is_amax) {
+  const auto src = input.scalar_type();
+  TORCH_CHECK(src == at::kFloat || src == at::kBFloat16, "CastToFp8Hybrid input must be of float or bfloat16 dtype.");
+  c10::cuda::CUDAGuard guard(input.device());
+  at::Tensor in = input.contiguous();
+  auto one_scale = [&](const OptTensor& s, at::Tensor& keep, int* mode) -> const float* {
+    *mode = B200Q_BCAST_NONE;
+    if (!s.has_value() || !s->defined()) return nullptr;
+    TORCH_CHECK(s->numel() == 1, "CastToFp8Hybrid scales must have one element, got ", s->sizes());
+    keep = s->to(in.device(), at::kFloat).reshape({1}).contiguous();
+    *mode = B200Q_BCAST_SCALAR_DEV;
+    return keep.data_ptr<float>();
+  };
+  at::Tensor k152, k143;
+  int m152, m143;
+  const float* p152 = one_scale(scale_152, k152, &m152);
+  const float* p143 = one_scale(scale_143, k143, &m143);
+  at::Tensor o152 = at::empty(in.sizes(), in.options().dtype(at::kFloat8_e5m2));
+  at::Tensor o143 = at::empty(in.sizes(), in.options().dtype(at::kFloat8_e4m3fn));
+  at::Tensor amax = is_amax ? at::empty({}, in.options().dtype(at::kFloat)) : at::empty({0}, in.options().dtype(at::kFloat));
+  uint64_t seed = (uint64_t)g_sr_seed.load(), offset = 0;
+  if (stochastic_rounding) offset = (uint64_t)g_sr_offset.fetch_add(1);
+  check_status(b200q_cast_to_fp8_hybrid(in.data_ptr(), to_b200q_dtype(src), o152.data_ptr(), o143.data_ptr(), p152, 1.f, m152,
+                                        p143, 1.f, m143, in.numel(), is_amax ? amax.data_ptr<float>() : nullptr,
+                                        stochastic_rounding ? B200Q_ROUND_STOCHASTIC : B200Q_ROUND_RNE, seed, offset, 0,
+                                        g_mul_in_fp32.load() ? B200Q_CAST_MUL_IN_FP32 : 0, current_stream()),
+               "cast_to_fp8_hybrid");
+  return {o152, o143, amax};
+}
+
 // ------------------------------------------------------------------ cast_from_fp8
 at::Tensor cast_from_fp8_common(const at::Tensor& input, const ScaleArg& scale, at::ScalarType out_dtype,
                                 OptShape scale_shape) {
@@ -641,6 +675,11 @@ std::tuple<at::Tensor, at::Tensor> meta_cast_to_fp8_v2_scalar(const at::Tensor& 
                                                               at::ScalarType d, OptShape) { return meta_cast_to(i, a, d); }
 std::tuple<at::Tensor, at::Tensor> meta_cast_to_fp8_v2_list(const at::Tensor& i, c10::ArrayRef<double>, bool, bool a,
                                                             at::ScalarType d, OptShape) { return meta_cast_to(i, a, d); }
+std::tuple<at::Tensor, at::Tensor, at::Tensor> meta_cast_to_fp8_hybrid(const at::Tensor& i, const OptTensor&, const OptTensor&,
+                                                                       bool, bool is_amax) {
+  return {at::empty(i.sizes(), i.options().dtype(at::kFloat8_e5m2)), at::empty(i.sizes(), i.options().dtype(at::kFloat8_e4m3fn)),
+          is_amax ? at::empty({}, i.options().dtype(at::kFloat)) : at::empty({0}, i.options().dtype(at::kFloat))};
+}
 at::Tensor meta_cast_from(const at::Tensor& i, at::ScalarType d) { return at::empty(i.sizes(), i.options().dtype(d)); }
 at::Tensor meta_cast_from_fp8(const at::Tensor& i, const OptTensor&, at::ScalarType d, OptShape) { return meta_cast_from(i, d); }
 at::Tensor meta_cast_from_fp8_scalar(const at::Tensor& i, double, at::ScalarType d, OptShape) { return meta_cast_from(i, d); }
@@ -674,6 +713,7 @@ TORCH_LIBRARY(hpu, m) {
   m.def("cast_to_fp8_v2(Tensor input, Tensor? scale=None, bool stochastic_rounding=False, bool is_amax=False, ScalarType dtype=None, int[]? scale_shape=None) -> (Tensor, Tensor)");
   m.def("cast_to_fp8_v2.scalar(Tensor input, float scale, bool stochastic_rounding=False, bool is_amax=False, ScalarType dtype=None, int[]? scale_shape=None) -> (Tensor, Tensor)");
   m.def("cast_to_fp8_v2.scalar_list(Tensor input, float[] scale, bool stochastic_rounding=False, bool is_amax=False, ScalarType dtype=None, int[]? scale_shape=None) -> (Tensor, Tensor)");
+  m.def("cast_to_fp8_hybrid(Tensor input, Tensor? scale_152=None, Tensor? scale_143=None, bool stochastic_rounding=False, bool is_amax=False) -> (Tensor, Tensor, Tensor)");
   m.def("convert_from_int4(Tensor input, Tensor scale, Tensor? zero_point, ScalarType out_dtype) -> Tensor");
   m.def("convert_from_uint4(Tensor input, Tensor scale, Tensor? zero_point, ScalarType out_dtype) -> Tensor");
   m.def("cast_from_fp8(Tensor input, Tensor? scale, ScalarType out_dtype, int[]? scale_shape=None) -> Tensor");
@@ -687,6 +727,7 @@ TORCH_LIBRARY(hpu, m) {
 
 TORCH_LIBRARY_IMPL(hpu, CUDA, m) {
   m.impl("cast_to_fp8", cast_to_fp8);
+  m.impl("cast_to_fp8_hybrid", cast_to_fp8_hybrid);
   m.impl("cast_to_fp8_v2", cast_to_fp8_v2);
   m.impl("cast_to_fp8_v2.scalar", cast_to_fp8_v2_scalar);
   m.impl("cast_to_fp8_v2.scalar_list", cast_to_fp8_v2_scalar_list);
@@ -702,6 +743,7 @@ TORCH_LIBRARY_IMPL(hpu, CUDA, m) {
 }
 
 TORCH_LIBRARY_IMPL(hpu, Meta, m) {
+  m.impl("cast_to_fp8_hybrid", meta_cast_to_fp8_hybrid);
   m.impl("cast_to_fp8_v2", meta_cast_to_fp8_v2);
   m.impl("cast_to_fp8_v2.scalar", meta_cast_to_fp8_v2_scalar);
   m.impl("cast_to_fp8_v2.scalar_list", meta_cast_to_fp8_v2_list);

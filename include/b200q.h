@@ -92,6 +92,20 @@ int b200q_cast_to_fp8(const void* in, int in_dtype, void* out, int out_dtype,
                       void* stream);
 
 /*
+ * cast_to_fp8_hybrid: one pass over the input, two outputs: e5m2 = fp8(in * scale_e5m2) (RNE or
+ * stochastic) and e4m3 = fp8(in * scale_e4m3) (always RNE), plus the optional amax.
+ * Replaces the node emitted by CastToFp8Hybrid::AddNode,
+ * hpu_ops/backend/cast_to_fp8_hybrid_gen.cpp:39-100 (schema scripts/hpu_op.yaml:7365-7366).
+ * Scales are per tensor: B200Q_BCAST_NONE, _SCALAR_HOST or _SCALAR_DEV.  Other arguments as
+ * b200q_cast_to_fp8.
+ */
+int b200q_cast_to_fp8_hybrid(const void* in, int in_dtype, void* out_e5m2, void* out_e4m3,
+                             const float* scale_e5m2, float scale_e5m2_host, int scale_e5m2_mode,
+                             const float* scale_e4m3, float scale_e4m3_host, int scale_e4m3_mode,
+                             int64_t n, float* amax, int rounding_e5m2, uint64_t seed,
+                             uint64_t offset, uint64_t first_index, int flags, void* stream);
+
+/*
  * cast_from_fp8: out = T(in) * T(scale), rounded once in T = out_dtype (F32 or BF16).
  * Replaces `convert_from_fp8_{f32,bf16}`, CastFromFp8::AddNode,
  * hpu_ops/backend/fp8_ops.cpp:265-308.

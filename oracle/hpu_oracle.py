@@ -252,6 +252,19 @@ def cast_to_fp8_v2(input: torch.Tensor, scale: ScaleArg = None, stochastic_round
     return out, amax
 
 
+def cast_to_fp8_hybrid(input, scale_152=None, scale_143=None, stochastic_rounding: bool = False, is_amax: bool = False, *,
+                       mul_in_fp32: bool = False, seed: int = 1234, offset: int = 0):
+    """(e5m2, e4m3, amax) -- hpu_ops/backend/cast_to_fp8_hybrid_gen.cpp:39-100.  Stochastic rounding
+    applies to the e5m2 output only: the reference test compares the e4m3 output with the RNE
+    emulation even when stochastic rounding is on (test_hpu_fp8_ops_any_mode.py:331-338)."""
+    if input.dtype not in (torch.float32, torch.bfloat16):
+        raise RuntimeError("CastToFp8Hybrid input must be of float or bfloat16 dtype.")
+    o152, amax = cast_to_fp8_v2(input, scale_152, stochastic_rounding, is_amax, torch.float8_e5m2,
+                                mul_in_fp32=mul_in_fp32, seed=seed, offset=offset)
+    o143, _ = cast_to_fp8_v2(input, scale_143, False, False, torch.float8_e4m3fn, mul_in_fp32=mul_in_fp32)
+    return o152, o143, amax
+
+
 def cast_from_fp8(input: torch.Tensor, scale: ScaleArg, out_dtype: torch.dtype, scale_shape=None):
     """out = T(input) * scale.to(T), rounded once in T  -- fp8_ops.cpp:265-308 and
     test_hpu_fp8_ops_any_mode.py:85-87."""

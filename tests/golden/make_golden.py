@@ -76,6 +76,31 @@ def golden_cast():
     print("cast_rne.npz:", idx, "cases")
 
 
+def golden_hybrid():
+    """Inputs and expected values of test_cast_to_fp8_hybrid (test_hpu_fp8_ops_any_mode.py:266-346):
+    scales 1.3 (e5m2) and 0.7 (e4m3), expected = simulateFp8Precision(input * scale.to(dtype))."""
+    out = {}
+    g = torch.Generator().manual_seed(0xC001A1 + 1)
+    idx = 0
+    for shape, dtype in (((64, 48), torch.float32), ((64, 48), torch.bfloat16), ((16, 24, 8), torch.bfloat16)):
+        pos = torch.rand(shape, dtype=dtype, generator=g) * 30 + 10
+        x = torch.cat((pos, -pos))
+        s152, s143 = torch.tensor(1.3), torch.tensor(0.7)
+        low152 = fp8_utils.simulateFp8Precision(x * s152.to(dtype), torch.float8_e5m2)
+        low143 = fp8_utils.simulateFp8Precision(x * s143.to(dtype), torch.float8_e4m3fn)
+        k = f"h{idx}"
+        out[k + "_x"] = _bits(x)
+        out[k + "_low152"] = _bits(low152)
+        out[k + "_low143"] = _bits(low143)
+        out[k + "_back152"] = _bits(low152 * s152.reciprocal().to(dtype))
+        out[k + "_back143"] = _bits(low143 * s143.reciprocal().to(dtype))
+        out[k + "_meta"] = np.array([str(dtype)])
+        idx += 1
+    out["n"] = np.array(idx)
+    np.savez_compressed(os.path.join(HERE, "hybrid.npz"), **out)
+    print("hybrid.npz:", idx, "cases")
+
+
 def golden_gemm():
     """Operands of test_fp8_gemm_v2 (test_hpu_fp8_ops_any_mode.py:352-484): A [24,12] and
     B [24,36] = rand*10+30, per-tensor scales 0.9*max/amax, trans_A=True; expected =
@@ -206,5 +231,6 @@ def golden_int4():
 
 if __name__ == "__main__":
     golden_cast()
+    golden_hybrid()
     golden_gemm()
     golden_int4()

@@ -304,3 +304,39 @@ def test_swiglu_cast(ops):
     a, b = _bytes(out).int(), _bytes(ref).int()
     assert (a - b).abs().max() <= 1 and (a != b).float().mean() < 2e-3
     assert abs(amax.item() - ramax.item()) <= 2 ** -7 * ramax.item()
+
+
+def test_hybrid_cast_matches_reference_emulation_and_oracle(ops):
+    """cast_to_fp8_hybrid (test_hpu_fp8_ops_any_mode.py:266-352): golden vectors from the reference's
+    emulation, then scale / stochastic / amax variants against the oracle."""
+    z = np.load(os.path.join(GOLDEN, "hybrid.npz"))
+    for i in range(int(z["n"])):
+        k = f"h{i}"
+        dtype = _DT[z[k + "_meta"][0]]
+        x = _from_bits(z[k + "_x"], dtype)
+        s152, s143 = torch.tensor(1.3), torch.tensor(0.7)
+        o152, o143, amax = torch.ops.hpu.cast_to_fp8_hybrid(x.cuda(), s152.cuda(), s143.cuda(), False, True)
+        assert o152.dtype == torch.float8_e5m2 and o143.dtype == torch.float8_e4m3fn
+        assert torch.equal(o152.cpu().to(dtype), _from_bits(z[k + "_low152"], dtype))
+        assert torch.equal(o143.cpu().to(dtype), _from_bits(z[k + "_low143"], dtype))
+        assert amax.dim() == 0 and amax.cpu() == x.abs().max().float()
+        b152 = torch.ops.hpu.cast_from_fp8(o152, s152.reciprocal().cuda(), dtype)
+        b143 = torch.ops.hpu.cast_from_fp8(o143, s143.reciprocal().cuda(), dtype)
+        assert torch.equal(b152.cpu(), _from_bits(z[k + "_back152"], dtype))
+        assert torch.equal(b143.cpu(), _from_bits(z[k + "_back143"], dtype))
+    g = torch.Generator().manual_seed(3)
+    for dtype in (torch.float32, torch.bfloat16):
+        x = (torch.randn((1 << 18) + 7, generator=g) * 20).to(dtype)
+        for s5, s4 in ((None, None), (torch.tensor(2.5), None), (torch.tensor(0.3), torch.tensor(4.0))):
+            for sr in (False, True):
+                ops.set_sr_seed(1234)
+                o152, o143, amax = torch.ops.hpu.cast_to_fp8_hybrid(x.cuda(), _c(s5), _c(s4), sr, False)
+                r152, r143, _ = O.cast_to_fp8_hybrid(x, s5, s4, sr, False, seed=1234, offset=0)
+                assert torch.equal(_bytes(o152), _bytes(r152)) and torch.equal(_bytes(o143), _bytes(r143))
+                assert amax.numel() == 0
+    with pytest.raises(RuntimeError, match="CastToFp8Hybrid input must be of float or bfloat16 dtype."):
+        torch.ops.hpu.cast_to_fp8_hybrid(torch.zeros(4, dtype=torch.float16).cuda(), None, None, False, False)
+
+
+def _c(t):
+    return None if t is None else t.cuda()

@@ -191,3 +191,18 @@ def test_sftz_below_min_subnormal():
     r, _ = O.cast_to_fp8_v2(x, None, True, False, torch.float8_e5m2)
     assert r.float().unique().tolist() == [0.0, 2.0 ** -16]
     assert abs(r.float().mean().item() - float(x[0, 0])) < 0.1 * v
+
+
+def test_hybrid_golden():
+    z = np.load(os.path.join(GOLDEN, "hybrid.npz"))
+    for i in range(int(z["n"])):
+        k = f"h{i}"
+        dtype = _DT[z[k + "_meta"][0]]
+        x = _from_bits(z[k + "_x"], dtype)
+        o152, o143, amax = O.cast_to_fp8_hybrid(x, torch.tensor(1.3), torch.tensor(0.7), False, True)
+        assert torch.equal(o152.to(dtype), _from_bits(z[k + "_low152"], dtype))
+        assert torch.equal(o143.to(dtype), _from_bits(z[k + "_low143"], dtype))
+        assert amax == x.abs().max().float()
+        s152, s143, a0 = O.cast_to_fp8_hybrid(x, torch.tensor(1.3), torch.tensor(0.7), True, False)
+        assert torch.equal(s143.view(torch.uint8), o143.view(torch.uint8))      # e4m3 stays RNE
+        assert not torch.equal(s152.view(torch.uint8), o152.view(torch.uint8)) and a0.numel() == 0
