@@ -16,7 +16,7 @@ CAST_MUL_IN_FP32 = 1
 
 EXPORTS = [
     "b200q_strerror", "b200q_last_cuda_error", "b200q_device_status", "b200q_launch_count",
-    "b200q_cast_to_fp8", "b200q_cast_to_fp8_hybrid", "b200q_cast_from_fp8", "b200q_dequant_int4", "b200q_fp8_gemm",
+    "b200q_cast_to_fp8", "b200q_cast_to_fp8_hybrid", "b200q_cast_from_fp8", "b200q_dequant_int4", "b200q_gptq_repack", "b200q_fp8_gemm",
     "b200q_w4a16_gemm", "b200q_w4a16_workspace_bytes", "b200q_w4a16_gemm_noalloc", "b200q_swiglu_cast_fp8",
 ]
 
@@ -58,6 +58,8 @@ def _bind():
     lib.b200q_dequant_int4.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p,
                                        C.c_int64, C.c_int64, C.c_int64, C.c_int, C.c_void_p]
     lib.b200q_fp8_gemm.argtypes = [C.POINTER(GemmArgs)]
+    lib.b200q_gptq_repack.argtypes = [C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_void_p, C.c_void_p, C.c_int64,
+                                      C.c_void_p]
     lib.b200q_w4a16_gemm.argtypes = [C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int,
                                      C.c_int64, C.c_int64, C.c_int64, C.c_int64, C.c_void_p, C.c_int, C.c_int64,
                                      C.c_void_p, C.c_size_t, C.c_void_p]

@@ -47,6 +47,7 @@ int dequant_int4_impl(const int32_t*, const void*, const void*, int, int, int, v
 int w4a16_gemm_impl(const void*, int64_t, const int32_t*, const void*, const int32_t*, int, int, int64_t, int64_t,
                     int64_t, int64_t, void*, int, int64_t, void*, size_t, cudaStream_t);
 size_t w4a16_workspace_bytes_impl(int64_t, int64_t, int64_t);
+int gptq_repack_impl(const int32_t*, int32_t*, int64_t, int64_t, const int32_t*, int32_t*, int64_t, cudaStream_t);
 int w4a16_gemm_noalloc_impl(const void*, int64_t, const int32_t*, const void*, const int32_t*, int, int, int64_t, int64_t,
                             int64_t, int64_t, void*, int, int64_t, cudaStream_t);
 
@@ -200,6 +201,14 @@ int b200q_fp8_gemm(const b200q_gemm_args* a) {
     }
   }
   return gemm_generic_launch(g, st);
+}
+
+int b200q_gptq_repack(const int32_t* qweight, int32_t* qweight_out, int64_t K, int64_t N, const int32_t* qzeros,
+                      int32_t* qzeros_out, int64_t zeros_words, void* stream) {
+  if (K < 0 || N < 0 || zeros_words < 0) return B200Q_ERR_BAD_ARGUMENT;
+  if (K * N > 0 && (!qweight || !qweight_out)) return B200Q_ERR_BAD_ARGUMENT;
+  if (qzeros && zeros_words > 0 && !qzeros_out) return B200Q_ERR_BAD_ARGUMENT;
+  return gptq_repack_impl(qweight, qweight_out, K, N, qzeros, qzeros_out, zeros_words, static_cast<cudaStream_t>(stream));
 }
 
 size_t b200q_w4a16_workspace_bytes(int64_t M, int64_t N, int64_t K) {

@@ -326,4 +326,56 @@ int dequant_int4_impl(const int32_t* packed, const void* scale, const void* zp, 
   return B200Q_OK;
 }
 
+// ------------------------------------------------------------------ AutoGPTQ -> operator layout
+// AutoGPTQ checkpoints pack the weight nibbles along K (qweight [K/8][N], nibble i of word (p, n)
+// is W[8p+i][n]) and store zero points minus one (qzeros [K/g][N/8], packed along N).  The
+// operator wants nibbles packed along N ([K][N/8]) and the true zero points.  One thread
+// transposes an 8x8 nibble block: 8 consecutive words of a packed row in, one word for each
+// of 8 consecutive rows out.
+__global__ void __launch_bounds__(256) gptq_repack_weight_kernel(const int32_t* __restrict__ in, int32_t* __restrict__ out,
+                                                                 int64_t K8, int64_t N8) {
+  const int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (t >= K8 * N8) return;
+  const int64_t p = t / N8, m = t % N8;
+  const int64_t N = N8 * 8;
+  uint32_t w[8];
+  const uint4* src = reinterpret_cast<const uint4*>(in + p * N + m * 8);
+  uint4 a = __ldcs(src), b = __ldcs(src + 1);
+  w[0] = a.x; w[1] = a.y; w[2] = a.z; w[3] = a.w; w[4] = b.x; w[5] = b.y; w[6] = b.z; w[7] = b.w;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    uint32_t o = 0;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) o |= ((w[j] >> (4 * i)) & 0xFu) << (4 * j);
+    out[(p * 8 + i) * N8 + m] = (int32_t)o;
+  }
+}
+
+// every nibble + 1 (mod 16)
+__global__ void __launch_bounds__(256) gptq_zeros_plus_one_kernel(const int32_t* __restrict__ in, int32_t* __restrict__ out,
+                                                                  int64_t n) {
+  const int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (t >= n) return;
+  const uint32_t z = (uint32_t)in[t];
+  const uint32_t lo = ((z & 0x0F0F0F0Fu) + 0x01010101u) & 0x0F0F0F0Fu;
+  const uint32_t hi = (((z >> 4) & 0x0F0F0F0Fu) + 0x01010101u) & 0x0F0F0F0Fu;
+  out[t] = (int32_t)(lo | (hi << 4));
+}
+
+int gptq_repack_impl(const int32_t* qweight, int32_t* qweight_out, int64_t K, int64_t N, const int32_t* qzeros,
+                     int32_t* qzeros_out, int64_t zeros_words, cudaStream_t st) {
+  if (K % 8 || N % 8) return B200Q_ERR_UNSUPPORTED;
+  if ((reinterpret_cast<uintptr_t>(qweight) & 15) || (N % 4)) return B200Q_ERR_UNSUPPORTED;
+  const int64_t items = (K / 8) * (N / 8);
+  if (items > 0) {
+    gptq_repack_weight_kernel<<<(unsigned)((items + 255) / 256), 256, 0, st>>>(qweight, qweight_out, K / 8, N / 8);
+    B200Q_LAUNCH_CHECK();
+  }
+  if (qzeros && zeros_words > 0) {
+    gptq_zeros_plus_one_kernel<<<(unsigned)((zeros_words + 255) / 256), 256, 0, st>>>(qzeros, qzeros_out, zeros_words);
+    B200Q_LAUNCH_CHECK();
+  }
+  return B200Q_OK;
+}
+
 }  // namespace b200q

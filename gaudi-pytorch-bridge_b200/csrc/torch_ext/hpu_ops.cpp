@@ -377,6 +377,31 @@ at::Tensor dequant_kpacked(const at::Tensor& qweight, const at::Tensor& scales, 
   return out;
 }
 
+// AutoGPTQ checkpoint tensors -> operator layout (the reference's test repacks on the host,
+// tests/pytest_working/any_mode/test_hpu_convert_from_int4.py:380-395).
+std::tuple<at::Tensor, at::Tensor> gptq_repack(const at::Tensor& qweight, const OptTensor& qzeros) {
+  TORCH_CHECK(qweight.dim() == 2 && qweight.scalar_type() == at::kInt, "gptq_repack: qweight must be int32 [K/8, N]");
+  c10::cuda::CUDAGuard guard(qweight.device());
+  at::Tensor q = qweight.contiguous();
+  const int64_t K = q.size(0) * 8, N = q.size(1);
+  TORCH_CHECK(N % 8 == 0, "gptq_repack: N must be a multiple of 8");
+  at::Tensor out = at::empty({K, N / 8}, q.options());
+  at::Tensor z, zout;
+  if (qzeros.has_value() && qzeros->defined()) {
+    TORCH_CHECK(qzeros->scalar_type() == at::kInt, "gptq_repack: qzeros must be int32");
+    z = qzeros->contiguous();
+    zout = at::empty_like(z);
+  } else {
+    zout = at::empty({0}, q.options());
+  }
+  check_status(b200q_gptq_repack(q.data_ptr<int32_t>(), out.data_ptr<int32_t>(), K, N,
+                                 z.defined() ? z.data_ptr<int32_t>() : nullptr,
+                                 z.defined() ? zout.data_ptr<int32_t>() : nullptr, z.defined() ? z.numel() : 0,
+                                 current_stream()),
+               "gptq_repack");
+  return {out, zout};
+}
+
 // ------------------------------------------------------------------ fp8_gemm_v2
 // hpu_ops/common/batched_matmul_output_shape.cpp:34-88
 std::vector<int64_t> matmul_out_shape(c10::IntArrayRef a, c10::IntArrayRef b, bool ta, bool tb) {
@@ -760,6 +785,7 @@ TORCH_LIBRARY_IMPL(hpu, Meta, m) {
 TORCH_LIBRARY(b200q, m) {
   m.def("w4a16_gemm(Tensor x, Tensor qweight, Tensor scales, Tensor? qzeros, int group_size, bool k_packed, ScalarType out_dtype) -> Tensor");
   m.def("dequant_kpacked(Tensor qweight, Tensor scales, Tensor? qzeros, ScalarType out_dtype) -> Tensor");
+  m.def("gptq_repack(Tensor qweight, Tensor? qzeros) -> (Tensor, Tensor)");
   m.def("swiglu_cast_fp8(Tensor gate, Tensor up, float scale, bool is_amax) -> (Tensor, Tensor)");
   m.def("set_sr_seed(int seed) -> ()", set_sr_seed);
   m.def("set_cast_mul_in_fp32(bool on) -> ()", set_cast_mul_in_fp32);
@@ -770,5 +796,6 @@ TORCH_LIBRARY(b200q, m) {
 TORCH_LIBRARY_IMPL(b200q, CUDA, m) {
   m.impl("w4a16_gemm", w4a16_gemm);
   m.impl("dequant_kpacked", dequant_kpacked);
+  m.impl("gptq_repack", gptq_repack);
   m.impl("swiglu_cast_fp8", swiglu_cast_fp8);
 }

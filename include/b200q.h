@@ -142,6 +142,17 @@ int b200q_dequant_int4(const int32_t* packed, const void* scale, const void* zp,
                        int64_t scale_rows, int k_packed, void* stream);
 
 /*
+ * gptq_repack: AutoGPTQ checkpoint tensors -> the operator's layout, on the device.
+ * qweight int32 [K/8][N] (nibbles packed along K) -> qweight_out int32 [K][N/8] (packed along N);
+ * qzeros (stored minus one, any shape, `zeros_words` int32 words) -> qzeros_out = every nibble + 1.
+ * Replaces the host-side repack the reference's test does before calling convert_from_uint4
+ * (tests/pytest_working/any_mode/test_hpu_convert_from_int4.py:380-395, hpu_preprocessing).
+ * qzeros may be NULL.  Needs K % 8 == 0, N % 8 == 0 and a 16-byte aligned qweight.
+ */
+int b200q_gptq_repack(const int32_t* qweight, int32_t* qweight_out, int64_t K, int64_t N,
+                      const int32_t* qzeros, int32_t* qzeros_out, int64_t zeros_words, void* stream);
+
+/*
  * fp8_gemm: out = (op(A) @ op(B)) * a_scale * b_scale [+ bias] [+ D], fp32 accumulation.
  * Replaces `fp8_gemm_{f32,bf16}`, Fp8GemmV2::AddNode, hpu_ops/backend/fp8_ops.cpp:403-496
  * (node inputs [A, B, A_scale_inv, B_scale_inv, bias, D]).
