@@ -140,7 +140,7 @@ w4a16_kernel(const __grid_constant__ CUtensorMap map_act, const __grid_constant_
       mbar_init(bar_empty + 8 * s, 1);
     }
     for (int b = 0; b < NWBUF; ++b) {
-      mbar_init(bar_wready + 8 * b, C::kExpandWarps * 32);
+      mbar_init(bar_wready + 8 * b, C::kExpandWarps);  // one arrival per expander warp
       mbar_init(bar_wfree + 8 * b, 1);
     }
     for (int a = 0; a < 2; ++a) {
@@ -196,12 +196,18 @@ w4a16_kernel(const __grid_constant__ CUtensorMap map_act, const __grid_constant_
           }
           const uint32_t full = bar_full + 8 * stage;
           const uint32_t sbase = smem_base + stage * C::kStageBytes;
-          mbar_arrive_expect_tx(full, C::kTxBytes + (p.zp ? C::kZpBytes : 0));
+          // scales / zero points travel only with the first stage of a k-group (the expanders
+          // keep them in registers until the group changes)
+          const int grp = (kb * kK) / p.group;
+          const bool new_group = kb == kb0 || grp != ((kb - 1) * kK) / p.group;
+          mbar_arrive_expect_tx(full, C::kActBytes + C::kRawBytes +
+                                          (new_group ? C::kScaleBytes + (p.zp ? C::kZpBytes : 0) : 0));
           tma_load_2d(sbase, &map_act, full, kb * kK, act_row0);
           tma_load_2d(sbase + C::kActBytes, &map_raw, full, n0 / 8, kb * kK);
-          const int grp = (kb * kK) / p.group;
-          tma_load_2d(sbase + C::kMetaOffset, &map_scale, full, n0, grp);
-          if (p.zp) tma_load_2d(sbase + C::kZpOffset, &map_zp, full, n0 / 8, grp);
+          if (new_group) {
+            tma_load_2d(sbase + C::kMetaOffset, &map_scale, full, n0, grp);
+            if (p.zp) tma_load_2d(sbase + C::kZpOffset, &map_zp, full, n0 / 8, grp);
+          }
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
       }
@@ -387,8 +393,12 @@ w4a16_kernel(const __grid_constant__ CUtensorMap map_act, const __grid_constant_
                  bf2_mul(bf2_sub(nib_pair(wv[j], 2), g.zr[2]), g.sp[2]),
                  bf2_mul(bf2_sub(nib_pair(wv[j], 3), g.zr[3]), g.sp[3]));
         }
-        fence_proxy_async_smem();  // generic-proxy writes -> visible to the tensor core's async proxy
-        mbar_arrive(bar_wready + 8 * wb);
+        // every thread publishes its own writes to the async proxy (the tensor core's view of
+        // shared memory); the warp then arrives once -- an arrival per thread would put hundreds
+        // of serialised shared-memory atomics on the barrier every stage
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar_wready + 8 * wb);
         if (++stage == STAGES) { stage = 0; phase ^= 1; }
         if (++wb == NWBUF) { wb = 0; wphase ^= 1; }
       }
