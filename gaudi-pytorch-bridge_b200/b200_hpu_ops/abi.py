@@ -15,7 +15,7 @@ ZP_NONE, ZP_PACKED, ZP_FLOAT = 0, 1, 2
 CAST_MUL_IN_FP32 = 1
 
 EXPORTS = [
-    "b200q_strerror", "b200q_last_cuda_error", "b200q_device_status", "b200q_launch_count",
+    "b200q_strerror", "b200q_last_cuda_error", "b200q_device_status", "b200q_selftest_wait_timeout", "b200q_launch_count",
     "b200q_cast_to_fp8", "b200q_cast_to_fp8_hybrid", "b200q_cast_from_fp8", "b200q_dequant_int4", "b200q_gptq_repack", "b200q_fp8_gemm",
     "b200q_w4a16_gemm", "b200q_w4a16_workspace_bytes", "b200q_w4a16_gemm_noalloc", "b200q_swiglu_cast_fp8",
 ]
@@ -37,6 +37,7 @@ class GemmArgs(C.Structure):
         ("bias_ld", C.c_int64), ("bias_batch_stride", C.c_int64),
         ("D", C.c_void_p), ("d_dtype", C.c_int), ("ldd", C.c_int64), ("d_batch_stride", C.c_int64),
         ("force_generic", C.c_int), ("stream", C.c_void_p),
+        ("out8_dtype", C.c_int), ("out8_scale", C.c_void_p), ("out8_scale_host", C.c_float),
     ]
 
 
@@ -47,6 +48,7 @@ def _bind():
     lib.b200q_last_cuda_error.restype = C.c_char_p
     lib.b200q_device_status.argtypes = [C.POINTER(C.c_int)]
     lib.b200q_launch_count.restype = C.c_uint64
+    lib.b200q_selftest_wait_timeout.argtypes = [C.c_int, C.c_void_p]
     lib.b200q_cast_to_fp8.argtypes = [C.c_void_p, C.c_int, C.c_void_p, C.c_int, C.c_void_p, C.c_float, C.c_int,
                                       C.c_int64, C.c_int64, C.c_void_p, C.c_int, C.c_uint64, C.c_uint64, C.c_uint64,
                                       C.c_int, C.c_void_p]

@@ -4,6 +4,7 @@
 
 #include "common.cuh"
 #include "gemm_common.cuh"
+#include "tcgen05_ptx.cuh"
 
 namespace b200q {
 
@@ -34,6 +35,24 @@ int* device_status_ptr() {
   }
   cache[dev].store(static_cast<int*>(addr), std::memory_order_release);
   return static_cast<int*>(addr);
+}
+
+// Self-test of the bounded-wait mechanism: one warp waits on an mbarrier that nothing ever
+// arrives at, with a short poll limit.  The wait must give up, record `code` in the status
+// word and let the kernel finish normally -- the same path a production kernel takes when a
+// producer or a peer never shows up.
+__global__ void wait_timeout_selftest_kernel(int* status, int code, uint32_t limit) {
+  __shared__ uint64_t bar;
+  __shared__ int abort_flag;
+  const uint32_t b = ptx::smem_u32(&bar);
+  if (threadIdx.x == 0) {
+    ptx::mbar_init(b, 1);
+    abort_flag = 0;
+    ptx::fence_barrier_init();
+  }
+  __syncthreads();
+  ptx::mbar_wait(b, 0, &abort_flag, status, code, 0, limit);  // phase 0 never completes
+  __syncthreads();
 }
 
 int cast_to_fp8_impl(const void*, int, void*, int, const float*, float, int, int64_t, int64_t, float*, int, uint64_t,
@@ -93,6 +112,15 @@ int b200q_device_status(int* code_out) {
   }
   if (code_out) *code_out = code;
   return code == 0 ? B200Q_OK : B200Q_ERR_DEVICE_TIMEOUT;
+}
+
+int b200q_selftest_wait_timeout(int code, void* stream) {
+  int* status = device_status_ptr();
+  if (!status) return B200Q_ERR_CUDA;
+  if (code == 0) return B200Q_ERR_BAD_ARGUMENT;
+  wait_timeout_selftest_kernel<<<1, 32, 0, static_cast<cudaStream_t>(stream)>>>(status, code, 1u << 12);
+  B200Q_LAUNCH_CHECK();
+  return B200Q_OK;
 }
 
 int b200q_cast_to_fp8(const void* in, int in_dtype, void* out, int out_dtype, const float* scale, float scale_host,
@@ -176,6 +204,8 @@ int b200q_fp8_gemm(const b200q_gemm_args* a) {
   g.bias = a->bias; g.bias_dtype = a->bias_dtype; g.bias_mode = a->bias_mode; g.bias_ld = a->bias_ld;
   g.bias_batch_stride = a->bias_batch_stride; g.D = a->D; g.d_dtype = a->d_dtype; g.ldd = a->ldd;
   g.d_batch_stride = a->d_batch_stride;
+  g.out8_dtype = a->out8_dtype; g.out8_scale = a->out8_scale; g.out8_scale_host = a->out8_scale_host;
+  if (g.out8_dtype != 0 && !is_fp8(g.out8_dtype)) return B200Q_ERR_BAD_ARGUMENT;
   cudaStream_t st = static_cast<cudaStream_t>(a->stream);
   if (!a->force_generic) {
     if (g.batch == 1) {
@@ -189,7 +219,7 @@ int b200q_fp8_gemm(const b200q_gemm_args* a) {
         gb.batch = 1;
         gb.A = static_cast<const uint8_t*>(g.A) + b * g.a_batch_stride;
         gb.B = static_cast<const uint8_t*>(g.B) + b * g.b_batch_stride;
-        gb.out = static_cast<uint8_t*>(g.out) + b * g.out_batch_stride * elem(g.out_dtype);
+        gb.out = static_cast<uint8_t*>(g.out) + b * g.out_batch_stride * (g.out8_dtype ? 1 : elem(g.out_dtype));
         if (g.bias_mode == B200Q_BCAST_FULL)
           gb.bias = static_cast<const uint8_t*>(g.bias) + b * g.bias_batch_stride * elem(g.bias_dtype);
         if (g.D) gb.D = static_cast<const uint8_t*>(g.D) + b * g.d_batch_stride * elem(g.d_dtype);

@@ -26,7 +26,31 @@ struct GemmParams {
   const void* D;
   int d_dtype;
   int64_t ldd, d_batch_stride;
+  // fused output cast: 0 = none, else B200Q_E4M3 / B200Q_E5M2: the result is rounded to out_dtype
+  // (as the unfused GEMM would store it), multiplied by the output scale in out_dtype and
+  // rounded to fp8 -- the composition cast_to_fp8_v2(fp8_gemm_v2(...), scale) bit for bit
+  int out8_dtype;
+  const float* out8_scale;  // device scalar, or null: out8_scale_host
+  float out8_scale_host;
 };
+
+// value in out_dtype -> fp8 byte of the fused output cast
+__device__ __forceinline__ uint32_t out8_byte(const GemmParams& p, float v, float s) {
+  float t, y;
+  if (p.out_dtype == B200Q_BF16) {
+    t = round_to_bf16(v);
+    y = round_to_bf16(t * round_to_bf16(s));
+  } else {
+    t = v;
+    y = t * s;
+  }
+  uint32_t b = p.out8_dtype == B200Q_E4M3 ? (cvt_fp8x2<B200Q_E4M3>(y, 0.f) & 0xFFu) : (cvt_fp8x2<B200Q_E5M2>(y, 0.f) & 0xFFu);
+  if (y != y) b = 0x7Fu;
+  return b;
+}
+__device__ __forceinline__ float out8_scale_value(const GemmParams& p) {
+  return p.out8_scale ? __ldg(p.out8_scale) : p.out8_scale_host;
+}
 
 __device__ __forceinline__ float bcast_scale(const float* dev, float host, int mode, int64_t m, int64_t n, int64_t N) {
   switch (mode) {
@@ -63,6 +87,10 @@ __device__ __forceinline__ float epilogue_value(const GemmParams& p, int64_t b, 
 __device__ __forceinline__ void epilogue_store_one(const GemmParams& p, int64_t b, int64_t m, int64_t n, float acc) {
   float v = epilogue_value(p, b, m, n, acc);
   int64_t idx = b * p.out_batch_stride + m * p.ldo + n;
+  if (p.out8_dtype) {
+    static_cast<uint8_t*>(p.out)[idx] = (uint8_t)out8_byte(p, v, out8_scale_value(p));
+    return;
+  }
   if (p.out_dtype == B200Q_BF16) static_cast<__nv_bfloat16*>(p.out)[idx] = __float2bfloat16_rn(v);
   else static_cast<float*>(p.out)[idx] = v;
 }

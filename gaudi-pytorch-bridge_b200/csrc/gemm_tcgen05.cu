@@ -103,6 +103,7 @@ __device__ __forceinline__ void epi_drain(const GemmParams& g, uint32_t t_row, c
   const int64_t x = e.x;
   const bool x_in = e.x_in;
   const float rA = e.rA, rB = e.rB, rBias = e.rBias;
+  const float s8 = g.out8_dtype ? out8_scale_value(g) : 1.f;
 #pragma unroll 1
   for (int c0 = 0; c0 < BN; c0 += 32) {
     uint32_t r[32];
@@ -135,7 +136,22 @@ __device__ __forceinline__ void epi_drain(const GemmParams& g, uint32_t t_row, c
             }
           }
         }
-        if (g.out_dtype == B200Q_BF16) {
+        if (g.out8_dtype) {
+          uint8_t* o = static_cast<uint8_t*>(g.out) + m * g.ldo + n0;
+          uint32_t w[CW / 4];
+#pragma unroll
+          for (int j = 0; j < CW; j += 4)
+            w[j / 4] = out8_byte(g, v[j], s8) | (out8_byte(g, v[j + 1], s8) << 8) | (out8_byte(g, v[j + 2], s8) << 16) |
+                       (out8_byte(g, v[j + 3], s8) << 24);
+          if (n0 + CW <= g.N && (reinterpret_cast<uintptr_t>(o) & 15) == 0) {
+#pragma unroll
+            for (int j = 0; j < CW / 4; j += 4) *reinterpret_cast<uint4*>(o + 4 * j) = make_uint4(w[j], w[j + 1], w[j + 2], w[j + 3]);
+          } else {
+#pragma unroll
+            for (int j = 0; j < CW; ++j)
+              if (n0 + j < g.N) o[j] = (uint8_t)(w[j / 4] >> (8 * (j & 3)));
+          }
+        } else if (g.out_dtype == B200Q_BF16) {
           __nv_bfloat16* o = static_cast<__nv_bfloat16*>(g.out) + m * g.ldo + n0;
           if (n0 + CW <= g.N && (reinterpret_cast<uintptr_t>(o) & 15) == 0) {
 #pragma unroll
@@ -172,7 +188,8 @@ __device__ __forceinline__ void epi_drain(const GemmParams& g, uint32_t t_row, c
             float o = v[j];
             if (g.bias_mode == B200Q_BCAST_FULL) o += ld_out_typed(g.bias, g.bias_dtype, m * g.bias_ld + n);
             if (g.D) o += ld_out_typed(g.D, g.d_dtype, m * g.ldd + n);
-            if (g.out_dtype == B200Q_BF16) static_cast<__nv_bfloat16*>(g.out)[m * g.ldo + n] = __float2bfloat16_rn(o);
+            if (g.out8_dtype) static_cast<uint8_t*>(g.out)[m * g.ldo + n] = (uint8_t)out8_byte(g, o, s8);
+            else if (g.out_dtype == B200Q_BF16) static_cast<__nv_bfloat16*>(g.out)[m * g.ldo + n] = __float2bfloat16_rn(o);
             else static_cast<float*>(g.out)[m * g.ldo + n] = o;
           }
         }

@@ -63,8 +63,8 @@ __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity)
 // slots from the warps that feed the tensor core.
 constexpr uint32_t kWaitLimit = 1u << 24;
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status,
-                                          int code, uint32_t backoff_ns = 0) {
-  for (uint32_t i = 0; i < kWaitLimit; ++i) {
+                                          int code, uint32_t backoff_ns = 0, uint32_t limit = kWaitLimit) {
+  for (uint32_t i = 0; i < limit; ++i) {
 #ifdef B200Q_SPIN_TEST_WAIT
     if (mbar_test_wait(bar, parity)) return true;
 #else

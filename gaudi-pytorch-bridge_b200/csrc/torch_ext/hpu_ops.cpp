@@ -490,9 +490,11 @@ ScaleArg to_scale_arg(const OptTensor& t) {
   return s;
 }
 
+// out8_dtype / out8_scale: fused output cast (b200q::fp8_gemm_cast); Undefined = plain fp8_gemm_v2.
 at::Tensor fp8_gemm_v2_common(const at::Tensor& A, bool trans_A, const at::Tensor& B, bool trans_B, const OptTensor& D,
                               at::ScalarType out_dtype, const ScaleArg& A_scale_inv, const ScaleArg& B_scale_inv,
-                              const OptTensor& bias, bool accumulate, OptShape B_scale_shape) {
+                              const OptTensor& bias, bool accumulate, OptShape B_scale_shape,
+                              at::ScalarType out8_dtype = at::ScalarType::Undefined, double out8_scale = 1.0) {
   TORCH_CHECK(is_fp8(A.scalar_type()) && is_fp8(B.scalar_type()), "fp8_gemm_v2 inputs must be float8 tensors, got ",
               A.scalar_type(), " and ", B.scalar_type());
   TORCH_CHECK(out_dtype == at::kFloat || out_dtype == at::kBFloat16,
@@ -519,10 +521,17 @@ at::Tensor fp8_gemm_v2_common(const at::Tensor& A, bool trans_A, const at::Tenso
     bshape = at::infer_size(ab, bb);
   }
   int64_t batch = numel_of(bshape);
-  at::Tensor out = at::empty(out_shape, A.options().dtype(out_dtype));
+  const bool fused_cast = out8_dtype != at::ScalarType::Undefined;
+  TORCH_CHECK(!fused_cast || is_fp8(out8_dtype), "fp8_gemm_cast: the output dtype must be float8_e5m2 or float8_e4m3fn");
+  at::Tensor out = at::empty(out_shape, A.options().dtype(fused_cast ? out8_dtype : out_dtype));
   if (out.numel() == 0) return out;
 
   b200q_gemm_args g{};
+  if (fused_cast) {
+    g.out8_dtype = to_b200q_dtype(out8_dtype);
+    g.out8_scale = nullptr;
+    g.out8_scale_host = (float)out8_scale;
+  }
   int64_t Mk = M;  // M as the kernel sees it (batch may be folded in)
   bool folded = false;
   if (batch > 1 && b.dim() == 2 && !ta) {
@@ -625,6 +634,39 @@ at::Tensor& fp8_gemm(const at::Tensor& A, bool trans_A, const at::Tensor& B, boo
                              c10::nullopt);
   out.copy_(r);
   return out;
+}
+
+// GEMM with the cast of its result fused into the epilogue: cast_to_fp8_v2(fp8_gemm_v2(...), out_scale, RNE).
+at::Tensor fp8_gemm_cast(const at::Tensor& A, bool trans_A, const at::Tensor& B, bool trans_B, const OptTensor& D,
+                         at::ScalarType mid_dtype, const OptTensor& A_scale_inv, const OptTensor& B_scale_inv,
+                         const OptTensor& bias, bool accumulate, OptShape B_scale_shape, double out_scale,
+                         at::ScalarType out_dtype) {
+  return fp8_gemm_v2_common(A, trans_A, B, trans_B, D, mid_dtype, to_scale_arg(A_scale_inv), to_scale_arg(B_scale_inv), bias,
+                            accumulate, B_scale_shape, out_dtype, out_scale);
+}
+
+// aten::_scaled_mm-shaped entry (the reference lowers _scaled_mm to the same fp8_gemm node,
+// hpu_ops/backend/scaled_mm_gen.cpp:66-140): out = (a @ b) * scale_a * scale_b + bias; b is usually the
+// transposed view of an [N, K] weight, which is recognised and passed as a K-major operand.
+at::Tensor scaled_mm(const at::Tensor& a, const at::Tensor& b, const at::Tensor& scale_a, const at::Tensor& scale_b,
+                     const OptTensor& bias, const OptTensor& scale_result, at::ScalarType out_dtype) {
+  TORCH_CHECK(a.dim() == 2 && b.dim() == 2, "scaled_mm: 2-D operands expected");
+  const bool b_is_transposed_view = b.stride(0) == 1 && b.stride(1) >= b.size(0) && b.size(0) > 1;
+  at::Tensor bb = b_is_transposed_view ? b.t() : b;
+  at::Tensor sb = scale_b;
+  OptShape shape = c10::nullopt;
+  std::vector<int64_t> shp;
+  if (sb.numel() > 1) {  // row-wise scaling: scale_b is [1, N]
+    shp = {1, sb.numel()};
+    shape = shp;
+  }
+  if (is_fp8(out_dtype)) {
+    double s = scale_result.has_value() && scale_result->defined() ? scale_result->item<double>() : 1.0;
+    return fp8_gemm_v2_common(a, false, bb, b_is_transposed_view, c10::nullopt, at::kBFloat16, ScaleArg(scale_a), ScaleArg(sb),
+                              bias, false, shape, out_dtype, s);
+  }
+  return fp8_gemm_v2_common(a, false, bb, b_is_transposed_view, c10::nullopt, out_dtype, ScaleArg(scale_a), ScaleArg(sb), bias,
+                            false, shape);
 }
 
 // ------------------------------------------------------------------ b200q:: extras
@@ -786,6 +828,8 @@ TORCH_LIBRARY(b200q, m) {
   m.def("w4a16_gemm(Tensor x, Tensor qweight, Tensor scales, Tensor? qzeros, int group_size, bool k_packed, ScalarType out_dtype) -> Tensor");
   m.def("dequant_kpacked(Tensor qweight, Tensor scales, Tensor? qzeros, ScalarType out_dtype) -> Tensor");
   m.def("gptq_repack(Tensor qweight, Tensor? qzeros) -> (Tensor, Tensor)");
+  m.def("fp8_gemm_cast(Tensor A, bool trans_A, Tensor B, bool trans_B, Tensor? D, ScalarType mid_dtype, Tensor? A_scale_inv, Tensor? B_scale_inv, Tensor? bias, bool accumulate, int[]? B_scale_shape, float out_scale, ScalarType out_dtype) -> Tensor");
+  m.def("scaled_mm(Tensor a, Tensor b, Tensor scale_a, Tensor scale_b, Tensor? bias, Tensor? scale_result, ScalarType out_dtype) -> Tensor");
   m.def("swiglu_cast_fp8(Tensor gate, Tensor up, float scale, bool is_amax) -> (Tensor, Tensor)");
   m.def("set_sr_seed(int seed) -> ()", set_sr_seed);
   m.def("set_cast_mul_in_fp32(bool on) -> ()", set_cast_mul_in_fp32);
@@ -797,5 +841,7 @@ TORCH_LIBRARY_IMPL(b200q, CUDA, m) {
   m.impl("w4a16_gemm", w4a16_gemm);
   m.impl("dequant_kpacked", dequant_kpacked);
   m.impl("gptq_repack", gptq_repack);
+  m.impl("fp8_gemm_cast", fp8_gemm_cast);
+  m.impl("scaled_mm", scaled_mm);
   m.impl("swiglu_cast_fp8", swiglu_cast_fp8);
 }

@@ -66,6 +66,13 @@ const char* b200q_last_cuda_error(void);
 /* Synchronises the current device, reads and clears the device status word.
  * 0 = every bounded wait completed; otherwise a kernel-specific code. */
 int b200q_device_status(int* code_out);
+/* Launches a one-warp kernel whose only wait can never be satisfied and has a short poll limit:
+ * the wait gives up, stores `code` (non-zero) in the device status word and the kernel ends
+ * normally.  b200q_device_status() then reports B200Q_ERR_DEVICE_TIMEOUT with that code and the
+ * context stays usable.  Exercises the path every tcgen05 kernel here takes when a barrier is
+ * never signalled (the reference maps device errors to exceptions in
+ * backend/synapse_helpers/synapse_error.h). */
+int b200q_selftest_wait_timeout(int code, void* stream);
 /* Number of kernels this library has launched in this process (all threads). */
 uint64_t b200q_launch_count(void);
 
@@ -191,6 +198,14 @@ typedef struct b200q_gemm_args {
   int64_t ldd, d_batch_stride;
   int force_generic; /* 1 = skip the tcgen05 path (testing) */
   void* stream;
+  /* Fused output cast (0 = off): with out8_dtype = E4M3 / E5M2, `out` receives fp8 bytes (ldo in
+   * bytes = elements) equal to cast_to_fp8(out_dtype(result), out8_scale) -- the GEMM result is
+   * rounded to out_dtype first, then scaled and rounded to fp8 (RNE, saturating), which is the
+   * cast -> MME fusion of the reference's graph compiler (hpu_ops/backend/fp8_ops.cpp:478-480)
+   * with the numerics of the unfused pair of operators. */
+  int out8_dtype;
+  const float* out8_scale; /* device scalar or NULL */
+  float out8_scale_host;   /* used when out8_scale is NULL */
 } b200q_gemm_args;
 
 int b200q_fp8_gemm(const b200q_gemm_args* args);

@@ -314,3 +314,41 @@ def test_tcgen05_batched(ops):
            [1, 320], tol=1e-5)
     Bt = _rand_fp8((2, 256, 320), torch.float8_e5m2, g)   # [K][N] storage, batch broadcast against A's
     _check(A, False, Bt, False, None, torch.bfloat16)
+
+
+@pytest.mark.parametrize("mid", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("out8", FP8)
+@pytest.mark.parametrize("M,N,K", [(256, 512, 256), (16, 384, 512), (130, 257, 96), (24, 36, 12)])
+def test_fused_output_cast_equals_unfused_pair(ops, mid, out8, M, N, K):
+    """fp8_gemm_cast == cast_to_fp8_v2(fp8_gemm_v2(...), scale) byte for byte (same kernels, the cast
+    moved into the epilogue), and close to the oracle's composition."""
+    g = torch.Generator().manual_seed(M + N)
+    A = _rand_fp8((M, K), torch.float8_e4m3fn, g)
+    B = _rand_fp8((N, K), torch.float8_e4m3fn, g)
+    sA, sB = torch.tensor(0.5), torch.rand(N, generator=g) + 0.5
+    bias = torch.randn(N, generator=g).to(torch.bfloat16)
+    scale = 3.7
+    fused = torch.ops.b200q.fp8_gemm_cast(A.cuda(), False, B.cuda(), True, None, mid, sA.cuda(), sB.cuda(), bias.cuda(), False,
+                                          [1, N], scale, out8)
+    plain = torch.ops.hpu.fp8_gemm_v2(A.cuda(), False, B.cuda(), True, None, mid, sA.cuda(), sB.cuda(), bias.cuda(), False, [1, N])
+    two, _ = torch.ops.hpu.cast_to_fp8_v2(plain, scale, False, False, out8)
+    assert fused.dtype == out8 and fused.shape == (M, N)
+    assert torch.equal(fused.view(torch.uint8), two.view(torch.uint8))
+    ref, _ = O.cast_to_fp8_v2(O.fp8_gemm_v2(A, False, B, True, None, mid, sA, sB, bias, False, [1, N]), scale, False, False, out8)
+    assert O.rel_frobenius(fused.float(), ref.float()) <= 4e-2   # one fp8 step on the few results that sit on a tie
+
+
+def test_scaled_mm_entry(ops):
+    g = torch.Generator().manual_seed(12)
+    M, N, K = 64, 256, 128
+    a = _rand_fp8((M, K), torch.float8_e4m3fn, g)
+    w = _rand_fp8((N, K), torch.float8_e4m3fn, g)
+    sa, sw = torch.tensor(0.25), torch.tensor(2.0)
+    bias = torch.randn(N, generator=g).to(torch.bfloat16)
+    r = torch.ops.b200q.scaled_mm(a.cuda(), w.cuda().t(), sa.cuda(), sw.cuda(), bias.cuda(), None, torch.bfloat16)
+    e = O.fp8_gemm_v2(a, False, w, True, None, torch.bfloat16, sa, sw, bias)
+    assert O.rel_frobenius(r, e) <= TOL
+    r2 = torch.ops.b200q.scaled_mm(a.cuda(), w.t().contiguous().cuda(), sa.cuda(), sw.cuda(), None, None, torch.float32)
+    assert O.rel_frobenius(r2, O.fp8_gemm_v2(a, False, w, True, None, torch.float32, sa, sw)) <= 1e-5
+    r8 = torch.ops.b200q.scaled_mm(a.cuda(), w.cuda().t(), sa.cuda(), sw.cuda(), None, torch.tensor(0.5).cuda(), torch.float8_e4m3fn)
+    assert r8.dtype == torch.float8_e4m3fn
