@@ -184,6 +184,41 @@ __device__ __forceinline__ void umma_f8_pair(uint32_t d_tmem, uint64_t adesc, ui
       "}\n" ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
       : "memory");
 }
+__device__ __forceinline__ void umma_f16_pair(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                              uint32_t accumulate) {
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "setp.ne.b32 p, %4, 0;\n"
+      "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n"
+      "}\n" ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// Bounded wait on a barrier that threads of the peer CTA arrive on (cluster-scope acquire, so
+// that what they wrote to their shared memory before arriving is ordered before what follows).
+__device__ __forceinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status,
+                                                  int code) {
+  for (uint32_t i = 0; i < kWaitLimit; ++i) {
+    uint32_t ok;
+    asm volatile(
+        "{\n"
+        ".reg .pred p;\n"
+        "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n"
+        "selp.u32 %0, 1, 0, p;\n"
+        "}\n"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+    if (ok) return true;
+    if ((i & 255u) == 255u) {
+      if (*abort_flag) return false;
+      if (i > 4096u) __nanosleep(64);
+    }
+  }
+  *abort_flag = 1;
+  atomicCAS(status, 0, code);
+  return false;
+}
 // Completion of the pair's MMAs signalled on the barrier at the same offset in both CTAs.
 __device__ __forceinline__ void umma_commit_pair_both(uint32_t bar) {
   asm volatile(
@@ -197,6 +232,13 @@ __device__ __forceinline__ void umma_commit_pair_both(uint32_t bar) {
 // Arrive on a barrier addressed in the cluster window (own CTA or the peer).
 __device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
   asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+// The same with the default (CTA-scope) release: no cluster-wide fence is executed, which on
+// B200 costs about a thousand cycles per arrival.  Enough when what the arrival publishes is
+// this CTA's own shared memory, already made visible to the async proxy by
+// fence.proxy.async, and read there by the tensor core of this same SM.
+__device__ __forceinline__ void mbar_arrive_remote(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
 }
 
 // 32 lanes x 32 consecutive 32-bit columns: thread t of the warp gets lane (base lane + t).

@@ -23,6 +23,8 @@
 //              tiles are summed by a second kernel (deterministic: no atomics).
 #include <cuda.h>
 
+#include <cstdlib>
+
 #include "common.cuh"
 #include "tcgen05_ptx.cuh"
 #include "tma_host.cuh"
@@ -419,6 +421,324 @@ w4a16_kernel(const __grid_constant__ CUtensorMap map_act, const __grid_constant_
   }
 }
 
+
+// ------------------------------------------------------------------------ CTA-pair form (large M)
+// Two CTAs of a cluster share a 256-token x 256-column tile.  Each CTA loads its own 128 token
+// rows and expands its own 128 weight columns per stage (half the expansion work and half the
+// expanded-tile stores per CTA for the same tensor-core work as a 128 x 256 tile); the even CTA
+// issues tcgen05.mma.cta_group::2 (M = 256, N = 256), which reads both CTAs' shared memory.
+// Both CTAs' expander warps arrive (remotely for the odd CTA) on the even CTA's "weights ready"
+// barrier; ring stages, weight buffers and accumulators are released in both CTAs by multicast
+// tcgen05.commit, as in the FP8 pair kernel.
+template <int STAGES, int NWBUF>
+struct PairCfg {
+  static constexpr int kActBytes = 128 * 128;
+  static constexpr int kRawBytes = kRawUnit;               // 64 k x 16 words
+  static constexpr int kMetaOffset = kActBytes + kRawBytes;
+  static constexpr int kScaleBytes = kUnit * 2, kZpBytes = kUnit / 2;
+  static constexpr int kZpOffset = kMetaOffset + 512;
+  static constexpr int kStageBytes = ((kMetaOffset + 1024 + 1023) / 1024) * 1024;
+  static constexpr int kWBufBytes = kUnit * 128;           // 128 columns x 64 k bf16
+  static constexpr int kRing = STAGES * kStageBytes;
+  static constexpr int kWOffset = kRing;
+  static constexpr int kBarOffset = kWOffset + NWBUF * kWBufBytes;
+  static constexpr int kNumBars = 3 * STAGES + 2 * NWBUF + 4;
+  static constexpr int kTotal = kBarOffset + kNumBars * 8 + 16;
+  static constexpr int kExpandWarps = 8;   // per stage
+  static constexpr int kExpandGroups = 2;  // warp groups taking alternate stages
+  static constexpr int kThreads = 32 * (6 + kExpandWarps * kExpandGroups);
+};
+
+template <int STAGES, int NWBUF>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__((PairCfg<STAGES, NWBUF>::kThreads), 1)
+w4a16_pair_kernel(const __grid_constant__ CUtensorMap map_act, const __grid_constant__ CUtensorMap map_raw,
+                  const __grid_constant__ CUtensorMap map_scale, const __grid_constant__ CUtensorMap map_zp, const Params p) {
+  using C = PairCfg<STAGES, NWBUF>;
+  constexpr int BN = 256;
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::kBarOffset);
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + C::kNumBars);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  volatile int* epi_stop = reinterpret_cast<volatile int*>(tmem_slot + 2);
+
+  const uint32_t rank = cluster_ctarank();
+  const uint32_t smem_base = smem_u32(smem);
+  const uint32_t wbuf_base = smem_base + C::kWOffset;
+  const uint32_t bar_full = smem_u32(bars), bar_empty = bar_full + 8 * STAGES;
+  const uint32_t bar_raw = bar_empty + 8 * STAGES;  // this CTA's packed weights (+ scales) of a stage landed
+  const uint32_t bar_wready = bar_raw + 8 * STAGES, bar_wfree = bar_wready + 8 * NWBUF;
+  const uint32_t bar_tfull = bar_wfree + 8 * NWBUF, bar_tempty = bar_tfull + 16;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(bar_full + 8 * s, 1);
+      mbar_init(bar_empty + 8 * s, 1);
+      mbar_init(bar_raw + 8 * s, 1);
+    }
+    for (int b = 0; b < NWBUF; ++b) {
+      mbar_init(bar_wready + 8 * b, 2 * C::kExpandWarps);  // even CTA: expander warps of both CTAs
+      mbar_init(bar_wfree + 8 * b, 1);
+    }
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(bar_tfull + 8 * a, 1);
+      mbar_init(bar_tempty + 8 * a, 2 * kEpiThreads);
+    }
+    *abort_flag = 0;
+    *epi_stop = 0;
+    fence_barrier_init();
+    fence_proxy_async_smem();
+    tma_prefetch_desc(&map_act);
+    tma_prefetch_desc(&map_raw);
+    tma_prefetch_desc(&map_scale);
+    if (p.zp) tma_prefetch_desc(&map_zp);
+  }
+  __syncthreads();
+  if (warp == 1) {
+    tmem_alloc_pair(smem_u32(tmem_slot), 512);
+    tmem_relinquish_pair();
+  }
+  tc_fence_before();
+  cluster_sync_all();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  const int pair = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
+  const int num_tiles = p.x_tiles * p.y_tiles;  // 256-token x 256-column tiles
+  const int num_kb = p.num_kb;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      uint32_t stage = 0, phase = 0;
+      bool ok = true;
+      for (int tile = pair; tile < num_tiles && ok; tile += num_pairs) {
+        const int xt = tile % p.x_tiles, yt = tile / p.x_tiles;
+        const int act_row0 = xt * 256 + (int)rank * 128;
+        const int n0 = yt * BN + (int)rank * kUnit;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(bar_empty + 8 * stage, phase ^ 1, abort_flag, p.status, kErrProducer)) {
+            ok = false;
+            break;
+          }
+          const uint32_t full = (bar_full + 8 * stage) & kPeerBitMask;
+          const uint32_t sbase = smem_base + stage * C::kStageBytes;
+          const int grp = (kb * kK) / p.group;
+          const bool new_group = true;  // every stage carries its scales: alternate stages go to different warps
+          // activations of both CTAs complete on the even CTA's barrier (the MMA issuer waits
+          // there); each CTA's packed weights complete on its own barrier (its expanders wait there)
+          if (rank == 0) mbar_arrive_expect_tx(bar_full + 8 * stage, 2 * C::kActBytes);
+          tma_load_2d_pair(sbase, &map_act, full, kb * kK, act_row0);
+          const uint32_t rawb = bar_raw + 8 * stage;
+          mbar_arrive_expect_tx(rawb, C::kRawBytes + (new_group ? C::kScaleBytes + (p.zp ? C::kZpBytes : 0) : 0));
+          tma_load_2d(sbase + C::kActBytes, &map_raw, rawb, n0 / 8, kb * kK);
+          if (new_group) {
+            tma_load_2d(sbase + C::kMetaOffset, &map_scale, rawb, n0, grp);
+            if (p.zp) tma_load_2d(sbase + C::kZpOffset, &map_zp, rawb, n0 / 8, grp);
+          }
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0 && rank == 0) {
+      const uint32_t idesc = umma_idesc_major(1u, 1u, 256, BN, 0u, 1u);
+      const uint64_t da0 = smem_desc_k_sw128(smem_base);
+      const uint64_t dw0 = smem_desc_mn_sw128(wbuf_base, (kK / 8) * 1024, 1024);
+      uint32_t stage = 0, phase = 0, wb = 0, wphase = 0;
+      int it = 0;
+      bool ok = true;
+      for (int tile = pair; tile < num_tiles && ok; tile += num_pairs, ++it) {
+        const uint32_t acc = it & 1, acc_phase = (it >> 1) & 1;
+        if (!mbar_wait(bar_tempty + 8 * acc, acc_phase ^ 1, abort_flag, p.status, kErrMmaTmem)) break;
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + acc * BN;
+        for (int kb = 0; kb < num_kb; ++kb) {
+          if (!mbar_wait(bar_full + 8 * stage, phase, abort_flag, p.status, kErrMma) ||
+              !mbar_wait(bar_wready + 8 * wb, wphase, abort_flag, p.status, kErrMma)) {
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint64_t da = da0 + (uint64_t)(stage * (uint32_t)(C::kStageBytes >> 4));
+          const uint64_t dw = dw0 + (uint64_t)(wb * (uint32_t)(C::kWBufBytes >> 4));
+          umma_f16_pair(d_tmem, da, dw, idesc, kb != 0);
+#pragma unroll
+          for (int k = 1; k < kK / 16; ++k)
+            umma_f16_pair(d_tmem, da + k * (kUmmaKBytes >> 4), dw + k * (2048 >> 4), idesc, 1u);
+          umma_commit_pair_both(bar_empty + 8 * stage);
+          umma_commit_pair_both(bar_wfree + 8 * wb);
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+          if (++wb == NWBUF) { wb = 0; wphase ^= 1; }
+        }
+        if (ok) umma_commit_pair_both(bar_tfull + 8 * acc);
+      }
+    }
+  } else if (warp < 6) {
+    const int q = warp & 3;
+    const int et = threadIdx.x - 64;
+    int it = 0;
+    for (int tile = pair; tile < num_tiles; tile += num_pairs, ++it) {
+      const int xt = tile % p.x_tiles, yt = tile / p.x_tiles;
+      const uint32_t acc = it & 1, acc_phase = (it >> 1) & 1;
+      mbar_wait(bar_tfull + 8 * acc, acc_phase, abort_flag, p.status, kErrEpilogue, 128);
+      named_bar_sync(1, kEpiThreads);
+      if (et == 0) *epi_stop = *abort_flag;
+      named_bar_sync(1, kEpiThreads);
+      if (*epi_stop) break;
+      tc_fence_after();
+      const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16) + acc * BN;
+      const int64_t m = (int64_t)xt * 256 + (int64_t)rank * 128 + q * 32 + lane;
+      const int64_t y0 = (int64_t)yt * BN;
+#pragma unroll 1
+      for (int c0 = 0; c0 < BN; c0 += 32) {
+        uint32_t r[32];
+        tmem_ld_32x32(t_row + c0, r);
+        tmem_ld_wait();
+        {  // tile-position order -> column order (see the single-CTA kernel)
+          uint32_t t[32];
+#pragma unroll
+          for (int j = 0; j < 32; ++j) t[(j & ~7) + ((j & 7) >> 1) + 4 * (j & 1)] = r[j];
+#pragma unroll
+          for (int j = 0; j < 32; ++j) r[j] = t[j];
+        }
+        const int64_t n0 = y0 + c0;
+        if (m < p.M) {
+          if (p.out_dtype == B200Q_BF16) {
+            __nv_bfloat16* o = static_cast<__nv_bfloat16*>(p.out) + m * p.ldo + n0;
+            if (n0 + 32 <= p.N && (reinterpret_cast<uintptr_t>(o) & 15) == 0) {
+#pragma unroll
+              for (int j = 0; j < 32; j += 8)
+                *reinterpret_cast<uint4*>(o + j) = make_uint4(
+                    pack_bf16x2(__uint_as_float(r[j]), __uint_as_float(r[j + 1])),
+                    pack_bf16x2(__uint_as_float(r[j + 2]), __uint_as_float(r[j + 3])),
+                    pack_bf16x2(__uint_as_float(r[j + 4]), __uint_as_float(r[j + 5])),
+                    pack_bf16x2(__uint_as_float(r[j + 6]), __uint_as_float(r[j + 7])));
+            } else {
+#pragma unroll
+              for (int j = 0; j < 32; ++j)
+                if (n0 + j < p.N) o[j] = __float2bfloat16_rn(__uint_as_float(r[j]));
+            }
+          } else {
+            float* o = static_cast<float*>(p.out) + m * p.ldo + n0;
+#pragma unroll
+            for (int j = 0; j < 32; ++j)
+              if (n0 + j < p.N) o[j] = __uint_as_float(r[j]);
+          }
+        }
+      }
+      tc_fence_before();
+      mbar_arrive_cluster((bar_tempty + 8 * acc) & kPeerBitMask);
+    }
+  } else {
+    // expanders: this CTA's 128 columns (one unit), 8 warps, 4 packed words per thread and stage
+    const int et = (threadIdx.x - 192) % (C::kExpandWarps * 32);
+    const uint32_t my_parity = (threadIdx.x - 192) / (C::kExpandWarps * 32);
+    uint32_t kcount = 0;
+    constexpr int W = 16;
+    constexpr int kRowsPerPass = C::kExpandWarps * 32 / W;  // 16
+    constexpr int kPasses = kK / kRowsPerPass;              // 4
+    const int ngl = et % W, kr = et / W;
+    const bool has_zp = p.zp != nullptr;
+    uint32_t stage = 0, phase = 0, wb = 0, wphase = 0;
+    bool ok = true;
+    for (int tile = pair; tile < num_tiles && ok; tile += num_pairs) {
+      GroupRegs g;
+      int g_cur = -1;
+      for (int kb = 0; kb < num_kb; ++kb, ++kcount) {
+        if ((kcount % C::kExpandGroups) != my_parity) {
+          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+          if (++wb == NWBUF) { wb = 0; wphase ^= 1; }
+          continue;
+        }
+        if (!mbar_wait(bar_raw + 8 * stage, phase, abort_flag, p.status, kErrExpand) ||
+            !mbar_wait(bar_wfree + 8 * wb, wphase ^ 1, abort_flag, p.status, kErrExpand)) {
+          ok = false;
+          break;
+        }
+        const uint32_t sbase = smem_base + stage * C::kStageBytes;
+        const int grp = (kb * kK) / p.group;
+        if (grp != g_cur) {
+          uint4 sv;
+          asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
+                       : "=r"(sv.x), "=r"(sv.y), "=r"(sv.z), "=r"(sv.w)
+                       : "r"(sbase + C::kMetaOffset + ngl * 16));
+          const uint32_t zw = has_zp ? lds32(sbase + C::kZpOffset + ngl * 4) : 0u;
+          make_group(g, sv, zw, has_zp);
+          g_cur = grp;
+        }
+        const uint32_t raw = sbase + C::kActBytes + (kr * W + ngl) * 4;
+        const uint32_t krow = kr & 7;
+        const uint32_t wt = wbuf_base + wb * C::kWBufBytes + ((ngl >> 3) * (kK / 8) + (kr >> 3)) * 1024 + krow * 128 +
+                            (((ngl & 7) ^ krow) << 4);
+        uint32_t wv[kPasses];
+#pragma unroll
+        for (int j = 0; j < kPasses; ++j) wv[j] = lds32(raw + j * kRowsPerPass * W * 4);
+#pragma unroll
+        for (int j = 0; j < kPasses; ++j) {
+          sts128(wt + j * (kRowsPerPass / 8) * 1024, bf2_mul(bf2_sub(nib_pair(wv[j], 0), g.zr[0]), g.sp[0]),
+                 bf2_mul(bf2_sub(nib_pair(wv[j], 1), g.zr[1]), g.sp[1]),
+                 bf2_mul(bf2_sub(nib_pair(wv[j], 2), g.zr[2]), g.sp[2]),
+                 bf2_mul(bf2_sub(nib_pair(wv[j], 3), g.zr[3]), g.sp[3]));
+        }
+        fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) {
+          if (rank == 0) mbar_arrive(bar_wready + 8 * wb);
+          else mbar_arrive_remote((bar_wready + 8 * wb) & kPeerBitMask);  // the even CTA's barrier
+        }
+        if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        if (++wb == NWBUF) { wb = 0; wphase ^= 1; }
+      }
+    }
+  }
+
+  __syncwarp();
+  tc_fence_before();
+  __syncthreads();
+  if (*abort_flag) {
+    for (int i = 0; i < 200; ++i) __nanosleep(1000);
+  }
+  cluster_sync_all();
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc_pair(tmem_base, 512);
+  }
+}
+
+template <int STAGES, int NWBUF>
+static int launch_pair(const CUtensorMap& ma, const CUtensorMap& mr, const CUtensorMap& ms, const CUtensorMap& mz,
+                       const Params& p, cudaStream_t st) {
+  using C = PairCfg<STAGES, NWBUF>;
+  constexpr int smem = C::kTotal + 1024;
+  static_assert(smem <= 227 * 1024, "shared memory budget");
+  static_assert(smem > 116 * 1024, "one CTA per SM: two CTAs must never contend for TMEM");
+  auto kern = w4a16_pair_kernel<STAGES, NWBUF>;
+  static std::atomic<int> resident_pairs[kMaxDevices];
+  const int dev = current_device_index();
+  if (dev < 0) return B200Q_ERR_CUDA;
+  int clusters = resident_pairs[dev].load(std::memory_order_acquire);
+  if (clusters == 0) {
+    B200Q_CUDA_OK(cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, smem));
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(kNumSMs, 1, 1);
+    cfg.blockDim = dim3(C::kThreads, 1, 1);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    if (cudaOccupancyMaxActiveClusters(&clusters, kern, &cfg) != cudaSuccess || clusters < 1) {
+      cudaGetLastError();
+      clusters = -1;
+    }
+    resident_pairs[dev].store(clusters, std::memory_order_release);
+  }
+  if (clusters < 0) return B200Q_ERR_UNSUPPORTED;
+  const int tiles = p.x_tiles * p.y_tiles;
+  const int pairs = tiles < clusters ? tiles : clusters;
+  kern<<<2 * pairs, C::kThreads, smem, st>>>(ma, mr, ms, mz, p);
+  B200Q_LAUNCH_CHECK();
+  return B200Q_OK;
+}
+
 // Sum the fp32 partial tiles of a split-K run and round once to the output dtype.
 __global__ void __launch_bounds__(256) splitk_reduce_kernel(const float* __restrict__ partial, void* out, int out_dtype,
                                                             int64_t M, int64_t N, int64_t ldo, int splits) {
@@ -515,6 +835,32 @@ int w4a16_gemm_impl(const void* x, int64_t ldx, const int32_t* qweight, const vo
   } else {
     mz = ms;  // never dereferenced
   }
+  static const bool no_pairs = std::getenv("B200Q_W4A16_NO_PAIRS") != nullptr;
+  if (!swap && bn_w == 256 && M > 128 && !no_pairs) {
+    // CTA pairs: 256-token x 256-column tiles, each CTA expands 128 columns
+    w4::Params pp = p;
+    pp.x_tiles = (int)((M + 255) / 256);
+    pp.y_tiles = (int)((N + 255) / 256);
+    CUtensorMap mr1, ms1, mz1;
+    rc = make_tma_map_2d(&mr1, qweight, CU_TENSOR_MAP_DATA_TYPE_INT32, 4, N / 8, K, (N / 8) * 4, 16, w4::kK,
+                         CU_TENSOR_MAP_SWIZZLE_NONE);
+    if (rc) return rc;
+    rc = make_tma_map_2d(&ms1, scale, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, N, K / group, N * 2, 128, 1, CU_TENSOR_MAP_SWIZZLE_NONE);
+    if (rc) return rc;
+    mz1 = ms1;
+    if (p.zp) {
+      rc = make_tma_map_2d(&mz1, p.zp, CU_TENSOR_MAP_DATA_TYPE_INT32, 4, N / 8, K / group, (N / 8) * 4, 16, 1,
+                           CU_TENSOR_MAP_SWIZZLE_NONE);
+      if (rc) return rc;
+    }
+    rc = make_tma_map_2d(&ma, x, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, K, M, ldx * 2, w4::kK, 128, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc) return rc;
+    static const int pair_cfg = std::getenv("B200Q_W4A16_PAIR_CFG") ? std::atoi(std::getenv("B200Q_W4A16_PAIR_CFG")) : 0;
+    if (pair_cfg == 1) rc = w4::launch_pair<4, 8>(ma, mr1, ms1, mz1, pp, st);
+    else if (pair_cfg == 2) rc = w4::launch_pair<5, 6>(ma, mr1, ms1, mz1, pp, st);
+    else rc = w4::launch_pair<6, 4>(ma, mr1, ms1, mz1, pp, st);
+    if (rc != B200Q_ERR_UNSUPPORTED) return rc;
+  }
   if (!swap) {
     p.x_tiles = (int)((M + 127) / 128);
     const int bn = bn_w;
@@ -590,3 +936,4 @@ int w4a16_gemm_noalloc_impl(const void* x, int64_t ldx, const int32_t* qweight, 
 size_t w4a16_noalloc_max_bytes_impl() { return kStaticScratchBytes; }
 
 }  // namespace b200q
+
