@@ -427,33 +427,43 @@ w4a16_kernel(const __grid_constant__ CUtensorMap map_act, const __grid_constant_
 // rows and expands its own 128 weight columns per stage (half the expansion work and half the
 // expanded-tile stores per CTA for the same tensor-core work as a 128 x 256 tile); the even CTA
 // issues tcgen05.mma.cta_group::2 (M = 256, N = 256), which reads both CTAs' shared memory.
-// Both CTAs' expander warps arrive (remotely for the odd CTA) on the even CTA's "weights ready"
-// barrier; ring stages, weight buffers and accumulators are released in both CTAs by multicast
-// tcgen05.commit, as in the FP8 pair kernel.
-template <int STAGES, int NWBUF>
+//
+// A ring stage holds everything of one 64-deep k-block: activations, packed weights, scales /
+// zero points and the expanded bf16 weight tile.  Per stage there are three barriers:
+//   raw[s]    (each CTA)  this CTA's packed weights and scales landed           -> expanders
+//   ready[s]  (even CTA)  activations of both CTAs landed (transaction bytes) and the
+//                         expander warps of both CTAs finished the tile        -> MMA issuer
+//   empty[s]  (each CTA)  the MMAs that read the stage retired (multicast commit) -> producer
+// The expanders need no "tile free" barrier: raw[s] completes only after this CTA's producer
+// saw empty[s] and refilled the stage.  The MMA issuer waits on one barrier per stage, and
+// commits once.  Expander warps come in kExpandGroups groups that take alternate stages: the
+// chain wait -> load -> expand -> store -> fence -> arrive of one stage is several times
+// longer than the tensor-core time of a stage, so several stages are expanded concurrently.
+template <int STAGES, int GROUPS>
 struct PairCfg {
   static constexpr int kActBytes = 128 * 128;
-  static constexpr int kRawBytes = kRawUnit;               // 64 k x 16 words
-  static constexpr int kMetaOffset = kActBytes + kRawBytes;
+  static constexpr int kRawOffset = kActBytes;
+  static constexpr int kRawBytes = kRawUnit;  // 64 k x 16 words
+  static constexpr int kMetaOffset = kRawOffset + kRawBytes;
   static constexpr int kScaleBytes = kUnit * 2, kZpBytes = kUnit / 2;
   static constexpr int kZpOffset = kMetaOffset + 512;
-  static constexpr int kStageBytes = ((kMetaOffset + 1024 + 1023) / 1024) * 1024;
-  static constexpr int kWBufBytes = kUnit * 128;           // 128 columns x 64 k bf16
-  static constexpr int kRing = STAGES * kStageBytes;
-  static constexpr int kWOffset = kRing;
-  static constexpr int kBarOffset = kWOffset + NWBUF * kWBufBytes;
-  static constexpr int kNumBars = 3 * STAGES + 2 * NWBUF + 4;
+  static constexpr int kWOffset = kMetaOffset + 1024;  // 1024-byte aligned (swizzle atom)
+  static constexpr int kWBytes = kUnit * 128;          // 128 columns x 64 k bf16
+  static constexpr int kStageBytes = kWOffset + kWBytes;
+  static constexpr int kBarOffset = STAGES * kStageBytes;
+  static constexpr int kNumBars = 3 * STAGES + 4;
   static constexpr int kTotal = kBarOffset + kNumBars * 8 + 16;
-  static constexpr int kExpandWarps = 8;   // per stage
-  static constexpr int kExpandGroups = 2;  // warp groups taking alternate stages
+  static constexpr int kExpandWarps = 8;  // per stage
+  static constexpr int kExpandGroups = GROUPS;
   static constexpr int kThreads = 32 * (6 + kExpandWarps * kExpandGroups);
+  static_assert(kWOffset % 1024 == 0 && kStageBytes % 1024 == 0, "swizzled tiles need 1024-byte alignment");
 };
 
-template <int STAGES, int NWBUF>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__((PairCfg<STAGES, NWBUF>::kThreads), 1)
+template <int STAGES, int GROUPS>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__((PairCfg<STAGES, GROUPS>::kThreads), 1)
 w4a16_pair_kernel(const __grid_constant__ CUtensorMap map_act, const __grid_constant__ CUtensorMap map_raw,
                   const __grid_constant__ CUtensorMap map_scale, const __grid_constant__ CUtensorMap map_zp, const Params p) {
-  using C = PairCfg<STAGES, NWBUF>;
+  using C = PairCfg<STAGES, GROUPS>;
   constexpr int BN = 256;
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -464,22 +474,15 @@ w4a16_pair_kernel(const __grid_constant__ CUtensorMap map_act, const __grid_cons
 
   const uint32_t rank = cluster_ctarank();
   const uint32_t smem_base = smem_u32(smem);
-  const uint32_t wbuf_base = smem_base + C::kWOffset;
-  const uint32_t bar_full = smem_u32(bars), bar_empty = bar_full + 8 * STAGES;
-  const uint32_t bar_raw = bar_empty + 8 * STAGES;  // this CTA's packed weights (+ scales) of a stage landed
-  const uint32_t bar_wready = bar_raw + 8 * STAGES, bar_wfree = bar_wready + 8 * NWBUF;
-  const uint32_t bar_tfull = bar_wfree + 8 * NWBUF, bar_tempty = bar_tfull + 16;
+  const uint32_t bar_ready = smem_u32(bars), bar_empty = bar_ready + 8 * STAGES, bar_raw = bar_empty + 8 * STAGES;
+  const uint32_t bar_tfull = bar_raw + 8 * STAGES, bar_tempty = bar_tfull + 16;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
-      mbar_init(bar_full + 8 * s, 1);
+      mbar_init(bar_ready + 8 * s, 1 + 2 * C::kExpandWarps);  // producer + expander warps of both CTAs
       mbar_init(bar_empty + 8 * s, 1);
       mbar_init(bar_raw + 8 * s, 1);
-    }
-    for (int b = 0; b < NWBUF; ++b) {
-      mbar_init(bar_wready + 8 * b, 2 * C::kExpandWarps);  // even CTA: expander warps of both CTAs
-      mbar_init(bar_wfree + 8 * b, 1);
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(bar_tfull + 8 * a, 1);
@@ -509,9 +512,11 @@ w4a16_pair_kernel(const __grid_constant__ CUtensorMap map_act, const __grid_cons
   const int num_kb = p.num_kb;
 
   if (warp == 0) {
+    // ------------------------------------------------------------ TMA producer
     if (lane == 0) {
       uint32_t stage = 0, phase = 0;
       bool ok = true;
+      const uint32_t meta_bytes = C::kScaleBytes + (p.zp ? C::kZpBytes : 0);
       for (int tile = pair; tile < num_tiles && ok; tile += num_pairs) {
         const int xt = tile % p.x_tiles, yt = tile / p.x_tiles;
         const int act_row0 = xt * 256 + (int)rank * 128;
@@ -521,31 +526,28 @@ w4a16_pair_kernel(const __grid_constant__ CUtensorMap map_act, const __grid_cons
             ok = false;
             break;
           }
-          const uint32_t full = (bar_full + 8 * stage) & kPeerBitMask;
           const uint32_t sbase = smem_base + stage * C::kStageBytes;
           const int grp = (kb * kK) / p.group;
-          const bool new_group = true;  // every stage carries its scales: alternate stages go to different warps
-          // activations of both CTAs complete on the even CTA's barrier (the MMA issuer waits
-          // there); each CTA's packed weights complete on its own barrier (its expanders wait there)
-          if (rank == 0) mbar_arrive_expect_tx(bar_full + 8 * stage, 2 * C::kActBytes);
-          tma_load_2d_pair(sbase, &map_act, full, kb * kK, act_row0);
+          // packed weights and scales first: the expanders are the longer chain
           const uint32_t rawb = bar_raw + 8 * stage;
-          mbar_arrive_expect_tx(rawb, C::kRawBytes + (new_group ? C::kScaleBytes + (p.zp ? C::kZpBytes : 0) : 0));
-          tma_load_2d(sbase + C::kActBytes, &map_raw, rawb, n0 / 8, kb * kK);
-          if (new_group) {
-            tma_load_2d(sbase + C::kMetaOffset, &map_scale, rawb, n0, grp);
-            if (p.zp) tma_load_2d(sbase + C::kZpOffset, &map_zp, rawb, n0 / 8, grp);
-          }
+          mbar_arrive_expect_tx(rawb, C::kRawBytes + meta_bytes);
+          tma_load_2d(sbase + C::kRawOffset, &map_raw, rawb, n0 / 8, kb * kK);
+          tma_load_2d(sbase + C::kMetaOffset, &map_scale, rawb, n0, grp);
+          if (p.zp) tma_load_2d(sbase + C::kZpOffset, &map_zp, rawb, n0 / 8, grp);
+          // activations of both CTAs complete on the even CTA's barrier
+          if (rank == 0) mbar_arrive_expect_tx(bar_ready + 8 * stage, 2 * C::kActBytes);
+          tma_load_2d_pair(sbase, &map_act, (bar_ready + 8 * stage) & kPeerBitMask, kb * kK, act_row0);
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
       }
     }
   } else if (warp == 1) {
+    // ------------------------------------------------------------ MMA issuer (even CTA)
     if (lane == 0 && rank == 0) {
       const uint32_t idesc = umma_idesc_major(1u, 1u, 256, BN, 0u, 1u);
       const uint64_t da0 = smem_desc_k_sw128(smem_base);
-      const uint64_t dw0 = smem_desc_mn_sw128(wbuf_base, (kK / 8) * 1024, 1024);
-      uint32_t stage = 0, phase = 0, wb = 0, wphase = 0;
+      const uint64_t dw0 = smem_desc_mn_sw128(smem_base + C::kWOffset, (kK / 8) * 1024, 1024);
+      uint32_t stage = 0, phase = 0;
       int it = 0;
       bool ok = true;
       for (int tile = pair; tile < num_tiles && ok; tile += num_pairs, ++it) {
@@ -554,27 +556,25 @@ w4a16_pair_kernel(const __grid_constant__ CUtensorMap map_act, const __grid_cons
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN;
         for (int kb = 0; kb < num_kb; ++kb) {
-          if (!mbar_wait(bar_full + 8 * stage, phase, abort_flag, p.status, kErrMma) ||
-              !mbar_wait(bar_wready + 8 * wb, wphase, abort_flag, p.status, kErrMma)) {
+          if (!mbar_wait(bar_ready + 8 * stage, phase, abort_flag, p.status, kErrMma)) {
             ok = false;
             break;
           }
           tc_fence_after();
-          const uint64_t da = da0 + (uint64_t)(stage * (uint32_t)(C::kStageBytes >> 4));
-          const uint64_t dw = dw0 + (uint64_t)(wb * (uint32_t)(C::kWBufBytes >> 4));
+          const uint64_t soff = (uint64_t)(stage * (uint32_t)(C::kStageBytes >> 4));
+          const uint64_t da = da0 + soff, dw = dw0 + soff;
           umma_f16_pair(d_tmem, da, dw, idesc, kb != 0);
 #pragma unroll
           for (int k = 1; k < kK / 16; ++k)
             umma_f16_pair(d_tmem, da + k * (kUmmaKBytes >> 4), dw + k * (2048 >> 4), idesc, 1u);
           umma_commit_pair_both(bar_empty + 8 * stage);
-          umma_commit_pair_both(bar_wfree + 8 * wb);
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
-          if (++wb == NWBUF) { wb = 0; wphase ^= 1; }
         }
         if (ok) umma_commit_pair_both(bar_tfull + 8 * acc);
       }
     }
   } else if (warp < 6) {
+    // ------------------------------------------------------------ epilogue (warps 2..5)
     const int q = warp & 3;
     const int et = threadIdx.x - 64;
     int it = 0;
@@ -628,67 +628,63 @@ w4a16_pair_kernel(const __grid_constant__ CUtensorMap map_act, const __grid_cons
         }
       }
       tc_fence_before();
-      mbar_arrive_cluster((bar_tempty + 8 * acc) & kPeerBitMask);
+      mbar_arrive_remote((bar_tempty + 8 * acc) & kPeerBitMask);  // the even CTA's barrier
     }
   } else {
-    // expanders: this CTA's 128 columns (one unit), 8 warps, 4 packed words per thread and stage
+    // ------------------------------------------------------------ expanders (warps 6..)
+    // this CTA's 128 columns: 8 warps per stage, 4 packed words per thread
     const int et = (threadIdx.x - 192) % (C::kExpandWarps * 32);
-    const uint32_t my_parity = (threadIdx.x - 192) / (C::kExpandWarps * 32);
-    uint32_t kcount = 0;
+    const int my_group = (threadIdx.x - 192) / (C::kExpandWarps * 32);
     constexpr int W = 16;
     constexpr int kRowsPerPass = C::kExpandWarps * 32 / W;  // 16
     constexpr int kPasses = kK / kRowsPerPass;              // 4
     const int ngl = et % W, kr = et / W;
     const bool has_zp = p.zp != nullptr;
-    uint32_t stage = 0, phase = 0, wb = 0, wphase = 0;
+    const uint32_t krow = kr & 7;
+    const uint32_t raw_off = C::kRawOffset + (kr * W + ngl) * 4;
+    const uint32_t wt_off = C::kWOffset + ((ngl >> 3) * (kK / 8) + (kr >> 3)) * 1024 + krow * 128 + (((ngl & 7) ^ krow) << 4);
+    uint32_t stage = 0, phase = 0;
+    int turn = 0;  // whose stage this is
     bool ok = true;
     for (int tile = pair; tile < num_tiles && ok; tile += num_pairs) {
       GroupRegs g;
       int g_cur = -1;
-      for (int kb = 0; kb < num_kb; ++kb, ++kcount) {
-        if ((kcount % C::kExpandGroups) != my_parity) {
-          if (++stage == STAGES) { stage = 0; phase ^= 1; }
-          if (++wb == NWBUF) { wb = 0; wphase ^= 1; }
-          continue;
-        }
-        if (!mbar_wait(bar_raw + 8 * stage, phase, abort_flag, p.status, kErrExpand) ||
-            !mbar_wait(bar_wfree + 8 * wb, wphase ^ 1, abort_flag, p.status, kErrExpand)) {
-          ok = false;
-          break;
-        }
-        const uint32_t sbase = smem_base + stage * C::kStageBytes;
-        const int grp = (kb * kK) / p.group;
-        if (grp != g_cur) {
-          uint4 sv;
-          asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
-                       : "=r"(sv.x), "=r"(sv.y), "=r"(sv.z), "=r"(sv.w)
-                       : "r"(sbase + C::kMetaOffset + ngl * 16));
-          const uint32_t zw = has_zp ? lds32(sbase + C::kZpOffset + ngl * 4) : 0u;
-          make_group(g, sv, zw, has_zp);
-          g_cur = grp;
-        }
-        const uint32_t raw = sbase + C::kActBytes + (kr * W + ngl) * 4;
-        const uint32_t krow = kr & 7;
-        const uint32_t wt = wbuf_base + wb * C::kWBufBytes + ((ngl >> 3) * (kK / 8) + (kr >> 3)) * 1024 + krow * 128 +
-                            (((ngl & 7) ^ krow) << 4);
-        uint32_t wv[kPasses];
+      for (int kb = 0; kb < num_kb; ++kb) {
+        if (turn == my_group) {
+          if (!mbar_wait(bar_raw + 8 * stage, phase, abort_flag, p.status, kErrExpand)) {
+            ok = false;
+            break;
+          }
+          const uint32_t sbase = smem_base + stage * C::kStageBytes;
+          const int grp = (kb * kK) / p.group;
+          if (grp != g_cur) {
+            uint4 sv;
+            asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
+                         : "=r"(sv.x), "=r"(sv.y), "=r"(sv.z), "=r"(sv.w)
+                         : "r"(sbase + C::kMetaOffset + ngl * 16));
+            const uint32_t zw = has_zp ? lds32(sbase + C::kZpOffset + ngl * 4) : 0u;
+            make_group(g, sv, zw, has_zp);
+            g_cur = grp;
+          }
+          uint32_t wv[kPasses];
 #pragma unroll
-        for (int j = 0; j < kPasses; ++j) wv[j] = lds32(raw + j * kRowsPerPass * W * 4);
+          for (int j = 0; j < kPasses; ++j) wv[j] = lds32(sbase + raw_off + j * kRowsPerPass * W * 4);
 #pragma unroll
-        for (int j = 0; j < kPasses; ++j) {
-          sts128(wt + j * (kRowsPerPass / 8) * 1024, bf2_mul(bf2_sub(nib_pair(wv[j], 0), g.zr[0]), g.sp[0]),
-                 bf2_mul(bf2_sub(nib_pair(wv[j], 1), g.zr[1]), g.sp[1]),
-                 bf2_mul(bf2_sub(nib_pair(wv[j], 2), g.zr[2]), g.sp[2]),
-                 bf2_mul(bf2_sub(nib_pair(wv[j], 3), g.zr[3]), g.sp[3]));
+          for (int j = 0; j < kPasses; ++j) {
+            sts128(sbase + wt_off + j * (kRowsPerPass / 8) * 1024, bf2_mul(bf2_sub(nib_pair(wv[j], 0), g.zr[0]), g.sp[0]),
+                   bf2_mul(bf2_sub(nib_pair(wv[j], 1), g.zr[1]), g.sp[1]),
+                   bf2_mul(bf2_sub(nib_pair(wv[j], 2), g.zr[2]), g.sp[2]),
+                   bf2_mul(bf2_sub(nib_pair(wv[j], 3), g.zr[3]), g.sp[3]));
+          }
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) {
+            if (rank == 0) mbar_arrive(bar_ready + 8 * stage);
+            else mbar_arrive_remote((bar_ready + 8 * stage) & kPeerBitMask);  // the even CTA's barrier
+          }
         }
-        fence_proxy_async_smem();
-        __syncwarp();
-        if (lane == 0) {
-          if (rank == 0) mbar_arrive(bar_wready + 8 * wb);
-          else mbar_arrive_remote((bar_wready + 8 * wb) & kPeerBitMask);  // the even CTA's barrier
-        }
+        if (++turn == C::kExpandGroups) turn = 0;
         if (++stage == STAGES) { stage = 0; phase ^= 1; }
-        if (++wb == NWBUF) { wb = 0; wphase ^= 1; }
       }
     }
   }
@@ -706,14 +702,14 @@ w4a16_pair_kernel(const __grid_constant__ CUtensorMap map_act, const __grid_cons
   }
 }
 
-template <int STAGES, int NWBUF>
+template <int STAGES, int GROUPS>
 static int launch_pair(const CUtensorMap& ma, const CUtensorMap& mr, const CUtensorMap& ms, const CUtensorMap& mz,
                        const Params& p, cudaStream_t st) {
-  using C = PairCfg<STAGES, NWBUF>;
+  using C = PairCfg<STAGES, GROUPS>;
   constexpr int smem = C::kTotal + 1024;
   static_assert(smem <= 227 * 1024, "shared memory budget");
   static_assert(smem > 116 * 1024, "one CTA per SM: two CTAs must never contend for TMEM");
-  auto kern = w4a16_pair_kernel<STAGES, NWBUF>;
+  auto kern = w4a16_pair_kernel<STAGES, GROUPS>;
   static std::atomic<int> resident_pairs[kMaxDevices];
   const int dev = current_device_index();
   if (dev < 0) return B200Q_ERR_CUDA;
@@ -856,9 +852,9 @@ int w4a16_gemm_impl(const void* x, int64_t ldx, const int32_t* qweight, const vo
     rc = make_tma_map_2d(&ma, x, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, K, M, ldx * 2, w4::kK, 128, CU_TENSOR_MAP_SWIZZLE_128B);
     if (rc) return rc;
     static const int pair_cfg = std::getenv("B200Q_W4A16_PAIR_CFG") ? std::atoi(std::getenv("B200Q_W4A16_PAIR_CFG")) : 0;
-    if (pair_cfg == 1) rc = w4::launch_pair<4, 8>(ma, mr1, ms1, mz1, pp, st);
-    else if (pair_cfg == 2) rc = w4::launch_pair<5, 6>(ma, mr1, ms1, mz1, pp, st);
-    else rc = w4::launch_pair<6, 4>(ma, mr1, ms1, mz1, pp, st);
+    if (pair_cfg == 1) rc = w4::launch_pair<6, 3>(ma, mr1, ms1, mz1, pp, st);
+    else if (pair_cfg == 2) rc = w4::launch_pair<5, 2>(ma, mr1, ms1, mz1, pp, st);
+    else rc = w4::launch_pair<6, 2>(ma, mr1, ms1, mz1, pp, st);
     if (rc != B200Q_ERR_UNSUPPORTED) return rc;
   }
   if (!swap) {
