@@ -56,6 +56,35 @@ __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity)
   return ok;
 }
 
+// try_wait with a suspend-time hint (nanoseconds): the hardware may park the thread for up to
+// that long while the phase is incomplete, instead of returning to a polling loop that takes
+// issue slots from the other warps of its scheduler.
+__device__ __forceinline__ uint32_t mbar_try_wait_hint(uint32_t bar, uint32_t parity, uint32_t hint_ns) {
+  uint32_t ok;
+  asm volatile(
+      "{\n"
+      ".reg .pred p;\n"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n"
+      "selp.u32 %0, 1, 0, p;\n"
+      "}\n"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity), "r"(hint_ns)
+      : "memory");
+  return ok;
+}
+__device__ __forceinline__ bool mbar_wait_parked(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status,
+                                                 int code, uint32_t hint_ns, uint32_t limit = 1u << 22) {
+  for (uint32_t i = 0; i < limit; ++i) {
+    if (mbar_try_wait_hint(bar, parity, hint_ns)) return true;
+    if ((i & 63u) == 63u) {
+      if (*abort_flag) return false;
+    }
+  }
+  *abort_flag = 1;
+  atomicCAS(status, 0, code);
+  return false;
+}
+
 // Bounded wait.  `abort_flag` is a shared-memory word any role may set; the wait gives up
 // when it is set or after kWaitLimit polls (seconds of wall time), and then sets it itself.
 // `backoff_ns` > 0 makes a waiter that is not on the critical path (an epilogue warp waiting

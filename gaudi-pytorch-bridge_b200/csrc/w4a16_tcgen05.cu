@@ -50,36 +50,56 @@ struct Params {
   float* partial;              // [splits][M][N] fp32 (splits > 1)
   int64_t M, N, K, ldo;
   int group, out_dtype;
+  int group_shift;  // log2(group / 64) when that is a power of two, else -1 (the kernels then divide)
   int x_tiles, y_tiles, num_kb, splits, kb_per_split;
   int* status;
 };
 
-template <int BN, bool SWAP, int STAGES, int NWBUF>
+template <int BN, bool SWAP, int STAGES, int GROUPS, int AR = 0, int EW = 0>
 struct Cfg {
   static constexpr int kUnits = SWAP ? 1 : BN / kUnit;
-  static constexpr int kActRows = SWAP ? BN : 128;
+  // Activation rows held per stage.  The MMA always reads 128 rows (SWAP: BN rows) through its
+  // descriptor; with AR < 128 in the token-major form the rows beyond AR are whatever follows in
+  // the stage (packed weights, the expanded tile).  Each output row depends on its own operand
+  // row only, and rows >= M are never stored, so for M <= AR nothing needs to be there.
+  static constexpr int kActRows = AR ? AR : (SWAP ? BN : 128);
+  static_assert(AR == 0 || (!SWAP && AR <= 128 && AR % 8 == 0), "narrow activation tiles: token-major form only");
   static constexpr int kActBytes = kActRows * 128;
   static constexpr int kRawBytes = kUnits * kRawUnit;
   // group scales (bf16) and packed zero points of the stage's k-group ride in the same ring:
   // fetched from global memory by the expanders they would put a DRAM/L2 latency on every
   // group change, in the ring they are covered by the pipeline depth like everything else
   static constexpr int kWCols = kUnits * kUnit;
-  static constexpr int kMetaOffset = kActBytes + kRawBytes;
+  static constexpr int kRawOffset = kActBytes;
+  static constexpr int kMetaOffset = kRawOffset + kRawBytes;
   static constexpr int kScaleBytes = kWCols * 2, kZpBytes = kWCols / 2;
   static constexpr int kZpOffset = kMetaOffset + 512;
-  static constexpr int kStageBytes = ((kMetaOffset + 1024 + 1023) / 1024) * 1024;
-  static constexpr int kTxBytes = kActBytes + kRawBytes + kScaleBytes;  // + kZpBytes when there are zero points
+  // the expanded bf16 tile (kWCols columns x 64 k, MN-major, 128-byte swizzle) is part of the stage
+  static constexpr int kWOffset = kMetaOffset + 1024;
+  static constexpr int kWBytes = kWCols * 128;
+  static constexpr int kStageBytes = kWOffset + kWBytes;
   static constexpr int kRawRowWords = kUnits * 16;  // packed words per k-row of the stage's tile
-  static constexpr int kWBufBytes = kUnits * kUnit * 128;
-  static constexpr int kRing = STAGES * kStageBytes;
-  static constexpr int kWOffset = kRing;
-  static constexpr int kBarOffset = kWOffset + NWBUF * kWBufBytes;
-  static constexpr int kNumBars = 2 * STAGES + 2 * NWBUF + 4;
+  static constexpr int kBarOffset = STAGES * kStageBytes;
+  static constexpr int kNumBars = 3 * STAGES + 4;
   static constexpr int kTotal = kBarOffset + kNumBars * 8 + 16;
-  // 8 expander warps per 128 weight columns: each thread expands 4 packed words per stage
-  static constexpr int kSplit = 2;
-  static constexpr int kExpandWarps = 4 * kUnits * kSplit;
-  static constexpr int kThreads = 32 * (6 + kExpandWarps);
+  // 8 expander warps per 128 weight columns and stage (4 packed words per thread), in GROUPS
+  // groups that take alternate stages
+  static constexpr int kExpandWarps = EW ? EW : 8 * kUnits;
+  static constexpr int kExpandGroups = GROUPS;
+  // Warp roles are placed by scheduler (warp % 4): the producers (warps 0 and 12) and the MMA
+  // issuer (warp 4) have scheduler 0 to themselves; their per-stage instruction chains
+  // (barrier wait, copies, MMAs, commit) run 25-40 % faster than when they compete with
+  // expander warps for issue slots and the shared-memory instruction queue.  Epilogue: warps
+  // 1, 2, 3 and 8 (TMEM lane quarters 1, 2, 3, 0; asleep during the main loop).  Expanders: the
+  // warps >= 5 with warp % 4 != 0, in order.  Other warps of scheduler 0 idle.
+  static constexpr int kLastExpander = kExpandWarps * kExpandGroups - 1;
+  static constexpr int kExpWarpsEnd = 5 + (kLastExpander / 3) * 4 + kLastExpander % 3 + 1;
+  static constexpr int kWarps = kExpWarpsEnd < 13 ? 13 : kExpWarpsEnd;
+  static_assert(kWarps <= 32, "too many expander warps for one CTA");
+  static constexpr int kThreads = 32 * kWarps;
+  static_assert(kWOffset % 1024 == 0 && kStageBytes % 1024 == 0, "swizzled tiles need 1024-byte alignment");
+  static_assert(kStageBytes >= 128 * 128, "the 128-row operand read must stay inside the stage");
+  static_assert(kK % (kExpandWarps * 32 / kRawRowWords) == 0, "expander passes");
   static constexpr uint32_t kTmemCols = (2 * BN) < 32 ? 32 : 2 * BN;
 };
 
@@ -117,11 +137,11 @@ __device__ __forceinline__ void make_group(GroupRegs& g, uint4 s, uint32_t zw, b
   for (int i = 0; i < 4; ++i) g.zr[i] = has_zp ? nib_pair(zw, i) : 0x43004300u;
 }
 
-template <int BN, bool SWAP, int STAGES, int NWBUF>
-__global__ void __launch_bounds__((Cfg<BN, SWAP, STAGES, NWBUF>::kThreads), 1)
+template <int BN, bool SWAP, int STAGES, int GROUPS, int AR = 0, int EW = 0>
+__global__ void __launch_bounds__((Cfg<BN, SWAP, STAGES, GROUPS, AR, EW>::kThreads), 1)
 w4a16_kernel(const __grid_constant__ CUtensorMap map_act, const __grid_constant__ CUtensorMap map_raw,
              const __grid_constant__ CUtensorMap map_scale, const __grid_constant__ CUtensorMap map_zp, const Params p) {
-  using C = Cfg<BN, SWAP, STAGES, NWBUF>;
+  using C = Cfg<BN, SWAP, STAGES, GROUPS, AR, EW>;
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::kBarOffset);
@@ -130,20 +150,27 @@ w4a16_kernel(const __grid_constant__ CUtensorMap map_act, const __grid_constant_
   volatile int* epi_stop = reinterpret_cast<volatile int*>(tmem_slot + 2);
 
   const uint32_t smem_base = smem_u32(smem);
-  const uint32_t wbuf_base = smem_base + C::kWOffset;
-  const uint32_t bar_full = smem_u32(bars), bar_empty = bar_full + 8 * STAGES;
-  const uint32_t bar_wready = bar_empty + 8 * STAGES, bar_wfree = bar_wready + 8 * NWBUF;
-  const uint32_t bar_tfull = bar_wfree + 8 * NWBUF, bar_tempty = bar_tfull + 16;
+  // per stage: raw[s] packed weights + scales landed (-> expanders); ready[s] activations landed
+  // and every expander warp of the stage's group finished the tile (-> MMA issuer); empty[s] the
+  // MMAs that read the stage retired (-> producer).  raw[s] completes only after the producer saw
+  // empty[s], so the expanders need no barrier of their own for the tile being free.
+  const uint32_t bar_ready = smem_u32(bars), bar_empty = bar_ready + 8 * STAGES, bar_raw = bar_empty + 8 * STAGES;
+  const uint32_t bar_tfull = bar_raw + 8 * STAGES, bar_tempty = bar_tfull + 16;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  enum { kProducer, kProducerMeta, kMma, kEpilogue, kExpander, kIdle };
+  const int ewarp = ((warp - 5) >> 2) * 3 + ((warp & 3) - 1);  // expander warp index (valid when that role)
+  const int role = warp == 0    ? kProducer
+                   : warp == 4  ? kMma
+                   : warp == 12 ? kProducerMeta
+                   : (warp < 4 || warp == 8) ? kEpilogue
+                   : ((warp & 3) != 0 && ewarp < C::kExpandWarps * C::kExpandGroups) ? kExpander
+                                                                                      : kIdle;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
-      mbar_init(bar_full + 8 * s, 1);
-      mbar_init(bar_empty + 8 * s, 1);
-    }
-    for (int b = 0; b < NWBUF; ++b) {
-      mbar_init(bar_wready + 8 * b, C::kExpandWarps);  // one arrival per expander warp
-      mbar_init(bar_wfree + 8 * b, 1);
+      mbar_init(bar_ready + 8 * s, 1 + C::kExpandWarps);  // producer + one arrival per expander warp
+      mbar_init(bar_empty + 8 * s, 1);  // one commit; both producers wait on it
+      mbar_init(bar_raw + 8 * s, 2);  // the two producer warps
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(bar_tfull + 8 * a, 1);
@@ -181,9 +208,15 @@ w4a16_kernel(const __grid_constant__ CUtensorMap map_act, const __grid_constant_
     kb1 = min(p.num_kb, kb0 + p.kb_per_split);
   };
 
-  if (warp == 0) {
-    // ------------------------------------------------------------ TMA producer
+  if (role == kProducer || role == kProducerMeta) {
+    // ------------------------------------------------------------ TMA producers
+    // Two warps, because one thread that waits for the stage and issues four copies and two
+    // expect_tx needs more cycles per stage than anything else in the kernel at small M:
+    //   warp 0   packed weights (-> raw[s]) and activations (-> ready[s])
+    //   warp 12  scales and zero points (-> raw[s]); every stage carries them because
+    //            consecutive stages go to different expander warps
     if (lane == 0) {
+      const bool meta = role == kProducerMeta;
       uint32_t stage = 0, phase = 0;
       bool ok = true;
       for (int w = blockIdx.x; w < num_work && ok; w += gridDim.x) {
@@ -196,32 +229,31 @@ w4a16_kernel(const __grid_constant__ CUtensorMap map_act, const __grid_constant_
             ok = false;
             break;
           }
-          const uint32_t full = bar_full + 8 * stage;
           const uint32_t sbase = smem_base + stage * C::kStageBytes;
-          // scales / zero points travel only with the first stage of a k-group (the expanders
-          // keep them in registers until the group changes)
-          const int grp = (kb * kK) / p.group;
-          const bool new_group = kb == kb0 || grp != ((kb - 1) * kK) / p.group;
-          mbar_arrive_expect_tx(full, C::kActBytes + C::kRawBytes +
-                                          (new_group ? C::kScaleBytes + (p.zp ? C::kZpBytes : 0) : 0));
-          tma_load_2d(sbase, &map_act, full, kb * kK, act_row0);
-          tma_load_2d(sbase + C::kActBytes, &map_raw, full, n0 / 8, kb * kK);
-          if (new_group) {
-            tma_load_2d(sbase + C::kMetaOffset, &map_scale, full, n0, grp);
-            if (p.zp) tma_load_2d(sbase + C::kZpOffset, &map_zp, full, n0 / 8, grp);
+          const uint32_t rawb = bar_raw + 8 * stage;
+          if (meta) {
+            const int grp = p.group_shift >= 0 ? (kb >> p.group_shift) : (kb * kK) / p.group;
+            mbar_arrive_expect_tx(rawb, C::kScaleBytes + (p.zp ? C::kZpBytes : 0));
+            tma_load_2d(sbase + C::kMetaOffset, &map_scale, rawb, n0, grp);
+            if (p.zp) tma_load_2d(sbase + C::kZpOffset, &map_zp, rawb, n0 / 8, grp);
+          } else {
+            mbar_arrive_expect_tx(rawb, C::kRawBytes);
+            tma_load_2d(sbase + C::kRawOffset, &map_raw, rawb, n0 / 8, kb * kK);
+            mbar_arrive_expect_tx(bar_ready + 8 * stage, C::kActBytes);
+            tma_load_2d(sbase, &map_act, bar_ready + 8 * stage, kb * kK, act_row0);
           }
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
       }
     }
-  } else if (warp == 1) {
+  } else if (role == kMma) {
     // ------------------------------------------------------------ MMA issuer
     if (lane == 0) {
       // bf16 x bf16; the expanded weights are the MN-major operand (A when swapped, else B)
       const uint32_t idesc = umma_idesc_major(1u, 1u, 128, BN, SWAP ? 1u : 0u, SWAP ? 0u : 1u);
       const uint64_t da0 = smem_desc_k_sw128(smem_base);
-      const uint64_t dw0 = smem_desc_mn_sw128(wbuf_base, (kK / 8) * 1024, 1024);
-      uint32_t stage = 0, phase = 0, wb = 0, wphase = 0;
+      const uint64_t dw0 = smem_desc_mn_sw128(smem_base + C::kWOffset, (kK / 8) * 1024, 1024);
+      uint32_t stage = 0, phase = 0;
       int it = 0;
       bool ok = true;
       for (int w = blockIdx.x; w < num_work && ok; w += gridDim.x, ++it) {
@@ -232,17 +264,16 @@ w4a16_kernel(const __grid_constant__ CUtensorMap map_act, const __grid_constant_
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN;
         for (int kb = kb0; kb < kb1; ++kb) {
-          if (!mbar_wait(bar_full + 8 * stage, phase, abort_flag, p.status, kErrMma) ||
-              !mbar_wait(bar_wready + 8 * wb, wphase, abort_flag, p.status, kErrMma)) {
+          if (!mbar_wait(bar_ready + 8 * stage, phase, abort_flag, p.status, kErrMma)) {
             ok = false;
             break;
           }
           tc_fence_after();
           // activations: K-major, 32 bytes per k-step inside the 128-byte row; weights: MN-major,
           // two 8-k atoms (2048 bytes) per k-step, column blocks 8 atoms apart (descriptors of
-          // stage 0 / buffer 0 are hoisted out of the loop)
-          const uint64_t da = da0 + (uint64_t)(stage * (uint32_t)(C::kStageBytes >> 4));
-          const uint64_t dw = dw0 + (uint64_t)(wb * (uint32_t)(C::kWBufBytes >> 4));
+          // stage 0 are hoisted out of the loop)
+          const uint64_t soff = (uint64_t)(stage * (uint32_t)(C::kStageBytes >> 4));
+          const uint64_t da = da0 + soff, dw = dw0 + soff;
           umma_f16(d_tmem, SWAP ? dw : da, SWAP ? da : dw, idesc, kb != kb0);
 #pragma unroll
           for (int k = 1; k < kK / 16; ++k) {
@@ -250,17 +281,15 @@ w4a16_kernel(const __grid_constant__ CUtensorMap map_act, const __grid_constant_
             umma_f16(d_tmem, SWAP ? w2 : a, SWAP ? a : w2, idesc, 1u);
           }
           umma_commit(bar_empty + 8 * stage);
-          umma_commit(bar_wfree + 8 * wb);
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
-          if (++wb == NWBUF) { wb = 0; wphase ^= 1; }
         }
         if (ok) umma_commit(bar_tfull + 8 * acc);
       }
     }
-  } else if (warp < 6) {
-    // ------------------------------------------------------------ epilogue (warps 2..5)
+  } else if (role == kEpilogue) {
+    // ------------------------------------------------------------ epilogue
     const int q = warp & 3;
-    const int et = threadIdx.x - 64;
+    const int et = q * 32 + lane;
     int it = 0;
     for (int w = blockIdx.x; w < num_work; w += gridDim.x, ++it) {
       int xt, yt, kb0, kb1, split;
@@ -343,16 +372,25 @@ w4a16_kernel(const __grid_constant__ CUtensorMap map_act, const __grid_constant_
       tc_fence_before();
       mbar_arrive(bar_tempty + 8 * acc);
     }
-  } else {
-    // ------------------------------------------------------------ expanders (warps 6..)
-    const int et = threadIdx.x - 192;           // 0 .. kExpandWarps*32-1
-    constexpr int W = C::kRawRowWords;          // packed words per k-row (16 per 128 columns)
-    constexpr int kRowsPerPass = C::kExpandWarps * 32 / W;  // k-rows covered by all threads at once (8 * kSplit)
+  } else if (role == kExpander) {
+    // ------------------------------------------------------------ expanders
+    const int et = (ewarp % C::kExpandWarps) * 32 + lane;  // position inside the group
+    const int my_group = ewarp / C::kExpandWarps;          // the stages this warp takes
+    constexpr int W = C::kRawRowWords;                      // packed words per k-row (16 per 128 columns)
+    constexpr int kRowsPerPass = C::kExpandWarps * 32 / W;  // k-rows covered by the group at once (16)
     constexpr int kPasses = kK / kRowsPerPass;
-    const int ngl = et % W;                     // column group (8 columns) inside the stage's tile
-    const int kr = et / W;                      // first k-row of this thread; then every kRowsPerPass
+    const int ngl = et % W;                                 // column group (8 columns) inside the stage's tile
+    const int kr = et / W;                                  // first k-row of this thread; then every kRowsPerPass
     const bool has_zp = p.zp != nullptr;
-    uint32_t stage = 0, phase = 0, wb = 0, wphase = 0;
+    // Raw tile: row k holds W consecutive words, so a warp reads 32 consecutive words.
+    // Expanded tile: column block b = ngl / 8 (64 columns), 16-byte chunk c = ngl % 8 of the
+    // 128-byte row k % 8 of atom (b, k / 8), chunk XOR-swizzled with the row: the 8 lanes of
+    // a quarter warp write the 8 chunks of one row.
+    const uint32_t krow = kr & 7;
+    const uint32_t raw_off = C::kRawOffset + (kr * W + ngl) * 4;
+    const uint32_t wt_off = C::kWOffset + ((ngl >> 3) * (kK / 8) + (kr >> 3)) * 1024 + krow * 128 + (((ngl & 7) ^ krow) << 4);
+    uint32_t stage = 0, phase = 0;
+    int turn = 0;  // the group whose stage this is
     bool ok = true;
     for (int w = blockIdx.x; w < num_work && ok; w += gridDim.x) {
       int xt, yt, kb0, kb1, split;
@@ -360,49 +398,42 @@ w4a16_kernel(const __grid_constant__ CUtensorMap map_act, const __grid_constant_
       GroupRegs g;
       int g_cur = -1;
       for (int kb = kb0; kb < kb1; ++kb) {
-        if (!mbar_wait(bar_full + 8 * stage, phase, abort_flag, p.status, kErrExpand) ||
-            !mbar_wait(bar_wfree + 8 * wb, wphase ^ 1, abort_flag, p.status, kErrExpand)) {
-          ok = false;
-          break;
-        }
-        const uint32_t sbase = smem_base + stage * C::kStageBytes;
-        const int grp = (kb * kK) / p.group;
-        if (grp != g_cur) {  // this stage's ring slot holds the group's scales / zero points
-          uint4 sv;
-          asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
-                       : "=r"(sv.x), "=r"(sv.y), "=r"(sv.z), "=r"(sv.w)
-                       : "r"(sbase + C::kMetaOffset + ngl * 16));
-          const uint32_t zw = has_zp ? lds32(sbase + C::kZpOffset + ngl * 4) : 0u;
-          make_group(g, sv, zw, has_zp);
-          g_cur = grp;
-        }
-        // Raw tile: row k holds W consecutive words, so a warp reads 32 consecutive words.
-        // Expanded tile: column block b = ngl / 8 (64 columns), 16-byte chunk c = ngl % 8 of the
-        // 128-byte row k % 8 of atom (b, k / 8), chunk XOR-swizzled with the row: the 8 lanes of
-        // a quarter warp write the 8 chunks of one row.
-        const uint32_t raw = sbase + C::kActBytes + (kr * W + ngl) * 4;
-        const uint32_t krow = kr & 7;
-        const uint32_t wt = wbuf_base + wb * C::kWBufBytes + ((ngl >> 3) * (kK / 8) + (kr >> 3)) * 1024 + krow * 128 +
-                            (((ngl & 7) ^ krow) << 4);
-        uint32_t wv[kPasses];
+        if (turn == my_group) {
+          if (!mbar_wait(bar_raw + 8 * stage, phase, abort_flag, p.status, kErrExpand)) {
+            ok = false;
+            break;
+          }
+          const uint32_t sbase = smem_base + stage * C::kStageBytes;
+          const int grp = p.group_shift >= 0 ? (kb >> p.group_shift) : (kb * kK) / p.group;
+          if (grp != g_cur) {  // scales / zero points stay in registers while the k-group lasts
+            uint4 sv;
+            asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
+                         : "=r"(sv.x), "=r"(sv.y), "=r"(sv.z), "=r"(sv.w)
+                         : "r"(sbase + C::kMetaOffset + ngl * 16));
+            const uint32_t zw = has_zp ? lds32(sbase + C::kZpOffset + ngl * 4) : 0u;
+            make_group(g, sv, zw, has_zp);
+            g_cur = grp;
+          }
+          uint32_t wv[kPasses];
 #pragma unroll
-        for (int j = 0; j < kPasses; ++j) wv[j] = lds32(raw + j * kRowsPerPass * W * 4);
+          for (int j = 0; j < kPasses; ++j) wv[j] = lds32(sbase + raw_off + j * kRowsPerPass * W * 4);
 #pragma unroll
-        for (int j = 0; j < kPasses; ++j) {
-          // pair i = columns (i, i+4): stored in that order, the epilogue restores the column order
-          sts128(wt + j * (kRowsPerPass / 8) * 1024, bf2_mul(bf2_sub(nib_pair(wv[j], 0), g.zr[0]), g.sp[0]),
-                 bf2_mul(bf2_sub(nib_pair(wv[j], 1), g.zr[1]), g.sp[1]),
-                 bf2_mul(bf2_sub(nib_pair(wv[j], 2), g.zr[2]), g.sp[2]),
-                 bf2_mul(bf2_sub(nib_pair(wv[j], 3), g.zr[3]), g.sp[3]));
+          for (int j = 0; j < kPasses; ++j) {
+            // pair i = columns (i, i+4): stored in that order, the epilogue restores the column order
+            sts128(sbase + wt_off + j * (kRowsPerPass / 8) * 1024, bf2_mul(bf2_sub(nib_pair(wv[j], 0), g.zr[0]), g.sp[0]),
+                   bf2_mul(bf2_sub(nib_pair(wv[j], 1), g.zr[1]), g.sp[1]),
+                   bf2_mul(bf2_sub(nib_pair(wv[j], 2), g.zr[2]), g.sp[2]),
+                   bf2_mul(bf2_sub(nib_pair(wv[j], 3), g.zr[3]), g.sp[3]));
+          }
+          // every thread publishes its own writes to the async proxy (the tensor core's view of
+          // shared memory); the warp then arrives once -- an arrival per thread would put hundreds
+          // of serialised shared-memory atomics on the barrier every stage
+          fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(bar_ready + 8 * stage);
         }
-        // every thread publishes its own writes to the async proxy (the tensor core's view of
-        // shared memory); the warp then arrives once -- an arrival per thread would put hundreds
-        // of serialised shared-memory atomics on the barrier every stage
-        fence_proxy_async_smem();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(bar_wready + 8 * wb);
+        if (++turn == C::kExpandGroups) turn = 0;
         if (++stage == STAGES) { stage = 0; phase ^= 1; }
-        if (++wb == NWBUF) { wb = 0; wphase ^= 1; }
       }
     }
   }
@@ -455,7 +486,16 @@ struct PairCfg {
   static constexpr int kTotal = kBarOffset + kNumBars * 8 + 16;
   static constexpr int kExpandWarps = 8;  // per stage
   static constexpr int kExpandGroups = GROUPS;
-  static constexpr int kThreads = 32 * (6 + kExpandWarps * kExpandGroups);
+  // Warp roles are placed by scheduler (warp % 4): the producer (warp 0) and the MMA issuer
+  // (warp 4) share scheduler 0 with no expander warp; their per-stage instruction chains
+  // (barrier wait, copies, MMAs, commit) run 25-40 % faster than when they compete with
+  // expander warps for issue slots and the shared-memory instruction queue.  Epilogue: warps
+  // 1, 2, 3 and 8 (TMEM lane quarters 1, 2, 3, 0; asleep during the main loop).  Expanders: the
+  // warps >= 5 with warp % 4 != 0, in order.  Other warps of scheduler 0 idle.
+  static constexpr int kLastExpander = kExpandWarps * kExpandGroups - 1;
+  static constexpr int kWarps = 5 + (kLastExpander / 3) * 4 + kLastExpander % 3 + 1;
+  static_assert(kWarps <= 32, "too many expander warps for one CTA");
+  static constexpr int kThreads = 32 * kWarps;
   static_assert(kWOffset % 1024 == 0 && kStageBytes % 1024 == 0, "swizzled tiles need 1024-byte alignment");
 };
 
@@ -477,6 +517,13 @@ w4a16_pair_kernel(const __grid_constant__ CUtensorMap map_act, const __grid_cons
   const uint32_t bar_ready = smem_u32(bars), bar_empty = bar_ready + 8 * STAGES, bar_raw = bar_empty + 8 * STAGES;
   const uint32_t bar_tfull = bar_raw + 8 * STAGES, bar_tempty = bar_tfull + 16;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  enum { kProducer, kMma, kEpilogue, kExpander, kIdle };
+  const int ewarp = ((warp - 5) >> 2) * 3 + ((warp & 3) - 1);  // expander warp index (valid when that role)
+  const int role = warp == 0 ? kProducer
+                   : warp == 4 ? kMma
+                   : (warp < 4 || warp == 8) ? kEpilogue
+                   : ((warp & 3) != 0 && ewarp < C::kExpandWarps * C::kExpandGroups) ? kExpander
+                                                                                      : kIdle;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) {
@@ -511,7 +558,7 @@ w4a16_pair_kernel(const __grid_constant__ CUtensorMap map_act, const __grid_cons
   const int num_tiles = p.x_tiles * p.y_tiles;  // 256-token x 256-column tiles
   const int num_kb = p.num_kb;
 
-  if (warp == 0) {
+  if (role == kProducer) {
     // ------------------------------------------------------------ TMA producer
     if (lane == 0) {
       uint32_t stage = 0, phase = 0;
@@ -527,7 +574,7 @@ w4a16_pair_kernel(const __grid_constant__ CUtensorMap map_act, const __grid_cons
             break;
           }
           const uint32_t sbase = smem_base + stage * C::kStageBytes;
-          const int grp = (kb * kK) / p.group;
+          const int grp = p.group_shift >= 0 ? (kb >> p.group_shift) : (kb * kK) / p.group;
           // packed weights and scales first: the expanders are the longer chain
           const uint32_t rawb = bar_raw + 8 * stage;
           mbar_arrive_expect_tx(rawb, C::kRawBytes + meta_bytes);
@@ -541,7 +588,7 @@ w4a16_pair_kernel(const __grid_constant__ CUtensorMap map_act, const __grid_cons
         }
       }
     }
-  } else if (warp == 1) {
+  } else if (role == kMma) {
     // ------------------------------------------------------------ MMA issuer (even CTA)
     if (lane == 0 && rank == 0) {
       const uint32_t idesc = umma_idesc_major(1u, 1u, 256, BN, 0u, 1u);
@@ -573,10 +620,10 @@ w4a16_pair_kernel(const __grid_constant__ CUtensorMap map_act, const __grid_cons
         if (ok) umma_commit_pair_both(bar_tfull + 8 * acc);
       }
     }
-  } else if (warp < 6) {
-    // ------------------------------------------------------------ epilogue (warps 2..5)
+  } else if (role == kEpilogue) {
+    // ------------------------------------------------------------ epilogue
     const int q = warp & 3;
-    const int et = threadIdx.x - 64;
+    const int et = q * 32 + lane;
     int it = 0;
     for (int tile = pair; tile < num_tiles; tile += num_pairs, ++it) {
       const int xt = tile % p.x_tiles, yt = tile / p.x_tiles;
@@ -630,11 +677,11 @@ w4a16_pair_kernel(const __grid_constant__ CUtensorMap map_act, const __grid_cons
       tc_fence_before();
       mbar_arrive_remote((bar_tempty + 8 * acc) & kPeerBitMask);  // the even CTA's barrier
     }
-  } else {
-    // ------------------------------------------------------------ expanders (warps 6..)
+  } else if (role == kExpander) {
+    // ------------------------------------------------------------ expanders
     // this CTA's 128 columns: 8 warps per stage, 4 packed words per thread
-    const int et = (threadIdx.x - 192) % (C::kExpandWarps * 32);
-    const int my_group = (threadIdx.x - 192) / (C::kExpandWarps * 32);
+    const int et = (ewarp % C::kExpandWarps) * 32 + lane;
+    const int my_group = ewarp / C::kExpandWarps;
     constexpr int W = 16;
     constexpr int kRowsPerPass = C::kExpandWarps * 32 / W;  // 16
     constexpr int kPasses = kK / kRowsPerPass;              // 4
@@ -656,7 +703,7 @@ w4a16_pair_kernel(const __grid_constant__ CUtensorMap map_act, const __grid_cons
             break;
           }
           const uint32_t sbase = smem_base + stage * C::kStageBytes;
-          const int grp = (kb * kK) / p.group;
+          const int grp = p.group_shift >= 0 ? (kb >> p.group_shift) : (kb * kK) / p.group;
           if (grp != g_cur) {
             uint4 sv;
             asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
@@ -748,15 +795,15 @@ __global__ void __launch_bounds__(256) splitk_reduce_kernel(const float* __restr
   }
 }
 
-template <int BN, bool SWAP, int STAGES, int NWBUF>
+template <int BN, bool SWAP, int STAGES, int GROUPS, int AR = 0, int EW = 0>
 static int launch(const CUtensorMap& ma, const CUtensorMap& mr, const CUtensorMap& ms, const CUtensorMap& mz, const Params& p,
                   cudaStream_t st) {
-  using C = Cfg<BN, SWAP, STAGES, NWBUF>;
+  using C = Cfg<BN, SWAP, STAGES, GROUPS, AR, EW>;
   constexpr int smem = C::kTotal + 1024;
   static_assert(smem <= 227 * 1024, "shared memory budget");
   // TMEM: CTAs that share an SM must never ask for more than 512 columns together
   static_assert(C::kTmemCols * (227 * 1024 / smem) <= 512, "TMEM over-subscription");
-  auto kern = w4a16_kernel<BN, SWAP, STAGES, NWBUF>;
+  auto kern = w4a16_kernel<BN, SWAP, STAGES, GROUPS, AR, EW>;
   static std::atomic<int> configured[kMaxDevices];
   const int dev = current_device_index();
   if (dev < 0) return B200Q_ERR_CUDA;
@@ -778,11 +825,18 @@ static int launch(const CUtensorMap& ma, const CUtensorMap& mr, const CUtensorMa
 // fp32 workspace that goes with it.
 static int w4a16_splits(int64_t M, int64_t N, int64_t K) {
   if (M > 128) return 1;
-  const int64_t tiles = ((N + 127) / 128) * ((M + 127) / 128);
+  // 128-token x 256-column tiles; the split count that minimises the busiest CTA's k-blocks
+  // (plus a few per work item for its pipeline fill and its partial-tile epilogue)
+  const int64_t tiles = (N + 255) / 256;
   const int64_t num_kb = K / w4::kK;
-  int s = 1;
-  while (tiles * s < 2 * kNumSMs && s * 2 <= num_kb / 4 && s < 16) s *= 2;  // >= 4 stages of k per split
-  const int64_t per = (num_kb + s - 1) / s;
+  int64_t best_cost = 0;
+  int best = 1;
+  for (int s = 1; s <= 16 && s * 4 <= num_kb; ++s) {
+    const int64_t rounds = (tiles * s + kNumSMs - 1) / kNumSMs;
+    const int64_t cost = rounds * ((num_kb + s - 1) / s + 4);
+    if (s == 1 || cost < best_cost) { best_cost = cost; best = s; }
+  }
+  const int64_t per = (num_kb + best - 1) / best;
   return (int)((num_kb + per - 1) / per);  // drop splits that would be empty
 }
 
@@ -803,6 +857,12 @@ int w4a16_gemm_impl(const void* x, int64_t ldx, const int32_t* qweight, const vo
   p.scale = static_cast<const __nv_bfloat16*>(scale);
   p.zp = zp_kind == B200Q_ZP_PACKED ? zp : nullptr;
   p.out = out; p.partial = nullptr; p.M = M; p.N = N; p.K = K; p.ldo = ldo; p.group = (int)group;
+  {
+    const int64_t gk = group / w4::kK;
+    p.group_shift = -1;
+    for (int sh = 0; sh < 24; ++sh)
+      if (gk == (1ll << sh)) p.group_shift = sh;
+  }
   p.out_dtype = out_dtype; p.num_kb = (int)(K / w4::kK);
   p.status = device_status_ptr();
   if (!p.status) return B200Q_ERR_CUDA;
@@ -852,8 +912,7 @@ int w4a16_gemm_impl(const void* x, int64_t ldx, const int32_t* qweight, const vo
     rc = make_tma_map_2d(&ma, x, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, K, M, ldx * 2, w4::kK, 128, CU_TENSOR_MAP_SWIZZLE_128B);
     if (rc) return rc;
     static const int pair_cfg = std::getenv("B200Q_W4A16_PAIR_CFG") ? std::atoi(std::getenv("B200Q_W4A16_PAIR_CFG")) : 0;
-    if (pair_cfg == 1) rc = w4::launch_pair<6, 3>(ma, mr1, ms1, mz1, pp, st);
-    else if (pair_cfg == 2) rc = w4::launch_pair<5, 2>(ma, mr1, ms1, mz1, pp, st);
+    if (pair_cfg == 2) rc = w4::launch_pair<5, 2>(ma, mr1, ms1, mz1, pp, st);
     else rc = w4::launch_pair<6, 2>(ma, mr1, ms1, mz1, pp, st);
     if (rc != B200Q_ERR_UNSUPPORTED) return rc;
   }
@@ -863,19 +922,47 @@ int w4a16_gemm_impl(const void* x, int64_t ldx, const int32_t* qweight, const vo
     p.y_tiles = (int)((N + bn - 1) / bn);
     rc = make_tma_map_2d(&ma, x, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, K, M, ldx * 2, w4::kK, 128, CU_TENSOR_MAP_SWIZZLE_128B);
     if (rc) return rc;
-    if (bn == 256) rc = w4::launch<256, false, 4, 3>(ma, mr, ms, mz, p, st);
-    else rc = w4::launch<128, false, 5, 4>(ma, mr, ms, mz, p, st);
+    if (bn == 256) rc = w4::launch<256, false, 3, 1>(ma, mr, ms, mz, p, st);
+    else rc = w4::launch<128, false, 6, 2>(ma, mr, ms, mz, p, st);
+  } else if (std::getenv("B200Q_W4A16_SWAP") == nullptr) {
+    // small M, token-major with a narrow activation tile: 128 x 256 MMAs cover twice the weight
+    // columns per instruction of the weight-major form, whose issue rate is what bounds it
+    p.x_tiles = 1;
+    p.y_tiles = (int)((N + 255) / 256);
+    CUtensorMap mr2, ms2, mz2;
+    rc = make_tma_map_2d(&mr2, qweight, CU_TENSOR_MAP_DATA_TYPE_INT32, 4, N / 8, K, (N / 8) * 4, 32, w4::kK,
+                         CU_TENSOR_MAP_SWIZZLE_NONE);
+    if (rc) return rc;
+    rc = make_tma_map_2d(&ms2, scale, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, N, K / group, N * 2, 256, 1, CU_TENSOR_MAP_SWIZZLE_NONE);
+    if (rc) return rc;
+    mz2 = ms2;
+    if (p.zp) {
+      rc = make_tma_map_2d(&mz2, p.zp, CU_TENSOR_MAP_DATA_TYPE_INT32, 4, N / 8, K / group, (N / 8) * 4, 32, 1,
+                           CU_TENSOR_MAP_SWIZZLE_NONE);
+      if (rc) return rc;
+    }
+    const int ar = M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : 128;
+    rc = make_tma_map_2d(&ma, x, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, K, M, ldx * 2, w4::kK, ar, CU_TENSOR_MAP_SWIZZLE_128B);
+    if (rc) return rc;
+    switch (ar) {
+      case 16: rc = w4::launch<256, false, 5, 2, 16, 8>(ma, mr2, ms2, mz2, p, st); break;
+      case 32: rc = w4::launch<256, false, 5, 2, 32, 8>(ma, mr2, ms2, mz2, p, st); break;
+      case 64: rc = w4::launch<256, false, 4, 2, 64, 8>(ma, mr2, ms2, mz2, p, st); break;
+      default: rc = w4::launch<256, false, 3, 1>(ma, mr2, ms2, mz2, p, st); break;
+    }
   } else {
     p.x_tiles = (int)((N + 127) / 128);
     const int bn = M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : 128;
+    p.splits = 1;  // (weight-major form kept for comparison only)
+    p.kb_per_split = p.num_kb;
     p.y_tiles = (int)((M + bn - 1) / bn);
     rc = make_tma_map_2d(&ma, x, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, K, M, ldx * 2, w4::kK, bn, CU_TENSOR_MAP_SWIZZLE_128B);
     if (rc) return rc;
     switch (bn) {
-      case 16: rc = w4::launch<16, true, 6, 3>(ma, mr, ms, mz, p, st); break;
-      case 32: rc = w4::launch<32, true, 6, 3>(ma, mr, ms, mz, p, st); break;
-      case 64: rc = w4::launch<64, true, 6, 3>(ma, mr, ms, mz, p, st); break;
-      default: rc = w4::launch<128, true, 5, 3>(ma, mr, ms, mz, p, st); break;
+      case 16: rc = w4::launch<16, true, 8, 2>(ma, mr, ms, mz, p, st); break;
+      case 32: rc = w4::launch<32, true, 8, 2>(ma, mr, ms, mz, p, st); break;
+      case 64: rc = w4::launch<64, true, 7, 2>(ma, mr, ms, mz, p, st); break;
+      default: rc = w4::launch<128, true, 6, 2>(ma, mr, ms, mz, p, st); break;
     }
   }
   if (rc) return rc;
@@ -932,4 +1019,5 @@ int w4a16_gemm_noalloc_impl(const void* x, int64_t ldx, const int32_t* qweight, 
 size_t w4a16_noalloc_max_bytes_impl() { return kStaticScratchBytes; }
 
 }  // namespace b200q
+
 
