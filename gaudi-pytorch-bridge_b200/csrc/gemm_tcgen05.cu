@@ -44,6 +44,7 @@ struct TcGemmParams {
   int a_fmt_bits, b_fmt_bits;  // 0 = e4m3, 1 = e5m2 (lane-side, column-side)
   int x_mn, y_mn;              // 1 = that operand is stored MN-major ([K][rows], rows contiguous)
   int* status;                 // device status word (bounded waits report here)
+  int no_probe;                // 1 = the MMA issuer ignores its look-ahead barrier probe (for comparison)
 };
 
 template <int BN, int STAGES>
@@ -292,7 +293,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
       const uint64_t yd0 = p.y_mn ? smem_desc_mn_sw128(smem_base + L::kXBytes, kBlockK * 128, 1024)
                                   : smem_desc_k_sw128(smem_base + L::kXBytes);
       const uint32_t xstep = p.x_mn ? (4096u >> 4) : (kUmmaK >> 4), ystep = p.y_mn ? (4096u >> 4) : (kUmmaK >> 4);
-      uint32_t stage = 0, phase = 0;
+      uint32_t stage = 0, phase = 0, ready = 0;
       int it = 0;
       bool ok = true;
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++it) {
@@ -301,18 +302,29 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN;
         for (int kb = 0; kb < num_kb; ++kb) {
-          if (!mbar_wait(bar_full + 8 * stage, phase, abort_flag, p.status, kErrMma)) {
+          if (!ready && !mbar_wait(bar_full + 8 * stage, phase, abort_flag, p.status, kErrMma)) {
             ok = false;
             break;
           }
           tc_fence_after();
           const uint64_t xd = xd0 + (uint64_t)(stage * (uint32_t)(L::kStageBytes >> 4));
           const uint64_t yd = yd0 + (uint64_t)(stage * (uint32_t)(L::kStageBytes >> 4));
-          umma_f8(d_tmem, xd, yd, idesc, kb != 0);
+          // the stage's four MMAs and its commit (the stage is reusable once they have read it),
+          // with a probe of the next stage's barrier issued before and read after them
+          const uint32_t nstage = stage + 1 == STAGES ? 0 : stage + 1;
+          const uint32_t nphase = nstage == 0 ? phase ^ 1 : phase;
+          static_assert(kBlockK / kUmmaK == 4, "umma_stage4_probe issues 4 MMAs");
+          if (p.no_probe) {
+            umma_f8(d_tmem, xd, yd, idesc, kb != 0);
 #pragma unroll
-          for (int k = 1; k < kBlockK / kUmmaK; ++k) umma_f8(d_tmem, xd + k * xstep, yd + k * ystep, idesc, 1u);
-          umma_commit(bar_empty + 8 * stage);  // stage reusable once these MMAs have read it
-          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+            for (int k = 1; k < kBlockK / kUmmaK; ++k) umma_f8(d_tmem, xd + k * xstep, yd + k * ystep, idesc, 1u);
+            umma_commit(bar_empty + 8 * stage);
+          } else {
+            ready = umma_stage4_probe<false, false>(d_tmem, xd, yd, idesc, kb != 0, bar_empty + 8 * stage,
+                                                    bar_full + 8 * nstage, nphase, xstep, ystep);
+          }
+          stage = nstage;
+          phase = nphase;
         }
         if (ok) umma_commit(bar_tfull + 8 * acc);  // accumulator complete
       }
@@ -464,7 +476,8 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
       const uint32_t idesc = umma_idesc(p.a_fmt_bits, p.b_fmt_bits, 2 * kBlockX, BN);
       // hoisted descriptors: see the single-CTA kernel
       const uint64_t xd0 = smem_desc_k_sw128(smem_base), yd0 = smem_desc_k_sw128(smem_base + L::kXBytes);
-      uint32_t stage = 0, phase = 0;
+      uint32_t stage = 0, phase = 0, ready = 0;
+      const bool no_probe = p.no_probe != 0;
       int it = 0;
       bool ok = true;
       for (int tile = pair; tile < num_tiles && ok; tile += num_pairs, ++it) {
@@ -473,19 +486,29 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN;
         for (int kb = 0; kb < num_kb; ++kb) {
-          if (!mbar_wait(bar_full + 8 * stage, phase, abort_flag, p.status, kErrMma)) {
+          if (!ready && !mbar_wait(bar_full + 8 * stage, phase, abort_flag, p.status, kErrMma)) {
             ok = false;
             break;
           }
           tc_fence_after();
           const uint64_t xd = xd0 + (uint64_t)(stage * (uint32_t)(L::kStageBytes >> 4));
           const uint64_t yd = yd0 + (uint64_t)(stage * (uint32_t)(L::kStageBytes >> 4));
-          umma_f8_pair(d_tmem, xd, yd, idesc, kb != 0);
+          // the stage's MMAs and commit, with a probe of the next stage's barrier around them
+          const uint32_t nstage = stage + 1 == STAGES ? 0 : stage + 1;
+          const uint32_t nphase = nstage == 0 ? phase ^ 1 : phase;
+          static_assert(kBlockK / kUmmaK == 4 && (kUmmaK >> 4) == 2, "umma_stage4_probe issues 4 MMAs 32 bytes apart");
+          if (no_probe) {
+            umma_f8_pair(d_tmem, xd, yd, idesc, kb != 0);
 #pragma unroll
-          for (int k = 1; k < kBlockK / kUmmaK; ++k)
-            umma_f8_pair(d_tmem, xd + k * (kUmmaK >> 4), yd + k * (kUmmaK >> 4), idesc, 1u);
-          umma_commit_pair_both(bar_empty + 8 * stage);
-          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+            for (int k = 1; k < kBlockK / kUmmaK; ++k)
+              umma_f8_pair(d_tmem, xd + k * (kUmmaK >> 4), yd + k * (kUmmaK >> 4), idesc, 1u);
+            umma_commit_pair_both(bar_empty + 8 * stage);
+          } else {
+            ready = umma_stage4_probe<false, true>(d_tmem, xd, yd, idesc, kb != 0, bar_empty + 8 * stage,
+                                                   bar_full + 8 * nstage, nphase, 2, 2);
+          }
+          stage = nstage;
+          phase = nphase;
         }
         if (ok) umma_commit_pair_both(bar_tfull + 8 * acc);
       }
@@ -617,6 +640,8 @@ int gemm_tcgen05_launch(const GemmParams& g, cudaStream_t st) {
 
   TcGemmParams tp;
   tp.g = g;
+  static const bool no_probe = std::getenv("B200Q_GEMM_NO_PROBE") != nullptr;
+  tp.no_probe = no_probe;
   tp.status = device_status_ptr();
   if (!tp.status) return B200Q_ERR_CUDA;
   tp.num_kb = (int)((g.K + kBlockK - 1) / kBlockK);

@@ -213,6 +213,59 @@ __device__ __forceinline__ void umma_f8_pair(uint32_t d_tmem, uint64_t adesc, ui
       "}\n" ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
       : "memory");
 }
+// One ring stage in a single instruction sequence: a non-blocking probe of the NEXT stage's
+// barrier is issued first and its result is read only after the stage's four MMAs (operand
+// descriptors advancing by astep / bstep 16-byte units) and its commit have been issued.  A
+// probe that succeeds lets the issuer skip the blocking wait of the next stage: the round trip
+// of the wait -- a few hundred cycles when shared memory is busy -- then overlaps the MMA issue
+// instead of adding to it.  Returns 1 when the next stage is already complete.
+// F16: kind::f16 (bf16 operands), else kind::f8f6f4.  PAIR: cta_group::2 with a commit
+// multicast to both CTAs of the pair, else cta_group::1.
+template <bool F16, bool PAIR>
+__device__ __forceinline__ uint32_t umma_stage4_probe(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                                      uint32_t accumulate, uint32_t commit_bar, uint32_t next_bar,
+                                                      uint32_t next_parity, uint64_t astep, uint64_t bstep) {
+  uint32_t ready;
+#define B200Q_MMA_OP(G, KIND) "tcgen05.mma.cta_group::" G ".kind::" KIND " "
+#define B200Q_STAGE4(G, KIND, COMMIT)                                                    \
+  asm volatile(                                                                          \
+      "{\n"                                                                              \
+      ".reg .pred p, q, t;\n"                                                            \
+      ".reg .b64 a1, b1, a2, b2, a3, b3;\n"                                              \
+      ".reg .b16 m;\n"                                                                   \
+      "mbarrier.test_wait.parity.shared::cta.b64 q, [%7], %8;\n"                         \
+      "setp.ne.b32 p, %5, 0;\n"                                                          \
+      "setp.eq.b32 t, 0, 0;\n"                                                           \
+      "add.u64 a1, %2, %9;\n"                                                            \
+      "add.u64 b1, %3, %10;\n"                                                           \
+      "add.u64 a2, a1, %9;\n"                                                            \
+      "add.u64 b2, b1, %10;\n"                                                           \
+      "add.u64 a3, a2, %9;\n"                                                            \
+      "add.u64 b3, b2, %10;\n"                                                           \
+      B200Q_MMA_OP(G, KIND) "[%1], %2, %3, %4, p;\n"                                     \
+      B200Q_MMA_OP(G, KIND) "[%1], a1, b1, %4, t;\n"                                     \
+      B200Q_MMA_OP(G, KIND) "[%1], a2, b2, %4, t;\n"                                     \
+      B200Q_MMA_OP(G, KIND) "[%1], a3, b3, %4, t;\n"                                     \
+      "mov.b16 m, 3;\n"                                                                  \
+      COMMIT                                                                             \
+      "selp.u32 %0, 1, 0, q;\n"                                                          \
+      "}\n"                                                                              \
+      : "=r"(ready)                                                                      \
+      : "r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate), "r"(commit_bar), "r"(next_bar), \
+        "r"(next_parity), "l"(astep), "l"(bstep)                                         \
+      : "memory")
+#define B200Q_COMMIT_PAIR "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%6], m;\n"
+#define B200Q_COMMIT_ONE "tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%6];\n"
+  if constexpr (PAIR && !F16) B200Q_STAGE4("2", "f8f6f4", B200Q_COMMIT_PAIR);
+  else if constexpr (PAIR && F16) B200Q_STAGE4("2", "f16", B200Q_COMMIT_PAIR);
+  else if constexpr (!PAIR && !F16) B200Q_STAGE4("1", "f8f6f4", B200Q_COMMIT_ONE);
+  else B200Q_STAGE4("1", "f16", B200Q_COMMIT_ONE);
+#undef B200Q_COMMIT_ONE
+#undef B200Q_COMMIT_PAIR
+#undef B200Q_STAGE4
+#undef B200Q_MMA_OP
+  return ready;
+}
 __device__ __forceinline__ void umma_f16_pair(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
                                               uint32_t accumulate) {
   asm volatile(

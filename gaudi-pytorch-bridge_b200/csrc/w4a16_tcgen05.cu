@@ -253,7 +253,7 @@ w4a16_kernel(const __grid_constant__ CUtensorMap map_act, const __grid_constant_
       const uint32_t idesc = umma_idesc_major(1u, 1u, 128, BN, SWAP ? 1u : 0u, SWAP ? 0u : 1u);
       const uint64_t da0 = smem_desc_k_sw128(smem_base);
       const uint64_t dw0 = smem_desc_mn_sw128(smem_base + C::kWOffset, (kK / 8) * 1024, 1024);
-      uint32_t stage = 0, phase = 0;
+      uint32_t stage = 0, phase = 0, ready = 0;
       int it = 0;
       bool ok = true;
       for (int w = blockIdx.x; w < num_work && ok; w += gridDim.x, ++it) {
@@ -264,24 +264,26 @@ w4a16_kernel(const __grid_constant__ CUtensorMap map_act, const __grid_constant_
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN;
         for (int kb = kb0; kb < kb1; ++kb) {
-          if (!mbar_wait(bar_ready + 8 * stage, phase, abort_flag, p.status, kErrMma)) {
+          if (!ready && !mbar_wait(bar_ready + 8 * stage, phase, abort_flag, p.status, kErrMma)) {
             ok = false;
             break;
           }
           tc_fence_after();
           // activations: K-major, 32 bytes per k-step inside the 128-byte row; weights: MN-major,
           // two 8-k atoms (2048 bytes) per k-step, column blocks 8 atoms apart (descriptors of
-          // stage 0 are hoisted out of the loop)
+          // stage 0 are hoisted out of the loop).  Four MMAs and the commit in one sequence, with
+          // a probe of the next stage's barrier issued before and read after them.
           const uint64_t soff = (uint64_t)(stage * (uint32_t)(C::kStageBytes >> 4));
           const uint64_t da = da0 + soff, dw = dw0 + soff;
-          umma_f16(d_tmem, SWAP ? dw : da, SWAP ? da : dw, idesc, kb != kb0);
-#pragma unroll
-          for (int k = 1; k < kK / 16; ++k) {
-            const uint64_t a = da + k * (kUmmaKBytes >> 4), w2 = dw + k * (2048 >> 4);
-            umma_f16(d_tmem, SWAP ? w2 : a, SWAP ? a : w2, idesc, 1u);
-          }
-          umma_commit(bar_empty + 8 * stage);
-          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+          const uint32_t nstage = stage + 1 == STAGES ? 0 : stage + 1;
+          const uint32_t nphase = nstage == 0 ? phase ^ 1 : phase;
+          static_assert(kK / 16 == 4, "umma_stage4_probe issues 4 MMAs");
+          constexpr uint64_t kActStep = kUmmaKBytes >> 4, kWStep = 2048 >> 4;
+          ready = umma_stage4_probe<true, false>(d_tmem, SWAP ? dw : da, SWAP ? da : dw, idesc, kb != kb0,
+                                                 bar_empty + 8 * stage, bar_ready + 8 * nstage, nphase,
+                                                 SWAP ? kWStep : kActStep, SWAP ? kActStep : kWStep);
+          stage = nstage;
+          phase = nphase;
         }
         if (ok) umma_commit(bar_tfull + 8 * acc);
       }
@@ -594,7 +596,7 @@ w4a16_pair_kernel(const __grid_constant__ CUtensorMap map_act, const __grid_cons
       const uint32_t idesc = umma_idesc_major(1u, 1u, 256, BN, 0u, 1u);
       const uint64_t da0 = smem_desc_k_sw128(smem_base);
       const uint64_t dw0 = smem_desc_mn_sw128(smem_base + C::kWOffset, (kK / 8) * 1024, 1024);
-      uint32_t stage = 0, phase = 0;
+      uint32_t stage = 0, phase = 0, ready = 0;
       int it = 0;
       bool ok = true;
       for (int tile = pair; tile < num_tiles && ok; tile += num_pairs, ++it) {
@@ -603,19 +605,22 @@ w4a16_pair_kernel(const __grid_constant__ CUtensorMap map_act, const __grid_cons
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN;
         for (int kb = 0; kb < num_kb; ++kb) {
-          if (!mbar_wait(bar_ready + 8 * stage, phase, abort_flag, p.status, kErrMma)) {
+          if (!ready && !mbar_wait(bar_ready + 8 * stage, phase, abort_flag, p.status, kErrMma)) {
             ok = false;
             break;
           }
           tc_fence_after();
           const uint64_t soff = (uint64_t)(stage * (uint32_t)(C::kStageBytes >> 4));
           const uint64_t da = da0 + soff, dw = dw0 + soff;
-          umma_f16_pair(d_tmem, da, dw, idesc, kb != 0);
-#pragma unroll
-          for (int k = 1; k < kK / 16; ++k)
-            umma_f16_pair(d_tmem, da + k * (kUmmaKBytes >> 4), dw + k * (2048 >> 4), idesc, 1u);
-          umma_commit_pair_both(bar_empty + 8 * stage);
-          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+          // four MMAs and the commit in one sequence, with a probe of the next stage's barrier
+          // issued before and read after them
+          const uint32_t nstage = stage + 1 == STAGES ? 0 : stage + 1;
+          const uint32_t nphase = nstage == 0 ? phase ^ 1 : phase;
+          static_assert(kK / 16 == 4, "umma_stage4_probe issues 4 MMAs");
+          ready = umma_stage4_probe<true, true>(d_tmem, da, dw, idesc, kb != 0, bar_empty + 8 * stage,
+                                                bar_ready + 8 * nstage, nphase, kUmmaKBytes >> 4, 2048 >> 4);
+          stage = nstage;
+          phase = nphase;
         }
         if (ok) umma_commit_pair_both(bar_tfull + 8 * acc);
       }
