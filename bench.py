@@ -33,13 +33,13 @@ M_, K_, N_ = 4096, 4096, 14336
 # `ncu --set full` captures summarised under profiles/ (same shapes as the workloads below).
 # Traffic below the algorithmic bytes means part of the output was still in L2 when the kernel ended.
 NCU_DRAM_TRAFFIC_BYTES = {
-    "gemm": 149.1e6,         # profiles/fp8_gemm_pair_kernel_4096x14336x4096.md
+    "gemm": 149.5e6,         # profiles/fp8_gemm_pair_kernel_4096x14336x4096.md
     "gemm_m16": 59.0e6,      # profiles/fp8_gemm_swap_kernel_m16_14336x4096.md
     "cast_rne": 163.5e6,     # profiles/cast_bf16_rne_fast_kernel_64M.md
     "cast_sr": 166.9e6,      # profiles/cast_bf16_sr_fast_kernel_64M.md
     "uncast": 145.6e6,       # profiles/cast_from_fp8_kernel_64M.md
     "dequant": 112.5e6,      # profiles/dequant_rowpacked_bf16_kernel_8192x8192.md
-    "w4a16_m2048": 81.8e6,   # profiles/w4a16_kernel_m2048_8192x8192.md
+    "w4a16_m2048": 84.8e6,   # profiles/w4a16_pair_kernel_m2048_8192x8192.md
     "w4a16_m16": 35.2e6,     # profiles/w4a16_kernel_m16_8192x8192.md
 }
 
