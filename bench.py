@@ -228,6 +228,30 @@ def run_ours(args):
         dtype = "bf16->e5m2+e4m3"
         l2 = "3 rotating tensors"
         e2e_setup = None
+    elif wl == "cast_current":
+        # current scaling: amax pass -> scale on the device -> cast with the device scalar scale
+        n = args.elems
+        g = torch.Generator(device=dev).manual_seed(7 + rank)
+        xs = [torch.randn(n, device=dev, generator=g, dtype=torch.float32).to(torch.bfloat16) for _ in range(3)]
+        o8 = [torch.empty(n, device=dev, dtype=torch.float8_e4m3fn) for _ in range(3)]
+        amax = torch.zeros((), device=dev, dtype=torch.float32)
+        cs = torch.ones(1, device=dev, dtype=torch.float32)
+
+        def step(i):
+            j = i % 3
+            abi.check(abi.lib.b200q_amax(abi.ptr(xs[j]), abi.BF16, n, abi.ptr(amax), abi.stream_ptr()))
+            abi.check(abi.lib.b200q_scale_from_amax(abi.ptr(amax), abi.ptr(cs), None, 448.0, 1, 0, abi.stream_ptr()))
+            abi.check(abi.lib.b200q_cast_to_fp8(abi.ptr(xs[j]), abi.BF16, abi.ptr(o8[j]), abi.E4M3, abi.ptr(cs), 1.0,
+                                                abi.BCAST_SCALAR_DEV, 1, n, None, abi.ROUND_RNE, 1234, 0, 0, 0, abi.stream_ptr()))
+        launches_per_step = 3
+        algo_bytes = 5 * n
+        bound, unit_per_step, unit = "hbm", algo_bytes / 1e9, "GB/s"
+        peak, peak_note = peaks["hbm_gbs"], "measured copy bandwidth"
+        metric = "current-scaling cast (amax pass + scale + cast_to_fp8_v2 e4m3 RNE) GB/s"
+        workload = f"amax -> 2^floor(log2(448/amax)) -> cast_to_fp8_v2 on {n} bf16 elements ~N(0,1); 5 B/element"
+        dtype = "bf16->e4m3"
+        l2 = "3 rotating tensors"
+        e2e_setup = None
     elif wl in ("cast_rne", "cast_sr", "uncast"):
         n = args.elems
         g = torch.Generator(device=dev).manual_seed(7 + rank)

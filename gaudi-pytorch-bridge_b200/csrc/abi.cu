@@ -61,6 +61,9 @@ int cast_hybrid_impl(const void*, int, void*, void*, const float*, float, int, c
                      uint64_t, uint64_t, uint64_t, int, cudaStream_t);
 int cast_from_fp8_impl(const void*, int, void*, int, const float*, float, int, int64_t, int64_t, cudaStream_t);
 int swiglu_cast_impl(const void*, int64_t, const void*, int64_t, void*, float, int64_t, int64_t, float*, cudaStream_t);
+int amax_impl(const void*, int, int64_t, float*, cudaStream_t);
+int scale_from_amax_impl(const float*, float*, float*, float, int, int, cudaStream_t);
+int amax_history_impl(float*, int, int, const float*, int, float*, float*, float, int, int, cudaStream_t);
 int dequant_int4_impl(const int32_t*, const void*, const void*, int, int, int, void*, int64_t, int64_t, int64_t, int,
                       cudaStream_t);
 int w4a16_gemm_impl(const void*, int64_t, const int32_t*, const void*, const int32_t*, int, int, int64_t, int64_t,
@@ -167,6 +170,21 @@ int b200q_swiglu_cast_fp8(const void* gate, int64_t ld_gate, const void* up, int
   if (rows * cols > 0 && (!gate || !up || !out)) return B200Q_ERR_BAD_ARGUMENT;
   return swiglu_cast_impl(gate, ld_gate, up, ld_up, out, scale_host, rows, cols, amax,
                           static_cast<cudaStream_t>(stream));
+}
+
+int b200q_amax(const void* in, int in_dtype, int64_t n, float* amax, void* stream) {
+  return amax_impl(in, in_dtype, n, amax, static_cast<cudaStream_t>(stream));
+}
+
+int b200q_scale_from_amax(const float* amax, float* scale, float* scale_inv, float fp8_max, int pow2, int margin,
+                          void* stream) {
+  return scale_from_amax_impl(amax, scale, scale_inv, fp8_max, pow2, margin, static_cast<cudaStream_t>(stream));
+}
+
+int b200q_amax_history_update(float* history, int len, int pos, const float* new_amax, int use_max, float* scale,
+                              float* scale_inv, float fp8_max, int pow2, int margin, void* stream) {
+  return amax_history_impl(history, len, pos, new_amax, use_max, scale, scale_inv, fp8_max, pow2, margin,
+                           static_cast<cudaStream_t>(stream));
 }
 
 int b200q_dequant_int4(const int32_t* packed, const void* scale, const void* zp, int zp_kind, int is_signed,

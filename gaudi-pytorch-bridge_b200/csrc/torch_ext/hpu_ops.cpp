@@ -715,6 +715,56 @@ std::tuple<at::Tensor, at::Tensor> swiglu_cast_fp8(const at::Tensor& gate, const
   return {out, amax};
 }
 
+// ---- FP8 scale management (lazy_optimizer_kernels.cpp:113-126) ----
+static float fp8_max_of(at::ScalarType dtype) {
+  TORCH_CHECK(is_fp8(dtype), "fp8 dtype must be float8_e5m2 or float8_e4m3fn, got ", dtype);
+  return dtype == at::kFloat8_e4m3fn ? 448.f : 57344.f;
+}
+
+at::Tensor amax_op(const at::Tensor& input) {
+  TORCH_CHECK(input.scalar_type() == at::kFloat || input.scalar_type() == at::kBFloat16, "amax: input must be float or bfloat16");
+  c10::cuda::CUDAGuard guard(input.device());
+  at::Tensor in = input.contiguous();
+  at::Tensor amax = at::empty({}, in.options().dtype(at::kFloat));
+  check_status(b200q_amax(in.data_ptr(), to_b200q_dtype(in.scalar_type()), in.numel(), amax.data_ptr<float>(), current_stream()), "amax");
+  return amax;
+}
+
+at::Tensor& scale_from_amax_(at::Tensor& scale, const at::Tensor& amax, double fp8_max, bool pow2, int64_t margin) {
+  TORCH_CHECK(scale.scalar_type() == at::kFloat && amax.scalar_type() == at::kFloat && scale.numel() == 1 && amax.numel() == 1,
+              "scale_from_amax_: scale and amax must be one-element float tensors");
+  c10::cuda::CUDAGuard guard(scale.device());
+  check_status(b200q_scale_from_amax(amax.data_ptr<float>(), scale.data_ptr<float>(), nullptr, (float)fp8_max, pow2, (int)margin,
+                                     current_stream()),
+               "scale_from_amax_");
+  return scale;
+}
+
+at::Tensor& amax_history_update_(at::Tensor& scale, at::Tensor& history, int64_t pos, const at::Tensor& new_amax, bool use_max,
+                                 double fp8_max, bool pow2, int64_t margin) {
+  TORCH_CHECK(scale.scalar_type() == at::kFloat && history.scalar_type() == at::kFloat && new_amax.scalar_type() == at::kFloat &&
+                  scale.numel() == 1 && new_amax.numel() == 1 && history.dim() == 1 && history.is_contiguous(),
+              "amax_history_update_: float tensors, one-element scale / new_amax, contiguous 1-D history");
+  TORCH_CHECK(pos >= 0 && pos < history.numel(), "amax_history_update_: pos out of range");
+  c10::cuda::CUDAGuard guard(scale.device());
+  check_status(b200q_amax_history_update(history.data_ptr<float>(), (int)history.numel(), (int)pos, new_amax.data_ptr<float>(),
+                                         use_max, scale.data_ptr<float>(), nullptr, (float)fp8_max, pow2, (int)margin,
+                                         current_stream()),
+               "amax_history_update_");
+  return scale;
+}
+
+// CastMomentToFp8WithScale: amax -> power-of-two scale (kept when amax == 0) -> stochastic cast
+// with that scale; three launches on the current stream, nothing read back to the host.
+at::Tensor cast_moment_to_fp8(const at::Tensor& moment, at::Tensor& scale, at::ScalarType dtype) {
+  const float fmax = fp8_max_of(dtype);
+  at::Tensor amax = amax_op(moment);
+  scale_from_amax_(scale, amax, fmax, true, 0);
+  const std::vector<int64_t> one{1};
+  auto r = cast_to_fp8_v2(moment, scale, true, false, dtype, at::IntArrayRef(one));
+  return std::get<0>(r);
+}
+
 void set_sr_seed(int64_t seed) {
   g_sr_seed.store(seed);
   g_sr_offset.store(0);
@@ -831,6 +881,10 @@ TORCH_LIBRARY(b200q, m) {
   m.def("fp8_gemm_cast(Tensor A, bool trans_A, Tensor B, bool trans_B, Tensor? D, ScalarType mid_dtype, Tensor? A_scale_inv, Tensor? B_scale_inv, Tensor? bias, bool accumulate, int[]? B_scale_shape, float out_scale, ScalarType out_dtype) -> Tensor");
   m.def("scaled_mm(Tensor a, Tensor b, Tensor scale_a, Tensor scale_b, Tensor? bias, Tensor? scale_result, ScalarType out_dtype) -> Tensor");
   m.def("swiglu_cast_fp8(Tensor gate, Tensor up, float scale, bool is_amax) -> (Tensor, Tensor)");
+  m.def("amax(Tensor input) -> Tensor");
+  m.def("scale_from_amax_(Tensor(a!) scale, Tensor amax, float fp8_max, bool pow2=True, int margin=0) -> Tensor(a!)");
+  m.def("amax_history_update_(Tensor(a!) scale, Tensor(b!) history, int pos, Tensor new_amax, bool use_max, float fp8_max, bool pow2=True, int margin=0) -> Tensor(a!)");
+  m.def("cast_moment_to_fp8(Tensor moment, Tensor(a!) scale, ScalarType dtype) -> Tensor");
   m.def("set_sr_seed(int seed) -> ()", set_sr_seed);
   m.def("set_cast_mul_in_fp32(bool on) -> ()", set_cast_mul_in_fp32);
   m.def("launch_count() -> int", launch_count);
@@ -844,4 +898,8 @@ TORCH_LIBRARY_IMPL(b200q, CUDA, m) {
   m.impl("fp8_gemm_cast", fp8_gemm_cast);
   m.impl("scaled_mm", scaled_mm);
   m.impl("swiglu_cast_fp8", swiglu_cast_fp8);
+  m.impl("amax", amax_op);
+  m.impl("scale_from_amax_", scale_from_amax_);
+  m.impl("amax_history_update_", amax_history_update_);
+  m.impl("cast_moment_to_fp8", cast_moment_to_fp8);
 }

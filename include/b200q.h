@@ -273,6 +273,29 @@ int b200q_swiglu_cast_fp8(const void* gate, int64_t ld_gate, const void* up, int
                           void* out, float scale_host, int64_t rows, int64_t cols, float* amax,
                           void* stream);
 
+/*
+ * FP8 scale management (current and delayed scaling) with all state on the device.
+ * Follows the composition the reference builds from ATen ops for its FP8 optimizer state,
+ * habana_kernels/lazy_optimizer_kernels.cpp:113-126 (CastMomentToFp8WithScale):
+ *   amax = max(abs(x)); exp = floor(log2(fp8_max / amax)); sf = 2^exp;
+ *   scale = where(amax > 0, sf, scale); cast_to_fp8_v2(x, scale, true, false, dtype, {1}).
+ *
+ * b200q_amax: *amax = max |in[i]| over n contiguous bf16 / fp32 elements (NaN propagates;
+ *   0 for n == 0).  `in` 16-byte aligned.
+ * b200q_scale_from_amax: when *amax > 0, *scale = 2^floor(log2(fp8_max / *amax)) (pow2 != 0;
+ *   the exponent is taken exactly from the quotient's bit pattern) or (fp8_max / *amax) / 2^margin
+ *   (pow2 == 0); otherwise *scale is kept.  scale_inv (may be NULL) receives 1 / *scale.
+ * b200q_amax_history_update: delayed scaling.  history[len] is a ring of earlier amax values:
+ *   history[pos] = *new_amax, then the scale as above from max(history) (use_max != 0) or from
+ *   the newest entry.
+ */
+int b200q_amax(const void* in, int in_dtype, int64_t n, float* amax, void* stream);
+int b200q_scale_from_amax(const float* amax, float* scale, float* scale_inv, float fp8_max, int pow2,
+                          int margin, void* stream);
+int b200q_amax_history_update(float* history, int len, int pos, const float* new_amax, int use_max,
+                              float* scale, float* scale_inv, float fp8_max, int pow2, int margin,
+                              void* stream);
+
 #ifdef __cplusplus
 }
 #endif
