@@ -228,6 +228,26 @@ def run_ours(args):
         dtype = "bf16->e5m2+e4m3"
         l2 = "3 rotating tensors"
         e2e_setup = None
+    elif wl == "softmax_fp8":
+        # attention-probability shaped: rows x cols bf16 -> e4m3 with scales (3 B/element)
+        rows_, cols_ = 16384, 4096
+        g = torch.Generator(device=dev).manual_seed(7 + rank)
+        xs = [(torch.randn(rows_, cols_, device=dev, generator=g, dtype=torch.float32) * 2).to(torch.bfloat16) for _ in range(3)]
+        o8 = [torch.empty(rows_, cols_, device=dev, dtype=torch.float8_e4m3fn) for _ in range(3)]
+
+        def step(i):
+            j = i % 3
+            abi.check(abi.lib.b200q_softmax_fp8(abi.ptr(xs[j]), abi.BF16, abi.ptr(o8[j]), 1, rows_, cols_, 0.125, None, None, None,
+                                                240.0, None, 0, None, None, abi.stream_ptr()))
+        launches_per_step = 1
+        algo_bytes = 3 * rows_ * cols_
+        bound, unit_per_step, unit = "hbm", algo_bytes / 1e9, "GB/s"
+        peak, peak_note = peaks["hbm_gbs"], "measured copy bandwidth"
+        metric = "softmax_fp8 (bf16 in, e4m3 out) GB/s"
+        workload = f"softmax_fp8 over the last dim of [{rows_}, {cols_}] bf16 ~N(0,2), input scale 0.125, output scale 240; 3 B/element"
+        dtype = "bf16->e4m3 (fp32 softmax)"
+        l2 = "3 rotating tensors"
+        e2e_setup = None
     elif wl == "cast_current":
         # current scaling: amax pass -> scale on the device -> cast with the device scalar scale
         n = args.elems

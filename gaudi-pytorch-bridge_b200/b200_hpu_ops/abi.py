@@ -19,6 +19,7 @@ EXPORTS = [
     "b200q_cast_to_fp8", "b200q_cast_to_fp8_hybrid", "b200q_cast_from_fp8", "b200q_dequant_int4", "b200q_gptq_repack", "b200q_fp8_gemm",
     "b200q_w4a16_gemm", "b200q_w4a16_workspace_bytes", "b200q_w4a16_gemm_noalloc", "b200q_swiglu_cast_fp8",
     "b200q_amax", "b200q_scale_from_amax", "b200q_amax_history_update",
+    "b200q_softmax_fp8", "b200q_sum_fp8_workspace_bytes", "b200q_sum_fp8", "b200q_in_place_interleave",
 ]
 
 DTYPE = {torch.float32: F32, torch.bfloat16: BF16, torch.float8_e4m3fn: E4M3, torch.float8_e5m2: E5M2}
@@ -69,6 +70,13 @@ def _bind():
     lib.b200q_w4a16_gemm_noalloc.argtypes = [C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int,
                                              C.c_int64, C.c_int64, C.c_int64, C.c_int64, C.c_void_p, C.c_int, C.c_int64,
                                              C.c_void_p]
+    lib.b200q_softmax_fp8.argtypes = [C.c_void_p, C.c_int, C.c_void_p, C.c_int, C.c_int64, C.c_int64, C.c_float, C.c_void_p,
+                                      C.c_void_p, C.c_void_p, C.c_float, C.c_void_p, C.c_int, C.c_void_p, C.c_void_p, C.c_void_p]
+    lib.b200q_sum_fp8_workspace_bytes.restype = C.c_size_t
+    lib.b200q_sum_fp8_workspace_bytes.argtypes = [C.c_int64, C.c_int64, C.c_int64]
+    lib.b200q_sum_fp8.argtypes = [C.c_void_p, C.c_int, C.c_void_p, C.c_int, C.c_int64, C.c_int64, C.c_int64, C.c_void_p, C.c_size_t,
+                                  C.c_void_p]
+    lib.b200q_in_place_interleave.argtypes = [C.c_void_p, C.c_int64, C.c_int64, C.c_void_p]
     lib.b200q_amax.argtypes = [C.c_void_p, C.c_int, C.c_int64, C.c_void_p, C.c_void_p]
     lib.b200q_scale_from_amax.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_float, C.c_int, C.c_int, C.c_void_p]
     lib.b200q_amax_history_update.argtypes = [C.c_void_p, C.c_int, C.c_int, C.c_void_p, C.c_int, C.c_void_p, C.c_void_p,

@@ -3,6 +3,7 @@
 #include <string.h>
 
 #include "common.cuh"
+#include "fp8_misc.cuh"
 #include "gemm_common.cuh"
 #include "tcgen05_ptx.cuh"
 
@@ -61,6 +62,10 @@ int cast_hybrid_impl(const void*, int, void*, void*, const float*, float, int, c
                      uint64_t, uint64_t, uint64_t, int, cudaStream_t);
 int cast_from_fp8_impl(const void*, int, void*, int, const float*, float, int, int64_t, int64_t, cudaStream_t);
 int swiglu_cast_impl(const void*, int64_t, const void*, int64_t, void*, float, int64_t, int64_t, float*, cudaStream_t);
+int softmax_fp8_impl(const SoftmaxParams&, cudaStream_t);
+int sum_fp8_impl(const void*, int, void*, int, int64_t, int64_t, int64_t, void*, size_t, cudaStream_t);
+size_t sum_fp8_workspace_bytes_impl(int64_t, int64_t, int64_t);
+int in_place_interleave_impl(void*, int64_t, int64_t, cudaStream_t);
 int amax_impl(const void*, int, int64_t, float*, cudaStream_t);
 int scale_from_amax_impl(const float*, float*, float*, float, int, int, cudaStream_t);
 int amax_history_impl(float*, int, int, const float*, int, float*, float*, float, int, int, cudaStream_t);
@@ -170,6 +175,48 @@ int b200q_swiglu_cast_fp8(const void* gate, int64_t ld_gate, const void* up, int
   if (rows * cols > 0 && (!gate || !up || !out)) return B200Q_ERR_BAD_ARGUMENT;
   return swiglu_cast_impl(gate, ld_gate, up, ld_up, out, scale_host, rows, cols, amax,
                           static_cast<cudaStream_t>(stream));
+}
+
+int b200q_softmax_fp8(const void* in, int in_dtype, void* out, int out_fp8, int64_t rows, int64_t cols, float pre_scale_host,
+                      const float* input_scale, const float* inv_attn_heads, const float* output_scale,
+                      float output_scale_host, const void* fused_add, int nd, const int64_t* lead_sizes,
+                      const int64_t* fused_add_strides, void* stream) {
+  if (rows < 0 || cols < 0 || nd < 0 || nd > 7) return B200Q_ERR_BAD_ARGUMENT;
+  if (in_dtype != B200Q_BF16 && in_dtype != B200Q_E4M3) return B200Q_ERR_BAD_ARGUMENT;
+  if (rows * cols > 0 && (!in || !out)) return B200Q_ERR_BAD_ARGUMENT;
+  if (fused_add && (!lead_sizes || !fused_add_strides)) return B200Q_ERR_BAD_ARGUMENT;
+  SoftmaxParams p;
+  p.in = in; p.in_dtype = in_dtype; p.out = out; p.out_fp8 = out_fp8; p.rows = rows; p.cols = cols;
+  p.pre_scale = pre_scale_host; p.input_scale = input_scale; p.inv_attn_heads = inv_attn_heads;
+  p.output_scale = output_scale; p.output_scale_host = output_scale_host;
+  p.fused_add = static_cast<const __nv_bfloat16*>(fused_add);
+  p.nd = fused_add ? nd : 0;
+  int64_t prod = 1;
+  for (int d = 0; d < 7; ++d) {
+    p.size[d] = (fused_add && d < nd) ? lead_sizes[d] : 1;
+    p.fa_stride[d] = (fused_add && d < nd) ? fused_add_strides[d] : 0;
+    if (p.size[d] < 1 && rows > 0) return B200Q_ERR_BAD_ARGUMENT;
+    prod *= p.size[d];
+  }
+  if (fused_add && prod != rows) return B200Q_ERR_BAD_ARGUMENT;
+  return softmax_fp8_impl(p, static_cast<cudaStream_t>(stream));
+}
+
+size_t b200q_sum_fp8_workspace_bytes(int64_t outer, int64_t reduce, int64_t inner) {
+  if (outer < 0 || reduce < 0 || inner < 0) return 0;
+  return sum_fp8_workspace_bytes_impl(outer, reduce, inner);
+}
+
+int b200q_sum_fp8(const void* in, int in_dtype, void* out, int out_dtype, int64_t outer, int64_t reduce, int64_t inner,
+                  void* workspace, size_t workspace_bytes, void* stream) {
+  if (out_dtype != B200Q_F32 && out_dtype != B200Q_BF16 && out_dtype != B200Q_E4M3 && out_dtype != B200Q_E5M2)
+    return B200Q_ERR_BAD_ARGUMENT;
+  return sum_fp8_impl(in, in_dtype, out, out_dtype, outer, reduce, inner, workspace, workspace_bytes,
+                      static_cast<cudaStream_t>(stream));
+}
+
+int b200q_in_place_interleave(void* data, int64_t n_rows, int64_t row_bytes, void* stream) {
+  return in_place_interleave_impl(data, n_rows, row_bytes, static_cast<cudaStream_t>(stream));
 }
 
 int b200q_amax(const void* in, int in_dtype, int64_t n, float* amax, void* stream) {

@@ -1,0 +1,390 @@
+// The smaller FP8 operators of the reference that sit beside the casts and the GEMM:
+//   softmax_fp8          hpu_ops/backend/softmax_fp8_gen.cpp:65-160  (scaled softmax, bf16 or e4m3 out)
+//   sum_fp8              hpu_ops/backend/fp8_ops_gen.cpp:20-49       (sum over fp8 input, fp32 accumulate)
+//   in_place_interleave_ hpu_ops/backend/fp8_ops.cpp:498-545         (row j <- row j / 4, in place)
+// All three are bandwidth-bound; none allocates.
+#include "common.cuh"
+#include "fp8_misc.cuh"
+
+namespace b200q {
+
+// ---------------------------------------------------------------------------- softmax_fp8
+// x = in * inv_attn_heads * input_scale + fused_add   (fp32; a factor that is absent is 1 / 0)
+// y = softmax(x) over the last dimension, rounded to bf16
+// out = y (bf16)                       without scales
+//     = e4m3(bf16(y * output_scale))   with scales (RNE, saturating)
+// One warp per row; the row is read twice (online max / sum of exponentials, then the write
+// pass), the second time from L1 / L2.
+__device__ __forceinline__ float ld_softmax_in(const SoftmaxParams& p, int64_t i) {
+  if (p.in_dtype == B200Q_BF16) return __bfloat162float(static_cast<const __nv_bfloat16*>(p.in)[i]);
+  const __nv_fp8_storage_t b = static_cast<const __nv_fp8_storage_t*>(p.in)[i];
+  return __half2float(__half(__nv_cvt_fp8_to_halfraw(b, __NV_E4M3)));
+}
+
+__global__ void __launch_bounds__(256) softmax_fp8_kernel(const SoftmaxParams p) {
+  const int lane = threadIdx.x & 31;
+  const int64_t row = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (row >= p.rows) return;
+  float pre = p.pre_scale;
+  if (p.inv_attn_heads) pre *= __ldg(p.inv_attn_heads);
+  if (p.input_scale) pre *= __ldg(p.input_scale);
+  const __nv_bfloat16* fa = nullptr;
+  if (p.fused_add) {
+    int64_t r = row, off = 0;
+    for (int d = p.nd - 1; d >= 0; --d) {
+      off += (r % p.size[d]) * p.fa_stride[d];
+      r /= p.size[d];
+    }
+    fa = p.fused_add + off;
+  }
+  const int64_t base = row * p.cols;
+  // pass 1: running maximum and sum of exp(x - max)
+  float m = -INFINITY, s = 0.f;
+  for (int64_t c = lane; c < p.cols; c += 32) {
+    float x = ld_softmax_in(p, base + c) * pre;
+    if (fa) x += __bfloat162float(fa[c]);
+    if (x > m) {
+      s = s * expf(m - x) + 1.f;
+      m = x;
+    } else {
+      s += expf(x - m);
+    }
+  }
+#pragma unroll
+  for (int o = 16; o; o >>= 1) {
+    const float m2 = __shfl_xor_sync(0xFFFFFFFFu, m, o), s2 = __shfl_xor_sync(0xFFFFFFFFu, s, o);
+    const float mm = fmaxf(m, m2);
+    s = (m == -INFINITY ? 0.f : s * expf(m - mm)) + (m2 == -INFINITY ? 0.f : s2 * expf(m2 - mm));
+    m = mm;
+  }
+  const float inv = 1.f / s;
+  const float so = p.output_scale ? __ldg(p.output_scale) : p.output_scale_host;
+  // pass 2
+  for (int64_t c = lane; c < p.cols; c += 32) {
+    float x = ld_softmax_in(p, base + c) * pre;
+    if (fa) x += __bfloat162float(fa[c]);
+    const float y = round_to_bf16(expf(x - m) * inv);
+    if (p.out_fp8) {
+      const float z = round_to_bf16(y * so);
+      uint32_t b = cvt_fp8x2<B200Q_E4M3>(z, 0.f) & 0xFFu;
+      if (z != z) b = 0x7Fu;
+      static_cast<uint8_t*>(p.out)[base + c] = (uint8_t)b;
+    } else {
+      static_cast<__nv_bfloat16*>(p.out)[base + c] = __float2bfloat16_rn(y);
+    }
+  }
+}
+
+// bf16 rows of up to 32 * 8 * NV elements whose length is a multiple of 8: the row is read once,
+// with 16-byte loads, and stays in registers (packed) for the three passes max / sum / write.
+__device__ __forceinline__ float ex2_approx(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
+
+template <int NV>
+__global__ void __launch_bounds__(256) softmax_bf16_rowreg_kernel(const SoftmaxParams p) {
+  const int lane = threadIdx.x & 31;
+  const int64_t row = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (row >= p.rows) return;
+  float pre = p.pre_scale;
+  if (p.inv_attn_heads) pre *= __ldg(p.inv_attn_heads);
+  if (p.input_scale) pre *= __ldg(p.input_scale);
+  // exponentials as 2^(x * log2(e) - max): one multiply folded into the input scaling and one
+  // ex2.approx (2 ulp) per value instead of a full expf
+  constexpr float kLog2e = 1.4426950408889634f;
+  pre *= kLog2e;
+  const uint4* fa = nullptr;
+  if (p.fused_add) {
+    int64_t r = row, off = 0;
+    for (int d = p.nd - 1; d >= 0; --d) {
+      off += (r % p.size[d]) * p.fa_stride[d];
+      r /= p.size[d];
+    }
+    fa = reinterpret_cast<const uint4*>(p.fused_add + off);
+  }
+  const int nvec = (int)(p.cols >> 3);
+  const uint4* src = reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(p.in) + row * p.cols);
+  uint4 w[NV];
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    const int v = lane + 32 * i;
+    w[i] = v < nvec ? __ldcs(src + v) : make_uint4(0, 0, 0, 0);
+  }
+  // x_j of vector i (recomputed in every pass: 8 multiplies are cheaper than 8 registers)
+  auto values = [&](int i, float* x) {
+    const uint32_t ws[4] = {w[i].x, w[i].y, w[i].z, w[i].w};
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      x[2 * k] = bf16_bits_to_float(ws[k] & 0xFFFFu) * pre;
+      x[2 * k + 1] = bf16_bits_to_float(ws[k] >> 16) * pre;
+    }
+    if (fa) {
+      const uint4 f = __ldg(fa + lane + 32 * i);
+      const uint32_t fs[4] = {f.x, f.y, f.z, f.w};
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        x[2 * k] = fmaf(bf16_bits_to_float(fs[k] & 0xFFFFu), kLog2e, x[2 * k]);
+        x[2 * k + 1] = fmaf(bf16_bits_to_float(fs[k] >> 16), kLog2e, x[2 * k + 1]);
+      }
+    }
+  };
+  float m = -INFINITY;
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    if (lane + 32 * i < nvec) {
+      float x[8];
+      values(i, x);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) m = fmaxf(m, x[j]);
+    }
+  }
+#pragma unroll
+  for (int o = 16; o; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xFFFFFFFFu, m, o));
+  float s = 0.f;
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    if (lane + 32 * i < nvec) {
+      float x[8];
+      values(i, x);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) s += ex2_approx(x[j] - m);
+    }
+  }
+#pragma unroll
+  for (int o = 16; o; o >>= 1) s += __shfl_xor_sync(0xFFFFFFFFu, s, o);
+  const float inv = 1.f / s;
+  const float so = p.output_scale ? __ldg(p.output_scale) : p.output_scale_host;
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    const int v = lane + 32 * i;
+    if (v < nvec) {
+      float x[8], y[8];
+      values(i, x);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) y[j] = round_to_bf16(ex2_approx(x[j] - m) * inv);
+      if (p.out_fp8) {
+        uint32_t o2[2] = {0, 0};
+#pragma unroll
+        for (int j = 0; j < 8; j += 2) {
+          const float z0 = round_to_bf16(y[j] * so), z1 = round_to_bf16(y[j + 1] * so);
+          uint32_t b = cvt_fp8x2<B200Q_E4M3>(z0, z1) & 0xFFFFu;
+          if (z0 != z0) b = (b & 0xFF00u) | 0x7Fu;
+          if (z1 != z1) b = (b & 0x00FFu) | 0x7F00u;
+          o2[j >> 2] |= b << (16 * ((j >> 1) & 1));
+        }
+        __stcs(reinterpret_cast<uint2*>(static_cast<uint8_t*>(p.out) + row * p.cols) + v, make_uint2(o2[0], o2[1]));
+      } else {
+        __stcs(reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(p.out) + row * p.cols) + v,
+               make_uint4(pack_bf16x2(y[0], y[1]), pack_bf16x2(y[2], y[3]), pack_bf16x2(y[4], y[5]), pack_bf16x2(y[6], y[7])));
+      }
+    }
+  }
+}
+
+template <int NV>
+static int launch_softmax_rowreg(const SoftmaxParams& p, cudaStream_t st) {
+  const int warps = 8;
+  const int64_t blocks = (p.rows + warps - 1) / warps;
+  if (blocks > 0x7FFFFFFF) return B200Q_ERR_TOO_LARGE;
+  softmax_bf16_rowreg_kernel<NV><<<(int)blocks, warps * 32, 0, st>>>(p);
+  B200Q_LAUNCH_CHECK();
+  return B200Q_OK;
+}
+
+int softmax_fp8_impl(const SoftmaxParams& p, cudaStream_t st) {
+  if (p.rows == 0 || p.cols == 0) return B200Q_OK;
+  // fast path: bf16 rows that fit a warp's registers, 16-byte aligned everywhere
+  bool fa_ok = true;
+  if (p.fused_add) {
+    fa_ok = (reinterpret_cast<uintptr_t>(p.fused_add) & 15) == 0;
+    for (int d = 0; d < p.nd; ++d) fa_ok = fa_ok && (p.fa_stride[d] % 8) == 0;
+  }
+  if (p.in_dtype == B200Q_BF16 && (p.cols % 8) == 0 && p.cols <= 32 * 8 * 16 && fa_ok &&
+      ((reinterpret_cast<uintptr_t>(p.in) | reinterpret_cast<uintptr_t>(p.out)) & 15) == 0) {
+    const int64_t per_lane = (p.cols / 8 + 31) / 32;
+    if (per_lane <= 1) return launch_softmax_rowreg<1>(p, st);
+    if (per_lane <= 2) return launch_softmax_rowreg<2>(p, st);
+    if (per_lane <= 4) return launch_softmax_rowreg<4>(p, st);
+    if (per_lane <= 8) return launch_softmax_rowreg<8>(p, st);
+    return launch_softmax_rowreg<16>(p, st);
+  }
+  const int warps = 8;
+  const int64_t blocks = (p.rows + warps - 1) / warps;
+  if (blocks > 0x7FFFFFFF) return B200Q_ERR_TOO_LARGE;
+  softmax_fp8_kernel<<<(int)blocks, warps * 32, 0, st>>>(p);
+  B200Q_LAUNCH_CHECK();
+  return B200Q_OK;
+}
+
+// ---------------------------------------------------------------------------- sum_fp8
+// in viewed as [outer][reduce][inner] (contiguous), fp32 accumulation in a fixed order:
+// chunk c of the reduce range is summed sequentially by one thread (inner > 1) or by one block
+// with a fixed tree (inner == 1); the chunk sums are then added in chunk order.  Same result
+// on every run.
+template <int FMT>
+__device__ __forceinline__ float fp8_to_float(uint8_t b) {
+  return __half2float(__half(__nv_cvt_fp8_to_halfraw(b, Fp8Fmt<FMT>::kInterp)));
+}
+
+template <int FMT>
+__global__ void __launch_bounds__(256) sum_fp8_strided_kernel(const uint8_t* __restrict__ in, float* __restrict__ partial,
+                                                              int64_t outer, int64_t reduce, int64_t inner, int chunks) {
+  const int64_t n_out = outer * inner;
+  const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= n_out) return;
+  const int chunk = blockIdx.y;
+  const int64_t per = (reduce + chunks - 1) / chunks;
+  const int64_t r0 = chunk * per, r1 = min(reduce, r0 + per);
+  const int64_t o = idx / inner, i = idx % inner;
+  const uint8_t* src = in + (o * reduce) * inner + i;
+  float acc = 0.f;
+  for (int64_t r = r0; r < r1; ++r) acc += fp8_to_float<FMT>(src[r * inner]);
+  partial[(int64_t)chunk * n_out + idx] = acc;
+}
+
+template <int FMT>
+__global__ void __launch_bounds__(256) sum_fp8_rows_kernel(const uint8_t* __restrict__ in, float* __restrict__ partial,
+                                                           int64_t outer, int64_t reduce, int chunks) {
+  // grid (outer, chunks): one block sums one chunk of one row
+  const int64_t row = blockIdx.x;
+  const int chunk = blockIdx.y;
+  const int64_t per = (reduce + chunks - 1) / chunks;
+  const int64_t r0 = (int64_t)chunk * per, r1 = min(reduce, r0 + per);
+  const int64_t len = r1 > r0 ? r1 - r0 : 0;
+  const uint8_t* s = in + row * reduce + r0;
+  float acc = 0.f;
+  // bytes up to the first 16-byte boundary, 16-byte vectors, bytes after the last vector
+  int64_t head = (16 - (int64_t)(reinterpret_cast<uintptr_t>(s) & 15)) & 15;
+  if (head > len) head = len;
+  if ((int64_t)threadIdx.x < head) acc += fp8_to_float<FMT>(s[threadIdx.x]);
+  const int64_t nvec = (len - head) / 16;
+  const uint4* v = reinterpret_cast<const uint4*>(s + head);
+  for (int64_t i = threadIdx.x; i < nvec; i += blockDim.x) {
+    const uint4 w = v[i];
+    const uint32_t ws[4] = {w.x, w.y, w.z, w.w};
+#pragma unroll
+    for (int k = 0; k < 4; ++k)
+#pragma unroll
+      for (int b = 0; b < 4; ++b) acc += fp8_to_float<FMT>((uint8_t)(ws[k] >> (8 * b)));
+  }
+  const int64_t tail0 = head + nvec * 16;
+  if (threadIdx.x < 16 && tail0 + (int64_t)threadIdx.x < len) acc += fp8_to_float<FMT>(s[tail0 + threadIdx.x]);
+  // fixed-order block tree
+  __shared__ float sm[256];
+  sm[threadIdx.x] = acc;
+  __syncthreads();
+  for (int o = 128; o; o >>= 1) {
+    if ((int)threadIdx.x < o) sm[threadIdx.x] += sm[threadIdx.x + o];
+    __syncthreads();
+  }
+  if (threadIdx.x == 0) partial[(int64_t)chunk * outer + row] = sm[0];
+}
+
+template <int FMT>
+__global__ void __launch_bounds__(256) sum_fp8_finish_kernel(const float* __restrict__ partial, void* out, int out_dtype,
+                                                             int64_t n_out, int chunks) {
+  const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= n_out) return;
+  float acc = 0.f;
+  for (int c = 0; c < chunks; ++c) acc += partial[(int64_t)c * n_out + idx];
+  if (out_dtype == B200Q_F32) {
+    static_cast<float*>(out)[idx] = acc;
+  } else if (out_dtype == B200Q_BF16) {
+    static_cast<__nv_bfloat16*>(out)[idx] = __float2bfloat16_rn(acc);
+  } else {
+    uint32_t b = out_dtype == B200Q_E4M3 ? (cvt_fp8x2<B200Q_E4M3>(acc, 0.f) & 0xFFu) : (cvt_fp8x2<B200Q_E5M2>(acc, 0.f) & 0xFFu);
+    if (acc != acc) b = 0x7Fu;
+    static_cast<uint8_t*>(out)[idx] = (uint8_t)b;
+  }
+}
+
+int sum_fp8_chunks(int64_t outer, int64_t reduce, int64_t inner) {
+  // enough chunks to occupy the device when there are few outputs, each at least 4096 elements
+  const int64_t n_out = outer * inner;
+  int64_t want = (int64_t)kNumSMs * 8 * 256 / (n_out > 0 ? n_out : 1);
+  if (inner == 1) want = (int64_t)kNumSMs * 4 / (outer > 0 ? outer : 1);
+  int64_t cap = reduce / 4096;
+  if (want > cap) want = cap;
+  if (want < 1) want = 1;
+  if (want > 1024) want = 1024;
+  return (int)want;
+}
+
+size_t sum_fp8_workspace_bytes_impl(int64_t outer, int64_t reduce, int64_t inner) {
+  return (size_t)sum_fp8_chunks(outer, reduce, inner) * (size_t)(outer * inner) * sizeof(float);
+}
+
+int sum_fp8_impl(const void* in, int in_dtype, void* out, int out_dtype, int64_t outer, int64_t reduce, int64_t inner,
+                 void* workspace, size_t workspace_bytes, cudaStream_t st) {
+  if (outer < 0 || reduce < 0 || inner < 0) return B200Q_ERR_BAD_ARGUMENT;
+  if (in_dtype != B200Q_E4M3 && in_dtype != B200Q_E5M2) return B200Q_ERR_BAD_ARGUMENT;
+  const int64_t n_out = outer * inner;
+  if (n_out == 0) return B200Q_OK;
+  if (!out || (reduce > 0 && !in)) return B200Q_ERR_BAD_ARGUMENT;
+  const int chunks = sum_fp8_chunks(outer, reduce, inner);
+  if (!workspace || workspace_bytes < (size_t)chunks * n_out * sizeof(float)) return B200Q_ERR_BAD_ARGUMENT;
+  float* partial = static_cast<float*>(workspace);
+  const uint8_t* src = static_cast<const uint8_t*>(in);
+  const int fin_blocks = (int)((n_out + 255) / 256);
+  if (inner == 1) {
+    if (outer > 0x7FFFFFFF) return B200Q_ERR_TOO_LARGE;
+    dim3 grid((unsigned)outer, (unsigned)chunks);
+    if (in_dtype == B200Q_E4M3) sum_fp8_rows_kernel<B200Q_E4M3><<<grid, 256, 0, st>>>(src, partial, outer, reduce, chunks);
+    else sum_fp8_rows_kernel<B200Q_E5M2><<<grid, 256, 0, st>>>(src, partial, outer, reduce, chunks);
+  } else {
+    dim3 grid((unsigned)((n_out + 255) / 256), (unsigned)chunks);
+    if (in_dtype == B200Q_E4M3) sum_fp8_strided_kernel<B200Q_E4M3><<<grid, 256, 0, st>>>(src, partial, outer, reduce, inner, chunks);
+    else sum_fp8_strided_kernel<B200Q_E5M2><<<grid, 256, 0, st>>>(src, partial, outer, reduce, inner, chunks);
+  }
+  B200Q_LAUNCH_CHECK();
+  sum_fp8_finish_kernel<0><<<fin_blocks, 256, 0, st>>>(partial, out, out_dtype, n_out, chunks);
+  B200Q_LAUNCH_CHECK();
+  return B200Q_OK;
+}
+
+// ---------------------------------------------------------------------------- in_place_interleave_
+// rows[j] <- rows[j / 4] for j in [0, n_rows), in place.  A row is a destination and, for j <
+// n_rows / 4, also a source; destinations [lo, hi) with lo > (hi - 1) / 4 have all their sources
+// below lo, so the rows are rewritten in phases from the top: [n/4, n), then [n/16, n/4), ...
+__global__ void __launch_bounds__(256) interleave_phase_kernel(uint8_t* base, int64_t row_bytes, int64_t lo, int64_t hi) {
+  const int64_t row = lo + blockIdx.y;
+  if (row >= hi) return;
+  const uint8_t* src = base + (row >> 2) * row_bytes;
+  uint8_t* dst = base + row * row_bytes;
+  if (src == dst) return;
+  const int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x, stride = (int64_t)gridDim.x * blockDim.x;
+  if ((row_bytes & 15) == 0 && (reinterpret_cast<uintptr_t>(base) & 15) == 0) {
+    const uint4* s4 = reinterpret_cast<const uint4*>(src);
+    uint4* d4 = reinterpret_cast<uint4*>(dst);
+    for (int64_t i = t; i < row_bytes / 16; i += stride) d4[i] = s4[i];
+  } else {
+    for (int64_t i = t; i < row_bytes; i += stride) dst[i] = src[i];
+  }
+}
+
+int in_place_interleave_impl(void* data, int64_t n_rows, int64_t row_bytes, cudaStream_t st) {
+  if (n_rows < 0 || row_bytes < 0 || (n_rows % 4) != 0) return B200Q_ERR_BAD_ARGUMENT;
+  if (n_rows == 0 || row_bytes == 0) return B200Q_OK;
+  if (!data) return B200Q_ERR_BAD_ARGUMENT;
+  int64_t hi = n_rows;
+  while (hi > 1) {
+    const int64_t lo = (hi - 1) / 4 + 1;
+    int64_t bx = (row_bytes / 16 + 255) / 256;
+    if (bx < 1) bx = 1;
+    if (bx > 64) bx = 64;
+    int64_t done = lo;
+    while (done < hi) {  // grid.y is limited to 65535 rows per launch
+      const int64_t rows = (hi - done) < 65535 ? (hi - done) : 65535;
+      interleave_phase_kernel<<<dim3((unsigned)bx, (unsigned)rows), 256, 0, st>>>(static_cast<uint8_t*>(data), row_bytes, done,
+                                                                                 done + rows);
+      B200Q_LAUNCH_CHECK();
+      done += rows;
+    }
+    hi = lo;
+  }
+  return B200Q_OK;
+}
+
+}  // namespace b200q

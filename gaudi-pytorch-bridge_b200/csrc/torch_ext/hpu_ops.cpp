@@ -715,6 +715,145 @@ std::tuple<at::Tensor, at::Tensor> swiglu_cast_fp8(const at::Tensor& gate, const
   return {out, amax};
 }
 
+// ---- softmax_fp8 (hpu_ops/backend/softmax_fp8_gen.cpp:65-160; schemas scripts/hpu_op.yaml:7399-7418) ----
+struct SoftmaxScale {  // absent | device scalar | host scalar
+  const float* dev = nullptr;
+  float host = 1.f;
+  bool given = false;
+  at::Tensor keep;
+};
+static SoftmaxScale softmax_scale(const OptTensor& t, const at::Tensor& like) {
+  SoftmaxScale s;
+  if (t.has_value() && t->defined()) {
+    TORCH_CHECK(t->scalar_type() == at::kFloat, "Input scale must be of dtype: ", at::kFloat);
+    TORCH_CHECK(t->numel() == 1, "softmax_fp8 scales must have one element");
+    s.keep = t->to(like.device()).contiguous();
+    s.dev = s.keep.data_ptr<float>();
+    s.given = true;
+  }
+  return s;
+}
+static SoftmaxScale softmax_scale(double v) {
+  SoftmaxScale s;
+  s.host = (float)v;
+  s.given = true;
+  return s;
+}
+
+at::Tensor softmax_fp8_common(const at::Tensor& input, int64_t dim, const SoftmaxScale& in_s, const SoftmaxScale& out_s,
+                              const SoftmaxScale& heads, const OptTensor& fused_add) {
+  const auto dt = input.scalar_type();
+  TORCH_CHECK(dt == at::kBFloat16 || dt == at::kFloat8_e4m3fn,
+              "Input tensor must be of torch.bfloat16 or torch.float8_e4m3fn dtype.");
+  TORCH_CHECK(in_s.given == out_s.given, "Output and input scales must be both given or None");
+  TORCH_CHECK(dt != at::kFloat8_e4m3fn || in_s.given, "If Input is of torch.float8_e4m3fn dtype then input scale must be given.");
+  const int64_t rank = input.dim();
+  TORCH_CHECK(rank >= 1 && rank <= 8, "softmax_fp8: input rank must be 1..8");
+  dim = at::maybe_wrap_dim(dim, rank, /*wrap_scalar=*/true);
+  TORCH_CHECK(dim == rank - 1, "softmax_fp8: only the last dimension is supported");
+  c10::cuda::CUDAGuard guard(input.device());
+  at::Tensor in = input.contiguous();
+  const bool fp8_out = in_s.given;
+  at::Tensor out = at::empty(in.sizes(), in.options().dtype(fp8_out ? at::kFloat8_e4m3fn : at::kBFloat16));
+  at::Tensor fa;
+  std::vector<int64_t> lead(in.sizes().begin(), in.sizes().end() - 1), fa_strides(lead.size(), 0);
+  if (fused_add.has_value() && fused_add->defined()) {
+    TORCH_CHECK(in_s.given, "FusedAdd available only for Float8 output, but input scale is not given.");
+    TORCH_CHECK(fused_add->scalar_type() == at::kBFloat16, "Input fused_add must be of dtype: ", at::kBFloat16);
+    TORCH_CHECK(fused_add->dim() == rank, "FusedAdd tensor must have the same rank as the input tensor");
+    TORCH_CHECK(fused_add->size(0) == in.size(0) && fused_add->size(rank - 1) == in.size(rank - 1),
+                "FusedAdd tensor must have the same first and last dim as the input tensor");
+    for (int64_t d = 1; d < rank - 1; ++d)
+      TORCH_CHECK(fused_add->size(d) == 1 || fused_add->size(d) == in.size(d),
+                  "FusedAdd tensor's dim other than first and last should be equal to 1 or the same as the input tensor");
+    fa = fused_add->contiguous();
+    for (int64_t d = 0; d < rank - 1; ++d) fa_strides[d] = fa.size(d) == 1 && in.size(d) != 1 ? 0 : fa.stride(d);
+  }
+  const int64_t cols = rank ? in.size(rank - 1) : 1;
+  const int64_t rows = cols ? in.numel() / cols : 0;
+  float pre = 1.f;
+  if (in_s.given && !in_s.dev) pre *= in_s.host;
+  if (heads.given && !heads.dev) pre *= heads.host;
+  check_status(b200q_softmax_fp8(in.data_ptr(), to_b200q_dtype(dt), out.data_ptr(), fp8_out, rows, cols, pre, in_s.dev, heads.dev,
+                                 out_s.dev, out_s.given ? out_s.host : 1.f, fa.defined() ? fa.data_ptr() : nullptr,
+                                 (int)lead.size(), lead.data(), fa_strides.data(), current_stream()),
+               "softmax_fp8");
+  return out;
+}
+at::Tensor softmax_fp8(const at::Tensor& input, int64_t dim, const OptTensor& input_scale, const OptTensor& output_scale,
+                       const OptTensor& inv_attn_heads, const OptTensor& fused_add) {
+  return softmax_fp8_common(input, dim, softmax_scale(input_scale, input), softmax_scale(output_scale, input),
+                            softmax_scale(inv_attn_heads, input), fused_add);
+}
+at::Tensor softmax_fp8_scalar_scales(const at::Tensor& input, int64_t dim, double input_scale, double output_scale,
+                                     const OptTensor& inv_attn_heads, const OptTensor& fused_add) {
+  return softmax_fp8_common(input, dim, softmax_scale(input_scale), softmax_scale(output_scale),
+                            softmax_scale(inv_attn_heads, input), fused_add);
+}
+at::Tensor softmax_fp8_scalar(const at::Tensor& input, int64_t dim, double input_scale, double output_scale,
+                              double inv_attn_heads, const OptTensor& fused_add) {
+  return softmax_fp8_common(input, dim, softmax_scale(input_scale), softmax_scale(output_scale), softmax_scale(inv_attn_heads),
+                            fused_add);
+}
+
+// ---- sum_fp8 (hpu_ops/backend/fp8_ops_gen.cpp:20-49; schema scripts/hpu_op.yaml:7448-7449) ----
+at::Tensor sum_fp8(const at::Tensor& self, at::OptionalIntArrayRef dim, bool keepdim, c10::optional<at::ScalarType> out_dtype) {
+  TORCH_CHECK(is_fp8(self.scalar_type()), "sum_fp8: input must be float8_e5m2 or float8_e4m3fn");
+  const at::ScalarType odt = out_dtype.value_or(self.scalar_type());
+  TORCH_CHECK(is_fp8(odt) || odt == at::kFloat || odt == at::kBFloat16, "sum_fp8: unsupported out_dtype ", odt);
+  c10::cuda::CUDAGuard guard(self.device());
+  const int64_t rank = self.dim();
+  std::vector<bool> red(rank, false);
+  if (!dim.has_value() || dim->empty()) {
+    std::fill(red.begin(), red.end(), true);
+  } else {
+    for (int64_t d : *dim) red[at::maybe_wrap_dim(d, rank)] = true;
+  }
+  // kept dims first, reduced dims last: [outer][reduce][1]; when the reduced dims already are a
+  // leading / trailing / middle block of the contiguous tensor no copy is made
+  std::vector<int64_t> kept, reduced, out_shape;
+  for (int64_t d = 0; d < rank; ++d) {
+    (red[d] ? reduced : kept).push_back(d);
+    if (!red[d]) out_shape.push_back(self.size(d));
+    else if (keepdim) out_shape.push_back(1);
+  }
+  int64_t outer = 1, reduce = 1, inner = 1;
+  at::Tensor src = self.contiguous();
+  bool block = true;  // reduced dims contiguous in index space?
+  for (size_t i = 1; i < reduced.size(); ++i) block = block && reduced[i] == reduced[i - 1] + 1;
+  if (block) {
+    const int64_t first = reduced.empty() ? rank : reduced.front(), last = reduced.empty() ? rank - 1 : reduced.back();
+    for (int64_t d = 0; d < first; ++d) outer *= self.size(d);
+    for (int64_t d : reduced) reduce *= self.size(d);
+    for (int64_t d = last + 1; d < rank; ++d) inner *= self.size(d);
+  } else {
+    std::vector<int64_t> perm = kept;
+    perm.insert(perm.end(), reduced.begin(), reduced.end());
+    src = self.view(at::kByte).permute(perm).contiguous();
+    for (int64_t d : kept) outer *= self.size(d);
+    for (int64_t d : reduced) reduce *= self.size(d);
+  }
+  at::Tensor out = at::empty(out_shape, self.options().dtype(odt));
+  const size_t ws_bytes = b200q_sum_fp8_workspace_bytes(outer, reduce, inner);
+  at::Tensor ws = at::empty({(int64_t)((ws_bytes + 3) / 4)}, self.options().dtype(at::kFloat));
+  check_status(b200q_sum_fp8(src.data_ptr(), to_b200q_dtype(self.scalar_type()), out.data_ptr(), to_b200q_dtype(odt), outer, reduce,
+                             inner, ws.data_ptr(), ws_bytes, current_stream()),
+               "sum_fp8");
+  return out;
+}
+
+// ---- in_place_interleave_ (hpu_ops/backend/fp8_ops.cpp:498-545; kernels_register.cpp:2548) ----
+at::Tensor& in_place_interleave_(at::Tensor& self) {
+  TORCH_CHECK(self.dim() == 4, "Input has to be a 4D tensor.");
+  TORCH_CHECK(self.size(0) % 4 == 0, "Batch size has to be a multiple of 4.");
+  TORCH_CHECK(self.is_contiguous(), "in_place_interleave_: input must be contiguous");
+  c10::cuda::CUDAGuard guard(self.device());
+  const int64_t rows = self.size(0);
+  const int64_t row_bytes = rows ? (int64_t)(self.numel() / rows) * (int64_t)self.element_size() : 0;
+  check_status(b200q_in_place_interleave(self.data_ptr(), rows, row_bytes, current_stream()), "in_place_interleave_");
+  return self;
+}
+
 // ---- FP8 scale management (lazy_optimizer_kernels.cpp:113-126) ----
 static float fp8_max_of(at::ScalarType dtype) {
   TORCH_CHECK(is_fp8(dtype), "fp8 dtype must be float8_e5m2 or float8_e4m3fn, got ", dtype);
@@ -839,6 +978,11 @@ TORCH_LIBRARY(hpu, m) {
   m.def("fp8_gemm(Tensor A, bool trans_A, Tensor B, bool trans_B, Tensor D, ScalarType out_dtype, Tensor? A_scale_inv, Tensor? B_scale_inv, Tensor? bias, bool accumulate, Tensor(a!) out) -> Tensor(a!)");
   m.def("fp8_gemm_v2(Tensor A, bool trans_A, Tensor B, bool trans_B, Tensor? D, ScalarType out_dtype, Tensor? A_scale_inv=None, Tensor? B_scale_inv=None, Tensor? bias=None, bool accumulate=False, int[]? B_scale_shape=None) -> Tensor");
   m.def("fp8_gemm_v2.scalar(Tensor A, bool trans_A, Tensor B, bool trans_B, Tensor? D, ScalarType out_dtype, float A_scale_inv, float B_scale_inv, Tensor? bias=None, bool accumulate=False, int[]? B_scale_shape=None) -> Tensor");
+  m.def("softmax_fp8(Tensor input, int dim, Tensor? input_scale=None, Tensor? output_scale=None, Tensor? inv_attn_heads=None, Tensor? fused_add=None) -> Tensor");
+  m.def("softmax_fp8.Scalar_scales(Tensor input, int dim, float input_scale, float output_scale, Tensor? inv_attn_heads=None, Tensor? fused_add=None) -> Tensor");
+  m.def("softmax_fp8.Scalar(Tensor input, int dim, float input_scale, float output_scale, float inv_attn_heads, Tensor? fused_add=None) -> Tensor");
+  m.def("sum_fp8(Tensor self, int[1]? dim=None, bool keepdim=False, ScalarType? out_dtype=None) -> Tensor");
+  m.def("in_place_interleave_(Tensor(a!) self) -> (Tensor(a!))");
   m.def("fp8_gemm_v2.scalar_list(Tensor A, bool trans_A, Tensor B, bool trans_B, Tensor? D, ScalarType out_dtype, float[] A_scale_inv, float[] B_scale_inv, Tensor? bias=None, bool accumulate=False, int[]? B_scale_shape=None) -> Tensor");
 }
 
@@ -853,13 +997,49 @@ TORCH_LIBRARY_IMPL(hpu, CUDA, m) {
   m.impl("cast_from_fp8", cast_from_fp8);
   m.impl("cast_from_fp8.scalar", cast_from_fp8_scalar);
   m.impl("cast_from_fp8.scalar_list", cast_from_fp8_scalar_list);
+  m.impl("softmax_fp8", softmax_fp8);
+  m.impl("softmax_fp8.Scalar_scales", softmax_fp8_scalar_scales);
+  m.impl("softmax_fp8.Scalar", softmax_fp8_scalar);
+  m.impl("sum_fp8", sum_fp8);
+  m.impl("in_place_interleave_", in_place_interleave_);
   m.impl("fp8_gemm", fp8_gemm);
   m.impl("fp8_gemm_v2", fp8_gemm_v2);
   m.impl("fp8_gemm_v2.scalar", fp8_gemm_v2_scalar);
   m.impl("fp8_gemm_v2.scalar_list", fp8_gemm_v2_scalar_list);
 }
 
+// softmax_fp8_gen.cpp:65-72 (SoftmaxFp8Meta), fp8_ops_gen.cpp:20-34 (SumFp8Meta)
+at::Tensor meta_softmax_fp8(const at::Tensor& input, int64_t, const OptTensor& input_scale, const OptTensor&, const OptTensor&,
+                            const OptTensor&) {
+  const bool scaled = input_scale.has_value() && input_scale->defined();
+  return at::empty(input.sizes(), input.options().dtype(scaled ? at::kFloat8_e4m3fn : at::kBFloat16));
+}
+at::Tensor meta_softmax_fp8_scalar_scales(const at::Tensor& input, int64_t, double, double, const OptTensor&, const OptTensor&) {
+  return at::empty(input.sizes(), input.options().dtype(at::kFloat8_e4m3fn));
+}
+at::Tensor meta_softmax_fp8_scalar(const at::Tensor& input, int64_t, double, double, double, const OptTensor&) {
+  return at::empty(input.sizes(), input.options().dtype(at::kFloat8_e4m3fn));
+}
+at::Tensor meta_sum_fp8(const at::Tensor& self, at::OptionalIntArrayRef dim, bool keepdim, c10::optional<at::ScalarType> out_dtype) {
+  const int64_t rank = self.dim();
+  std::vector<bool> red(rank, !dim.has_value() || dim->empty());
+  if (dim.has_value())
+    for (int64_t d : *dim) red[at::maybe_wrap_dim(d, rank)] = true;
+  std::vector<int64_t> shape;
+  for (int64_t d = 0; d < rank; ++d) {
+    if (!red[d]) shape.push_back(self.size(d));
+    else if (keepdim) shape.push_back(1);
+  }
+  return at::empty(shape, self.options().dtype(out_dtype.value_or(self.scalar_type())));
+}
+at::Tensor& meta_in_place_interleave_(at::Tensor& self) { return self; }
+
 TORCH_LIBRARY_IMPL(hpu, Meta, m) {
+  m.impl("softmax_fp8", meta_softmax_fp8);
+  m.impl("softmax_fp8.Scalar_scales", meta_softmax_fp8_scalar_scales);
+  m.impl("softmax_fp8.Scalar", meta_softmax_fp8_scalar);
+  m.impl("sum_fp8", meta_sum_fp8);
+  m.impl("in_place_interleave_", meta_in_place_interleave_);
   m.impl("cast_to_fp8_hybrid", meta_cast_to_fp8_hybrid);
   m.impl("cast_to_fp8_v2", meta_cast_to_fp8_v2);
   m.impl("cast_to_fp8_v2.scalar", meta_cast_to_fp8_v2_scalar);

@@ -296,6 +296,42 @@ int b200q_amax_history_update(float* history, int len, int pos, const float* new
                               float* scale, float* scale_inv, float fp8_max, int pow2, int margin,
                               void* stream);
 
+/*
+ * softmax_fp8 (hpu_ops/backend/softmax_fp8_gen.cpp:65-160, node softmax_fwd in its HF8 modes):
+ *   x = in * inv_attn_heads * input_scale + fused_add   (fp32; absent factors are 1, absent addend 0)
+ *   y = softmax over the last dimension, rounded to bf16
+ *   out = y as bf16 (out_fp8 == 0) or e4m3(bf16(y * output_scale)) (out_fp8 != 0; RNE, saturating)
+ * in: bf16 or e4m3, [rows][cols] contiguous.  The three scales are device scalars or NULL; a
+ * NULL input_scale / inv_attn_heads contributes the host factor `pre_scale_host` instead (pass 1
+ * when neither is given), a NULL output_scale the host value `output_scale_host`.
+ * fused_add (bf16 or NULL) broadcasts over the leading dimensions: `nd` leading sizes in
+ * `lead_sizes` (their product is `rows`) and its strides in elements in `fused_add_strides` (0
+ * where it broadcasts); its last dimension is `cols`, contiguous.  nd <= 7.
+ */
+int b200q_softmax_fp8(const void* in, int in_dtype, void* out, int out_fp8, int64_t rows,
+                      int64_t cols, float pre_scale_host, const float* input_scale,
+                      const float* inv_attn_heads, const float* output_scale,
+                      float output_scale_host, const void* fused_add, int nd,
+                      const int64_t* lead_sizes, const int64_t* fused_add_strides, void* stream);
+
+/*
+ * sum_fp8 (hpu_ops/backend/fp8_ops_gen.cpp:20-49, node reduce_sum): the e4m3 / e5m2 input viewed
+ * as [outer][reduce][inner] (contiguous) is summed over `reduce` in fp32, in a fixed order, and
+ * written as out_dtype (fp32, bf16, or an fp8 format: RNE, saturating) to [outer][inner].
+ * `workspace`: b200q_sum_fp8_workspace_bytes(outer, reduce, inner) bytes of device memory.
+ */
+size_t b200q_sum_fp8_workspace_bytes(int64_t outer, int64_t reduce, int64_t inner);
+int b200q_sum_fp8(const void* in, int in_dtype, void* out, int out_dtype, int64_t outer,
+                  int64_t reduce, int64_t inner, void* workspace, size_t workspace_bytes,
+                  void* stream);
+
+/*
+ * in_place_interleave_ (hpu_ops/backend/fp8_ops.cpp:498-545, node in_place_interleave_fwd):
+ * row j of `data` ([n_rows][row_bytes], n_rows % 4 == 0) becomes the old row j / 4, in place --
+ * every one of the first n_rows / 4 rows repeated four times.  Any element type.
+ */
+int b200q_in_place_interleave(void* data, int64_t n_rows, int64_t row_bytes, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -1,0 +1,151 @@
+"""softmax_fp8, sum_fp8 and in_place_interleave_ on the GPU against the oracle; cases mirror
+tests/pytest_working/any_mode/test_hpu_fp8_ops_any_mode.py:795-824,980-1048 and
+test_hpu_sum_fp8.py:30-55 of the reference."""
+import pytest
+import torch
+
+from oracle import hpu_oracle as O
+
+E4M3, E5M2 = torch.float8_e4m3fn, torch.float8_e5m2
+
+
+@pytest.fixture(scope="module")
+def ops():
+    import b200_hpu_ops
+    assert torch.cuda.is_available()
+    return b200_hpu_ops
+
+
+def _fp8_steps_apart(a8, b8):
+    """|difference| in fp8 codes (same format, same sign region)."""
+    a, b = a8.view(torch.uint8).int(), b8.view(torch.uint8).int()
+    return (a - b).abs()
+
+
+# ---------------------------------------------------------------- softmax_fp8
+@pytest.mark.gpu
+@pytest.mark.parametrize("is_scale,input_dtype", [(True, E4M3), (True, torch.bfloat16), (False, torch.bfloat16)])
+@pytest.mark.parametrize("is_inv_attn_heads", [True, False])
+@pytest.mark.parametrize("fused_add_shape", [None, (5, 4, 4, 6), (5, 1, 1, 6)])
+def test_softmax_fp8_reference_cases(ops, is_scale, is_inv_attn_heads, fused_add_shape, input_dtype):
+    g = torch.Generator().manual_seed(17)
+    shape = (5, 4, 4, 6)
+    x = (torch.rand(shape, generator=g) * 4.0).to(torch.bfloat16)
+    xin = x.to(input_dtype)
+    s_in = torch.tensor(0.05) if is_scale else None
+    s_out = torch.tensor(2.5) if is_scale else None
+    heads = torch.tensor(0.1) if is_inv_attn_heads else None
+    fa = torch.rand(fused_add_shape, generator=g).to(torch.bfloat16) if (fused_add_shape and is_scale) else None
+    cu = lambda t: None if t is None else t.cuda()  # noqa: E731
+    got = torch.ops.hpu.softmax_fp8(xin.cuda(), -1, cu(s_in), cu(s_out), cu(heads), cu(fa)).cpu()
+    want = O.softmax_fp8(xin, -1, s_in, s_out, heads, fa)
+    assert got.dtype == want.dtype == (E4M3 if is_scale else torch.bfloat16)
+    if is_scale:
+        d = _fp8_steps_apart(got, want)
+        assert int(d.max()) <= 1 and float((d != 0).float().mean()) < 0.02
+    else:
+        assert torch.allclose(got.float(), want.float(), rtol=2 ** -7, atol=1e-6)
+    # the reference test's own emulation and tolerance (bf16 arithmetic step by step)
+    ref = x.to(input_dtype).to(torch.bfloat16)
+    if is_inv_attn_heads:
+        ref = ref * heads
+    if is_scale:
+        ref = ref * s_in
+        if fa is not None:
+            ref = ref + fa
+    ref = torch.softmax(ref, -1).to(torch.bfloat16)
+    if is_scale:
+        ref = (ref * s_out).to(E4M3)
+    assert torch.allclose(got.float(), ref.float(), atol=1e-2, rtol=0.1251)
+    # scalar overloads give the same bytes
+    if is_scale:
+        if fa is None or True:
+            g2 = torch.ops.hpu.softmax_fp8.Scalar_scales(xin.cuda(), -1, 0.05, 2.5, cu(heads), cu(fa)).cpu()
+            assert torch.equal(g2.view(torch.uint8), got.view(torch.uint8))
+        if is_inv_attn_heads:
+            g3 = torch.ops.hpu.softmax_fp8.Scalar(xin.cuda(), -1, 0.05, 2.5, 0.1, cu(fa)).cpu()
+            d3 = _fp8_steps_apart(g3, got)  # host product of the two scalars vs device products
+            assert int(d3.max()) <= 1
+
+
+@pytest.mark.gpu
+def test_softmax_fp8_long_rows_and_errors(ops):
+    g = torch.Generator().manual_seed(3)
+    x = (torch.randn(37, 4099, generator=g) * 3).to(torch.bfloat16)
+    got = torch.ops.hpu.softmax_fp8(x.cuda(), 1, None, None, None, None).cpu()
+    want = O.softmax_fp8(x, 1)
+    assert torch.allclose(got.float(), want.float(), rtol=2 ** -7, atol=1e-7)
+    assert torch.allclose(got.float().sum(-1), torch.ones(37), atol=2e-2)
+    s = torch.tensor(1.0).cuda()
+    with pytest.raises(RuntimeError, match="Output and input scales must be both given or None"):
+        torch.ops.hpu.softmax_fp8(x.cuda(), -1, s, None, None, None)
+    with pytest.raises(RuntimeError, match="then input scale must be given"):
+        torch.ops.hpu.softmax_fp8(x.cuda().to(E4M3), -1, None, None, None, None)
+    with pytest.raises(RuntimeError, match="FusedAdd available only for Float8 output"):
+        torch.ops.hpu.softmax_fp8(x.cuda(), -1, None, None, None, x.cuda())
+    with pytest.raises(RuntimeError, match="must be of torch.bfloat16 or torch.float8_e4m3fn"):
+        torch.ops.hpu.softmax_fp8(x.cuda().float(), -1, None, None, None, None)
+    assert ops.device_status() == 0
+
+
+# ---------------------------------------------------------------- sum_fp8
+@pytest.mark.gpu
+@pytest.mark.parametrize("dim", [0, 1, 2, (0, 1), (0, 2), None])
+@pytest.mark.parametrize("keep_dim", [True, False])
+@pytest.mark.parametrize("dtype", [E5M2, E4M3])
+@pytest.mark.parametrize("out_dtype", [None, torch.float])
+def test_sum_fp8_reference_cases(ops, dim, keep_dim, dtype, out_dtype):
+    g = torch.Generator().manual_seed(29)
+    x = (torch.randn((10, 20, 30), generator=g) * 10.0).to(dtype)
+    d = None if dim is None else ([dim] if isinstance(dim, int) else list(dim))
+    got = torch.ops.hpu.sum_fp8(x.cuda(), d, keep_dim, out_dtype).cpu()
+    exact = torch.sum(x.to(torch.float64), d if d is not None else list(range(3)), keep_dim)
+    assert got.shape == exact.shape
+    if out_dtype:
+        assert got.dtype == out_dtype
+        # fp32 accumulation in a fixed order: within a few ulp of the exact sum
+        assert torch.allclose(got.double(), exact, rtol=4e-7, atol=4e-7 * float(x.float().abs().sum() / max(1, exact.numel())))
+    else:
+        assert got.dtype == dtype
+        want = O.sum_fp8(x, d, keep_dim, None)
+        steps = _fp8_steps_apart(got, want)
+        assert int(steps.max()) <= 1 and float((steps != 0).float().mean()) <= 0.02
+
+
+@pytest.mark.gpu
+def test_sum_fp8_large_and_deterministic(ops):
+    g = torch.Generator(device="cuda").manual_seed(1)
+    x = torch.randn(3, 1 << 20, device="cuda", generator=g).to(E4M3)
+    a = torch.ops.hpu.sum_fp8(x, [1], False, torch.float)
+    b = torch.ops.hpu.sum_fp8(x, [1], False, torch.float)
+    assert torch.equal(a, b)
+    exact = x.double().sum(1)
+    assert torch.allclose(a.double(), exact, rtol=1e-5, atol=1e-2)
+    tot = torch.ops.hpu.sum_fp8(x, None, False, torch.float)
+    assert tot.shape == () and abs(float(tot) - float(exact.sum())) < 0.05
+    col = torch.ops.hpu.sum_fp8(x, [0], True, torch.float)
+    assert col.shape == (1, 1 << 20) and torch.allclose(col.double(), x.double().sum(0, keepdim=True), atol=1e-5)
+    assert ops.device_status() == 0
+
+
+# ---------------------------------------------------------------- in_place_interleave_
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", [torch.bfloat16, E5M2, E4M3, torch.float32])
+@pytest.mark.parametrize("shape", [(8, 2, 2, 5), (4, 1, 1, 1), (64, 3, 5, 7), (1024, 2, 4, 8)])
+def test_in_place_interleave(ops, dtype, shape):
+    g = torch.Generator().manual_seed(shape[0])
+    x = (torch.randn(shape, generator=g) * 10.0).to(torch.bfloat16).to(dtype)
+    xc = x.cuda()
+    r = torch.ops.hpu.in_place_interleave_(xc)
+    assert r.data_ptr() == xc.data_ptr()
+    want = O.in_place_interleave(x.view(torch.uint8) if dtype in (E5M2, E4M3) else x)
+    got = xc.cpu().view(torch.uint8) if dtype in (E5M2, E4M3) else xc.cpu()
+    assert torch.equal(got, want)
+
+
+@pytest.mark.gpu
+def test_in_place_interleave_errors(ops):
+    with pytest.raises(RuntimeError, match="Input has to be a 4D tensor."):
+        torch.ops.hpu.in_place_interleave_(torch.zeros(8, 2, 2, device="cuda"))
+    with pytest.raises(RuntimeError, match="Batch size has to be a multiple of 4."):
+        torch.ops.hpu.in_place_interleave_(torch.zeros(6, 2, 2, 2, device="cuda"))
