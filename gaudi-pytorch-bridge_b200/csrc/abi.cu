@@ -66,6 +66,8 @@ int softmax_fp8_impl(const SoftmaxParams&, cudaStream_t);
 int sum_fp8_impl(const void*, int, void*, int, int64_t, int64_t, int64_t, void*, size_t, cudaStream_t);
 size_t sum_fp8_workspace_bytes_impl(int64_t, int64_t, int64_t);
 int in_place_interleave_impl(void*, int64_t, int64_t, cudaStream_t);
+int im2col_u8_impl(const void*, void*, int64_t, int64_t, int64_t, int64_t, int, int, int, int, int, int, int, int, int64_t, int64_t,
+                   int64_t, cudaStream_t);
 int amax_impl(const void*, int, int64_t, float*, cudaStream_t);
 int scale_from_amax_impl(const float*, float*, float*, float, int, int, cudaStream_t);
 int amax_history_impl(float*, int, int, const float*, int, float*, float*, float, int, int, cudaStream_t);
@@ -217,6 +219,11 @@ int b200q_sum_fp8(const void* in, int in_dtype, void* out, int out_dtype, int64_
 
 int b200q_in_place_interleave(void* data, int64_t n_rows, int64_t row_bytes, void* stream) {
   return in_place_interleave_impl(data, n_rows, row_bytes, static_cast<cudaStream_t>(stream));
+}
+
+int b200q_im2col_fp8(const void* in, void* out, int64_t N, int64_t C, int64_t H, int64_t W, int kh, int kw, int sh, int sw,
+                     int ph, int pw, int dh, int dw, int64_t c0, int64_t cg, int64_t ld_out, void* stream) {
+  return im2col_u8_impl(in, out, N, C, H, W, kh, kw, sh, sw, ph, pw, dh, dw, c0, cg, ld_out, static_cast<cudaStream_t>(stream));
 }
 
 int b200q_amax(const void* in, int in_dtype, int64_t n, float* amax, void* stream) {

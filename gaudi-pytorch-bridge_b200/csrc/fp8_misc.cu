@@ -387,4 +387,60 @@ int in_place_interleave_impl(void* data, int64_t n_rows, int64_t row_bytes, cuda
   return B200Q_OK;
 }
 
+// ---------------------------------------------------------------------------- im2col for conv2d_fp8
+// One-byte elements.  out[(n, ho, wo)][k], k = (c, i, j) over the channels [c0, c0 + cg) and the
+// kernel window, zero where the window leaves the image and for k in [cg * kh * kw, ld_out):
+// the K-major left operand of the GEMM that computes the convolution (K padded to ld_out).
+struct Im2colParams {
+  const uint8_t* in;
+  uint8_t* out;
+  int64_t N, C, H, W, Ho, Wo;
+  int kh, kw, sh, sw, ph, pw, dh, dw;
+  int64_t c0, cg, ld_out;
+};
+
+__global__ void __launch_bounds__(256) im2col_u8_kernel(const Im2colParams p) {
+  const int64_t words_per_row = p.ld_out >> 2;  // ld_out is a multiple of 16
+  const int64_t total = p.N * p.Ho * p.Wo * words_per_row;
+  const int64_t K = p.cg * p.kh * p.kw;
+  for (int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; t < total; t += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t row = t / words_per_row;
+    const int64_t k0 = (t % words_per_row) * 4;
+    const int64_t wo = row % p.Wo, ho = (row / p.Wo) % p.Ho, n = row / (p.Wo * p.Ho);
+    uint32_t word = 0;
+#pragma unroll
+    for (int b = 0; b < 4; ++b) {
+      const int64_t k = k0 + b;
+      if (k < K) {
+        const int64_t j = k % p.kw, i = (k / p.kw) % p.kh, c = p.c0 + k / (p.kw * p.kh);
+        const int64_t y = ho * p.sh - p.ph + i * p.dh, x = wo * p.sw - p.pw + j * p.dw;
+        if (y >= 0 && y < p.H && x >= 0 && x < p.W) word |= (uint32_t)p.in[((n * p.C + c) * p.H + y) * p.W + x] << (8 * b);
+      }
+    }
+    reinterpret_cast<uint32_t*>(p.out)[t] = word;
+  }
+}
+
+int im2col_u8_impl(const void* in, void* out, int64_t N, int64_t C, int64_t H, int64_t W, int kh, int kw, int sh, int sw,
+                   int ph, int pw, int dh, int dw, int64_t c0, int64_t cg, int64_t ld_out, cudaStream_t st) {
+  if (N < 0 || C < 0 || H < 0 || W < 0 || kh < 1 || kw < 1 || sh < 1 || sw < 1 || ph < 0 || pw < 0 || dh < 1 || dw < 1 ||
+      c0 < 0 || cg < 0 || c0 + cg > C || (ld_out & 15) || ld_out < cg * kh * kw)
+    return B200Q_ERR_BAD_ARGUMENT;
+  Im2colParams p;
+  p.in = static_cast<const uint8_t*>(in); p.out = static_cast<uint8_t*>(out);
+  p.N = N; p.C = C; p.H = H; p.W = W;
+  p.Ho = (H + 2 * ph - dh * (kh - 1) - 1) / sh + 1;
+  p.Wo = (W + 2 * pw - dw * (kw - 1) - 1) / sw + 1;
+  p.kh = kh; p.kw = kw; p.sh = sh; p.sw = sw; p.ph = ph; p.pw = pw; p.dh = dh; p.dw = dw;
+  p.c0 = c0; p.cg = cg; p.ld_out = ld_out;
+  if (p.Ho <= 0 || p.Wo <= 0 || N == 0) return B200Q_OK;
+  if (!in || !out) return B200Q_ERR_BAD_ARGUMENT;
+  const int64_t total = N * p.Ho * p.Wo * (ld_out >> 2);
+  int64_t blocks = (total + 255) / 256;
+  if (blocks > kNumSMs * 32) blocks = kNumSMs * 32;
+  im2col_u8_kernel<<<(int)blocks, 256, 0, st>>>(p);
+  B200Q_LAUNCH_CHECK();
+  return B200Q_OK;
+}
+
 }  // namespace b200q

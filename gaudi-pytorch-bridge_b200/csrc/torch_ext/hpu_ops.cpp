@@ -854,6 +854,94 @@ at::Tensor& in_place_interleave_(at::Tensor& self) {
   return self;
 }
 
+// ---- conv2d_fp8 (hpu_ops/backend/fp8_ops.cpp:547-705; schemas scripts/hpu_op.yaml:7371-7391) ----
+static std::vector<int64_t> expand2(at::IntArrayRef v, const char* name) {
+  TORCH_CHECK(v.size() == 1 || v.size() == 2, "conv2d_fp8: ", name, " must have 1 or 2 elements");
+  return v.size() == 1 ? std::vector<int64_t>{v[0], v[0]} : std::vector<int64_t>{v[0], v[1]};
+}
+static std::vector<int64_t> conv2d_out_shape(at::IntArrayRef in, at::IntArrayRef wt, const std::vector<int64_t>& stride,
+                                             const std::vector<int64_t>& padding, const std::vector<int64_t>& dilation) {
+  std::vector<int64_t> o{in[0], wt[0]};
+  for (int i = 0; i < 2; ++i) o.push_back((in[i + 2] + 2 * padding[i] - dilation[i] * (wt[i + 2] - 1) - 1) / stride[i] + 1);
+  return o;
+}
+
+// scale: absent, a one-element tensor, or a host scalar
+struct ConvScale {
+  OptTensor t;
+  double v = 1.0;
+  bool is_tensor = false;
+};
+
+at::Tensor conv2d_fp8_common(const at::Tensor& input, const at::Tensor& weight, const OptTensor& bias, at::IntArrayRef stride_,
+                             at::IntArrayRef padding_, at::IntArrayRef dilation_, int64_t groups,
+                             c10::optional<at::ScalarType> out_dtype_, const ConvScale& s_in, const ConvScale& s_w) {
+  TORCH_CHECK(input.dim() == 4 && weight.dim() == 4, "Input and weight must be 4D tensors");
+  if (bias.has_value() && bias->defined())
+    TORCH_CHECK(bias->dim() == 1 && bias->size(0) == weight.size(0), "Bias must be 1D tensor with size equal to weight dim0");
+  TORCH_CHECK(is_fp8(input.scalar_type()) && is_fp8(weight.scalar_type()), "conv2d_fp8: input and weight must be float8 tensors");
+  for (const ConvScale* sc : {&s_in, &s_w})
+    if (sc->is_tensor) TORCH_CHECK(sc->t->numel() == 1, "Multi-element scale tensors are not supported yet.");
+  const auto stride = expand2(stride_, "stride"), padding = expand2(padding_, "padding"), dilation = expand2(dilation_, "dilation");
+  const at::ScalarType odt = out_dtype_.value_or(at::kBFloat16);
+  TORCH_CHECK(odt == at::kBFloat16 || odt == at::kFloat, "conv2d_fp8: out_dtype must be bfloat16 or float");
+  const int64_t N = input.size(0), C = input.size(1), H = input.size(2), W = input.size(3);
+  const int64_t Co = weight.size(0), Cg = weight.size(1), kh = weight.size(2), kw = weight.size(3);
+  TORCH_CHECK(groups >= 1 && C == Cg * groups && Co % groups == 0, "conv2d_fp8: channels do not match groups");
+  const auto oshape = conv2d_out_shape(input.sizes(), weight.sizes(), stride, padding, dilation);
+  const int64_t Ho = oshape[2], Wo = oshape[3];
+  TORCH_CHECK(Ho > 0 && Wo > 0, "conv2d_fp8: empty output");
+  c10::cuda::CUDAGuard guard(input.device());
+  at::Tensor in = input.contiguous(), w = weight.contiguous();
+  const int64_t K = Cg * kh * kw, Kp = (K + 15) / 16 * 16, rows = N * Ho * Wo, Cog = Co / groups;
+  // scales: both host scalars -> the .scalar GEMM entry; otherwise one-element tensors
+  auto as_tensor = [&](const ConvScale& sc) {
+    if (sc.is_tensor) return sc.t->to(in.device()).to(at::kFloat).reshape({1});
+    return at::full({1}, sc.v, in.options().dtype(at::kFloat));
+  };
+  const bool host_scales = !s_in.is_tensor && !s_w.is_tensor;
+  at::Tensor ts_in, ts_w;
+  if (!host_scales) { ts_in = as_tensor(s_in); ts_w = as_tensor(s_w); }
+  std::vector<at::Tensor> parts;
+  for (int64_t g = 0; g < groups; ++g) {
+    at::Tensor cols = at::empty({rows, Kp}, in.options());
+    check_status(b200q_im2col_fp8(in.data_ptr(), cols.data_ptr(), N, C, H, W, (int)kh, (int)kw, (int)stride[0], (int)stride[1],
+                                  (int)padding[0], (int)padding[1], (int)dilation[0], (int)dilation[1], g * Cg, Cg, Kp,
+                                  current_stream()),
+                 "conv2d_fp8 (im2col)");
+    at::Tensor wg = w.narrow(0, g * Cog, Cog).reshape({Cog, K});
+    if (Kp != K) {
+      at::Tensor wp = at::zeros({Cog, Kp}, w.options().dtype(at::kByte));
+      wp.narrow(1, 0, K).copy_(wg.view(at::kByte));
+      wg = wp.view(w.scalar_type());
+    }
+    OptTensor bg;
+    if (bias.has_value() && bias->defined()) bg = bias->narrow(0, g * Cog, Cog).to(odt);
+    at::Tensor o2 = host_scales ? fp8_gemm_v2_scalar(cols, false, wg, true, c10::nullopt, odt, s_in.v, s_w.v, bg, false, c10::nullopt)
+                                : fp8_gemm_v2(cols, false, wg, true, c10::nullopt, odt, ts_in, ts_w, bg, false, c10::nullopt);
+    parts.push_back(o2);
+  }
+  at::Tensor out2d = groups == 1 ? parts[0] : at::cat(parts, 1);
+  // [N*Ho*Wo, Co] is the channels-last image: return it as an NCHW-shaped view
+  return out2d.view({N, Ho, Wo, Co}).permute({0, 3, 1, 2});
+}
+at::Tensor conv2d_fp8(const at::Tensor& input, const at::Tensor& weight, const OptTensor& bias, at::IntArrayRef stride,
+                      at::IntArrayRef padding, at::IntArrayRef dilation, int64_t groups, c10::optional<at::ScalarType> out_dtype,
+                      const OptTensor& scale_input, const OptTensor& scale_weight) {
+  ConvScale a, b;
+  if (scale_input.has_value() && scale_input->defined()) { a.t = scale_input; a.is_tensor = true; }
+  if (scale_weight.has_value() && scale_weight->defined()) { b.t = scale_weight; b.is_tensor = true; }
+  return conv2d_fp8_common(input, weight, bias, stride, padding, dilation, groups, out_dtype, a, b);
+}
+at::Tensor conv2d_fp8_scalar(const at::Tensor& input, const at::Tensor& weight, const OptTensor& bias, at::IntArrayRef stride,
+                             at::IntArrayRef padding, at::IntArrayRef dilation, int64_t groups,
+                             c10::optional<at::ScalarType> out_dtype, double scale_input, double scale_weight) {
+  ConvScale a, b;
+  a.v = scale_input;
+  b.v = scale_weight;
+  return conv2d_fp8_common(input, weight, bias, stride, padding, dilation, groups, out_dtype, a, b);
+}
+
 // ---- FP8 scale management (lazy_optimizer_kernels.cpp:113-126) ----
 static float fp8_max_of(at::ScalarType dtype) {
   TORCH_CHECK(is_fp8(dtype), "fp8 dtype must be float8_e5m2 or float8_e4m3fn, got ", dtype);
@@ -978,6 +1066,8 @@ TORCH_LIBRARY(hpu, m) {
   m.def("fp8_gemm(Tensor A, bool trans_A, Tensor B, bool trans_B, Tensor D, ScalarType out_dtype, Tensor? A_scale_inv, Tensor? B_scale_inv, Tensor? bias, bool accumulate, Tensor(a!) out) -> Tensor(a!)");
   m.def("fp8_gemm_v2(Tensor A, bool trans_A, Tensor B, bool trans_B, Tensor? D, ScalarType out_dtype, Tensor? A_scale_inv=None, Tensor? B_scale_inv=None, Tensor? bias=None, bool accumulate=False, int[]? B_scale_shape=None) -> Tensor");
   m.def("fp8_gemm_v2.scalar(Tensor A, bool trans_A, Tensor B, bool trans_B, Tensor? D, ScalarType out_dtype, float A_scale_inv, float B_scale_inv, Tensor? bias=None, bool accumulate=False, int[]? B_scale_shape=None) -> Tensor");
+  m.def("conv2d_fp8(Tensor input, Tensor weight, Tensor? bias=None, SymInt[2] stride=1, SymInt[2] padding=0, SymInt[2] dilation=1, int groups=1, ScalarType? out_dtype=None, Tensor? scale_input=None, Tensor? scale_weight=None) -> Tensor");
+  m.def("conv2d_fp8.scalar(Tensor input, Tensor weight, Tensor? bias=None, SymInt[2] stride=1, SymInt[2] padding=0, SymInt[2] dilation=1, int groups=1, ScalarType? out_dtype=None, float scale_input=1.0, float scale_weight=1.0) -> Tensor");
   m.def("softmax_fp8(Tensor input, int dim, Tensor? input_scale=None, Tensor? output_scale=None, Tensor? inv_attn_heads=None, Tensor? fused_add=None) -> Tensor");
   m.def("softmax_fp8.Scalar_scales(Tensor input, int dim, float input_scale, float output_scale, Tensor? inv_attn_heads=None, Tensor? fused_add=None) -> Tensor");
   m.def("softmax_fp8.Scalar(Tensor input, int dim, float input_scale, float output_scale, float inv_attn_heads, Tensor? fused_add=None) -> Tensor");
@@ -997,6 +1087,8 @@ TORCH_LIBRARY_IMPL(hpu, CUDA, m) {
   m.impl("cast_from_fp8", cast_from_fp8);
   m.impl("cast_from_fp8.scalar", cast_from_fp8_scalar);
   m.impl("cast_from_fp8.scalar_list", cast_from_fp8_scalar_list);
+  m.impl("conv2d_fp8", conv2d_fp8);
+  m.impl("conv2d_fp8.scalar", conv2d_fp8_scalar);
   m.impl("softmax_fp8", softmax_fp8);
   m.impl("softmax_fp8.Scalar_scales", softmax_fp8_scalar_scales);
   m.impl("softmax_fp8.Scalar", softmax_fp8_scalar);
@@ -1033,8 +1125,24 @@ at::Tensor meta_sum_fp8(const at::Tensor& self, at::OptionalIntArrayRef dim, boo
   return at::empty(shape, self.options().dtype(out_dtype.value_or(self.scalar_type())));
 }
 at::Tensor& meta_in_place_interleave_(at::Tensor& self) { return self; }
+// fp8_ops.cpp:594-612 (Conv2dFp8Meta)
+at::Tensor meta_conv2d_fp8(const at::Tensor& input, const at::Tensor& weight, const OptTensor&, at::IntArrayRef stride,
+                           at::IntArrayRef padding, at::IntArrayRef dilation, int64_t, c10::optional<at::ScalarType> out_dtype,
+                           const OptTensor&, const OptTensor&) {
+  TORCH_CHECK(input.dim() == 4 && weight.dim() == 4, "Input and weight must be 4D tensors");
+  return at::empty(conv2d_out_shape(input.sizes(), weight.sizes(), expand2(stride, "stride"), expand2(padding, "padding"),
+                                    expand2(dilation, "dilation")),
+                   input.options().dtype(out_dtype.value_or(at::kBFloat16)));
+}
+at::Tensor meta_conv2d_fp8_scalar(const at::Tensor& input, const at::Tensor& weight, const OptTensor& b, at::IntArrayRef stride,
+                                  at::IntArrayRef padding, at::IntArrayRef dilation, int64_t g,
+                                  c10::optional<at::ScalarType> out_dtype, double, double) {
+  return meta_conv2d_fp8(input, weight, b, stride, padding, dilation, g, out_dtype, c10::nullopt, c10::nullopt);
+}
 
 TORCH_LIBRARY_IMPL(hpu, Meta, m) {
+  m.impl("conv2d_fp8", meta_conv2d_fp8);
+  m.impl("conv2d_fp8.scalar", meta_conv2d_fp8_scalar);
   m.impl("softmax_fp8", meta_softmax_fp8);
   m.impl("softmax_fp8.Scalar_scales", meta_softmax_fp8_scalar_scales);
   m.impl("softmax_fp8.Scalar", meta_softmax_fp8_scalar);

@@ -17,10 +17,9 @@
 //   warp 1        MMA issuer: tcgen05.mma.kind::f16 (bf16 x bf16 -> fp32 in TMEM)
 //   warps 2..5    epilogue: tcgen05.ld, convert, store (or fp32 partials for split-K)
 //
-// SWAP = false (large M): lanes <- 128 tokens, columns <- BN weight columns.
-// SWAP = true  (small M): lanes <- 128 weight columns, columns <- BN tokens; K is split over
-//              several CTAs per tile so that every SM streams weights, and the fp32 partial
-//              tiles are summed by a second kernel (deterministic: no atomics).
+// Lanes <- 128 tokens, columns <- BN weight columns.  Small M (<= 128): only AR token rows are
+// loaded (see Cfg), K is split over several CTAs per tile so that every SM streams weights, and
+// the fp32 partial tiles are summed by a second kernel (deterministic: no atomics).
 #include <cuda.h>
 
 #include <cstdlib>
@@ -55,15 +54,15 @@ struct Params {
   int* status;
 };
 
-template <int BN, bool SWAP, int STAGES, int GROUPS, int AR = 0, int EW = 0>
+template <int BN, int STAGES, int GROUPS, int AR = 0, int EW = 0>
 struct Cfg {
-  static constexpr int kUnits = SWAP ? 1 : BN / kUnit;
-  // Activation rows held per stage.  The MMA always reads 128 rows (SWAP: BN rows) through its
+  static constexpr int kUnits = BN / kUnit;
+  // Activation rows held per stage.  The MMA always reads 128 rows through its
   // descriptor; with AR < 128 in the token-major form the rows beyond AR are whatever follows in
   // the stage (packed weights, the expanded tile).  Each output row depends on its own operand
   // row only, and rows >= M are never stored, so for M <= AR nothing needs to be there.
-  static constexpr int kActRows = AR ? AR : (SWAP ? BN : 128);
-  static_assert(AR == 0 || (!SWAP && AR <= 128 && AR % 8 == 0), "narrow activation tiles: token-major form only");
+  static constexpr int kActRows = AR ? AR : 128;
+  static_assert(AR == 0 || (AR <= 128 && AR % 8 == 0), "narrow activation tile: a multiple of 8 rows");
   static constexpr int kActBytes = kActRows * 128;
   static constexpr int kRawBytes = kUnits * kRawUnit;
   // group scales (bf16) and packed zero points of the stage's k-group ride in the same ring:
@@ -137,11 +136,11 @@ __device__ __forceinline__ void make_group(GroupRegs& g, uint4 s, uint32_t zw, b
   for (int i = 0; i < 4; ++i) g.zr[i] = has_zp ? nib_pair(zw, i) : 0x43004300u;
 }
 
-template <int BN, bool SWAP, int STAGES, int GROUPS, int AR = 0, int EW = 0>
-__global__ void __launch_bounds__((Cfg<BN, SWAP, STAGES, GROUPS, AR, EW>::kThreads), 1)
+template <int BN, int STAGES, int GROUPS, int AR = 0, int EW = 0>
+__global__ void __launch_bounds__((Cfg<BN, STAGES, GROUPS, AR, EW>::kThreads), 1)
 w4a16_kernel(const __grid_constant__ CUtensorMap map_act, const __grid_constant__ CUtensorMap map_raw,
              const __grid_constant__ CUtensorMap map_scale, const __grid_constant__ CUtensorMap map_zp, const Params p) {
-  using C = Cfg<BN, SWAP, STAGES, GROUPS, AR, EW>;
+  using C = Cfg<BN, STAGES, GROUPS, AR, EW>;
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::kBarOffset);
@@ -222,8 +221,8 @@ w4a16_kernel(const __grid_constant__ CUtensorMap map_act, const __grid_constant_
       for (int w = blockIdx.x; w < num_work && ok; w += gridDim.x) {
         int xt, yt, kb0, kb1, split;
         decode(w, xt, yt, kb0, kb1, split);
-        const int act_row0 = (SWAP ? yt * BN : xt * 128);
-        const int n0 = (SWAP ? xt * 128 : yt * BN);
+        const int act_row0 = xt * 128;
+        const int n0 = yt * BN;
         for (int kb = kb0; kb < kb1; ++kb) {
           if (!mbar_wait(bar_empty + 8 * stage, phase ^ 1, abort_flag, p.status, kErrProducer)) {
             ok = false;
@@ -249,8 +248,8 @@ w4a16_kernel(const __grid_constant__ CUtensorMap map_act, const __grid_constant_
   } else if (role == kMma) {
     // ------------------------------------------------------------ MMA issuer
     if (lane == 0) {
-      // bf16 x bf16; the expanded weights are the MN-major operand (A when swapped, else B)
-      const uint32_t idesc = umma_idesc_major(1u, 1u, 128, BN, SWAP ? 1u : 0u, SWAP ? 0u : 1u);
+      // bf16 x bf16; the expanded weights are the MN-major B operand
+      const uint32_t idesc = umma_idesc_major(1u, 1u, 128, BN, 0u, 1u);
       const uint64_t da0 = smem_desc_k_sw128(smem_base);
       const uint64_t dw0 = smem_desc_mn_sw128(smem_base + C::kWOffset, (kK / 8) * 1024, 1024);
       uint32_t stage = 0, phase = 0, ready = 0;
@@ -279,9 +278,8 @@ w4a16_kernel(const __grid_constant__ CUtensorMap map_act, const __grid_constant_
           const uint32_t nphase = nstage == 0 ? phase ^ 1 : phase;
           static_assert(kK / 16 == 4, "umma_stage4_probe issues 4 MMAs");
           constexpr uint64_t kActStep = kUmmaKBytes >> 4, kWStep = 2048 >> 4;
-          ready = umma_stage4_probe<true, false>(d_tmem, SWAP ? dw : da, SWAP ? da : dw, idesc, kb != kb0,
-                                                 bar_empty + 8 * stage, bar_ready + 8 * nstage, nphase,
-                                                 SWAP ? kWStep : kActStep, SWAP ? kActStep : kWStep);
+          ready = umma_stage4_probe<true, false>(d_tmem, da, dw, idesc, kb != kb0, bar_empty + 8 * stage,
+                                                 bar_ready + 8 * nstage, nphase, kActStep, kWStep);
           stage = nstage;
           phase = nphase;
         }
@@ -305,10 +303,9 @@ w4a16_kernel(const __grid_constant__ CUtensorMap map_act, const __grid_constant_
       tc_fence_after();
       const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16) + acc * BN;
       // The weight columns inside every group of 8 sit at tile positions (0,4,1,5,2,6,3,7) (the
-      // order the nibble pairs were stored in): position p holds column (p >> 1) + 4 * (p & 1).
-      const int pos = q * 32 + lane;
-      const int64_t x = (int64_t)xt * 128 +
-                        (SWAP ? (pos & ~7) + ((pos & 7) >> 1) + 4 * (pos & 1) : pos);  // token, or weight column n
+      // order the nibble pairs were stored in): position p holds column (p >> 1) + 4 * (p & 1);
+      // the registers read from TMEM are renamed into column order below.
+      const int64_t m = (int64_t)xt * 128 + q * 32 + lane;  // this thread's token
       const int64_t y0 = (int64_t)yt * BN;
       constexpr int CW = (BN % 32 == 0) ? 32 : 16;
 #pragma unroll 1
@@ -317,57 +314,41 @@ w4a16_kernel(const __grid_constant__ CUtensorMap map_act, const __grid_constant_
         if (BN % 32 == 0) tmem_ld_32x32(t_row + c0, r);
         else tmem_ld_32x16(t_row + c0, r);
         tmem_ld_wait();
-        if (!SWAP) {
-          // registers are in tile-position order: rename them into column order (free: all static)
-          {
-            uint32_t t[32];
+        // registers are in tile-position order: rename them into column order (free: all static)
+        {
+          uint32_t t[32];
 #pragma unroll
-            for (int j = 0; j < CW; ++j) t[(j & ~7) + ((j & 7) >> 1) + 4 * (j & 1)] = r[j];
+          for (int j = 0; j < CW; ++j) t[(j & ~7) + ((j & 7) >> 1) + 4 * (j & 1)] = r[j];
 #pragma unroll
-            for (int j = 0; j < CW; ++j) r[j] = t[j];
-          }
-          const int64_t m = x, n0 = y0 + c0;
-          if (m < p.M) {
-            if (p.splits > 1) {
-              float* o = p.partial + ((int64_t)split * p.M + m) * p.N + n0;
+          for (int j = 0; j < CW; ++j) r[j] = t[j];
+        }
+        const int64_t n0 = y0 + c0;
+        if (m < p.M) {
+          if (p.splits > 1) {
+            float* o = p.partial + ((int64_t)split * p.M + m) * p.N + n0;
 #pragma unroll
-              for (int j = 0; j < CW; ++j)
-                if (n0 + j < p.N) o[j] = __uint_as_float(r[j]);
-            } else if (p.out_dtype == B200Q_BF16) {
-              __nv_bfloat16* o = static_cast<__nv_bfloat16*>(p.out) + m * p.ldo + n0;
-              if (n0 + CW <= p.N && (reinterpret_cast<uintptr_t>(o) & 15) == 0) {
+            for (int j = 0; j < CW; ++j)
+              if (n0 + j < p.N) o[j] = __uint_as_float(r[j]);
+          } else if (p.out_dtype == B200Q_BF16) {
+            __nv_bfloat16* o = static_cast<__nv_bfloat16*>(p.out) + m * p.ldo + n0;
+            if (n0 + CW <= p.N && (reinterpret_cast<uintptr_t>(o) & 15) == 0) {
 #pragma unroll
-                for (int j = 0; j < CW; j += 8)
-                  *reinterpret_cast<uint4*>(o + j) = make_uint4(
-                      pack_bf16x2(__uint_as_float(r[j]), __uint_as_float(r[j + 1])),
-                      pack_bf16x2(__uint_as_float(r[j + 2]), __uint_as_float(r[j + 3])),
-                      pack_bf16x2(__uint_as_float(r[j + 4]), __uint_as_float(r[j + 5])),
-                      pack_bf16x2(__uint_as_float(r[j + 6]), __uint_as_float(r[j + 7])));
-              } else {
-#pragma unroll
-                for (int j = 0; j < CW; ++j)
-                  if (n0 + j < p.N) o[j] = __float2bfloat16_rn(__uint_as_float(r[j]));
-              }
+              for (int j = 0; j < CW; j += 8)
+                *reinterpret_cast<uint4*>(o + j) = make_uint4(
+                    pack_bf16x2(__uint_as_float(r[j]), __uint_as_float(r[j + 1])),
+                    pack_bf16x2(__uint_as_float(r[j + 2]), __uint_as_float(r[j + 3])),
+                    pack_bf16x2(__uint_as_float(r[j + 4]), __uint_as_float(r[j + 5])),
+                    pack_bf16x2(__uint_as_float(r[j + 6]), __uint_as_float(r[j + 7])));
             } else {
-              float* o = static_cast<float*>(p.out) + m * p.ldo + n0;
 #pragma unroll
               for (int j = 0; j < CW; ++j)
-                if (n0 + j < p.N) o[j] = __uint_as_float(r[j]);
+                if (n0 + j < p.N) o[j] = __float2bfloat16_rn(__uint_as_float(r[j]));
             }
-          }
-        } else {
-          const int64_t n = x;
-          if (n < p.N) {
+          } else {
+            float* o = static_cast<float*>(p.out) + m * p.ldo + n0;
 #pragma unroll
-            for (int j = 0; j < CW; ++j) {
-              const int64_t m = y0 + c0 + j;
-              if (m < p.M) {
-                const float v = __uint_as_float(r[j]);
-                if (p.splits > 1) p.partial[((int64_t)split * p.M + m) * p.N + n] = v;
-                else if (p.out_dtype == B200Q_BF16) static_cast<__nv_bfloat16*>(p.out)[m * p.ldo + n] = __float2bfloat16_rn(v);
-                else static_cast<float*>(p.out)[m * p.ldo + n] = v;
-              }
-            }
+            for (int j = 0; j < CW; ++j)
+              if (n0 + j < p.N) o[j] = __uint_as_float(r[j]);
           }
         }
       }
@@ -800,15 +781,15 @@ __global__ void __launch_bounds__(256) splitk_reduce_kernel(const float* __restr
   }
 }
 
-template <int BN, bool SWAP, int STAGES, int GROUPS, int AR = 0, int EW = 0>
+template <int BN, int STAGES, int GROUPS, int AR = 0, int EW = 0>
 static int launch(const CUtensorMap& ma, const CUtensorMap& mr, const CUtensorMap& ms, const CUtensorMap& mz, const Params& p,
                   cudaStream_t st) {
-  using C = Cfg<BN, SWAP, STAGES, GROUPS, AR, EW>;
+  using C = Cfg<BN, STAGES, GROUPS, AR, EW>;
   constexpr int smem = C::kTotal + 1024;
   static_assert(smem <= 227 * 1024, "shared memory budget");
   // TMEM: CTAs that share an SM must never ask for more than 512 columns together
   static_assert(C::kTmemCols * (227 * 1024 / smem) <= 512, "TMEM over-subscription");
-  auto kern = w4a16_kernel<BN, SWAP, STAGES, GROUPS, AR, EW>;
+  auto kern = w4a16_kernel<BN, STAGES, GROUPS, AR, EW>;
   static std::atomic<int> configured[kMaxDevices];
   const int dev = current_device_index();
   if (dev < 0) return B200Q_ERR_CUDA;
@@ -871,8 +852,8 @@ int w4a16_gemm_impl(const void* x, int64_t ldx, const int32_t* qweight, const vo
   p.out_dtype = out_dtype; p.num_kb = (int)(K / w4::kK);
   p.status = device_status_ptr();
   if (!p.status) return B200Q_ERR_CUDA;
-  const bool swap = M <= 128;
-  p.splits = swap ? w4a16_splits(M, N, K) : 1;
+  const bool small_m = M <= 128;
+  p.splits = small_m ? w4a16_splits(M, N, K) : 1;
   p.kb_per_split = (p.num_kb + p.splits - 1) / p.splits;
   if (p.splits > 1) {
     const size_t need = (size_t)p.splits * (size_t)M * (size_t)N * sizeof(float);
@@ -881,7 +862,7 @@ int w4a16_gemm_impl(const void* x, int64_t ldx, const int32_t* qweight, const vo
   }
   CUtensorMap ma, mr;
   int rc = 0;
-  const int bn_w = (!swap && N > 128) ? 256 : 128;  // weight columns per stage tile
+  const int bn_w = (!small_m && N > 128) ? 256 : 128;  // weight columns per stage tile
   rc = make_tma_map_2d(&mr, qweight, CU_TENSOR_MAP_DATA_TYPE_INT32, 4, N / 8, K, (N / 8) * 4, bn_w / 8, w4::kK,
                        CU_TENSOR_MAP_SWIZZLE_NONE);
   if (rc) return rc;
@@ -897,7 +878,7 @@ int w4a16_gemm_impl(const void* x, int64_t ldx, const int32_t* qweight, const vo
     mz = ms;  // never dereferenced
   }
   static const bool no_pairs = std::getenv("B200Q_W4A16_NO_PAIRS") != nullptr;
-  if (!swap && bn_w == 256 && M > 128 && !no_pairs) {
+  if (bn_w == 256 && !no_pairs) {
     // CTA pairs: 256-token x 256-column tiles, each CTA expands 128 columns
     w4::Params pp = p;
     pp.x_tiles = (int)((M + 255) / 256);
@@ -921,15 +902,15 @@ int w4a16_gemm_impl(const void* x, int64_t ldx, const int32_t* qweight, const vo
     else rc = w4::launch_pair<6, 2>(ma, mr1, ms1, mz1, pp, st);
     if (rc != B200Q_ERR_UNSUPPORTED) return rc;
   }
-  if (!swap) {
+  if (!small_m) {
     p.x_tiles = (int)((M + 127) / 128);
     const int bn = bn_w;
     p.y_tiles = (int)((N + bn - 1) / bn);
     rc = make_tma_map_2d(&ma, x, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, K, M, ldx * 2, w4::kK, 128, CU_TENSOR_MAP_SWIZZLE_128B);
     if (rc) return rc;
-    if (bn == 256) rc = w4::launch<256, false, 3, 1>(ma, mr, ms, mz, p, st);
-    else rc = w4::launch<128, false, 6, 2>(ma, mr, ms, mz, p, st);
-  } else if (std::getenv("B200Q_W4A16_SWAP") == nullptr) {
+    if (bn == 256) rc = w4::launch<256, 3, 1>(ma, mr, ms, mz, p, st);
+    else rc = w4::launch<128, 6, 2>(ma, mr, ms, mz, p, st);
+  } else {
     // small M, token-major with a narrow activation tile: 128 x 256 MMAs cover twice the weight
     // columns per instruction of the weight-major form, whose issue rate is what bounds it
     p.x_tiles = 1;
@@ -950,24 +931,10 @@ int w4a16_gemm_impl(const void* x, int64_t ldx, const int32_t* qweight, const vo
     rc = make_tma_map_2d(&ma, x, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, K, M, ldx * 2, w4::kK, ar, CU_TENSOR_MAP_SWIZZLE_128B);
     if (rc) return rc;
     switch (ar) {
-      case 16: rc = w4::launch<256, false, 5, 2, 16, 8>(ma, mr2, ms2, mz2, p, st); break;
-      case 32: rc = w4::launch<256, false, 5, 2, 32, 8>(ma, mr2, ms2, mz2, p, st); break;
-      case 64: rc = w4::launch<256, false, 4, 2, 64, 8>(ma, mr2, ms2, mz2, p, st); break;
-      default: rc = w4::launch<256, false, 3, 1>(ma, mr2, ms2, mz2, p, st); break;
-    }
-  } else {
-    p.x_tiles = (int)((N + 127) / 128);
-    const int bn = M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : 128;
-    p.splits = 1;  // (weight-major form kept for comparison only)
-    p.kb_per_split = p.num_kb;
-    p.y_tiles = (int)((M + bn - 1) / bn);
-    rc = make_tma_map_2d(&ma, x, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, K, M, ldx * 2, w4::kK, bn, CU_TENSOR_MAP_SWIZZLE_128B);
-    if (rc) return rc;
-    switch (bn) {
-      case 16: rc = w4::launch<16, true, 8, 2>(ma, mr, ms, mz, p, st); break;
-      case 32: rc = w4::launch<32, true, 8, 2>(ma, mr, ms, mz, p, st); break;
-      case 64: rc = w4::launch<64, true, 7, 2>(ma, mr, ms, mz, p, st); break;
-      default: rc = w4::launch<128, true, 6, 2>(ma, mr, ms, mz, p, st); break;
+      case 16: rc = w4::launch<256, 5, 2, 16, 8>(ma, mr2, ms2, mz2, p, st); break;
+      case 32: rc = w4::launch<256, 5, 2, 32, 8>(ma, mr2, ms2, mz2, p, st); break;
+      case 64: rc = w4::launch<256, 4, 2, 64, 8>(ma, mr2, ms2, mz2, p, st); break;
+      default: rc = w4::launch<256, 3, 1>(ma, mr2, ms2, mz2, p, st); break;
     }
   }
   if (rc) return rc;

@@ -332,6 +332,18 @@ int b200q_sum_fp8(const void* in, int in_dtype, void* out, int out_dtype, int64_
  */
 int b200q_in_place_interleave(void* data, int64_t n_rows, int64_t row_bytes, void* stream);
 
+/*
+ * im2col for conv2d_fp8 (hpu_ops/backend/fp8_ops.cpp:547-705: the reference hands the convolution
+ * to one MME node; here it is this gather followed by b200q_fp8_gemm against the weight viewed as
+ * [C_out][C_g * kh * kw]).  in: one-byte elements [N][C][H][W]; out: [N * Ho * Wo][ld_out] with
+ * column k = (c - c0, i, j) over the channels [c0, c0 + cg) and the kh x kw window (stride sh/sw,
+ * padding ph/pw, dilation dh/dw), zero outside the image and for k >= cg * kh * kw.
+ * ld_out: a multiple of 16, >= cg * kh * kw.  Ho = (H + 2 ph - dh (kh - 1) - 1) / sh + 1, Wo alike.
+ */
+int b200q_im2col_fp8(const void* in, void* out, int64_t N, int64_t C, int64_t H, int64_t W, int kh,
+                     int kw, int sh, int sw, int ph, int pw, int dh, int dw, int64_t c0, int64_t cg,
+                     int64_t ld_out, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

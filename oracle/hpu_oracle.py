@@ -472,6 +472,26 @@ def sum_fp8(input, dim=None, keepdim=False, out_dtype=None):
     return _rne_to_fp8(s, od) if od in FP8_MAX else s.to(od)
 
 
+def conv2d_fp8(input, weight, bias=None, stride=1, padding=0, dilation=1, groups=1, out_dtype=None, scale_input=None,
+               scale_weight=None):
+    """hpu_ops/backend/fp8_ops.cpp:547-705: ``conv2d(input, weight) * scale_input * scale_weight + bias``
+    on fp8 operands, fp32 accumulation, result in ``out_dtype`` (bf16 when None)."""
+    if input.dim() != 4 or weight.dim() != 4:
+        raise RuntimeError("Input and weight must be 4D tensors")
+    if bias is not None and (bias.dim() != 1 or bias.shape[0] != weight.shape[0]):
+        raise RuntimeError("Bias must be 1D tensor with size equal to weight dim0")
+    for sc in (scale_input, scale_weight):
+        if isinstance(sc, torch.Tensor) and sc.numel() != 1:
+            raise RuntimeError("Multi-element scale tensors are not supported yet.")
+    od = out_dtype or torch.bfloat16
+    y = torch.nn.functional.conv2d(input.to(torch.float64), weight.to(torch.float64), None, stride, padding, dilation, groups).float()
+    f32 = lambda v: torch.ones((), dtype=torch.float32) if v is None else torch.as_tensor(v, dtype=torch.float32).reshape(())  # noqa: E731
+    y = (y * f32(scale_input)) * f32(scale_weight)
+    if bias is not None:
+        y = y + bias.float().reshape(1, -1, 1, 1)
+    return y.to(od)
+
+
 def in_place_interleave(input):
     """hpu_ops/backend/fp8_ops.cpp:498-545 with the semantics its test pins
     (test_hpu_fp8_ops_any_mode.py:795-824): row j of the 4-D input becomes row j // 4."""

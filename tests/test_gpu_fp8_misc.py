@@ -149,3 +149,60 @@ def test_in_place_interleave_errors(ops):
         torch.ops.hpu.in_place_interleave_(torch.zeros(8, 2, 2, device="cuda"))
     with pytest.raises(RuntimeError, match="Batch size has to be a multiple of 4."):
         torch.ops.hpu.in_place_interleave_(torch.zeros(6, 2, 2, 2, device="cuda"))
+
+
+# ---------------------------------------------------------------- conv2d_fp8
+@pytest.mark.gpu
+@pytest.mark.parametrize("scaleA", [True, False])
+@pytest.mark.parametrize("scaleB", [True, False])
+@pytest.mark.parametrize("bias", [True, False])
+@pytest.mark.parametrize("out_dtype", [torch.float, torch.bfloat16])
+@pytest.mark.parametrize("fp8_dtype", [E5M2, E4M3])
+def test_conv2d_fp8_reference_case(ops, scaleA, scaleB, bias, out_dtype, fp8_dtype):
+    """test_hpu_fp8_ops_any_mode.py:830-897: N,C,H,W = 8,3,28,28, 16 output channels, 2x2 kernel."""
+    g = torch.Generator().manual_seed(41)
+    x = torch.rand((8, 3, 28, 28), generator=g).to(out_dtype).to(fp8_dtype)
+    w = torch.rand((16, 3, 2, 2), generator=g).to(out_dtype).to(fp8_dtype)
+    b = torch.rand(16, generator=g).to(out_dtype).to(fp8_dtype).to(out_dtype) if bias else None
+    sa = torch.tensor(1.4).to(out_dtype) if scaleA else None
+    sb = torch.tensor(2.3).to(out_dtype) if scaleB else None
+    cu = lambda t: None if t is None else t.cuda()  # noqa: E731
+    args = [x.cuda(), w.cuda(), cu(b), (1, 1), (0, 0), (1,), 1, out_dtype]
+    if sa is not None or sb is not None:
+        args += [cu(sa), cu(sb)]
+    got = torch.ops.hpu.conv2d_fp8(*args).cpu()
+    want = O.conv2d_fp8(x, w, b, (1, 1), (0, 0), (1, 1), 1, out_dtype, sa, sb)
+    assert got.shape == want.shape == (8, 16, 27, 27) and got.dtype == out_dtype
+    assert O.rel_frobenius(got, want) <= (1e-2 if out_dtype == torch.bfloat16 else 1e-5)
+    # the reference test's own bound
+    ref = torch.nn.functional.conv2d(x.to(out_dtype), w.to(out_dtype), None, (1, 1), (0, 0), (1, 1), 1)
+    ref = ref * ((sa if sa is not None else 1) * (sb if sb is not None else 1))
+    if b is not None:
+        ref = ref + b.reshape(1, -1, 1, 1)
+    rtol = 0.02 if (out_dtype == torch.bfloat16 and (scaleA or scaleB)) else 1e-2
+    assert torch.allclose(got.float(), ref.float(), atol=1e-2, rtol=rtol)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("cfg", [
+    dict(N=2, C=32, H=17, W=19, Co=48, k=(3, 3), stride=(2, 1), padding=(1, 2), dilation=(1, 2), groups=1),
+    dict(N=3, C=16, H=9, W=9, Co=24, k=(3, 1), stride=(1, 1), padding=(0, 0), dilation=(1, 1), groups=4),
+    dict(N=1, C=64, H=14, W=14, Co=128, k=(1, 1), stride=(1, 1), padding=(0, 0), dilation=(1, 1), groups=1),
+])
+def test_conv2d_fp8_shapes_and_scalar_overload(ops, cfg):
+    g = torch.Generator().manual_seed(cfg["C"])
+    x = torch.randn((cfg["N"], cfg["C"], cfg["H"], cfg["W"]), generator=g).to(E4M3)
+    w = (torch.randn((cfg["Co"], cfg["C"] // cfg["groups"]) + cfg["k"], generator=g) * 0.3).to(E4M3)
+    b = torch.randn(cfg["Co"], generator=g)
+    got = torch.ops.hpu.conv2d_fp8.scalar(x.cuda(), w.cuda(), b.cuda(), cfg["stride"], cfg["padding"], cfg["dilation"], cfg["groups"],
+                                          torch.float, 0.5, 0.25).cpu()
+    want = O.conv2d_fp8(x, w, b, cfg["stride"], cfg["padding"], cfg["dilation"], cfg["groups"], torch.float, 0.5, 0.25)
+    assert got.shape == want.shape
+    assert O.rel_frobenius(got, want) <= 1e-5
+    with pytest.raises(RuntimeError, match="Input and weight must be 4D tensors"):
+        torch.ops.hpu.conv2d_fp8(x.cuda()[0], w.cuda())
+    with pytest.raises(RuntimeError, match="Bias must be 1D tensor with size equal to weight dim0"):
+        torch.ops.hpu.conv2d_fp8(x.cuda(), w.cuda(), b.cuda()[:-1])
+    with pytest.raises(RuntimeError, match="Multi-element scale tensors are not supported yet."):
+        torch.ops.hpu.conv2d_fp8(x.cuda(), w.cuda(), None, (1, 1), (0, 0), (1, 1), cfg["groups"], None, torch.ones(2).cuda(), None)
+    assert ops.device_status() == 0
