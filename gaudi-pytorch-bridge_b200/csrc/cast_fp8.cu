@@ -205,6 +205,17 @@ __device__ __forceinline__ uint32_t bf16x2_mul(uint32_t a, uint32_t b) {
   __nv_bfloat162 r = __hmul2(*reinterpret_cast<__nv_bfloat162*>(&a), *reinterpret_cast<__nv_bfloat162*>(&b));
   return *reinterpret_cast<uint32_t*>(&r);
 }
+// unsigned 16-bit minimum / maximum of both halves, one instruction each
+__device__ __forceinline__ uint32_t min_u16x2(uint32_t a, uint32_t b) {
+  uint32_t d;
+  asm("min.u16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+  return d;
+}
+__device__ __forceinline__ uint32_t max_u16x2(uint32_t a, uint32_t b) {
+  uint32_t d;
+  asm("max.u16x2 %0, %1, %2;" : "=r"(d) : "r"(a), "r"(b));
+  return d;
+}
 __device__ __forceinline__ uint32_t bf16x2_max_nan(uint32_t a, uint32_t b) {
   __nv_bfloat162 r = __hmax2_nan(*reinterpret_cast<__nv_bfloat162*>(&a), *reinterpret_cast<__nv_bfloat162*>(&b));
   return *reinterpret_cast<uint32_t*>(&r);
@@ -309,15 +320,16 @@ __device__ __forceinline__ uint4 cast16_bf16_sr(const uint4 a, const uint4 b, ui
   constexpr uint32_t kMinNormalBf16 = (uint32_t)Fp8Fmt<FMT>::kEmin << 7;  // bf16 bits of 2^Emin
   uint32_t w[8] = {a.x, a.y, a.z, a.w, b.x, b.y, b.z, b.w};
   uint32_t y[8];
-  uint32_t lo_mag = 0xFFFFFFFFu, hi_mag = 0;  // min / max of the 15-bit magnitudes in the chunk
+  uint32_t lo2 = 0xFFFFFFFFu, hi2 = 0;  // packed running min / max of the 15-bit magnitudes (both halves)
 #pragma unroll
   for (int i = 0; i < 8; ++i) {
     amax2 = bf16x2_max_nan(amax2, w[i] & 0x7FFF7FFFu);
     y[i] = has_scale ? bf16x2_mul(w[i], s2) : w[i];
     const uint32_t m = y[i] & 0x7FFF7FFFu;
-    lo_mag = min(lo_mag, min(m & 0xFFFFu, m >> 16));
-    hi_mag = max(hi_mag, max(m & 0xFFFFu, m >> 16));
+    lo2 = min_u16x2(lo2, m);
+    hi2 = max_u16x2(hi2, m);
   }
+  const uint32_t lo_mag = min(lo2 & 0xFFFFu, lo2 >> 16), hi_mag = max(hi2 & 0xFFFFu, hi2 >> 16);
   const uint4 r = philox4x32_10(gi >> 4, seed, offset);
   const uint32_t rw[4] = {r.x, r.y, r.z, r.w};
   uint32_t o[4];
