@@ -105,6 +105,8 @@ __device__ __forceinline__ void epi_drain(const GemmParams& g, uint32_t t_row, c
   const bool x_in = e.x_in;
   const float rA = e.rA, rB = e.rB, rBias = e.rBias;
   const float s8 = g.out8_dtype ? out8_scale_value(g) : 1.f;
+  constexpr int kColMode = SWAP ? B200Q_BCAST_PER_ROW : B200Q_BCAST_PER_COL;
+  const bool col_ops = g.a_scale_mode == kColMode || g.b_scale_mode == kColMode || g.bias_mode == kColMode;
 #pragma unroll 1
   for (int c0 = 0; c0 < BN; c0 += 32) {
     uint32_t r[32];
@@ -116,12 +118,18 @@ __device__ __forceinline__ void epi_drain(const GemmParams& g, uint32_t t_row, c
     tmem_ld_wait();
     constexpr int CW = (BN % 32 == 0) ? 32 : 16;
     float v[CW];
+    if (col_ops) {
 #pragma unroll
-    for (int j = 0; j < CW; ++j) {
-      float a = __uint_as_float(r[j]);
-      a = a * (rA * cA[c0 + j]);
-      a = a * (rB * cB[c0 + j]);
-      v[j] = a + (rBias + cBias[c0 + j]);
+      for (int j = 0; j < CW; ++j) {
+        float a = __uint_as_float(r[j]);
+        a = a * (rA * cA[c0 + j]);
+        a = a * (rB * cB[c0 + j]);
+        v[j] = a + (rBias + cBias[c0 + j]);
+      }
+    } else {
+      // no column-side operand (the staged arrays hold 1, 1, 0): same arithmetic from registers
+#pragma unroll
+      for (int j = 0; j < CW; ++j) v[j] = (__uint_as_float(r[j]) * rA) * rB + rBias;
     }
     if (!SWAP) {
       // thread = output row m, registers = CW consecutive output columns n
@@ -181,7 +189,23 @@ __device__ __forceinline__ void epi_drain(const GemmParams& g, uint32_t t_row, c
     } else {
       // thread = output column n (weight row), registers = CW consecutive tokens m
       const int64_t n = x;
-      if (x_in) {
+      if (x_in && !full_extra && !g.out8_dtype) {
+        // the common cases with every run-time choice hoisted out of the per-element loop (the
+        // general loop below re-decides dtype, bias and accumulate input for every element and
+        // runs several times slower)
+        const int64_t left = g.M - (y0 + c0);
+        if (g.out_dtype == B200Q_BF16) {
+          __nv_bfloat16* o = static_cast<__nv_bfloat16*>(g.out) + (y0 + c0) * g.ldo + n;
+#pragma unroll
+          for (int j = 0; j < CW; ++j)
+            if (j < left) o[(int64_t)j * g.ldo] = __float2bfloat16_rn(v[j]);
+        } else {
+          float* o = static_cast<float*>(g.out) + (y0 + c0) * g.ldo + n;
+#pragma unroll
+          for (int j = 0; j < CW; ++j)
+            if (j < left) o[(int64_t)j * g.ldo] = v[j];
+        }
+      } else if (x_in) {
 #pragma unroll
         for (int j = 0; j < CW; ++j) {
           const int64_t m = y0 + c0 + j;
@@ -727,3 +751,4 @@ int gemm_tcgen05_launch(const GemmParams& g, cudaStream_t st) {
 }
 
 }  // namespace b200q
+
