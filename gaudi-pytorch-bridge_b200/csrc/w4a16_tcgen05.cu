@@ -54,51 +54,59 @@ struct Params {
   int* status;
 };
 
-template <int BN, int STAGES, int GROUPS, int AR = 0, int EW = 0>
+// Shared memory of the single-CTA kernel is two rings, because the two things a k-block needs
+// live for very different times:
+//   raw ring  (RS slots)  packed weights [64 k][W words] + the k-group's scales / zero points.
+//                         Small (4.5 KB per 128 columns) and in flight for a whole DRAM round
+//                         trip: many slots, so that enough bytes are outstanding per SM.
+//   work ring (WS slots)  activations (bf16, K-major, 128-byte swizzle) + the expanded bf16
+//                         tile (MN-major, 128-byte swizzle).  Large (16 KB per 128 columns) and
+//                         live only from the expansion to the MMAs that read it: few slots.
+template <int BN, int RS, int WS, int GROUPS, int AR = 0, int EW = 0>
 struct Cfg {
   static constexpr int kUnits = BN / kUnit;
-  // Activation rows held per stage.  The MMA always reads 128 rows through its
-  // descriptor; with AR < 128 in the token-major form the rows beyond AR are whatever follows in
-  // the stage (packed weights, the expanded tile).  Each output row depends on its own operand
-  // row only, and rows >= M are never stored, so for M <= AR nothing needs to be there.
+  // Activation rows held per work slot.  The MMA always reads 128 rows through its descriptor;
+  // with AR < 128 the rows beyond AR are whatever follows in the slot (the expanded tile).  Each
+  // output row depends on its own operand row only, and rows >= M are never stored, so for
+  // M <= AR nothing needs to be there.
   static constexpr int kActRows = AR ? AR : 128;
   static_assert(AR == 0 || (AR <= 128 && AR % 8 == 0), "narrow activation tile: a multiple of 8 rows");
   static constexpr int kActBytes = kActRows * 128;
-  static constexpr int kRawBytes = kUnits * kRawUnit;
-  // group scales (bf16) and packed zero points of the stage's k-group ride in the same ring:
-  // fetched from global memory by the expanders they would put a DRAM/L2 latency on every
-  // group change, in the ring they are covered by the pipeline depth like everything else
   static constexpr int kWCols = kUnits * kUnit;
-  static constexpr int kRawOffset = kActBytes;
-  static constexpr int kMetaOffset = kRawOffset + kRawBytes;
+  // work slot
+  static constexpr int kWOffset = (kActBytes + 1023) / 1024 * 1024;  // expanded tile, 1024-byte aligned
+  static constexpr int kWBytes = kWCols * 128;
+  static constexpr int kWorkSlotBytes = kWOffset + kWBytes;
+  // raw slot: packed weights, then scales (bf16) at +0 and packed zero points at +512 of a 1 KB block
+  static constexpr int kRawBytes = kUnits * kRawUnit;
+  static constexpr int kMetaOffset = kRawBytes;
   static constexpr int kScaleBytes = kWCols * 2, kZpBytes = kWCols / 2;
   static constexpr int kZpOffset = kMetaOffset + 512;
-  // the expanded bf16 tile (kWCols columns x 64 k, MN-major, 128-byte swizzle) is part of the stage
-  static constexpr int kWOffset = kMetaOffset + 1024;
-  static constexpr int kWBytes = kWCols * 128;
-  static constexpr int kStageBytes = kWOffset + kWBytes;
-  static constexpr int kRawRowWords = kUnits * 16;  // packed words per k-row of the stage's tile
-  static constexpr int kBarOffset = STAGES * kStageBytes;
-  static constexpr int kNumBars = 3 * STAGES + 4;
+  static constexpr int kRawSlotBytes = kRawBytes + 1024;
+  static constexpr int kRawRowWords = kUnits * 16;  // packed words per k-row of the slot's tile
+  static constexpr int kRawRing = WS * kWorkSlotBytes;  // offset of the raw ring
+  static constexpr int kBarOffset = kRawRing + RS * kRawSlotBytes;
+  static constexpr int kNumBars = 2 * RS + 2 * WS + 4;
   static constexpr int kTotal = kBarOffset + kNumBars * 8 + 16;
-  // 8 expander warps per 128 weight columns and stage (4 packed words per thread), in GROUPS
-  // groups that take alternate stages
+  // 8 expander warps per 128 weight columns and k-block (4 packed words per thread), in GROUPS
+  // groups that take alternate k-blocks
   static constexpr int kExpandWarps = EW ? EW : 8 * kUnits;
   static constexpr int kExpandGroups = GROUPS;
-  // Warp roles are placed by scheduler (warp % 4): the producers (warps 0 and 12) and the MMA
-  // issuer (warp 4) have scheduler 0 to themselves; their per-stage instruction chains
+  // Warp roles are placed by scheduler (warp % 4): the three producers (warps 0, 12, 16) and the
+  // MMA issuer (warp 4) have scheduler 0 to themselves; their per-k-block instruction chains
   // (barrier wait, copies, MMAs, commit) run 25-40 % faster than when they compete with
   // expander warps for issue slots and the shared-memory instruction queue.  Epilogue: warps
   // 1, 2, 3 and 8 (TMEM lane quarters 1, 2, 3, 0; asleep during the main loop).  Expanders: the
   // warps >= 5 with warp % 4 != 0, in order.  Other warps of scheduler 0 idle.
   static constexpr int kLastExpander = kExpandWarps * kExpandGroups - 1;
   static constexpr int kExpWarpsEnd = 5 + (kLastExpander / 3) * 4 + kLastExpander % 3 + 1;
-  static constexpr int kWarps = kExpWarpsEnd < 13 ? 13 : kExpWarpsEnd;
+  static constexpr int kWarps = kExpWarpsEnd < 17 ? 17 : kExpWarpsEnd;
   static_assert(kWarps <= 32, "too many expander warps for one CTA");
   static constexpr int kThreads = 32 * kWarps;
-  static_assert(kWOffset % 1024 == 0 && kStageBytes % 1024 == 0, "swizzled tiles need 1024-byte alignment");
-  static_assert(kStageBytes >= 128 * 128, "the 128-row operand read must stay inside the stage");
+  static_assert(kWorkSlotBytes % 1024 == 0 && kRawSlotBytes % 1024 == 0, "swizzled tiles need 1024-byte alignment");
+  static_assert(kWorkSlotBytes >= 128 * 128, "the 128-row operand read must stay inside the slot");
   static_assert(kK % (kExpandWarps * 32 / kRawRowWords) == 0, "expander passes");
+  static_assert(WS >= GROUPS, "every expander group needs a work slot of its own");
   static constexpr uint32_t kTmemCols = (2 * BN) < 32 ? 32 : 2 * BN;
 };
 
@@ -136,11 +144,11 @@ __device__ __forceinline__ void make_group(GroupRegs& g, uint4 s, uint32_t zw, b
   for (int i = 0; i < 4; ++i) g.zr[i] = has_zp ? nib_pair(zw, i) : 0x43004300u;
 }
 
-template <int BN, int STAGES, int GROUPS, int AR = 0, int EW = 0>
-__global__ void __launch_bounds__((Cfg<BN, STAGES, GROUPS, AR, EW>::kThreads), 1)
+template <int BN, int RS, int WS, int GROUPS, int AR = 0, int EW = 0>
+__global__ void __launch_bounds__((Cfg<BN, RS, WS, GROUPS, AR, EW>::kThreads), 1)
 w4a16_kernel(const __grid_constant__ CUtensorMap map_act, const __grid_constant__ CUtensorMap map_raw,
              const __grid_constant__ CUtensorMap map_scale, const __grid_constant__ CUtensorMap map_zp, const Params p) {
-  using C = Cfg<BN, STAGES, GROUPS, AR, EW>;
+  using C = Cfg<BN, RS, WS, GROUPS, AR, EW>;
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
   uint64_t* bars = reinterpret_cast<uint64_t*>(smem + C::kBarOffset);
@@ -149,27 +157,35 @@ w4a16_kernel(const __grid_constant__ CUtensorMap map_act, const __grid_constant_
   volatile int* epi_stop = reinterpret_cast<volatile int*>(tmem_slot + 2);
 
   const uint32_t smem_base = smem_u32(smem);
-  // per stage: raw[s] packed weights + scales landed (-> expanders); ready[s] activations landed
-  // and every expander warp of the stage's group finished the tile (-> MMA issuer); empty[s] the
-  // MMAs that read the stage retired (-> producer).  raw[s] completes only after the producer saw
-  // empty[s], so the expanders need no barrier of their own for the tile being free.
-  const uint32_t bar_ready = smem_u32(bars), bar_empty = bar_ready + 8 * STAGES, bar_raw = bar_empty + 8 * STAGES;
-  const uint32_t bar_tfull = bar_raw + 8 * STAGES, bar_tempty = bar_tfull + 16;
+  // raw_full[r]   packed weights + scales of a k-block landed in raw slot r      -> expanders
+  // raw_empty[r]  the k-block of raw slot r is done (tcgen05.commit after its MMAs: a second
+  //               commit by the MMA issuer costs less than an arrival by every expander warp,
+  //               whose chain per k-block is the longest in the kernel)                -> raw producers
+  // w_ready[w]    activations landed in work slot w and the tile is expanded        -> MMA issuer
+  // w_empty[w]    the MMAs that read work slot w retired (tcgen05.commit)           -> act producer, expanders
+  const uint32_t raw_base = smem_base + C::kRawRing;
+  const uint32_t bar_raw_full = smem_u32(bars), bar_raw_empty = bar_raw_full + 8 * RS;
+  const uint32_t bar_w_ready = bar_raw_empty + 8 * RS, bar_w_empty = bar_w_ready + 8 * WS;
+  const uint32_t bar_tfull = bar_w_empty + 8 * WS, bar_tempty = bar_tfull + 16;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  enum { kProducer, kProducerMeta, kMma, kEpilogue, kExpander, kIdle };
+  enum { kProducer, kProducerMeta, kProducerAct, kMma, kEpilogue, kExpander, kIdle };
   const int ewarp = ((warp - 5) >> 2) * 3 + ((warp & 3) - 1);  // expander warp index (valid when that role)
   const int role = warp == 0    ? kProducer
                    : warp == 4  ? kMma
                    : warp == 12 ? kProducerMeta
+                   : warp == 16 ? kProducerAct
                    : (warp < 4 || warp == 8) ? kEpilogue
                    : ((warp & 3) != 0 && ewarp < C::kExpandWarps * C::kExpandGroups) ? kExpander
                                                                                       : kIdle;
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < STAGES; ++s) {
-      mbar_init(bar_ready + 8 * s, 1 + C::kExpandWarps);  // producer + one arrival per expander warp
-      mbar_init(bar_empty + 8 * s, 1);  // one commit; both producers wait on it
-      mbar_init(bar_raw + 8 * s, 2);  // the two producer warps
+    for (int r = 0; r < RS; ++r) {
+      mbar_init(bar_raw_full + 8 * r, 2);                  // the two raw-ring producer warps
+      mbar_init(bar_raw_empty + 8 * r, 1);                 // one commit (see the MMA issuer)
+    }
+    for (int w = 0; w < WS; ++w) {
+      mbar_init(bar_w_ready + 8 * w, 1 + C::kExpandWarps);  // act producer + one arrival per expander warp
+      mbar_init(bar_w_empty + 8 * w, 1);                    // one commit
     }
     for (int a = 0; a < 2; ++a) {
       mbar_init(bar_tfull + 8 * a, 1);
@@ -208,40 +224,57 @@ w4a16_kernel(const __grid_constant__ CUtensorMap map_act, const __grid_constant_
   };
 
   if (role == kProducer || role == kProducerMeta) {
-    // ------------------------------------------------------------ TMA producers
-    // Two warps, because one thread that waits for the stage and issues four copies and two
-    // expect_tx needs more cycles per stage than anything else in the kernel at small M:
-    //   warp 0   packed weights (-> raw[s]) and activations (-> ready[s])
-    //   warp 12  scales and zero points (-> raw[s]); every stage carries them because
-    //            consecutive stages go to different expander warps
+    // ------------------------------------------------------------ raw-ring producers
+    // Two warps, because one thread that waits for the slot and issues three copies and the
+    // expect_tx needs more cycles per k-block than anything else in the kernel at small M:
+    //   warp 0   packed weights
+    //   warp 12  scales and zero points; every k-block carries them because consecutive
+    //            k-blocks go to different expander warps
     if (lane == 0) {
       const bool meta = role == kProducerMeta;
-      uint32_t stage = 0, phase = 0;
+      uint32_t slot = 0, phase = 0;
+      bool ok = true;
+      for (int w = blockIdx.x; w < num_work && ok; w += gridDim.x) {
+        int xt, yt, kb0, kb1, split;
+        decode(w, xt, yt, kb0, kb1, split);
+        const int n0 = yt * BN;
+        for (int kb = kb0; kb < kb1; ++kb) {
+          if (!mbar_wait(bar_raw_empty + 8 * slot, phase ^ 1, abort_flag, p.status, kErrProducer)) {
+            ok = false;
+            break;
+          }
+          const uint32_t sbase = raw_base + slot * C::kRawSlotBytes;
+          const uint32_t full = bar_raw_full + 8 * slot;
+          if (meta) {
+            const int grp = p.group_shift >= 0 ? (kb >> p.group_shift) : (kb * kK) / p.group;
+            mbar_arrive_expect_tx(full, C::kScaleBytes + (p.zp ? C::kZpBytes : 0));
+            tma_load_2d(sbase + C::kMetaOffset, &map_scale, full, n0, grp);
+            if (p.zp) tma_load_2d(sbase + C::kZpOffset, &map_zp, full, n0 / 8, grp);
+          } else {
+            mbar_arrive_expect_tx(full, C::kRawBytes);
+            tma_load_2d(sbase, &map_raw, full, n0 / 8, kb * kK);
+          }
+          if (++slot == RS) { slot = 0; phase ^= 1; }
+        }
+      }
+    }
+  } else if (role == kProducerAct) {
+    // ------------------------------------------------------------ activation producer (work ring)
+    if (lane == 0) {
+      uint32_t slot = 0, phase = 0;
       bool ok = true;
       for (int w = blockIdx.x; w < num_work && ok; w += gridDim.x) {
         int xt, yt, kb0, kb1, split;
         decode(w, xt, yt, kb0, kb1, split);
         const int act_row0 = xt * 128;
-        const int n0 = yt * BN;
         for (int kb = kb0; kb < kb1; ++kb) {
-          if (!mbar_wait(bar_empty + 8 * stage, phase ^ 1, abort_flag, p.status, kErrProducer)) {
+          if (!mbar_wait(bar_w_empty + 8 * slot, phase ^ 1, abort_flag, p.status, kErrProducer)) {
             ok = false;
             break;
           }
-          const uint32_t sbase = smem_base + stage * C::kStageBytes;
-          const uint32_t rawb = bar_raw + 8 * stage;
-          if (meta) {
-            const int grp = p.group_shift >= 0 ? (kb >> p.group_shift) : (kb * kK) / p.group;
-            mbar_arrive_expect_tx(rawb, C::kScaleBytes + (p.zp ? C::kZpBytes : 0));
-            tma_load_2d(sbase + C::kMetaOffset, &map_scale, rawb, n0, grp);
-            if (p.zp) tma_load_2d(sbase + C::kZpOffset, &map_zp, rawb, n0 / 8, grp);
-          } else {
-            mbar_arrive_expect_tx(rawb, C::kRawBytes);
-            tma_load_2d(sbase + C::kRawOffset, &map_raw, rawb, n0 / 8, kb * kK);
-            mbar_arrive_expect_tx(bar_ready + 8 * stage, C::kActBytes);
-            tma_load_2d(sbase, &map_act, bar_ready + 8 * stage, kb * kK, act_row0);
-          }
-          if (++stage == STAGES) { stage = 0; phase ^= 1; }
+          mbar_arrive_expect_tx(bar_w_ready + 8 * slot, C::kActBytes);
+          tma_load_2d(smem_base + slot * C::kWorkSlotBytes, &map_act, bar_w_ready + 8 * slot, kb * kK, act_row0);
+          if (++slot == WS) { slot = 0; phase ^= 1; }
         }
       }
     }
@@ -252,7 +285,9 @@ w4a16_kernel(const __grid_constant__ CUtensorMap map_act, const __grid_constant_
       const uint32_t idesc = umma_idesc_major(1u, 1u, 128, BN, 0u, 1u);
       const uint64_t da0 = smem_desc_k_sw128(smem_base);
       const uint64_t dw0 = smem_desc_mn_sw128(smem_base + C::kWOffset, (kK / 8) * 1024, 1024);
-      uint32_t stage = 0, phase = 0, ready = 0;
+      uint32_t stage = 0, phase = 0, ready = 0;  // work-ring slot
+      constexpr int STAGES = WS;
+      uint32_t rslot = 0;
       int it = 0;
       bool ok = true;
       for (int w = blockIdx.x; w < num_work && ok; w += gridDim.x, ++it) {
@@ -263,23 +298,25 @@ w4a16_kernel(const __grid_constant__ CUtensorMap map_act, const __grid_constant_
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN;
         for (int kb = kb0; kb < kb1; ++kb) {
-          if (!ready && !mbar_wait(bar_ready + 8 * stage, phase, abort_flag, p.status, kErrMma)) {
+          if (!ready && !mbar_wait(bar_w_ready + 8 * stage, phase, abort_flag, p.status, kErrMma)) {
             ok = false;
             break;
           }
           tc_fence_after();
           // activations: K-major, 32 bytes per k-step inside the 128-byte row; weights: MN-major,
           // two 8-k atoms (2048 bytes) per k-step, column blocks 8 atoms apart (descriptors of
-          // stage 0 are hoisted out of the loop).  Four MMAs and the commit in one sequence, with
-          // a probe of the next stage's barrier issued before and read after them.
-          const uint64_t soff = (uint64_t)(stage * (uint32_t)(C::kStageBytes >> 4));
+          // slot 0 are hoisted out of the loop).  Four MMAs and the commit in one sequence, with
+          // a probe of the next slot's barrier issued before and read after them.
+          const uint64_t soff = (uint64_t)(stage * (uint32_t)(C::kWorkSlotBytes >> 4));
           const uint64_t da = da0 + soff, dw = dw0 + soff;
           const uint32_t nstage = stage + 1 == STAGES ? 0 : stage + 1;
           const uint32_t nphase = nstage == 0 ? phase ^ 1 : phase;
           static_assert(kK / 16 == 4, "umma_stage4_probe issues 4 MMAs");
           constexpr uint64_t kActStep = kUmmaKBytes >> 4, kWStep = 2048 >> 4;
-          ready = umma_stage4_probe<true, false>(d_tmem, da, dw, idesc, kb != kb0, bar_empty + 8 * stage,
-                                                 bar_ready + 8 * nstage, nphase, kActStep, kWStep);
+          ready = umma_stage4_probe<true, false>(d_tmem, da, dw, idesc, kb != kb0, bar_w_empty + 8 * stage,
+                                                 bar_w_ready + 8 * nstage, nphase, kActStep, kWStep);
+          umma_commit(bar_raw_empty + 8 * rslot);  // the expanders read raw slot rslot before they arrived on w_ready
+          if (++rslot == RS) rslot = 0;
           stage = nstage;
           phase = nphase;
         }
@@ -370,54 +407,67 @@ w4a16_kernel(const __grid_constant__ CUtensorMap map_act, const __grid_constant_
     // 128-byte row k % 8 of atom (b, k / 8), chunk XOR-swizzled with the row: the 8 lanes of
     // a quarter warp write the 8 chunks of one row.
     const uint32_t krow = kr & 7;
-    const uint32_t raw_off = C::kRawOffset + (kr * W + ngl) * 4;
+    const uint32_t raw_off = (kr * W + ngl) * 4;
     const uint32_t wt_off = C::kWOffset + ((ngl >> 3) * (kK / 8) + (kr >> 3)) * 1024 + krow * 128 + (((ngl & 7) ^ krow) << 4);
-    uint32_t stage = 0, phase = 0;
-    int turn = 0;  // the group whose stage this is
+    // This warp takes every kExpandGroups-th k-block of the CTA's sequence (which runs on across
+    // work items), starting with number my_group: the ring positions advance by that many slots.
+    uint32_t rslot = 0, rphase = 0, wslot = 0, wphase = 0;
+    auto advance = [](uint32_t& slot, uint32_t& phase, int n, int size) {
+      slot += n;
+      while (slot >= (uint32_t)size) { slot -= size; phase ^= 1; }
+    };
+    advance(rslot, rphase, my_group, RS);
+    advance(wslot, wphase, my_group, WS);
+    int lead = my_group;  // k-blocks of the next work item that belong to other groups before ours
     bool ok = true;
     for (int w = blockIdx.x; w < num_work && ok; w += gridDim.x) {
       int xt, yt, kb0, kb1, split;
       decode(w, xt, yt, kb0, kb1, split);
       GroupRegs g;
       int g_cur = -1;
-      for (int kb = kb0; kb < kb1; ++kb) {
-        if (turn == my_group) {
-          if (!mbar_wait(bar_raw + 8 * stage, phase, abort_flag, p.status, kErrExpand)) {
+      int kb = kb0 + lead;
+      for (; kb < kb1; kb += C::kExpandGroups) {
+        {
+          // the packed weights have landed and the work slot's previous tile has been consumed
+          if (!mbar_wait(bar_raw_full + 8 * rslot, rphase, abort_flag, p.status, kErrExpand) ||
+              !mbar_wait(bar_w_empty + 8 * wslot, wphase ^ 1, abort_flag, p.status, kErrExpand)) {
             ok = false;
             break;
           }
-          const uint32_t sbase = smem_base + stage * C::kStageBytes;
+          const uint32_t rbase = raw_base + rslot * C::kRawSlotBytes;
+          const uint32_t wbase = smem_base + wslot * C::kWorkSlotBytes;
           const int grp = p.group_shift >= 0 ? (kb >> p.group_shift) : (kb * kK) / p.group;
           if (grp != g_cur) {  // scales / zero points stay in registers while the k-group lasts
             uint4 sv;
             asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];"
                          : "=r"(sv.x), "=r"(sv.y), "=r"(sv.z), "=r"(sv.w)
-                         : "r"(sbase + C::kMetaOffset + ngl * 16));
-            const uint32_t zw = has_zp ? lds32(sbase + C::kZpOffset + ngl * 4) : 0u;
+                         : "r"(rbase + C::kMetaOffset + ngl * 16));
+            const uint32_t zw = has_zp ? lds32(rbase + C::kZpOffset + ngl * 4) : 0u;
             make_group(g, sv, zw, has_zp);
             g_cur = grp;
           }
           uint32_t wv[kPasses];
 #pragma unroll
-          for (int j = 0; j < kPasses; ++j) wv[j] = lds32(sbase + raw_off + j * kRowsPerPass * W * 4);
+          for (int j = 0; j < kPasses; ++j) wv[j] = lds32(rbase + raw_off + j * kRowsPerPass * W * 4);
 #pragma unroll
           for (int j = 0; j < kPasses; ++j) {
             // pair i = columns (i, i+4): stored in that order, the epilogue restores the column order
-            sts128(sbase + wt_off + j * (kRowsPerPass / 8) * 1024, bf2_mul(bf2_sub(nib_pair(wv[j], 0), g.zr[0]), g.sp[0]),
+            sts128(wbase + wt_off + j * (kRowsPerPass / 8) * 1024, bf2_mul(bf2_sub(nib_pair(wv[j], 0), g.zr[0]), g.sp[0]),
                    bf2_mul(bf2_sub(nib_pair(wv[j], 1), g.zr[1]), g.sp[1]),
                    bf2_mul(bf2_sub(nib_pair(wv[j], 2), g.zr[2]), g.sp[2]),
                    bf2_mul(bf2_sub(nib_pair(wv[j], 3), g.zr[3]), g.sp[3]));
           }
           // every thread publishes its own writes to the async proxy (the tensor core's view of
           // shared memory); the warp then arrives once -- an arrival per thread would put hundreds
-          // of serialised shared-memory atomics on the barrier every stage
+          // of serialised shared-memory atomics on the barrier every k-block
           fence_proxy_async_smem();
           __syncwarp();
-          if (lane == 0) mbar_arrive(bar_ready + 8 * stage);
+          if (lane == 0) mbar_arrive(bar_w_ready + 8 * wslot);
         }
-        if (++turn == C::kExpandGroups) turn = 0;
-        if (++stage == STAGES) { stage = 0; phase ^= 1; }
+        advance(rslot, rphase, C::kExpandGroups, RS);
+        advance(wslot, wphase, C::kExpandGroups, WS);
       }
+      lead = kb - kb1;  // how far the stride overshot this work item's range
     }
   }
 
@@ -781,15 +831,15 @@ __global__ void __launch_bounds__(256) splitk_reduce_kernel(const float* __restr
   }
 }
 
-template <int BN, int STAGES, int GROUPS, int AR = 0, int EW = 0>
+template <int BN, int RS, int WS, int GROUPS, int AR = 0, int EW = 0>
 static int launch(const CUtensorMap& ma, const CUtensorMap& mr, const CUtensorMap& ms, const CUtensorMap& mz, const Params& p,
                   cudaStream_t st) {
-  using C = Cfg<BN, STAGES, GROUPS, AR, EW>;
+  using C = Cfg<BN, RS, WS, GROUPS, AR, EW>;
   constexpr int smem = C::kTotal + 1024;
   static_assert(smem <= 227 * 1024, "shared memory budget");
   // TMEM: CTAs that share an SM must never ask for more than 512 columns together
   static_assert(C::kTmemCols * (227 * 1024 / smem) <= 512, "TMEM over-subscription");
-  auto kern = w4a16_kernel<BN, STAGES, GROUPS, AR, EW>;
+  auto kern = w4a16_kernel<BN, RS, WS, GROUPS, AR, EW>;
   static std::atomic<int> configured[kMaxDevices];
   const int dev = current_device_index();
   if (dev < 0) return B200Q_ERR_CUDA;
@@ -908,8 +958,8 @@ int w4a16_gemm_impl(const void* x, int64_t ldx, const int32_t* qweight, const vo
     p.y_tiles = (int)((N + bn - 1) / bn);
     rc = make_tma_map_2d(&ma, x, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, K, M, ldx * 2, w4::kK, 128, CU_TENSOR_MAP_SWIZZLE_128B);
     if (rc) return rc;
-    if (bn == 256) rc = w4::launch<256, 3, 1>(ma, mr, ms, mz, p, st);
-    else rc = w4::launch<128, 6, 2>(ma, mr, ms, mz, p, st);
+    if (bn == 256) rc = w4::launch<256, 8, 3, 1>(ma, mr, ms, mz, p, st);
+    else rc = w4::launch<128, 12, 4, 2>(ma, mr, ms, mz, p, st);
   } else {
     // small M, token-major with a narrow activation tile: 128 x 256 MMAs cover twice the weight
     // columns per instruction of the weight-major form, whose issue rate is what bounds it
@@ -931,10 +981,10 @@ int w4a16_gemm_impl(const void* x, int64_t ldx, const int32_t* qweight, const vo
     rc = make_tma_map_2d(&ma, x, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, K, M, ldx * 2, w4::kK, ar, CU_TENSOR_MAP_SWIZZLE_128B);
     if (rc) return rc;
     switch (ar) {
-      case 16: rc = w4::launch<256, 5, 2, 16, 8>(ma, mr2, ms2, mz2, p, st); break;
-      case 32: rc = w4::launch<256, 5, 2, 32, 8>(ma, mr2, ms2, mz2, p, st); break;
-      case 64: rc = w4::launch<256, 4, 2, 64, 8>(ma, mr2, ms2, mz2, p, st); break;
-      default: rc = w4::launch<256, 3, 1>(ma, mr2, ms2, mz2, p, st); break;
+      case 16: rc = w4::launch<256, 12, 3, 2, 16, 8>(ma, mr2, ms2, mz2, p, st); break;
+      case 32: rc = w4::launch<256, 11, 3, 2, 32, 8>(ma, mr2, ms2, mz2, p, st); break;
+      case 64: rc = w4::launch<256, 10, 3, 2, 64, 8>(ma, mr2, ms2, mz2, p, st); break;
+      default: rc = w4::launch<256, 8, 3, 1>(ma, mr2, ms2, mz2, p, st); break;
     }
   }
   if (rc) return rc;
@@ -991,5 +1041,6 @@ int w4a16_gemm_noalloc_impl(const void* x, int64_t ldx, const int32_t* qweight, 
 size_t w4a16_noalloc_max_bytes_impl() { return kStaticScratchBytes; }
 
 }  // namespace b200q
+
 
 
