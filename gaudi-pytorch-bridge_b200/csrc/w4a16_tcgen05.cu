@@ -97,11 +97,14 @@ struct Cfg {
   // (barrier wait, copies, MMAs, commit) run 25-40 % faster than when they compete with
   // expander warps for issue slots and the shared-memory instruction queue.  Epilogue: warps
   // 1, 2, 3 and 8 (TMEM lane quarters 1, 2, 3, 0; asleep during the main loop).  Expanders: the
-  // warps >= 5 with warp % 4 != 0, in order.  Other warps of scheduler 0 idle.
-  static constexpr int kLastExpander = kExpandWarps * kExpandGroups - 1;
+  // warps >= 5 with warp % 4 != 0, in order (21 of them in a 32-warp CTA); a configuration with
+  // more expander warps than that also takes warps 20, 24 and 28 of scheduler 0.
+  static constexpr int kNumExpanders = kExpandWarps * kExpandGroups;
+  static constexpr int kOffS0 = 21;  // expander warps available outside scheduler 0
+  static constexpr int kLastExpander = (kNumExpanders <= kOffS0 ? kNumExpanders : kOffS0) - 1;
   static constexpr int kExpWarpsEnd = 5 + (kLastExpander / 3) * 4 + kLastExpander % 3 + 1;
-  static constexpr int kWarps = kExpWarpsEnd < 17 ? 17 : kExpWarpsEnd;
-  static_assert(kWarps <= 32, "too many expander warps for one CTA");
+  static constexpr int kWarps = kNumExpanders > kOffS0 ? 32 : (kExpWarpsEnd < 17 ? 17 : kExpWarpsEnd);
+  static_assert(kNumExpanders <= kOffS0 + 3, "too many expander warps for one CTA");
   static constexpr int kThreads = 32 * kWarps;
   static_assert(kWorkSlotBytes % 1024 == 0 && kRawSlotBytes % 1024 == 0, "swizzled tiles need 1024-byte alignment");
   static_assert(kWorkSlotBytes >= 128 * 128, "the 128-row operand read must stay inside the slot");
@@ -169,14 +172,15 @@ w4a16_kernel(const __grid_constant__ CUtensorMap map_act, const __grid_constant_
   const uint32_t bar_tfull = bar_w_empty + 8 * WS, bar_tempty = bar_tfull + 16;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   enum { kProducer, kProducerMeta, kProducerAct, kMma, kEpilogue, kExpander, kIdle };
-  const int ewarp = ((warp - 5) >> 2) * 3 + ((warp & 3) - 1);  // expander warp index (valid when that role)
+  // expander warp index (valid when that role): warps off scheduler 0 first, then 20, 24, 28
+  const int ewarp = (warp & 3) != 0 ? ((warp - 5) >> 2) * 3 + ((warp & 3) - 1) : C::kOffS0 + ((warp - 20) >> 2);
   const int role = warp == 0    ? kProducer
                    : warp == 4  ? kMma
                    : warp == 12 ? kProducerMeta
                    : warp == 16 ? kProducerAct
                    : (warp < 4 || warp == 8) ? kEpilogue
-                   : ((warp & 3) != 0 && ewarp < C::kExpandWarps * C::kExpandGroups) ? kExpander
-                                                                                      : kIdle;
+                   : (((warp & 3) != 0 || warp >= 20) && ewarp < C::kNumExpanders) ? kExpander
+                                                                                    : kIdle;
 
   if (threadIdx.x == 0) {
     for (int r = 0; r < RS; ++r) {
@@ -363,9 +367,15 @@ w4a16_kernel(const __grid_constant__ CUtensorMap map_act, const __grid_constant_
         if (m < p.M) {
           if (p.splits > 1) {
             float* o = p.partial + ((int64_t)split * p.M + m) * p.N + n0;
+            if (n0 + CW <= p.N && (reinterpret_cast<uintptr_t>(o) & 15) == 0) {
 #pragma unroll
-            for (int j = 0; j < CW; ++j)
-              if (n0 + j < p.N) o[j] = __uint_as_float(r[j]);
+              for (int j = 0; j < CW; j += 4)
+                *reinterpret_cast<uint4*>(o + j) = make_uint4(r[j], r[j + 1], r[j + 2], r[j + 3]);
+            } else {
+#pragma unroll
+              for (int j = 0; j < CW; ++j)
+                if (n0 + j < p.N) o[j] = __uint_as_float(r[j]);
+            }
           } else if (p.out_dtype == B200Q_BF16) {
             __nv_bfloat16* o = static_cast<__nv_bfloat16*>(p.out) + m * p.ldo + n0;
             if (n0 + CW <= p.N && (reinterpret_cast<uintptr_t>(o) & 15) == 0) {
@@ -383,9 +393,15 @@ w4a16_kernel(const __grid_constant__ CUtensorMap map_act, const __grid_constant_
             }
           } else {
             float* o = static_cast<float*>(p.out) + m * p.ldo + n0;
+            if (n0 + CW <= p.N && (reinterpret_cast<uintptr_t>(o) & 15) == 0) {
 #pragma unroll
-            for (int j = 0; j < CW; ++j)
-              if (n0 + j < p.N) o[j] = __uint_as_float(r[j]);
+              for (int j = 0; j < CW; j += 4)
+                *reinterpret_cast<uint4*>(o + j) = make_uint4(r[j], r[j + 1], r[j + 2], r[j + 3]);
+            } else {
+#pragma unroll
+              for (int j = 0; j < CW; ++j)
+                if (n0 + j < p.N) o[j] = __uint_as_float(r[j]);
+            }
           }
         }
       }
@@ -704,9 +720,15 @@ w4a16_pair_kernel(const __grid_constant__ CUtensorMap map_act, const __grid_cons
             }
           } else {
             float* o = static_cast<float*>(p.out) + m * p.ldo + n0;
+            if (n0 + 32 <= p.N && (reinterpret_cast<uintptr_t>(o) & 15) == 0) {
 #pragma unroll
-            for (int j = 0; j < 32; ++j)
-              if (n0 + j < p.N) o[j] = __uint_as_float(r[j]);
+              for (int j = 0; j < 32; j += 4)
+                *reinterpret_cast<uint4*>(o + j) = make_uint4(r[j], r[j + 1], r[j + 2], r[j + 3]);
+            } else {
+#pragma unroll
+              for (int j = 0; j < 32; ++j)
+                if (n0 + j < p.N) o[j] = __uint_as_float(r[j]);
+            }
           }
         }
       }
@@ -980,11 +1002,13 @@ int w4a16_gemm_impl(const void* x, int64_t ldx, const int32_t* qweight, const vo
     const int ar = M <= 16 ? 16 : M <= 32 ? 32 : M <= 64 ? 64 : 128;
     rc = make_tma_map_2d(&ma, x, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, K, M, ldx * 2, w4::kK, ar, CU_TENSOR_MAP_SWIZZLE_128B);
     if (rc) return rc;
+    // three expander groups over four work slots (24 expander warps, 32 warps in all): the
+    // expand -> MMA -> release round trip of a work slot is what paces small M
     switch (ar) {
-      case 16: rc = w4::launch<256, 12, 3, 2, 16, 8>(ma, mr2, ms2, mz2, p, st); break;
-      case 32: rc = w4::launch<256, 11, 3, 2, 32, 8>(ma, mr2, ms2, mz2, p, st); break;
-      case 64: rc = w4::launch<256, 10, 3, 2, 64, 8>(ma, mr2, ms2, mz2, p, st); break;
-      default: rc = w4::launch<256, 8, 3, 1>(ma, mr2, ms2, mz2, p, st); break;
+      case 16: rc = w4::launch<256, 8, 4, 3, 16, 8>(ma, mr2, ms2, mz2, p, st); break;
+      case 32: rc = w4::launch<256, 8, 4, 3, 32, 8>(ma, mr2, ms2, mz2, p, st); break;
+      case 64: rc = w4::launch<256, 6, 4, 3, 64, 8>(ma, mr2, ms2, mz2, p, st); break;
+      default: rc = w4::launch<256, 7, 3, 3, 0, 8>(ma, mr2, ms2, mz2, p, st); break;
     }
   }
   if (rc) return rc;
