@@ -969,9 +969,7 @@ int w4a16_gemm_impl(const void* x, int64_t ldx, const int32_t* qweight, const vo
     }
     rc = make_tma_map_2d(&ma, x, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, K, M, ldx * 2, w4::kK, 128, CU_TENSOR_MAP_SWIZZLE_128B);
     if (rc) return rc;
-    static const int pair_cfg = std::getenv("B200Q_W4A16_PAIR_CFG") ? std::atoi(std::getenv("B200Q_W4A16_PAIR_CFG")) : 0;
-    if (pair_cfg == 2) rc = w4::launch_pair<5, 2>(ma, mr1, ms1, mz1, pp, st);
-    else rc = w4::launch_pair<6, 2>(ma, mr1, ms1, mz1, pp, st);
+    rc = w4::launch_pair<6, 2>(ma, mr1, ms1, mz1, pp, st);
     if (rc != B200Q_ERR_UNSUPPORTED) return rc;
   }
   if (!small_m) {
