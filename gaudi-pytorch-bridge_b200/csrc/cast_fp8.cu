@@ -835,6 +835,51 @@ int swiglu_cast_impl(const void* gate, int64_t ld_gate, const void* up, int64_t 
   return B200Q_OK;
 }
 
+// bf16 input, both outputs rounded to nearest even, product in bf16, everything 16-byte
+// aligned: the packed path of cast_bf16_rne_fast_kernel with two scales and two stores.
+__global__ void __launch_bounds__(256) cast_hybrid_bf16_rne_fast_kernel(HybridParams p) {
+  const __nv_bfloat16* __restrict__ in = static_cast<const __nv_bfloat16*>(p.in);
+  const int64_t tid = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
+  const int64_t nthreads = (int64_t)gridDim.x * blockDim.x;
+  const int64_t nvec = p.n / 16;
+  float s5 = 1.f, s4 = 1.f;
+  if (p.has152) s5 = p.dev152 ? __ldg(p.s152) : p.s152_host;
+  if (p.has143) s4 = p.dev143 ? __ldg(p.s143) : p.s143_host;
+  const uint32_t s5_2 = pack_bf16x2(s5, s5), s4_2 = pack_bf16x2(s4, s4);
+  uint32_t amax2 = 0, unused = 0;
+  int64_t v = tid;
+  for (; v + nthreads < nvec; v += 2 * nthreads) {  // two independent chunks in flight per thread
+    const int64_t b0 = v * 16, b1 = (v + nthreads) * 16;
+    const uint4* q0 = reinterpret_cast<const uint4*>(in + b0);
+    const uint4* q1 = reinterpret_cast<const uint4*>(in + b1);
+    const uint4 a0 = __ldcs(q0), a1 = __ldcs(q0 + 1), c0 = __ldcs(q1), c1 = __ldcs(q1 + 1);
+    __stcs(reinterpret_cast<uint4*>(p.out152 + b0), cast16_bf16_rne<B200Q_E5M2>(a0, a1, s5_2, p.has152, amax2));
+    __stcs(reinterpret_cast<uint4*>(p.out143 + b0), cast16_bf16_rne<B200Q_E4M3>(a0, a1, s4_2, p.has143, unused));
+    __stcs(reinterpret_cast<uint4*>(p.out152 + b1), cast16_bf16_rne<B200Q_E5M2>(c0, c1, s5_2, p.has152, amax2));
+    __stcs(reinterpret_cast<uint4*>(p.out143 + b1), cast16_bf16_rne<B200Q_E4M3>(c0, c1, s4_2, p.has143, unused));
+  }
+  for (; v < nvec; v += nthreads) {
+    const int64_t b0 = v * 16;
+    const uint4* q0 = reinterpret_cast<const uint4*>(in + b0);
+    const uint4 a0 = __ldcs(q0), a1 = __ldcs(q0 + 1);
+    __stcs(reinterpret_cast<uint4*>(p.out152 + b0), cast16_bf16_rne<B200Q_E5M2>(a0, a1, s5_2, p.has152, amax2));
+    __stcs(reinterpret_cast<uint4*>(p.out143 + b0), cast16_bf16_rne<B200Q_E4M3>(a0, a1, s4_2, p.has143, unused));
+  }
+  uint32_t amax_bits = max(amax2 << 16, amax2 & 0xFFFF0000u);
+  for (int64_t i = nvec * 16 + tid; i < p.n; i += nthreads) {  // fewer than 16 elements
+    const float x = __bfloat162float(in[i]);
+    amax_bits = max(amax_bits, __float_as_uint(x) & 0x7FFFFFFFu);
+    const float y5 = p.has152 ? round_to_bf16(x * round_to_bf16(s5)) : x;
+    const float y4 = p.has143 ? round_to_bf16(x * round_to_bf16(s4)) : x;
+    uint32_t b5 = cvt_fp8x2<B200Q_E5M2>(y5, 0.f) & 0xFFu, b4 = cvt_fp8x2<B200Q_E4M3>(y4, 0.f) & 0xFFu;
+    if (y5 != y5) b5 = 0x7Fu;
+    if (y4 != y4) b4 = 0x7Fu;
+    p.out152[i] = (uint8_t)b5;
+    p.out143[i] = (uint8_t)b4;
+  }
+  if (p.amax) block_amax_to_global(amax_bits, p.amax);
+}
+
 int cast_hybrid_impl(const void* in, int in_dtype, void* out152, void* out143, const float* s152, float s152_host,
                      int mode152, const float* s143, float s143_host, int mode143, int64_t n, float* amax, int rounding,
                      uint64_t seed, uint64_t offset, uint64_t first_index, int flags, cudaStream_t st) {
@@ -849,7 +894,11 @@ int cast_hybrid_impl(const void* in, int in_dtype, void* out152, void* out143, c
   p.mul_fp32 = (flags & B200Q_CAST_MUL_IN_FP32) ? 1 : 0;
   const int64_t items = (n + 15) / 16;
   const bool sr = rounding == B200Q_ROUND_STOCHASTIC;
-  if (in_dtype == B200Q_BF16) {
+  const bool all_aligned = ((reinterpret_cast<uintptr_t>(in) | reinterpret_cast<uintptr_t>(out152) |
+                             reinterpret_cast<uintptr_t>(out143)) & 15) == 0;
+  if (in_dtype == B200Q_BF16 && !sr && !p.mul_fp32 && all_aligned) {
+    launch_persistent(cast_hybrid_bf16_rne_fast_kernel, items, st, p);
+  } else if (in_dtype == B200Q_BF16) {
     if (sr) launch_persistent(cast_hybrid_kernel<__nv_bfloat16, true>, items, st, p);
     else launch_persistent(cast_hybrid_kernel<__nv_bfloat16, false>, items, st, p);
   } else {
