@@ -1,7 +1,7 @@
 """Generate the golden fixtures in this directory from the reference's own test helpers.
 
-Run once, in a container that has the reference tree (default /root/reference,
-or pass its path):  ``python tests/golden/make_golden.py [REFERENCE_ROOT]``.
+Run once, in a container that has the reference tree, with its path as the argument (or in the
+environment variable ``REFERENCE_ROOT``):  ``python tests/golden/make_golden.py REFERENCE_ROOT``.
 Nothing at test time reads the reference tree; only the ``.npz`` files written
 here are used.
 
@@ -24,7 +24,9 @@ import sys
 import numpy as np
 import torch
 
-REF = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+REF = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("REFERENCE_ROOT", "")
+if not os.path.isdir(os.path.join(REF, "tests", "pytest_working")):
+    sys.exit("usage: make_golden.py REFERENCE_ROOT  (the checkout of the reference repository)")
 HERE = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, os.path.join(REF, "tests", "pytest_working"))
 
