@@ -413,12 +413,15 @@ def run_ours(args):
         sgu = torch.full((2 * fl,), 0.02 / 100 / (448.0 / 5.0) * 448.0 / 5.0, device=dev)
         sdn = torch.full((d,), 0.02 / 100, device=dev)
         shard = tp_mlp.MlpShard(wgu, sgu, wd, sdn, fl)
-        mlp = tp_mlp.TpFp8Mlp(shard, 448.0 / 5.0, 448.0 / 8.0, row_blocks=args.row_blocks)
+        # (random weights: any row order is as good as any other, so the shard is used as the
+        # interleaved gate/up layout the fused epilogue expects)
+        mlp = tp_mlp.TpFp8Mlp(shard, 448.0 / 5.0, 448.0 / 8.0, row_blocks=args.row_blocks,
+                              fused_gate_up=not args.unfused_mlp)
         xs = [torch.randn(T, d, device=dev, generator=g, dtype=torch.float32).to(torch.bfloat16) for _ in range(2)]
 
         def step(i):
             mlp(xs[i % 2])
-        launches_per_step = 4 if world == 1 else 3 + args.row_blocks
+        launches_per_step = (4 if world == 1 else 3 + args.row_blocks) - (0 if args.unfused_mlp else 1)
         flops = tp_mlp.mlp_flops(T, d, f)
         algo_bytes = 3 * d * fl + 2 * T * d * 2 + T * d + 3 * T * fl * 2 + T * fl
         bound, unit_per_step, unit = "tensor", flops / 1e12 / world, "TFLOP/s"   # per-rank share; value sums ranks
@@ -639,6 +642,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="gemm")
+    ap.add_argument("--unfused-mlp", action="store_true", help="mlp workload: separate SwiGLU + cast kernel instead of the GEMM epilogue")
     ap.add_argument("--elems", type=int, default=1 << 26)
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-graph", action="store_true", help="do not replay short kernels from a CUDA graph")

@@ -40,6 +40,7 @@ class GemmArgs(C.Structure):
         ("D", C.c_void_p), ("d_dtype", C.c_int), ("ldd", C.c_int64), ("d_batch_stride", C.c_int64),
         ("force_generic", C.c_int), ("stream", C.c_void_p),
         ("out8_dtype", C.c_int), ("out8_scale", C.c_void_p), ("out8_scale_host", C.c_float),
+        ("swiglu", C.c_int),
     ]
 
 

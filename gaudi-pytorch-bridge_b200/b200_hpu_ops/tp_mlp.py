@@ -47,19 +47,38 @@ def shard_bounds(n: int, tp: int, rank: int):
     return rank * step, (rank + 1) * step
 
 
-def shard_mlp(w_gate8, w_up8, w_down8, s_gate_inv, s_up_inv, s_down_inv, tp: int, rank: int) -> MlpShard:
-    """Slice full e4m3 weights ([f, d], [f, d], [d, f]) and their scale_inv vectors for one rank."""
+def interleave_blocks(gate: torch.Tensor, up: torch.Tensor, block: int = 128) -> torch.Tensor:
+    """[f, ...] gate and up -> [2f, ...] with blocks of `block` gate rows followed by the `block` up rows of
+    the same hidden units: the layout whose 256-row tiles hold both halves of a SwiGLU."""
+    f = gate.shape[0]
+    if f % block:
+        raise ValueError(f"hidden size {f} is not a multiple of {block}")
+    g = gate.reshape(f // block, 1, block, *gate.shape[1:])
+    u = up.reshape(f // block, 1, block, *up.shape[1:])
+    return torch.cat([g, u], dim=1).reshape(2 * f, *gate.shape[1:]).contiguous()
+
+
+def shard_mlp(w_gate8, w_up8, w_down8, s_gate_inv, s_up_inv, s_down_inv, tp: int, rank: int,
+              interleave: bool = False) -> MlpShard:
+    """Slice full e4m3 weights ([f, d], [f, d], [d, f]) and their scale_inv vectors for one rank.
+    interleave=True stores gate and up rows in alternating blocks of 128 (see interleave_blocks) so that
+    the gate/up GEMM can apply the SwiGLU in its epilogue (TpFp8Mlp(fused_gate_up=True))."""
     f = w_gate8.shape[0]
     lo, hi = shard_bounds(f, tp, rank)
-    gu = torch.cat([w_gate8[lo:hi].view(torch.uint8), w_up8[lo:hi].view(torch.uint8)], dim=0).view(E4M3).contiguous()
-    sgu = torch.cat([s_gate_inv[lo:hi], s_up_inv[lo:hi]]).float().contiguous()
+    g8, u8 = w_gate8[lo:hi].view(torch.uint8), w_up8[lo:hi].view(torch.uint8)
+    if interleave:
+        gu = interleave_blocks(g8, u8).view(E4M3)
+        sgu = interleave_blocks(s_gate_inv[lo:hi].float(), s_up_inv[lo:hi].float())
+    else:
+        gu = torch.cat([g8, u8], dim=0).view(E4M3).contiguous()
+        sgu = torch.cat([s_gate_inv[lo:hi], s_up_inv[lo:hi]]).float().contiguous()
     wd = w_down8.view(torch.uint8)[:, lo:hi].contiguous().view(E4M3)
     return MlpShard(gu, sgu, wd, s_down_inv.float().contiguous(), hi - lo)
 
 
 class TpFp8Mlp:
     def __init__(self, shard: MlpShard, x_scale: float, act_scale: float, group=None, row_blocks: int = 4,
-                 ops=None, fused_swiglu: bool = True):
+                 ops=None, fused_swiglu: bool = True, fused_gate_up: bool = False):
         self.s = shard
         self.x_scale = float(x_scale)
         self.act_scale = float(act_scale)
@@ -67,6 +86,9 @@ class TpFp8Mlp:
         self.row_blocks = int(row_blocks)
         self.ops = ops if ops is not None else torch.ops.hpu
         self.fused_swiglu = fused_swiglu and ops is None
+        # the shard's gate/up weights are interleaved (shard_mlp(..., interleave=True)): SwiGLU and the
+        # cast run in the GEMM's epilogue and the bf16 [tokens, 2f] intermediate is never written
+        self.fused_gate_up = fused_gate_up and ops is None
         dev = shard.w_gate_up.device
         self._xs_inv = torch.tensor(1.0 / self.x_scale, dtype=torch.float32, device=dev)
         self._as_inv = torch.tensor(1.0 / self.act_scale, dtype=torch.float32, device=dev)
@@ -104,7 +126,11 @@ class TpFp8Mlp:
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         import torch.distributed as dist
 
-        h8 = self.activation(self.gate_up(x))
+        if self.fused_gate_up:
+            x8, _ = self.ops.cast_to_fp8_v2(x, self.x_scale, False, False, E4M3)
+            h8 = torch.ops.b200q.fp8_gemm_swiglu_cast(x8, self.s.w_gate_up, self._xs_inv, self.s.s_gate_up_inv, self.act_scale)
+        else:
+            h8 = self.activation(self.gate_up(x))
         tp = dist.get_world_size(self.group) if (dist.is_available() and dist.is_initialized()) else 1
         if tp == 1:
             return self.down_partial(h8)

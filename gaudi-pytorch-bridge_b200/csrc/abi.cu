@@ -278,7 +278,13 @@ int b200q_fp8_gemm(const b200q_gemm_args* a) {
   g.d_batch_stride = a->d_batch_stride;
   g.out8_dtype = a->out8_dtype; g.out8_scale = a->out8_scale; g.out8_scale_host = a->out8_scale_host;
   if (g.out8_dtype != 0 && !is_fp8(g.out8_dtype)) return B200Q_ERR_BAD_ARGUMENT;
+  g.swiglu = a->swiglu;
   cudaStream_t st = static_cast<cudaStream_t>(a->stream);
+  if (g.swiglu) {
+    if (g.out8_dtype != B200Q_E4M3) return B200Q_ERR_BAD_ARGUMENT;
+    if (g.batch != 1 || g.D || g.trans_a || !g.trans_b || a->force_generic) return B200Q_ERR_UNSUPPORTED;
+    return gemm_tcgen05_launch(g, st);  // B200Q_ERR_UNSUPPORTED when the shape has no fused kernel
+  }
   if (!a->force_generic) {
     if (g.batch == 1) {
       int rc = gemm_tcgen05_launch(g, st);

@@ -40,11 +40,6 @@ __device__ __forceinline__ float scaled(float x, float s, float s_in_dtype, int 
   return x * s;
 }
 
-template <int FMT>
-__device__ __forceinline__ float clampf(float v) {
-  // fminf/fmaxf drop NaN; NaN bytes are patched by the caller from the unclamped value.
-  return fminf(fmaxf(v, -Fp8Fmt<FMT>::kMax), Fp8Fmt<FMT>::kMax);
-}
 
 // Every NaN becomes the canonical byte 0x7F in both formats (the sign of a NaN that went
 // through a multiply differs between CPUs and GPUs, so it is not carried).
@@ -646,11 +641,6 @@ struct SwigluParams {
   float* amax;
 };
 
-__device__ __forceinline__ float silu_mul_bf16(float g, float u) {
-  // silu in fp32, product rounded once to bf16 (the dtype the unfused graph would hold)
-  float s = g / (1.f + expf(-g));
-  return round_to_bf16(s * u);
-}
 
 __global__ void __launch_bounds__(256) swiglu_cast_kernel(SwigluParams p) {
   const int64_t vec_per_row = p.cols / 16;

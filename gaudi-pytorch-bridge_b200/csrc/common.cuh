@@ -88,6 +88,20 @@ __device__ __forceinline__ float fp8_to_float(uint32_t byte) {
   return __half2float(*reinterpret_cast<__half*>(&h));
 }
 
+template <int FMT>
+__device__ __forceinline__ float clampf(float v) {
+  // fminf/fmaxf drop NaN; NaN bytes are patched by the caller from the unclamped value.
+  return fminf(fmaxf(v, -Fp8Fmt<FMT>::kMax), Fp8Fmt<FMT>::kMax);
+}
+
+// silu(g) * u: silu in fp32, product rounded once to bf16 (the dtype the unfused graph would
+// hold).  Shared by the stand-alone SwiGLU + cast kernel and the fused GEMM epilogue, which
+// must produce the same bytes.
+__device__ __forceinline__ float silu_mul_bf16(float g, float u) {
+  float s = g / (1.f + expf(-g));
+  return round_to_bf16(s * u);
+}
+
 // Philox4x32-10; counter = (block lo, block hi, offset lo, offset hi), key = seed.
 __device__ __forceinline__ uint4 philox4x32_10(uint64_t block, uint64_t seed, uint64_t offset) {
   uint32_t c0 = (uint32_t)block, c1 = (uint32_t)(block >> 32);

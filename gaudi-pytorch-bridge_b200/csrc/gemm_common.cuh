@@ -32,6 +32,12 @@ struct GemmParams {
   int out8_dtype;
   const float* out8_scale;  // device scalar, or null: out8_scale_host
   float out8_scale_host;
+  // fused SwiGLU (needs out8_dtype = E4M3): B holds gate and up weights interleaved in blocks of
+  // 128 rows (rows [256 b, 256 b + 128) gate, the next 128 up, both of hidden units
+  // [128 b, 128 b + 128)); `out` receives e4m3 [M][N / 2]:
+  //   cast(bf16(silu(gate) * up), out8 scale)  with gate / up rounded to out_dtype first,
+  // the bytes of fp8_gemm_v2 followed by the SwiGLU + cast kernel
+  int swiglu;
 };
 
 // value in out_dtype -> fp8 byte of the fused output cast

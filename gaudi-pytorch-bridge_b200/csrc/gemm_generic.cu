@@ -56,6 +56,7 @@ __global__ void __launch_bounds__(256) gemm_generic_kernel(GemmParams p) {
 }
 
 int gemm_generic_launch(const GemmParams& p, cudaStream_t st) {
+  if (p.swiglu) return B200Q_ERR_UNSUPPORTED;  // the fused SwiGLU epilogue exists in the CTA-pair kernel only
   if (p.M == 0 || p.N == 0 || p.batch == 0) return B200Q_OK;
   dim3 grid((unsigned)((p.N + GT - 1) / GT), (unsigned)((p.M + GT - 1) / GT), (unsigned)p.batch);
   if (grid.y > 65535u || grid.z > 65535u) return B200Q_ERR_TOO_LARGE;

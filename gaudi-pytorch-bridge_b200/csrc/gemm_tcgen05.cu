@@ -223,6 +223,58 @@ __device__ __forceinline__ void epi_drain(const GemmParams& g, uint32_t t_row, c
   }
 }
 
+// Fused SwiGLU epilogue of a 256-column tile whose columns [0, 128) are gate and [128, 256) up
+// projections of the same 128 hidden units (GemmParams::swiglu): both halves get the GEMM's
+// scale / bias epilogue and its rounding to bf16, then silu(gate) * up -> bf16 -> * scale -> bf16
+// -> e4m3, with the same device functions as swiglu_cast_kernel so that the bytes are those of
+// the unfused pair of operators.  128 bytes per row and tile instead of 512 + a second pass.
+__device__ __forceinline__ void epi_drain_swiglu(const GemmParams& g, uint32_t t_row, const EpiRow& e, int64_t y0,
+                                                 const float* cA, const float* cB, const float* cBias) {
+  const int64_t m = e.x;
+  const float rA = e.rA, rB = e.rB, rBias = e.rBias;
+  const float s_act = round_to_bf16(out8_scale_value(g));
+  const int64_t f0 = (y0 >> 8) << 7;  // first hidden unit of the tile
+  const int64_t F = g.N >> 1;
+#pragma unroll 1
+  for (int c0 = 0; c0 < 128; c0 += 32) {
+    uint32_t rg[32], ru[32];
+    tmem_ld_32x32(t_row + c0, rg);
+    tmem_ld_32x32(t_row + 128 + c0, ru);
+    tmem_ld_wait();
+    uint32_t o[8];
+#pragma unroll
+    for (int j = 0; j < 32; j += 4) {
+      float y[4];
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        const int cg = c0 + j + q, cu = 128 + cg;
+        float a = __uint_as_float(rg[j + q]);
+        a = a * (rA * cA[cg]);
+        a = a * (rB * cB[cg]);
+        a = round_to_bf16(a + (rBias + cBias[cg]));
+        float b = __uint_as_float(ru[j + q]);
+        b = b * (rA * cA[cu]);
+        b = b * (rB * cB[cu]);
+        b = round_to_bf16(b + (rBias + cBias[cu]));
+        y[q] = round_to_bf16(silu_mul_bf16(a, b) * s_act);
+      }
+      o[j >> 2] = cvt_fp8x2<B200Q_E4M3>(clampf<B200Q_E4M3>(y[0]), clampf<B200Q_E4M3>(y[1])) |
+                  (cvt_fp8x2<B200Q_E4M3>(clampf<B200Q_E4M3>(y[2]), clampf<B200Q_E4M3>(y[3])) << 16);
+    }
+    if (e.x_in) {
+      uint8_t* dst = static_cast<uint8_t*>(g.out) + m * g.ldo + f0 + c0;
+      if (f0 + c0 + 32 <= F && (reinterpret_cast<uintptr_t>(dst) & 15) == 0) {
+        *reinterpret_cast<uint4*>(dst) = make_uint4(o[0], o[1], o[2], o[3]);
+        *reinterpret_cast<uint4*>(dst + 16) = make_uint4(o[4], o[5], o[6], o[7]);
+      } else {
+#pragma unroll
+        for (int j = 0; j < 32; ++j)
+          if (f0 + c0 + j < F) dst[j] = (uint8_t)(o[j >> 2] >> (8 * (j & 3)));
+      }
+    }
+  }
+}
+
 template <int BN, int STAGES, bool SWAP>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_y,
@@ -557,7 +609,8 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
       named_bar_sync(1, kEpiThreads);
       if (*epi_stop) break;
       tc_fence_after();
-      epi_drain<BN, false>(g, tmem_base + ((uint32_t)(q * 32) << 16) + acc * BN, er, y0, cA, cB, cBias);
+      if (BN == 256 && g.swiglu) epi_drain_swiglu(g, tmem_base + ((uint32_t)(q * 32) << 16) + acc * BN, er, y0, cA, cB, cBias);
+      else epi_drain<BN, false>(g, tmem_base + ((uint32_t)(q * 32) << 16) + acc * BN, er, y0, cA, cB, cBias);
       tc_fence_before();
       mbar_arrive_cluster((bar_tempty + 8 * acc) & kPeerBitMask);  // the even CTA's barrier
     }
@@ -662,6 +715,10 @@ int gemm_tcgen05_launch(const GemmParams& g, cudaStream_t st) {
   if (g.M <= 0 || g.N <= 0) return B200Q_ERR_UNSUPPORTED;
   if (g.M > (1ll << 30) || g.N > (1ll << 30) || g.K > (1ll << 30)) return B200Q_ERR_UNSUPPORTED;
 
+  // fused SwiGLU: CTA-pair kernel only, whole 256-column tiles, bf16 intermediate
+  if (g.swiglu && (g.M <= 128 || (g.N % 256) || a_mn || b_mn || g.out_dtype != B200Q_BF16 || g.out8_dtype != B200Q_E4M3))
+    return B200Q_ERR_UNSUPPORTED;
+
   TcGemmParams tp;
   tp.g = g;
   static const bool no_probe = std::getenv("B200Q_GEMM_NO_PROBE") != nullptr;
@@ -712,6 +769,7 @@ int gemm_tcgen05_launch(const GemmParams& g, cudaStream_t st) {
       }
       static const int forced = std::getenv("B200Q_GEMM_PAIR_BN") ? std::atoi(std::getenv("B200Q_GEMM_PAIR_BN")) : 0;
       if (forced == 256 || forced == 224 || forced == 192) bp = forced;
+      if (g.swiglu) bp = 256;  // gate and up halves of a tile
       pp.y_tiles = (int)((g.N + bp - 1) / bp);
       rc = make_operand_map(&my, g.B, g.N, g.K, g.ldb, bp / 2);
       if (rc) return rc;
@@ -722,6 +780,7 @@ int gemm_tcgen05_launch(const GemmParams& g, cudaStream_t st) {
       }
       if (rc != B200Q_ERR_UNSUPPORTED) return rc;
     }
+    if (g.swiglu) return B200Q_ERR_UNSUPPORTED;  // only the pair kernel has the fused SwiGLU epilogue
     rc = make_map(&my, g.B, g.N, g.K, g.ldb, b_mn, bn);
     if (rc) return rc;
     switch (bn) {

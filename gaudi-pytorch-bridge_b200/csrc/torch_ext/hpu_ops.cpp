@@ -700,6 +700,57 @@ at::Tensor w4a16_gemm(const at::Tensor& x, const at::Tensor& qweight, const at::
   return out;
 }
 
+std::tuple<at::Tensor, at::Tensor> swiglu_cast_fp8(const at::Tensor& gate, const at::Tensor& up, double scale, bool is_amax);
+
+// Gate / up projection GEMM with the SwiGLU + cast in its epilogue.  w_gate_up: e4m3 [2f, d] with
+// gate and up rows interleaved in blocks of 128 (rows [256 b, 256 b + 128) gate, next 128 up, of
+// hidden units [128 b, 128 b + 128)); w_scale_inv [2f] in the same order.  Returns e4m3 [M, f] =
+// swiglu_cast_fp8 of fp8_gemm_v2(x8, w_gate_up^T) -- the same bytes -- without writing the bf16
+// [M, 2f] intermediate when the shape has a fused kernel (M > 128, 2f % 256 == 0).
+at::Tensor fp8_gemm_swiglu_cast(const at::Tensor& x8, const at::Tensor& w_gate_up, const OptTensor& x_scale_inv,
+                                const OptTensor& w_scale_inv, double act_scale) {
+  TORCH_CHECK(is_fp8(x8.scalar_type()) && is_fp8(w_gate_up.scalar_type()) && x8.dim() == 2 && w_gate_up.dim() == 2 &&
+                  x8.size(1) == w_gate_up.size(1) && w_gate_up.size(0) % 256 == 0,
+              "fp8_gemm_swiglu_cast: x8 [M, d] and w_gate_up [2f, d] float8, 2f a multiple of 256");
+  c10::cuda::CUDAGuard guard(x8.device());
+  const int64_t M = x8.size(0), N = w_gate_up.size(0), K = x8.size(1), F = N / 2;
+  at::Tensor a = x8.contiguous(), b = w_gate_up.contiguous();
+  at::Tensor out = at::empty({M, F}, x8.options().dtype(at::kFloat8_e4m3fn));
+  if (out.numel() == 0) return out;
+  b200q_gemm_args g{};
+  g.A = a.data_ptr(); g.B = b.data_ptr();
+  g.a_dtype = to_b200q_dtype(a.scalar_type()); g.b_dtype = to_b200q_dtype(b.scalar_type());
+  g.trans_a = 0; g.trans_b = 1;
+  g.M = M; g.N = N; g.K = K; g.lda = K; g.ldb = K; g.batch = 1;
+  g.out = out.data_ptr(); g.out_dtype = B200Q_BF16; g.ldo = F;
+  at::Tensor sa, sb;
+  if (x_scale_inv.has_value() && x_scale_inv->defined()) {
+    TORCH_CHECK(x_scale_inv->numel() == 1, "fp8_gemm_swiglu_cast: x_scale_inv must have one element");
+    sa = x_scale_inv->to(at::kFloat).contiguous();
+    g.a_scale = sa.data_ptr<float>(); g.a_scale_mode = B200Q_BCAST_SCALAR_DEV;
+  }
+  if (w_scale_inv.has_value() && w_scale_inv->defined()) {
+    TORCH_CHECK(w_scale_inv->numel() == 1 || w_scale_inv->numel() == N, "fp8_gemm_swiglu_cast: w_scale_inv must have 1 or 2f elements");
+    sb = w_scale_inv->to(at::kFloat).contiguous();
+    g.b_scale = sb.data_ptr<float>(); g.b_scale_mode = sb.numel() == 1 ? B200Q_BCAST_SCALAR_DEV : B200Q_BCAST_PER_COL;
+  }
+  g.out8_dtype = B200Q_E4M3; g.out8_scale = nullptr; g.out8_scale_host = (float)act_scale;
+  g.swiglu = 1;
+  g.stream = current_stream();
+  const int rc = b200q_fp8_gemm(&g);
+  if (rc == B200Q_ERR_UNSUPPORTED) {
+    // no fused kernel for this shape: the two operators, on the de-interleaved halves
+    std::vector<int64_t> one_n{1, N};
+    at::Tensor gu = fp8_gemm_v2(a, false, b, true, c10::nullopt, at::kBFloat16, x_scale_inv, w_scale_inv, c10::nullopt, false,
+                                sb.defined() && sb.numel() == N ? OptShape(at::IntArrayRef(one_n)) : OptShape(c10::nullopt));
+    at::Tensor v = gu.view({M, F / 128, 2, 128});
+    at::Tensor gate = v.select(2, 0).reshape({M, F}), up = v.select(2, 1).reshape({M, F});
+    return std::get<0>(swiglu_cast_fp8(gate, up, act_scale, false));
+  }
+  check_status(rc, "fp8_gemm_swiglu_cast");
+  return out;
+}
+
 std::tuple<at::Tensor, at::Tensor> swiglu_cast_fp8(const at::Tensor& gate, const at::Tensor& up, double scale,
                                                    bool is_amax) {
   TORCH_CHECK(gate.scalar_type() == at::kBFloat16 && up.scalar_type() == at::kBFloat16 && gate.dim() == 2 &&
@@ -1169,6 +1220,7 @@ TORCH_LIBRARY(b200q, m) {
   m.def("fp8_gemm_cast(Tensor A, bool trans_A, Tensor B, bool trans_B, Tensor? D, ScalarType mid_dtype, Tensor? A_scale_inv, Tensor? B_scale_inv, Tensor? bias, bool accumulate, int[]? B_scale_shape, float out_scale, ScalarType out_dtype) -> Tensor");
   m.def("scaled_mm(Tensor a, Tensor b, Tensor scale_a, Tensor scale_b, Tensor? bias, Tensor? scale_result, ScalarType out_dtype) -> Tensor");
   m.def("swiglu_cast_fp8(Tensor gate, Tensor up, float scale, bool is_amax) -> (Tensor, Tensor)");
+  m.def("fp8_gemm_swiglu_cast(Tensor x8, Tensor w_gate_up, Tensor? x_scale_inv, Tensor? w_scale_inv, float act_scale) -> Tensor");
   m.def("amax(Tensor input) -> Tensor");
   m.def("scale_from_amax_(Tensor(a!) scale, Tensor amax, float fp8_max, bool pow2=True, int margin=0) -> Tensor(a!)");
   m.def("amax_history_update_(Tensor(a!) scale, Tensor(b!) history, int pos, Tensor new_amax, bool use_max, float fp8_max, bool pow2=True, int margin=0) -> Tensor(a!)");
@@ -1186,6 +1238,7 @@ TORCH_LIBRARY_IMPL(b200q, CUDA, m) {
   m.impl("fp8_gemm_cast", fp8_gemm_cast);
   m.impl("scaled_mm", scaled_mm);
   m.impl("swiglu_cast_fp8", swiglu_cast_fp8);
+  m.impl("fp8_gemm_swiglu_cast", fp8_gemm_swiglu_cast);
   m.impl("amax", amax_op);
   m.impl("scale_from_amax_", scale_from_amax_);
   m.impl("amax_history_update_", amax_history_update_);

@@ -206,6 +206,14 @@ typedef struct b200q_gemm_args {
   int out8_dtype;
   const float* out8_scale; /* device scalar or NULL */
   float out8_scale_host;   /* used when out8_scale is NULL */
+  /* Fused SwiGLU (0 = off; needs out8_dtype = E4M3, trans_a = 0, trans_b = 1, batch = 1, no D,
+   * N % 256 == 0, M > 128; other cases return B200Q_ERR_UNSUPPORTED): B holds the gate and up
+   * projection weights interleaved in blocks of 128 rows -- rows [256 b, 256 b + 128) are gate
+   * rows, the next 128 up rows, both of hidden units [128 b, 128 b + 128), and the per-channel
+   * scales / bias follow the same order.  `out` receives e4m3 [M][N / 2] (ldo in elements):
+   * cast(bf16(silu(gate) * up), out8 scale) with gate / up rounded to out_dtype first, i.e. the
+   * bytes of this GEMM followed by b200q_swiglu_cast_fp8, without the [M][N] round trip. */
+  int swiglu;
 } b200q_gemm_args;
 
 int b200q_fp8_gemm(const b200q_gemm_args* args);

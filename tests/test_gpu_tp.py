@@ -41,6 +41,27 @@ def test_mlp_single_device_matches_oracle():
     assert b200_hpu_ops.device_status() == 0
 
 
+@pytest.mark.parametrize("T", [64, 256, 300])
+def test_fused_gate_up_swiglu_is_bit_identical(T):
+    """The gate/up GEMM with SwiGLU + cast in its epilogue (interleaved weights) against the two
+    operators: same e4m3 bytes, hence the same MLP output bit for bit.  T = 64 has no fused kernel
+    and takes the operator's own composition."""
+    import b200_hpu_ops
+    from b200_hpu_ops import tp_mlp
+    x, wg8, wu8, wd8, sg, su, sd, xs, acs = _problem(T, 512, 1024, seed=T)
+    args = (wg8.cuda(), wu8.cuda(), wd8.cuda(), sg.cuda(), su.cuda(), sd.cuda(), 1, 0)
+    plain = tp_mlp.TpFp8Mlp(tp_mlp.shard_mlp(*args), xs, acs)
+    shard_i = tp_mlp.shard_mlp(*args, interleave=True)
+    fused = tp_mlp.TpFp8Mlp(shard_i, xs, acs, fused_gate_up=True)
+    h_plain = plain.activation(plain.gate_up(x.cuda()))
+    x8, _ = torch.ops.hpu.cast_to_fp8_v2(x.cuda(), xs, False, False, torch.float8_e4m3fn)
+    h_fused = torch.ops.b200q.fp8_gemm_swiglu_cast(x8, shard_i.w_gate_up, fused._xs_inv, shard_i.s_gate_up_inv, acs)
+    assert h_fused.shape == h_plain.shape == (T, 1024)
+    assert torch.equal(h_fused.view(torch.uint8), h_plain.view(torch.uint8))
+    assert torch.equal(fused(x.cuda()), plain(x.cuda()))
+    assert b200_hpu_ops.device_status() == 0
+
+
 def _free_port():
     s = socket.socket()
     s.bind(("127.0.0.1", 0))
