@@ -8,13 +8,24 @@ One JSON line on stdout (rank 0).  With N > 1 (launched through torch.distribute
 rank per GPU) every rank owns one 14336-column shard of a [14336*N, 4096] weight
 (column-parallel, no data-path collective): per-GPU work is fixed, scaling is "weak".
 
---workload selects other members of the operator family for the same JSON contract:
-  gemm (default) | gemm_m1 | gemm_m16 | gemm_m128 | cast_rne | cast_sr | uncast | dequant | w4a16_m2048 | w4a16_m16 |
-  mlp (tensor-parallel FP8 SwiGLU MLP, strong scaling over the ranks)
+The default (headline) line carries three sub-records beside the contract's keys:
+  "mlp"        at every N: the tensor-parallel FP8 SwiGLU MLP (8192 tokens, d=8192, ffn=28672) sharded
+               over the N ranks (strong scaling) -- step time, TFLOP/s per GPU, the stand-alone
+               all-reduce of its 134 MB output, the exposed part of the collective, and a parity
+               check of the same code path on a small instance against the CPU oracle;
+  "family"     N = 1 only: the other operators of the metric (casts, dequant, decode GEMMs, W4A16),
+               a few milliseconds each;
+  "sustained"  N = 1 only: the headline GEMM over a timed region of >= 1.5 s with the clock record.
+
+--workload selects one member of the operator family for the same JSON contract:
+  gemm (default) | gemm_m1 | gemm_m16 | gemm_m128 | cast_rne | cast_sr | uncast | cast_hybrid | cast_current |
+  softmax_fp8 | dequant | dequant_kpacked | w4a16_m2048 | w4a16_m16 | mlp | scaled_mm_lib
+(scaled_mm_lib times torch._scaled_mm -- the vendor library -- on the headline shape, as context only).
 --impl reference times the CPU restatement of the reference semantics (the oracle; the
 reference itself has no arithmetic for these operators) on the host cores.
 """
 import argparse
+import gc
 import json
 import os
 import sys
@@ -29,19 +40,19 @@ import torch  # noqa: E402
 
 M_, K_, N_ = 4096, 4096, 14336
 
-# dram__bytes_read.sum + dram__bytes_write.sum of one launch of the workload's kernel, from the
-# `ncu --set full` captures summarised under profiles/ (same shapes as the workloads below).
-# Traffic below the algorithmic bytes means part of the output was still in L2 when the kernel ended.
-NCU_DRAM_TRAFFIC_BYTES = {
-    "gemm": 149.5e6,         # profiles/fp8_gemm_pair_kernel_4096x14336x4096.md
-    "gemm_m16": 59.0e6,      # profiles/fp8_gemm_swap_kernel_m16_14336x4096.md
-    "cast_rne": 163.5e6,     # profiles/cast_bf16_rne_fast_kernel_64M.md
-    "cast_sr": 166.9e6,      # profiles/cast_bf16_sr_fast_kernel_64M.md
-    "uncast": 145.6e6,       # profiles/cast_from_fp8_kernel_64M.md
-    "dequant": 112.5e6,      # profiles/dequant_rowpacked_bf16_kernel_8192x8192.md
-    "w4a16_m2048": 84.8e6,   # profiles/w4a16_pair_kernel_m2048_8192x8192.md
-    "w4a16_m16": 35.2e6,     # profiles/w4a16_kernel_m16_8192x8192.md
-}
+
+def headline_workload_name(M=M_):
+    return f"fp8_gemm_v2 e4m3 M={M} K={K_} N={N_} per rank, per-channel B_scale_inv, bf16 bias, bf16 out"
+
+
+def ncu_traffic_table():
+    """dram__bytes_read.sum + dram__bytes_write.sum of one launch of each workload's kernel, as
+    recorded in profiles/traffic.json from the `ncu --set full` captures summarised beside it."""
+    p = os.path.join(ROOT, "profiles", "traffic.json")
+    try:
+        return {k: v["dram_bytes_per_launch"] for k, v in json.load(open(p)).items() if isinstance(v, dict)}
+    except Exception:
+        return {}
 
 
 def measured_peaks():
@@ -63,7 +74,6 @@ class ClockSampler:
         self.samples = []
         self.ok = False
         self._stop = threading.Event()
-        self._mark = None
         try:
             import pynvml
             pynvml.nvmlInit()
@@ -95,6 +105,7 @@ class ClockSampler:
 
     def start(self):
         if self.ok:
+            self._stop.clear()
             self.t = threading.Thread(target=self._loop, daemon=True)
             self.t.start()
 
@@ -144,51 +155,106 @@ def gemm_bytes(M, N, K):
     return M * K + N * K + 4 * N + 2 * N + 2 * M * N
 
 
-def run_ours(args):
-    import b200_hpu_ops
+class Workload:
+    """What one --workload name runs: a step function plus the figures its roofline needs."""
+    launches_per_step = 1
+    e2e_setup = None
+    scaling = "weak"
+    graph_ok = True
+    flops = None
+
+
+def int4_operands(Kd, Nd, dev, g, k_packed=False):
+    shape = (Kd // 8, Nd) if k_packed else (Kd, Nd // 8)
+    packed = torch.randint(-2 ** 31, 2 ** 31 - 1, shape, device=dev, dtype=torch.int32, generator=g)
+    sc = (torch.rand(Kd // 128, Nd, device=dev, generator=g) * 0.015 + 0.005).to(torch.bfloat16)
+    zp = torch.randint(-2 ** 31, 2 ** 31 - 1, (Kd // 128, Nd // 8), device=dev, dtype=torch.int32, generator=g)
+    return packed, sc, zp
+
+
+def int4_bytes(Kd, Nd):
+    return Kd * Nd // 2 + (Kd // 128) * Nd * 2 + (Kd // 128) * Nd // 2
+
+
+def build_mlp_shard(dev, rank, world, d, f):
+    """Random e4m3 weights of one rank's shard of the MLP, in the interleaved gate/up layout."""
+    from b200_hpu_ops import tp_mlp
+    lo, hi = tp_mlp.shard_bounds(f, world, rank)
+    fl = hi - lo
+
+    def rand_e4m3(rows, cols, seed):
+        gg = torch.Generator(device=dev).manual_seed(seed)
+        w = torch.empty(rows, cols, device=dev, dtype=torch.float8_e4m3fn)
+        blk = 4096
+        for r0 in range(0, rows, blk):
+            r1 = min(rows, r0 + blk)
+            t = (torch.randn(r1 - r0, cols, device=dev, generator=gg, dtype=torch.float32) * 100).to(torch.bfloat16)
+            w[r0:r1] = torch.ops.hpu.cast_to_fp8_v2(t, None, False, False, torch.float8_e4m3fn)[0]
+        return w
+
+    wgu = rand_e4m3(2 * fl, d, 100 + rank)
+    wd = rand_e4m3(d, fl, 200 + rank)
+    sgu = torch.full((2 * fl,), 0.02 / 100, device=dev)
+    sdn = torch.full((d,), 0.02 / 100, device=dev)
+    # (random weights: any row order is as good as any other, so the shard is used as the
+    # interleaved gate/up layout the fused epilogue expects)
+    return tp_mlp.MlpShard(wgu, sgu, wd, sdn, fl)
+
+
+def build_workload(wl, args, dev, rank, world, peaks):
+    import b200_hpu_ops  # noqa: F401
     from b200_hpu_ops import abi
 
-    rank = int(os.environ.get("RANK", "0"))
-    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
-    world = int(os.environ.get("WORLD_SIZE", "1"))
-    dist = None
-    if world > 1:
-        import torch.distributed as dist
-        torch.cuda.set_device(local_rank)
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
-    dev = torch.device("cuda", local_rank if world > 1 else 0)
-    torch.cuda.set_device(dev)
-    peaks = measured_peaks()
-    wl = args.workload
-    steps, warmup = args.steps, max(args.warmup, 3)
-    scaling = "weak"
+    w = Workload()
+    w.name = wl
+    hbm = (peaks["hbm_gbs"], "measured copy bandwidth" if peaks["which"] == "measured" else "fallback copy bandwidth")
 
-    # ------------------------------------------------------------------ build the step function
-    if wl.startswith("gemm"):
-        M = {"gemm": M_, "gemm_m1": 1, "gemm_m16": 16, "gemm_m128": 128}[wl]
+    def hbm_bound(algo_bytes):
+        w.algo_bytes = algo_bytes
+        w.bound, w.unit_per_step, w.unit = "hbm", algo_bytes / 1e9, "GB/s"
+        w.peak, w.peak_note = hbm
+
+    if wl.startswith("gemm") or wl == "scaled_mm_lib":
+        M = {"gemm": M_, "scaled_mm_lib": M_, "gemm_m1": 1, "gemm_m16": 16, "gemm_m128": 128}[wl]
         sets = synth_gemm_inputs(M, N_, K_, dev, 1000 + rank, 3)  # 3 rotating sets: > L2 between reuses
         outs = [torch.empty(M, N_, device=dev, dtype=torch.bfloat16) for _ in sets]
-
-        def step(i):
-            s = sets[i % len(sets)]
-            abi.fp8_gemm_nt(s["a8"], s["b8"], torch.bfloat16, float_sa[i % len(sets)], s["sb_inv"], s["bias"],
-                            out=outs[i % len(sets)])
-
         float_sa = [float(s["sa_inv"]) for s in sets]
-        launches_per_step = 1
-        flops = 2.0 * M * N_ * K_
-        algo_bytes = gemm_bytes(M, N_, K_)
-        if M >= 1024:
-            bound, unit_per_step, unit = "tensor", flops / 1e12, "TFLOP/s"
-            peak = 2.0 * peaks["bf16_tflops"]
-            peak_note = "2 x measured cuBLAS bf16 burst (no fp8 entry in MEASURED_PEAKS.json); nominal dense fp8 4500"
+        ws = abi.fp8_gemm_workspace(M, N_, K_, dev)
+
+        if wl == "scaled_mm_lib":
+            # context only: the vendor library on the same operands (row-wise scales: per-token
+            # ones for A, the per-channel scale_inv for B; bias added by the library)
+            sa_rows = [s["sa_inv"].reshape(1, 1).expand(M, 1).contiguous() for s in sets]
+
+            def step(i):
+                j = i % len(sets)
+                s = sets[j]
+                torch._scaled_mm(s["a8"], s["b8"].t(), scale_a=sa_rows[j], scale_b=s["sb_inv"].reshape(1, N_),
+                                 bias=s["bias"], out_dtype=torch.bfloat16, out=outs[j])
+            w.graph_ok = False
         else:
-            bound, unit_per_step, unit = "hbm", algo_bytes / 1e9, "GB/s"
-            peak, peak_note = peaks["hbm_gbs"], "measured copy bandwidth"
-        metric = "fp8_gemm_v2 TFLOP/s" if M >= 1024 else "fp8_gemm_v2 weight-stream GB/s"
-        workload = f"fp8_gemm_v2 e4m3 M={M} K={K_} N={N_} per rank, per-channel B_scale_inv, bf16 bias, bf16 out"
-        dtype = "fp8_e4m3 (fp32 accumulate)"
-        l2 = "3 rotating operand/output sets per rank (>= 3 x working set), no flush"
+            def step(i):
+                j = i % len(sets)
+                s = sets[j]
+                abi.fp8_gemm_nt(s["a8"], s["b8"], torch.bfloat16, float_sa[j], s["sb_inv"], s["bias"], out=outs[j],
+                                workspace=ws)
+
+        w.step = step
+        w.flops = 2.0 * M * N_ * K_
+        w.algo_bytes = gemm_bytes(M, N_, K_)
+        if M >= 1024:
+            w.bound, w.unit_per_step, w.unit = "tensor", w.flops / 1e12, "TFLOP/s"
+            w.peak = 2.0 * peaks["bf16_tflops"]
+            w.peak_note = "2 x measured cuBLAS bf16 burst (no fp8 entry in MEASURED_PEAKS.json); nominal dense fp8 4500"
+            w.graph_ok = False
+        else:
+            hbm_bound(w.algo_bytes)
+        w.metric = "fp8_gemm_v2 TFLOP/s" if M >= 1024 else "fp8_gemm_v2 weight-stream GB/s"
+        if wl == "scaled_mm_lib":
+            w.metric = "torch._scaled_mm (vendor library, context only) TFLOP/s"
+        w.workload = headline_workload_name(M)
+        w.dtype = "fp8_e4m3 (fp32 accumulate)"
+        w.l2 = "3 rotating operand/output sets per rank (>= 3 x working set), no flush"
 
         def e2e_setup():
             s = sets[0]
@@ -235,6 +301,9 @@ def run_ours(args):
             e2e_step.join = e2e_join
             return e2e_step, host_a.numel(), host_out[0].numel() * 2
 
+        if wl == "gemm":
+            w.e2e_setup = e2e_setup
+
     elif wl == "cast_hybrid":
         n = args.elems
         g = torch.Generator(device=dev).manual_seed(7 + rank)
@@ -248,15 +317,12 @@ def run_ours(args):
             abi.check(abi.lib.b200q_cast_to_fp8_hybrid(abi.ptr(xs[j]), abi.BF16, abi.ptr(o5[j]), abi.ptr(o4[j]), None, 1000.0,
                                                        abi.BCAST_SCALAR_HOST, None, 8.0, abi.BCAST_SCALAR_HOST, n, abi.ptr(amax),
                                                        abi.ROUND_RNE, 1234, 0, 0, 0, abi.stream_ptr()))
-        launches_per_step = 1
-        algo_bytes = 4 * n
-        bound, unit_per_step, unit = "hbm", algo_bytes / 1e9, "GB/s"
-        peak, peak_note = peaks["hbm_gbs"], "measured copy bandwidth"
-        metric = "cast_to_fp8_hybrid (e5m2 + e4m3, RNE, amax) GB/s"
-        workload = f"cast_to_fp8_hybrid on {n} bf16 elements ~N(0,1)"
-        dtype = "bf16->e5m2+e4m3"
-        l2 = "3 rotating tensors"
-        e2e_setup = None
+        w.step = step
+        hbm_bound(4 * n)
+        w.metric = "cast_to_fp8_hybrid (e5m2 + e4m3, RNE, amax) GB/s"
+        w.workload = f"cast_to_fp8_hybrid on {n} bf16 elements ~N(0,1)"
+        w.dtype = "bf16->e5m2+e4m3"
+        w.l2 = "3 rotating tensors"
     elif wl == "softmax_fp8":
         # attention-probability shaped: rows x cols bf16 -> e4m3 with scales (3 B/element)
         rows_, cols_ = 16384, 4096
@@ -268,15 +334,12 @@ def run_ours(args):
             j = i % 3
             abi.check(abi.lib.b200q_softmax_fp8(abi.ptr(xs[j]), abi.BF16, abi.ptr(o8[j]), 1, rows_, cols_, 0.125, None, None, None,
                                                 240.0, None, 0, None, None, abi.stream_ptr()))
-        launches_per_step = 1
-        algo_bytes = 3 * rows_ * cols_
-        bound, unit_per_step, unit = "hbm", algo_bytes / 1e9, "GB/s"
-        peak, peak_note = peaks["hbm_gbs"], "measured copy bandwidth"
-        metric = "softmax_fp8 (bf16 in, e4m3 out) GB/s"
-        workload = f"softmax_fp8 over the last dim of [{rows_}, {cols_}] bf16 ~N(0,2), input scale 0.125, output scale 240; 3 B/element"
-        dtype = "bf16->e4m3 (fp32 softmax)"
-        l2 = "3 rotating tensors"
-        e2e_setup = None
+        w.step = step
+        hbm_bound(3 * rows_ * cols_)
+        w.metric = "softmax_fp8 (bf16 in, e4m3 out) GB/s"
+        w.workload = f"softmax_fp8 over the last dim of [{rows_}, {cols_}] bf16 ~N(0,2), input scale 0.125, output scale 240; 3 B/element"
+        w.dtype = "bf16->e4m3 (fp32 softmax)"
+        w.l2 = "3 rotating tensors"
     elif wl == "cast_current":
         # current scaling: amax pass -> scale on the device -> cast with the device scalar scale
         n = args.elems
@@ -292,15 +355,13 @@ def run_ours(args):
             abi.check(abi.lib.b200q_scale_from_amax(abi.ptr(amax), abi.ptr(cs), None, 448.0, 1, 0, abi.stream_ptr()))
             abi.check(abi.lib.b200q_cast_to_fp8(abi.ptr(xs[j]), abi.BF16, abi.ptr(o8[j]), abi.E4M3, abi.ptr(cs), 1.0,
                                                 abi.BCAST_SCALAR_DEV, 1, n, None, abi.ROUND_RNE, 1234, 0, 0, 0, abi.stream_ptr()))
-        launches_per_step = 3
-        algo_bytes = 5 * n
-        bound, unit_per_step, unit = "hbm", algo_bytes / 1e9, "GB/s"
-        peak, peak_note = peaks["hbm_gbs"], "measured copy bandwidth"
-        metric = "current-scaling cast (amax pass + scale + cast_to_fp8_v2 e4m3 RNE) GB/s"
-        workload = f"amax -> 2^floor(log2(448/amax)) -> cast_to_fp8_v2 on {n} bf16 elements ~N(0,1); 5 B/element"
-        dtype = "bf16->e4m3"
-        l2 = "3 rotating tensors"
-        e2e_setup = None
+        w.step = step
+        w.launches_per_step = 3
+        hbm_bound(5 * n)
+        w.metric = "current-scaling cast (amax pass + scale + cast_to_fp8_v2 e4m3 RNE) GB/s"
+        w.workload = f"amax -> 2^floor(log2(448/amax)) -> cast_to_fp8_v2 on {n} bf16 elements ~N(0,1); 5 B/element"
+        w.dtype = "bf16->e4m3"
+        w.l2 = "3 rotating tensors"
     elif wl in ("cast_rne", "cast_sr", "uncast"):
         n = args.elems
         g = torch.Generator(device=dev).manual_seed(7 + rank)
@@ -329,126 +390,118 @@ def run_ours(args):
                 j = i % 3
                 abi.check(abi.lib.b200q_cast_to_fp8(abi.ptr(xs[j]), abi.BF16, abi.ptr(x8s[j]), abi.DTYPE[fp8], None, scale,
                                                     abi.BCAST_SCALAR_HOST, 1, n, abi.ptr(amax), rnd, 1234, i, 0, 0, abi.stream_ptr()))
-        launches_per_step = 1
-        algo_bytes = 3 * n
-        bound, unit_per_step, unit = "hbm", algo_bytes / 1e9, "GB/s"
-        peak, peak_note = peaks["hbm_gbs"], "measured copy bandwidth"
-        metric = {"cast_rne": "cast_to_fp8_v2 (e4m3, RNE, amax) GB/s", "cast_sr": "cast_to_fp8_v2 (e5m2, stochastic, amax) GB/s",
-                  "uncast": "cast_from_fp8 (to bf16) GB/s"}[wl]
-        workload = f"{wl} on {n} bf16 elements ~N(0,1) with 0.1% outliers at +-50"
-        dtype = "bf16->fp8" if wl != "uncast" else "fp8->bf16"
-        l2 = "3 rotating tensors" + (" (each larger than L2)" if 2 * n > 126e6 else " (set larger than L2)" if 9 * n > 126e6 else " (fits L2: launch/L2-bound case)")
-        e2e_setup = None
-    elif wl == "dequant":
+        w.step = step
+        hbm_bound(3 * n)
+        w.metric = {"cast_rne": "cast_to_fp8_v2 (e4m3, RNE, amax) GB/s", "cast_sr": "cast_to_fp8_v2 (e5m2, stochastic, amax) GB/s",
+                    "uncast": "cast_from_fp8 (to bf16) GB/s"}[wl]
+        w.workload = f"{wl} on {n} bf16 elements ~N(0,1) with 0.1% outliers at +-50"
+        w.dtype = "bf16->fp8" if wl != "uncast" else "fp8->bf16"
+        w.l2 = "3 rotating tensors" + (" (each larger than L2)" if 2 * n > 126e6 else " (set larger than L2)" if 9 * n > 126e6 else " (fits L2: launch/L2-bound case)")
+    elif wl in ("dequant", "dequant_kpacked"):
         Kd = Nd = 8192
+        kp = wl == "dequant_kpacked"
         g = torch.Generator(device=dev).manual_seed(11 + rank)
-        ws = []
-        for _ in range(3):
-            packed = torch.randint(-2 ** 31, 2 ** 31 - 1, (Kd, Nd // 8), device=dev, dtype=torch.int32, generator=g)
-            sc = (torch.rand(Kd // 128, Nd, device=dev, generator=g) * 0.015 + 0.005).to(torch.bfloat16)
-            zp = torch.randint(-2 ** 31, 2 ** 31 - 1, (Kd // 128, Nd // 8), device=dev, dtype=torch.int32, generator=g)
-            ws.append((packed, sc, zp, torch.empty(Kd, Nd, device=dev, dtype=torch.bfloat16)))
+        ws = [int4_operands(Kd, Nd, dev, g, kp) + (torch.empty(Kd, Nd, device=dev, dtype=torch.bfloat16),) for _ in range(3)]
 
         def step(i):
             p, sc, zp, o = ws[i % 3]
-            abi.check(abi.lib.b200q_dequant_int4(abi.ptr(p), abi.ptr(sc), abi.ptr(zp), abi.ZP_PACKED, 0, abi.BF16,
-                                                 abi.ptr(o), Kd, Nd // 8, Kd // 128, 0, abi.stream_ptr()))
-        launches_per_step = 1
-        algo_bytes = Kd * Nd // 2 + (Kd // 128) * Nd * 2 + (Kd // 128) * Nd // 2 + Kd * Nd * 2
-        bound, unit_per_step, unit = "hbm", algo_bytes / 1e9, "GB/s"
-        peak, peak_note = peaks["hbm_gbs"], "measured copy bandwidth"
-        metric = "convert_from_uint4 (to bf16) GB/s"
-        workload = "convert_from_uint4 K=N=8192, group 128, packed zero points, bf16 out"
-        dtype = "u4->bf16"
-        l2 = "3 rotating weight/output sets (each larger than L2)"
-        e2e_setup = None
+            if kp:
+                abi.check(abi.lib.b200q_dequant_int4(abi.ptr(p), abi.ptr(sc), abi.ptr(zp), abi.ZP_PACKED, 0, abi.BF16,
+                                                     abi.ptr(o), Kd, Nd, Kd // 128, 1, abi.stream_ptr()))
+            else:
+                abi.check(abi.lib.b200q_dequant_int4(abi.ptr(p), abi.ptr(sc), abi.ptr(zp), abi.ZP_PACKED, 0, abi.BF16,
+                                                     abi.ptr(o), Kd, Nd // 8, Kd // 128, 0, abi.stream_ptr()))
+        w.step = step
+        hbm_bound(int4_bytes(Kd, Nd) + Kd * Nd * 2)
+        w.metric = "convert_from_uint4 (to bf16) GB/s"
+        w.workload = "convert_from_uint4 K=N=8192, group 128, packed zero points, bf16 out" + \
+            (", AutoGPTQ [K/8, N] layout" if kp else ", operator [K, N/8] layout")
+        w.dtype = "u4->bf16"
+        w.l2 = "3 rotating weight/output sets (each larger than L2)"
     elif wl.startswith("w4a16"):
-        Mw = {"w4a16_m2048": 2048, "w4a16_m16": 16}[wl]
+        kp = wl.endswith("_kpacked")
+        Mw = {"w4a16_m2048": 2048, "w4a16_m16": 16}[wl.replace("_kpacked", "")]
         Kd = Nd = 8192
         g = torch.Generator(device=dev).manual_seed(13 + rank)
         ws = []
         for _ in range(3):
-            packed = torch.randint(-2 ** 31, 2 ** 31 - 1, (Kd, Nd // 8), device=dev, dtype=torch.int32, generator=g)
-            sc = (torch.rand(Kd // 128, Nd, device=dev, generator=g) * 0.015 + 0.005).to(torch.bfloat16)
-            zp = torch.randint(-2 ** 31, 2 ** 31 - 1, (Kd // 128, Nd // 8), device=dev, dtype=torch.int32, generator=g)
+            packed, sc, zp = int4_operands(Kd, Nd, dev, g, kp)
             x = torch.randn(Mw, Kd, device=dev, generator=g, dtype=torch.float32).to(torch.bfloat16)
             ws.append((x, packed, sc, zp))
 
         def step(i):
             x, p, sc, zp = ws[i % 3]
-            torch.ops.b200q.w4a16_gemm(x, p, sc, zp, 128, False, torch.bfloat16)
-        launches_per_step = 1
-        flops = 2.0 * Mw * Kd * Nd
-        algo_bytes = Kd * Nd // 2 + (Kd // 128) * Nd * 2 + (Kd // 128) * Nd // 2 + 2 * Mw * Kd + 2 * Mw * Nd
+            torch.ops.b200q.w4a16_gemm(x, p, sc, zp, 128, kp, torch.bfloat16)
+        w.step = step
+        w.flops = 2.0 * Mw * Kd * Nd
+        w.algo_bytes = int4_bytes(Kd, Nd) + 2 * Mw * Kd + 2 * Mw * Nd
         if Mw >= 1024:
-            bound, unit_per_step, unit = "tensor", flops / 1e12, "TFLOP/s"
-            peak, peak_note = peaks["bf16_tflops"], "measured cuBLAS bf16 burst"
+            w.bound, w.unit_per_step, w.unit = "tensor", w.flops / 1e12, "TFLOP/s"
+            w.peak, w.peak_note = peaks["bf16_tflops"], "measured cuBLAS bf16 burst"
         else:
-            bound, unit_per_step, unit = "hbm", algo_bytes / 1e9, "GB/s"
-            peak, peak_note = peaks["hbm_gbs"], "measured copy bandwidth"
-        metric = "w4a16_gemm " + unit
-        workload = f"w4a16_gemm M={Mw} K=N=8192 group 128 packed zero points, bf16 out"
-        dtype = "u4 x bf16 (fp32 accumulate)"
-        l2 = "3 rotating operand sets"
-        e2e_setup = None
+            hbm_bound(w.algo_bytes)
+        w.metric = "w4a16_gemm " + w.unit
+        w.workload = f"w4a16_gemm M={Mw} K=N=8192 group 128 packed zero points, bf16 out" + (", AutoGPTQ [K/8, N] layout" if kp else "")
+        w.dtype = "u4 x bf16 (fp32 accumulate)"
+        w.l2 = "3 rotating operand sets"
     elif wl == "mlp":
         from b200_hpu_ops import tp_mlp
         T, d, f = args.tokens, 8192, 28672
-        lo, hi = tp_mlp.shard_bounds(f, world, rank)
-        fl = hi - lo
+        shard = build_mlp_shard(dev, rank, world, d, f)
+        fl = shard.f_local
         g = torch.Generator(device=dev).manual_seed(17)  # same seed on every rank: x is replicated
-
-        def rand_e4m3(rows, cols, seed):
-            gg = torch.Generator(device=dev).manual_seed(seed)
-            w = torch.empty(rows, cols, device=dev, dtype=torch.float8_e4m3fn)
-            blk = 4096
-            for r0 in range(0, rows, blk):
-                r1 = min(rows, r0 + blk)
-                t = (torch.randn(r1 - r0, cols, device=dev, generator=gg, dtype=torch.float32) * 100).to(torch.bfloat16)
-                w[r0:r1] = torch.ops.hpu.cast_to_fp8_v2(t, None, False, False, torch.float8_e4m3fn)[0]
-            return w
-
-        wgu = rand_e4m3(2 * fl, d, 100 + rank)
-        wd = rand_e4m3(d, fl, 200 + rank)
-        sgu = torch.full((2 * fl,), 0.02 / 100 / (448.0 / 5.0) * 448.0 / 5.0, device=dev)
-        sdn = torch.full((d,), 0.02 / 100, device=dev)
-        shard = tp_mlp.MlpShard(wgu, sgu, wd, sdn, fl)
-        # (random weights: any row order is as good as any other, so the shard is used as the
-        # interleaved gate/up layout the fused epilogue expects)
         mlp = tp_mlp.TpFp8Mlp(shard, 448.0 / 5.0, 448.0 / 8.0, row_blocks=args.row_blocks,
-                              fused_gate_up=not args.unfused_mlp)
+                              fused_gate_up=not args.unfused_mlp, comm=args.mlp_comm)
         xs = [torch.randn(T, d, device=dev, generator=g, dtype=torch.float32).to(torch.bfloat16) for _ in range(2)]
+        w.mlp = mlp
 
         def step(i):
             mlp(xs[i % 2])
-        launches_per_step = (4 if world == 1 else 3 + args.row_blocks) - (0 if args.unfused_mlp else 1)
-        flops = tp_mlp.mlp_flops(T, d, f)
-        algo_bytes = 3 * d * fl + 2 * T * d * 2 + T * d + 3 * T * fl * 2 + T * fl
-        bound, unit_per_step, unit = "tensor", flops / 1e12 / world, "TFLOP/s"   # per-rank share; value sums ranks
-        peak = 2.0 * peaks["bf16_tflops"]
-        peak_note = "2 x measured cuBLAS bf16 burst; the step also holds casts, SwiGLU and (tp>1) the all-reduce"
-        metric = "tensor-parallel FP8 SwiGLU MLP TFLOP/s (whole job)"
-        workload = f"Llama-3-70B-shaped MLP d=8192 ffn=28672 tokens={T}, tp={world}: gate/up column-parallel, down row-parallel + bf16 all-reduce"
-        dtype = "fp8_e4m3 (fp32 accumulate), bf16 activations"
-        l2 = "2 rotating activation tensors; weights (705 MB / tp) exceed L2"
-        scaling = "strong"
-        e2e_setup = None
+        w.step = step
+        w.launches_per_step = mlp.launches_per_step(world)
+        w.flops = tp_mlp.mlp_flops(T, d, f)
+        w.algo_bytes = 3 * d * fl + 2 * T * d * 2 + T * d + 3 * T * fl * 2 + T * fl
+        w.bound, w.unit_per_step, w.unit = "tensor", w.flops / 1e12 / world, "TFLOP/s"   # per-rank share; value sums ranks
+        w.peak = 2.0 * peaks["bf16_tflops"]
+        w.peak_note = "2 x measured cuBLAS bf16 burst; the step also holds casts, SwiGLU and (tp>1) the all-reduce"
+        w.metric = "tensor-parallel FP8 SwiGLU MLP TFLOP/s (whole job)"
+        w.workload = f"Llama-3-70B-shaped MLP d=8192 ffn=28672 tokens={T}, tp={world}: gate/up column-parallel, down row-parallel + bf16 all-reduce"
+        w.dtype = "fp8_e4m3 (fp32 accumulate), bf16 activations"
+        w.l2 = "2 rotating activation tensors; weights (705 MB / tp) exceed L2"
+        w.scaling = "strong"
+        w.graph_ok = False
+        w.parallelism = mlp.describe(world)
     else:
         raise SystemExit(f"unknown workload {wl}")
+    if not hasattr(w, "parallelism"):
+        w.parallelism = f"column-parallel over {world} rank(s), no collective"
+    return w
+
+
+def max_over_ranks(ms, dist, dev):
+    if dist is None:
+        return ms
+    t = torch.tensor([ms], device=dev, dtype=torch.float64)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return float(t.item())
+
+
+def time_workload(w, steps, warmup, dist, dev, use_graph, min_ms=0.0):
+    """W warm-up steps, then `steps` timed ones (repeated until the region lasts min_ms) between
+    barriers, CUDA events on the launching stream, max over ranks.  Short kernels (decode GEMMs,
+    casts, dequant: 5-50 us) are replayed from a CUDA graph of G consecutive steps so that the
+    host's per-call work does not pace the device; G divides the step count."""
+    import b200_hpu_ops
 
     def barrier():
         if dist is not None:
             dist.barrier()
         torch.cuda.synchronize()
 
-    # ------------------------------------------------------------------ device-resident timing
     sampler = ClockSampler(dev.index or 0)
     for i in range(warmup):
-        step(i)
+        w.step(i)
     barrier()
-    # Short kernels (decode GEMMs, casts, dequant: 5-50 us) are replayed from a CUDA graph of G
-    # consecutive steps so that the host's per-call work does not pace the device; G divides K.
-    use_graph = (not args.no_graph) and wl not in ("gemm", "mlp")
     G = 1
     if use_graph:
         G = max(d for d in range(1, 26) if steps % d == 0)
@@ -457,11 +510,11 @@ def run_ours(args):
         graph = torch.cuda.CUDAGraph()
         with torch.cuda.stream(side):
             for i in range(3):
-                step(i)
+                w.step(i)
             side.synchronize()
             with torch.cuda.graph(graph, stream=side):
                 for i in range(G):
-                    step(i)
+                    w.step(i)
         torch.cuda.current_stream().wait_stream(side)
         torch.cuda.synchronize()
 
@@ -471,85 +524,258 @@ def run_ours(args):
     else:
         def run_steps(k):
             for i in range(k):
-                step(i)
+                w.step(i)
     sampler.start()
     run_steps(max(G, (warmup // G) * G))  # a second warm-up under the sampler so short runs still have samples under load
     torch.cuda.synchronize()
     n0 = b200_hpu_ops.launch_count()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    total_steps = 0
     barrier()
     t0 = time.perf_counter()
     e0.record()
-    run_steps(steps)
+    while True:
+        run_steps(steps)
+        total_steps += steps
+        if min_ms <= 0.0:
+            break
+        e1.record()
+        e1.synchronize()
+        if e0.elapsed_time(e1) >= min_ms:
+            break
     e1.record()
     barrier()
     t1 = time.perf_counter()
     sampler.stop()
-    ms_total = e0.elapsed_time(e1)
-    launches = (b200_hpu_ops.launch_count() - n0) if not use_graph else steps * launches_per_step
+    ms_total = max_over_ranks(e0.elapsed_time(e1), dist, dev)
+    launches = (b200_hpu_ops.launch_count() - n0) if not use_graph else total_steps * w.launches_per_step
     status = b200_hpu_ops.device_status()
     if status != 0:
         raise SystemExit(f"device status {status}: a bounded wait inside a kernel ran out")
+    return {"ms_total": ms_total, "ms_step": ms_total / total_steps, "steps": total_steps, "launches": int(launches),
+            "graph_steps": G if use_graph else 0, "clocks": sampler.summary(t0, t1)}
+
+
+# ----------------------------------------------------------------------------- sub-records
+def family_record(args, dev, peaks):
+    """The other operators BASELINE.json's metric names, each timed for a few milliseconds."""
+    members = [("cast_rne", 1 << 24), ("cast_rne", 1 << 26), ("cast_sr", 1 << 24), ("cast_sr", 1 << 26),
+               ("uncast", 1 << 24), ("uncast", 1 << 26), ("dequant", None), ("dequant_kpacked", None),
+               ("gemm_m1", None), ("gemm_m16", None), ("gemm_m128", None), ("w4a16_m16", None), ("w4a16_m2048", None)]
+    out = {}
+    for name, elems in members:
+        a = argparse.Namespace(**vars(args))
+        if elems:
+            a.elems = elems
+        key = name if not elems else f"{name}_2p{elems.bit_length() - 1}"
+        try:
+            w = build_workload(name, a, dev, 0, 1, peaks)
+            r = time_workload(w, 100, 5, None, dev, w.graph_ok, min_ms=3.0)
+            rate = w.unit_per_step / (r["ms_step"] / 1e3)
+            out[key] = {"value": rate, "unit": w.unit, "frac": rate / w.peak, "bound": w.bound, "us_per_launch": r["ms_step"] * 1e3,
+                        "launches": r["launches"], "workload": w.workload,
+                        "clocks": {k: r["clocks"].get(k) for k in ("sm_mhz", "sm_max_mhz", "reasons")}}
+        except Exception as e:  # one member failing must not take the headline line with it
+            out[key] = {"error": repr(e)[:200]}
+        w = None
+        gc.collect()
+        torch.cuda.empty_cache()
+    return out
+
+
+def sustained_record(w, dev, peaks):
+    """The headline GEMM over >= 1.5 s: the power-capped companion of the burst number."""
+    r = time_workload(w, 500, 3, None, dev, False, min_ms=1500.0)
+    rate = w.unit_per_step / (r["ms_step"] / 1e3)
+    peak = 2.0 * peaks["bf16_sustained"]
+    return {"value": rate, "unit": w.unit, "seconds": r["ms_total"] / 1e3, "steps": r["steps"], "peak": peak, "frac": rate / peak,
+            "peak_source": peaks["which"] + ": 2 x cuBLAS bf16 throughput of a seconds-long loop (bf16_tflops_sustained)",
+            "clocks": r["clocks"]}
+
+
+def mlp_parity(dev, rank, world, dist):
+    """The code path the MLP record times (interleaved gate/up weights, SwiGLU + cast in the GEMM
+    epilogue, row-parallel down projection + collective), on a small instance:
+    rel_frobenius of the tp=N result against the CPU oracle (rank 0), and byte equality of every
+    rank's e4m3 intermediate with the same columns of the tp=1 computation."""
+    from b200_hpu_ops import tp_mlp
+    T, d, f = 512, 1024, 4096
+    g = torch.Generator().manual_seed(5)
+    x = torch.randn(T, d, generator=g).to(torch.bfloat16)
+    ws = [(torch.randn(f, d, generator=g) * 0.05).to(torch.bfloat16), (torch.randn(f, d, generator=g) * 0.05).to(torch.bfloat16),
+          (torch.randn(d, f, generator=g) * 0.05).to(torch.bfloat16)]
+    q8, sinv = [], []
+    for wt in ws:
+        s = 448.0 / wt.float().abs().amax(dim=1, keepdim=True)
+        w8, _ = torch.ops.hpu.cast_to_fp8_v2(wt.to(dev), s.to(dev), False, False, torch.float8_e4m3fn, list(s.shape))
+        q8.append(w8)
+        sinv.append((1.0 / s).reshape(-1).float().to(dev))
+    xs, acs = 448.0 / 5.0, 448.0 / 2.0
+    full = tp_mlp.shard_mlp(q8[0], q8[1], q8[2], sinv[0], sinv[1], sinv[2], 1, 0, interleave=True)
+    mine = tp_mlp.shard_mlp(q8[0], q8[1], q8[2], sinv[0], sinv[1], sinv[2], world, rank, interleave=True)
+    m1 = tp_mlp.TpFp8Mlp(full, xs, acs, fused_gate_up=True)
+    mn = tp_mlp.TpFp8Mlp(mine, xs, acs, fused_gate_up=True, row_blocks=4)
+    xd = x.to(dev)
+    h_full = m1.hidden(xd)
+    h_mine = mn.hidden(xd)
+    lo, hi = tp_mlp.shard_bounds(f, world, rank)
+    mism = (h_full[:, lo:hi].view(torch.uint8) != h_mine.view(torch.uint8)).sum().to(torch.float64).reshape(1)
+    y = mn(xd)
+    torch.cuda.synchronize()
     if dist is not None:
-        t = torch.tensor([ms_total], device=dev, dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms_total = float(t.item())
-    ms_step = ms_total / steps
-    value = world * unit_per_step / (ms_step / 1e3)
-    kernel_rate = unit_per_step / (ms_step / 1e3)  # one launch per step: the step time is the launch time
-    if bound == "tensor" and ms_total > 1000.0:
+        dist.all_reduce(mism, op=dist.ReduceOp.SUM)
+    rec = {"shape": f"tokens={T} d={d} ffn={f}, tp={world}, fused gate/up epilogue, {mn.describe(world)}",
+           "hidden_e4m3_bytes_differing_from_tp1": int(mism.item())}
+    if rank == 0:
+        from oracle import hpu_oracle as O  # the checker, outside every timed region
+        ref = O.fp8_swiglu_mlp(x, q8[0].cpu(), q8[1].cpu(), q8[2].cpu(), sinv[0].cpu(), sinv[1].cpu(), sinv[2].cpu(), xs, acs)
+        rec["rel_frobenius_vs_oracle"] = float(O.rel_frobenius(y, ref))
+        rec["tolerance"] = 1e-2
+        rec["ok"] = bool(rec["rel_frobenius_vs_oracle"] <= 1e-2 and rec["hidden_e4m3_bytes_differing_from_tp1"] == 0)
+    return rec
+
+
+def mlp_record(args, dev, rank, world, dist, peaks):
+    """Tensor-parallel MLP over the `world` ranks of this run (strong scaling)."""
+    a = argparse.Namespace(**vars(args))
+    w = build_workload("mlp", a, dev, rank, world, peaks)
+    steps = max(3, min(args.steps, 20))
+    r = time_workload(w, steps, 3, dist, dev, False)
+    rec = {"ms_per_step": r["ms_step"], "steps": steps, "tflops_per_gpu": w.unit_per_step / (r["ms_step"] / 1e3),
+           "tflops_whole_job": world * w.unit_per_step / (r["ms_step"] / 1e3), "scaling": "strong", "workload": w.workload,
+           "parallelism": w.parallelism, "gpu_launches": r["launches"], "clocks": r["clocks"]}
+    if world > 1:
+        # the same step with the collective left out: what of the collective is not hidden
+        w.mlp.skip_collective = True
+        r0 = time_workload(w, steps, 3, dist, dev, False)
+        w.mlp.skip_collective = False
+        rec["ms_per_step_without_collective"] = r0["ms_step"]
+        rec["exposed_collective_ms"] = r["ms_step"] - r0["ms_step"]
+        # the stand-alone NCCL all-reduce of the [tokens, d] bf16 output
+        buf = torch.zeros(args.tokens, 8192, device=dev, dtype=torch.bfloat16)
+        for _ in range(3):
+            dist.all_reduce(buf)
+        torch.cuda.synchronize()
+        dist.barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(10):
+            dist.all_reduce(buf)
+        e1.record()
+        torch.cuda.synchronize()
+        ms = max_over_ranks(e0.elapsed_time(e1), dist, dev) / 10
+        nbytes = buf.numel() * 2
+        rec["allreduce_alone"] = {"ms": ms, "bytes": nbytes, "bus_gbs": nbytes * 2 * (world - 1) / world / (ms / 1e3) / 1e9,
+                                  "what": "NCCL bf16 SUM all-reduce of the whole output, nothing else running"}
+        del buf
+    w = None
+    gc.collect()
+    torch.cuda.empty_cache()
+    rec["parity"] = mlp_parity(dev, rank, world, dist)
+    return rec
+
+
+# ----------------------------------------------------------------------------- our arm
+def run_ours(args):
+    import b200_hpu_ops  # noqa: F401
+
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        torch.cuda.set_device(local_rank)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+    dev = torch.device("cuda", local_rank if world > 1 else 0)
+    torch.cuda.set_device(dev)
+    peaks = measured_peaks()
+    wl = args.workload
+    steps, warmup = args.steps, max(args.warmup, 3)
+
+    w = build_workload(wl, args, dev, rank, world, peaks)
+    # descriptive fields, kept after the workload's tensors are released below
+    d = {k: getattr(w, k) for k in ("metric", "unit", "scaling", "dtype", "workload", "l2", "parallelism", "bound",
+                                    "algo_bytes", "launches_per_step")}
+    use_graph = (not args.no_graph) and w.graph_ok
+    r = time_workload(w, steps, warmup, dist, dev, use_graph)
+    ms_step = r["ms_step"]
+    value = world * w.unit_per_step / (ms_step / 1e3)
+    kernel_rate = w.unit_per_step / (ms_step / 1e3)  # one launch per step: the step time is the launch time
+    peak, peak_note = w.peak, w.peak_note
+    if w.bound == "tensor" and r["ms_total"] > 1000.0:
         # a seconds-long loop runs under the power cap: compare with the sustained cuBLAS figure
         peak = peak * peaks["bf16_sustained"] / peaks["bf16_tflops"]
         peak_note += "; timed region > 1 s, so the sustained (power-capped) figure is used"
 
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
     # ------------------------------------------------------------------ end to end through the operator
     e2e = None
-    if e2e_setup is not None:
-        e2e_step, h2d, d2h = e2e_setup()
+    if w.e2e_setup is not None:
+        e2e_step, h2d, d2h = w.e2e_setup()
         join = getattr(e2e_step, "join", lambda: None)
         for i in range(3):
             e2e_step(i)
         join()
         barrier()
         ksteps = max(3, min(steps, 30))
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         e0.record()
         for i in range(ksteps):
             e2e_step(i)
         join()  # the timing stream waits for the upload, operator and download streams
         e1.record()
         barrier()
-        ms = e0.elapsed_time(e1)
-        if dist is not None:
-            t = torch.tensor([ms], device=dev, dtype=torch.float64)
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-            ms = float(t.item())
-        e2e = {"value": world * unit_per_step / (ms / ksteps / 1e3), "unit": unit, "h2d_bytes_per_step": h2d,
+        ms = max_over_ranks(e0.elapsed_time(e1), dist, dev)
+        e2e = {"value": world * w.unit_per_step / (ms / ksteps / 1e3), "unit": w.unit, "h2d_bytes_per_step": h2d,
                "d2h_bytes_per_step": d2h, "steps": ksteps,
                "path": "torch.ops.hpu.fp8_gemm_v2; activations copied from pinned host memory and the full output "
                        "copied back to pinned host memory every step (weights resident); upload, operator and "
                        "download on three streams with two buffers, so consecutive steps overlap"}
+
+    # ------------------------------------------------------------------ sub-records of the headline line
+    extras = {}
+    if wl == "gemm" and not args.headline_only:
+        if world == 1:
+            extras["sustained"] = sustained_record(w, dev, peaks)
+        w = None
+        gc.collect()
+        torch.cuda.empty_cache()
+        if world == 1:
+            extras["family"] = family_record(args, dev, peaks)
+        try:
+            extras["mlp"] = mlp_record(args, dev, rank, world, dist, peaks)
+        except Exception as e:
+            if world > 1:
+                raise  # a rank that stopped here would leave the others inside a collective
+            extras["mlp"] = {"error": repr(e)[:300]}
 
     # ------------------------------------------------------------------ CPU baseline (rank 0, N=1)
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline and wl == "gemm":
         cpu = cpu_gemm_baseline(budget_s=12.0)
 
-    traffic = NCU_DRAM_TRAFFIC_BYTES.get(wl if wl not in ("cast_rne", "cast_sr", "uncast") or args.elems == 1 << 26 else None)
+    traffic = ncu_traffic_table().get(wl if wl not in ("cast_rne", "cast_sr", "uncast") or args.elems == 1 << 26 else None)
 
     if rank == 0:
         line = {
-            "metric": metric, "value": value, "unit": unit, "n_gpus": world, "steps": steps, "warmup": warmup,
-            "ms_per_step": ms_step, "higher_is_better": True, "scaling": scaling, "vs_baseline": None,
-            "dtype": dtype, "data": "synthetic (seeded normal activations/weights, random-init; no dataset involved)",
-            "config": {"workload": workload, "l2": l2, "parallelism": (f"column-parallel over {world} rank(s), no collective" if wl != "mlp"
-                                       else f"tp{world}: column-parallel gate/up, row-parallel down, NCCL all-reduce in {args.row_blocks} row blocks")},
-            "roofline": {"bound": bound, "achieved": kernel_rate, "peak": peak, "unit": unit, "frac": kernel_rate / peak,
-                         "traffic": traffic, "peak_source": peaks["which"] + ": " + peak_note,
-                         "algorithmic_bytes_per_launch": algo_bytes},
-            "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": int(launches),
-            "launches_per_step": launches_per_step, "cuda_graph_steps": G if use_graph else 0,
-            "clocks": sampler.summary(t0, t1),
+            "metric": d["metric"], "value": value, "unit": d["unit"], "n_gpus": world, "steps": steps, "warmup": warmup,
+            "ms_per_step": ms_step, "higher_is_better": True, "scaling": d["scaling"], "vs_baseline": None,
+            "dtype": d["dtype"], "data": "synthetic (seeded normal activations/weights, random-init; no dataset involved)",
+            "config": {"workload": d["workload"], "l2": d["l2"], "parallelism": d["parallelism"]},
+            "roofline": {"bound": d["bound"], "achieved": kernel_rate, "peak": peak, "unit": d["unit"], "frac": kernel_rate / peak,
+                         "traffic": traffic, "traffic_source": "profiles/traffic.json (ncu dram bytes of one launch)" if traffic else None,
+                         "peak_source": peaks["which"] + ": " + peak_note,
+                         "algorithmic_bytes_per_launch": d["algo_bytes"]},
+            "cpu_baseline": cpu, "e2e": e2e, "gpu_launches": r["launches"],
+            "launches_per_step": d["launches_per_step"], "cuda_graph_steps": r["graph_steps"],
+            "clocks": r["clocks"],
         }
+        line.update(extras)
         print(json.dumps(line))
     if dist is not None:
         dist.destroy_process_group()
@@ -617,17 +843,17 @@ def run_reference(args):
     times = [_cpu_run(*sample) for _ in range(steps)]
     total = sum(times)
     value = 2.0 * m * N_ * K_ * steps / total / 1e12
-    base = {"value": value, "unit": "TFLOP/s", "cores": cores, "kind": "port",
-            "sample": f"each step: first {m} of 4096 rows of A against the full 14336x4096 weight"}
+    what = f"each step: the first {m} of 4096 rows of A against the full 14336x4096 weight"
+    base = {"value": value, "unit": "TFLOP/s", "cores": cores, "kind": "port", "sample": what}
     line = {
         "impl": "reference", "metric": "fp8_gemm_v2 TFLOP/s", "value": value, "unit": "TFLOP/s",
         "n_gpus": world, "steps": steps, "warmup": warmup, "ms_per_step": total / steps * 1e3, "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "fp8_e4m3 (fp32 accumulate on the CPU)",
         "data": "synthetic (same generator family as the GPU arm)",
-        "config": {"workload": f"fp8_gemm_v2 e4m3 M={M_} K={K_} N={N_} per rank, per-channel B_scale_inv, bf16 bias, "
-                               f"bf16 out (bounded sample: {m} rows per step)",
-                   "note": "the reference has no CPU or GPU arithmetic for this operator; this is the CPU "
-                           "restatement of its semantics (oracle/hpu_oracle.py) on all host threads"},
+        "config": {"workload": headline_workload_name(), "l2": "host memory", "parallelism": "host threads of rank 0"},
+        "sample": what,
+        "note": "the reference has no CPU or GPU arithmetic for this operator; this is the CPU restatement of its "
+                "semantics (oracle/hpu_oracle.py) on all host threads",
         "cpu_baseline": base,
         "e2e": {"value": value, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
@@ -643,11 +869,14 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="gemm")
     ap.add_argument("--unfused-mlp", action="store_true", help="mlp workload: separate SwiGLU + cast kernel instead of the GEMM epilogue")
+    ap.add_argument("--mlp-comm", default="auto", choices=["auto", "nccl", "fused"],
+                    help="mlp workload: how the row-parallel partial sums are reduced (see b200_hpu_ops/tp_mlp.py)")
     ap.add_argument("--elems", type=int, default=1 << 26)
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--headline-only", action="store_true", help="gemm workload: leave out the mlp / family / sustained sub-records")
     ap.add_argument("--no-graph", action="store_true", help="do not replay short kernels from a CUDA graph")
     ap.add_argument("--tokens", type=int, default=8192)
-    ap.add_argument("--row-blocks", type=int, default=4)
+    ap.add_argument("--row-blocks", type=int, default=8)
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

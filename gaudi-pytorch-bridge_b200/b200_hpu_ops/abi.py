@@ -162,8 +162,13 @@ def cast_from_fp8(x8, out_dtype, scale=None, scale_mode=None, rows=None, cols=No
     return out
 
 
+def fp8_gemm_workspace(M, N, K, device):
+    """Scratch tensor for fp8_gemm_nt(workspace=...) at this shape, or None when the launch needs none."""
+    return None
+
+
 def fp8_gemm_nt(a8, b8, out_dtype=torch.bfloat16, a_scale=None, b_scale=None, bias=None, out=None,
-                force_generic=False):
+                force_generic=False, workspace=None):
     """out[M][N] = a8[M][K] . b8[N][K]^T with scalar (float) a_scale, per-column fp32 CUDA b_scale [N]
     (or float), optional per-column bias [N]: the projection-GEMM form, straight through the C ABI."""
     M, K = a8.shape

@@ -77,8 +77,13 @@ def shard_mlp(w_gate8, w_up8, w_down8, s_gate_inv, s_up_inv, s_down_inv, tp: int
 
 
 class TpFp8Mlp:
-    def __init__(self, shard: MlpShard, x_scale: float, act_scale: float, group=None, row_blocks: int = 4,
-                 ops=None, fused_swiglu: bool = True, fused_gate_up: bool = False):
+    """comm: how the row-parallel partial sums become the result at tp > 1.
+    "nccl"  one NCCL bf16 SUM all-reduce per block of token rows, issued asynchronously so that
+            block i's reduction overlaps block i+1's down-projection GEMM;
+    "auto"  "nccl"."""
+
+    def __init__(self, shard: MlpShard, x_scale: float, act_scale: float, group=None, row_blocks: int = 8,
+                 ops=None, fused_swiglu: bool = True, fused_gate_up: bool = False, comm: str = "auto"):
         self.s = shard
         self.x_scale = float(x_scale)
         self.act_scale = float(act_scale)
@@ -89,9 +94,24 @@ class TpFp8Mlp:
         # the shard's gate/up weights are interleaved (shard_mlp(..., interleave=True)): SwiGLU and the
         # cast run in the GEMM's epilogue and the bf16 [tokens, 2f] intermediate is never written
         self.fused_gate_up = fused_gate_up and ops is None
+        if comm not in ("auto", "nccl"):
+            raise ValueError(f"unknown comm mode {comm!r}")
+        self.comm = "nccl"
+        self.skip_collective = False  # measurement only: leaves the partial sums unreduced
         dev = shard.w_gate_up.device
         self._xs_inv = torch.tensor(1.0 / self.x_scale, dtype=torch.float32, device=dev)
         self._as_inv = torch.tensor(1.0 / self.act_scale, dtype=torch.float32, device=dev)
+
+    def describe(self, tp: int) -> str:
+        if tp == 1:
+            return "tp1: one device, no collective"
+        return (f"tp{tp}: column-parallel gate/up, row-parallel down, NCCL bf16 all-reduce in {self.row_blocks} row "
+                f"blocks overlapping the down-projection GEMMs")
+
+    def launches_per_step(self, tp: int) -> int:
+        """Kernels of this library per forward (the collective's own kernels are not counted)."""
+        head = 2 if self.fused_gate_up else 3  # cast, gate/up GEMM (+ SwiGLU/cast kernel)
+        return head + (1 if tp == 1 else self.row_blocks)
 
     # -- the three local stages ------------------------------------------------------------
     def gate_up(self, x: torch.Tensor) -> torch.Tensor:
@@ -108,6 +128,13 @@ class TpFp8Mlp:
         h = (torch.nn.functional.silu(gu[:, :f].float()) * gu[:, f:].float()).to(torch.bfloat16)
         h8, _ = self.ops.cast_to_fp8_v2(h, self.act_scale, False, False, E4M3)
         return h8
+
+    def hidden(self, x: torch.Tensor) -> torch.Tensor:
+        """e4m3 [tokens, f_local]: this rank's columns of cast(silu(gate) * up)."""
+        if self.fused_gate_up:
+            x8, _ = self.ops.cast_to_fp8_v2(x, self.x_scale, False, False, E4M3)
+            return torch.ops.b200q.fp8_gemm_swiglu_cast(x8, self.s.w_gate_up, self._xs_inv, self.s.s_gate_up_inv, self.act_scale)
+        return self.activation(self.gate_up(x))
 
     def down_partial(self, h8: torch.Tensor, out: Optional[torch.Tensor] = None) -> torch.Tensor:
         d = self.s.w_down.shape[0]
@@ -126,11 +153,7 @@ class TpFp8Mlp:
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         import torch.distributed as dist
 
-        if self.fused_gate_up:
-            x8, _ = self.ops.cast_to_fp8_v2(x, self.x_scale, False, False, E4M3)
-            h8 = torch.ops.b200q.fp8_gemm_swiglu_cast(x8, self.s.w_gate_up, self._xs_inv, self.s.s_gate_up_inv, self.act_scale)
-        else:
-            h8 = self.activation(self.gate_up(x))
+        h8 = self.hidden(x)
         tp = dist.get_world_size(self.group) if (dist.is_available() and dist.is_initialized()) else 1
         if tp == 1:
             return self.down_partial(h8)
@@ -146,7 +169,8 @@ class TpFp8Mlp:
             self.down_partial(h8[lo:hi], out[lo:hi])
             # the collective of this block runs on the communicator's stream while the next
             # block's GEMM runs on the compute stream
-            works.append(dist.all_reduce(out[lo:hi], op=dist.ReduceOp.SUM, group=self.group, async_op=True))
+            if not self.skip_collective:
+                works.append(dist.all_reduce(out[lo:hi], op=dist.ReduceOp.SUM, group=self.group, async_op=True))
         for w in works:
             w.wait()
         return out

@@ -887,6 +887,7 @@ static int w4a16_splits(int64_t M, int64_t N, int64_t K) {
   // (plus a few per work item for its pipeline fill and its partial-tile epilogue)
   const int64_t tiles = (N + 255) / 256;
   const int64_t num_kb = K / w4::kK;
+  if (num_kb <= 0) return 1;  // K below one k-block: nothing to split (and nothing to divide by below)
   int64_t best_cost = 0;
   int best = 1;
   for (int s = 1; s <= 16 && s * 4 <= num_kb; ++s) {
@@ -899,6 +900,7 @@ static int w4a16_splits(int64_t M, int64_t N, int64_t K) {
 }
 
 size_t w4a16_workspace_bytes_impl(int64_t M, int64_t N, int64_t K) {
+  if (M <= 0 || N <= 0 || K <= 0 || K % w4::kK || N % 32) return 0;  // shapes the fused kernel does not take
   const int s = w4a16_splits(M, N, K);
   return s > 1 ? (size_t)s * (size_t)M * (size_t)N * sizeof(float) : 0;
 }
@@ -907,6 +909,12 @@ int w4a16_gemm_impl(const void* x, int64_t ldx, const int32_t* qweight, const vo
                     int zp_kind, int k_packed, int64_t M, int64_t N, int64_t K, int64_t group, void* out,
                     int out_dtype, int64_t ldo, void* workspace, size_t workspace_bytes, cudaStream_t st) {
   if (k_packed) return B200Q_ERR_UNSUPPORTED;  // the fused kernel takes the operator layout [K][N/8]
+  if (K == 0) {
+    // an empty contraction: the result is all zeros (rows may be strided)
+    const size_t esz = out_dtype == B200Q_BF16 ? 2 : 4;
+    B200Q_CUDA_OK(cudaMemset2DAsync(out, (size_t)ldo * esz, 0, (size_t)N * esz, (size_t)M, st));
+    return B200Q_OK;
+  }
   if (K % w4::kK || group % w4::kK || K % group || N % 32 || ldx % 8) return B200Q_ERR_UNSUPPORTED;
   if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(qweight) | reinterpret_cast<uintptr_t>(scale)) & 15)
     return B200Q_ERR_UNSUPPORTED;
@@ -1049,6 +1057,8 @@ static int static_scratch_ptr(float** out) {
 int w4a16_gemm_noalloc_impl(const void* x, int64_t ldx, const int32_t* qweight, const void* scale, const int32_t* zp,
                             int zp_kind, int k_packed, int64_t M, int64_t N, int64_t K, int64_t group, void* out,
                             int out_dtype, int64_t ldo, cudaStream_t st) {
+  // (shapes the fused kernel rejects report a zero workspace here and are refused, with their
+  // own code, by the argument checks of w4a16_gemm_impl)
   const size_t need = w4a16_workspace_bytes_impl(M, N, K);
   if (need > kStaticScratchBytes) return B200Q_ERR_TOO_LARGE;
   float* scratch = nullptr;

@@ -27,6 +27,9 @@ def test_header_symbols_are_exported():
 
 
 SCHEMAS = {
+    # legacy out-variants, habana_kernels/kernels_register.cpp:2427,2445
+    "cast_to_fp8": "hpu::cast_to_fp8(Tensor input, Tensor? scale, bool stochastic_rounding, Tensor(a!) out, Tensor(b!) amax) -> (Tensor(a!), Tensor(b!))",
+    "fp8_gemm": "hpu::fp8_gemm(Tensor A, bool trans_A, Tensor B, bool trans_B, Tensor D, ScalarType out_dtype, Tensor? A_scale_inv, Tensor? B_scale_inv, Tensor? bias, bool accumulate, Tensor(a!) out) -> Tensor(a!)",
     "cast_to_fp8_hybrid": "hpu::cast_to_fp8_hybrid(Tensor input, Tensor? scale_152=None, Tensor? scale_143=None, bool stochastic_rounding=False, bool is_amax=False) -> (Tensor, Tensor, Tensor)",
     "cast_to_fp8_v2": "hpu::cast_to_fp8_v2(Tensor input, Tensor? scale=None, bool stochastic_rounding=False, bool is_amax=False, ScalarType dtype=None, int[]? scale_shape=None) -> (Tensor, Tensor)",
     "cast_to_fp8_v2.scalar": "hpu::cast_to_fp8_v2.scalar(Tensor input, float scale, bool stochastic_rounding=False, bool is_amax=False, ScalarType dtype=None, int[]? scale_shape=None) -> (Tensor, Tensor)",
@@ -113,3 +116,13 @@ def test_abi_rejects_bad_arguments_without_a_gpu():
     g.a_dtype = abi.F32
     assert abi.lib.b200q_fp8_gemm(ctypes.byref(g)) == -1
     assert abi.lib.b200q_dequant_int4(None, None, None, 7, 0, abi.BF16, None, 1, 1, 1, 0, None) == -1
+
+
+@pytest.mark.parametrize("K", [0, 1, 32, 63])
+def test_w4a16_workspace_query_below_one_k_block(K):
+    """Shapes the fused W4A16 kernel does not take (K not a multiple of its 64-deep k-block) ask for
+    no workspace; the size query must not do arithmetic on them (it once divided by zero)."""
+    from b200_hpu_ops import abi
+    for M in (1, 4, 128, 4096):
+        assert abi.lib.b200q_w4a16_workspace_bytes(M, 64, K) == 0
+    assert abi.lib.b200q_w4a16_workspace_bytes(16, 8192, 8192) > 0

@@ -213,3 +213,19 @@ def test_gptq_repack_matches_reference_host_repack(ops):
     zq = torch.randint(0, 16, (K // 128, N), generator=g)
     qw, qz = torch.ops.b200q.gptq_repack(kpacked.cuda(), O.pack_nibbles((zq - 1) & 0xF).cuda())
     assert torch.equal(qw.cpu(), O.pack_nibbles(w)) and torch.equal(qz.cpu(), O.pack_nibbles(zq))
+
+
+def test_w4a16_degenerate_k():
+    """K = 32 (below the kernel's 64-deep k-block) is refused with an error, K = 0 gives zeros."""
+    dev = "cuda"
+    x = torch.randn(4, 32, device=dev).to(torch.bfloat16)
+    qw = torch.zeros(32, 8, dtype=torch.int32, device=dev)
+    sc = torch.ones(1, 64, dtype=torch.bfloat16, device=dev)
+    with pytest.raises(RuntimeError):
+        torch.ops.b200q.w4a16_gemm(x, qw, sc, None, 32, False, torch.bfloat16)
+    from b200_hpu_ops import abi
+    out = torch.full((4, 64), 7.0, dtype=torch.bfloat16, device=dev)
+    rc = abi.lib.b200q_w4a16_gemm(abi.ptr(x), 0, abi.ptr(qw), abi.ptr(sc), None, abi.ZP_NONE, 0, 4, 64, 0, 64,
+                                  abi.ptr(out), abi.BF16, 64, None, 0, abi.stream_ptr())
+    assert rc == 0
+    assert torch.count_nonzero(out).item() == 0

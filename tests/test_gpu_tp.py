@@ -71,25 +71,47 @@ def _free_port():
 
 
 def _worker(rank, world, port, q):
+    """One NCCL rank: the interleaved gate/up shard with the SwiGLU + cast in the GEMM epilogue --
+    the configuration bench.py's mlp record times -- against the oracle, plus the bytes of the
+    e4m3 intermediate against the same columns computed without sharding."""
     sys.path.insert(0, ROOT)
     sys.path.insert(0, os.path.join(ROOT, "gaudi-pytorch-bridge_b200"))
     os.environ["MASTER_ADDR"] = "127.0.0.1"
     os.environ["MASTER_PORT"] = str(port)
     import torch.distributed as dist
-    torch.cuda.set_device(rank)
-    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+    inited = False
     try:
+        torch.cuda.set_device(rank)
+        dist.init_process_group("nccl", rank=rank, world_size=world, device_id=torch.device("cuda", rank))
+        inited = True
         import b200_hpu_ops
         from b200_hpu_ops import tp_mlp
-        x, wg8, wu8, wd8, sg, su, sd, xs, acs = _problem(512, 512, 2048)
+        T, d, f = 512, 512, 2048
+        x, wg8, wu8, wd8, sg, su, sd, xs, acs = _problem(T, d, f)
         dev = torch.device("cuda", rank)
-        shard = tp_mlp.shard_mlp(wg8.to(dev), wu8.to(dev), wd8.to(dev), sg.to(dev), su.to(dev), sd.to(dev), world, rank)
-        y = tp_mlp.TpFp8Mlp(shard, xs, acs, row_blocks=4)(x.to(dev))
-        torch.cuda.synchronize()
+        args = (wg8.to(dev), wu8.to(dev), wd8.to(dev), sg.to(dev), su.to(dev), sd.to(dev))
         ref = O.fp8_swiglu_mlp(x, wg8, wu8, wd8, sg, su, sd, xs, acs)
-        q.put((rank, O.rel_frobenius(y, ref), b200_hpu_ops.device_status()))
+        errs = []
+        for comm in COMM_MODES:
+            shard = tp_mlp.shard_mlp(*args, world, rank, interleave=True)
+            mlp = tp_mlp.TpFp8Mlp(shard, xs, acs, row_blocks=4, fused_gate_up=True, comm=comm)
+            full = tp_mlp.TpFp8Mlp(tp_mlp.shard_mlp(*args, 1, 0, interleave=True), xs, acs, fused_gate_up=True)
+            lo, hi = tp_mlp.shard_bounds(f, world, rank)
+            h_mine, h_full = mlp.hidden(x.to(dev)), full.hidden(x.to(dev))
+            same = torch.equal(h_mine.view(torch.uint8), h_full[:, lo:hi].view(torch.uint8))
+            for _ in range(2):  # twice: buffers and flags of the first call are reused by the second
+                y = mlp(x.to(dev))
+            torch.cuda.synchronize()
+            errs.append((comm, float(O.rel_frobenius(y, ref)), same))
+        q.put((rank, errs, b200_hpu_ops.device_status()))
+    except Exception as e:  # report instead of leaving the parent waiting on the queue
+        q.put((rank, repr(e), -1))
     finally:
-        dist.destroy_process_group()
+        if inited:
+            dist.destroy_process_group()
+
+
+COMM_MODES = ("nccl",)
 
 
 @pytest.mark.parametrize("world", [2, 4, 8])
@@ -103,10 +125,21 @@ def test_mlp_tensor_parallel_nccl(world):
     procs = [ctx.Process(target=_worker, args=(r, world, port, q)) for r in range(world)]
     for p in procs:
         p.start()
-    res = [q.get(timeout=300) for _ in range(world)]
+    try:
+        res = [q.get(timeout=300) for _ in range(world)]
+        for p in procs:
+            p.join(timeout=120)
+    finally:
+        for p in procs:  # never leave a rank behind inside a collective, holding its GPU
+            if p.is_alive():
+                p.terminate()
+                p.join(timeout=10)
+                if p.is_alive():
+                    p.kill()
+    for rank, errs, status in res:
+        assert status == 0, (rank, errs)
+        for comm, err, same in errs:
+            assert same, (rank, comm, "e4m3 intermediate differs from the unsharded computation")
+            assert err <= 1e-2, (rank, comm, err)
     for p in procs:
-        p.join(timeout=120)
         assert p.exitcode == 0
-    for rank, err, status in res:
-        assert status == 0
-        assert err <= 1e-2, (rank, err)
