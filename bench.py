@@ -219,7 +219,6 @@ def build_workload(wl, args, dev, rank, world, peaks):
         sets = synth_gemm_inputs(M, N_, K_, dev, 1000 + rank, 3)  # 3 rotating sets: > L2 between reuses
         outs = [torch.empty(M, N_, device=dev, dtype=torch.bfloat16) for _ in sets]
         float_sa = [float(s["sa_inv"]) for s in sets]
-        ws = abi.fp8_gemm_workspace(M, N_, K_, dev)
 
         if wl == "scaled_mm_lib":
             # context only: the vendor library on the same operands (row-wise scales: per-token
@@ -236,8 +235,7 @@ def build_workload(wl, args, dev, rank, world, peaks):
             def step(i):
                 j = i % len(sets)
                 s = sets[j]
-                abi.fp8_gemm_nt(s["a8"], s["b8"], torch.bfloat16, float_sa[j], s["sb_inv"], s["bias"], out=outs[j],
-                                workspace=ws)
+                abi.fp8_gemm_nt(s["a8"], s["b8"], torch.bfloat16, float_sa[j], s["sb_inv"], s["bias"], out=outs[j])
 
         w.step = step
         w.flops = 2.0 * M * N_ * K_
@@ -458,7 +456,7 @@ def build_workload(wl, args, dev, rank, world, peaks):
         def step(i):
             mlp(xs[i % 2])
         w.step = step
-        w.launches_per_step = mlp.launches_per_step(world)
+        w.launches_per_step = mlp.launches_per_step(world, T)
         w.flops = tp_mlp.mlp_flops(T, d, f)
         w.algo_bytes = 3 * d * fl + 2 * T * d * 2 + T * d + 3 * T * fl * 2 + T * fl
         w.bound, w.unit_per_step, w.unit = "tensor", w.flops / 1e12 / world, "TFLOP/s"   # per-rank share; value sums ranks
@@ -470,7 +468,7 @@ def build_workload(wl, args, dev, rank, world, peaks):
         w.l2 = "2 rotating activation tensors; weights (705 MB / tp) exceed L2"
         w.scaling = "strong"
         w.graph_ok = False
-        w.parallelism = mlp.describe(world)
+        w.parallelism = mlp.describe(world, T)
     else:
         raise SystemExit(f"unknown workload {wl}")
     if not hasattr(w, "parallelism"):
@@ -593,13 +591,13 @@ def sustained_record(w, dev, peaks):
             "clocks": r["clocks"]}
 
 
-def mlp_parity(dev, rank, world, dist):
+def mlp_parity(dev, rank, world, dist, comm="auto"):
     """The code path the MLP record times (interleaved gate/up weights, SwiGLU + cast in the GEMM
     epilogue, row-parallel down projection + collective), on a small instance:
     rel_frobenius of the tp=N result against the CPU oracle (rank 0), and byte equality of every
     rank's e4m3 intermediate with the same columns of the tp=1 computation."""
     from b200_hpu_ops import tp_mlp
-    T, d, f = 512, 1024, 4096
+    T, d, f = 1024, 1024, 4096  # whole 128-row tiles per rank up to 8 ranks, as at full size
     g = torch.Generator().manual_seed(5)
     x = torch.randn(T, d, generator=g).to(torch.bfloat16)
     ws = [(torch.randn(f, d, generator=g) * 0.05).to(torch.bfloat16), (torch.randn(f, d, generator=g) * 0.05).to(torch.bfloat16),
@@ -614,7 +612,7 @@ def mlp_parity(dev, rank, world, dist):
     full = tp_mlp.shard_mlp(q8[0], q8[1], q8[2], sinv[0], sinv[1], sinv[2], 1, 0, interleave=True)
     mine = tp_mlp.shard_mlp(q8[0], q8[1], q8[2], sinv[0], sinv[1], sinv[2], world, rank, interleave=True)
     m1 = tp_mlp.TpFp8Mlp(full, xs, acs, fused_gate_up=True)
-    mn = tp_mlp.TpFp8Mlp(mine, xs, acs, fused_gate_up=True, row_blocks=4)
+    mn = tp_mlp.TpFp8Mlp(mine, xs, acs, fused_gate_up=True, row_blocks=4, comm=comm)
     xd = x.to(dev)
     h_full = m1.hidden(xd)
     h_mine = mn.hidden(xd)
@@ -624,7 +622,7 @@ def mlp_parity(dev, rank, world, dist):
     torch.cuda.synchronize()
     if dist is not None:
         dist.all_reduce(mism, op=dist.ReduceOp.SUM)
-    rec = {"shape": f"tokens={T} d={d} ffn={f}, tp={world}, fused gate/up epilogue, {mn.describe(world)}",
+    rec = {"shape": f"tokens={T} d={d} ffn={f}, tp={world}, fused gate/up epilogue, {mn.describe(world, T)}",
            "hidden_e4m3_bytes_differing_from_tp1": int(mism.item())}
     if rank == 0:
         from oracle import hpu_oracle as O  # the checker, outside every timed region
@@ -671,7 +669,7 @@ def mlp_record(args, dev, rank, world, dist, peaks):
     w = None
     gc.collect()
     torch.cuda.empty_cache()
-    rec["parity"] = mlp_parity(dev, rank, world, dist)
+    rec["parity"] = mlp_parity(dev, rank, world, dist, args.mlp_comm)
     return rec
 
 

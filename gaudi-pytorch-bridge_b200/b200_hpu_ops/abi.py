@@ -16,7 +16,7 @@ CAST_MUL_IN_FP32 = 1
 
 EXPORTS = [
     "b200q_strerror", "b200q_last_cuda_error", "b200q_device_status", "b200q_selftest_wait_timeout", "b200q_launch_count",
-    "b200q_cast_to_fp8", "b200q_cast_to_fp8_hybrid", "b200q_cast_from_fp8", "b200q_dequant_int4", "b200q_gptq_repack", "b200q_fp8_gemm",
+    "b200q_cast_to_fp8", "b200q_cast_to_fp8_hybrid", "b200q_cast_from_fp8", "b200q_dequant_int4", "b200q_gptq_repack", "b200q_fp8_gemm", "b200q_tp_reduce_bcast",
     "b200q_w4a16_gemm", "b200q_w4a16_workspace_bytes", "b200q_w4a16_gemm_noalloc", "b200q_swiglu_cast_fp8",
     "b200q_amax", "b200q_scale_from_amax", "b200q_amax_history_update",
     "b200q_softmax_fp8", "b200q_sum_fp8_workspace_bytes", "b200q_sum_fp8", "b200q_in_place_interleave", "b200q_im2col_fp8",
@@ -41,6 +41,7 @@ class GemmArgs(C.Structure):
         ("force_generic", C.c_int), ("stream", C.c_void_p),
         ("out8_dtype", C.c_int), ("out8_scale", C.c_void_p), ("out8_scale_host", C.c_float),
         ("swiglu", C.c_int),
+        ("route_out", C.c_void_p * 8), ("route_count", C.c_int), ("route_rows", C.c_int64), ("route_row_offset", C.c_int64),
     ]
 
 
@@ -63,6 +64,7 @@ def _bind():
     lib.b200q_dequant_int4.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p,
                                        C.c_int64, C.c_int64, C.c_int64, C.c_int, C.c_void_p]
     lib.b200q_fp8_gemm.argtypes = [C.POINTER(GemmArgs)]
+    lib.b200q_tp_reduce_bcast.argtypes = [C.c_void_p, C.POINTER(C.c_void_p), C.c_int, C.c_int, C.c_int64, C.c_int64, C.c_void_p]
     lib.b200q_gptq_repack.argtypes = [C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_void_p, C.c_void_p, C.c_int64,
                                       C.c_void_p]
     lib.b200q_w4a16_gemm.argtypes = [C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int,
@@ -162,26 +164,30 @@ def cast_from_fp8(x8, out_dtype, scale=None, scale_mode=None, rows=None, cols=No
     return out
 
 
-def fp8_gemm_workspace(M, N, K, device):
-    """Scratch tensor for fp8_gemm_nt(workspace=...) at this shape, or None when the launch needs none."""
-    return None
-
-
 def fp8_gemm_nt(a8, b8, out_dtype=torch.bfloat16, a_scale=None, b_scale=None, bias=None, out=None,
-                force_generic=False, workspace=None):
+                force_generic=False, route=None):
     """out[M][N] = a8[M][K] . b8[N][K]^T with scalar (float) a_scale, per-column fp32 CUDA b_scale [N]
     (or float), optional per-column bias [N]: the projection-GEMM form, straight through the C ABI."""
     M, K = a8.shape
     N = b8.shape[0]
-    if out is None:
-        out = torch.empty((M, N), dtype=out_dtype, device=a8.device)
     g = GemmArgs()
+    if route is not None:
+        # (pointers, rows per block, row offset inside a block): block i = m // rows of the result
+        # goes to pointers[i] (bf16 [.., N], possibly another GPU's memory); nothing is returned
+        ptrs, rows, offset = route
+        for i, q in enumerate(ptrs):
+            g.route_out[i] = q
+        g.route_count, g.route_rows, g.route_row_offset = len(ptrs), rows, offset
+        g.out, g.out_dtype, g.ldo = ptrs[0], BF16, N
+    elif out is None:
+        out = torch.empty((M, N), dtype=out_dtype, device=a8.device)
     g.A, g.B = a8.data_ptr(), b8.data_ptr()
     g.a_dtype, g.b_dtype = DTYPE[a8.dtype], DTYPE[b8.dtype]
     g.trans_a, g.trans_b = 0, 1
     g.M, g.N, g.K, g.lda, g.ldb = M, N, K, a8.stride(0), b8.stride(0)
     g.batch = 1
-    g.out, g.out_dtype, g.ldo = out.data_ptr(), DTYPE[out.dtype], out.stride(0)
+    if route is None:
+        g.out, g.out_dtype, g.ldo = out.data_ptr(), DTYPE[out.dtype], out.stride(0)
     for name, s in (("a", a_scale), ("b", b_scale)):
         if s is None:
             setattr(g, name + "_scale_mode", BCAST_NONE)
@@ -197,3 +203,9 @@ def fp8_gemm_nt(a8, b8, out_dtype=torch.bfloat16, a_scale=None, b_scale=None, bi
     g.stream = torch.cuda.current_stream().cuda_stream
     check(lib.b200q_fp8_gemm(C.byref(g)), "b200q_fp8_gemm")
     return out
+
+
+def tp_reduce_bcast(stage, out_ptrs, me, rows, d):
+    """b200q_tp_reduce_bcast on the current stream; out_ptrs = every rank's output buffer address."""
+    arr = (C.c_void_p * len(out_ptrs))(*out_ptrs)
+    check(lib.b200q_tp_reduce_bcast(ptr(stage), arr, len(out_ptrs), me, rows, d, stream_ptr()), "b200q_tp_reduce_bcast")

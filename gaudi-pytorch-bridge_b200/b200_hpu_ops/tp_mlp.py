@@ -76,11 +76,47 @@ def shard_mlp(w_gate8, w_up8, w_down8, s_gate_inv, s_up_inv, s_down_inv, tp: int
     return MlpShard(gu, sgu, wd, s_down_inv.float().contiguous(), hi - lo)
 
 
+class PeerBuffers:
+    """Two bf16 [tokens, d] buffers per rank that every rank of the group can address: `stage`
+    (slot s of rank r = rank s's partial sums of the token rows r owns) and `out` (the finished
+    result).  Allocated and exchanged through torch's symmetric-memory allocator (CUDA virtual
+    memory handles passed between the processes, peer access over NVLink); the kernels see plain
+    device pointers.  barrier() is a kernel on the current stream that returns once every rank of
+    the group has reached it."""
+
+    def __init__(self, tokens: int, d: int, device, group=None):
+        import torch.distributed as dist
+        import torch.distributed._symmetric_memory as symm
+
+        group = group if group is not None else dist.group.WORLD
+        self.tp, self.rank = dist.get_world_size(group), dist.get_rank(group)
+        if tokens % (self.tp * 128):
+            raise ValueError(f"{tokens} tokens do not split into {self.tp} blocks of whole 128-row tiles")
+        self.tokens, self.d, self.rows = tokens, d, tokens // self.tp
+        self.stage = symm.empty(tokens, d, dtype=torch.bfloat16, device=device)
+        self.out = symm.empty(tokens, d, dtype=torch.bfloat16, device=device)
+        self._hs = symm.rendezvous(self.stage, group.group_name)
+        self._ho = symm.rendezvous(self.out, group.group_name)
+        self.stage_ptrs = [int(p) for p in self._hs.buffer_ptrs]
+        self.out_ptrs = [int(p) for p in self._ho.buffer_ptrs]
+
+    def barrier(self):
+        # (the wait inside gives up after 20 s instead of spinning for ever on a rank that died)
+        self._hs.barrier(0, 20000)
+
+
 class TpFp8Mlp:
     """comm: how the row-parallel partial sums become the result at tp > 1.
-    "nccl"  one NCCL bf16 SUM all-reduce per block of token rows, issued asynchronously so that
-            block i's reduction overlaps block i+1's down-projection GEMM;
-    "auto"  "nccl"."""
+    "nccl"   one NCCL bf16 SUM all-reduce per block of token rows, issued asynchronously so that
+             block i's reduction overlaps block i+1's down-projection GEMM;
+    "fused"  the down-projection GEMM writes each 128-row block of its partial sums straight into
+             the staging buffer of the rank that owns those token rows (routed output: peer
+             stores over NVLink from the GEMM's epilogue, tile by tile while the main loop
+             runs), then every rank adds the tp partial sums of its rows in fp32 and writes the
+             result into all ranks' outputs (b200q_tp_reduce_bcast).  One GEMM launch for all
+             tokens, no NCCL call on the path; two barriers across the ranks per forward.  The
+             result is returned in a buffer that the next forward overwrites;
+    "auto"   "fused" on CUDA ranks when tokens divide into tp blocks of whole tiles, else "nccl"."""
 
     def __init__(self, shard: MlpShard, x_scale: float, act_scale: float, group=None, row_blocks: int = 8,
                  ops=None, fused_swiglu: bool = True, fused_gate_up: bool = False, comm: str = "auto"):
@@ -94,24 +130,38 @@ class TpFp8Mlp:
         # the shard's gate/up weights are interleaved (shard_mlp(..., interleave=True)): SwiGLU and the
         # cast run in the GEMM's epilogue and the bf16 [tokens, 2f] intermediate is never written
         self.fused_gate_up = fused_gate_up and ops is None
-        if comm not in ("auto", "nccl"):
+        if comm not in ("auto", "nccl", "fused"):
             raise ValueError(f"unknown comm mode {comm!r}")
-        self.comm = "nccl"
+        self.comm = comm
+        self._peer: Optional[PeerBuffers] = None
         self.skip_collective = False  # measurement only: leaves the partial sums unreduced
         dev = shard.w_gate_up.device
         self._xs_inv = torch.tensor(1.0 / self.x_scale, dtype=torch.float32, device=dev)
         self._as_inv = torch.tensor(1.0 / self.act_scale, dtype=torch.float32, device=dev)
 
-    def describe(self, tp: int) -> str:
+    def _mode(self, tp: int, tokens: int) -> str:
         if tp == 1:
+            return "none"
+        can_fuse = self.ops is torch.ops.hpu and tokens % (tp * 128) == 0 and tokens // tp >= 128 and tokens > 128
+        if self.comm == "fused" and not can_fuse:
+            raise ValueError(f"comm='fused' needs CUDA operators and tokens divisible into {tp} blocks of whole 128-row tiles")
+        return "fused" if (self.comm in ("auto", "fused") and can_fuse) else "nccl"
+
+    def describe(self, tp: int, tokens: int = 8192) -> str:
+        mode = self._mode(tp, tokens)
+        if mode == "none":
             return "tp1: one device, no collective"
+        if mode == "fused":
+            return (f"tp{tp}: column-parallel gate/up, row-parallel down whose epilogue stores each partial-sum block into "
+                    f"its owner's memory over NVLink, then fp32 reduce + broadcast by the owners (no NCCL on the path)")
         return (f"tp{tp}: column-parallel gate/up, row-parallel down, NCCL bf16 all-reduce in {self.row_blocks} row "
                 f"blocks overlapping the down-projection GEMMs")
 
-    def launches_per_step(self, tp: int) -> int:
-        """Kernels of this library per forward (the collective's own kernels are not counted)."""
+    def launches_per_step(self, tp: int, tokens: int = 8192) -> int:
+        """Kernels of this library per forward (NCCL's and the barrier's kernels are not counted)."""
         head = 2 if self.fused_gate_up else 3  # cast, gate/up GEMM (+ SwiGLU/cast kernel)
-        return head + (1 if tp == 1 else self.row_blocks)
+        mode = self._mode(tp, tokens)
+        return head + (1 if mode == "none" else 2 if mode == "fused" else self.row_blocks)
 
     # -- the three local stages ------------------------------------------------------------
     def gate_up(self, x: torch.Tensor) -> torch.Tensor:
@@ -157,6 +207,8 @@ class TpFp8Mlp:
         tp = dist.get_world_size(self.group) if (dist.is_available() and dist.is_initialized()) else 1
         if tp == 1:
             return self.down_partial(h8)
+        if self._mode(tp, h8.shape[0]) == "fused":
+            return self._down_fused(h8)
         rows = h8.shape[0]
         nblk = max(1, min(self.row_blocks, rows))
         step = (rows + nblk - 1) // nblk
@@ -174,6 +226,23 @@ class TpFp8Mlp:
         for w in works:
             w.wait()
         return out
+
+    def _down_fused(self, h8: torch.Tensor) -> torch.Tensor:
+        from . import abi
+        tokens, d = h8.shape[0], self.s.w_down.shape[0]
+        pb = self._peer
+        if pb is None or pb.tokens != tokens or pb.d != d:
+            pb = self._peer = PeerBuffers(tokens, d, h8.device, self.group)
+            pb.barrier()
+        # rank r's partial sums of block i (token rows [i * rows, (i + 1) * rows)) -> slot r of rank i's stage
+        abi.fp8_gemm_nt(h8, self.s.w_down, torch.bfloat16, 1.0 / self.act_scale, self.s.s_down_inv, None,
+                        route=(pb.stage_ptrs, pb.rows, pb.rank * pb.rows))
+        if self.skip_collective:
+            return pb.out
+        pb.barrier()   # every rank's partial sums have landed
+        abi.tp_reduce_bcast(pb.stage, pb.out_ptrs, pb.rank, pb.rows, d)
+        pb.barrier()   # every rank's rows of the result have landed (and the stages are free again)
+        return pb.out
 
     __call__ = forward
 

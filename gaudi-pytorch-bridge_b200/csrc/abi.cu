@@ -76,6 +76,7 @@ int dequant_int4_impl(const int32_t*, const void*, const void*, int, int, int, v
 int w4a16_gemm_impl(const void*, int64_t, const int32_t*, const void*, const int32_t*, int, int, int64_t, int64_t,
                     int64_t, int64_t, void*, int, int64_t, void*, size_t, cudaStream_t);
 size_t w4a16_workspace_bytes_impl(int64_t, int64_t, int64_t);
+int tp_reduce_bcast_impl(const void*, void* const*, int, int, int64_t, int64_t, cudaStream_t);
 int gptq_repack_impl(const int32_t*, int32_t*, int64_t, int64_t, const int32_t*, int32_t*, int64_t, cudaStream_t);
 int w4a16_gemm_noalloc_impl(const void*, int64_t, const int32_t*, const void*, const int32_t*, int, int, int64_t, int64_t,
                             int64_t, int64_t, void*, int, int64_t, cudaStream_t);
@@ -265,7 +266,7 @@ int b200q_fp8_gemm(const b200q_gemm_args* a) {
   if (a->D && !is_wide(a->d_dtype)) return B200Q_ERR_BAD_ARGUMENT;
   const int64_t work = a->M * a->N * a->batch;
   if (work == 0) return B200Q_OK;
-  if (!a->out || (a->K > 0 && (!a->A || !a->B))) return B200Q_ERR_BAD_ARGUMENT;
+  if ((!a->out && a->route_count <= 0) || (a->K > 0 && (!a->A || !a->B))) return B200Q_ERR_BAD_ARGUMENT;
   GemmParams g;
   g.A = a->A; g.B = a->B; g.a_dtype = a->a_dtype; g.b_dtype = a->b_dtype; g.trans_a = a->trans_a; g.trans_b = a->trans_b;
   g.M = a->M; g.N = a->N; g.K = a->K; g.lda = a->lda; g.ldb = a->ldb;
@@ -279,7 +280,16 @@ int b200q_fp8_gemm(const b200q_gemm_args* a) {
   g.out8_dtype = a->out8_dtype; g.out8_scale = a->out8_scale; g.out8_scale_host = a->out8_scale_host;
   if (g.out8_dtype != 0 && !is_fp8(g.out8_dtype)) return B200Q_ERR_BAD_ARGUMENT;
   g.swiglu = a->swiglu;
+  g.route_count = a->route_count; g.route_rows = a->route_rows; g.route_row_offset = a->route_row_offset;
+  for (int i = 0; i < 8; ++i) g.route_out[i] = a->route_out[i];
+  if (g.route_count < 0 || g.route_count > 8) return B200Q_ERR_BAD_ARGUMENT;
+  for (int i = 0; i < g.route_count; ++i)
+    if (!g.route_out[i] || (reinterpret_cast<uintptr_t>(g.route_out[i]) & 15)) return B200Q_ERR_BAD_ARGUMENT;
   cudaStream_t st = static_cast<cudaStream_t>(a->stream);
+  if (g.route_count > 0) {
+    if (g.batch != 1 || a->force_generic || g.route_row_offset < 0) return B200Q_ERR_UNSUPPORTED;
+    return gemm_tcgen05_launch(g, st);  // B200Q_ERR_UNSUPPORTED when the shape has no routed kernel
+  }
   if (g.swiglu) {
     if (g.out8_dtype != B200Q_E4M3) return B200Q_ERR_BAD_ARGUMENT;
     if (g.batch != 1 || g.D || g.trans_a || !g.trans_b || a->force_generic) return B200Q_ERR_UNSUPPORTED;
@@ -317,6 +327,12 @@ int b200q_gptq_repack(const int32_t* qweight, int32_t* qweight_out, int64_t K, i
   if (K * N > 0 && (!qweight || !qweight_out)) return B200Q_ERR_BAD_ARGUMENT;
   if (qzeros && zeros_words > 0 && !qzeros_out) return B200Q_ERR_BAD_ARGUMENT;
   return gptq_repack_impl(qweight, qweight_out, K, N, qzeros, qzeros_out, zeros_words, static_cast<cudaStream_t>(stream));
+}
+
+int b200q_tp_reduce_bcast(const void* stage, void* const* out_ptrs_host, int tp, int me, int64_t rows, int64_t d,
+                          void* stream) {
+  if (!stage || !out_ptrs_host || rows < 0 || d < 0) return B200Q_ERR_BAD_ARGUMENT;
+  return tp_reduce_bcast_impl(stage, out_ptrs_host, tp, me, rows, d, static_cast<cudaStream_t>(stream));
 }
 
 size_t b200q_w4a16_workspace_bytes(int64_t M, int64_t N, int64_t K) {

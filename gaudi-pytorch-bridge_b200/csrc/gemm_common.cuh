@@ -38,6 +38,14 @@ struct GemmParams {
   //   cast(bf16(silu(gate) * up), out8 scale)  with gate / up rounded to out_dtype first,
   // the bytes of fp8_gemm_v2 followed by the SwiGLU + cast kernel
   int swiglu;
+  // Routed output (route_count > 0; bf16 results of the CTA-pair kernel only): block
+  // i = m / route_rows of the token rows goes to buffer route_out[i] -- which may be memory of
+  // another GPU mapped into this process -- at row route_row_offset + m % route_rows.  The
+  // row-parallel projection of a tensor-parallel layer uses it to deliver each partial-sum block
+  // straight to the rank that reduces it.
+  void* route_out[8];
+  int route_count;
+  int64_t route_rows, route_row_offset;
 };
 
 // value in out_dtype -> fp8 byte of the fused output cast

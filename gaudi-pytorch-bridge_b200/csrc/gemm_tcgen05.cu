@@ -96,17 +96,160 @@ __device__ __forceinline__ EpiRow epi_stage_operands(const GemmParams& g, int64_
   return r;
 }
 
+// Run-time choices of the epilogue that are the same for every element of a launch.
+struct EpiFlags {
+  bool full_extra, colA, colB, colBias;
+  float s8;
+};
+template <bool SWAP>
+__device__ __forceinline__ EpiFlags epi_flags(const GemmParams& g) {
+  constexpr int kColMode = SWAP ? B200Q_BCAST_PER_ROW : B200Q_BCAST_PER_COL;
+  EpiFlags f;
+  f.full_extra = g.bias_mode == B200Q_BCAST_FULL || g.D != nullptr;
+  f.colA = g.a_scale_mode == kColMode;
+  f.colB = g.b_scale_mode == kColMode;
+  f.colBias = g.bias_mode == kColMode;
+  f.s8 = g.out8_dtype ? out8_scale_value(g) : 1.f;
+  return f;
+}
+
+// CW accumulator values of this thread's lane (columns c0 .. c0 + CW of the tile) -> scaled,
+// biased, rounded, stored.  The column-side operands come from shared memory as 16-byte vectors
+// and only those that exist are read (a sixth of the shared-memory instructions of reading
+// three scalars per element).
+template <int CW>
+__device__ __forceinline__ void epi_values(const uint32_t* r, int c0, const EpiRow& e, const float* cA, const float* cB,
+                                           const float* cBias, const EpiFlags& f, float* v) {
+  const float rA = e.rA, rB = e.rB, rBias = e.rBias;
+  if (f.colA || f.colB || f.colBias) {
+#pragma unroll
+    for (int j = 0; j < CW; j += 4) {
+      const float4 one = make_float4(1.f, 1.f, 1.f, 1.f), zero = make_float4(0.f, 0.f, 0.f, 0.f);
+      const float4 sa = f.colA ? *reinterpret_cast<const float4*>(cA + c0 + j) : one;
+      const float4 sb = f.colB ? *reinterpret_cast<const float4*>(cB + c0 + j) : one;
+      const float4 bb = f.colBias ? *reinterpret_cast<const float4*>(cBias + c0 + j) : zero;
+      const float sav[4] = {sa.x, sa.y, sa.z, sa.w}, sbv[4] = {sb.x, sb.y, sb.z, sb.w}, bbv[4] = {bb.x, bb.y, bb.z, bb.w};
+#pragma unroll
+      for (int q = 0; q < 4; ++q) {
+        float a = __uint_as_float(r[j + q]);
+        a = a * (rA * sav[q]);
+        a = a * (rB * sbv[q]);
+        v[j + q] = a + (rBias + bbv[q]);
+      }
+    }
+  } else {
+    // no column-side operand (the staged arrays hold 1, 1, 0): same arithmetic from registers
+#pragma unroll
+    for (int j = 0; j < CW; ++j) v[j] = (__uint_as_float(r[j]) * rA) * rB + rBias;
+  }
+}
+
+template <int BN, bool SWAP>
+__device__ __forceinline__ void epi_chunk(const GemmParams& g, const uint32_t* r, int c0, const EpiRow& e, int64_t y0,
+                                          const float* cA, const float* cB, const float* cBias, const EpiFlags& f) {
+  constexpr int CW = (BN % 32 == 0) ? 32 : 16;
+  const int64_t x = e.x;
+  const bool x_in = e.x_in;
+  const float s8 = f.s8;
+  const bool full_extra = f.full_extra;
+  float v[CW];
+  epi_values<CW>(r, c0, e, cA, cB, cBias, f, v);
+  if (!SWAP) {
+    // thread = output row m, registers = CW consecutive output columns n
+    const int64_t m = x, n0 = y0 + c0;
+    if (x_in) {
+      if (full_extra) {
+#pragma unroll
+        for (int j = 0; j < CW; ++j) {
+          const int64_t n = n0 + j;
+          if (n < g.N) {
+            if (g.bias_mode == B200Q_BCAST_FULL) v[j] += ld_out_typed(g.bias, g.bias_dtype, m * g.bias_ld + n);
+            if (g.D) v[j] += ld_out_typed(g.D, g.d_dtype, m * g.ldd + n);
+          }
+        }
+      }
+      if (g.out8_dtype) {
+        uint8_t* o = static_cast<uint8_t*>(g.out) + m * g.ldo + n0;
+        uint32_t w[CW / 4];
+#pragma unroll
+        for (int j = 0; j < CW; j += 4)
+          w[j / 4] = out8_byte(g, v[j], s8) | (out8_byte(g, v[j + 1], s8) << 8) | (out8_byte(g, v[j + 2], s8) << 16) |
+                     (out8_byte(g, v[j + 3], s8) << 24);
+        if (n0 + CW <= g.N && (reinterpret_cast<uintptr_t>(o) & 15) == 0) {
+#pragma unroll
+          for (int j = 0; j < CW / 4; j += 4) *reinterpret_cast<uint4*>(o + 4 * j) = make_uint4(w[j], w[j + 1], w[j + 2], w[j + 3]);
+        } else {
+#pragma unroll
+          for (int j = 0; j < CW; ++j)
+            if (n0 + j < g.N) o[j] = (uint8_t)(w[j / 4] >> (8 * (j & 3)));
+        }
+      } else if (g.out_dtype == B200Q_BF16) {
+        __nv_bfloat16* o = static_cast<__nv_bfloat16*>(g.out) + m * g.ldo + n0;
+        if (n0 + CW <= g.N && (reinterpret_cast<uintptr_t>(o) & 15) == 0) {
+#pragma unroll
+          for (int j = 0; j < CW; j += 8)
+            *reinterpret_cast<uint4*>(o + j) =
+                make_uint4(pack_bf16x2(v[j], v[j + 1]), pack_bf16x2(v[j + 2], v[j + 3]),
+                           pack_bf16x2(v[j + 4], v[j + 5]), pack_bf16x2(v[j + 6], v[j + 7]));
+        } else {
+#pragma unroll
+          for (int j = 0; j < CW; ++j)
+            if (n0 + j < g.N) o[j] = __float2bfloat16_rn(v[j]);
+        }
+      } else {
+        float* o = static_cast<float*>(g.out) + m * g.ldo + n0;
+        if (n0 + CW <= g.N && (reinterpret_cast<uintptr_t>(o) & 15) == 0) {
+#pragma unroll
+          for (int j = 0; j < CW; j += 4)
+            *reinterpret_cast<float4*>(o + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+        } else {
+#pragma unroll
+          for (int j = 0; j < CW; ++j)
+            if (n0 + j < g.N) o[j] = v[j];
+        }
+      }
+    }
+  } else {
+    // thread = output column n (weight row), registers = CW consecutive tokens m
+    const int64_t n = x;
+    if (x_in && !full_extra && !g.out8_dtype) {
+      // the common cases with every run-time choice hoisted out of the per-element loop (the
+      // general loop below re-decides dtype, bias and accumulate input for every element and
+      // runs several times slower)
+      const int64_t left = g.M - (y0 + c0);
+      if (g.out_dtype == B200Q_BF16) {
+        __nv_bfloat16* o = static_cast<__nv_bfloat16*>(g.out) + (y0 + c0) * g.ldo + n;
+#pragma unroll
+        for (int j = 0; j < CW; ++j)
+          if (j < left) o[(int64_t)j * g.ldo] = __float2bfloat16_rn(v[j]);
+      } else {
+        float* o = static_cast<float*>(g.out) + (y0 + c0) * g.ldo + n;
+#pragma unroll
+        for (int j = 0; j < CW; ++j)
+          if (j < left) o[(int64_t)j * g.ldo] = v[j];
+      }
+    } else if (x_in) {
+#pragma unroll
+      for (int j = 0; j < CW; ++j) {
+        const int64_t m = y0 + c0 + j;
+        if (m < g.M) {
+          float o = v[j];
+          if (g.bias_mode == B200Q_BCAST_FULL) o += ld_out_typed(g.bias, g.bias_dtype, m * g.bias_ld + n);
+          if (g.D) o += ld_out_typed(g.D, g.d_dtype, m * g.ldd + n);
+          if (g.out8_dtype) static_cast<uint8_t*>(g.out)[m * g.ldo + n] = (uint8_t)out8_byte(g, o, s8);
+          else if (g.out_dtype == B200Q_BF16) static_cast<__nv_bfloat16*>(g.out)[m * g.ldo + n] = __float2bfloat16_rn(o);
+          else static_cast<float*>(g.out)[m * g.ldo + n] = o;
+        }
+      }
+    }
+  }
+}
+
 // TMEM accumulator (this warp's 32 lanes, BN columns from t_row) -> scaled, biased, rounded, stored.
 template <int BN, bool SWAP>
 __device__ __forceinline__ void epi_drain(const GemmParams& g, uint32_t t_row, const EpiRow& e, int64_t y0,
                                           const float* cA, const float* cB, const float* cBias) {
-  const bool full_extra = g.bias_mode == B200Q_BCAST_FULL || g.D != nullptr;
-  const int64_t x = e.x;
-  const bool x_in = e.x_in;
-  const float rA = e.rA, rB = e.rB, rBias = e.rBias;
-  const float s8 = g.out8_dtype ? out8_scale_value(g) : 1.f;
-  constexpr int kColMode = SWAP ? B200Q_BCAST_PER_ROW : B200Q_BCAST_PER_COL;
-  const bool col_ops = g.a_scale_mode == kColMode || g.b_scale_mode == kColMode || g.bias_mode == kColMode;
+  const EpiFlags f = epi_flags<SWAP>(g);
 #pragma unroll 1
   for (int c0 = 0; c0 < BN; c0 += 32) {
     uint32_t r[32];
@@ -116,110 +259,52 @@ __device__ __forceinline__ void epi_drain(const GemmParams& g, uint32_t t_row, c
       tmem_ld_32x16(t_row + c0, r);  // BN == 16
     }
     tmem_ld_wait();
-    constexpr int CW = (BN % 32 == 0) ? 32 : 16;
-    float v[CW];
-    if (col_ops) {
+    epi_chunk<BN, SWAP>(g, r, c0, e, y0, cA, cB, cBias, f);
+  }
+}
+
+// Routed bf16 output (GemmParams::route_*): the rows of this CTA's tile belong to one destination
+// buffer, possibly in another GPU's memory.  A thread's 64 output columns go through a 4 KB
+// shared-memory patch of its warp (row per thread, 16-byte pieces XOR-swizzled by row so that
+// neither side has bank conflicts) and leave as whole 128-byte row segments, four rows per store
+// instruction: a peer write crosses NVLink as full lines instead of 32 scattered 16-byte pieces.
+template <int BN>
+__device__ __forceinline__ void epi_drain_routed(const GemmParams& g, uint32_t t_row, const EpiRow& e, int64_t row0,
+                                                 int64_t y0, const float* cA, const float* cB, const float* cBias,
+                                                 uint4* patch, int lane) {
+  static_assert(BN % 64 == 0, "routed output is written in 64-column groups");
+  const EpiFlags f = epi_flags<false>(g);
+  // destination of this warp's 32 rows (row0 = first row; all of them in one route block)
+  const int64_t blk = row0 / g.route_rows;
+  __nv_bfloat16* dst0 = static_cast<__nv_bfloat16*>(g.route_out[blk]) +
+                        (g.route_row_offset + (row0 - blk * g.route_rows)) * g.ldo;
+#pragma unroll 1
+  for (int c0 = 0; c0 < BN; c0 += 64) {
 #pragma unroll
-      for (int j = 0; j < CW; ++j) {
-        float a = __uint_as_float(r[j]);
-        a = a * (rA * cA[c0 + j]);
-        a = a * (rB * cB[c0 + j]);
-        v[j] = a + (rBias + cBias[c0 + j]);
-      }
-    } else {
-      // no column-side operand (the staged arrays hold 1, 1, 0): same arithmetic from registers
+    for (int h = 0; h < 2; ++h) {
+      uint32_t r[32];
+      tmem_ld_32x32(t_row + c0 + 32 * h, r);
+      tmem_ld_wait();
+      float v[32];
+      epi_values<32>(r, c0 + 32 * h, e, cA, cB, cBias, f, v);
 #pragma unroll
-      for (int j = 0; j < CW; ++j) v[j] = (__uint_as_float(r[j]) * rA) * rB + rBias;
-    }
-    if (!SWAP) {
-      // thread = output row m, registers = CW consecutive output columns n
-      const int64_t m = x, n0 = y0 + c0;
-      if (x_in) {
-        if (full_extra) {
-#pragma unroll
-          for (int j = 0; j < CW; ++j) {
-            const int64_t n = n0 + j;
-            if (n < g.N) {
-              if (g.bias_mode == B200Q_BCAST_FULL) v[j] += ld_out_typed(g.bias, g.bias_dtype, m * g.bias_ld + n);
-              if (g.D) v[j] += ld_out_typed(g.D, g.d_dtype, m * g.ldd + n);
-            }
-          }
-        }
-        if (g.out8_dtype) {
-          uint8_t* o = static_cast<uint8_t*>(g.out) + m * g.ldo + n0;
-          uint32_t w[CW / 4];
-#pragma unroll
-          for (int j = 0; j < CW; j += 4)
-            w[j / 4] = out8_byte(g, v[j], s8) | (out8_byte(g, v[j + 1], s8) << 8) | (out8_byte(g, v[j + 2], s8) << 16) |
-                       (out8_byte(g, v[j + 3], s8) << 24);
-          if (n0 + CW <= g.N && (reinterpret_cast<uintptr_t>(o) & 15) == 0) {
-#pragma unroll
-            for (int j = 0; j < CW / 4; j += 4) *reinterpret_cast<uint4*>(o + 4 * j) = make_uint4(w[j], w[j + 1], w[j + 2], w[j + 3]);
-          } else {
-#pragma unroll
-            for (int j = 0; j < CW; ++j)
-              if (n0 + j < g.N) o[j] = (uint8_t)(w[j / 4] >> (8 * (j & 3)));
-          }
-        } else if (g.out_dtype == B200Q_BF16) {
-          __nv_bfloat16* o = static_cast<__nv_bfloat16*>(g.out) + m * g.ldo + n0;
-          if (n0 + CW <= g.N && (reinterpret_cast<uintptr_t>(o) & 15) == 0) {
-#pragma unroll
-            for (int j = 0; j < CW; j += 8)
-              *reinterpret_cast<uint4*>(o + j) =
-                  make_uint4(pack_bf16x2(v[j], v[j + 1]), pack_bf16x2(v[j + 2], v[j + 3]),
-                             pack_bf16x2(v[j + 4], v[j + 5]), pack_bf16x2(v[j + 6], v[j + 7]));
-          } else {
-#pragma unroll
-            for (int j = 0; j < CW; ++j)
-              if (n0 + j < g.N) o[j] = __float2bfloat16_rn(v[j]);
-          }
-        } else {
-          float* o = static_cast<float*>(g.out) + m * g.ldo + n0;
-          if (n0 + CW <= g.N && (reinterpret_cast<uintptr_t>(o) & 15) == 0) {
-#pragma unroll
-            for (int j = 0; j < CW; j += 4)
-              *reinterpret_cast<float4*>(o + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
-          } else {
-#pragma unroll
-            for (int j = 0; j < CW; ++j)
-              if (n0 + j < g.N) o[j] = v[j];
-          }
-        }
-      }
-    } else {
-      // thread = output column n (weight row), registers = CW consecutive tokens m
-      const int64_t n = x;
-      if (x_in && !full_extra && !g.out8_dtype) {
-        // the common cases with every run-time choice hoisted out of the per-element loop (the
-        // general loop below re-decides dtype, bias and accumulate input for every element and
-        // runs several times slower)
-        const int64_t left = g.M - (y0 + c0);
-        if (g.out_dtype == B200Q_BF16) {
-          __nv_bfloat16* o = static_cast<__nv_bfloat16*>(g.out) + (y0 + c0) * g.ldo + n;
-#pragma unroll
-          for (int j = 0; j < CW; ++j)
-            if (j < left) o[(int64_t)j * g.ldo] = __float2bfloat16_rn(v[j]);
-        } else {
-          float* o = static_cast<float*>(g.out) + (y0 + c0) * g.ldo + n;
-#pragma unroll
-          for (int j = 0; j < CW; ++j)
-            if (j < left) o[(int64_t)j * g.ldo] = v[j];
-        }
-      } else if (x_in) {
-#pragma unroll
-        for (int j = 0; j < CW; ++j) {
-          const int64_t m = y0 + c0 + j;
-          if (m < g.M) {
-            float o = v[j];
-            if (g.bias_mode == B200Q_BCAST_FULL) o += ld_out_typed(g.bias, g.bias_dtype, m * g.bias_ld + n);
-            if (g.D) o += ld_out_typed(g.D, g.d_dtype, m * g.ldd + n);
-            if (g.out8_dtype) static_cast<uint8_t*>(g.out)[m * g.ldo + n] = (uint8_t)out8_byte(g, o, s8);
-            else if (g.out_dtype == B200Q_BF16) static_cast<__nv_bfloat16*>(g.out)[m * g.ldo + n] = __float2bfloat16_rn(o);
-            else static_cast<float*>(g.out)[m * g.ldo + n] = o;
-          }
-        }
+      for (int k = 0; k < 4; ++k) {
+        const int piece = 4 * h + k;
+        patch[lane * 8 + (piece ^ (lane & 7))] =
+            make_uint4(pack_bf16x2(v[8 * k], v[8 * k + 1]), pack_bf16x2(v[8 * k + 2], v[8 * k + 3]),
+                       pack_bf16x2(v[8 * k + 4], v[8 * k + 5]), pack_bf16x2(v[8 * k + 6], v[8 * k + 7]));
       }
     }
+    __syncwarp();
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      const int row = 4 * k + (lane >> 3), piece = lane & 7;
+      const uint4 val = patch[row * 8 + (piece ^ (row & 7))];
+      const int64_t n = y0 + c0 + piece * 8;
+      if (row0 + row < g.M && n + 8 <= g.N)
+        *reinterpret_cast<uint4*>(dst0 + (int64_t)row * g.ldo + n) = val;
+    }
+    __syncwarp();
   }
 }
 
@@ -469,7 +554,9 @@ struct PairSmem {
   static constexpr int kStageBytes = kXBytes + kYBytes;
   static constexpr int kRing = STAGES * kStageBytes;
   static constexpr int kEpiFloats = 2 * 3 * BN;
-  static constexpr int kBarOffset = kRing + kEpiFloats * 4;
+  static constexpr int kPatchOffset = kRing + kEpiFloats * 4;  // 4 epilogue warps x 4 KB (routed output)
+  static constexpr int kPatchBytes = (BN % 64 == 0) ? 4 * 4096 : 0;
+  static constexpr int kBarOffset = kPatchOffset + kPatchBytes;
   static constexpr int kNumBars = 2 * STAGES + 4;
   static constexpr int kTotal = kBarOffset + kNumBars * 8 + 16;
 };
@@ -609,8 +696,16 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
       named_bar_sync(1, kEpiThreads);
       if (*epi_stop) break;
       tc_fence_after();
-      if (BN == 256 && g.swiglu) epi_drain_swiglu(g, tmem_base + ((uint32_t)(q * 32) << 16) + acc * BN, er, y0, cA, cB, cBias);
-      else epi_drain<BN, false>(g, tmem_base + ((uint32_t)(q * 32) << 16) + acc * BN, er, y0, cA, cB, cBias);
+      const uint32_t t_row = tmem_base + ((uint32_t)(q * 32) << 16) + acc * BN;
+      if (BN == 256 && g.swiglu) {
+        epi_drain_swiglu(g, t_row, er, y0, cA, cB, cBias);
+      } else if (BN % 64 == 0 && g.route_count > 0) {
+        if constexpr (BN % 64 == 0)
+          epi_drain_routed<BN>(g, t_row, er, x0 + q * 32, y0, cA, cB, cBias,
+                               reinterpret_cast<uint4*>(smem + L::kPatchOffset) + q * 256, lane);
+      } else {
+        epi_drain<BN, false>(g, t_row, er, y0, cA, cB, cBias);
+      }
       tc_fence_before();
       mbar_arrive_cluster((bar_tempty + 8 * acc) & kPeerBitMask);  // the even CTA's barrier
     }
@@ -719,6 +814,13 @@ int gemm_tcgen05_launch(const GemmParams& g, cudaStream_t st) {
   if (g.swiglu && (g.M <= 128 || (g.N % 256) || a_mn || b_mn || g.out_dtype != B200Q_BF16 || g.out8_dtype != B200Q_E4M3))
     return B200Q_ERR_UNSUPPORTED;
 
+  // routed output: bf16 rows through the CTA-pair kernel, every 128-row block inside one route block
+  const bool routed = g.route_count > 0;
+  if (routed && (g.M <= 128 || g.N <= 128 || a_mn || b_mn || g.out_dtype != B200Q_BF16 || g.out8_dtype || g.swiglu || g.D ||
+                 g.bias_mode == B200Q_BCAST_FULL || (g.N % 8) || (g.ldo % 8) || g.route_rows <= 0 || (g.route_rows % 128) ||
+                 g.route_count > 8 || (g.M + g.route_rows - 1) / g.route_rows > g.route_count))
+    return B200Q_ERR_UNSUPPORTED;
+
   TcGemmParams tp;
   tp.g = g;
   static const bool no_probe = std::getenv("B200Q_GEMM_NO_PROBE") != nullptr;
@@ -763,12 +865,13 @@ int gemm_tcgen05_launch(const GemmParams& g, cudaStream_t st) {
       double bestp = 1e30;
       static const int kPairWidths[] = {256, 224, 192};
       for (int w : kPairWidths) {
+        if (routed && (w % 64)) continue;
         const int64_t tiles = (int64_t)pp.x_tiles * ((g.N + w - 1) / w);
         const double cost = (double)((tiles + kNumSMs / 2 - 1) / (kNumSMs / 2)) * (w + kTileOverheadCols);
         if (cost < bestp) { bestp = cost; bp = w; }
       }
       static const int forced = std::getenv("B200Q_GEMM_PAIR_BN") ? std::atoi(std::getenv("B200Q_GEMM_PAIR_BN")) : 0;
-      if (forced == 256 || forced == 224 || forced == 192) bp = forced;
+      if ((forced == 256 || forced == 224 || forced == 192) && !(routed && (forced % 64))) bp = forced;
       if (g.swiglu) bp = 256;  // gate and up halves of a tile
       pp.y_tiles = (int)((g.N + bp - 1) / bp);
       rc = make_operand_map(&my, g.B, g.N, g.K, g.ldb, bp / 2);
@@ -780,7 +883,7 @@ int gemm_tcgen05_launch(const GemmParams& g, cudaStream_t st) {
       }
       if (rc != B200Q_ERR_UNSUPPORTED) return rc;
     }
-    if (g.swiglu) return B200Q_ERR_UNSUPPORTED;  // only the pair kernel has the fused SwiGLU epilogue
+    if (g.swiglu || routed) return B200Q_ERR_UNSUPPORTED;  // only the pair kernel has these epilogues
     rc = make_map(&my, g.B, g.N, g.K, g.ldb, b_mn, bn);
     if (rc) return rc;
     switch (bn) {

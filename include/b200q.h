@@ -214,9 +214,41 @@ typedef struct b200q_gemm_args {
    * cast(bf16(silu(gate) * up), out8 scale) with gate / up rounded to out_dtype first, i.e. the
    * bytes of this GEMM followed by b200q_swiglu_cast_fp8, without the [M][N] round trip. */
   int swiglu;
+  /* Routed output (route_count = 0: off).  With route_count = r in 1..8, block i = m / route_rows of
+   * the token rows is written to route_out[i] (bf16, row stride ldo) at row
+   * route_row_offset + m % route_rows instead of to `out`; the buffers may be memory of other
+   * GPUs mapped into this process (peer access enabled), which are then written with plain
+   * stores of whole 128-byte row segments.  This is how the row-parallel projection of a
+   * tensor-parallel layer hands each block of partial sums to the rank that reduces it while
+   * the GEMM is still running; b200q_tp_reduce_bcast finishes the job.  Needs M > 128, bf16
+   * output, K-major operands, no D / element-wise bias / fused cast, N % 8 == 0,
+   * route_rows % 128 == 0, 16-byte aligned buffers; otherwise B200Q_ERR_UNSUPPORTED.  The
+   * reference has no counterpart: its collective is a separate call on the finished tensor
+   * (python_packages/habana_frameworks/torch/distributed/hccl/process_group_hccl_base.cpp:412-497). */
+  void* route_out[8];
+  int route_count;
+  int64_t route_rows, route_row_offset;
 } b200q_gemm_args;
 
 int b200q_fp8_gemm(const b200q_gemm_args* args);
+
+/*
+ * tp_reduce_bcast: the reduction half of a SUM all-reduce whose scatter half was done by the
+ * producer (routed GEMM output above).  Stands in for ProcessGroupHcclBase::allreduce,
+ * python_packages/habana_frameworks/torch/distributed/hccl/process_group_hccl_base.cpp:412-497,
+ * on the output of a row-parallel projection.
+ *
+ * stage          this rank's staging buffer, bf16 [tp][rows][d]: slot s holds rank s's partial sums
+ *                of the `rows` token rows this rank owns
+ * out_ptrs_host  HOST array of tp device pointers: the full output bf16 [tp*rows][d] of every rank,
+ *                in rank order (own buffer included; the others are peer mappings)
+ * The tp slots are added in slot order in fp32 and rounded once to bf16; rows
+ * [me*rows, (me+1)*rows) of every output receive the same bytes.  The caller orders this call
+ * after every rank's producer (a barrier across the ranks) and the consumers of the outputs
+ * after every rank's call.
+ */
+int b200q_tp_reduce_bcast(const void* stage, void* const* out_ptrs_host, int tp, int me, int64_t rows,
+                          int64_t d, void* stream);
 
 /*
  * w4a16_gemm: out[M][N] = x[M][K] @ W[K][N], W = (nibble - zp) * scale rounded to bf16 exactly

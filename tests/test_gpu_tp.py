@@ -86,7 +86,7 @@ def _worker(rank, world, port, q):
         inited = True
         import b200_hpu_ops
         from b200_hpu_ops import tp_mlp
-        T, d, f = 512, 512, 2048
+        T, d, f = 1024, 512, 2048  # 1024 tokens: whole 128-row tiles per rank up to 8 ranks
         x, wg8, wu8, wd8, sg, su, sd, xs, acs = _problem(T, d, f)
         dev = torch.device("cuda", rank)
         args = (wg8.to(dev), wu8.to(dev), wd8.to(dev), sg.to(dev), su.to(dev), sd.to(dev))
@@ -100,7 +100,7 @@ def _worker(rank, world, port, q):
             h_mine, h_full = mlp.hidden(x.to(dev)), full.hidden(x.to(dev))
             same = torch.equal(h_mine.view(torch.uint8), h_full[:, lo:hi].view(torch.uint8))
             for _ in range(2):  # twice: buffers and flags of the first call are reused by the second
-                y = mlp(x.to(dev))
+                y = mlp(x.to(dev)).clone()
             torch.cuda.synchronize()
             errs.append((comm, float(O.rel_frobenius(y, ref)), same))
         q.put((rank, errs, b200_hpu_ops.device_status()))
@@ -111,7 +111,7 @@ def _worker(rank, world, port, q):
             dist.destroy_process_group()
 
 
-COMM_MODES = ("nccl",)
+COMM_MODES = ("nccl", "fused")
 
 
 @pytest.mark.parametrize("world", [2, 4, 8])
