@@ -559,7 +559,8 @@ def family_record(args, dev, peaks):
     """The other operators BASELINE.json's metric names, each timed for a few milliseconds."""
     members = [("cast_rne", 1 << 24), ("cast_rne", 1 << 26), ("cast_sr", 1 << 24), ("cast_sr", 1 << 26),
                ("uncast", 1 << 24), ("uncast", 1 << 26), ("dequant", None), ("dequant_kpacked", None),
-               ("gemm_m1", None), ("gemm_m16", None), ("gemm_m128", None), ("w4a16_m16", None), ("w4a16_m2048", None)]
+               ("gemm_m1", None), ("gemm_m16", None), ("gemm_m128", None), ("w4a16_m16", None), ("w4a16_m16_kpacked", None),
+               ("w4a16_m2048", None)]
     out = {}
     for name, elems in members:
         a = argparse.Namespace(**vars(args))

@@ -689,6 +689,17 @@ at::Tensor w4a16_gemm(const at::Tensor& x, const at::Tensor& qweight, const at::
     zp_kind = B200Q_ZP_PACKED;
   }
   at::Tensor out = at::empty({M, N}, xc.options().dtype(out_dtype));
+  if (k_packed && M > 16) {
+    // The AutoGPTQ layout [K/8, N] is read directly only by the few-token kernel; more tokens go
+    // through one repack pass into the operator layout [K, N/8] (a weight-sized copy: callers
+    // that keep weights resident should call b200q::gptq_repack once instead).
+    TORCH_CHECK(K % 8 == 0 && N % 8 == 0, "w4a16_gemm: K and N must be multiples of 8");
+    at::Tensor q2 = at::empty({K, N / 8}, q.options());
+    check_status(b200q_gptq_repack(q.data_ptr<int32_t>(), q2.data_ptr<int32_t>(), K, N, nullptr, nullptr, 0, current_stream()),
+                 "w4a16_gemm (repack)");
+    q = q2;
+    k_packed = false;
+  }
   const size_t ws_bytes = b200q_w4a16_workspace_bytes(M, N, K);
   at::Tensor ws;
   if (ws_bytes) ws = at::empty({(int64_t)ws_bytes}, xc.options().dtype(at::kByte));

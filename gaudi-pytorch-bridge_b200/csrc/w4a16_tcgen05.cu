@@ -899,8 +899,15 @@ static int w4a16_splits(int64_t M, int64_t N, int64_t K) {
   return (int)((num_kb + per - 1) / per);  // drop splits that would be empty
 }
 
+// few-token kernel (w4a16_smallm.cu)
+bool w4a16_smallm_eligible(int64_t M, int64_t N, int64_t K, int64_t group, int k_packed);
+int w4a16_smallm_launch(const void* x, int64_t ldx, const int32_t* qweight, const void* scale, const int32_t* zp,
+                        int k_packed, int64_t M, int64_t N, int64_t K, int64_t group, void* out, int out_dtype,
+                        int64_t ldo, cudaStream_t st);
+
 size_t w4a16_workspace_bytes_impl(int64_t M, int64_t N, int64_t K) {
   if (M <= 0 || N <= 0 || K <= 0 || K % w4::kK || N % 32) return 0;  // shapes the fused kernel does not take
+  if (w4a16_smallm_eligible(M, N, K, w4::kK, 0)) return 0;  // reduced inside its clusters: no scratch
   const int s = w4a16_splits(M, N, K);
   return s > 1 ? (size_t)s * (size_t)M * (size_t)N * sizeof(float) : 0;
 }
@@ -908,13 +915,19 @@ size_t w4a16_workspace_bytes_impl(int64_t M, int64_t N, int64_t K) {
 int w4a16_gemm_impl(const void* x, int64_t ldx, const int32_t* qweight, const void* scale, const int32_t* zp,
                     int zp_kind, int k_packed, int64_t M, int64_t N, int64_t K, int64_t group, void* out,
                     int out_dtype, int64_t ldo, void* workspace, size_t workspace_bytes, cudaStream_t st) {
-  if (k_packed) return B200Q_ERR_UNSUPPORTED;  // the fused kernel takes the operator layout [K][N/8]
   if (K == 0) {
     // an empty contraction: the result is all zeros (rows may be strided)
     const size_t esz = out_dtype == B200Q_BF16 ? 2 : 4;
     B200Q_CUDA_OK(cudaMemset2DAsync(out, (size_t)ldo * esz, 0, (size_t)N * esz, (size_t)M, st));
     return B200Q_OK;
   }
+  // a handful of tokens: the streaming kernel (either weight layout)
+  if (w4a16_smallm_eligible(M, N, K, group, k_packed)) {
+    const int rc = w4a16_smallm_launch(x, ldx, qweight, scale, zp_kind == B200Q_ZP_PACKED ? zp : nullptr, k_packed, M, N, K,
+                                       group, out, out_dtype, ldo, st);
+    if (rc != B200Q_ERR_UNSUPPORTED) return rc;
+  }
+  if (k_packed) return B200Q_ERR_UNSUPPORTED;  // the tcgen05 kernels take the operator layout [K][N/8]
   if (K % w4::kK || group % w4::kK || K % group || N % 32 || ldx % 8) return B200Q_ERR_UNSUPPORTED;
   if ((reinterpret_cast<uintptr_t>(x) | reinterpret_cast<uintptr_t>(qweight) | reinterpret_cast<uintptr_t>(scale)) & 15)
     return B200Q_ERR_UNSUPPORTED;

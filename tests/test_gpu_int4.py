@@ -229,3 +229,54 @@ def test_w4a16_degenerate_k():
                                   abi.ptr(out), abi.BF16, 64, None, 0, abi.stream_ptr())
     assert rc == 0
     assert torch.count_nonzero(out).item() == 0
+
+
+def _pack_k(w):
+    """[K, N] nibble values -> AutoGPTQ layout [K/8, N]: nibble i of word (r, n) is w[8r + i, n]."""
+    return O.pack_nibbles(w.t().contiguous()).t().contiguous()
+
+
+@pytest.mark.parametrize("M", [1, 5, 8, 9, 16])
+@pytest.mark.parametrize("N,K,group", [(512, 256, 128), (1024, 2048, 64), (512, 4096, 128), (1024, 8192, 128)])
+@pytest.mark.parametrize("k_packed", [False, True])
+def test_w4a16_few_tokens_kernel(ops, M, N, K, group, k_packed):
+    """M <= 16 takes the streaming kernel (cluster-reduced, no scratch) for both weight layouts:
+    fp32 output against the unfused GPU composition (same bf16 weights, fp32 sums), bf16 output
+    against the oracle, and a one-hot probe that reads single weight rows back exactly."""
+    if k_packed and K % 1024:
+        pytest.skip("the AutoGPTQ-layout form of the kernel needs K % 1024 == 0")
+    g = torch.Generator().manual_seed(M * 131 + N + K)
+    for with_zp in (True, False):
+        w = torch.randint(0, 16, (K, N), generator=g)
+        qw = _pack_k(w) if k_packed else O.pack_nibbles(w)
+        scale = (torch.rand(K // group, N, generator=g) * 0.015 + 0.005).to(torch.bfloat16)
+        zp = O.pack_nibbles(torch.randint(0, 16, (K // group, N), generator=g)) if with_zp else None
+        x = torch.randn(M, K, generator=g).to(torch.bfloat16)
+        zc = None if zp is None else zp.cuda()
+        assert ops.abi.lib.b200q_w4a16_workspace_bytes(M, N, K) == 0
+        wdq = O.convert_from_uint4(O.pack_nibbles(w), scale, zp, torch.bfloat16)
+        r32 = torch.ops.b200q.w4a16_gemm(x.cuda(), qw.cuda(), scale.cuda(), zc, group, k_packed, torch.float32)
+        e32 = (x.double() @ wdq.double()).float()
+        assert O.rel_frobenius(r32, e32) <= 2e-5
+        r = torch.ops.b200q.w4a16_gemm(x.cuda(), qw.cuda(), scale.cuda(), zc, group, k_packed, torch.bfloat16)
+        assert r.dtype == torch.bfloat16 and r.shape == (M, N)
+        assert O.rel_frobenius(r, e32) <= 1e-2
+        assert torch.equal(r, torch.ops.b200q.w4a16_gemm(x.cuda(), qw.cuda(), scale.cuda(), zc, group, k_packed, torch.bfloat16))
+        rows = (torch.arange(M) * 397 + 11) % K
+        hot = torch.zeros(M, K)
+        hot[torch.arange(M), rows] = 1.0
+        rh = torch.ops.b200q.w4a16_gemm(hot.to(torch.bfloat16).cuda(), qw.cuda(), scale.cuda(), zc, group, k_packed, torch.float32)
+        assert torch.equal(rh.cpu(), wdq.float()[rows])
+    assert ops.device_status() == 0
+
+
+def test_w4a16_kpacked_many_tokens_goes_through_repack(ops):
+    g = torch.Generator().manual_seed(77)
+    M, N, K, group = 160, 512, 1024, 128
+    w = torch.randint(0, 16, (K, N), generator=g)
+    scale = (torch.rand(K // group, N, generator=g) * 0.015 + 0.005).to(torch.bfloat16)
+    zp = O.pack_nibbles(torch.randint(0, 16, (K // group, N), generator=g))
+    x = torch.randn(M, K, generator=g).to(torch.bfloat16)
+    a = torch.ops.b200q.w4a16_gemm(x.cuda(), _pack_k(w).cuda(), scale.cuda(), zp.cuda(), group, True, torch.bfloat16)
+    b = torch.ops.b200q.w4a16_gemm(x.cuda(), O.pack_nibbles(w).cuda(), scale.cuda(), zp.cuda(), group, False, torch.bfloat16)
+    assert torch.equal(a, b)

@@ -48,8 +48,9 @@ def test_noalloc_matches_workspace_entry_twice_in_a_row():
     from b200_hpu_ops import abi
     from oracle import hpu_oracle as O
 
-    # two different problems back to back, both on the split-K path (so the scratch is really used)
-    for call, (M, N, K, group, dt) in enumerate([(16, 2048, 4096, 128, torch.bfloat16), (5, 1024, 2048, 64, torch.float32)]):
+    # two different problems back to back, both on the split-K path (so the scratch is really used;
+    # 16 tokens or fewer would take the kernel that reduces inside its clusters and needs none)
+    for call, (M, N, K, group, dt) in enumerate([(24, 2048, 4096, 128, torch.bfloat16), (21, 1024, 2048, 64, torch.float32)]):
         x, qw, scale, zp = _case(M, N, K, group, seed=100 + call)
         ref = torch.empty(M, N, dtype=dt, device="cuda")
         need = _with_workspace(abi, x, qw, scale, zp, group, ref)
