@@ -42,6 +42,7 @@ class GemmArgs(C.Structure):
         ("out8_dtype", C.c_int), ("out8_scale", C.c_void_p), ("out8_scale_host", C.c_float),
         ("swiglu", C.c_int),
         ("route_out", C.c_void_p * 8), ("route_count", C.c_int), ("route_rows", C.c_int64), ("route_row_offset", C.c_int64),
+        ("out8_amax", C.c_void_p),
     ]
 
 

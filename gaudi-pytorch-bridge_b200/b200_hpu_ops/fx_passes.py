@@ -126,9 +126,14 @@ def replace_pattern_quant_dequant_mm_addmm(gm: fx.GraphModule, device="cuda") ->
         if not _is(x_dq, "dequantize_per_tensor.default"):
             continue
         x_q, w_q = x_dq.args[0], w_dq.args[0]
-        if x_view is not None:
+        if x_view is not None and len(x_view.users) == 1:
             x_view.args = (x_q,) + tuple(x_view.args[1:])  # reshape the fp8 tensor instead
             gemm_in = x_view
+        elif x_view is not None:
+            # the reshaped activation feeds other nodes too (several projections of one
+            # activation): they keep the dequantised view, this GEMM gets a view of the fp8 tensor
+            with gm.graph.inserting_before(node):
+                gemm_in = gm.graph.call_function(x_view.target, (x_q,) + tuple(x_view.args[1:]))
         else:
             gemm_in = x_q
         s_x = rw.scale_buffer(x_dq.args[1], node)
@@ -137,7 +142,7 @@ def replace_pattern_quant_dequant_mm_addmm(gm: fx.GraphModule, device="cuda") ->
             gemm = gm.graph.call_function(hpu.fp8_gemm_v2.default,
                                           (gemm_in, False, w_q, True, None, torch.bfloat16, s_x, s_w, bias))
         node.replace_all_uses_with(gemm)
-        dead += [node, w_t, w_dq, x_dq]
+        dead += [node, w_t, w_dq, x_view if x_view is not gemm_in else None, x_dq]
         rw.replaced += 1
     if rw.replaced:
         rw.finish(dead)
@@ -151,9 +156,14 @@ def replace_pattern_quant_dequant_bmm(gm: fx.GraphModule, device="cuda") -> int:
     for node in list(gm.graph.nodes):
         if not _is(node, "bmm.default"):
             continue
-        a_dq, _ = _trace_to_dequant(node.args[0])
+        a_dq, a_path = _trace_to_dequant(node.args[0])
         b_dq, b_path = _trace_to_dequant(node.args[1])
         if a_dq is None or b_dq is None:
+            continue
+        # The rewrite feeds the fp8 tensors through the shape-only nodes between the dequantise
+        # nodes and this bmm.  That is only right when nothing else reads those nodes: with a
+        # second consumer the operand is left alone and this bmm keeps its bf16 form.
+        if any(len(n.users) != 1 for n in [a_dq, b_dq] + a_path + b_path):
             continue
         # fold a transpose of the last two dims on the B side into trans_B, drop a no-op expand.
         # b_path lists the shape-only nodes from the bmm upwards, so b_path[:i] comes AFTER node i

@@ -20,15 +20,25 @@ FP8_MAX = {torch.float8_e4m3fn: 448.0, torch.float8_e5m2: 57344.0}
 
 
 def current_scaling_cast(x: torch.Tensor, dtype: torch.dtype = torch.float8_e4m3fn, stochastic_rounding: bool = False,
-                         pow2: bool = True, margin: int = 0, scale: torch.Tensor | None = None):
+                         pow2: bool = True, margin: int = 0, scale: torch.Tensor | None = None, group=None, ops=None):
     """Returns (fp8 tensor, scale, amax); ``scale`` (one-element fp32, updated in place when given)
-    multiplies the input, its reciprocal is the ``scale_inv`` of the consumer."""
-    ops = torch.ops.b200q
-    amax = ops.amax(x)
+    multiplies the input, its reciprocal is the ``scale_inv`` of the consumer.
+
+    ``group``: the tensor is a shard of a larger one (rows of an activation split over the
+    ranks of a process group): the amax is made global with one 4-byte MAX all-reduce before
+    the scale is derived, so that every rank casts with the same scale and the shards
+    concatenate to the bytes of the unsharded cast.  Nothing else crosses the ranks.
+    ``ops``: operator namespaces ``(b200q-like, hpu-like)``; the default is this package's CUDA
+    operators (CPU ranks in tests pass stand-ins)."""
+    b200q, hpu = ops if ops is not None else (torch.ops.b200q, torch.ops.hpu)
+    amax = b200q.amax(x)
+    if group is not None:
+        import torch.distributed as dist
+        dist.all_reduce(amax, op=dist.ReduceOp.MAX, group=group)
     if scale is None:
         scale = torch.ones(1, dtype=torch.float32, device=x.device)
-    ops.scale_from_amax_(scale, amax, FP8_MAX[dtype], pow2, margin)
-    out, _ = torch.ops.hpu.cast_to_fp8_v2(x, scale, stochastic_rounding, False, dtype, [1])
+    b200q.scale_from_amax_(scale, amax, FP8_MAX[dtype], pow2, margin)
+    out, _ = hpu.cast_to_fp8_v2(x, scale, stochastic_rounding, False, dtype, [1])
     return out, scale, amax
 
 

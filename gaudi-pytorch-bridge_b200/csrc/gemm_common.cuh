@@ -46,6 +46,7 @@ struct GemmParams {
   void* route_out[8];
   int route_count;
   int64_t route_rows, route_row_offset;
+  float* out8_amax;  // fused output cast only: max |fp8 value written| (atomic max on the bit pattern), or null
 };
 
 // value in out_dtype -> fp8 byte of the fused output cast
@@ -64,6 +65,13 @@ __device__ __forceinline__ uint32_t out8_byte(const GemmParams& p, float v, floa
 }
 __device__ __forceinline__ float out8_scale_value(const GemmParams& p) {
   return p.out8_scale ? __ldg(p.out8_scale) : p.out8_scale_host;
+}
+
+// magnitude code (fp8 byte without its sign) -> the running maximum of |out|; codes order like the
+// magnitudes they stand for, and the all-ones code is NaN (e4m3) or NaN / above inf (e5m2)
+__device__ __forceinline__ void out8_amax_update(const GemmParams& p, uint32_t code) {
+  const float mag = p.out8_dtype == B200Q_E4M3 ? fp8_to_float<B200Q_E4M3>(code) : fp8_to_float<B200Q_E5M2>(code);
+  atomicMax(reinterpret_cast<unsigned int*>(p.out8_amax), __float_as_uint(mag));
 }
 
 __device__ __forceinline__ float bcast_scale(const float* dev, float host, int mode, int64_t m, int64_t n, int64_t N) {
@@ -102,7 +110,9 @@ __device__ __forceinline__ void epilogue_store_one(const GemmParams& p, int64_t 
   float v = epilogue_value(p, b, m, n, acc);
   int64_t idx = b * p.out_batch_stride + m * p.ldo + n;
   if (p.out8_dtype) {
-    static_cast<uint8_t*>(p.out)[idx] = (uint8_t)out8_byte(p, v, out8_scale_value(p));
+    const uint32_t byte = out8_byte(p, v, out8_scale_value(p));
+    static_cast<uint8_t*>(p.out)[idx] = (uint8_t)byte;
+    if (p.out8_amax) out8_amax_update(p, byte & 0x7Fu);
     return;
   }
   if (p.out_dtype == B200Q_BF16) static_cast<__nv_bfloat16*>(p.out)[idx] = __float2bfloat16_rn(v);

@@ -146,7 +146,8 @@ __device__ __forceinline__ void epi_values(const uint32_t* r, int c0, const EpiR
 
 template <int BN, bool SWAP>
 __device__ __forceinline__ void epi_chunk(const GemmParams& g, const uint32_t* r, int c0, const EpiRow& e, int64_t y0,
-                                          const float* cA, const float* cB, const float* cBias, const EpiFlags& f) {
+                                          const float* cA, const float* cB, const float* cBias, const EpiFlags& f,
+                                          uint32_t& code_max) {
   constexpr int CW = (BN % 32 == 0) ? 32 : 16;
   const int64_t x = e.x;
   const bool x_in = e.x_in;
@@ -178,10 +179,15 @@ __device__ __forceinline__ void epi_chunk(const GemmParams& g, const uint32_t* r
         if (n0 + CW <= g.N && (reinterpret_cast<uintptr_t>(o) & 15) == 0) {
 #pragma unroll
           for (int j = 0; j < CW / 4; j += 4) *reinterpret_cast<uint4*>(o + 4 * j) = make_uint4(w[j], w[j + 1], w[j + 2], w[j + 3]);
+#pragma unroll
+          for (int j = 0; j < CW / 4; ++j) code_max = __vmaxu4(code_max, w[j] & 0x7F7F7F7Fu);
         } else {
 #pragma unroll
           for (int j = 0; j < CW; ++j)
-            if (n0 + j < g.N) o[j] = (uint8_t)(w[j / 4] >> (8 * (j & 3)));
+            if (n0 + j < g.N) {
+              o[j] = (uint8_t)(w[j / 4] >> (8 * (j & 3)));
+              code_max = max(code_max, (w[j / 4] >> (8 * (j & 3))) & 0x7Fu);
+            }
         }
       } else if (g.out_dtype == B200Q_BF16) {
         __nv_bfloat16* o = static_cast<__nv_bfloat16*>(g.out) + m * g.ldo + n0;
@@ -236,8 +242,11 @@ __device__ __forceinline__ void epi_chunk(const GemmParams& g, const uint32_t* r
           float o = v[j];
           if (g.bias_mode == B200Q_BCAST_FULL) o += ld_out_typed(g.bias, g.bias_dtype, m * g.bias_ld + n);
           if (g.D) o += ld_out_typed(g.D, g.d_dtype, m * g.ldd + n);
-          if (g.out8_dtype) static_cast<uint8_t*>(g.out)[m * g.ldo + n] = (uint8_t)out8_byte(g, o, s8);
-          else if (g.out_dtype == B200Q_BF16) static_cast<__nv_bfloat16*>(g.out)[m * g.ldo + n] = __float2bfloat16_rn(o);
+          if (g.out8_dtype) {
+            const uint32_t byte = out8_byte(g, o, s8);
+            static_cast<uint8_t*>(g.out)[m * g.ldo + n] = (uint8_t)byte;
+            code_max = max(code_max, byte & 0x7Fu);
+          } else if (g.out_dtype == B200Q_BF16) static_cast<__nv_bfloat16*>(g.out)[m * g.ldo + n] = __float2bfloat16_rn(o);
           else static_cast<float*>(g.out)[m * g.ldo + n] = o;
         }
       }
@@ -250,6 +259,7 @@ template <int BN, bool SWAP>
 __device__ __forceinline__ void epi_drain(const GemmParams& g, uint32_t t_row, const EpiRow& e, int64_t y0,
                                           const float* cA, const float* cB, const float* cBias) {
   const EpiFlags f = epi_flags<SWAP>(g);
+  uint32_t code_max = 0;  // fused output cast: largest magnitude code (fp8 byte & 0x7F) this thread wrote, per byte lane
 #pragma unroll 1
   for (int c0 = 0; c0 < BN; c0 += 32) {
     uint32_t r[32];
@@ -259,7 +269,12 @@ __device__ __forceinline__ void epi_drain(const GemmParams& g, uint32_t t_row, c
       tmem_ld_32x16(t_row + c0, r);  // BN == 16
     }
     tmem_ld_wait();
-    epi_chunk<BN, SWAP>(g, r, c0, e, y0, cA, cB, cBias, f);
+    epi_chunk<BN, SWAP>(g, r, c0, e, y0, cA, cB, cBias, f, code_max);
+  }
+  if (g.out8_amax) {
+    uint32_t m = max(max(code_max & 0xFFu, (code_max >> 8) & 0xFFu), max((code_max >> 16) & 0xFFu, code_max >> 24));
+    m = __reduce_max_sync(0xFFFFFFFFu, m);
+    if ((threadIdx.x & 31) == 0 && m) out8_amax_update(g, m);
   }
 }
 

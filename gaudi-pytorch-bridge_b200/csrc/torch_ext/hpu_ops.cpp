@@ -494,7 +494,8 @@ ScaleArg to_scale_arg(const OptTensor& t) {
 at::Tensor fp8_gemm_v2_common(const at::Tensor& A, bool trans_A, const at::Tensor& B, bool trans_B, const OptTensor& D,
                               at::ScalarType out_dtype, const ScaleArg& A_scale_inv, const ScaleArg& B_scale_inv,
                               const OptTensor& bias, bool accumulate, OptShape B_scale_shape,
-                              at::ScalarType out8_dtype = at::ScalarType::Undefined, double out8_scale = 1.0) {
+                              at::ScalarType out8_dtype = at::ScalarType::Undefined, double out8_scale = 1.0,
+                              const OptTensor& out8_scale_dev = c10::nullopt, at::Tensor* out8_amax = nullptr) {
   TORCH_CHECK(is_fp8(A.scalar_type()) && is_fp8(B.scalar_type()), "fp8_gemm_v2 inputs must be float8 tensors, got ",
               A.scalar_type(), " and ", B.scalar_type());
   TORCH_CHECK(out_dtype == at::kFloat || out_dtype == at::kBFloat16,
@@ -522,6 +523,7 @@ at::Tensor fp8_gemm_v2_common(const at::Tensor& A, bool trans_A, const at::Tenso
   }
   int64_t batch = numel_of(bshape);
   const bool fused_cast = out8_dtype != at::ScalarType::Undefined;
+  at::Tensor out8_scale_keep;
   TORCH_CHECK(!fused_cast || is_fp8(out8_dtype), "fp8_gemm_cast: the output dtype must be float8_e5m2 or float8_e4m3fn");
   at::Tensor out = at::empty(out_shape, A.options().dtype(fused_cast ? out8_dtype : out_dtype));
   if (out.numel() == 0) return out;
@@ -531,6 +533,15 @@ at::Tensor fp8_gemm_v2_common(const at::Tensor& A, bool trans_A, const at::Tenso
     g.out8_dtype = to_b200q_dtype(out8_dtype);
     g.out8_scale = nullptr;
     g.out8_scale_host = (float)out8_scale;
+    if (out8_scale_dev.has_value() && out8_scale_dev->defined()) {  // a device scalar: no read-back to the host
+      TORCH_CHECK(out8_scale_dev->numel() == 1, "the output scale must have one element");
+      out8_scale_keep = out8_scale_dev->to(A.device(), at::kFloat).reshape({1}).contiguous();
+      g.out8_scale = out8_scale_keep.data_ptr<float>();
+    }
+    if (out8_amax) {
+      *out8_amax = at::zeros({}, A.options().dtype(at::kFloat));
+      g.out8_amax = out8_amax->data_ptr<float>();
+    }
   }
   int64_t Mk = M;  // M as the kernel sees it (batch may be folded in)
   bool folded = false;
@@ -648,8 +659,12 @@ at::Tensor fp8_gemm_cast(const at::Tensor& A, bool trans_A, const at::Tensor& B,
 // aten::_scaled_mm-shaped entry (the reference lowers _scaled_mm to the same fp8_gemm node,
 // hpu_ops/backend/scaled_mm_gen.cpp:66-140): out = (a @ b) * scale_a * scale_b + bias; b is usually the
 // transposed view of an [N, K] weight, which is recognised and passed as a K-major operand.
-at::Tensor scaled_mm(const at::Tensor& a, const at::Tensor& b, const at::Tensor& scale_a, const at::Tensor& scale_b,
-                     const OptTensor& bias, const OptTensor& scale_result, at::ScalarType out_dtype) {
+// Returns (out, amax): for a float8 out_dtype amax = max |out| of the values written (taken in the
+// GEMM's epilogue, scaled_mm_gen.cpp:283-320); for other output dtypes the reference computes no
+// amax and a zero is returned.
+std::tuple<at::Tensor, at::Tensor> scaled_mm(const at::Tensor& a, const at::Tensor& b, const at::Tensor& scale_a,
+                                             const at::Tensor& scale_b, const OptTensor& bias,
+                                             const OptTensor& scale_result, at::ScalarType out_dtype) {
   TORCH_CHECK(a.dim() == 2 && b.dim() == 2, "scaled_mm: 2-D operands expected");
   const bool b_is_transposed_view = b.stride(0) == 1 && b.stride(1) >= b.size(0) && b.size(0) > 1;
   at::Tensor bb = b_is_transposed_view ? b.t() : b;
@@ -661,12 +676,14 @@ at::Tensor scaled_mm(const at::Tensor& a, const at::Tensor& b, const at::Tensor&
     shape = shp;
   }
   if (is_fp8(out_dtype)) {
-    double s = scale_result.has_value() && scale_result->defined() ? scale_result->item<double>() : 1.0;
-    return fp8_gemm_v2_common(a, false, bb, b_is_transposed_view, c10::nullopt, at::kBFloat16, ScaleArg(scale_a), ScaleArg(sb),
-                              bias, false, shape, out_dtype, s);
+    at::Tensor amax;
+    at::Tensor out = fp8_gemm_v2_common(a, false, bb, b_is_transposed_view, c10::nullopt, at::kBFloat16, ScaleArg(scale_a),
+                                        ScaleArg(sb), bias, false, shape, out_dtype, 1.0, scale_result, &amax);
+    return {out, amax};
   }
-  return fp8_gemm_v2_common(a, false, bb, b_is_transposed_view, c10::nullopt, out_dtype, ScaleArg(scale_a), ScaleArg(sb), bias,
-                            false, shape);
+  at::Tensor out = fp8_gemm_v2_common(a, false, bb, b_is_transposed_view, c10::nullopt, out_dtype, ScaleArg(scale_a),
+                                      ScaleArg(sb), bias, false, shape);
+  return {out, at::zeros({}, a.options().dtype(at::kFloat))};
 }
 
 // ------------------------------------------------------------------ b200q:: extras
@@ -812,7 +829,14 @@ at::Tensor softmax_fp8_common(const at::Tensor& input, int64_t dim, const Softma
   const int64_t rank = input.dim();
   TORCH_CHECK(rank >= 1 && rank <= 8, "softmax_fp8: input rank must be 1..8");
   dim = at::maybe_wrap_dim(dim, rank, /*wrap_scalar=*/true);
-  TORCH_CHECK(dim == rank - 1, "softmax_fp8: only the last dimension is supported");
+  if (dim != rank - 1) {
+    // the row kernel reduces over the last dimension: move `dim` there, run, move it back (the
+    // reference passes any dim to its kernel, softmax_fp8_gen.cpp:65-160); fused_add's layout
+    // rules are stated for the last dimension only
+    TORCH_CHECK(!(fused_add.has_value() && fused_add->defined()), "softmax_fp8: fused_add needs dim = -1");
+    at::Tensor moved = input.transpose(dim, rank - 1).contiguous();
+    return softmax_fp8_common(moved, rank - 1, in_s, out_s, heads, fused_add).transpose(dim, rank - 1).contiguous();
+  }
   c10::cuda::CUDAGuard guard(input.device());
   at::Tensor in = input.contiguous();
   const bool fp8_out = in_s.given;
@@ -1229,7 +1253,7 @@ TORCH_LIBRARY(b200q, m) {
   m.def("dequant_kpacked(Tensor qweight, Tensor scales, Tensor? qzeros, ScalarType out_dtype) -> Tensor");
   m.def("gptq_repack(Tensor qweight, Tensor? qzeros) -> (Tensor, Tensor)");
   m.def("fp8_gemm_cast(Tensor A, bool trans_A, Tensor B, bool trans_B, Tensor? D, ScalarType mid_dtype, Tensor? A_scale_inv, Tensor? B_scale_inv, Tensor? bias, bool accumulate, int[]? B_scale_shape, float out_scale, ScalarType out_dtype) -> Tensor");
-  m.def("scaled_mm(Tensor a, Tensor b, Tensor scale_a, Tensor scale_b, Tensor? bias, Tensor? scale_result, ScalarType out_dtype) -> Tensor");
+  m.def("scaled_mm(Tensor a, Tensor b, Tensor scale_a, Tensor scale_b, Tensor? bias, Tensor? scale_result, ScalarType out_dtype) -> (Tensor, Tensor)");
   m.def("swiglu_cast_fp8(Tensor gate, Tensor up, float scale, bool is_amax) -> (Tensor, Tensor)");
   m.def("fp8_gemm_swiglu_cast(Tensor x8, Tensor w_gate_up, Tensor? x_scale_inv, Tensor? w_scale_inv, float act_scale) -> Tensor");
   m.def("amax(Tensor input) -> Tensor");

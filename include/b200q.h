@@ -228,6 +228,12 @@ typedef struct b200q_gemm_args {
   void* route_out[8];
   int route_count;
   int64_t route_rows, route_row_offset;
+  /* With a fused output cast (out8_dtype != 0): NULL, or one fp32 that receives max |out|, the
+   * largest magnitude among the fp8 values written (as aten::_scaled_mm returns it for float8
+   * outputs in the reference, hpu_ops/backend/scaled_mm_gen.cpp:283-320: abs + reduce_max over
+   * the casted result), taken in the epilogue while the values are in registers.  The caller
+   * zeroes it before the call; it is updated with atomic max, a NaN output makes it NaN. */
+  float* out8_amax;
 } b200q_gemm_args;
 
 int b200q_fp8_gemm(const b200q_gemm_args* args);

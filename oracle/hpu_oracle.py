@@ -442,8 +442,9 @@ def softmax_fp8(input, dim, input_scale=None, output_scale=None, inv_attn_heads=
         raise RuntimeError("If Input is of torch.float8_e4m3fn dtype then input scale must be given.")
     if fused_add is not None and input_scale is None:
         raise RuntimeError("FusedAdd available only for Float8 output, but input scale is not given.")
-    if dim % input.dim() != input.dim() - 1:
-        raise RuntimeError("softmax_fp8: only the last dimension is supported")
+    dim = dim % input.dim()
+    if dim != input.dim() - 1 and fused_add is not None:
+        raise RuntimeError("softmax_fp8: fused_add needs dim = -1")
     f32 = lambda v: torch.as_tensor(v, dtype=torch.float32).reshape(())  # noqa: E731
     pre = torch.ones((), dtype=torch.float32)
     if inv_attn_heads is not None:
@@ -453,7 +454,7 @@ def softmax_fp8(input, dim, input_scale=None, output_scale=None, inv_attn_heads=
     x = input.float() * pre
     if fused_add is not None:
         x = x + fused_add.float()
-    y = torch.softmax(x, -1).to(torch.bfloat16)
+    y = torch.softmax(x, dim).to(torch.bfloat16)
     if input_scale is None:
         return y
     z = (y.float() * f32(output_scale)).to(torch.bfloat16).float()

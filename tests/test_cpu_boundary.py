@@ -125,4 +125,5 @@ def test_w4a16_workspace_query_below_one_k_block(K):
     from b200_hpu_ops import abi
     for M in (1, 4, 128, 4096):
         assert abi.lib.b200q_w4a16_workspace_bytes(M, 64, K) == 0
-    assert abi.lib.b200q_w4a16_workspace_bytes(16, 8192, 8192) > 0
+    assert abi.lib.b200q_w4a16_workspace_bytes(64, 8192, 8192) > 0   # split-K path
+    assert abi.lib.b200q_w4a16_workspace_bytes(16, 8192, 8192) == 0  # few-token kernel: reduced inside its clusters

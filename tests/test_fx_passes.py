@@ -102,6 +102,50 @@ def test_untouched_when_no_pattern():
     assert sum(pm.replaced.values()) == 0 and _names(gm) == ["mm.default"]
 
 
+def test_two_projections_share_one_reshaped_activation():
+    """Two linears on one view of one dequantised activation (what CSE leaves of q/k/v
+    projections): both must become FP8 GEMMs fed by fp8 tensors, none may be left as an aten.mm
+    reading an fp8 tensor."""
+    from b200_hpu_ops.fx_passes import PatternMatchAndReplacer
+
+    g = fx.Graph()
+    x, w1, w2 = g.placeholder("x"), g.placeholder("w1"), g.placeholder("w2")
+    _, xd = _qdq(g, x, SX)
+    xin = g.call_function(aten.view.default, (xd, (6, 64)))
+    outs = []
+    for w in (w1, w2):
+        _, wd = _qdq(g, w, SW)
+        outs.append(g.call_function(aten.mm.default, (xin, g.call_function(aten.transpose.int, (wd, 0, 1)))))
+    g.output(tuple(outs))
+    gm = fx.GraphModule(torch.nn.Module(), g)
+    pm = PatternMatchAndReplacer(gm, device="meta")
+    pm.run()
+    names = _names(gm)
+    assert pm.replaced["mm_addmm"] == 2 and names.count("fp8_gemm_v2.default") == 2
+    assert not any(n.startswith(("mm.", "dequantize_per_tensor")) for n in names), names
+    a, b = gm(torch.empty(2, 3, 64, device="meta", dtype=torch.bfloat16), torch.empty(32, 64, device="meta", dtype=torch.bfloat16),
+              torch.empty(16, 64, device="meta", dtype=torch.bfloat16))
+    assert tuple(a.shape) == (6, 32) and tuple(b.shape) == (6, 16)
+
+
+def test_bmm_operand_with_a_second_consumer_is_left_alone():
+    """A dequantised operand that something else reads as well must keep its bf16 values: the bmm
+    is not rewritten rather than handing fp8 bytes to the other consumer."""
+    from b200_hpu_ops.fx_passes import replace_pattern_quant_dequant_bmm
+
+    g = fx.Graph()
+    a, b = g.placeholder("a"), g.placeholder("b")
+    _, ad = _qdq(g, a, SX)
+    _, bd = _qdq(g, b, SW)
+    bt = g.call_function(aten.transpose.int, (bd, 1, 2))
+    bmm = g.call_function(aten.bmm.default, (ad, bt))
+    other = g.call_function(aten.sum.default, (ad,))
+    g.output((bmm, other))
+    gm = fx.GraphModule(torch.nn.Module(), g)
+    assert replace_pattern_quant_dequant_bmm(gm, device="meta") == 0
+    assert "bmm.default" in _names(gm) and _names(gm).count("dequantize_per_tensor.default") == 2
+
+
 @pytest.mark.gpu
 @pytest.mark.parametrize("with_bias", [False, True])
 def test_linear_rewrite_numerics(with_bias):

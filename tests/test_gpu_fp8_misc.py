@@ -69,6 +69,24 @@ def test_softmax_fp8_reference_cases(ops, is_scale, is_inv_attn_heads, fused_add
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("dim", [0, 1, -2])
+def test_softmax_fp8_over_another_dimension(ops, dim):
+    """The reference hands any `dim` to its kernel (softmax_fp8_gen.cpp:65-160); here the row kernel
+    runs on the tensor with `dim` moved to the end."""
+    g = torch.Generator().manual_seed(9 + dim)
+    x = (torch.randn(6, 40, 24, generator=g) * 2).to(torch.bfloat16)
+    r = torch.ops.hpu.softmax_fp8(x.cuda(), dim)
+    e = O.softmax_fp8(x, dim)
+    assert r.shape == e.shape and r.dtype == torch.bfloat16
+    assert torch.allclose(r.cpu().float(), e.float(), atol=4e-3, rtol=2e-2)
+    r8 = torch.ops.hpu.softmax_fp8(x.cuda(), dim, 0.5, 240.0)
+    e8 = O.softmax_fp8(x, dim, 0.5, 240.0)
+    assert r8.dtype == torch.float8_e4m3fn
+    d = (r8.cpu().view(torch.uint8).int() - e8.view(torch.uint8).int()).abs()
+    assert int(d.max()) <= 1 and float((d > 0).float().mean()) < 0.02
+
+
+@pytest.mark.gpu
 def test_softmax_fp8_long_rows_and_errors(ops):
     g = torch.Generator().manual_seed(3)
     x = (torch.randn(37, 4099, generator=g) * 3).to(torch.bfloat16)

@@ -345,10 +345,32 @@ def test_scaled_mm_entry(ops):
     w = _rand_fp8((N, K), torch.float8_e4m3fn, g)
     sa, sw = torch.tensor(0.25), torch.tensor(2.0)
     bias = torch.randn(N, generator=g).to(torch.bfloat16)
-    r = torch.ops.b200q.scaled_mm(a.cuda(), w.cuda().t(), sa.cuda(), sw.cuda(), bias.cuda(), None, torch.bfloat16)
+    r, _ = torch.ops.b200q.scaled_mm(a.cuda(), w.cuda().t(), sa.cuda(), sw.cuda(), bias.cuda(), None, torch.bfloat16)
     e = O.fp8_gemm_v2(a, False, w, True, None, torch.bfloat16, sa, sw, bias)
     assert O.rel_frobenius(r, e) <= TOL
-    r2 = torch.ops.b200q.scaled_mm(a.cuda(), w.t().contiguous().cuda(), sa.cuda(), sw.cuda(), None, None, torch.float32)
+    r2, _ = torch.ops.b200q.scaled_mm(a.cuda(), w.t().contiguous().cuda(), sa.cuda(), sw.cuda(), None, None, torch.float32)
     assert O.rel_frobenius(r2, O.fp8_gemm_v2(a, False, w, True, None, torch.float32, sa, sw)) <= 1e-5
-    r8 = torch.ops.b200q.scaled_mm(a.cuda(), w.cuda().t(), sa.cuda(), sw.cuda(), None, torch.tensor(0.5).cuda(), torch.float8_e4m3fn)
-    assert r8.dtype == torch.float8_e4m3fn
+
+
+@pytest.mark.parametrize("out8", FP8)
+@pytest.mark.parametrize("M,N,K", [(64, 256, 128), (300, 520, 256), (1, 384, 512), (16, 1792, 1024)])
+def test_scaled_mm_fp8_output_and_amax(ops, out8, M, N, K):
+    """float8 output of the _scaled_mm-shaped entry: the bytes are cast_to_fp8_v2(bf16 GEMM result,
+    scale_result) and the second output is max |out| of the values written
+    (hpu_ops/backend/scaled_mm_gen.cpp:283-320), taken inside the GEMM's epilogue."""
+    g = torch.Generator().manual_seed(M + N)
+    a = _rand_fp8((M, K), torch.float8_e4m3fn, g)
+    w = _rand_fp8((N, K), torch.float8_e4m3fn, g)
+    sa, sw, sr = torch.tensor(0.25), torch.rand(1, N, generator=g) + 0.5, torch.tensor(0.75)
+    bias = torch.randn(N, generator=g).to(torch.bfloat16)
+    r8, amax = torch.ops.b200q.scaled_mm(a.cuda(), w.cuda().t(), sa.cuda(), sw.cuda(), bias.cuda(), sr.cuda(), out8)
+    assert r8.dtype == out8 and amax.shape == () and amax.dtype == torch.float32
+    mid = torch.ops.hpu.fp8_gemm_v2(a.cuda(), False, w.cuda(), True, None, torch.bfloat16, sa.cuda(), sw.reshape(-1).cuda(),
+                                    bias.cuda(), False, [1, N])
+    two, _ = torch.ops.hpu.cast_to_fp8_v2(mid, sr.cuda(), False, False, out8)
+    assert torch.equal(r8.view(torch.uint8), two.view(torch.uint8))
+    assert amax.item() == r8.float().abs().max().item()
+    # against the oracle: one fp8 step on the few results that sit on a tie of the bf16 intermediate
+    ref, _ = O.cast_to_fp8_v2(O.fp8_gemm_v2(a, False, w, True, None, torch.bfloat16, sa, sw.reshape(-1), bias, False, [1, N]),
+                              sr, False, False, out8)
+    assert O.rel_frobenius(r8.float(), ref.float()) <= 4e-2

@@ -103,6 +103,17 @@ def _worker(rank, world, port, q):
                 y = mlp(x.to(dev)).clone()
             torch.cuda.synchronize()
             errs.append((comm, float(O.rel_frobenius(y, ref)), same))
+        # sharded current-scaling cast: rows split over the ranks, one MAX all-reduce of the amax,
+        # and the shards must be the bytes of the unsharded cast
+        from b200_hpu_ops import scaling
+        xr = (x.float() * 3).to(torch.bfloat16).to(dev)
+        rows = T // world
+        o_sh, sc_sh, _ = scaling.current_scaling_cast(xr[rank * rows:(rank + 1) * rows].contiguous(), group=dist.group.WORLD)
+        o_full, sc_full, _ = scaling.current_scaling_cast(xr)
+        torch.cuda.synchronize()
+        cast_ok = bool(torch.equal(o_sh.view(torch.uint8), o_full[rank * rows:(rank + 1) * rows].view(torch.uint8))
+                       and torch.equal(sc_sh, sc_full))
+        errs.append(("sharded_cast", 0.0 if cast_ok else 1.0, cast_ok))
         q.put((rank, errs, b200_hpu_ops.device_status()))
     except Exception as e:  # report instead of leaving the parent waiting on the queue
         q.put((rank, repr(e), -1))

@@ -112,3 +112,70 @@ def test_shard_bounds_and_errors():
     with pytest.raises(ValueError):
         m.shard_bounds(10, 4, 0)
     assert m.mlp_flops(8192, 8192, 28672) == pytest.approx(11.545e12, rel=1e-3)
+
+
+# ---------------------------------------------------------------------------- sharded current-scaling cast
+class _OracleB200Q:
+    """Stand-in for torch.ops.b200q on CPU ranks (test only)."""
+
+    @staticmethod
+    def amax(x):
+        return x.detach().abs().max().float().reshape(())
+
+    @staticmethod
+    def scale_from_amax_(scale, amax, fp8_max, pow2=True, margin=0):
+        from oracle import hpu_oracle as O
+        scale.copy_(O.scale_from_amax(amax, scale, fp8_max, pow2, margin).reshape(scale.shape))
+        return scale
+
+
+def _scaling_worker(rank, world, port, q):
+    sys.path.insert(0, ROOT)
+    os.environ["MASTER_ADDR"] = "127.0.0.1"
+    os.environ["MASTER_PORT"] = str(port)
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        import importlib.util
+        spec = importlib.util.spec_from_file_location(
+            "scaling", os.path.join(ROOT, "gaudi-pytorch-bridge_b200", "b200_hpu_ops", "scaling.py"))
+        scaling = importlib.util.module_from_spec(spec)
+        sys.modules["scaling"] = scaling
+        spec.loader.exec_module(scaling)
+        from oracle import hpu_oracle as O
+        g = torch.Generator().manual_seed(3)
+        x = (torch.randn(64, 96, generator=g) * 3).to(torch.bfloat16)
+        x[37, 5] = 41.0  # the global amax sits in one rank's rows only
+        rows = 64 // world
+        mine = x[rank * rows:(rank + 1) * rows].contiguous()
+        out, scale, amax = scaling.current_scaling_cast(mine, torch.float8_e4m3fn, group=dist.group.WORLD,
+                                                        ops=(_OracleB200Q, _OracleOps))
+        # the unsharded cast on one device
+        full_scale = O.scale_from_amax(x.abs().max().float(), torch.ones(()), 448.0, True)
+        full, _ = O.cast_to_fp8_v2(x, full_scale.reshape(1), False, False, torch.float8_e4m3fn, [1])
+        same = torch.equal(out.view(torch.uint8), full[rank * rows:(rank + 1) * rows].view(torch.uint8))
+        q.put((rank, float(amax), float(scale), float(full_scale), same))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_sharded_current_scaling_uses_the_global_amax():
+    """Rows split over 2 gloo ranks: one 4-byte MAX all-reduce makes the amax global, both ranks
+    derive the same scale, and the shards are the bytes of the unsharded cast."""
+    world = 2
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_scaling_worker, args=(r, world, port, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    try:
+        res = [q.get(timeout=180) for _ in range(world)]
+        for p in procs:
+            p.join(timeout=60)
+    finally:
+        for p in procs:
+            if p.is_alive():
+                p.terminate()
+    for rank, amax, scale, full_scale, same in res:
+        assert amax == 41.0 and scale == full_scale == 8.0, (rank, amax, scale, full_scale)
+        assert same, rank
