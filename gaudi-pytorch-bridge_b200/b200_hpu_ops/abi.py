@@ -16,7 +16,7 @@ CAST_MUL_IN_FP32 = 1
 
 EXPORTS = [
     "b200q_strerror", "b200q_last_cuda_error", "b200q_device_status", "b200q_selftest_wait_timeout", "b200q_launch_count",
-    "b200q_cast_to_fp8", "b200q_cast_to_fp8_hybrid", "b200q_cast_from_fp8", "b200q_dequant_int4", "b200q_gptq_repack", "b200q_fp8_gemm", "b200q_tp_reduce_bcast",
+    "b200q_cast_to_fp8", "b200q_cast_to_fp8_hybrid", "b200q_cast_from_fp8", "b200q_dequant_int4", "b200q_gptq_repack", "b200q_fp8_gemm", "b200q_tp_reduce_bcast", "b200q_fp8_sdpa_fwd",
     "b200q_w4a16_gemm", "b200q_w4a16_workspace_bytes", "b200q_w4a16_gemm_noalloc", "b200q_swiglu_cast_fp8",
     "b200q_amax", "b200q_scale_from_amax", "b200q_amax_history_update",
     "b200q_softmax_fp8", "b200q_sum_fp8_workspace_bytes", "b200q_sum_fp8", "b200q_in_place_interleave", "b200q_im2col_fp8",
@@ -46,6 +46,22 @@ class GemmArgs(C.Structure):
     ]
 
 
+class SdpaArgs(C.Structure):
+    _fields_ = [
+        ("q", C.c_void_p), ("k", C.c_void_p), ("v", C.c_void_p), ("out", C.c_void_p), ("out_dtype", C.c_int),
+        ("BH", C.c_int64), ("L", C.c_int64), ("S", C.c_int64), ("dqk", C.c_int), ("dv", C.c_int), ("kv_rep", C.c_int),
+        ("mask", C.c_void_p), ("mask_kind", C.c_int), ("mask_sb", C.c_int64), ("mask_sl", C.c_int64), ("causal", C.c_int),
+        ("softmax_scale", C.c_float),
+        ("d_scale_q", C.c_void_p), ("d_scale_k", C.c_void_p), ("d_scale_v", C.c_void_p), ("q_scale_s", C.c_void_p),
+        ("q_scale_o", C.c_void_p), ("d_scale_s", C.c_void_p),
+        ("d_scale_q_host", C.c_float), ("d_scale_k_host", C.c_float), ("d_scale_v_host", C.c_float),
+        ("q_scale_s_host", C.c_float), ("q_scale_o_host", C.c_float), ("d_scale_s_host", C.c_float),
+        ("d_scale_s_given", C.c_int),
+        ("m_out", C.c_void_p), ("linv_out", C.c_void_p), ("amax_s", C.c_void_p), ("amax_o", C.c_void_p),
+        ("force_plain", C.c_int), ("stream", C.c_void_p),
+    ]
+
+
 def _bind():
     lib = C.CDLL(_LIB_PATH, mode=C.RTLD_GLOBAL)
     lib.b200q_strerror.restype = C.c_char_p
@@ -65,6 +81,7 @@ def _bind():
     lib.b200q_dequant_int4.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_int, C.c_int, C.c_int, C.c_void_p,
                                        C.c_int64, C.c_int64, C.c_int64, C.c_int, C.c_void_p]
     lib.b200q_fp8_gemm.argtypes = [C.POINTER(GemmArgs)]
+    lib.b200q_fp8_sdpa_fwd.argtypes = [C.POINTER(SdpaArgs)]
     lib.b200q_tp_reduce_bcast.argtypes = [C.c_void_p, C.POINTER(C.c_void_p), C.c_int, C.c_int, C.c_int64, C.c_int64, C.c_void_p]
     lib.b200q_gptq_repack.argtypes = [C.c_void_p, C.c_void_p, C.c_int64, C.c_int64, C.c_void_p, C.c_void_p, C.c_int64,
                                       C.c_void_p]

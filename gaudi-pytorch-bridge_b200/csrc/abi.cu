@@ -77,6 +77,7 @@ int w4a16_gemm_impl(const void*, int64_t, const int32_t*, const void*, const int
                     int64_t, int64_t, void*, int, int64_t, void*, size_t, cudaStream_t);
 size_t w4a16_workspace_bytes_impl(int64_t, int64_t, int64_t);
 int tp_reduce_bcast_impl(const void*, void* const*, int, int, int64_t, int64_t, cudaStream_t);
+int sdpa_fp8_fwd_impl(const b200q_sdpa_args&, cudaStream_t);
 int gptq_repack_impl(const int32_t*, int32_t*, int64_t, int64_t, const int32_t*, int32_t*, int64_t, cudaStream_t);
 int w4a16_gemm_noalloc_impl(const void*, int64_t, const int32_t*, const void*, const int32_t*, int, int, int64_t, int64_t,
                             int64_t, int64_t, void*, int, int64_t, cudaStream_t);
@@ -328,6 +329,16 @@ int b200q_gptq_repack(const int32_t* qweight, int32_t* qweight_out, int64_t K, i
   if (K * N > 0 && (!qweight || !qweight_out)) return B200Q_ERR_BAD_ARGUMENT;
   if (qzeros && zeros_words > 0 && !qzeros_out) return B200Q_ERR_BAD_ARGUMENT;
   return gptq_repack_impl(qweight, qweight_out, K, N, qzeros, qzeros_out, zeros_words, static_cast<cudaStream_t>(stream));
+}
+
+int b200q_fp8_sdpa_fwd(const b200q_sdpa_args* a) {
+  if (!a) return B200Q_ERR_BAD_ARGUMENT;
+  if (a->BH < 0 || a->L < 0 || a->S < 1 || a->kv_rep < 1 || a->dqk < 1 || a->dv < 1) return B200Q_ERR_BAD_ARGUMENT;
+  if (a->BH * a->L == 0) return B200Q_OK;
+  if (!a->q || !a->k || !a->v || !a->out || a->BH % a->kv_rep) return B200Q_ERR_BAD_ARGUMENT;
+  if (a->out_dtype != B200Q_BF16 && a->out_dtype != B200Q_E4M3) return B200Q_ERR_BAD_ARGUMENT;
+  if (a->mask && (a->mask_kind < 1 || a->mask_kind > 3)) return B200Q_ERR_BAD_ARGUMENT;
+  return sdpa_fp8_fwd_impl(*a, static_cast<cudaStream_t>(a->stream));
 }
 
 int b200q_tp_reduce_bcast(const void* stage, void* const* out_ptrs_host, int tp, int me, int64_t rows, int64_t d,

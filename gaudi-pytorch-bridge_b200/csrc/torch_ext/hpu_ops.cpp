@@ -686,6 +686,178 @@ std::tuple<at::Tensor, at::Tensor> scaled_mm(const at::Tensor& a, const at::Tens
   return {out, at::zeros({}, a.options().dtype(at::kFloat))};
 }
 
+// ------------------------------------------------------------------ fp8_sdpa_recomp_fwd
+// habana_kernels/kernels_register.cpp:2525,2533; node hpu_ops/backend/sdpa_gen.cpp:820-1000; shapes
+// sdpa_gen.cpp:600-702; meta python_packages/habana_frameworks/torch/dynamo/_custom_op_meta_registrations.py:636-657.
+// Forward without dropout.  q / k / v: e4m3 [..., L, D]; the batch dimensions of k / v equal those of
+// q or broadcast along the LAST of them (multi-query [B, 1, S, D]; grouped-query as the reference's
+// caller reshapes it, q [B, G, R, L, D] against k / v [B, G, 1, S, D]).
+struct SdpaScale {
+  at::Tensor dev;  // one-element fp32 on the device, or undefined
+  float host = 1.f;
+  bool given = false;
+};
+static SdpaScale sdpa_scale(const OptTensor& t, const at::Device& d) {
+  SdpaScale s;
+  if (t.has_value() && t->defined() && t->numel() > 0) {
+    s.dev = t->to(d, at::kFloat).reshape(-1).slice(0, 0, 1).contiguous();
+    s.given = true;
+  }
+  return s;
+}
+static SdpaScale sdpa_scale(double v) {
+  SdpaScale s;
+  if (v != 0.) {  // the reference treats a scalar 0 as "not given" (sdpa_gen.cpp:893-905)
+    s.host = (float)v;
+    s.given = true;
+  }
+  return s;
+}
+
+std::tuple<at::Tensor, at::Tensor, at::Tensor, at::Tensor, at::Tensor, at::Tensor> fp8_sdpa_recomp_fwd_common(
+    const at::Tensor& q, const at::Tensor& k, const at::Tensor& v, const OptTensor& attention_mask, double p, double scale,
+    bool is_causal, bool requires_backward, c10::string_view softmax_mode, const SdpaScale& d_q, const SdpaScale& d_k,
+    const SdpaScale& d_v, const SdpaScale& q_s, const SdpaScale& q_o, const SdpaScale& d_s, bool is_amax_s, bool is_amax_o,
+    const OptTensor& valid_seq_len, c10::string_view seq_padding_type) {
+  (void)softmax_mode; (void)seq_padding_type;
+  TORCH_CHECK(q.scalar_type() == at::kFloat8_e4m3fn && k.scalar_type() == at::kFloat8_e4m3fn && v.scalar_type() == at::kFloat8_e4m3fn,
+              "fp8_sdpa_recomp_fwd: q, k and v must be float8_e4m3fn tensors");
+  TORCH_CHECK(p == 0.0, "fp8_sdpa_recomp_fwd: dropout is not supported");
+  TORCH_CHECK(!(valid_seq_len.has_value() && valid_seq_len->defined()), "fp8_sdpa_recomp_fwd: valid_seq_len is not supported");
+  const int64_t rank = q.dim();
+  TORCH_CHECK(rank >= 3 && k.dim() == rank && v.dim() == rank, "fp8_sdpa_recomp_fwd: q, k, v must have the same rank >= 3");
+  const int64_t L = q.size(-2), D = q.size(-1), S = k.size(-2), Dv = v.size(-1);
+  TORCH_CHECK(k.size(-1) == D && v.size(-2) == S, "fp8_sdpa_recomp_fwd: k / v do not match q");
+  TORCH_CHECK(S >= 1, "fp8_sdpa_recomp_fwd: no keys");
+  c10::cuda::CUDAGuard guard(q.device());
+  // batch layout: BH query heads, each reading key/value head bh / kv_rep
+  int64_t BH = 1, BHkv = 1;
+  for (int64_t d = 0; d < rank - 2; ++d) { BH *= q.size(d); BHkv *= k.size(d); }
+  at::Tensor kc = k, vc = v;
+  bool pattern_ok = BHkv > 0 && BH % BHkv == 0;
+  for (int64_t d = 0; d < rank - 2 && pattern_ok; ++d) {
+    const bool same = k.size(d) == q.size(d) && v.size(d) == q.size(d);
+    const bool last_bcast = d == rank - 3 && k.size(d) == 1 && v.size(d) == 1;
+    pattern_ok = same || last_bcast;
+  }
+  if (!pattern_ok) {  // any other broadcast: materialise it
+    std::vector<int64_t> ks(q.sizes().begin(), q.sizes().end() - 2), vs = ks;
+    ks.push_back(S); ks.push_back(D); vs.push_back(S); vs.push_back(Dv);
+    kc = k.expand(ks); vc = v.expand(vs);
+    BHkv = BH;
+  }
+  const int kv_rep = (int)(BH / BHkv);
+  at::Tensor qc = q.contiguous();
+  kc = kc.contiguous(); vc = vc.contiguous();
+  std::vector<int64_t> out_shape(q.sizes().begin(), q.sizes().end() - 1);
+  out_shape.push_back(Dv);
+  std::vector<int64_t> stat_shape(q.sizes().begin(), q.sizes().end() - 1);
+  stat_shape.push_back(1);
+  const bool fp8_out = q_o.given;
+  at::Tensor out = at::empty(out_shape, q.options().dtype(fp8_out ? at::kFloat8_e4m3fn : at::kBFloat16));
+  at::Tensor m = requires_backward ? at::empty(stat_shape, q.options().dtype(at::kBFloat16)) : at::zeros({1}, q.options().dtype(at::kBFloat16));
+  at::Tensor linv = requires_backward ? at::empty(stat_shape, q.options().dtype(at::kBFloat16)) : at::zeros({1}, q.options().dtype(at::kBFloat16));
+  at::Tensor seed = at::zeros({1}, q.options().dtype(at::kInt));
+  at::Tensor amax_s = at::zeros({1}, q.options().dtype(at::kFloat)), amax_o = at::zeros({1}, q.options().dtype(at::kFloat));
+  if (out.numel() == 0) return {out, m, linv, seed, amax_s, amax_o};
+
+  b200q_sdpa_args a{};
+  a.q = qc.data_ptr(); a.k = kc.data_ptr(); a.v = vc.data_ptr(); a.out = out.data_ptr();
+  a.out_dtype = fp8_out ? B200Q_E4M3 : B200Q_BF16;
+  a.BH = BH; a.L = L; a.S = S; a.dqk = (int)D; a.dv = (int)Dv; a.kv_rep = kv_rep;
+  a.causal = is_causal ? 1 : 0;
+  a.softmax_scale = (float)scale;
+  at::Tensor mask_keep;
+  if (attention_mask.has_value() && attention_mask->defined()) {
+    // broadcast the mask against [batch dims..., L, S]; batch-invariant / row-invariant masks keep stride 0
+    at::Tensor mk = attention_mask->to(q.device());
+    if (mk.scalar_type() == at::kBool) mk = mk.to(at::kByte);
+    else if (mk.scalar_type() != at::kBFloat16 && mk.scalar_type() != at::kFloat) mk = mk.to(at::kFloat);
+    TORCH_CHECK(mk.dim() <= rank && mk.size(-1) == S, "fp8_sdpa_recomp_fwd: the attention mask does not broadcast against [.., L, S]");
+    while (mk.dim() < rank) mk = mk.unsqueeze(0);
+    bool batch_invariant = true;
+    for (int64_t d = 0; d < rank - 2; ++d) {
+      TORCH_CHECK(mk.size(d) == 1 || mk.size(d) == q.size(d), "fp8_sdpa_recomp_fwd: the attention mask does not broadcast");
+      batch_invariant = batch_invariant && mk.size(d) == 1;
+    }
+    TORCH_CHECK(mk.size(-2) == 1 || mk.size(-2) == L, "fp8_sdpa_recomp_fwd: the attention mask does not broadcast");
+    const bool row_invariant = mk.size(-2) == 1;
+    if (!batch_invariant) {
+      std::vector<int64_t> full(q.sizes().begin(), q.sizes().end() - 2);
+      full.push_back(mk.size(-2)); full.push_back(S);
+      mk = mk.expand(full);
+    }
+    mask_keep = mk.contiguous();
+    a.mask = mask_keep.data_ptr();
+    a.mask_kind = mask_keep.scalar_type() == at::kBFloat16 ? 1 : mask_keep.scalar_type() == at::kFloat ? 2 : 3;
+    a.mask_sl = row_invariant ? 0 : S;
+    a.mask_sb = batch_invariant ? 0 : (row_invariant ? S : L * S);
+  }
+  const SdpaScale* sc[6] = {&d_q, &d_k, &d_v, &q_s, &q_o, &d_s};
+  const float** devs[6] = {&a.d_scale_q, &a.d_scale_k, &a.d_scale_v, &a.q_scale_s, &a.q_scale_o, &a.d_scale_s};
+  float* hosts[6] = {&a.d_scale_q_host, &a.d_scale_k_host, &a.d_scale_v_host, &a.q_scale_s_host, &a.q_scale_o_host, &a.d_scale_s_host};
+  for (int i = 0; i < 6; ++i) {
+    *hosts[i] = sc[i]->given ? sc[i]->host : 1.f;
+    *devs[i] = sc[i]->dev.defined() ? sc[i]->dev.data_ptr<float>() : nullptr;
+  }
+  a.d_scale_s_given = d_s.given ? 1 : 0;
+  if (requires_backward) { a.m_out = m.data_ptr(); a.linv_out = linv.data_ptr(); }
+  if (is_amax_s) a.amax_s = amax_s.data_ptr<float>();
+  if (is_amax_o) a.amax_o = amax_o.data_ptr<float>();
+  static const bool force_plain = std::getenv("B200Q_SDPA_PLAIN") != nullptr;  // comparison switch
+  a.force_plain = force_plain ? 1 : 0;
+  a.stream = current_stream();
+  check_status(b200q_fp8_sdpa_fwd(&a), "fp8_sdpa_recomp_fwd");
+  return {out, m, linv, seed, amax_s, amax_o};
+}
+
+std::tuple<at::Tensor, at::Tensor, at::Tensor, at::Tensor, at::Tensor, at::Tensor> fp8_sdpa_recomp_fwd(
+    const at::Tensor& q, const at::Tensor& k, const at::Tensor& v, const OptTensor& attention_mask, double p, double scale,
+    bool is_causal, bool requires_backward, c10::string_view softmax_mode, const OptTensor& d_scale_q, const OptTensor& d_scale_k,
+    const OptTensor& d_scale_v, const OptTensor& q_scale_s, const OptTensor& q_scale_o, const OptTensor& d_scale_s, bool is_amax_s,
+    bool is_amax_o, const OptTensor& valid_seq_len, c10::string_view seq_padding_type) {
+  const auto dev = q.device();
+  return fp8_sdpa_recomp_fwd_common(q, k, v, attention_mask, p, scale, is_causal, requires_backward, softmax_mode,
+                                    sdpa_scale(d_scale_q, dev), sdpa_scale(d_scale_k, dev), sdpa_scale(d_scale_v, dev),
+                                    sdpa_scale(q_scale_s, dev), sdpa_scale(q_scale_o, dev), sdpa_scale(d_scale_s, dev), is_amax_s,
+                                    is_amax_o, valid_seq_len, seq_padding_type);
+}
+std::tuple<at::Tensor, at::Tensor, at::Tensor, at::Tensor, at::Tensor, at::Tensor> fp8_sdpa_recomp_fwd_scalar(
+    const at::Tensor& q, const at::Tensor& k, const at::Tensor& v, const OptTensor& attention_mask, double p, double scale,
+    bool is_causal, bool requires_backward, c10::string_view softmax_mode, double d_scale_q, double d_scale_k, double d_scale_v,
+    double q_scale_s, double q_scale_o, double d_scale_s, bool is_amax_s, bool is_amax_o, const OptTensor& valid_seq_len,
+    c10::string_view seq_padding_type) {
+  return fp8_sdpa_recomp_fwd_common(q, k, v, attention_mask, p, scale, is_causal, requires_backward, softmax_mode,
+                                    sdpa_scale(d_scale_q), sdpa_scale(d_scale_k), sdpa_scale(d_scale_v), sdpa_scale(q_scale_s),
+                                    sdpa_scale(q_scale_o), sdpa_scale(d_scale_s), is_amax_s, is_amax_o, valid_seq_len,
+                                    seq_padding_type);
+}
+
+// Meta: shapes and dtypes of the six outputs (_custom_op_meta_registrations.py:636-657)
+static std::tuple<at::Tensor, at::Tensor, at::Tensor, at::Tensor, at::Tensor, at::Tensor> meta_sdpa_outputs(
+    const at::Tensor& q, const at::Tensor& v, bool fp8_out, bool requires_backward) {
+  std::vector<int64_t> out_shape(q.sizes().begin(), q.sizes().end() - 1);
+  out_shape.push_back(v.size(-1));
+  std::vector<int64_t> stat_shape(q.sizes().begin(), q.sizes().end() - 1);
+  stat_shape.push_back(1);
+  if (!requires_backward) stat_shape = {1};
+  auto o = q.options();
+  return {at::empty(out_shape, o.dtype(fp8_out ? at::kFloat8_e4m3fn : at::kBFloat16)), at::empty(stat_shape, o.dtype(at::kBFloat16)),
+          at::empty(stat_shape, o.dtype(at::kBFloat16)), at::empty({1}, o.dtype(at::kInt)), at::empty({1}, o.dtype(at::kFloat)),
+          at::empty({1}, o.dtype(at::kFloat))};
+}
+std::tuple<at::Tensor, at::Tensor, at::Tensor, at::Tensor, at::Tensor, at::Tensor> meta_fp8_sdpa_recomp_fwd(
+    const at::Tensor& q, const at::Tensor&, const at::Tensor& v, const OptTensor&, double, double, bool, bool requires_backward,
+    c10::string_view, const OptTensor&, const OptTensor&, const OptTensor&, const OptTensor&, const OptTensor& q_scale_o,
+    const OptTensor&, bool, bool, const OptTensor&, c10::string_view) {
+  return meta_sdpa_outputs(q, v, q_scale_o.has_value() && q_scale_o->defined() && q_scale_o->numel() > 0, requires_backward);
+}
+std::tuple<at::Tensor, at::Tensor, at::Tensor, at::Tensor, at::Tensor, at::Tensor> meta_fp8_sdpa_recomp_fwd_scalar(
+    const at::Tensor& q, const at::Tensor&, const at::Tensor& v, const OptTensor&, double, double, bool, bool requires_backward,
+    c10::string_view, double, double, double, double, double q_scale_o, double, bool, bool, const OptTensor&, c10::string_view) {
+  return meta_sdpa_outputs(q, v, q_scale_o != 0., requires_backward);
+}
+
 // ------------------------------------------------------------------ b200q:: extras
 at::Tensor w4a16_gemm(const at::Tensor& x, const at::Tensor& qweight, const at::Tensor& scales, const OptTensor& qzeros,
                       int64_t group_size, bool k_packed, at::ScalarType out_dtype) {
@@ -1159,6 +1331,8 @@ TORCH_LIBRARY(hpu, m) {
   m.def("softmax_fp8.Scalar(Tensor input, int dim, float input_scale, float output_scale, float inv_attn_heads, Tensor? fused_add=None) -> Tensor");
   m.def("sum_fp8(Tensor self, int[1]? dim=None, bool keepdim=False, ScalarType? out_dtype=None) -> Tensor");
   m.def("in_place_interleave_(Tensor(a!) self) -> (Tensor(a!))");
+  m.def("fp8_sdpa_recomp_fwd(Tensor q, Tensor k, Tensor v, Tensor? attention_mask, float p, float scale, bool is_causal, bool requires_backward, str softmax_mode, Tensor? d_scale_q, Tensor? d_scale_k, Tensor? d_scale_v, Tensor? q_scale_s, Tensor? q_scale_o, Tensor? d_scale_s, bool is_amax_s, bool is_amax_0, Tensor? valid_seq_len, str seq_padding_type ) -> (Tensor, Tensor, Tensor, Tensor, Tensor, Tensor)");
+  m.def("fp8_sdpa_recomp_fwd.scalar(Tensor q, Tensor k, Tensor v, Tensor? attention_mask, float p, float scale, bool is_causal, bool requires_backward, str softmax_mode, float d_scale_q, float d_scale_k, float d_scale_v, float q_scale_s, float q_scale_o, float d_scale_s, bool is_amax_s, bool is_amax_0, Tensor? valid_seq_len, str seq_padding_type ) -> (Tensor, Tensor, Tensor, Tensor, Tensor, Tensor)");
   m.def("fp8_gemm_v2.scalar_list(Tensor A, bool trans_A, Tensor B, bool trans_B, Tensor? D, ScalarType out_dtype, float[] A_scale_inv, float[] B_scale_inv, Tensor? bias=None, bool accumulate=False, int[]? B_scale_shape=None) -> Tensor");
 }
 
@@ -1180,6 +1354,8 @@ TORCH_LIBRARY_IMPL(hpu, CUDA, m) {
   m.impl("softmax_fp8.Scalar", softmax_fp8_scalar);
   m.impl("sum_fp8", sum_fp8);
   m.impl("in_place_interleave_", in_place_interleave_);
+  m.impl("fp8_sdpa_recomp_fwd", fp8_sdpa_recomp_fwd);
+  m.impl("fp8_sdpa_recomp_fwd.scalar", fp8_sdpa_recomp_fwd_scalar);
   m.impl("fp8_gemm", fp8_gemm);
   m.impl("fp8_gemm_v2", fp8_gemm_v2);
   m.impl("fp8_gemm_v2.scalar", fp8_gemm_v2_scalar);
@@ -1234,6 +1410,8 @@ TORCH_LIBRARY_IMPL(hpu, Meta, m) {
   m.impl("softmax_fp8.Scalar", meta_softmax_fp8_scalar);
   m.impl("sum_fp8", meta_sum_fp8);
   m.impl("in_place_interleave_", meta_in_place_interleave_);
+  m.impl("fp8_sdpa_recomp_fwd", meta_fp8_sdpa_recomp_fwd);
+  m.impl("fp8_sdpa_recomp_fwd.scalar", meta_fp8_sdpa_recomp_fwd_scalar);
   m.impl("cast_to_fp8_hybrid", meta_cast_to_fp8_hybrid);
   m.impl("cast_to_fp8_v2", meta_cast_to_fp8_v2);
   m.impl("cast_to_fp8_v2.scalar", meta_cast_to_fp8_v2_scalar);

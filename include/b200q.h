@@ -239,6 +239,50 @@ typedef struct b200q_gemm_args {
 int b200q_fp8_gemm(const b200q_gemm_args* args);
 
 /*
+ * fp8_sdpa_fwd: scaled-dot-product attention forward on e4m3 tensors,
+ *   out = softmax(q k^T * score_scale + mask) v,  probabilities re-quantised to e4m3 in between.
+ * Replaces the node `sdpa_recomp_fwd_*` emitted for hpu::fp8_sdpa_recomp_fwd,
+ * hpu_ops/backend/sdpa_gen.cpp:820-1000 (output shapes :600-702, fp8 scale inputs :875-882), forward
+ * only, no dropout, no valid_seq_len.  Quantisation points (the reference's are inside its closed
+ * kernel library; its test bounds the result against unquantised attention with atol 0.4):
+ *   S = (q k^T) * score_scale [+ mask] [causal: key <= query];  m = rowmax S;  Pt = exp(S - m);
+ *   l = rowsum Pt (fp32);  P8 = e4m3(min(Pt * q_scale_s, 448));  O = (P8 v) * o_scale / l;
+ *   out = bf16(O) or e4m3(O * q_scale_o).
+ * q [BH][L][dqk], k [BH / kv_rep][S][dqk], v [BH / kv_rep][S][dv], out [BH][L][dv] contiguous;
+ * query head bh reads key/value head bh / kv_rep (grouped- and multi-query attention).
+ * score_scale = d_scale_q * d_scale_k * softmax_scale;  o_scale = d_scale_s * d_scale_v, with
+ * d_scale_s = 1 / q_scale_s unless d_scale_s_given.  Each of the six scales is a device scalar
+ * (pointer set) or the *_host value (absent scales: pass 1).
+ * mask: NULL, or values addressed as mask[bh * mask_sb + row * mask_sl + key] (strides in
+ * elements, 0 = broadcast); mask_kind 1 = bf16 additive, 2 = fp32 additive, 3 = bytes, non-zero =
+ * keep.  m_out / linv_out: NULL or bf16 [BH][L] (row maximum of S and 1 / l).  amax_s / amax_o:
+ * NULL or one fp32 each, zeroed by the caller: largest probability (max over rows of 1 / l) and
+ * max |O|.  dqk = dv = 128 with 16-byte aligned tensors runs the tcgen05 kernel; other head
+ * dimensions (<= 256), or force_plain = 1, a plain CUDA kernel with the same arithmetic.
+ */
+typedef struct b200q_sdpa_args {
+  const void *q, *k, *v;
+  void* out;
+  int out_dtype; /* BF16 or E4M3 */
+  int64_t BH, L, S;
+  int dqk, dv, kv_rep;
+  const void* mask;
+  int mask_kind;
+  int64_t mask_sb, mask_sl;
+  int causal;
+  float softmax_scale;
+  const float *d_scale_q, *d_scale_k, *d_scale_v, *q_scale_s, *q_scale_o, *d_scale_s;
+  float d_scale_q_host, d_scale_k_host, d_scale_v_host, q_scale_s_host, q_scale_o_host, d_scale_s_host;
+  int d_scale_s_given;
+  void *m_out, *linv_out;
+  float *amax_s, *amax_o;
+  int force_plain;
+  void* stream;
+} b200q_sdpa_args;
+
+int b200q_fp8_sdpa_fwd(const b200q_sdpa_args* args);
+
+/*
  * tp_reduce_bcast: the reduction half of a SUM all-reduce whose scatter half was done by the
  * producer (routed GEMM output above).  Stands in for ProcessGroupHcclBase::allreduce,
  * python_packages/habana_frameworks/torch/distributed/hccl/process_group_hccl_base.cpp:412-497,

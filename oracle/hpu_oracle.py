@@ -551,3 +551,68 @@ def rel_frobenius(a: torch.Tensor, b: torch.Tensor) -> float:
     a = a.detach().cpu().double()
     b = b.detach().cpu().double()
     return float((a - b).norm() / max(b.norm(), 1e-30))
+
+
+# ---------------------------------------------------------------------------- FP8 SDPA (forward)
+SDPA_MASKED = -1.0e30  # what a masked-out score is set to (finite: exp gives exactly 0)
+
+
+def fp8_sdpa_recomp_fwd(q, k, v, attention_mask=None, p=0.0, scale=None, is_causal=False, requires_backward=False,
+                        softmax_mode="None", d_scale_q=None, d_scale_k=None, d_scale_v=None, q_scale_s=None,
+                        q_scale_o=None, d_scale_s=None, is_amax_s=False, is_amax_o=False, valid_seq_len=None,
+                        seq_padding_type="None"):
+    """hpu::fp8_sdpa_recomp_fwd (habana_kernels/kernels_register.cpp:2525; node built in
+    hpu_ops/backend/sdpa_gen.cpp:820-1000; Python caller
+    python_packages/habana_frameworks/torch/hpex/kernels/Fp8FusedSDPA.py:70-160), forward only, no
+    dropout.  The reference's arithmetic lives in its closed kernel library; what its test checks
+    the result against is plain attention on the unquantised tensors
+    (tests/pytest_working/any_mode/FusedSDPA/test_hpu_sdpa_fp8.py:292-320, atol 0.4 for fp8 runs).
+    This restatement fixes the quantisation points the way the B200 kernel has them:
+
+        S  = (q8 @ k8^T) * (d_scale_q * d_scale_k * scale)  [+ mask]  [causal: key <= query]
+        m  = rowmax(S);  Pt = exp(S - m);  l = rowsum(Pt)                       (fp32)
+        P8 = e4m3(Pt * q_scale_s)                       (q_scale_s absent = 1: Pt is in [0, 1])
+        O  = (P8 @ v8) * (d_scale_s * d_scale_v) / l    (d_scale_s absent = 1 / q_scale_s)
+        out = bf16(O), or e4m3(O * q_scale_o) when q_scale_o is given
+        amax_s = max softmax probability = max over rows of 1 / l;  amax_o = max |O|
+
+    Returns (out, m, linv, seed, amax_s, amax_o) with the reference's shapes
+    (sdpa_gen.cpp:600-702): m / linv are [..., L, 1] bf16 when requires_backward, else [1]."""
+    if p != 0.0:
+        raise RuntimeError("fp8_sdpa_recomp_fwd: dropout is not supported")
+    if valid_seq_len is not None:
+        raise RuntimeError("fp8_sdpa_recomp_fwd: valid_seq_len is not supported")
+    f = lambda s, d: float(d if s is None else (s.reshape(-1)[0] if isinstance(s, torch.Tensor) else s))  # noqa: E731
+    dq, dk, dv = f(d_scale_q, 1.0), f(d_scale_k, 1.0), f(d_scale_v, 1.0)
+    qs = f(q_scale_s, 1.0)
+    ds = f(d_scale_s, 1.0 / qs)
+    if scale is None:
+        scale = 1.0 / math.sqrt(q.shape[-1])
+    c = torch.tensor(dq, dtype=torch.float32) * torch.tensor(dk, dtype=torch.float32) * torch.tensor(float(scale), dtype=torch.float32)
+    s = torch.matmul(q.float(), k.float().transpose(-2, -1)) * c
+    L, S = q.shape[-2], k.shape[-2]
+    if attention_mask is not None:
+        if attention_mask.dtype == torch.bool:
+            s = s.masked_fill(~attention_mask, SDPA_MASKED)
+        else:
+            s = s + attention_mask.float()
+    if is_causal:
+        keep = torch.ones(L, S, dtype=torch.bool).tril(0)
+        s = s.masked_fill(~keep, SDPA_MASKED)
+    m = s.amax(dim=-1, keepdim=True)
+    pt = torch.exp2((s - m) * 1.4426950408889634)
+    l = pt.sum(dim=-1, keepdim=True)
+    p8 = _rne_to_fp8((pt * qs).clamp(max=448.0), torch.float8_e4m3fn)
+    o = torch.matmul(p8.float(), v.float()) * (torch.tensor(ds, dtype=torch.float32) * torch.tensor(dv, dtype=torch.float32)) / l
+    if q_scale_o is not None:
+        out = _rne_to_fp8((o * f(q_scale_o, 1.0)).clamp(-448.0, 448.0), torch.float8_e4m3fn)
+    else:
+        out = o.to(torch.bfloat16)
+    one = torch.zeros(1, dtype=torch.float32)
+    amax_s = (1.0 / l).max().reshape(1).float() if is_amax_s else one
+    amax_o = o.abs().max().reshape(1).float() if is_amax_o else one
+    if requires_backward:
+        m_out, linv = m.to(torch.bfloat16), (1.0 / l).to(torch.bfloat16)
+    else:
+        m_out, linv = torch.zeros(1, dtype=torch.bfloat16), torch.zeros(1, dtype=torch.bfloat16)
+    return out, m_out, linv, torch.zeros(1, dtype=torch.int32), amax_s, amax_o
