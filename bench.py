@@ -19,7 +19,7 @@ The default (headline) line carries three sub-records beside the contract's keys
 
 --workload selects one member of the operator family for the same JSON contract:
   gemm (default) | gemm_m1 | gemm_m16 | gemm_m128 | cast_rne | cast_sr | uncast | cast_hybrid | cast_current |
-  softmax_fp8 | dequant | dequant_kpacked | w4a16_m2048 | w4a16_m16 | mlp | scaled_mm_lib
+  softmax_fp8 | sdpa_fp8 | dequant | dequant_kpacked | w4a16_m2048 | w4a16_m16 | w4a16_m16_kpacked | mlp | scaled_mm_lib
 (scaled_mm_lib times torch._scaled_mm -- the vendor library -- on the headline shape, as context only).
 --impl reference times the CPU restatement of the reference semantics (the oracle; the
 reference itself has no arithmetic for these operators) on the host cores.
@@ -321,6 +321,41 @@ def build_workload(wl, args, dev, rank, world, peaks):
         w.workload = f"cast_to_fp8_hybrid on {n} bf16 elements ~N(0,1)"
         w.dtype = "bf16->e5m2+e4m3"
         w.l2 = "3 rotating tensors"
+    elif wl == "sdpa_fp8":
+        # causal self-attention of a Llama-3-70B-shaped layer shard: 8 query heads per GPU (tp = 8), one
+        # key/value head, head dimension 128, 2 sequences of 8192 tokens
+        import ctypes as C
+        Bq, Hq, Hkv, Ls, Dh = 2, 8, 1, 8192, 128
+        g = torch.Generator(device=dev).manual_seed(23 + rank)
+        mk = lambda *shape: torch.randn(*shape, device=dev, generator=g, dtype=torch.float32).mul(40).to(torch.float8_e4m3fn)  # noqa: E731
+        sets = [(mk(Bq * Hq, Ls, Dh), mk(Bq * Hkv, Ls, Dh), mk(Bq * Hkv, Ls, Dh), torch.empty(Bq * Hq, Ls, Dh, device=dev, dtype=torch.bfloat16))
+                for _ in range(3)]
+        argsets = []
+        for q8, k8, v8, o in sets:
+            a = abi.SdpaArgs()
+            a.q, a.k, a.v, a.out, a.out_dtype = q8.data_ptr(), k8.data_ptr(), v8.data_ptr(), o.data_ptr(), abi.BF16
+            a.BH, a.L, a.S, a.dqk, a.dv, a.kv_rep, a.causal = Bq * Hq, Ls, Ls, Dh, Dh, Hq // Hkv, 1
+            a.softmax_scale = 1.0 / Dh ** 0.5
+            a.d_scale_q_host = a.d_scale_k_host = a.d_scale_v_host = 1.0 / 40
+            a.q_scale_s_host, a.q_scale_o_host, a.d_scale_s_host = 256.0, 1.0, 1.0
+            argsets.append(a)
+
+        def step(i):
+            a = argsets[i % 3]
+            a.stream = torch.cuda.current_stream().cuda_stream
+            abi.check(abi.lib.b200q_fp8_sdpa_fwd(C.byref(a)))
+        w.step = step
+        # causal: half of the L x S score matrix; two products of 2 * D flop per score
+        w.flops = 2.0 * 2.0 * Bq * Hq * Ls * Ls * Dh / 2
+        w.algo_bytes = Bq * Hq * Ls * Dh + 2 * Bq * Hkv * Ls * Dh + 2 * Bq * Hq * Ls * Dh
+        w.bound, w.unit_per_step, w.unit = "tensor", w.flops / 1e12, "TFLOP/s"
+        w.peak = 2.0 * peaks["bf16_tflops"]
+        w.peak_note = "2 x measured cuBLAS bf16 burst; useful flops only (the kernel's second Q K^T pass is not counted)"
+        w.metric = "fp8_sdpa_recomp_fwd TFLOP/s (causal, useful flops)"
+        w.workload = f"fp8_sdpa_recomp_fwd e4m3 causal, {Bq} x {Hq} query heads over {Hkv} key/value head, {Ls} tokens, head dim {Dh}, bf16 out"
+        w.dtype = "fp8_e4m3 (fp32 accumulate), e4m3 probabilities"
+        w.l2 = "3 rotating q/k/v/out sets"
+        w.graph_ok = False
     elif wl == "softmax_fp8":
         # attention-probability shaped: rows x cols bf16 -> e4m3 with scales (3 B/element)
         rows_, cols_ = 16384, 4096
@@ -560,7 +595,7 @@ def family_record(args, dev, peaks):
     members = [("cast_rne", 1 << 24), ("cast_rne", 1 << 26), ("cast_sr", 1 << 24), ("cast_sr", 1 << 26),
                ("uncast", 1 << 24), ("uncast", 1 << 26), ("dequant", None), ("dequant_kpacked", None),
                ("gemm_m1", None), ("gemm_m16", None), ("gemm_m128", None), ("w4a16_m16", None), ("w4a16_m16_kpacked", None),
-               ("w4a16_m2048", None)]
+               ("w4a16_m2048", None), ("sdpa_fp8", None), ("softmax_fp8", None), ("cast_hybrid", None)]
     out = {}
     for name, elems in members:
         a = argparse.Namespace(**vars(args))

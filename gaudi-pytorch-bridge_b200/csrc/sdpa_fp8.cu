@@ -1,14 +1,18 @@
 // FP8 scaled-dot-product attention, forward: out = softmax(q k^T * scale + mask) v with q, k, v in
 // e4m3 and the probabilities re-quantised to e4m3 for the second product.
 //
-// tcgen05 kernel (head dimension 128), one CTA per (batch x head, block of 128 queries), 192 threads:
+// tcgen05 kernel (head dimension 128), one CTA per (batch x head, block of 128 queries), 320 threads:
 //   warp 0    TMA producer: the query tile once, then the key tiles (twice, see below) and value
 //             tiles through two shared-memory rings (128-byte swizzle, no multicast)
 //   warp 1    TMEM owner and MMA issuer: S = Q K^T (kind::f8f6f4, 128 x 128 x 32 per instruction)
 //             into one of two score buffers in TMEM, and O += P V with P read from shared memory
 //             (K-major) and V through an MN-major descriptor (V is stored [key][d]: no transpose)
-//   warps 2-5 softmax: thread = query row; tcgen05.ld of its score row, scale / mask / exp2, the
-//             e4m3 probabilities written into the swizzled P tile for the second product
+//   warps 2-9 softmax, two groups of four warps; a group owns one of the two score buffers (it takes
+//             every other key block) and thread = query row: tcgen05.ld of its score row, scale /
+//             mask / exp2, the e4m3 probabilities written into the swizzled P tile for the second
+//             product.  Blocks with nothing to mask take a path of one instruction per score in
+//             the first pass and 3.5 in the second (FFMA, ex2.approx, add, half a convert: the
+//             probability scale is folded into the exponent and divided out of the row sum).
 // Two passes over the keys: the first only takes the row maxima, the second recomputes the
 // scores and forms exp(S - max) against the final maximum.  The probabilities are therefore
 // quantised exactly where the CPU restatement quantises them (no running-maximum rescaling of
@@ -35,7 +39,7 @@ constexpr int kBM = 128;       // queries per CTA
 constexpr int kBN = 128;       // keys per block
 constexpr int kStages = 3;     // key / value ring depth
 constexpr int kTile = 128 * 128;  // bytes of every tile here
-constexpr int kThreads = 192;
+constexpr int kThreads = 320;   // producer warp, MMA warp, two softmax warpgroups
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kMasked = -1.0e30f;
 
@@ -76,6 +80,11 @@ __device__ __forceinline__ void load_scales(Params& p) {
 }
 
 // warp maximum of a non-negative float (bit patterns of non-negative floats order like the values)
+__device__ __forceinline__ float ex2_approx(float x) {
+  float y;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+  return y;
+}
 __device__ __forceinline__ float warp_max_f32_bits(float x) { return __uint_as_float(warp_max_u32(__float_as_uint(x))); }
 
 // mask term of (row, key) in the log2 domain
@@ -92,7 +101,8 @@ struct Smem {
   static constexpr int kK = kQ + kTile;
   static constexpr int kV = kK + kStages * kTile;
   static constexpr int kP = kV + kStages * kTile;
-  static constexpr int kBars = kP + 2 * kTile;
+  static constexpr int kRowStats = kP + 2 * kTile;        // [2 groups][128 rows] fp32: maxima, then sums
+  static constexpr int kBars = kRowStats + 2 * 128 * 4;
   // barriers: q_full, k_full[3], k_empty[3], v_full[3], v_empty[3], s_full[2], s_empty[2], p_full[2], p_empty[2], o_full
   static constexpr int kNumBars = 1 + 4 * kStages + 8 + 1;
   static constexpr int kTotal = kBars + kNumBars * 8 + 16;
@@ -117,7 +127,9 @@ sdpa_fp8_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
   const int64_t bh = blockIdx.y;
-  const int64_t q0 = (int64_t)blockIdx.x * kBM;
+  // (the last query blocks first: under a causal mask they have the most key blocks, and a long
+  // CTA that starts late is what the kernel ends on)
+  const int64_t q0 = (int64_t)(gridDim.x - 1 - blockIdx.x) * kBM;
   const int64_t kv = bh / p.kv_rep;
   // key blocks this query block needs (causal: keys beyond its last query are all masked)
   int64_t keys = p.S;
@@ -212,44 +224,75 @@ sdpa_fp8_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
       if (ok) umma_commit(bar_of);
     }
   } else {
-    // ------------------------------------------------------------ softmax (warps 2..5)
+    // ------------------------------------------------------------ softmax (warps 2..9)
+    const int grp = (warp - 2) >> 2;          // 0 / 1: the score buffer (and key blocks t = grp mod 2) of this group
     const int qtr = warp & 3;                 // TMEM lane quarter of this warp
     const int row = qtr * 32 + lane;          // query row inside the block = TMEM lane
     const int64_t qi = q0 + row;              // query index
-    const int st = threadIdx.x - 64;          // 0..127
+    const int st = (threadIdx.x - 64) & 127;  // 0..127 inside the group
+    const int bar_id = 1 + grp;               // named barrier of the group; 3 = both groups
     const uint32_t t_lane = tmem + ((uint32_t)(qtr * 32) << 16);
+    float* stats = reinterpret_cast<float*>(smem + Smem::kRowStats);
     float mx = kMasked;                       // row maximum, log2 domain
-    float lsum = 0.f;
+    float off = 0.f;                          // log2(q_scale_s) - mx (second pass)
+    float ls[4] = {0.f, 0.f, 0.f, 0.f};       // partial row sums of the scaled probabilities
+    const float lq = log2f(p.q_scale_s);
     bool stop = false;
-    for (int t = 0; t < 2 * nblk && !stop; ++t) {
-      const int j = t < nblk ? t : t - nblk;
-      const uint32_t sb = t & 1, sph = (t >> 1) & 1;
+    // nothing to mask in a block: no mask tensor, all of its keys exist and (causal) lie at or
+    // before the first query of this block
+    auto block_plain = [&](int j) {
+      const int64_t key0 = (int64_t)j * kBN;
+      return p.mask_kind == 0 && key0 + kBN <= p.S && (!p.causal || key0 + kBN - 1 <= q0);
+    };
+    // One key block of this group: scores -> row maximum (first pass) or e4m3 probabilities and
+    // row sum (second pass).  Returns false when a wait ran out.
+    auto do_tile = [&](int t) {
+      const bool second = t >= nblk;
+      const int j = second ? t - nblk : t;
+      const uint32_t sb = grp, sph = (t >> 1) & 1;
       mbar_wait(bar_sf + 8 * sb, sph, abort_flag, p.status, kErrSoftmax, 32);
-      if (t >= nblk && j >= 2) mbar_wait(bar_pe + 8 * (j & 1), ((j >> 1) - 1) & 1, abort_flag, p.status, kErrSoftmax, 32);
-      named_bar_sync(1, 128);
-      if (st == 0) *sm_stop = *abort_flag;
-      named_bar_sync(1, 128);
-      if (*sm_stop) { stop = true; break; }
+      if (second && j >= 2) mbar_wait(bar_pe + 8 * (j & 1), ((j >> 1) - 1) & 1, abort_flag, p.status, kErrSoftmax, 32);
+      named_bar_sync(bar_id, 128);
+      if (st == 0) sm_stop[grp] = *abort_flag;
+      named_bar_sync(bar_id, 128);
+      if (sm_stop[grp]) return false;
       tc_fence_after();
       const int64_t key0 = (int64_t)j * kBN;
+      const bool plain = block_plain(j);
       uint8_t* prow = smem + Smem::kP + (j & 1) * kTile + row * 128;
+      // the row in two halves of 64 scores: both loads of a half are in flight together
 #pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
-        uint32_t r[32];
-        tmem_ld_32x32(t_lane + sb * 128 + c * 32, r);
-        tmem_ld_wait();
+      for (int half = 0; half < 2; ++half) {
+      uint32_t rr[2][32];
+      tmem_ld_32x32(t_lane + sb * 128 + half * 64, rr[0]);
+      tmem_ld_32x32(t_lane + sb * 128 + half * 64 + 32, rr[1]);
+      tmem_ld_wait();
+#pragma unroll
+      for (int cc = 0; cc < 2; ++cc) {
+        const int c = 2 * half + cc;
+        const uint32_t* r = rr[cc];
         float x[32];
+        if (plain) {
 #pragma unroll
-        for (int e = 0; e < 32; ++e) {
-          const int64_t key = key0 + c * 32 + e;
-          float v = __uint_as_float(r[e]) * p.c_log2;
-          if (p.mask_kind) v += mask_term(p, bh, qi < p.L ? qi : p.L - 1, key < p.S ? key : p.S - 1);
-          if (key >= p.S || (p.causal && key > qi)) v = kMasked;
-          x[e] = v;
+          for (int e = 0; e < 32; ++e) x[e] = __uint_as_float(r[e]) * p.c_log2;
+        } else {
+#pragma unroll
+          for (int e = 0; e < 32; ++e) {
+            const int64_t key = key0 + c * 32 + e;
+            float v = __uint_as_float(r[e]) * p.c_log2;
+            if (p.mask_kind) v += mask_term(p, bh, qi < p.L ? qi : p.L - 1, key < p.S ? key : p.S - 1);
+            if (key >= p.S || (p.causal && key > qi)) v = kMasked;
+            x[e] = v;
+          }
         }
-        if (t < nblk) {
+        if (!second) {
+          float m4[4] = {mx, kMasked, kMasked, kMasked};
 #pragma unroll
-          for (int e = 0; e < 32; ++e) mx = fmaxf(mx, x[e]);
+          for (int e = 0; e < 32; e += 4) {
+            m4[0] = fmaxf(m4[0], x[e]); m4[1] = fmaxf(m4[1], x[e + 1]);
+            m4[2] = fmaxf(m4[2], x[e + 2]); m4[3] = fmaxf(m4[3], x[e + 3]);
+          }
+          mx = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
         } else {
           uint32_t w[8];
 #pragma unroll
@@ -257,10 +300,10 @@ sdpa_fp8_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
             float pr[4];
 #pragma unroll
             for (int u = 0; u < 4; ++u) {
-              pr[u] = exp2f(x[e + u] - mx);
-              lsum += pr[u];
-              pr[u] = fminf(pr[u] * p.q_scale_s, 448.f);
+              pr[u] = ex2_approx(x[e + u] + off);  // = exp(S - max) * q_scale_s
+              ls[u] += pr[u];
             }
+            // (the conversion saturates at 448: a probability scale beyond that cannot overflow)
             w[e >> 2] = cvt_fp8x2<B200Q_E4M3>(pr[0], pr[1]) | (cvt_fp8x2<B200Q_E4M3>(pr[2], pr[3]) << 16);
           }
           // 32 keys = two 16-byte pieces (2c, 2c + 1) of the row, XOR-swizzled by the row
@@ -268,21 +311,40 @@ sdpa_fp8_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
           *reinterpret_cast<uint4*>(prow + (((2 * c + 1) ^ (row & 7)) << 4)) = make_uint4(w[4], w[5], w[6], w[7]);
         }
       }
+      }
       tc_fence_before();
       mbar_arrive(bar_se + 8 * sb);  // the score buffer may be overwritten
-      if (t >= nblk) {
+      if (second) {
         fence_proxy_async_smem();    // the P tile is read by the tensor core (async proxy)
         mbar_arrive(bar_pf + 8 * (j & 1));
       }
-    }
-    // ---- output: O / l, scaled
+      return true;
+    };
+    // first pass: this group's blocks t = grp, grp + 2, ... < nblk
+    for (int t = grp; t < nblk && !stop; t += 2) stop = !do_tile(t);
+    // between the passes both groups meet (stopped or not, exactly once): the row maximum over
+    // all blocks
+    stats[grp * 128 + row] = mx;
+    named_bar_sync(3, 256);
+    mx = fmaxf(stats[row], stats[128 + row]);
+    off = lq - mx;
+    named_bar_sync(3, 256);
+    // second pass: tiles t = nblk .. 2 nblk - 1 with t = grp (mod 2)
+    for (int t = nblk + ((nblk & 1) == grp ? 0 : 1); t < 2 * nblk && !stop; t += 2) stop = !do_tile(t);
+    // ---- output: O / l, scaled.  The row sums of both groups are added, then group 0 writes the
+    // first 64 output columns of its rows and group 1 the other 64.
+    float lsum = (ls[0] + ls[1]) + (ls[2] + ls[3]);
     if (!stop && nblk > 0) {
       mbar_wait(bar_of, 0, abort_flag, p.status, kErrSoftmax, 64);
-      named_bar_sync(1, 128);
-      if (st == 0) *sm_stop = *abort_flag;
-      named_bar_sync(1, 128);
-      stop = *sm_stop != 0;
+      named_bar_sync(bar_id, 128);
+      if (st == 0) sm_stop[grp] = *abort_flag;
+      named_bar_sync(bar_id, 128);
+      stop = sm_stop[grp] != 0;
     }
+    // (both groups reach these two barriers exactly once, stopped or not)
+    stats[grp * 128 + row] = lsum;
+    named_bar_sync(3, 256);
+    lsum = (stats[row] + stats[128 + row]) / p.q_scale_s;
     if (!stop) {
       tc_fence_after();
       const float linv = lsum > 0.f ? 1.f / lsum : 0.f;
@@ -290,7 +352,7 @@ sdpa_fp8_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
       float amax_o = 0.f;
       const bool in = qi < p.L;
 #pragma unroll 1
-      for (int c = 0; c < 4; ++c) {
+      for (int c = 2 * grp; c < 2 * grp + 2; ++c) {
         uint32_t r[32];
         if (nblk > 0) {
           tmem_ld_32x32(t_lane + 256 + c * 32, r);
@@ -324,12 +386,12 @@ sdpa_fp8_tcgen05_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_
           }
         }
       }
-      if (in) {
+      if (in && grp == 0) {
         if (p.m_out) p.m_out[bh * p.L + qi] = __float2bfloat16_rn(mx / kLog2e);
         if (p.linv_out) p.linv_out[bh * p.L + qi] = __float2bfloat16_rn(linv);
       }
       // amax of the probabilities (1 / l of a row is its largest probability) and of the output
-      if (p.amax_s) {
+      if (p.amax_s && grp == 0) {
         const float a = warp_max_f32_bits(in ? linv : 0.f);
         if (lane == 0 && a > 0.f) atomicMax(reinterpret_cast<unsigned int*>(p.amax_s), __float_as_uint(a));
       }
