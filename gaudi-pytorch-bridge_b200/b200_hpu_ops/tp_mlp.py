@@ -134,6 +134,7 @@ class TpFp8Mlp:
             raise ValueError(f"unknown comm mode {comm!r}")
         self.comm = comm
         self._peer: Optional[PeerBuffers] = None
+        self._no_peer_buffers = False  # comm="auto": the ranks could not map each other's memory
         self.skip_collective = False  # measurement only: leaves the partial sums unreduced
         dev = shard.w_gate_up.device
         self._xs_inv = torch.tensor(1.0 / self.x_scale, dtype=torch.float32, device=dev)
@@ -145,6 +146,8 @@ class TpFp8Mlp:
         can_fuse = self.ops is torch.ops.hpu and tokens % (tp * 128) == 0 and tokens // tp >= 128 and tokens > 128
         if self.comm == "fused" and not can_fuse:
             raise ValueError(f"comm='fused' needs CUDA operators and tokens divisible into {tp} blocks of whole 128-row tiles")
+        if self.comm == "auto" and self._no_peer_buffers:
+            return "nccl"
         return "fused" if (self.comm in ("auto", "fused") and can_fuse) else "nccl"
 
     def describe(self, tp: int, tokens: int = 8192) -> str:
@@ -207,7 +210,7 @@ class TpFp8Mlp:
         tp = dist.get_world_size(self.group) if (dist.is_available() and dist.is_initialized()) else 1
         if tp == 1:
             return self.down_partial(h8)
-        if self._mode(tp, h8.shape[0]) == "fused":
+        if self._mode(tp, h8.shape[0]) == "fused" and self._ensure_peer_buffers(h8):
             return self._down_fused(h8)
         rows = h8.shape[0]
         nblk = max(1, min(self.row_blocks, rows))
@@ -227,13 +230,35 @@ class TpFp8Mlp:
             w.wait()
         return out
 
+    def _ensure_peer_buffers(self, h8: torch.Tensor) -> bool:
+        """Allocates and exchanges the peer-addressable buffers on first use.  The ranks agree on the
+        outcome (a MIN all-reduce of a success flag): with comm="auto" a failure anywhere -- peer
+        mapping not permitted on this machine -- turns every rank to the NCCL mode; with
+        comm="fused" it is an error."""
+        import torch.distributed as dist
+        tokens, d = h8.shape[0], self.s.w_down.shape[0]
+        if self._peer is not None and self._peer.tokens == tokens and self._peer.d == d:
+            return True
+        err = None
+        try:
+            pb = PeerBuffers(tokens, d, h8.device, self.group)
+        except Exception as e:  # noqa: BLE001  (whatever the allocator or the exchange raised)
+            pb, err = None, e
+        ok = torch.tensor([1 if pb is not None else 0], device=h8.device, dtype=torch.int32)
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN, group=self.group)
+        if int(ok.item()) == 0:
+            if self.comm == "fused":
+                raise RuntimeError(f"comm='fused': the ranks could not map each other's memory: {err!r}")
+            self._no_peer_buffers = True
+            return False
+        self._peer = pb
+        pb.barrier()
+        return True
+
     def _down_fused(self, h8: torch.Tensor) -> torch.Tensor:
         from . import abi
-        tokens, d = h8.shape[0], self.s.w_down.shape[0]
+        d = self.s.w_down.shape[0]
         pb = self._peer
-        if pb is None or pb.tokens != tokens or pb.d != d:
-            pb = self._peer = PeerBuffers(tokens, d, h8.device, self.group)
-            pb.barrier()
         # rank r's partial sums of block i (token rows [i * rows, (i + 1) * rows)) -> slot r of rank i's stage
         abi.fp8_gemm_nt(h8, self.s.w_down, torch.bfloat16, 1.0 / self.act_scale, self.s.s_down_inv, None,
                         route=(pb.stage_ptrs, pb.rows, pb.rank * pb.rows))

@@ -154,3 +154,43 @@ def test_mlp_tensor_parallel_nccl(world):
             assert err <= 1e-2, (rank, comm, err)
     for p in procs:
         assert p.exitcode == 0
+
+
+@pytest.mark.parametrize("tp", [2, 4, 8])
+@pytest.mark.parametrize("N", [512, 704])
+def test_routed_gemm_and_reduce_bcast_on_one_device(tp, N):
+    """The two kernels of the fused collective with the ranks emulated on one GPU: `tp` row-parallel
+    GEMMs (one K-shard each) route their partial sums into per-owner staging buffers, then every
+    owner adds the slots and writes its rows into all outputs.  Checked against the sum of the
+    bf16 partial products formed with the ordinary (unrouted) GEMM, and against the oracle."""
+    import b200_hpu_ops
+    from b200_hpu_ops import abi
+    T, Kf = 1024, 256 * tp
+    rows = T // tp
+    g = torch.Generator(device="cuda").manual_seed(tp * 7 + N)
+    h8 = torch.randn(T, Kf, device="cuda", generator=g).clamp(-3, 3).mul(50).to(torch.float8_e4m3fn)
+    w8 = torch.randn(N, Kf, device="cuda", generator=g).clamp(-3, 3).mul(50).to(torch.float8_e4m3fn)
+    sb = torch.rand(N, device="cuda", generator=g) * 1e-4 + 1e-4
+    stages = [torch.full((tp, rows, N), float("nan"), device="cuda", dtype=torch.bfloat16) for _ in range(tp)]
+    outs = [torch.full((T, N), float("nan"), device="cuda", dtype=torch.bfloat16) for _ in range(tp)]
+    partials = []
+    for r in range(tp):
+        hs, ws = h8[:, r * 256:(r + 1) * 256].contiguous(), w8[:, r * 256:(r + 1) * 256].contiguous()
+        abi.fp8_gemm_nt(hs, ws, torch.bfloat16, 0.01, sb, None, route=([s.data_ptr() for s in stages], rows, r * rows))
+        partials.append(abi.fp8_gemm_nt(hs, ws, torch.bfloat16, 0.01, sb, None))
+    # slot r of owner i holds rank r's partial sums of the rows owner i owns, bit for bit
+    for i in range(tp):
+        for r in range(tp):
+            assert torch.equal(stages[i][r], partials[r][i * rows:(i + 1) * rows]), (i, r)
+    for i in range(tp):
+        abi.tp_reduce_bcast(stages[i], [o.data_ptr() for o in outs], i, rows, N)
+    torch.cuda.synchronize()
+    acc = partials[0].float()
+    for pr in partials[1:]:
+        acc = acc + pr.float()   # fp32, in rank order
+    want = acc.to(torch.bfloat16)  # one rounding
+    for o in outs:
+        assert torch.equal(o, want)
+    ref = O.fp8_gemm_v2(h8.cpu(), False, w8.cpu(), True, None, torch.bfloat16, torch.tensor(0.01), sb.cpu(), None, False, [1, N])
+    assert O.rel_frobenius(outs[0], ref) <= 1e-2
+    assert b200_hpu_ops.device_status() == 0
