@@ -19,7 +19,7 @@ The default (headline) line carries three sub-records beside the contract's keys
 
 --workload selects one member of the operator family for the same JSON contract:
   gemm (default) | gemm_m1 | gemm_m16 | gemm_m128 | cast_rne | cast_sr | uncast | cast_hybrid | cast_current |
-  softmax_fp8 | sdpa_fp8 | dequant | dequant_kpacked | w4a16_m2048 | w4a16_m16 | w4a16_m16_kpacked | mlp | scaled_mm_lib
+  softmax_fp8 | sdpa_fp8 | conv2d_fp8 | dequant | dequant_kpacked | w4a16_m2048 | w4a16_m16 | w4a16_m16_kpacked | mlp | scaled_mm_lib
 (scaled_mm_lib times torch._scaled_mm -- the vendor library -- on the headline shape, as context only).
 --impl reference times the CPU restatement of the reference semantics (the oracle; the
 reference itself has no arithmetic for these operators) on the host cores.
@@ -355,6 +355,29 @@ def build_workload(wl, args, dev, rank, world, peaks):
         w.workload = f"fp8_sdpa_recomp_fwd e4m3 causal, {Bq} x {Hq} query heads over {Hkv} key/value head, {Ls} tokens, head dim {Dh}, bf16 out"
         w.dtype = "fp8_e4m3 (fp32 accumulate), e4m3 probabilities"
         w.l2 = "3 rotating q/k/v/out sets"
+        w.graph_ok = False
+    elif wl == "conv2d_fp8":
+        # a ResNet-50 stage-2 shaped 3x3 convolution through the operator (im2col kernel + the FP8 GEMM)
+        Nb, Cc, Hh, Ww, Co, kk = 32, 256, 56, 56, 256, 3
+        g = torch.Generator(device=dev).manual_seed(31 + rank)
+        xs = [torch.randn(Nb, Cc, Hh, Ww, device=dev, generator=g, dtype=torch.float32).to(torch.float8_e4m3fn) for _ in range(3)]
+        w8 = (torch.randn(Co, Cc, kk, kk, device=dev, generator=g, dtype=torch.float32) * 0.05).to(torch.float8_e4m3fn)
+        sx, sw = torch.tensor(0.5, device=dev), torch.tensor(0.25, device=dev)
+        keep = {}
+
+        def step(i):
+            keep["o"] = torch.ops.hpu.conv2d_fp8(xs[i % 3], w8, None, [1, 1], [1, 1], [1, 1], 1, torch.bfloat16, sx, sw)
+        w.step = step
+        w.launches_per_step = 2
+        w.flops = 2.0 * Nb * Hh * Ww * Co * Cc * kk * kk
+        w.algo_bytes = Nb * Cc * Hh * Ww + Co * Cc * kk * kk + 2 * Nb * Co * Hh * Ww
+        w.bound, w.unit_per_step, w.unit = "tensor", w.flops / 1e12, "TFLOP/s"
+        w.peak = 2.0 * peaks["bf16_tflops"]
+        w.peak_note = "2 x measured cuBLAS bf16 burst"
+        w.metric = "conv2d_fp8 TFLOP/s"
+        w.workload = f"conv2d_fp8 e4m3 [{Nb},{Cc},{Hh},{Ww}] * [{Co},{Cc},{kk},{kk}], stride 1, padding 1, bf16 out (im2col + GEMM, two launches)"
+        w.dtype = "fp8_e4m3 (fp32 accumulate)"
+        w.l2 = "3 rotating inputs; the 231 MB im2col matrix exceeds L2"
         w.graph_ok = False
     elif wl == "softmax_fp8":
         # attention-probability shaped: rows x cols bf16 -> e4m3 with scales (3 B/element)

@@ -5,6 +5,8 @@
 // warp shuffle, shared memory, one atomicMax per block).
 #include "common.cuh"
 
+#include <atomic>
+
 namespace b200q {
 
 enum ScaleClass { SC_ONE = 0, SC_COL = 1, SC_ROW = 2, SC_FULL = 3 };
@@ -676,11 +678,16 @@ __global__ void __launch_bounds__(256) swiglu_cast_kernel(SwigluParams p) {
 }
 
 // ------------------------------------------------------------------ host launchers
-// Grid for the grid-stride kernels: one block per 256 work items up to 16 times the number of
-// blocks that are resident at once, so that the block scheduler balances the SMs to within a
-// sixteenth of a wave whatever the size.
+// Grid for the grid-stride kernels, two shapes (measured on 2^24 and 2^26 elements):
+//  * one block per 256 items, capped at 16 waves of resident blocks -- the kernels with a few
+//    instructions per byte (RNE casts, cast_from_fp8, SwiGLU) run at the HBM rate this way;
+//  * ONE resident wave, balanced -- the kernels that are bound by instruction issue (stochastic
+//    rounding, the two-output hybrid cast) gain 7-10 %: with W = threads resident at once,
+//    every thread takes r = ceil(items / W) items and the grid is the number of 256-thread
+//    blocks that r items per thread need, ceil(items / (256 r)) <= the resident blocks; no block
+//    waits for another to retire and no thread has more than one item more than any other.
 template <typename Kernel>
-static int grid_for(Kernel kernel, int64_t n_items) {
+static int grid_for(Kernel kernel, int64_t n_items, bool one_wave = false) {
   static std::atomic<int> cached{0};  // per kernel instantiation; the same on every B200 of a process
   int per_sm = cached.load(std::memory_order_relaxed);
   if (per_sm == 0) {
@@ -688,15 +695,22 @@ static int grid_for(Kernel kernel, int64_t n_items) {
     cached.store(per_sm, std::memory_order_relaxed);
   }
   int64_t blocks = (n_items + 255) / 256;
-  int64_t cap = (int64_t)kNumSMs * per_sm * 16;
-  if (blocks > cap) blocks = cap;
+  const int64_t resident = (int64_t)kNumSMs * per_sm;
+  if (one_wave) {
+    if (blocks > resident) {
+      const int64_t r = (n_items + resident * 256 - 1) / (resident * 256);
+      blocks = (n_items + 256 * r - 1) / (256 * r);
+    }
+  } else if (blocks > resident * 16) {
+    blocks = resident * 16;
+  }
   if (blocks < 1) blocks = 1;
   return (int)blocks;
 }
 
 template <typename Kernel, typename Params>
-static void launch_persistent(Kernel kernel, int64_t items, cudaStream_t st, const Params& p) {
-  kernel<<<grid_for(kernel, items), 256, 0, st>>>(p);
+static void launch_persistent(Kernel kernel, int64_t items, cudaStream_t st, const Params& p, bool one_wave = false) {
+  kernel<<<grid_for(kernel, items, one_wave), 256, 0, st>>>(p);
 }
 
 template <typename InT, int FMT, bool SR>
@@ -751,11 +765,11 @@ int cast_to_fp8_impl(const void* in, int in_dtype, void* out, int out_dtype, con
   if (fast && sr) {
     const int64_t half = (items + 1) / 2;
     if (out_dtype == B200Q_E4M3) {
-      if (sc == SC_ROW) launch_persistent(cast_bf16_sr_fast_kernel<B200Q_E4M3, true>, half, st, p);
-      else launch_persistent(cast_bf16_sr_fast_kernel<B200Q_E4M3, false>, half, st, p);
+      if (sc == SC_ROW) launch_persistent(cast_bf16_sr_fast_kernel<B200Q_E4M3, true>, half, st, p, true);
+      else launch_persistent(cast_bf16_sr_fast_kernel<B200Q_E4M3, false>, half, st, p, true);
     } else {
-      if (sc == SC_ROW) launch_persistent(cast_bf16_sr_fast_kernel<B200Q_E5M2, true>, half, st, p);
-      else launch_persistent(cast_bf16_sr_fast_kernel<B200Q_E5M2, false>, half, st, p);
+      if (sc == SC_ROW) launch_persistent(cast_bf16_sr_fast_kernel<B200Q_E5M2, true>, half, st, p, true);
+      else launch_persistent(cast_bf16_sr_fast_kernel<B200Q_E5M2, false>, half, st, p, true);
     }
   } else if (fast) {
     const int64_t half = (items + 1) / 2;  // two chunks per thread and step
@@ -887,13 +901,13 @@ int cast_hybrid_impl(const void* in, int in_dtype, void* out152, void* out143, c
   const bool all_aligned = ((reinterpret_cast<uintptr_t>(in) | reinterpret_cast<uintptr_t>(out152) |
                              reinterpret_cast<uintptr_t>(out143)) & 15) == 0;
   if (in_dtype == B200Q_BF16 && !sr && !p.mul_fp32 && all_aligned) {
-    launch_persistent(cast_hybrid_bf16_rne_fast_kernel, items, st, p);
+    launch_persistent(cast_hybrid_bf16_rne_fast_kernel, items, st, p, true);
   } else if (in_dtype == B200Q_BF16) {
-    if (sr) launch_persistent(cast_hybrid_kernel<__nv_bfloat16, true>, items, st, p);
-    else launch_persistent(cast_hybrid_kernel<__nv_bfloat16, false>, items, st, p);
+    if (sr) launch_persistent(cast_hybrid_kernel<__nv_bfloat16, true>, items, st, p, true);
+    else launch_persistent(cast_hybrid_kernel<__nv_bfloat16, false>, items, st, p, true);
   } else {
-    if (sr) launch_persistent(cast_hybrid_kernel<float, true>, items, st, p);
-    else launch_persistent(cast_hybrid_kernel<float, false>, items, st, p);
+    if (sr) launch_persistent(cast_hybrid_kernel<float, true>, items, st, p, true);
+    else launch_persistent(cast_hybrid_kernel<float, false>, items, st, p, true);
   }
   B200Q_LAUNCH_CHECK();
   return B200Q_OK;

@@ -76,119 +76,167 @@ __global__ void __launch_bounds__(256) softmax_fp8_kernel(const SoftmaxParams p)
 }
 
 // bf16 rows of up to 32 * 8 * NV elements whose length is a multiple of 8: the row is read once,
-// with 16-byte loads, and stays in registers (packed) for the three passes max / sum / write.
+// with 16-byte loads, and stays in registers for the three passes max / sum / write.  The
+// kernel is bound by instruction issue and by the special-function unit, not by HBM, unless
+// every pass is lean, so:
+//   * without a fused addend the maximum is taken on the packed bf16 pairs (one instruction
+//     per two values; a negative input scale flips the sign bits first, x = (-raw) * (-scale));
+//   * every exponential is computed once (ex2.approx on x * log2(e) - max, 2 ulp) and kept as
+//     fp32 in the registers that held the packed input;
+//   * NaN is a property of the whole row (a NaN or +inf input, or a row of -inf, makes the sum
+//     NaN), so it is tested once per row, not per value;
+//   * an output scale that is a power of two commutes with the rounding to bf16, which saves
+//     the second rounding.
 __device__ __forceinline__ float ex2_approx(float x) {
   float y;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
 
-template <int NV>
-__global__ void __launch_bounds__(256) softmax_bf16_rowreg_kernel(const SoftmaxParams p) {
+__device__ __forceinline__ uint32_t max_bf16x2(uint32_t a, uint32_t b) {
+  uint32_t r;
+  asm("max.bf16x2 %0, %1, %2;" : "=r"(r) : "r"(a), "r"(b));
+  return r;
+}
+
+template <int NV, bool FA>
+__global__ void __launch_bounds__(128) softmax_bf16_rowreg_kernel(const SoftmaxParams p) {
   const int lane = threadIdx.x & 31;
   const int64_t row = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (row >= p.rows) return;
   float pre = p.pre_scale;
   if (p.inv_attn_heads) pre *= __ldg(p.inv_attn_heads);
   if (p.input_scale) pre *= __ldg(p.input_scale);
-  // exponentials as 2^(x * log2(e) - max): one multiply folded into the input scaling and one
-  // ex2.approx (2 ulp) per value instead of a full expf
   constexpr float kLog2e = 1.4426950408889634f;
   pre *= kLog2e;
-  const uint4* fa = nullptr;
-  if (p.fused_add) {
+  const int nvec = (int)(p.cols >> 3);
+  const uint4* src = reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(p.in) + row * p.cols);
+  uint32_t w[NV][4];
+#pragma unroll
+  for (int i = 0; i < NV; ++i) {
+    const int v = lane + 32 * i;
+    const uint4 t = v < nvec ? __ldcs(src + v) : make_uint4(0xFF80FF80u, 0xFF80FF80u, 0xFF80FF80u, 0xFF80FF80u);  // -inf
+    w[i][0] = t.x, w[i][1] = t.y, w[i][2] = t.z, w[i][3] = t.w;
+  }
+  float e[NV][8];  // x after pass 1 (with a fused addend only), the exponentials after pass 2
+  float m;
+  if constexpr (FA) {
     int64_t r = row, off = 0;
     for (int d = p.nd - 1; d >= 0; --d) {
       off += (r % p.size[d]) * p.fa_stride[d];
       r /= p.size[d];
     }
-    fa = reinterpret_cast<const uint4*>(p.fused_add + off);
-  }
-  const int nvec = (int)(p.cols >> 3);
-  const uint4* src = reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(p.in) + row * p.cols);
-  uint4 w[NV];
+    const uint4* fa = reinterpret_cast<const uint4*>(p.fused_add + off);
+    m = -INFINITY;
 #pragma unroll
-  for (int i = 0; i < NV; ++i) {
-    const int v = lane + 32 * i;
-    w[i] = v < nvec ? __ldcs(src + v) : make_uint4(0, 0, 0, 0);
-  }
-  // x_j of vector i (recomputed in every pass: 8 multiplies are cheaper than 8 registers)
-  auto values = [&](int i, float* x) {
-    const uint32_t ws[4] = {w[i].x, w[i].y, w[i].z, w[i].w};
+    for (int i = 0; i < NV; ++i) {
+      const int v = lane + 32 * i;
+      if (v < nvec) {
+        const uint4 f = __ldg(fa + v);
+        const uint32_t fs[4] = {f.x, f.y, f.z, f.w};
 #pragma unroll
-    for (int k = 0; k < 4; ++k) {
-      x[2 * k] = bf16_bits_to_float(ws[k] & 0xFFFFu) * pre;
-      x[2 * k + 1] = bf16_bits_to_float(ws[k] >> 16) * pre;
-    }
-    if (fa) {
-      const uint4 f = __ldg(fa + lane + 32 * i);
-      const uint32_t fs[4] = {f.x, f.y, f.z, f.w};
-#pragma unroll
-      for (int k = 0; k < 4; ++k) {
-        x[2 * k] = fmaf(bf16_bits_to_float(fs[k] & 0xFFFFu), kLog2e, x[2 * k]);
-        x[2 * k + 1] = fmaf(bf16_bits_to_float(fs[k] >> 16), kLog2e, x[2 * k + 1]);
+        for (int k = 0; k < 4; ++k) {
+          e[i][2 * k] = fmaf(__uint_as_float(fs[k] << 16), kLog2e, __uint_as_float(w[i][k] << 16) * pre);
+          e[i][2 * k + 1] = fmaf(__uint_as_float(fs[k] & 0xFFFF0000u), kLog2e, __uint_as_float(w[i][k] & 0xFFFF0000u) * pre);
+          m = fmaxf(m, fmaxf(e[i][2 * k], e[i][2 * k + 1]));
+        }
       }
     }
-  };
-  float m = -INFINITY;
+  } else {
+    if (pre < 0.f) {
+      pre = -pre;
 #pragma unroll
-  for (int i = 0; i < NV; ++i) {
-    if (lane + 32 * i < nvec) {
-      float x[8];
-      values(i, x);
+      for (int i = 0; i < NV; ++i) {
+        if (lane + 32 * i < nvec) {
 #pragma unroll
-      for (int j = 0; j < 8; ++j) m = fmaxf(m, x[j]);
+          for (int k = 0; k < 4; ++k) w[i][k] ^= 0x80008000u;
+        }
+      }
     }
+    uint32_t pm = 0xFF80FF80u;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+#pragma unroll
+      for (int k = 0; k < 4; ++k) pm = max_bf16x2(pm, w[i][k]);
+    }
+    m = fmaxf(__uint_as_float(pm << 16), __uint_as_float(pm & 0xFFFF0000u)) * pre;
   }
 #pragma unroll
   for (int o = 16; o; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xFFFFFFFFu, m, o));
   float s = 0.f;
+  const float neg_m = -m;
 #pragma unroll
   for (int i = 0; i < NV; ++i) {
     if (lane + 32 * i < nvec) {
-      float x[8];
-      values(i, x);
 #pragma unroll
-      for (int j = 0; j < 8; ++j) s += ex2_approx(x[j] - m);
+      for (int k = 0; k < 4; ++k) {
+        if constexpr (FA) {
+          e[i][2 * k] = ex2_approx(e[i][2 * k] + neg_m);
+          e[i][2 * k + 1] = ex2_approx(e[i][2 * k + 1] + neg_m);
+        } else {
+          e[i][2 * k] = ex2_approx(fmaf(__uint_as_float(w[i][k] << 16), pre, neg_m));
+          e[i][2 * k + 1] = ex2_approx(fmaf(__uint_as_float(w[i][k] & 0xFFFF0000u), pre, neg_m));
+        }
+        s += e[i][2 * k] + e[i][2 * k + 1];
+      }
     }
   }
 #pragma unroll
   for (int o = 16; o; o >>= 1) s += __shfl_xor_sync(0xFFFFFFFFu, s, o);
-  const float inv = 1.f / s;
+  float inv = 1.f / s;
   const float so = p.output_scale ? __ldg(p.output_scale) : p.output_scale_host;
+  uint2* out8 = reinterpret_cast<uint2*>(static_cast<uint8_t*>(p.out) + row * p.cols);
+  uint4* out16 = reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(p.out) + row * p.cols);
+  if (inv != inv) {  // the whole row is NaN
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      const int v = lane + 32 * i;
+      if (v < nvec) {
+        if (p.out_fp8) __stcs(out8 + v, make_uint2(0x7F7F7F7Fu, 0x7F7F7F7Fu));
+        else __stcs(out16 + v, make_uint4(0x7FFF7FFFu, 0x7FFF7FFFu, 0x7FFF7FFFu, 0x7FFF7FFFu));
+      }
+    }
+    return;
+  }
+  if (!p.out_fp8) {
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      const int v = lane + 32 * i;
+      if (v < nvec)
+        __stcs(out16 + v, make_uint4(pack_bf16x2(e[i][0] * inv, e[i][1] * inv), pack_bf16x2(e[i][2] * inv, e[i][3] * inv),
+                                     pack_bf16x2(e[i][4] * inv, e[i][5] * inv), pack_bf16x2(e[i][6] * inv, e[i][7] * inv)));
+    }
+    return;
+  }
+  // e4m3(bf16(bf16(e * inv) * so)).  so = 2^k (normal, finite): bf16(e * inv) * so == bf16(e * (inv * so))
+  // wherever the e4m3 result is not 0 on both sides, so one rounding is enough.
+  const uint32_t so_bits = __float_as_uint(so);
+  const uint32_t so_exp = (so_bits >> 23) & 0xFFu;
+  const bool pow2 = (so_bits & 0x807FFFFFu) == 0 && so_exp > 32 && so_exp < 222;
+  if (pow2) inv *= so;
 #pragma unroll
   for (int i = 0; i < NV; ++i) {
     const int v = lane + 32 * i;
-    if (v < nvec) {
-      float x[8], y[8];
-      values(i, x);
+    uint32_t o2[2];
 #pragma unroll
-      for (int j = 0; j < 8; ++j) y[j] = round_to_bf16(ex2_approx(x[j] - m) * inv);
-      if (p.out_fp8) {
-        uint32_t o2[2] = {0, 0};
-#pragma unroll
-        for (int j = 0; j < 8; j += 2) {
-          const float z0 = round_to_bf16(y[j] * so), z1 = round_to_bf16(y[j + 1] * so);
-          uint32_t b = cvt_fp8x2<B200Q_E4M3>(z0, z1) & 0xFFFFu;
-          if (z0 != z0) b = (b & 0xFF00u) | 0x7Fu;
-          if (z1 != z1) b = (b & 0x00FFu) | 0x7F00u;
-          o2[j >> 2] |= b << (16 * ((j >> 1) & 1));
-        }
-        __stcs(reinterpret_cast<uint2*>(static_cast<uint8_t*>(p.out) + row * p.cols) + v, make_uint2(o2[0], o2[1]));
-      } else {
-        __stcs(reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(p.out) + row * p.cols) + v,
-               make_uint4(pack_bf16x2(y[0], y[1]), pack_bf16x2(y[2], y[3]), pack_bf16x2(y[4], y[5]), pack_bf16x2(y[6], y[7])));
-      }
+    for (int k = 0; k < 4; ++k) {
+      uint32_t zb = pack_bf16x2(e[i][2 * k] * inv, e[i][2 * k + 1] * inv);
+      if (!pow2) zb = pack_bf16x2(__uint_as_float(zb << 16) * so, __uint_as_float(zb & 0xFFFF0000u) * so);
+      const uint32_t b = cvt_fp8x2<B200Q_E4M3>(__uint_as_float(zb << 16), __uint_as_float(zb & 0xFFFF0000u)) & 0xFFFFu;
+      if (k & 1) o2[k >> 1] |= b << 16;
+      else o2[k >> 1] = b;
     }
+    if (v < nvec) __stcs(out8 + v, make_uint2(o2[0], o2[1]));
   }
 }
 
 template <int NV>
 static int launch_softmax_rowreg(const SoftmaxParams& p, cudaStream_t st) {
-  const int warps = 8;
+  const int warps = 4;
   const int64_t blocks = (p.rows + warps - 1) / warps;
   if (blocks > 0x7FFFFFFF) return B200Q_ERR_TOO_LARGE;
-  softmax_bf16_rowreg_kernel<NV><<<(int)blocks, warps * 32, 0, st>>>(p);
+  if (p.fused_add) softmax_bf16_rowreg_kernel<NV, true><<<(int)blocks, warps * 32, 0, st>>>(p);
+  else softmax_bf16_rowreg_kernel<NV, false><<<(int)blocks, warps * 32, 0, st>>>(p);
   B200Q_LAUNCH_CHECK();
   return B200Q_OK;
 }

@@ -90,33 +90,57 @@ __device__ __forceinline__ float ld_out_typed(const void* base, int dtype, int64
                              : static_cast<const float*>(base)[idx];
 }
 
-// out = ((acc * sa) * sb) + bias + D, rounded once to the output dtype.
-__device__ __forceinline__ float epilogue_value(const GemmParams& p, int64_t b, int64_t m, int64_t n, float acc) {
-  float v = acc;
-  if (p.a_scale_mode != B200Q_BCAST_NONE) v *= bcast_scale(p.a_scale, p.a_scale_host, p.a_scale_mode, m, n, p.N);
-  if (p.b_scale_mode != B200Q_BCAST_NONE) v *= bcast_scale(p.b_scale, p.b_scale_host, p.b_scale_mode, m, n, p.N);
+// out = ((acc * sa) * sb) + bias + D, rounded once to the output dtype.  The operands of one
+// output element can be fetched ahead of its accumulator (epi_load) and applied later (epi_apply).
+struct EpiOperands {
+  float sa, sb, bias, d;
+};
+
+__device__ __forceinline__ EpiOperands epi_load(const GemmParams& p, int64_t b, int64_t m, int64_t n) {
+  EpiOperands o;
+  o.sa = p.a_scale_mode != B200Q_BCAST_NONE ? bcast_scale(p.a_scale, p.a_scale_host, p.a_scale_mode, m, n, p.N) : 1.f;
+  o.sb = p.b_scale_mode != B200Q_BCAST_NONE ? bcast_scale(p.b_scale, p.b_scale_host, p.b_scale_mode, m, n, p.N) : 1.f;
+  o.bias = 0.f;
   if (p.bias_mode != B200Q_BCAST_NONE) {
     int64_t idx = p.bias_mode == B200Q_BCAST_PER_COL   ? n
                   : p.bias_mode == B200Q_BCAST_PER_ROW ? m
                   : p.bias_mode == B200Q_BCAST_FULL    ? b * p.bias_batch_stride + m * p.bias_ld + n
                                                        : 0;
-    v += ld_out_typed(p.bias, p.bias_dtype, idx);
+    o.bias = ld_out_typed(p.bias, p.bias_dtype, idx);
   }
-  if (p.D) v += ld_out_typed(p.D, p.d_dtype, b * p.d_batch_stride + m * p.ldd + n);
+  o.d = p.D ? ld_out_typed(p.D, p.d_dtype, b * p.d_batch_stride + m * p.ldd + n) : 0.f;
+  return o;
+}
+
+__device__ __forceinline__ float epi_apply(const GemmParams& p, float acc, const EpiOperands& o) {
+  float v = acc;
+  if (p.a_scale_mode != B200Q_BCAST_NONE) v *= o.sa;
+  if (p.b_scale_mode != B200Q_BCAST_NONE) v *= o.sb;
+  if (p.bias_mode != B200Q_BCAST_NONE) v += o.bias;
+  if (p.D) v += o.d;
   return v;
 }
 
-__device__ __forceinline__ void epilogue_store_one(const GemmParams& p, int64_t b, int64_t m, int64_t n, float acc) {
-  float v = epilogue_value(p, b, m, n, acc);
+__device__ __forceinline__ float epilogue_value(const GemmParams& p, int64_t b, int64_t m, int64_t n, float acc) {
+  return epi_apply(p, acc, epi_load(p, b, m, n));
+}
+
+// v = the value before the rounding to the output dtype; s8 = out8_scale_value(p) (read by the caller:
+// once per thread, not once per element)
+__device__ __forceinline__ void epilogue_store_value(const GemmParams& p, int64_t b, int64_t m, int64_t n, float v, float s8) {
   int64_t idx = b * p.out_batch_stride + m * p.ldo + n;
   if (p.out8_dtype) {
-    const uint32_t byte = out8_byte(p, v, out8_scale_value(p));
+    const uint32_t byte = out8_byte(p, v, s8);
     static_cast<uint8_t*>(p.out)[idx] = (uint8_t)byte;
     if (p.out8_amax) out8_amax_update(p, byte & 0x7Fu);
     return;
   }
   if (p.out_dtype == B200Q_BF16) static_cast<__nv_bfloat16*>(p.out)[idx] = __float2bfloat16_rn(v);
   else static_cast<float*>(p.out)[idx] = v;
+}
+
+__device__ __forceinline__ void epilogue_store_one(const GemmParams& p, int64_t b, int64_t m, int64_t n, float acc) {
+  epilogue_store_value(p, b, m, n, epilogue_value(p, b, m, n, acc), p.out8_dtype ? out8_scale_value(p) : 1.f);
 }
 
 int gemm_generic_launch(const GemmParams& p, cudaStream_t st);

@@ -41,6 +41,9 @@ struct TcGemmParams {
   GemmParams g;
   int64_t x_rows, y_rows;  // extents of the lane-side / column-side operands
   int x_tiles, y_tiles, num_kb;
+  // rows of the lane-side operand a tile covers (single-CTA kernel): 128, or fewer (a multiple of 8)
+  // in the few-token form, where the tile count, not the tile height, must match the machine
+  int x_tile_rows;
   int a_fmt_bits, b_fmt_bits;  // 0 = e4m3, 1 = e5m2 (lane-side, column-side)
   int x_mn, y_mn;              // 1 = that operand is stored MN-major ([K][rows], rows contiguous)
   int* status;                 // device status word (bounded waits report here)
@@ -437,12 +440,14 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
             break;
           }
           const uint32_t full = bar_full + 8 * stage;
-          mbar_arrive_expect_tx(full, L::kStageBytes);
+          mbar_arrive_expect_tx(full, L::kStageBytes - (kBlockX - p.x_tile_rows) * kBlockK);
           // K-major operand: box = 128 bytes of k x rows.  MN-major operand (stored [K][rows]):
           // box = 128 rows (bytes) x 128 k, one box per 128-row block; either way a 128-byte-
           // swizzled tile of the same size lands in the stage.
           const uint32_t xs = smem_base + stage * L::kStageBytes, ys = xs + L::kXBytes;
-          if (!p.x_mn) tma_load_2d(xs, &map_x, full, kb * kBlockK, xt * kBlockX);
+          // (a tile shorter than 128 rows leaves the stage's other rows as they were: the MMA
+          // reads them into accumulator lanes that nobody stores)
+          if (!p.x_mn) tma_load_2d(xs, &map_x, full, kb * kBlockK, xt * p.x_tile_rows);
           else tma_load_2d(xs, &map_x, full, xt * kBlockX, kb * kBlockK);
           if (!p.y_mn) {
             tma_load_2d(ys, &map_y, full, kb * kBlockK, yt * BN);
@@ -514,12 +519,13 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
     for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++it) {
       const int xt = tile % p.x_tiles, yt = tile / p.x_tiles;
       const uint32_t acc = it & 1, acc_phase = (it >> 1) & 1;
-      const int64_t x0 = (int64_t)xt * kBlockX, y0 = (int64_t)yt * BN;
+      const int64_t x0 = (int64_t)xt * p.x_tile_rows, y0 = (int64_t)yt * BN;
+      const int64_t x_end = x0 + p.x_tile_rows < p.x_rows ? x0 + p.x_tile_rows : p.x_rows;  // rows of this tile only
       // column-side (per-y) epilogue operands for this tile -> shared memory
       float* cA = epi_f + acc * 3 * BN;
       float* cB = cA + BN;
       float* cBias = cB + BN;
-      const EpiRow er = epi_stage_operands<BN, SWAP>(g, p.x_rows, p.y_rows, x0 + q * 32 + lane, y0, et, cA, cB, cBias);
+      const EpiRow er = epi_stage_operands<BN, SWAP>(g, x_end, p.y_rows, x0 + q * 32 + lane, y0, et, cA, cB, cBias);
       // The wait can give up for some threads only; the decision to stop must be the same for
       // all 128 epilogue threads because they meet at named barriers: one thread samples the
       // abort flag between two barriers and everybody follows that sample.
@@ -852,6 +858,7 @@ int gemm_tcgen05_launch(const GemmParams& g, cudaStream_t st) {
     tp.a_fmt_bits = fmt_bits(g.a_dtype); tp.b_fmt_bits = fmt_bits(g.b_dtype);
     tp.x_mn = a_mn; tp.y_mn = b_mn;
     tp.x_tiles = (int)((g.M + kBlockX - 1) / kBlockX);
+    tp.x_tile_rows = kBlockX;
     // Column-tile width: the one that minimises (waves over the 148 SMs) x (tile cost).  Measured
     // on 4096 x 14336 x 4096: a wave of 224-column tiles takes 96 % of the time of a wave of
     // 256-column tiles (the k-block time is dominated by operand traffic that does not shrink with
@@ -912,10 +919,28 @@ int gemm_tcgen05_launch(const GemmParams& g, cudaStream_t st) {
   tp.x_rows = g.N; tp.y_rows = g.M;
   tp.a_fmt_bits = fmt_bits(g.b_dtype); tp.b_fmt_bits = fmt_bits(g.a_dtype);
   tp.x_mn = b_mn; tp.y_mn = 0;
-  tp.x_tiles = (int)((g.N + kBlockX - 1) / kBlockX);
   const int bn = g.M <= 16 ? 16 : g.M <= 32 ? 32 : g.M <= 64 ? 64 : 128;
   tp.y_tiles = (int)((g.M + bn - 1) / bn);
-  int rc = make_map(&mx, g.B, g.N, g.K, g.ldb, b_mn, kBlockX);
+  // Tile height.  The kernel is one pass over the weight bytes, and a CTA's share of them is
+  // (rounds of tiles over the SMs) x (tile rows): 14336 weight rows in 128-row tiles are 112 tiles,
+  // one round in which 36 SMs stay idle and the others stream 128 rows each; in 104-row tiles they
+  // are 138 tiles of a fifth fewer bytes.  The tensor core still multiplies 128 lanes; the lanes
+  // beyond the tile read whatever the stage holds and are not stored.  Heights are multiples of 8
+  // (the swizzle atom) from 32 up (a stage shorter than that keeps too few bytes in flight); the
+  // cost of a round has a height-independent part (pipeline fill, accumulator drain) of about 24 rows.
+  int rows = kBlockX;
+  if (!b_mn) {
+    static const bool fixed_height = std::getenv("B200Q_GEMM_SWAP_128") != nullptr;  // comparison switch
+    double best = 1e30;
+    for (int r = kBlockX; r >= 32 && !fixed_height; r -= 8) {
+      const int64_t tiles = ((g.N + r - 1) / r) * tp.y_tiles;
+      const double cost = (double)((tiles + kNumSMs - 1) / kNumSMs) * (r + 24);
+      if (cost < best) { best = cost; rows = r; }
+    }
+  }
+  tp.x_tile_rows = rows;
+  tp.x_tiles = (int)((g.N + rows - 1) / rows);
+  int rc = make_map(&mx, g.B, g.N, g.K, g.ldb, b_mn, rows);
   if (rc) return rc;
   rc = make_operand_map(&my, g.A, g.M, g.K, g.lda, bn);
   if (rc) return rc;

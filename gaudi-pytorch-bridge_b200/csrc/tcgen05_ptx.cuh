@@ -28,20 +28,6 @@ __device__ __forceinline__ void mbar_arrive_expect_tx(uint32_t bar, uint32_t byt
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
-// Non-blocking probe of a phase (test_wait never suspends the thread).
-__device__ __forceinline__ uint32_t mbar_test_wait(uint32_t bar, uint32_t parity) {
-  uint32_t ok;
-  asm volatile(
-      "{\n"
-      ".reg .pred p;\n"
-      "mbarrier.test_wait.parity.shared::cta.b64 p, [%1], %2;\n"
-      "selp.u32 %0, 1, 0, p;\n"
-      "}\n"
-      : "=r"(ok)
-      : "r"(bar), "r"(parity)
-      : "memory");
-  return ok;
-}
 __device__ __forceinline__ uint32_t mbar_try_wait(uint32_t bar, uint32_t parity) {
   uint32_t ok;
   asm volatile(
@@ -94,11 +80,7 @@ constexpr uint32_t kWaitLimit = 1u << 24;
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int* status,
                                           int code, uint32_t backoff_ns = 0, uint32_t limit = kWaitLimit) {
   for (uint32_t i = 0; i < limit; ++i) {
-#ifdef B200Q_SPIN_TEST_WAIT
-    if (mbar_test_wait(bar, parity)) return true;
-#else
     if (mbar_try_wait(bar, parity)) return true;
-#endif
     if (backoff_ns) __nanosleep(backoff_ns);
     if ((i & 255u) == 255u) {
       if (*abort_flag) return false;

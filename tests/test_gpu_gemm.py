@@ -238,6 +238,42 @@ def test_tcgen05_small_m_decode_shapes(ops, M):
            torch.randn(M, N, generator=g), True, [1, N], tol=1e-5)
 
 
+@pytest.mark.parametrize("M", [1, 5, 8, 9, 16])
+@pytest.mark.parametrize("N,K", [(8, 128), (100, 1024), (1000, 2176), (1792, 4096), (264, 6272), (520, 14336)])
+def test_few_token_shapes(ops, M, N, K):
+    """M <= 16 against K-major weights: the tile kernel with the weights on the lanes, in tiles of
+    32..128 weight rows chosen so that the tile count fits the SMs (N < 128 takes the generic
+    kernel); N need not be a multiple of the tile height or of 8."""
+    g = torch.Generator().manual_seed(M * 7 + N)
+    fa, fb = FP8[(M + N) % 2], FP8[(M // 2 + K // 128) % 2]
+    A = _rand_fp8((M, K), fa, g)
+    B = _rand_fp8((N, K), fb, g, -0.25, 0.25)
+    col = torch.rand(N, generator=g) + 0.5
+    bias = torch.randn(N, generator=g).to(torch.bfloat16)
+    _check(A, False, B, True, None, torch.bfloat16, torch.tensor(0.5), col, bias, False, [1, N])
+    D = torch.randn(M, N, generator=g)
+    _check(A, False, B, True, D, torch.float32, torch.rand(M, 1, generator=g) + 0.5, col, None, True, [1, N], tol=1e-5)
+    # exact small integers: every product and sum is representable, so any misplaced k or row shows
+    Ai = ((torch.arange(M).reshape(M, 1) * 3 + torch.arange(K).reshape(1, K)) % 5).float()
+    Bi = ((torch.arange(N).reshape(N, 1) % 7) + (torch.arange(K).reshape(1, K) % 3)).float()
+    r = torch.ops.hpu.fp8_gemm_v2(Ai.to(FP8[1]).cuda(), False, Bi.to(FP8[1]).cuda(), True, None, torch.float32)
+    assert torch.equal(r.cpu(), Ai @ Bi.t())
+
+
+@pytest.mark.parametrize("M", [1, 16, 128])
+def test_decode_shapes_full_width(ops, M):
+    """The benchmark's decode shape (14336 weight rows, K = 4096: 104-row tiles) and one whose
+    tiles take two rounds (28672 rows)."""
+    g = torch.Generator().manual_seed(40 + M)
+    for N in (14336, 28672):
+        K = 4096 if N == 14336 else 1024
+        A = _rand_fp8((M, K), FP8[1], g)
+        B = _rand_fp8((N, K), FP8[1], g, -0.25, 0.25)
+        col = torch.rand(N, generator=g) + 0.5
+        bias = torch.randn(N, generator=g).to(torch.bfloat16)
+        _check(A, False, B, True, None, torch.bfloat16, torch.tensor(0.5), col, bias, False, [1, N])
+
+
 def test_tcgen05_batch_folds_into_m(ops):
     g = torch.Generator().manual_seed(23)
     A = _rand_fp8((3, 5, 64, 128), torch.float8_e4m3fn, g)
