@@ -50,11 +50,15 @@ struct TcGemmParams {
   int no_probe;                // 1 = the MMA issuer ignores its look-ahead barrier probe (for comparison)
 };
 
-template <int BN, int STAGES>
+// KPS = k-blocks per ring stage.  A stage is KPS sub-stages [X tile][Y tile] of one k-block each;
+// the barrier handshake (full / empty) is per stage.
+template <int BN, int STAGES, int KPS = 1>
 struct SmemLayout {
   static constexpr int kXBytes = kBlockX * kBlockK;
   static constexpr int kYBytes = BN * kBlockK;
-  static constexpr int kStageBytes = kXBytes + kYBytes;
+  static constexpr int kSubBytes = kXBytes + kYBytes;
+  static constexpr int kStageBytes = KPS * kSubBytes;
+  static_assert(kSubBytes % 1024 == 0, "swizzled tiles need 1024-byte alignment");
   static constexpr int kRing = STAGES * kStageBytes;
   static constexpr int kEpiFloats = 2 * 3 * BN;  // per accumulator: col scale A, col scale B, col bias
   static constexpr int kBarOffset = kRing + kEpiFloats * 4;
@@ -378,11 +382,11 @@ __device__ __forceinline__ void epi_drain_swiglu(const GemmParams& g, uint32_t t
   }
 }
 
-template <int BN, int STAGES, bool SWAP>
+template <int BN, int STAGES, bool SWAP, int KPS = 1>
 __global__ void __launch_bounds__(kThreads, 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_constant__ CUtensorMap map_y,
                     const TcGemmParams p) {
-  using L = SmemLayout<BN, STAGES>;
+  using L = SmemLayout<BN, STAGES, KPS>;
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   // dynamic shared memory is only guaranteed 16-byte aligned: round up to the swizzle atom
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -434,27 +438,34 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
       bool ok = true;
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
         const int xt = tile % p.x_tiles, yt = tile / p.x_tiles;
-        for (int kb = 0; kb < num_kb; ++kb) {
+        for (int kb0 = 0; kb0 < num_kb; kb0 += KPS) {
           if (!mbar_wait(bar_empty + 8 * stage, phase ^ 1, abort_flag, p.status, kErrProducer)) {
             ok = false;
             break;
           }
+          const int nsub = num_kb - kb0 < KPS ? num_kb - kb0 : KPS;
           const uint32_t full = bar_full + 8 * stage;
-          mbar_arrive_expect_tx(full, L::kStageBytes - (kBlockX - p.x_tile_rows) * kBlockK);
+          mbar_arrive_expect_tx(full, nsub * (L::kSubBytes - (kBlockX - p.x_tile_rows) * kBlockK));
           // K-major operand: box = 128 bytes of k x rows.  MN-major operand (stored [K][rows]):
           // box = 128 rows (bytes) x 128 k, one box per 128-row block; either way a 128-byte-
           // swizzled tile of the same size lands in the stage.
-          const uint32_t xs = smem_base + stage * L::kStageBytes, ys = xs + L::kXBytes;
           // (a tile shorter than 128 rows leaves the stage's other rows as they were: the MMA
           // reads them into accumulator lanes that nobody stores)
-          if (!p.x_mn) tma_load_2d(xs, &map_x, full, kb * kBlockK, xt * p.x_tile_rows);
-          else tma_load_2d(xs, &map_x, full, xt * kBlockX, kb * kBlockK);
-          if (!p.y_mn) {
-            tma_load_2d(ys, &map_y, full, kb * kBlockK, yt * BN);
-          } else {
 #pragma unroll
-            for (int b = 0; b < BN / 128; ++b)
-              tma_load_2d(ys + b * (kBlockK * 128), &map_y, full, yt * BN + b * 128, kb * kBlockK);
+          for (int j = 0; j < KPS; ++j) {
+            if (j < nsub) {
+              const int kb = kb0 + j;
+              const uint32_t xs = smem_base + stage * L::kStageBytes + j * L::kSubBytes, ys = xs + L::kXBytes;
+              if (!p.x_mn) tma_load_2d(xs, &map_x, full, kb * kBlockK, xt * p.x_tile_rows);
+              else tma_load_2d(xs, &map_x, full, xt * kBlockX, kb * kBlockK);
+              if (!p.y_mn) {
+                tma_load_2d(ys, &map_y, full, kb * kBlockK, yt * BN);
+              } else {
+#pragma unroll
+                for (int b = 0; b < BN / 128; ++b)
+                  tma_load_2d(ys + b * (kBlockK * 128), &map_y, full, yt * BN + b * 128, kb * kBlockK);
+              }
+            }
           }
           if (++stage == STAGES) { stage = 0; phase ^= 1; }
         }
@@ -482,16 +493,30 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
         if (!mbar_wait(bar_tempty + 8 * acc, acc_phase ^ 1, abort_flag, p.status, kErrMmaTmem)) break;
         tc_fence_after();
         const uint32_t d_tmem = tmem_base + acc * BN;
-        for (int kb = 0; kb < num_kb; ++kb) {
+        for (int kb0 = 0; kb0 < num_kb; kb0 += KPS) {
           if (!ready && !mbar_wait(bar_full + 8 * stage, phase, abort_flag, p.status, kErrMma)) {
             ok = false;
             break;
           }
           tc_fence_after();
-          const uint64_t xd = xd0 + (uint64_t)(stage * (uint32_t)(L::kStageBytes >> 4));
-          const uint64_t yd = yd0 + (uint64_t)(stage * (uint32_t)(L::kStageBytes >> 4));
-          // the stage's four MMAs and its commit (the stage is reusable once they have read it),
-          // with a probe of the next stage's barrier issued before and read after them
+          const int nsub = num_kb - kb0 < KPS ? num_kb - kb0 : KPS;
+          uint64_t xd = xd0 + (uint64_t)(stage * (uint32_t)(L::kStageBytes >> 4));
+          uint64_t yd = yd0 + (uint64_t)(stage * (uint32_t)(L::kStageBytes >> 4));
+          // all but the last k-block of the stage: MMAs only
+#pragma unroll
+          for (int j = 0; j + 1 < KPS; ++j) {
+            if (j + 1 < nsub) {
+              umma_f8(d_tmem, xd, yd, idesc, (kb0 + j) != 0);
+#pragma unroll
+              for (int k = 1; k < kBlockK / kUmmaK; ++k) umma_f8(d_tmem, xd + k * xstep, yd + k * ystep, idesc, 1u);
+              xd += (uint32_t)(L::kSubBytes >> 4);
+              yd += (uint32_t)(L::kSubBytes >> 4);
+            }
+          }
+          const int kb = kb0 + nsub - 1;
+          // the last k-block's four MMAs and the stage's commit (the stage is reusable once the
+          // MMAs have read it), with a probe of the next stage's barrier issued before and read
+          // after them
           const uint32_t nstage = stage + 1 == STAGES ? 0 : stage + 1;
           const uint32_t nphase = nstage == 0 ? phase ^ 1 : phase;
           static_assert(kBlockK / kUmmaK == 4, "umma_stage4_probe issues 4 MMAs");
@@ -789,13 +814,13 @@ int make_operand_map(CUtensorMap* map, const void* base, int64_t rows, int64_t k
                          CU_TENSOR_MAP_SWIZZLE_128B);
 }
 
-template <int BN, int STAGES, bool SWAP>
+template <int BN, int STAGES, bool SWAP, int KPS = 1>
 static int launch_cfg(const CUtensorMap& mx, const CUtensorMap& my, const TcGemmParams& tp, cudaStream_t st) {
-  using L = SmemLayout<BN, STAGES>;
+  using L = SmemLayout<BN, STAGES, KPS>;
   constexpr int smem = L::kTotal + 1024;  // slack for the manual 1024-byte alignment
   static_assert(smem <= 227 * 1024, "shared memory budget");
   static_assert(smem > 116 * 1024, "one CTA per SM: two CTAs must never contend for TMEM");
-  auto kern = gemm_tcgen05_kernel<BN, STAGES, SWAP>;
+  auto kern = gemm_tcgen05_kernel<BN, STAGES, SWAP, KPS>;
   static std::atomic<int> configured[kMaxDevices];
   const int dev = current_device_index();
   if (dev < 0) return B200Q_ERR_CUDA;
@@ -944,6 +969,22 @@ int gemm_tcgen05_launch(const GemmParams& g, cudaStream_t st) {
   if (rc) return rc;
   rc = make_operand_map(&my, g.A, g.M, g.K, g.lda, bn);
   if (rc) return rc;
+  // Few tokens: neither the bytes nor the MMAs set the pace here -- measured, a k-block costs a CTA
+  // 0.25-0.3 us whatever the tile height (32 or 128 rows), with one MMA or none in place of four,
+  // with or without the token tile's load, with 7 ring stages or 10 -- so the per-stage work of
+  // the two single-thread roles (barrier round trips, commit) is spread over two k-blocks
+  // (-6 % at K = 4096, -16 % at K = 14336).
+  static const bool one_kb = std::getenv("B200Q_GEMM_SWAP_KPS1") != nullptr;  // comparison switch
+  if (!b_mn && !one_kb) {
+    switch (bn) {
+      case 16:  // long K: four k-blocks per stage (measured: 27 against 30 us at K = 14336; no gain at 4096)
+        if (tp.num_kb >= 64) return launch_cfg<16, 3, true, 4>(mx, my, tp, st);
+        return launch_cfg<16, 5, true, 2>(mx, my, tp, st);
+      case 32: return launch_cfg<32, 5, true, 2>(mx, my, tp, st);
+      case 64: return launch_cfg<64, 4, true, 2>(mx, my, tp, st);
+      default: return launch_cfg<128, 3, true, 2>(mx, my, tp, st);
+    }
+  }
   switch (bn) {
     case 16: return launch_cfg<16, 10, true>(mx, my, tp, st);
     case 32: return launch_cfg<32, 9, true>(mx, my, tp, st);
