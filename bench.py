@@ -618,7 +618,8 @@ def family_record(args, dev, peaks):
     members = [("cast_rne", 1 << 24), ("cast_rne", 1 << 26), ("cast_sr", 1 << 24), ("cast_sr", 1 << 26),
                ("uncast", 1 << 24), ("uncast", 1 << 26), ("dequant", None), ("dequant_kpacked", None),
                ("gemm_m1", None), ("gemm_m16", None), ("gemm_m128", None), ("w4a16_m16", None), ("w4a16_m16_kpacked", None),
-               ("w4a16_m2048", None), ("sdpa_fp8", None), ("softmax_fp8", None), ("cast_hybrid", None)]
+               ("w4a16_m2048", None), ("sdpa_fp8", None), ("softmax_fp8", None), ("cast_hybrid", None),
+               ("conv2d_fp8", None)]
     out = {}
     for name, elems in members:
         a = argparse.Namespace(**vars(args))

@@ -6,6 +6,8 @@
 #include "common.cuh"
 #include "fp8_misc.cuh"
 
+#include <atomic>
+
 namespace b200q {
 
 // ---------------------------------------------------------------------------- softmax_fp8
@@ -439,33 +441,79 @@ int in_place_interleave_impl(void* data, int64_t n_rows, int64_t row_bytes, cuda
 // One-byte elements.  out[(n, ho, wo)][k], k = (c, i, j) over the channels [c0, c0 + cg) and the
 // kernel window, zero where the window leaves the image and for k in [cg * kh * kw, ld_out):
 // the K-major left operand of the GEMM that computes the convolution (K padded to ld_out).
+//
+// A block builds the rows of one output line (n, ho) for a chunk of channels.  It first copies
+// the input patch it needs -- chunk channels x kh image rows, each with pw zero bytes on both
+// sides, rows outside the image as zeros -- into shared memory with coalesced loads, and a
+// table k -> patch offset of (c, i, j); the gather itself then has no bounds test and no
+// division: a warp takes one output pixel at a time, its lanes consecutive 4-byte words of k
+// (a 128-byte store per warp), each byte one shared-memory load at table[k] + wo * sw.
 struct Im2colParams {
   const uint8_t* in;
   uint8_t* out;
   int64_t N, C, H, W, Ho, Wo;
   int kh, kw, sh, sw, ph, pw, dh, dw;
   int64_t c0, cg, ld_out;
+  int chunk;     // channels per block (a multiple of 4 when there is more than one chunk)
+  int chunks;    // blocks per output line
+  int wp;        // padded patch row: W + 2 * pw bytes
+  int patch_al;  // bytes reserved for the patch (+ one zero byte for the K padding), multiple of 16
 };
 
 __global__ void __launch_bounds__(256) im2col_u8_kernel(const Im2colParams p) {
-  const int64_t words_per_row = p.ld_out >> 2;  // ld_out is a multiple of 16
-  const int64_t total = p.N * p.Ho * p.Wo * words_per_row;
-  const int64_t K = p.cg * p.kh * p.kw;
-  for (int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; t < total; t += (int64_t)gridDim.x * blockDim.x) {
-    const int64_t row = t / words_per_row;
-    const int64_t k0 = (t % words_per_row) * 4;
-    const int64_t wo = row % p.Wo, ho = (row / p.Wo) % p.Ho, n = row / (p.Wo * p.Ho);
-    uint32_t word = 0;
-#pragma unroll
-    for (int b = 0; b < 4; ++b) {
-      const int64_t k = k0 + b;
-      if (k < K) {
-        const int64_t j = k % p.kw, i = (k / p.kw) % p.kh, c = p.c0 + k / (p.kw * p.kh);
-        const int64_t y = ho * p.sh - p.ph + i * p.dh, x = wo * p.sw - p.pw + j * p.dw;
-        if (y >= 0 && y < p.H && x >= 0 && x < p.W) word |= (uint32_t)p.in[((n * p.C + c) * p.H + y) * p.W + x] << (8 * b);
-      }
+  extern __shared__ __align__(16) uint8_t im2col_smem[];
+  uint8_t* patch = im2col_smem;
+  uint32_t* table = reinterpret_cast<uint32_t*>(im2col_smem + p.patch_al);
+  const int64_t line = blockIdx.x / p.chunks;  // (n, ho)
+  const int ch = (int)(blockIdx.x % p.chunks);
+  const int64_t n = line / p.Ho, ho = line % p.Ho;
+  const int cc0 = ch * p.chunk;  // first channel of the chunk, relative to c0
+  const int cn = (int)(p.cg - cc0 < p.chunk ? p.cg - cc0 : p.chunk);
+  const int win = p.kh * p.kw;
+  const int64_t K = p.cg * win;
+  const int k_begin = cc0 * win;  // a multiple of 4 (chunk % 4 == 0 unless there is one chunk)
+  const int k_real = (cc0 + cn) * win;                                   // end of the real k of this chunk
+  const int k_end = ch == p.chunks - 1 ? (int)p.ld_out : k_real;         // the last chunk also writes the padding
+  const int zero_at = cn * p.kh * p.wp;                                   // a byte that is always 0
+  // patch: [c][i][x + pw]
+  for (int r = threadIdx.x >> 5; r < cn * p.kh; r += 8) {
+    const int c = r / p.kh, i = r - c * p.kh;
+    const int64_t y = ho * p.sh - p.ph + (int64_t)i * p.dh;
+    uint8_t* dst = patch + r * p.wp;
+    const bool inside = y >= 0 && y < p.H;
+    const uint8_t* src = p.in + ((n * p.C + p.c0 + cc0 + c) * p.H + (inside ? y : 0)) * p.W;
+    for (int x = threadIdx.x & 31; x < p.wp; x += 32) {
+      const int xi = x - p.pw;
+      dst[x] = (inside && xi >= 0 && xi < p.W) ? __ldg(src + xi) : (uint8_t)0;
     }
-    reinterpret_cast<uint32_t*>(p.out)[t] = word;
+  }
+  if (threadIdx.x == 0) patch[zero_at] = 0;
+  for (int k = k_begin + threadIdx.x; k < k_end; k += 256) {
+    uint32_t off = (uint32_t)zero_at;
+    if (k < k_real && k < K) {
+      const int kl = k - k_begin;
+      const int c = kl / win, rem = kl - c * win;
+      const int i = rem / p.kw, j = rem - i * p.kw;
+      off = (uint32_t)((c * p.kh + i) * p.wp + j * p.dw);
+    }
+    table[k - k_begin] = off;
+  }
+  __syncthreads();
+  const int words = (k_end - k_begin) >> 2;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  uint8_t* out_line = p.out + (line * p.Wo) * p.ld_out + k_begin;
+  for (int wo = warp; wo < p.Wo; wo += 8) {
+    const uint8_t* base = patch + wo * p.sw;
+    uint32_t* dst = reinterpret_cast<uint32_t*>(out_line + (int64_t)wo * p.ld_out);
+    for (int w = lane; w < words; w += 32) {
+      const uint4 t = *reinterpret_cast<const uint4*>(table + 4 * w);
+      const bool pad = (int)t.x == zero_at;  // (the zero byte does not move with wo)
+      const uint32_t b0 = pad ? 0u : base[t.x];
+      const uint32_t b1 = (int)t.y == zero_at ? 0u : base[t.y];
+      const uint32_t b2 = (int)t.z == zero_at ? 0u : base[t.z];
+      const uint32_t b3 = (int)t.w == zero_at ? 0u : base[t.w];
+      __stcs(dst + w, b0 | (b1 << 8) | (b2 << 16) | (b3 << 24));
+    }
   }
 }
 
@@ -483,10 +531,31 @@ int im2col_u8_impl(const void* in, void* out, int64_t N, int64_t C, int64_t H, i
   p.c0 = c0; p.cg = cg; p.ld_out = ld_out;
   if (p.Ho <= 0 || p.Wo <= 0 || N == 0) return B200Q_OK;
   if (!in || !out) return B200Q_ERR_BAD_ARGUMENT;
-  const int64_t total = N * p.Ho * p.Wo * (ld_out >> 2);
-  int64_t blocks = (total + 255) / 256;
-  if (blocks > kNumSMs * 32) blocks = kNumSMs * 32;
-  im2col_u8_kernel<<<(int)blocks, 256, 0, st>>>(p);
+  if (W + 2 * (int64_t)pw > (1 << 20) || N * p.Ho > (1ll << 30)) return B200Q_ERR_TOO_LARGE;
+  p.wp = (int)(W + 2 * pw);
+  // channels per block: patch (chunk * kh * wp bytes) + table (4 bytes per k, + the K padding) within 96 KB
+  const int64_t budget = 96 * 1024 - 4 * (ld_out - cg * kh * kw) - 64;
+  const int64_t per_channel = (int64_t)kh * p.wp + 4ll * kh * kw;
+  int64_t chunk = cg > 0 ? cg : 1;
+  if (chunk * per_channel > budget) {
+    chunk = (budget / per_channel) & ~3ll;
+    if (chunk < 4) return B200Q_ERR_TOO_LARGE;  // a single image row of 4 channels does not fit
+  }
+  p.chunk = (int)chunk;
+  p.chunks = (int)((cg + chunk - 1) / chunk);
+  if (p.chunks < 1) p.chunks = 1;
+  if (N * p.Ho * p.chunks > 0x7FFFFFFFll) return B200Q_ERR_TOO_LARGE;
+  p.patch_al = (int)((chunk * kh * p.wp + 1 + 15) & ~15ll);
+  const int64_t table_k = chunk * kh * kw + (ld_out - cg * kh * kw);
+  const int smem = p.patch_al + (int)(4 * ((table_k + 3) & ~3ll));
+  static std::atomic<int> configured[kMaxDevices];
+  const int dev = current_device_index();
+  if (dev < 0) return B200Q_ERR_CUDA;
+  if (!configured[dev].load(std::memory_order_acquire)) {
+    B200Q_CUDA_OK(cudaFuncSetAttribute(im2col_u8_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024));
+    configured[dev].store(1, std::memory_order_release);
+  }
+  im2col_u8_kernel<<<(int)(N * p.Ho * p.chunks), 256, smem, st>>>(p);
   B200Q_LAUNCH_CHECK();
   return B200Q_OK;
 }

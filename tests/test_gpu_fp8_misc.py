@@ -206,6 +206,9 @@ def test_conv2d_fp8_reference_case(ops, scaleA, scaleB, bias, out_dtype, fp8_dty
     dict(N=2, C=32, H=17, W=19, Co=48, k=(3, 3), stride=(2, 1), padding=(1, 2), dilation=(1, 2), groups=1),
     dict(N=3, C=16, H=9, W=9, Co=24, k=(3, 1), stride=(1, 1), padding=(0, 0), dilation=(1, 1), groups=4),
     dict(N=1, C=64, H=14, W=14, Co=128, k=(1, 1), stride=(1, 1), padding=(0, 0), dilation=(1, 1), groups=1),
+    # 512 channels x 3 rows x 66 bytes do not fit one block's shared memory: two channel chunks per output line
+    dict(N=1, C=512, H=6, W=64, Co=16, k=(3, 3), stride=(1, 1), padding=(1, 1), dilation=(1, 1), groups=1),
+    dict(N=2, C=6, H=11, W=23, Co=8, k=(2, 3), stride=(1, 2), padding=(1, 0), dilation=(2, 1), groups=2),
 ])
 def test_conv2d_fp8_shapes_and_scalar_overload(ops, cfg):
     g = torch.Generator().manual_seed(cfg["C"])
