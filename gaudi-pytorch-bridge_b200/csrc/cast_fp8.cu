@@ -686,14 +686,37 @@ __global__ void __launch_bounds__(256) swiglu_cast_kernel(SwigluParams p) {
 //    every thread takes r = ceil(items / W) items and the grid is the number of 256-thread
 //    blocks that r items per thread need, ceil(items / (256 r)) <= the resident blocks; no block
 //    waits for another to retire and no thread has more than one item more than any other.
+// Resident 256-thread blocks per SM of a kernel, looked up once per kernel FUNCTION (kernels that
+// share a signature share a C++ type, so a cache per template instantiation would hand one
+// kernel's occupancy to another); the same on every B200 of a process.
+static int blocks_per_sm(const void* kernel) {
+  constexpr int kSlots = 64;
+  static std::atomic<const void*> keys[kSlots];
+  static std::atomic<int> vals[kSlots];
+  for (int i = 0; i < kSlots; ++i) {
+    const void* k = keys[i].load(std::memory_order_acquire);
+    if (k == kernel) {
+      const int v = vals[i].load(std::memory_order_acquire);
+      if (v > 0) return v;
+      break;  // another thread is filling the slot: compute it here too
+    }
+    if (k == nullptr) break;
+  }
+  int per_sm = 0;
+  if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, 256, 0) != cudaSuccess || per_sm < 1) per_sm = 4;
+  for (int i = 0; i < kSlots; ++i) {
+    const void* expected = nullptr;
+    if (keys[i].compare_exchange_strong(expected, kernel, std::memory_order_acq_rel) || expected == kernel) {
+      vals[i].store(per_sm, std::memory_order_release);
+      break;
+    }
+  }
+  return per_sm;
+}
+
 template <typename Kernel>
 static int grid_for(Kernel kernel, int64_t n_items, bool one_wave = false) {
-  static std::atomic<int> cached{0};  // per kernel instantiation; the same on every B200 of a process
-  int per_sm = cached.load(std::memory_order_relaxed);
-  if (per_sm == 0) {
-    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kernel, 256, 0) != cudaSuccess || per_sm < 1) per_sm = 4;
-    cached.store(per_sm, std::memory_order_relaxed);
-  }
+  const int per_sm = blocks_per_sm(reinterpret_cast<const void*>(kernel));
   int64_t blocks = (n_items + 255) / 256;
   const int64_t resident = (int64_t)kNumSMs * per_sm;
   if (one_wave) {

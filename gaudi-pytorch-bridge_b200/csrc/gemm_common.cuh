@@ -90,8 +90,8 @@ __device__ __forceinline__ float ld_out_typed(const void* base, int dtype, int64
                              : static_cast<const float*>(base)[idx];
 }
 
-// out = ((acc * sa) * sb) + bias + D, rounded once to the output dtype.  The operands of one
-// output element can be fetched ahead of its accumulator (epi_load) and applied later (epi_apply).
+// out = ((acc * sa) * sb) + bias + D, rounded once to the output dtype; the fetch of an
+// element's operands (epi_load) is separate from their application (epi_apply).
 struct EpiOperands {
   float sa, sb, bias, d;
 };

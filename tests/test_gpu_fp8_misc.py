@@ -87,6 +87,34 @@ def test_softmax_fp8_over_another_dimension(ops, dim):
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("cols", [24, 256, 1000, 4096])
+def test_softmax_fp8_row_kernel_branches(ops, cols):
+    """The register-resident row kernel's special paths: a negative input scale (the packed maximum
+    runs on sign-flipped inputs), an output scale that is a power of two (folded into the
+    normalisation), rows with -inf entries, and rows that are NaN as a whole (a NaN, a +inf, or
+    only -inf in the row)."""
+    g = torch.Generator().manual_seed(cols)
+    x = (torch.randn(12, cols, generator=g) * 3).to(torch.bfloat16)
+    x[1, ::3] = float("-inf")
+    x[2, 5] = float("nan")
+    x[3, 7] = float("inf")
+    x[4, :] = float("-inf")
+    for s_in, s_out in [(-0.5, 240.0), (0.25, 256.0), (-1.0, 0.5), (1.0, 1.0)]:
+        got = torch.ops.hpu.softmax_fp8(x.cuda(), -1, s_in, s_out).cpu()
+        want = O.softmax_fp8(x, -1, s_in, s_out)
+        gn, wn = got.float().isnan(), want.float().isnan()
+        assert torch.equal(gn, wn), (s_in, s_out, gn.sum(), wn.sum())
+        assert bool(gn[2].all()) and bool(gn[4].all()) and not bool(gn[0].any())
+        ok = ~gn
+        d = (got.view(torch.uint8).int() - want.view(torch.uint8).int()).abs()[ok]
+        assert int(d.max()) <= 1 and float((d > 0).float().mean()) < 0.02, (s_in, s_out)
+    gb = torch.ops.hpu.softmax_fp8(x.cuda(), -1).cpu()  # bf16 output, no scales
+    wb = O.softmax_fp8(x, -1)
+    assert torch.equal(gb.isnan(), wb.isnan())
+    assert torch.allclose(gb.float().nan_to_num(0.0), wb.float().nan_to_num(0.0), rtol=2 ** -7, atol=1e-6)
+
+
+@pytest.mark.gpu
 def test_softmax_fp8_long_rows_and_errors(ops):
     g = torch.Generator().manual_seed(3)
     x = (torch.randn(37, 4099, generator=g) * 3).to(torch.bfloat16)
