@@ -443,11 +443,12 @@ int in_place_interleave_impl(void* data, int64_t n_rows, int64_t row_bytes, cuda
 // the K-major left operand of the GEMM that computes the convolution (K padded to ld_out).
 //
 // A block builds the rows of one output line (n, ho) for a chunk of channels.  It first copies
-// the input patch it needs -- chunk channels x kh image rows, each with pw zero bytes on both
-// sides, rows outside the image as zeros -- into shared memory with coalesced loads, and a
-// table k -> patch offset of (c, i, j); the gather itself then has no bounds test and no
-// division: a warp takes one output pixel at a time, its lanes consecutive 4-byte words of k
-// (a 128-byte store per warp), each byte one shared-memory load at table[k] + wo * sw.
+// the input patch it needs -- chunk channels x kh image rows, each padded with zero bytes on both
+// sides (the left pad rounded up to 4 so that the copy runs in 32-bit words), rows outside the
+// image as zeros, plus one row of zeros for the K padding -- into shared memory, and a table
+// k -> patch offset of (c, i, j); the gather itself then has no bounds test and no division: a
+// warp takes one output pixel at a time, its lanes consecutive 4-byte words of k (a 128-byte
+// store per warp), each byte one shared-memory load at table[k] + wo * sw.
 struct Im2colParams {
   const uint8_t* in;
   uint8_t* out;
@@ -456,8 +457,9 @@ struct Im2colParams {
   int64_t c0, cg, ld_out;
   int chunk;     // channels per block (a multiple of 4 when there is more than one chunk)
   int chunks;    // blocks per output line
-  int wp;        // padded patch row: W + 2 * pw bytes
-  int patch_al;  // bytes reserved for the patch (+ one zero byte for the K padding), multiple of 16
+  int lp;        // zero bytes in front of an image row in the patch: pw rounded up to 4
+  int pitch;     // bytes of a patch row: lp + W + pw rounded up to 4
+  int patch_al;  // bytes reserved for the patch and the row of zeros, a multiple of 16
 };
 
 __global__ void __launch_bounds__(256) im2col_u8_kernel(const Im2colParams p) {
@@ -472,29 +474,40 @@ __global__ void __launch_bounds__(256) im2col_u8_kernel(const Im2colParams p) {
   const int win = p.kh * p.kw;
   const int64_t K = p.cg * win;
   const int k_begin = cc0 * win;  // a multiple of 4 (chunk % 4 == 0 unless there is one chunk)
-  const int k_real = (cc0 + cn) * win;                                   // end of the real k of this chunk
-  const int k_end = ch == p.chunks - 1 ? (int)p.ld_out : k_real;         // the last chunk also writes the padding
-  const int zero_at = cn * p.kh * p.wp;                                   // a byte that is always 0
-  // patch: [c][i][x + pw]
-  for (int r = threadIdx.x >> 5; r < cn * p.kh; r += 8) {
+  const int k_real = (cc0 + cn) * win;                            // end of the real k of this chunk
+  const int k_end = ch == p.chunks - 1 ? (int)p.ld_out : k_real;  // the last chunk also writes the padding
+  const int zero_at = cn * p.kh * p.pitch;                         // a row of zeros
+  // patch: [c][i][lp + x], 16 threads per row, 32-bit words
+  const int wpr = p.pitch >> 2;
+  const bool words_ok = (p.W & 3) == 0 && (reinterpret_cast<uintptr_t>(p.in) & 3) == 0;
+  for (int r = threadIdx.x >> 4; r <= cn * p.kh; r += 16) {  // (the row cn * kh is the row of zeros)
     const int c = r / p.kh, i = r - c * p.kh;
     const int64_t y = ho * p.sh - p.ph + (int64_t)i * p.dh;
-    uint8_t* dst = patch + r * p.wp;
-    const bool inside = y >= 0 && y < p.H;
-    const uint8_t* src = p.in + ((n * p.C + p.c0 + cc0 + c) * p.H + (inside ? y : 0)) * p.W;
-    for (int x = threadIdx.x & 31; x < p.wp; x += 32) {
-      const int xi = x - p.pw;
-      dst[x] = (inside && xi >= 0 && xi < p.W) ? __ldg(src + xi) : (uint8_t)0;
+    const bool inside = r < cn * p.kh && y >= 0 && y < p.H;
+    const uint8_t* src = p.in + ((n * p.C + p.c0 + cc0 + (inside ? c : 0)) * p.H + (inside ? y : 0)) * p.W;
+    uint32_t* dst = reinterpret_cast<uint32_t*>(patch + r * p.pitch);
+    for (int c4 = threadIdx.x & 15; c4 < wpr; c4 += 16) {
+      const int x0 = 4 * c4 - p.lp;  // image column of the word's first byte
+      uint32_t word = 0;
+      if (inside) {
+        if (words_ok && x0 >= 0 && x0 + 4 <= p.W) {
+          word = __ldg(reinterpret_cast<const uint32_t*>(src + x0));
+        } else {
+#pragma unroll
+          for (int b = 0; b < 4; ++b)
+            if (x0 + b >= 0 && x0 + b < p.W) word |= (uint32_t)__ldg(src + x0 + b) << (8 * b);
+        }
+      }
+      dst[c4] = word;
     }
   }
-  if (threadIdx.x == 0) patch[zero_at] = 0;
   for (int k = k_begin + threadIdx.x; k < k_end; k += 256) {
     uint32_t off = (uint32_t)zero_at;
     if (k < k_real && k < K) {
       const int kl = k - k_begin;
       const int c = kl / win, rem = kl - c * win;
       const int i = rem / p.kw, j = rem - i * p.kw;
-      off = (uint32_t)((c * p.kh + i) * p.wp + j * p.dw);
+      off = (uint32_t)((c * p.kh + i) * p.pitch + (p.lp - p.pw) + j * p.dw);
     }
     table[k - k_begin] = off;
   }
@@ -503,16 +516,12 @@ __global__ void __launch_bounds__(256) im2col_u8_kernel(const Im2colParams p) {
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   uint8_t* out_line = p.out + (line * p.Wo) * p.ld_out + k_begin;
   for (int wo = warp; wo < p.Wo; wo += 8) {
-    const uint8_t* base = patch + wo * p.sw;
+    const uint8_t* base = patch + wo * p.sw;  // (an offset into the row of zeros stays inside it: wo * sw < pitch)
     uint32_t* dst = reinterpret_cast<uint32_t*>(out_line + (int64_t)wo * p.ld_out);
     for (int w = lane; w < words; w += 32) {
       const uint4 t = *reinterpret_cast<const uint4*>(table + 4 * w);
-      const bool pad = (int)t.x == zero_at;  // (the zero byte does not move with wo)
-      const uint32_t b0 = pad ? 0u : base[t.x];
-      const uint32_t b1 = (int)t.y == zero_at ? 0u : base[t.y];
-      const uint32_t b2 = (int)t.z == zero_at ? 0u : base[t.z];
-      const uint32_t b3 = (int)t.w == zero_at ? 0u : base[t.w];
-      __stcs(dst + w, b0 | (b1 << 8) | (b2 << 16) | (b3 << 24));
+      const uint32_t b0 = base[t.x], b1 = base[t.y], b2 = base[t.z], b3 = base[t.w];
+      __stcs(dst + w, __byte_perm(b0 | (b1 << 8), b2 | (b3 << 8), 0x5410));
     }
   }
 }
@@ -532,20 +541,30 @@ int im2col_u8_impl(const void* in, void* out, int64_t N, int64_t C, int64_t H, i
   if (p.Ho <= 0 || p.Wo <= 0 || N == 0) return B200Q_OK;
   if (!in || !out) return B200Q_ERR_BAD_ARGUMENT;
   if (W + 2 * (int64_t)pw > (1 << 20) || N * p.Ho > (1ll << 30)) return B200Q_ERR_TOO_LARGE;
-  p.wp = (int)(W + 2 * pw);
-  // channels per block: patch (chunk * kh * wp bytes) + table (4 bytes per k, + the K padding) within 96 KB
-  const int64_t budget = 96 * 1024 - 4 * (ld_out - cg * kh * kw) - 64;
-  const int64_t per_channel = (int64_t)kh * p.wp + 4ll * kh * kw;
+  p.lp = (pw + 3) & ~3;
+  // patch row pitch: an ODD number of 32-bit words, so that the rows (c, i) that the lanes of a warp
+  // gather from at one column fall into different banks (a pitch of 64 bytes put every second row
+  // on the same banks: 110 M conflicts on the benchmark's case against 9 M)
+  p.pitch = (int)((((p.lp + W + pw + 3) >> 2) | 1) << 2);
+  // channels per block: patch (chunk * kh rows + the row of zeros) + table (4 bytes per k, + the K
+  // padding) within about 40 KB, so that five blocks share an SM and the grid has several times
+  // as many blocks as the machine holds at once (the last wave costs little); equal chunks
+  const int64_t pad_k = ld_out - cg * kh * kw;
+  const int64_t per_channel = (int64_t)kh * p.pitch + 4ll * kh * kw;
+  int64_t budget = 40 * 1024 - 4 * pad_k - p.pitch - 64;
+  if (budget < 4 * per_channel) budget = 96 * 1024 - 4 * pad_k - p.pitch - 64;  // wide images: one block per SM or two
   int64_t chunk = cg > 0 ? cg : 1;
   if (chunk * per_channel > budget) {
-    chunk = (budget / per_channel) & ~3ll;
-    if (chunk < 4) return B200Q_ERR_TOO_LARGE;  // a single image row of 4 channels does not fit
+    const int64_t most = (budget / per_channel) & ~3ll;
+    if (most < 4) return B200Q_ERR_TOO_LARGE;  // the image rows of 4 channels do not fit
+    const int64_t parts = (cg + most - 1) / most;
+    chunk = ((cg + parts - 1) / parts + 3) & ~3ll;
   }
   p.chunk = (int)chunk;
   p.chunks = (int)((cg + chunk - 1) / chunk);
   if (p.chunks < 1) p.chunks = 1;
   if (N * p.Ho * p.chunks > 0x7FFFFFFFll) return B200Q_ERR_TOO_LARGE;
-  p.patch_al = (int)((chunk * kh * p.wp + 1 + 15) & ~15ll);
+  p.patch_al = (int)(((chunk * kh + 1) * p.pitch + 15) & ~15ll);
   const int64_t table_k = chunk * kh * kw + (ld_out - cg * kh * kw);
   const int smem = p.patch_al + (int)(4 * ((table_k + 3) & ~3ll));
   static std::atomic<int> configured[kMaxDevices];
