@@ -427,6 +427,12 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  // Launched with programmatic stream serialization (few-token form): everything above overlaps the
+  // tail of the kernel before this one in the stream; nothing below may start before that kernel
+  // and its writes are complete.  The kernel after this one may be set up as soon as every CTA
+  // of this one has got here.  (Both are no-ops in an ordinary launch.)
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
 
   const int num_tiles = p.x_tiles * p.y_tiles;
   const int num_kb = p.num_kb;
@@ -830,6 +836,24 @@ static int launch_cfg(const CUtensorMap& mx, const CUtensorMap& my, const TcGemm
   }
   int tiles = tp.x_tiles * tp.y_tiles;
   int grid = tiles < kNumSMs ? tiles : kNumSMs;
+  static const bool no_pdl = std::getenv("B200Q_GEMM_NO_PDL") != nullptr;  // comparison switch
+  if (SWAP && !no_pdl) {
+    // a few tokens: the kernel lasts 10-20 us and a launch gap of 2-3 us between two of them counts;
+    // let this one be set up (barriers, TMEM, descriptors) under the tail of its predecessor
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3((unsigned)grid);
+    cfg.blockDim = dim3(kThreads);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = st;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    B200Q_CUDA_OK(cudaLaunchKernelEx(&cfg, kern, mx, my, tp));
+    count_launch();
+    return B200Q_OK;
+  }
   kern<<<grid, kThreads, smem, st>>>(mx, my, tp);
   B200Q_LAUNCH_CHECK();
   return B200Q_OK;
