@@ -230,14 +230,27 @@ __global__ void __cluster_dims__(kCluster, 1, 1) __launch_bounds__(kThreads, 1) 
   int to_next_group = steps_per_group - (int)((k_begin % p.group) / kStepRows) + 1;
   if (KP == 0) {
     uint32_t sp[4], zr[4];  // {s_i, s_{i+4}}, {128 + z_i, 128 + z_{i+4}} of the thread's word column
-    auto load_group = [&](int64_t grp) {
-      const uint4 sv = __ldg(reinterpret_cast<const uint4*>(p.scale + grp * p.N + n0 + 8 * g));
+    // The scales and zero points of a group are fetched one group ahead: a load that is consumed at
+    // once comes back behind the cp.async traffic this warp has queued, i.e. after a full memory
+    // latency, once per group.
+    uint4 nsv;
+    uint32_t nz;
+    const int64_t last_grp = (p.K - 1) / p.group;
+    auto fetch_group = [&](int64_t grp) {
+      if (grp > last_grp) grp = last_grp;  // (never used then)
+      nsv = __ldg(reinterpret_cast<const uint4*>(p.scale + grp * p.N + n0 + 8 * g));
+      nz = p.zp ? (uint32_t)__ldg(p.zp + grp * (p.N / 8) + n0 / 8 + g) : 0u;
+    };
+    auto load_group = [&](int64_t grp) {  // takes what fetch_group(grp) asked for, asks for grp + 1
+      const uint4 sv = nsv;
+      const uint32_t z = nz;
+      fetch_group(grp + 1);
       sp[0] = __byte_perm(sv.x, sv.z, 0x5410); sp[1] = __byte_perm(sv.x, sv.z, 0x7632);
       sp[2] = __byte_perm(sv.y, sv.w, 0x5410); sp[3] = __byte_perm(sv.y, sv.w, 0x7632);
-      const uint32_t z = p.zp ? (uint32_t)__ldg(p.zp + grp * (p.N / 8) + n0 / 8 + g) : 0u;
 #pragma unroll
       for (int i = 0; i < 4; ++i) zr[i] = nib_pair(z, i);
     };
+    fetch_group(cur_grp);
     load_group(cur_grp);  // before the first wait: its latency hides under the weights'
     for (int s = 0; s < steps; ++s) {
       const int rest = steps - 1 - s;
