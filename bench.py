@@ -316,6 +316,7 @@ def build_workload(wl, args, dev, rank, world, peaks):
                                                        abi.BCAST_SCALAR_HOST, None, 8.0, abi.BCAST_SCALAR_HOST, n, abi.ptr(amax),
                                                        abi.ROUND_RNE, 1234, 0, 0, 0, abi.stream_ptr()))
         w.step = step
+        w.launches_per_step = 2  # the kernel that clears amax + the cast
         hbm_bound(4 * n)
         w.metric = "cast_to_fp8_hybrid (e5m2 + e4m3, RNE, amax) GB/s"
         w.workload = f"cast_to_fp8_hybrid on {n} bf16 elements ~N(0,1)"
@@ -447,6 +448,7 @@ def build_workload(wl, args, dev, rank, world, peaks):
                 abi.check(abi.lib.b200q_cast_to_fp8(abi.ptr(xs[j]), abi.BF16, abi.ptr(x8s[j]), abi.DTYPE[fp8], None, scale,
                                                     abi.BCAST_SCALAR_HOST, 1, n, abi.ptr(amax), rnd, 1234, i, 0, 0, abi.stream_ptr()))
         w.step = step
+        w.launches_per_step = 1 if wl == "uncast" else 2  # casts with amax: the kernel that clears it + the cast
         hbm_bound(3 * n)
         w.metric = {"cast_rne": "cast_to_fp8_v2 (e4m3, RNE, amax) GB/s", "cast_sr": "cast_to_fp8_v2 (e5m2, stochastic, amax) GB/s",
                     "uncast": "cast_from_fp8 (to bf16) GB/s"}[wl]

@@ -32,6 +32,36 @@ inline void count_launch() { g_launches.fetch_add(1, std::memory_order_relaxed);
     if (e__ != cudaSuccess) return ::b200q::record_cuda_error(e__, "launch"); \
   } while (0)
 
+// Programmatic dependent launch.  A kernel launched with launch_overlapped() may be set up and
+// start running before the kernel in front of it in the stream has finished; it must call
+// pdl_enter() before its first access to global memory (the call returns once that kernel
+// and its writes are complete), and everything before the call -- block scheduling, barrier and
+// tensor-memory set-up, descriptor prefetch -- overlaps the predecessor's tail.  pdl_enter() also
+// lets the successor be set up early in the same way.  Both parts are no-ops in an ordinary
+// launch.  Between two kernels of 10-30 us this takes 1.5-2.5 us of launch gap away.
+#ifdef __CUDACC__
+__device__ __forceinline__ void pdl_enter() {
+  asm volatile("griddepcontrol.wait;" ::: "memory");
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+
+template <typename... KArgs, typename... Args>
+inline cudaError_t launch_overlapped(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st,
+                                     Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
+}
+#endif
+
 // Per-device one-time setup helper: `slot` is a static array of kMaxDevices ints owned by the
 // caller (0 = not yet done on that device).  Returns the current device index or -1.
 constexpr int kMaxDevices = 64;
@@ -175,7 +205,12 @@ __device__ __forceinline__ void block_amax_to_global(uint32_t local_bits, float*
     int nw = (blockDim.x + 31) >> 5;
     uint32_t v = lane < nw ? s_warp[lane] : 0u;
     v = warp_max_u32(v);
-    if (lane == 0 && v != 0u) atomicMax(reinterpret_cast<unsigned int*>(amax), v);
+    if (lane == 0 && v != 0u) {
+      // (a kernel launched with programmatic stream serialization behind the kernel that clears
+      // `amax` must not touch it before that kernel is complete; a no-op in an ordinary launch)
+      asm volatile("griddepcontrol.wait;" ::: "memory");
+      atomicMax(reinterpret_cast<unsigned int*>(amax), v);
+    }
   }
 }
 

@@ -158,6 +158,7 @@ constexpr int kFastRows = 16;
 // of each of kFastRows consecutive rows (all loads issued before the first use).
 template <bool SIGNED>
 __global__ void __launch_bounds__(256) dequant_rowpacked_bf16_kernel(DequantParams p) {
+  pdl_enter();
   const int64_t bx = blockIdx.x % p.col_blocks, by = blockIdx.x / p.col_blocks;
   const int64_t cp = bx * blockDim.x + threadIdx.x;
   if (cp >= p.cols_packed) return;
@@ -203,6 +204,7 @@ constexpr int kRowsPerBlock = 8;
 // Operator layout: packed [rows][cols_packed] -> out [rows][8*cols_packed].
 template <typename T, bool SIGNED>
 __global__ void __launch_bounds__(256) dequant_rowpacked_kernel(DequantParams p) {
+  pdl_enter();
   const int64_t bx = blockIdx.x % p.col_blocks, by = blockIdx.x / p.col_blocks;
   const int64_t cp = bx * blockDim.x + threadIdx.x;
   if (cp >= p.cols_packed) return;
@@ -243,6 +245,7 @@ __global__ void __launch_bounds__(256) dequant_rowpacked_kernel(DequantParams p)
 // One thread takes 8 consecutive words of a packed row -> an 8x8 block of the output.
 template <typename T, bool SIGNED>
 __global__ void __launch_bounds__(256) dequant_kpacked_kernel(DequantParams p) {
+  pdl_enter();
   const int64_t cols = p.cols_packed;  // carries the number of columns in this layout
   const int64_t c8 = (blockIdx.x % p.col_blocks) * blockDim.x + threadIdx.x;  // block of 8 columns
   const int64_t pr = blockIdx.x / p.col_blocks;
@@ -280,6 +283,14 @@ __global__ void __launch_bounds__(256) dequant_kpacked_kernel(DequantParams p) {
   }
 }
 
+// every dequantisation kernel calls pdl_enter() first: it may be launched under its predecessor's tail
+template <typename Kernel, typename Params>
+static void launch_or_fallback(Kernel kernel, dim3 grid, cudaStream_t st, const Params& p) {
+  if (launch_overlapped(kernel, grid, dim3(256), 0, st, p) == cudaSuccess) return;
+  (void)cudaGetLastError();
+  kernel<<<grid, 256, 0, st>>>(p);
+}
+
 int dequant_int4_impl(const int32_t* packed, const void* scale, const void* zp, int zp_kind, int is_signed,
                       int out_dtype, void* out, int64_t rows, int64_t cols_packed, int64_t scale_rows, int k_packed,
                       cudaStream_t st) {
@@ -294,19 +305,19 @@ int dequant_int4_impl(const int32_t* packed, const void* scale, const void* zp, 
     p.col_blocks = (cols_packed + 255) / 256;
     const int64_t nblk = p.col_blocks * ((rows + kFastRows - 1) / kFastRows);
     if (nblk > 0x7FFFFFFFll) return B200Q_ERR_TOO_LARGE;
-    if (is_signed) dequant_rowpacked_bf16_kernel<true><<<(unsigned)nblk, 256, 0, st>>>(p);
-    else dequant_rowpacked_bf16_kernel<false><<<(unsigned)nblk, 256, 0, st>>>(p);
+    if (is_signed) launch_or_fallback(dequant_rowpacked_bf16_kernel<true>, dim3((unsigned)nblk), st, p);
+    else launch_or_fallback(dequant_rowpacked_bf16_kernel<false>, dim3((unsigned)nblk), st, p);
   } else if (!k_packed) {
     p.col_blocks = (cols_packed + 255) / 256;
     const int64_t nblk = p.col_blocks * ((rows + kRowsPerBlock - 1) / kRowsPerBlock);
     if (nblk > 0x7FFFFFFFll) return B200Q_ERR_TOO_LARGE;
     const unsigned grid = (unsigned)nblk;
     if (out_dtype == B200Q_BF16) {
-      if (is_signed) dequant_rowpacked_kernel<__nv_bfloat16, true><<<grid, 256, 0, st>>>(p);
-      else dequant_rowpacked_kernel<__nv_bfloat16, false><<<grid, 256, 0, st>>>(p);
+      if (is_signed) launch_or_fallback(dequant_rowpacked_kernel<__nv_bfloat16, true>, dim3(grid), st, p);
+      else launch_or_fallback(dequant_rowpacked_kernel<__nv_bfloat16, false>, dim3(grid), st, p);
     } else {
-      if (is_signed) dequant_rowpacked_kernel<float, true><<<grid, 256, 0, st>>>(p);
-      else dequant_rowpacked_kernel<float, false><<<grid, 256, 0, st>>>(p);
+      if (is_signed) launch_or_fallback(dequant_rowpacked_kernel<float, true>, dim3(grid), st, p);
+      else launch_or_fallback(dequant_rowpacked_kernel<float, false>, dim3(grid), st, p);
     }
   } else {
     if (rows % 8 || cols_packed % 8 || p.group_rows % 8 || zp_kind == B200Q_ZP_FLOAT) return B200Q_ERR_UNSUPPORTED;
@@ -315,11 +326,11 @@ int dequant_int4_impl(const int32_t* packed, const void* scale, const void* zp, 
     if (nblk > 0x7FFFFFFFll) return B200Q_ERR_TOO_LARGE;
     const unsigned grid = (unsigned)nblk;
     if (out_dtype == B200Q_BF16) {
-      if (is_signed) dequant_kpacked_kernel<__nv_bfloat16, true><<<grid, 256, 0, st>>>(p);
-      else dequant_kpacked_kernel<__nv_bfloat16, false><<<grid, 256, 0, st>>>(p);
+      if (is_signed) launch_or_fallback(dequant_kpacked_kernel<__nv_bfloat16, true>, dim3(grid), st, p);
+      else launch_or_fallback(dequant_kpacked_kernel<__nv_bfloat16, false>, dim3(grid), st, p);
     } else {
-      if (is_signed) dequant_kpacked_kernel<float, true><<<grid, 256, 0, st>>>(p);
-      else dequant_kpacked_kernel<float, false><<<grid, 256, 0, st>>>(p);
+      if (is_signed) launch_or_fallback(dequant_kpacked_kernel<float, true>, dim3(grid), st, p);
+      else launch_or_fallback(dequant_kpacked_kernel<float, false>, dim3(grid), st, p);
     }
   }
   B200Q_LAUNCH_CHECK();

@@ -24,6 +24,7 @@ __device__ __forceinline__ float ld_softmax_in(const SoftmaxParams& p, int64_t i
 }
 
 __global__ void __launch_bounds__(256) softmax_fp8_kernel(const SoftmaxParams p) {
+  pdl_enter();
   const int lane = threadIdx.x & 31;
   const int64_t row = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (row >= p.rows) return;
@@ -103,6 +104,7 @@ __device__ __forceinline__ uint32_t max_bf16x2(uint32_t a, uint32_t b) {
 
 template <int NV, bool FA>
 __global__ void __launch_bounds__(128) softmax_bf16_rowreg_kernel(const SoftmaxParams p) {
+  pdl_enter();
   const int lane = threadIdx.x & 31;
   const int64_t row = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   if (row >= p.rows) return;
@@ -237,8 +239,11 @@ static int launch_softmax_rowreg(const SoftmaxParams& p, cudaStream_t st) {
   const int warps = 4;
   const int64_t blocks = (p.rows + warps - 1) / warps;
   if (blocks > 0x7FFFFFFF) return B200Q_ERR_TOO_LARGE;
-  if (p.fused_add) softmax_bf16_rowreg_kernel<NV, true><<<(int)blocks, warps * 32, 0, st>>>(p);
-  else softmax_bf16_rowreg_kernel<NV, false><<<(int)blocks, warps * 32, 0, st>>>(p);
+  auto kern = p.fused_add ? softmax_bf16_rowreg_kernel<NV, true> : softmax_bf16_rowreg_kernel<NV, false>;
+  if (launch_overlapped(kern, dim3((unsigned)blocks), dim3(warps * 32), 0, st, p) != cudaSuccess) {  // (it calls pdl_enter())
+    (void)cudaGetLastError();
+    kern<<<(int)blocks, warps * 32, 0, st>>>(p);
+  }
   B200Q_LAUNCH_CHECK();
   return B200Q_OK;
 }
@@ -263,7 +268,10 @@ int softmax_fp8_impl(const SoftmaxParams& p, cudaStream_t st) {
   const int warps = 8;
   const int64_t blocks = (p.rows + warps - 1) / warps;
   if (blocks > 0x7FFFFFFF) return B200Q_ERR_TOO_LARGE;
-  softmax_fp8_kernel<<<(int)blocks, warps * 32, 0, st>>>(p);
+  if (launch_overlapped(softmax_fp8_kernel, dim3((unsigned)blocks), dim3(warps * 32), 0, st, p) != cudaSuccess) {
+    (void)cudaGetLastError();
+    softmax_fp8_kernel<<<(int)blocks, warps * 32, 0, st>>>(p);
+  }
   B200Q_LAUNCH_CHECK();
   return B200Q_OK;
 }

@@ -427,12 +427,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  // Launched with programmatic stream serialization (few-token form): everything above overlaps the
-  // tail of the kernel before this one in the stream; nothing below may start before that kernel
-  // and its writes are complete.  The kernel after this one may be set up as soon as every CTA
-  // of this one has got here.  (Both are no-ops in an ordinary launch.)
-  asm volatile("griddepcontrol.wait;" ::: "memory");
-  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+  pdl_enter();  // everything above may run under the tail of the kernel in front of this one
 
   const int num_tiles = p.x_tiles * p.y_tiles;
   const int num_kb = p.num_kb;
@@ -658,6 +653,7 @@ gemm_tcgen05_pair_kernel(const __grid_constant__ CUtensorMap map_x, const __grid
   cluster_sync_all();  // both CTAs' barriers are initialised before anything signals them remotely
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  pdl_enter();  // everything above may run under the tail of the kernel in front of this one
 
   const int pair = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
   const int num_tiles = p.x_tiles * p.y_tiles;  // x_tiles counts 256-row tiles here
@@ -807,7 +803,11 @@ static int launch_pair(const CUtensorMap& mx, const CUtensorMap& my, const TcGem
   if (clusters < 0) return B200Q_ERR_UNSUPPORTED;
   int tiles = tp.x_tiles * tp.y_tiles;
   int pairs = tiles < clusters ? tiles : clusters;
-  kern<<<2 * pairs, kThreads, smem, st>>>(mx, my, tp);
+  static const bool no_pdl = std::getenv("B200Q_GEMM_NO_PDL") != nullptr;  // comparison switch
+  if (no_pdl || launch_overlapped(kern, dim3((unsigned)(2 * pairs)), dim3(kThreads), smem, st, mx, my, tp) != cudaSuccess) {
+    if (!no_pdl) (void)cudaGetLastError();
+    kern<<<2 * pairs, kThreads, smem, st>>>(mx, my, tp);
+  }
   B200Q_LAUNCH_CHECK();
   return B200Q_OK;
 }
@@ -836,25 +836,13 @@ static int launch_cfg(const CUtensorMap& mx, const CUtensorMap& my, const TcGemm
   }
   int tiles = tp.x_tiles * tp.y_tiles;
   int grid = tiles < kNumSMs ? tiles : kNumSMs;
+  // the kernel's set-up (barriers, TMEM, descriptors) may run under the tail of its predecessor: with a few
+  // tokens it lasts 10-20 us and a launch gap of 2-3 us between two of them counts
   static const bool no_pdl = std::getenv("B200Q_GEMM_NO_PDL") != nullptr;  // comparison switch
-  if (SWAP && !no_pdl) {
-    // a few tokens: the kernel lasts 10-20 us and a launch gap of 2-3 us between two of them counts;
-    // let this one be set up (barriers, TMEM, descriptors) under the tail of its predecessor
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3((unsigned)grid);
-    cfg.blockDim = dim3(kThreads);
-    cfg.dynamicSmemBytes = smem;
-    cfg.stream = st;
-    cudaLaunchAttribute attr[1];
-    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[0].val.programmaticStreamSerializationAllowed = 1;
-    cfg.attrs = attr;
-    cfg.numAttrs = 1;
-    B200Q_CUDA_OK(cudaLaunchKernelEx(&cfg, kern, mx, my, tp));
-    count_launch();
-    return B200Q_OK;
+  if (no_pdl || launch_overlapped(kern, dim3((unsigned)grid), dim3(kThreads), smem, st, mx, my, tp) != cudaSuccess) {
+    if (!no_pdl) (void)cudaGetLastError();
+    kern<<<grid, kThreads, smem, st>>>(mx, my, tp);
   }
-  kern<<<grid, kThreads, smem, st>>>(mx, my, tp);
   B200Q_LAUNCH_CHECK();
   return B200Q_OK;
 }

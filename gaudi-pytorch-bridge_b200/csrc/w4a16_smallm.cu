@@ -137,6 +137,7 @@ __device__ __forceinline__ float ld_cluster_f32(uint32_t local_addr, uint32_t ra
 template <int MT, int KP>
 __global__ void __cluster_dims__(kCluster, 1, 1) __launch_bounds__(kThreads, 1) w4a16_smallm_kernel(const Params p) {
   extern __shared__ __align__(16) uint8_t smem[];
+  pdl_enter();  // launched under the tail of the kernel in front of it
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, g = lane >> 2, q = lane & 3;
   const int strip = warp & (kStrips - 1), khalf = warp / kStrips;  // (khalf: the warp's k-part)
   const uint32_t crank = cluster_rank();
@@ -438,7 +439,10 @@ static int launch(const Params& p, cudaStream_t st) {
     configured[dev].store(1, std::memory_order_release);
   }
   const int grid = (int)(p.N / kCols) * kCluster;
-  kern<<<grid, kThreads, kSmemBytes, st>>>(p);
+  if (launch_overlapped(kern, dim3((unsigned)grid), dim3(kThreads), kSmemBytes, st, p) != cudaSuccess) {
+    (void)cudaGetLastError();
+    kern<<<grid, kThreads, kSmemBytes, st>>>(p);
+  }
   B200Q_LAUNCH_CHECK();
   return B200Q_OK;
 }

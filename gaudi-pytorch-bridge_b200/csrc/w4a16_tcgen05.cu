@@ -602,6 +602,7 @@ w4a16_pair_kernel(const __grid_constant__ CUtensorMap map_act, const __grid_cons
   cluster_sync_all();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  pdl_enter();  // everything above may run under the tail of the kernel in front of this one
 
   const int pair = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
   const int num_tiles = p.x_tiles * p.y_tiles;  // 256-token x 256-column tiles
@@ -835,7 +836,10 @@ static int launch_pair(const CUtensorMap& ma, const CUtensorMap& mr, const CUten
   if (clusters < 0) return B200Q_ERR_UNSUPPORTED;
   const int tiles = p.x_tiles * p.y_tiles;
   const int pairs = tiles < clusters ? tiles : clusters;
-  kern<<<2 * pairs, C::kThreads, smem, st>>>(ma, mr, ms, mz, p);
+  if (launch_overlapped(kern, dim3((unsigned)(2 * pairs)), dim3(C::kThreads), smem, st, ma, mr, ms, mz, p) != cudaSuccess) {
+    (void)cudaGetLastError();
+    kern<<<2 * pairs, C::kThreads, smem, st>>>(ma, mr, ms, mz, p);
+  }
   B200Q_LAUNCH_CHECK();
   return B200Q_OK;
 }
