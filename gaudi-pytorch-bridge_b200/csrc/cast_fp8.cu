@@ -741,7 +741,7 @@ __global__ void clear_amax_kernel(float* amax) {
   *amax = 0.f;
 }
 
-static int clear_amax(float* amax, cudaStream_t st) {
+int clear_amax(float* amax, cudaStream_t st) {
   clear_amax_kernel<<<1, 1, 0, st>>>(amax);
   B200Q_LAUNCH_CHECK();
   return B200Q_OK;

@@ -62,6 +62,11 @@ inline cudaError_t launch_overlapped(void (*kernel)(KArgs...), dim3 grid, dim3 b
 }
 #endif
 
+// Clears an amax word with a one-thread kernel behind which the kernel that accumulates into it
+// (through block_amax_to_global, which waits for the clearing kernel before its atomicMax) can be
+// launched with launch_overlapped().  Defined beside the casts.
+int clear_amax(float* amax, cudaStream_t st);
+
 // Per-device one-time setup helper: `slot` is a static array of kMaxDevices ints owned by the
 // caller (0 = not yet done on that device).  Returns the current device index or -1.
 constexpr int kMaxDevices = 64;

@@ -56,14 +56,25 @@ int amax_impl(const void* in, int in_dtype, int64_t n, float* amax, cudaStream_t
   if (!amax || n < 0 || (n > 0 && !in)) return B200Q_ERR_BAD_ARGUMENT;
   if (in_dtype != B200Q_BF16 && in_dtype != B200Q_F32) return B200Q_ERR_BAD_ARGUMENT;
   if (reinterpret_cast<uintptr_t>(in) & 15) return B200Q_ERR_UNSUPPORTED;
-  B200Q_CUDA_OK(cudaMemsetAsync(amax, 0, sizeof(float), st));
+  if (int rc = clear_amax(amax, st)) return rc;
   if (n == 0) return B200Q_OK;
   const int64_t nvec = n / (in_dtype == B200Q_BF16 ? 8 : 4);
   int64_t blocks = (nvec + 256 * 4 - 1) / (256 * 4);
   if (blocks < 1) blocks = 1;
   if (blocks > kNumSMs * 16) blocks = kNumSMs * 16;  // two rounds of 8 resident blocks per SM
-  if (in_dtype == B200Q_BF16) amax_kernel<__nv_bfloat16><<<(int)blocks, 256, 0, st>>>(static_cast<const __nv_bfloat16*>(in), n, amax);
-  else amax_kernel<float><<<(int)blocks, 256, 0, st>>>(static_cast<const float*>(in), n, amax);
+  // (the pass starts under the clearing kernel and waits for it only before its atomicMax)
+  const dim3 grid((unsigned)blocks), block(256);
+  if (in_dtype == B200Q_BF16) {
+    if (launch_overlapped(amax_kernel<__nv_bfloat16>, grid, block, 0, st, static_cast<const __nv_bfloat16*>(in), n, amax) != cudaSuccess) {
+      (void)cudaGetLastError();
+      amax_kernel<__nv_bfloat16><<<grid, block, 0, st>>>(static_cast<const __nv_bfloat16*>(in), n, amax);
+    }
+  } else {
+    if (launch_overlapped(amax_kernel<float>, grid, block, 0, st, static_cast<const float*>(in), n, amax) != cudaSuccess) {
+      (void)cudaGetLastError();
+      amax_kernel<float><<<grid, block, 0, st>>>(static_cast<const float*>(in), n, amax);
+    }
+  }
   B200Q_LAUNCH_CHECK();
   return B200Q_OK;
 }
