@@ -235,7 +235,10 @@ def build_workload(wl, args, dev, rank, world, peaks):
             def step(i):
                 j = i % len(sets)
                 s = sets[j]
-                abi.fp8_gemm_nt(s["a8"], s["b8"], torch.bfloat16, float_sa[j], s["sb_inv"], s["bias"], out=outs[j])
+                # few tokens: the weights are declared static (b200q_gemm_args.b_static), as an inference
+                # engine would: the kernel may begin to read them under the tail of the launch before it
+                abi.fp8_gemm_nt(s["a8"], s["b8"], torch.bfloat16, float_sa[j], s["sb_inv"], s["bias"], out=outs[j],
+                                b_static=(M <= 128 and not args.no_static_weights))
 
         w.step = step
         w.flops = 2.0 * M * N_ * K_
@@ -251,6 +254,8 @@ def build_workload(wl, args, dev, rank, world, peaks):
         if wl == "scaled_mm_lib":
             w.metric = "torch._scaled_mm (vendor library, context only) TFLOP/s"
         w.workload = headline_workload_name(M)
+        if M <= 128 and wl != "scaled_mm_lib" and not args.no_static_weights:
+            w.workload += "; weights declared static (b_static)"
         w.dtype = "fp8_e4m3 (fp32 accumulate)"
         w.l2 = "3 rotating operand/output sets per rank (>= 3 x working set), no flush"
 
@@ -927,6 +932,8 @@ def main():
     ap.add_argument("--steps", type=int, default=300)
     ap.add_argument("--warmup", type=int, default=10)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-static-weights", action="store_true",
+                    help="few-token GEMM workloads: do not declare the weights static (comparison)")
     ap.add_argument("--workload", default="gemm")
     ap.add_argument("--unfused-mlp", action="store_true", help="mlp workload: separate SwiGLU + cast kernel instead of the GEMM epilogue")
     ap.add_argument("--mlp-comm", default="auto", choices=["auto", "nccl", "fused"],

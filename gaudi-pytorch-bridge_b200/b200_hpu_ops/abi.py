@@ -42,7 +42,7 @@ class GemmArgs(C.Structure):
         ("out8_dtype", C.c_int), ("out8_scale", C.c_void_p), ("out8_scale_host", C.c_float),
         ("swiglu", C.c_int),
         ("route_out", C.c_void_p * 8), ("route_count", C.c_int), ("route_rows", C.c_int64), ("route_row_offset", C.c_int64),
-        ("out8_amax", C.c_void_p),
+        ("out8_amax", C.c_void_p), ("b_static", C.c_int),
     ]
 
 
@@ -183,7 +183,7 @@ def cast_from_fp8(x8, out_dtype, scale=None, scale_mode=None, rows=None, cols=No
 
 
 def fp8_gemm_nt(a8, b8, out_dtype=torch.bfloat16, a_scale=None, b_scale=None, bias=None, out=None,
-                force_generic=False, route=None):
+                force_generic=False, route=None, b_static=False):
     """out[M][N] = a8[M][K] . b8[N][K]^T with scalar (float) a_scale, per-column fp32 CUDA b_scale [N]
     (or float), optional per-column bias [N]: the projection-GEMM form, straight through the C ABI."""
     M, K = a8.shape
@@ -218,6 +218,7 @@ def fp8_gemm_nt(a8, b8, out_dtype=torch.bfloat16, a_scale=None, b_scale=None, bi
     if bias is not None:
         g.bias, g.bias_dtype, g.bias_mode = bias.data_ptr(), DTYPE[bias.dtype], BCAST_PER_COL
     g.force_generic = 1 if force_generic else 0
+    g.b_static = 1 if b_static else 0  # the weights are not being written: see b200q_gemm_args.b_static
     g.stream = torch.cuda.current_stream().cuda_stream
     check(lib.b200q_fp8_gemm(C.byref(g)), "b200q_fp8_gemm")
     return out

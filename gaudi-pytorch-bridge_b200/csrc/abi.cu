@@ -282,6 +282,7 @@ int b200q_fp8_gemm(const b200q_gemm_args* a) {
   if (g.out8_dtype != 0 && !is_fp8(g.out8_dtype)) return B200Q_ERR_BAD_ARGUMENT;
   g.swiglu = a->swiglu;
   g.out8_amax = g.out8_dtype ? a->out8_amax : nullptr;
+  g.b_static = a->b_static ? 1 : 0;
   g.route_count = a->route_count; g.route_rows = a->route_rows; g.route_row_offset = a->route_row_offset;
   for (int i = 0; i < 8; ++i) g.route_out[i] = a->route_out[i];
   if (g.route_count < 0 || g.route_count > 8) return B200Q_ERR_BAD_ARGUMENT;

@@ -47,6 +47,7 @@ struct GemmParams {
   int route_count;
   int64_t route_rows, route_row_offset;
   float* out8_amax;  // fused output cast only: max |fp8 value written| (atomic max on the bit pattern), or null
+  int b_static;      // B is not written by work still in flight: it may be read before the preceding kernel completes
 };
 
 // value in out_dtype -> fp8 byte of the fused output cast

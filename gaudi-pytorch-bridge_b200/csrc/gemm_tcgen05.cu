@@ -427,25 +427,52 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_x, const __grid_cons
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
-  pdl_enter();  // everything above may run under the tail of the kernel in front of this one
-
   const int num_tiles = p.x_tiles * p.y_tiles;
   const int num_kb = p.num_kb;
+  // Everything above may run under the tail of the kernel in front of this one; nothing below may
+  // touch global memory before pdl_enter() -- except, in the few-token form with weights that
+  // nobody is writing (b_static), the producer's first ring-full of WEIGHT tiles, which it asks
+  // for before it waits: the first memory round trip of the launch overlaps the predecessor too.
+  int pre = 0;  // ring stages whose weight tiles were requested before the wait (producer thread only)
+  const bool early_weights = SWAP && p.g.b_static && !p.x_mn && warp == 0 && lane == 0 && (int)blockIdx.x < num_tiles;
+  if (early_weights) {
+    const int xt = (int)blockIdx.x % p.x_tiles;
+    for (int kb0 = 0; kb0 < num_kb && pre < STAGES; kb0 += KPS, ++pre) {
+      const int nsub = num_kb - kb0 < KPS ? num_kb - kb0 : KPS;
+      const uint32_t full = bar_full + 8 * pre;
+      mbar_arrive_expect_tx(full, nsub * (L::kSubBytes - (kBlockX - p.x_tile_rows) * kBlockK));
+#pragma unroll
+      for (int j = 0; j < KPS; ++j)
+        if (j < nsub)
+          tma_load_2d(smem_base + pre * L::kStageBytes + j * L::kSubBytes, &map_x, full, (kb0 + j) * kBlockK, xt * p.x_tile_rows);
+    }
+  }
+  pdl_enter();
 
   if (warp == 0) {
     // ------------------------------------------------------------ TMA producer
     if (lane == 0) {
       uint32_t stage = 0, phase = 0;
       bool ok = true;
+      int nth = 0;  // stages issued so far
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
         const int xt = tile % p.x_tiles, yt = tile / p.x_tiles;
-        for (int kb0 = 0; kb0 < num_kb; kb0 += KPS) {
+        for (int kb0 = 0; kb0 < num_kb; kb0 += KPS, ++nth) {
+          const int nsub = num_kb - kb0 < KPS ? num_kb - kb0 : KPS;
+          const uint32_t full = bar_full + 8 * stage;
+          if (nth < pre) {
+            // weights already on their way (and the barrier armed): the token tiles follow now
+#pragma unroll
+            for (int j = 0; j < KPS; ++j)
+              if (j < nsub)
+                tma_load_2d(smem_base + stage * L::kStageBytes + j * L::kSubBytes + L::kXBytes, &map_y, full, (kb0 + j) * kBlockK, yt * BN);
+            if (++stage == STAGES) { stage = 0; phase ^= 1; }
+            continue;
+          }
           if (!mbar_wait(bar_empty + 8 * stage, phase ^ 1, abort_flag, p.status, kErrProducer)) {
             ok = false;
             break;
           }
-          const int nsub = num_kb - kb0 < KPS ? num_kb - kb0 : KPS;
-          const uint32_t full = bar_full + 8 * stage;
           mbar_arrive_expect_tx(full, nsub * (L::kSubBytes - (kBlockX - p.x_tile_rows) * kBlockK));
           // K-major operand: box = 128 bytes of k x rows.  MN-major operand (stored [K][rows]):
           // box = 128 rows (bytes) x 128 k, one box per 128-row block; either way a 128-byte-

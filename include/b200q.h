@@ -234,6 +234,13 @@ typedef struct b200q_gemm_args {
    * the casted result), taken in the epilogue while the values are in registers.  The caller
    * zeroes it before the call; it is updated with atomic max, a NaN output makes it NaN. */
   float* out8_amax;
+  /* 1 = B (the weights) is not written by anything still in flight on the stream, as the weights of
+   * an inference engine are not: the few-token kernel (M <= 128) may then start to read B while the
+   * kernel in front of it in the stream is still finishing (it is launched with programmatic stream
+   * serialization and waits for that kernel only before it touches A, the scales, bias, D and out).
+   * 0 (default) = nothing is read before the preceding kernel is complete.  No counterpart in the
+   * reference (a graph compiler orders its loads). */
+  int b_static;
 } b200q_gemm_args;
 
 int b200q_fp8_gemm(const b200q_gemm_args* args);

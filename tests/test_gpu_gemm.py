@@ -274,6 +274,27 @@ def test_decode_shapes_full_width(ops, M):
         _check(A, False, B, True, None, torch.bfloat16, torch.tensor(0.5), col, bias, False, [1, N])
 
 
+@pytest.mark.parametrize("M,N,K", [(1, 1792, 4096), (16, 14336, 4096), (128, 1024, 1024), (16, 520, 14336)])
+def test_static_weights_flag_gives_the_same_bytes(ops, M, N, K):
+    """b200q_gemm_args.b_static only changes WHEN the few-token kernel starts to read the weights
+    (before or after the kernel in front of it has finished); back-to-back launches with and
+    without it, behind a kernel that writes the tokens, give the same bytes."""
+    from b200_hpu_ops import abi
+    g = torch.Generator(device="cuda").manual_seed(M + N)
+    b8 = (torch.randn(N, K, device="cuda", generator=g) * 0.1).to(torch.float8_e4m3fn)
+    sb = torch.rand(N, device="cuda", generator=g) + 0.5
+    bias = torch.randn(N, device="cuda", generator=g).to(torch.bfloat16)
+    outs = []
+    for flag in (False, True, True, False):
+        a = torch.randn(M, K, device="cuda", generator=torch.Generator(device="cuda").manual_seed(7))
+        a8 = a.to(torch.float8_e4m3fn)  # written by the kernel right in front of the GEMM
+        outs.append(abi.fp8_gemm_nt(a8, b8, torch.bfloat16, 0.5, sb, bias, b_static=flag))
+    torch.cuda.synchronize()
+    for o in outs[1:]:
+        assert torch.equal(o, outs[0])
+    assert ops.device_status() == 0
+
+
 def test_tcgen05_batch_folds_into_m(ops):
     g = torch.Generator().manual_seed(23)
     A = _rand_fp8((3, 5, 64, 128), torch.float8_e4m3fn, g)
