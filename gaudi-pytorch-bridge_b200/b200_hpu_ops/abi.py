@@ -15,7 +15,7 @@ ZP_NONE, ZP_PACKED, ZP_FLOAT = 0, 1, 2
 CAST_MUL_IN_FP32 = 1
 
 EXPORTS = [
-    "b200q_strerror", "b200q_last_cuda_error", "b200q_device_status", "b200q_selftest_wait_timeout", "b200q_launch_count",
+    "b200q_strerror", "b200q_last_cuda_error", "b200q_device_status", "b200q_selftest_wait_timeout", "b200q_launch_count", "b200q_sizeof_args",
     "b200q_cast_to_fp8", "b200q_cast_to_fp8_hybrid", "b200q_cast_from_fp8", "b200q_dequant_int4", "b200q_gptq_repack", "b200q_fp8_gemm", "b200q_tp_reduce_bcast", "b200q_fp8_sdpa_fwd",
     "b200q_w4a16_gemm", "b200q_w4a16_workspace_bytes", "b200q_w4a16_gemm_noalloc", "b200q_swiglu_cast_fp8",
     "b200q_amax", "b200q_scale_from_amax", "b200q_amax_history_update",
@@ -69,6 +69,8 @@ def _bind():
     lib.b200q_last_cuda_error.restype = C.c_char_p
     lib.b200q_device_status.argtypes = [C.POINTER(C.c_int)]
     lib.b200q_launch_count.restype = C.c_uint64
+    lib.b200q_sizeof_args.restype = C.c_size_t
+    lib.b200q_sizeof_args.argtypes = [C.c_int]
     lib.b200q_selftest_wait_timeout.argtypes = [C.c_int, C.c_void_p]
     lib.b200q_cast_to_fp8.argtypes = [C.c_void_p, C.c_int, C.c_void_p, C.c_int, C.c_void_p, C.c_float, C.c_int,
                                       C.c_int64, C.c_int64, C.c_void_p, C.c_int, C.c_uint64, C.c_uint64, C.c_uint64,

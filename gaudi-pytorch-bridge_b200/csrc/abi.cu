@@ -112,6 +112,10 @@ const char* b200q_last_cuda_error(void) { return t_cuda_error; }
 
 uint64_t b200q_launch_count(void) { return g_launches.load(std::memory_order_relaxed); }
 
+size_t b200q_sizeof_args(int which) {
+  return which == 0 ? sizeof(b200q_gemm_args) : which == 1 ? sizeof(b200q_sdpa_args) : 0;
+}
+
 int b200q_device_status(int* code_out) {
   int* p = device_status_ptr();
   if (!p) return B200Q_ERR_CUDA;

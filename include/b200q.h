@@ -75,6 +75,9 @@ int b200q_device_status(int* code_out);
 int b200q_selftest_wait_timeout(int code, void* stream);
 /* Number of kernels this library has launched in this process (all threads). */
 uint64_t b200q_launch_count(void);
+/* sizeof of an argument struct as this library was built: which = 0 b200q_gemm_args, 1 b200q_sdpa_args; 0 for
+ * any other value.  A binding that mirrors the structs (ctypes, cgo, JNI) checks its own layout against it. */
+size_t b200q_sizeof_args(int which);
 
 /*
  * cast_to_fp8: out = fp8(in * scale), optional amax = max|in| (of the unscaled input).

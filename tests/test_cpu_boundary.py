@@ -97,6 +97,16 @@ def test_meta_shapes_follow_reference():
                                   torch.empty(3, 5, 6, device="meta", dtype=f8), False, None, torch.bfloat16)
 
 
+def test_ctypes_mirrors_have_the_library_layout():
+    """The ctypes mirrors of the argument structs are as large as the C structs the library was built
+    with (a field added on one side only would shift everything behind it)."""
+    import ctypes
+    from b200_hpu_ops import abi
+    assert abi.lib.b200q_sizeof_args(0) == ctypes.sizeof(abi.GemmArgs)
+    assert abi.lib.b200q_sizeof_args(1) == ctypes.sizeof(abi.SdpaArgs)
+    assert abi.lib.b200q_sizeof_args(7) == 0
+
+
 def test_cpu_tensors_are_refused():
     with pytest.raises(NotImplementedError):
         torch.ops.hpu.cast_to_fp8_v2(torch.zeros(4), None, False, False, torch.float8_e4m3fn)
