@@ -534,6 +534,39 @@ __global__ void __launch_bounds__(256) im2col_u8_kernel(const Im2colParams p) {
   }
 }
 
+// Fallback for images whose rows do not fit the patch kernel's shared memory (a row of 4 channels x kh
+// lines beyond 96 KB): one 4-byte output word per thread, every byte located by division.
+__global__ void __launch_bounds__(256) im2col_u8_wide_kernel(const Im2colParams p) {
+  const int64_t words_per_row = p.ld_out >> 2;
+  const int64_t total = p.N * p.Ho * p.Wo * words_per_row;
+  const int64_t K = p.cg * p.kh * p.kw;
+  for (int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; t < total; t += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t row = t / words_per_row;
+    const int64_t k0 = (t % words_per_row) * 4;
+    const int64_t wo = row % p.Wo, ho = (row / p.Wo) % p.Ho, n = row / (p.Wo * p.Ho);
+    uint32_t word = 0;
+#pragma unroll
+    for (int b = 0; b < 4; ++b) {
+      const int64_t k = k0 + b;
+      if (k < K) {
+        const int64_t j = k % p.kw, i = (k / p.kw) % p.kh, c = p.c0 + k / (p.kw * p.kh);
+        const int64_t y = ho * p.sh - p.ph + i * p.dh, x = wo * p.sw - p.pw + j * p.dw;
+        if (y >= 0 && y < p.H && x >= 0 && x < p.W) word |= (uint32_t)p.in[((n * p.C + c) * p.H + y) * p.W + x] << (8 * b);
+      }
+    }
+    reinterpret_cast<uint32_t*>(p.out)[t] = word;
+  }
+}
+
+static int im2col_wide_launch(const Im2colParams& p, cudaStream_t st) {
+  const int64_t total = p.N * p.Ho * p.Wo * (p.ld_out >> 2);
+  int64_t blocks = (total + 255) / 256;
+  if (blocks > kNumSMs * 32) blocks = kNumSMs * 32;
+  im2col_u8_wide_kernel<<<(int)blocks, 256, 0, st>>>(p);
+  B200Q_LAUNCH_CHECK();
+  return B200Q_OK;
+}
+
 int im2col_u8_impl(const void* in, void* out, int64_t N, int64_t C, int64_t H, int64_t W, int kh, int kw, int sh, int sw,
                    int ph, int pw, int dh, int dw, int64_t c0, int64_t cg, int64_t ld_out, cudaStream_t st) {
   if (N < 0 || C < 0 || H < 0 || W < 0 || kh < 1 || kw < 1 || sh < 1 || sw < 1 || ph < 0 || pw < 0 || dh < 1 || dw < 1 ||
@@ -548,7 +581,8 @@ int im2col_u8_impl(const void* in, void* out, int64_t N, int64_t C, int64_t H, i
   p.c0 = c0; p.cg = cg; p.ld_out = ld_out;
   if (p.Ho <= 0 || p.Wo <= 0 || N == 0) return B200Q_OK;
   if (!in || !out) return B200Q_ERR_BAD_ARGUMENT;
-  if (W + 2 * (int64_t)pw > (1 << 20) || N * p.Ho > (1ll << 30)) return B200Q_ERR_TOO_LARGE;
+  p.chunk = p.chunks = p.lp = p.pitch = p.patch_al = 0;
+  if (W + 2 * (int64_t)pw > (1 << 20) || N * p.Ho > (1ll << 30)) return im2col_wide_launch(p, st);
   p.lp = (pw + 3) & ~3;
   // patch row pitch: an ODD number of 32-bit words, so that the rows (c, i) that the lanes of a warp
   // gather from at one column fall into different banks (a pitch of 64 bytes put every second row
@@ -564,14 +598,14 @@ int im2col_u8_impl(const void* in, void* out, int64_t N, int64_t C, int64_t H, i
   int64_t chunk = cg > 0 ? cg : 1;
   if (chunk * per_channel > budget) {
     const int64_t most = (budget / per_channel) & ~3ll;
-    if (most < 4) return B200Q_ERR_TOO_LARGE;  // the image rows of 4 channels do not fit
+    if (most < 4) return im2col_wide_launch(p, st);  // the image rows of 4 channels do not fit
     const int64_t parts = (cg + most - 1) / most;
     chunk = ((cg + parts - 1) / parts + 3) & ~3ll;
   }
   p.chunk = (int)chunk;
   p.chunks = (int)((cg + chunk - 1) / chunk);
   if (p.chunks < 1) p.chunks = 1;
-  if (N * p.Ho * p.chunks > 0x7FFFFFFFll) return B200Q_ERR_TOO_LARGE;
+  if (N * p.Ho * p.chunks > 0x7FFFFFFFll) return im2col_wide_launch(p, st);
   p.patch_al = (int)(((chunk * kh + 1) * p.pitch + 15) & ~15ll);
   const int64_t table_k = chunk * kh * kw + (ld_out - cg * kh * kw);
   const int smem = p.patch_al + (int)(4 * ((table_k + 3) & ~3ll));

@@ -237,6 +237,8 @@ def test_conv2d_fp8_reference_case(ops, scaleA, scaleB, bias, out_dtype, fp8_dty
     # 512 channels x 3 rows x 66 bytes do not fit one block's shared memory: two channel chunks per output line
     dict(N=1, C=512, H=6, W=64, Co=16, k=(3, 3), stride=(1, 1), padding=(1, 1), dilation=(1, 1), groups=1),
     dict(N=2, C=6, H=11, W=23, Co=8, k=(2, 3), stride=(1, 2), padding=(1, 0), dilation=(2, 1), groups=2),
+    # image rows too wide for the patch kernel's shared memory (3 channels x 3 lines x 12 KB): the fallback kernel
+    dict(N=1, C=3, H=4, W=12288, Co=8, k=(3, 3), stride=(1, 1), padding=(1, 1), dilation=(1, 1), groups=1),
 ])
 def test_conv2d_fp8_shapes_and_scalar_overload(ops, cfg):
     g = torch.Generator().manual_seed(cfg["C"])
