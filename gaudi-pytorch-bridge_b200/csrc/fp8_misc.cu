@@ -102,19 +102,35 @@ __device__ __forceinline__ uint32_t max_bf16x2(uint32_t a, uint32_t b) {
   return r;
 }
 
-template <int NV, bool FA>
+// WPR = warps per row (1, 2 or 4: rows of up to 4096, 8192, 16384 elements): each warp holds one
+// contiguous part of the row; maximum and sum are exchanged through shared memory with a barrier
+// of the row's warps only.
+template <int NV, bool FA, int WPR>
 __global__ void __launch_bounds__(128) softmax_bf16_rowreg_kernel(const SoftmaxParams p) {
   pdl_enter();
-  const int lane = threadIdx.x & 31;
-  const int64_t row = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-  if (row >= p.rows) return;
+  __shared__ float xch[2][4];
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const int64_t row = ((int64_t)blockIdx.x * 4 + warp) / WPR;
+  const int part = warp % WPR;
+  if (row >= p.rows) return;  // (the warps of a row leave together)
+  const int64_t part_cols = p.cols / WPR, col0 = part * part_cols;
+  auto row_reduce = [&](float v, int which, bool is_max) {  // over the row's warps, after the warp's own reduction
+    if (WPR == 1) return v;
+    if (lane == 0) xch[which][warp] = v;
+    asm volatile("bar.sync %0, %1;" ::"r"(1 + warp / WPR), "r"(32 * WPR) : "memory");
+    const int w0 = warp - part;
+    float r = xch[which][w0];
+#pragma unroll
+    for (int i = 1; i < WPR; ++i) r = is_max ? fmaxf(r, xch[which][w0 + i]) : r + xch[which][w0 + i];
+    return r;
+  };
   float pre = p.pre_scale;
   if (p.inv_attn_heads) pre *= __ldg(p.inv_attn_heads);
   if (p.input_scale) pre *= __ldg(p.input_scale);
   constexpr float kLog2e = 1.4426950408889634f;
   pre *= kLog2e;
-  const int nvec = (int)(p.cols >> 3);
-  const uint4* src = reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(p.in) + row * p.cols);
+  const int nvec = (int)(part_cols >> 3);
+  const uint4* src = reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(p.in) + row * p.cols + col0);
   uint32_t w[NV][4];
 #pragma unroll
   for (int i = 0; i < NV; ++i) {
@@ -130,7 +146,7 @@ __global__ void __launch_bounds__(128) softmax_bf16_rowreg_kernel(const SoftmaxP
       off += (r % p.size[d]) * p.fa_stride[d];
       r /= p.size[d];
     }
-    const uint4* fa = reinterpret_cast<const uint4*>(p.fused_add + off);
+    const uint4* fa = reinterpret_cast<const uint4*>(p.fused_add + off + col0);
     m = -INFINITY;
 #pragma unroll
     for (int i = 0; i < NV; ++i) {
@@ -167,6 +183,7 @@ __global__ void __launch_bounds__(128) softmax_bf16_rowreg_kernel(const SoftmaxP
   }
 #pragma unroll
   for (int o = 16; o; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xFFFFFFFFu, m, o));
+  m = row_reduce(m, 0, true);
   float s = 0.f;
   const float neg_m = -m;
 #pragma unroll
@@ -187,10 +204,11 @@ __global__ void __launch_bounds__(128) softmax_bf16_rowreg_kernel(const SoftmaxP
   }
 #pragma unroll
   for (int o = 16; o; o >>= 1) s += __shfl_xor_sync(0xFFFFFFFFu, s, o);
+  s = row_reduce(s, 1, false);
   float inv = 1.f / s;
   const float so = p.output_scale ? __ldg(p.output_scale) : p.output_scale_host;
-  uint2* out8 = reinterpret_cast<uint2*>(static_cast<uint8_t*>(p.out) + row * p.cols);
-  uint4* out16 = reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(p.out) + row * p.cols);
+  uint2* out8 = reinterpret_cast<uint2*>(static_cast<uint8_t*>(p.out) + row * p.cols + col0);
+  uint4* out16 = reinterpret_cast<uint4*>(static_cast<__nv_bfloat16*>(p.out) + row * p.cols + col0);
   if (inv != inv) {  // the whole row is NaN
 #pragma unroll
     for (int i = 0; i < NV; ++i) {
@@ -234,15 +252,15 @@ __global__ void __launch_bounds__(128) softmax_bf16_rowreg_kernel(const SoftmaxP
   }
 }
 
-template <int NV>
+template <int NV, int WPR>
 static int launch_softmax_rowreg(const SoftmaxParams& p, cudaStream_t st) {
-  const int warps = 4;
-  const int64_t blocks = (p.rows + warps - 1) / warps;
+  const int rows_per_block = 4 / WPR;
+  const int64_t blocks = (p.rows + rows_per_block - 1) / rows_per_block;
   if (blocks > 0x7FFFFFFF) return B200Q_ERR_TOO_LARGE;
-  auto kern = p.fused_add ? softmax_bf16_rowreg_kernel<NV, true> : softmax_bf16_rowreg_kernel<NV, false>;
-  if (launch_overlapped(kern, dim3((unsigned)blocks), dim3(warps * 32), 0, st, p) != cudaSuccess) {  // (it calls pdl_enter())
+  auto kern = p.fused_add ? softmax_bf16_rowreg_kernel<NV, true, WPR> : softmax_bf16_rowreg_kernel<NV, false, WPR>;
+  if (launch_overlapped(kern, dim3((unsigned)blocks), dim3(128), 0, st, p) != cudaSuccess) {  // (it calls pdl_enter())
     (void)cudaGetLastError();
-    kern<<<(int)blocks, warps * 32, 0, st>>>(p);
+    kern<<<(int)blocks, 128, 0, st>>>(p);
   }
   B200Q_LAUNCH_CHECK();
   return B200Q_OK;
@@ -256,14 +274,19 @@ int softmax_fp8_impl(const SoftmaxParams& p, cudaStream_t st) {
     fa_ok = (reinterpret_cast<uintptr_t>(p.fused_add) & 15) == 0;
     for (int d = 0; d < p.nd; ++d) fa_ok = fa_ok && (p.fa_stride[d] % 8) == 0;
   }
-  if (p.in_dtype == B200Q_BF16 && (p.cols % 8) == 0 && p.cols <= 32 * 8 * 16 && fa_ok &&
-      ((reinterpret_cast<uintptr_t>(p.in) | reinterpret_cast<uintptr_t>(p.out)) & 15) == 0) {
+  const bool aligned = ((reinterpret_cast<uintptr_t>(p.in) | reinterpret_cast<uintptr_t>(p.out)) & 15) == 0;
+  if (p.in_dtype == B200Q_BF16 && (p.cols % 8) == 0 && p.cols <= 32 * 8 * 16 && fa_ok && aligned) {
     const int64_t per_lane = (p.cols / 8 + 31) / 32;
-    if (per_lane <= 1) return launch_softmax_rowreg<1>(p, st);
-    if (per_lane <= 2) return launch_softmax_rowreg<2>(p, st);
-    if (per_lane <= 4) return launch_softmax_rowreg<4>(p, st);
-    if (per_lane <= 8) return launch_softmax_rowreg<8>(p, st);
-    return launch_softmax_rowreg<16>(p, st);
+    if (per_lane <= 1) return launch_softmax_rowreg<1, 1>(p, st);
+    if (per_lane <= 2) return launch_softmax_rowreg<2, 1>(p, st);
+    if (per_lane <= 4) return launch_softmax_rowreg<4, 1>(p, st);
+    if (per_lane <= 8) return launch_softmax_rowreg<8, 1>(p, st);
+    return launch_softmax_rowreg<16, 1>(p, st);
+  }
+  // longer rows: two or four warps per row, each with a contiguous part in its registers
+  if (p.in_dtype == B200Q_BF16 && fa_ok && aligned) {
+    if ((p.cols % 16) == 0 && p.cols <= 2 * 32 * 8 * 16) return launch_softmax_rowreg<16, 2>(p, st);
+    if ((p.cols % 32) == 0 && p.cols <= 4 * 32 * 8 * 16) return launch_softmax_rowreg<16, 4>(p, st);
   }
   const int warps = 8;
   const int64_t blocks = (p.rows + warps - 1) / warps;

@@ -87,10 +87,10 @@ def test_softmax_fp8_over_another_dimension(ops, dim):
 
 
 @pytest.mark.gpu
-@pytest.mark.parametrize("cols", [24, 256, 1000, 4096])
+@pytest.mark.parametrize("cols", [24, 256, 1000, 4096, 6144, 8192, 12288, 16384])
 def test_softmax_fp8_row_kernel_branches(ops, cols):
-    """The register-resident row kernel's special paths: a negative input scale (the packed maximum
-    runs on sign-flipped inputs), an output scale that is a power of two (folded into the
+    """The register-resident row kernel's special paths (one warp per row up to 4096 elements, two up
+    to 8192, four up to 16384): a negative input scale (the packed maximum runs on sign-flipped inputs), an output scale that is a power of two (folded into the
     normalisation), rows with -inf entries, and rows that are NaN as a whole (a NaN, a +inf, or
     only -inf in the row)."""
     g = torch.Generator().manual_seed(cols)
@@ -112,6 +112,20 @@ def test_softmax_fp8_row_kernel_branches(ops, cols):
     wb = O.softmax_fp8(x, -1)
     assert torch.equal(gb.isnan(), wb.isnan())
     assert torch.allclose(gb.float().nan_to_num(0.0), wb.float().nan_to_num(0.0), rtol=2 ** -7, atol=1e-6)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("cols", [2048, 8192])
+def test_softmax_fp8_fused_add_long_rows(ops, cols):
+    """fused_add (an attention-mask shaped addend, broadcast over the head dimension) with rows held by
+    one and by two warps."""
+    g = torch.Generator().manual_seed(cols)
+    x = (torch.randn(2, 3, 4, cols, generator=g) * 2).to(torch.bfloat16)
+    fa = (torch.randn(2, 1, 4, cols, generator=g)).to(torch.bfloat16)
+    got = torch.ops.hpu.softmax_fp8(x.cuda(), -1, torch.tensor(0.5).cuda(), torch.tensor(200.0).cuda(), None, fa.cuda()).cpu()
+    want = O.softmax_fp8(x, -1, torch.tensor(0.5), torch.tensor(200.0), None, fa)
+    d = _fp8_steps_apart(got, want)
+    assert int(d.max()) <= 1 and float((d != 0).float().mean()) < 0.02
 
 
 @pytest.mark.gpu
