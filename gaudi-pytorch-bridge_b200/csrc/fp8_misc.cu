@@ -616,11 +616,11 @@ int im2col_u8_impl(const void* in, void* out, int64_t N, int64_t C, int64_t H, i
   // as many blocks as the machine holds at once (the last wave costs little); equal chunks
   const int64_t pad_k = ld_out - cg * kh * kw;
   const int64_t per_channel = (int64_t)kh * p.pitch + 4ll * kh * kw;
-  int64_t budget = 40 * 1024 - 4 * pad_k - p.pitch - 64;
-  if (budget < 4 * per_channel) budget = 96 * 1024 - 4 * pad_k - p.pitch - 64;  // wide images: one block per SM or two
+  int64_t room = 40 * 1024 - 4 * pad_k - p.pitch - 64;
+  if (room < 4 * per_channel) room = 96 * 1024 - 4 * pad_k - p.pitch - 64;  // wide images: one block per SM or two
   int64_t chunk = cg > 0 ? cg : 1;
-  if (chunk * per_channel > budget) {
-    const int64_t most = (budget / per_channel) & ~3ll;
+  if (chunk * per_channel > room) {
+    const int64_t most = (room / per_channel) & ~3ll;
     if (most < 4) return im2col_wide_launch(p, st);  // the image rows of 4 channels do not fit
     const int64_t parts = (cg + most - 1) / most;
     chunk = ((cg + parts - 1) / parts + 3) & ~3ll;
