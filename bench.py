@@ -19,7 +19,7 @@ The default (headline) line carries three sub-records beside the contract's keys
 
 --workload selects one member of the operator family for the same JSON contract:
   gemm (default) | gemm_m1 | gemm_m16 | gemm_m128 | cast_rne | cast_sr | uncast | cast_hybrid | cast_current |
-  softmax_fp8 | sdpa_fp8 | conv2d_fp8 | dequant | dequant_kpacked | w4a16_m2048 | w4a16_m16 | w4a16_m16_kpacked | mlp | scaled_mm_lib
+  softmax_fp8 | sdpa_fp8 | conv2d_fp8 | dequant | dequant_kpacked | w4a16_m2048 | w4a16_m128 | w4a16_m16 | w4a16_m16_kpacked | mlp | scaled_mm_lib
 (scaled_mm_lib times torch._scaled_mm -- the vendor library -- on the headline shape, as context only).
 --impl reference times the CPU restatement of the reference semantics (the oracle; the
 reference itself has no arithmetic for these operators) on the host cores.
@@ -483,7 +483,7 @@ def build_workload(wl, args, dev, rank, world, peaks):
         w.l2 = "3 rotating weight/output sets (each larger than L2)"
     elif wl.startswith("w4a16"):
         kp = wl.endswith("_kpacked")
-        Mw = {"w4a16_m2048": 2048, "w4a16_m16": 16}[wl.replace("_kpacked", "")]
+        Mw = {"w4a16_m2048": 2048, "w4a16_m128": 128, "w4a16_m16": 16}[wl.replace("_kpacked", "")]
         Kd = Nd = 8192
         g = torch.Generator(device=dev).manual_seed(13 + rank)
         ws = []
