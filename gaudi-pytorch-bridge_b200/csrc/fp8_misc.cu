@@ -325,6 +325,48 @@ __global__ void __launch_bounds__(256) sum_fp8_strided_kernel(const uint8_t* __r
   partial[(int64_t)chunk * n_out + idx] = acc;
 }
 
+// inner a multiple of 16, 16-byte aligned rows: a thread owns 16 neighbouring inner positions, reads
+// them with one 16-byte load per reduce row (four rows in flight) and keeps 16 fp32 sums.
+template <int FMT>
+__global__ void __launch_bounds__(256) sum_fp8_strided16_kernel(const uint8_t* __restrict__ in, float* __restrict__ partial,
+                                                                int64_t outer, int64_t reduce, int64_t inner, int chunks) {
+  const int64_t inner16 = inner >> 4;
+  const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;  // (o, 16-group)
+  if (idx >= outer * inner16) return;
+  const int chunk = blockIdx.y;
+  const int64_t per = (reduce + chunks - 1) / chunks;
+  const int64_t r0 = chunk * per, r1 = min(reduce, r0 + per);
+  const int64_t o = idx / inner16, i0 = (idx - o * inner16) << 4;
+  const uint4* src = reinterpret_cast<const uint4*>(in + (o * reduce) * inner + i0);
+  const int64_t stride = inner >> 4;  // in 16-byte units
+  float acc[16];
+#pragma unroll
+  for (int j = 0; j < 16; ++j) acc[j] = 0.f;
+  auto add = [&](const uint4& v) {
+    const uint32_t w[4] = {v.x, v.y, v.z, v.w};
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        const __half2_raw hr = __nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)(w[k] >> (16 * h)), Fp8Fmt<FMT>::kInterp);
+        const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&hr));
+        acc[4 * k + 2 * h] += f.x;
+        acc[4 * k + 2 * h + 1] += f.y;
+      }
+    }
+  };
+  int64_t r = r0;
+  for (; r + 4 <= r1; r += 4) {  // rows in order: the sums do not depend on the unrolling
+    const uint4 a = __ldcs(src + r * stride), b = __ldcs(src + (r + 1) * stride), c = __ldcs(src + (r + 2) * stride),
+                d = __ldcs(src + (r + 3) * stride);
+    add(a); add(b); add(c); add(d);
+  }
+  for (; r < r1; ++r) add(__ldcs(src + r * stride));
+  float* dst = partial + (int64_t)chunk * (outer * inner) + o * inner + i0;
+#pragma unroll
+  for (int j = 0; j < 16; j += 4) *reinterpret_cast<float4*>(dst + j) = make_float4(acc[j], acc[j + 1], acc[j + 2], acc[j + 3]);
+}
+
 template <int FMT>
 __global__ void __launch_bounds__(256) sum_fp8_rows_kernel(const uint8_t* __restrict__ in, float* __restrict__ partial,
                                                            int64_t outer, int64_t reduce, int chunks) {
@@ -342,21 +384,29 @@ __global__ void __launch_bounds__(256) sum_fp8_rows_kernel(const uint8_t* __rest
   if ((int64_t)threadIdx.x < head) acc += fp8_to_float<FMT>(s[threadIdx.x]);
   const int64_t nvec = (len - head) / 16;
   const uint4* v = reinterpret_cast<const uint4*>(s + head);
+  float a4[4] = {0.f, 0.f, 0.f, 0.f};  // one chain per 32-bit word of the vector (fixed order all the same)
   for (int64_t i = threadIdx.x; i < nvec; i += blockDim.x) {
-    const uint4 w = v[i];
+    const uint4 w = __ldcs(v + i);
     const uint32_t ws[4] = {w.x, w.y, w.z, w.w};
 #pragma unroll
-    for (int k = 0; k < 4; ++k)
+    for (int k = 0; k < 4; ++k) {
 #pragma unroll
-      for (int b = 0; b < 4; ++b) acc += fp8_to_float<FMT>((uint8_t)(ws[k] >> (8 * b)));
+      for (int h = 0; h < 2; ++h) {
+        const __half2_raw hr = __nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)(ws[k] >> (16 * h)), Fp8Fmt<FMT>::kInterp);
+        const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&hr));
+        a4[k] += f.x;
+        a4[k] += f.y;
+      }
+    }
   }
+  acc += (a4[0] + a4[1]) + (a4[2] + a4[3]);
   const int64_t tail0 = head + nvec * 16;
   if (threadIdx.x < 16 && tail0 + (int64_t)threadIdx.x < len) acc += fp8_to_float<FMT>(s[tail0 + threadIdx.x]);
   // fixed-order block tree
   __shared__ float sm[256];
   sm[threadIdx.x] = acc;
   __syncthreads();
-  for (int o = 128; o; o >>= 1) {
+  for (int o = blockDim.x >> 1; o; o >>= 1) {  // (the block size is a power of two)
     if ((int)threadIdx.x < o) sm[threadIdx.x] += sm[threadIdx.x + o];
     __syncthreads();
   }
@@ -387,6 +437,10 @@ int sum_fp8_chunks(int64_t outer, int64_t reduce, int64_t inner) {
   int64_t want = (int64_t)kNumSMs * 8 * 256 / (n_out > 0 ? n_out : 1);
   if (inner == 1) want = (int64_t)kNumSMs * 4 / (outer > 0 ? outer : 1);
   int64_t cap = reduce / 4096;
+  if (inner > 1 && (inner % 16) == 0) {  // 16 positions per thread: fewer threads per chunk, shorter chunks
+    want = (int64_t)kNumSMs * 8 * 256 / (n_out / 16 > 0 ? n_out / 16 : 1);
+    cap = reduce / 64;
+  }
   if (want > cap) want = cap;
   if (want < 1) want = 1;
   if (want > 1024) want = 1024;
@@ -412,8 +466,16 @@ int sum_fp8_impl(const void* in, int in_dtype, void* out, int out_dtype, int64_t
   if (inner == 1) {
     if (outer > 0x7FFFFFFF) return B200Q_ERR_TOO_LARGE;
     dim3 grid((unsigned)outer, (unsigned)chunks);
-    if (in_dtype == B200Q_E4M3) sum_fp8_rows_kernel<B200Q_E4M3><<<grid, 256, 0, st>>>(src, partial, outer, reduce, chunks);
-    else sum_fp8_rows_kernel<B200Q_E5M2><<<grid, 256, 0, st>>>(src, partial, outer, reduce, chunks);
+    // threads per block: about four 16-byte vectors each (a short row in a big block is all tree and no sum)
+    const int64_t vecs = (reduce + chunks - 1) / chunks / 16;
+    int threads = 32;
+    while (threads < 256 && threads * 4 < vecs) threads *= 2;
+    if (in_dtype == B200Q_E4M3) sum_fp8_rows_kernel<B200Q_E4M3><<<grid, threads, 0, st>>>(src, partial, outer, reduce, chunks);
+    else sum_fp8_rows_kernel<B200Q_E5M2><<<grid, threads, 0, st>>>(src, partial, outer, reduce, chunks);
+  } else if ((inner % 16) == 0 && (reinterpret_cast<uintptr_t>(in) & 15) == 0) {
+    dim3 grid((unsigned)((n_out / 16 + 255) / 256), (unsigned)chunks);
+    if (in_dtype == B200Q_E4M3) sum_fp8_strided16_kernel<B200Q_E4M3><<<grid, 256, 0, st>>>(src, partial, outer, reduce, inner, chunks);
+    else sum_fp8_strided16_kernel<B200Q_E5M2><<<grid, 256, 0, st>>>(src, partial, outer, reduce, inner, chunks);
   } else {
     dim3 grid((unsigned)((n_out + 255) / 256), (unsigned)chunks);
     if (in_dtype == B200Q_E4M3) sum_fp8_strided_kernel<B200Q_E4M3><<<grid, 256, 0, st>>>(src, partial, outer, reduce, inner, chunks);

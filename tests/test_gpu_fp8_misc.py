@@ -188,6 +188,24 @@ def test_sum_fp8_large_and_deterministic(ops):
     assert ops.device_status() == 0
 
 
+@pytest.mark.gpu
+@pytest.mark.parametrize("dtype", [E4M3, E5M2])
+@pytest.mark.parametrize("shape,dim", [((4100, 512), 0), ((3, 700, 48), 1), ((2, 4097, 16), 1), ((5000, 40), 0)])
+def test_sum_fp8_over_an_outer_dimension(ops, dtype, shape, dim):
+    """Sums over a dimension that is not the last: positions of the kept inner dimensions in groups of
+    16 per thread when their number is a multiple of 16 (else one per thread), the reduce range in
+    chunks; fp32 accumulation, the same bits on every run."""
+    g = torch.Generator(device="cuda").manual_seed(shape[0])
+    x = (torch.randn(shape, device="cuda", generator=g) * 4).to(dtype)
+    a = torch.ops.hpu.sum_fp8(x, [dim], False, torch.float)
+    b = torch.ops.hpu.sum_fp8(x, [dim], False, torch.float)
+    assert torch.equal(a, b)
+    exact = x.double().sum(dim)
+    assert a.shape == exact.shape
+    assert torch.allclose(a.double(), exact, rtol=1e-5, atol=1e-3 * float(x.float().abs().max()))
+    assert ops.device_status() == 0
+
+
 # ---------------------------------------------------------------- in_place_interleave_
 @pytest.mark.gpu
 @pytest.mark.parametrize("dtype", [torch.bfloat16, E5M2, E4M3, torch.float32])
