@@ -105,7 +105,8 @@ __device__ __forceinline__ uint32_t max_bf16x2(uint32_t a, uint32_t b) {
 // WPR = warps per row (1, 2 or 4: rows of up to 4096, 8192, 16384 elements): each warp holds one
 // contiguous part of the row; maximum and sum are exchanged through shared memory with a barrier
 // of the row's warps only.
-template <int NV, bool FA, int WPR>
+// IN8: the input is e4m3 (exactly representable in bf16: converted to packed bf16 pairs as it is read).
+template <int NV, bool FA, int WPR, bool IN8>
 __global__ void __launch_bounds__(128) softmax_bf16_rowreg_kernel(const SoftmaxParams p) {
   pdl_enter();
   __shared__ float xch[2][4];
@@ -130,13 +131,34 @@ __global__ void __launch_bounds__(128) softmax_bf16_rowreg_kernel(const SoftmaxP
   constexpr float kLog2e = 1.4426950408889634f;
   pre *= kLog2e;
   const int nvec = (int)(part_cols >> 3);
-  const uint4* src = reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(p.in) + row * p.cols + col0);
   uint32_t w[NV][4];
+  if constexpr (IN8) {
+    const uint2* src = reinterpret_cast<const uint2*>(static_cast<const uint8_t*>(p.in) + row * p.cols + col0);
+    uint2 raw[NV];  // all loads first, so that they are in flight together
 #pragma unroll
-  for (int i = 0; i < NV; ++i) {
-    const int v = lane + 32 * i;
-    const uint4 t = v < nvec ? __ldcs(src + v) : make_uint4(0xFF80FF80u, 0xFF80FF80u, 0xFF80FF80u, 0xFF80FF80u);  // -inf
-    w[i][0] = t.x, w[i][1] = t.y, w[i][2] = t.z, w[i][3] = t.w;
+    for (int i = 0; i < NV; ++i) {
+      const int v = lane + 32 * i;
+      raw[i] = v < nvec ? __ldcs(src + v) : make_uint2(0xF8F8F8F8u, 0xF8F8F8F8u);  // (e4m3 has no infinity: patched below)
+    }
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      const uint32_t b[2] = {raw[i].x, raw[i].y};
+#pragma unroll
+      for (int k = 0; k < 4; ++k) {
+        const __half2_raw hr = __nv_cvt_fp8x2_to_halfraw2((__nv_fp8x2_storage_t)(b[k >> 1] >> (16 * (k & 1))), __NV_E4M3);
+        const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&hr));
+        w[i][k] = pack_bf16x2(f.x, f.y);
+      }
+      if (lane + 32 * i >= nvec) w[i][0] = w[i][1] = w[i][2] = w[i][3] = 0xFF80FF80u;  // -inf beyond the row
+    }
+  } else {
+    const uint4* src = reinterpret_cast<const uint4*>(static_cast<const __nv_bfloat16*>(p.in) + row * p.cols + col0);
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      const int v = lane + 32 * i;
+      const uint4 t = v < nvec ? __ldcs(src + v) : make_uint4(0xFF80FF80u, 0xFF80FF80u, 0xFF80FF80u, 0xFF80FF80u);  // -inf
+      w[i][0] = t.x, w[i][1] = t.y, w[i][2] = t.z, w[i][3] = t.w;
+    }
   }
   float e[NV][8];  // x after pass 1 (with a fused addend only), the exponentials after pass 2
   float m;
@@ -257,7 +279,9 @@ static int launch_softmax_rowreg(const SoftmaxParams& p, cudaStream_t st) {
   const int rows_per_block = 4 / WPR;
   const int64_t blocks = (p.rows + rows_per_block - 1) / rows_per_block;
   if (blocks > 0x7FFFFFFF) return B200Q_ERR_TOO_LARGE;
-  auto kern = p.fused_add ? softmax_bf16_rowreg_kernel<NV, true, WPR> : softmax_bf16_rowreg_kernel<NV, false, WPR>;
+  auto kern = p.in_dtype == B200Q_BF16
+                  ? (p.fused_add ? softmax_bf16_rowreg_kernel<NV, true, WPR, false> : softmax_bf16_rowreg_kernel<NV, false, WPR, false>)
+                  : (p.fused_add ? softmax_bf16_rowreg_kernel<NV, true, WPR, true> : softmax_bf16_rowreg_kernel<NV, false, WPR, true>);
   if (launch_overlapped(kern, dim3((unsigned)blocks), dim3(128), 0, st, p) != cudaSuccess) {  // (it calls pdl_enter())
     (void)cudaGetLastError();
     kern<<<(int)blocks, 128, 0, st>>>(p);
@@ -275,7 +299,8 @@ int softmax_fp8_impl(const SoftmaxParams& p, cudaStream_t st) {
     for (int d = 0; d < p.nd; ++d) fa_ok = fa_ok && (p.fa_stride[d] % 8) == 0;
   }
   const bool aligned = ((reinterpret_cast<uintptr_t>(p.in) | reinterpret_cast<uintptr_t>(p.out)) & 15) == 0;
-  if (p.in_dtype == B200Q_BF16 && (p.cols % 8) == 0 && p.cols <= 32 * 8 * 16 && fa_ok && aligned) {
+  const bool in_ok = p.in_dtype == B200Q_BF16 || p.in_dtype == B200Q_E4M3;
+  if (in_ok && (p.cols % 8) == 0 && p.cols <= 32 * 8 * 16 && fa_ok && aligned) {
     const int64_t per_lane = (p.cols / 8 + 31) / 32;
     if (per_lane <= 1) return launch_softmax_rowreg<1, 1>(p, st);
     if (per_lane <= 2) return launch_softmax_rowreg<2, 1>(p, st);
@@ -284,7 +309,7 @@ int softmax_fp8_impl(const SoftmaxParams& p, cudaStream_t st) {
     return launch_softmax_rowreg<16, 1>(p, st);
   }
   // longer rows: two or four warps per row, each with a contiguous part in its registers
-  if (p.in_dtype == B200Q_BF16 && fa_ok && aligned) {
+  if (in_ok && fa_ok && aligned) {
     if ((p.cols % 16) == 0 && p.cols <= 2 * 32 * 8 * 16) return launch_softmax_rowreg<16, 2>(p, st);
     if ((p.cols % 32) == 0 && p.cols <= 4 * 32 * 8 * 16) return launch_softmax_rowreg<16, 4>(p, st);
   }

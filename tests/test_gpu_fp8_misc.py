@@ -115,6 +115,25 @@ def test_softmax_fp8_row_kernel_branches(ops, cols):
 
 
 @pytest.mark.gpu
+@pytest.mark.parametrize("cols", [64, 1000, 4096, 8192])
+def test_softmax_fp8_e4m3_input_rows(ops, cols):
+    """e4m3 scores in, e4m3 probabilities out (the reference's is_scale / float8 input case) through
+    the register-resident row kernel: the input is exact in bf16, so the result is the bf16 kernel's."""
+    g = torch.Generator().manual_seed(cols + 1)
+    x = (torch.randn(9, cols, generator=g) * 3).to(E4M3)
+    x.view(torch.uint8)[2, 5] = 0x7F  # a NaN score: the whole row is NaN
+    for s_in, s_out in [(0.5, 240.0), (-0.25, 256.0)]:
+        got = torch.ops.hpu.softmax_fp8(x.cuda(), -1, s_in, s_out).cpu()
+        want = O.softmax_fp8(x, -1, s_in, s_out)
+        gn, wn = got.float().isnan(), want.float().isnan()
+        assert torch.equal(gn, wn) and bool(gn[2].all())
+        d = (got.view(torch.uint8).int() - want.view(torch.uint8).int()).abs()[~gn]
+        assert int(d.max()) <= 1 and float((d > 0).float().mean()) < 0.02
+        same = torch.ops.hpu.softmax_fp8(x.to(torch.bfloat16).cuda(), -1, s_in, s_out).cpu()
+        assert torch.equal(same.view(torch.uint8), got.view(torch.uint8))
+
+
+@pytest.mark.gpu
 @pytest.mark.parametrize("cols", [2048, 8192])
 def test_softmax_fp8_fused_add_long_rows(ops, cols):
     """fused_add (an attention-mask shaped addend, broadcast over the head dimension) with rows held by
