@@ -167,14 +167,39 @@ __device__ __forceinline__ void epi_chunk(const GemmParams& g, const uint32_t* r
     const int64_t m = x, n0 = y0 + c0;
     if (x_in) {
       if (full_extra) {
+        // element-wise bias, then the accumulate input D: 16-byte loads of the thread's row segment where
+        // the segment is whole and aligned (a 2-byte load per element and lane, each lane in another row,
+        // made the accumulate form 3.5 times slower than the plain one), else element by element
+        auto add_rowseg = [&](const void* base, int dtype, int64_t ld) {
+          const int esz = dtype == B200Q_BF16 ? 2 : 4;
+          const uint8_t* ptr = static_cast<const uint8_t*>(base) + (m * ld + n0) * esz;
+          if (n0 + CW <= g.N && (reinterpret_cast<uintptr_t>(ptr) & 15) == 0) {
+            if (dtype == B200Q_BF16) {
 #pragma unroll
-        for (int j = 0; j < CW; ++j) {
-          const int64_t n = n0 + j;
-          if (n < g.N) {
-            if (g.bias_mode == B200Q_BCAST_FULL) v[j] += ld_out_typed(g.bias, g.bias_dtype, m * g.bias_ld + n);
-            if (g.D) v[j] += ld_out_typed(g.D, g.d_dtype, m * g.ldd + n);
+              for (int j = 0; j < CW; j += 8) {
+                const uint4 d = __ldg(reinterpret_cast<const uint4*>(ptr + 2 * j));
+                const uint32_t w[4] = {d.x, d.y, d.z, d.w};
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {
+                  v[j + 2 * k] += __uint_as_float(w[k] << 16);
+                  v[j + 2 * k + 1] += __uint_as_float(w[k] & 0xFFFF0000u);
+                }
+              }
+            } else {
+#pragma unroll
+              for (int j = 0; j < CW; j += 4) {
+                const float4 d = __ldg(reinterpret_cast<const float4*>(ptr + 4 * j));
+                v[j] += d.x, v[j + 1] += d.y, v[j + 2] += d.z, v[j + 3] += d.w;
+              }
+            }
+          } else {
+#pragma unroll
+            for (int j = 0; j < CW; ++j)
+              if (n0 + j < g.N) v[j] += ld_out_typed(base, dtype, m * ld + n0 + j);
           }
-        }
+        };
+        if (g.bias_mode == B200Q_BCAST_FULL) add_rowseg(g.bias, g.bias_dtype, g.bias_ld);
+        if (g.D) add_rowseg(g.D, g.d_dtype, g.ldd);
       }
       if (g.out8_dtype) {
         uint8_t* o = static_cast<uint8_t*>(g.out) + m * g.ldo + n0;
@@ -204,6 +229,11 @@ __device__ __forceinline__ void epi_chunk(const GemmParams& g, const uint32_t* r
             *reinterpret_cast<uint4*>(o + j) =
                 make_uint4(pack_bf16x2(v[j], v[j + 1]), pack_bf16x2(v[j + 2], v[j + 3]),
                            pack_bf16x2(v[j + 4], v[j + 5]), pack_bf16x2(v[j + 6], v[j + 7]));
+        } else if (n0 + CW <= g.N && (reinterpret_cast<uintptr_t>(o) & 7) == 0) {
+          // a row pitch that is a multiple of 8 bytes only (N % 8 == 4): 8-byte stores
+#pragma unroll
+          for (int j = 0; j < CW; j += 4)
+            *reinterpret_cast<uint2*>(o + j) = make_uint2(pack_bf16x2(v[j], v[j + 1]), pack_bf16x2(v[j + 2], v[j + 3]));
         } else {
 #pragma unroll
           for (int j = 0; j < CW; ++j)

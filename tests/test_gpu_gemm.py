@@ -295,6 +295,23 @@ def test_static_weights_flag_gives_the_same_bytes(ops, M, N, K):
     assert ops.device_status() == 0
 
 
+@pytest.mark.parametrize("N", [516, 520, 518])
+@pytest.mark.parametrize("od", [torch.bfloat16, torch.float32])
+def test_epilogue_row_segments(ops, N, od):
+    """The epilogue's wide loads and stores: accumulate input D and element-wise bias read as 16-byte
+    row segments where a row is 16-byte aligned, 8-byte stores when the row pitch is a multiple of 8
+    bytes only (N = 516 with bf16), element by element otherwise (N = 518)."""
+    g = torch.Generator().manual_seed(N)
+    M, K = 300, 256
+    A, B = _rand_fp8((M, K), FP8[1], g), _rand_fp8((N, K), FP8[1], g)
+    D = torch.randn(M, N, generator=g).to(od)
+    fullb = torch.randn(M, N, generator=g).to(od)
+    col = torch.rand(1, N, generator=g) + 0.5
+    _check(A, False, B, True, D, od, torch.tensor(0.5), col, None, True, [1, N], tol=1e-2 if od == torch.bfloat16 else 1e-5)
+    _check(A, False, B, True, D, od, torch.tensor(0.5), col, fullb, True, [1, N], tol=1e-2 if od == torch.bfloat16 else 1e-5)
+    _check(A, False, B, True, None, od, torch.tensor(0.5), col, None, False, [1, N], tol=1e-2 if od == torch.bfloat16 else 1e-5)
+
+
 def test_tcgen05_batch_folds_into_m(ops):
     g = torch.Generator().manual_seed(23)
     A = _rand_fp8((3, 5, 64, 128), torch.float8_e4m3fn, g)
