@@ -563,10 +563,27 @@ at::Tensor fp8_gemm_v2_common(const at::Tensor& A, bool trans_A, const at::Tenso
   };
   as_matrix(a);
   as_matrix(b);
+  // K not a multiple of 16 with an operand stored [rows][K]: its row pitch is not 16-byte granular and
+  // the tensor-core kernels (TMA) cannot take it; the CUDA-core kernel that can is two to three orders
+  // of magnitude slower.  For problems large enough to matter both operands are copied into
+  // buffers with K rounded up to 16, the extra k filled with zeros (fp8 0x00 = +0 adds nothing).
+  int64_t Kk = K;
+  if ((K % 16) != 0 && (!ta || tb) && (double)Mk * (double)N * (double)K >= (double)(1 << 26)) {
+    Kk = (K + 15) / 16 * 16;
+    auto pad_k = [&](at::Tensor& t, int64_t kdim) {
+      auto sizes = t.sizes().vec();
+      sizes[t.dim() + kdim] = Kk;
+      at::Tensor padded = at::zeros(sizes, t.options().dtype(at::kByte));
+      padded.narrow(kdim, 0, K).copy_(t.view(at::kByte));
+      t = padded.view(t.scalar_type());
+    };
+    pad_k(a, ta ? -2 : -1);
+    pad_k(b, tb ? -1 : -2);
+  }
   const int64_t kbatch = folded ? 1 : batch;
   g.A = a.data_ptr(); g.B = b.data_ptr();
   g.a_dtype = to_b200q_dtype(a.scalar_type()); g.b_dtype = to_b200q_dtype(b.scalar_type());
-  g.trans_a = ta; g.trans_b = tb; g.M = Mk; g.N = N; g.K = K;
+  g.trans_a = ta; g.trans_b = tb; g.M = Mk; g.N = N; g.K = Kk;
   g.lda = a.size(-2) > 1 ? a.stride(-2) : a.size(-1);
   g.ldb = b.size(-2) > 1 ? b.stride(-2) : b.size(-1);
   g.batch = kbatch;

@@ -376,6 +376,30 @@ def test_tcgen05_mn_major_k_not_multiple_of_16(ops):
     _check(A, True, B, False, None, torch.float32, None, None, None, False, None, tol=1e-5)
 
 
+@pytest.mark.parametrize("tA,tB", [(False, True), (True, True), (False, False)])
+def test_large_k_not_multiple_of_16_is_padded(ops, tA, tB):
+    """An operand stored [rows][K] with K % 16 != 0 has no 16-byte row pitch; above 2^26 products the
+    operator copies both operands into zero-padded buffers.  Exact on small integers (the zeros add
+    nothing), and within tolerance of the oracle with scales, bias and accumulation."""
+    g = torch.Generator().manual_seed(5)
+    M, N, K = 512, 528, 1000 if not (tA and tB) else 1003
+    Ai = torch.randint(-4, 5, (K, M) if tA else (M, K), generator=g).float()
+    Bi = torch.randint(-4, 5, (N, K) if tB else (K, N), generator=g).float()
+    r = torch.ops.hpu.fp8_gemm_v2(Ai.to(torch.float8_e4m3fn).cuda(), tA, Bi.to(torch.float8_e5m2).cuda(), tB, None,
+                                  torch.float32)
+    assert torch.equal(r.cpu(), (Ai.t() if tA else Ai) @ (Bi.t() if tB else Bi))
+    A = _rand_fp8(tuple(Ai.shape), torch.float8_e4m3fn, g)
+    B = _rand_fp8(tuple(Bi.shape), torch.float8_e4m3fn, g)
+    D = torch.randn(M, N, generator=g)
+    _check(A, tA, B, tB, D, torch.float32, torch.tensor(0.5), torch.rand(N, generator=g) + 0.5,
+           torch.randn(N, generator=g), True, [1, N], tol=1e-5)
+    # batched, folded into M
+    A3 = _rand_fp8((3, 256, 1000), torch.float8_e4m3fn, g)
+    B2 = _rand_fp8((528, 1000), torch.float8_e4m3fn, g)
+    _check(A3, False, B2, True, None, torch.bfloat16)
+    assert ops.device_status() == 0
+
+
 def test_tcgen05_batched(ops):
     """Batched operands (both with batch dimensions, or a broadcast one) run one tensor-core launch
     per batch item."""
