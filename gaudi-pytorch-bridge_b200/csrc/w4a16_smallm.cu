@@ -7,8 +7,8 @@
 //     k-part w / 4 of the CTA's k-slice.  A thread-block cluster of 4 CTAs splits K into 4 slices
 //     (16 with the k-parts): N / 256 clusters, 128 CTAs for N = 8192, all resident at once
 //     (clusters of 8 left a sixth of the SMs unused: 15 of them fit on the GPU).
-//   * every warp copies its part with cp.async into a ring of its own (8 KB in flight per warp,
-//     128 KB per SM) and shares no barrier with any other warp in the main loop; the 16 tokens'
+//   * every warp copies its part with cp.async into a ring of its own (6 - 8 KB in flight per warp,
+//     about 100 KB per SM) and shares no barrier with any other warp in the main loop; the 16 tokens'
 //     activations of a k-part are staged in shared memory 512 k-rows at a time by its four warps
 //     (one barrier among them per 512 rows), in the order the MMA fragments read them.
 //   * a thread reads whole packed words from the ring, expands them in registers with packed
@@ -41,6 +41,9 @@ constexpr int kStrip = 64;            // output columns per warp
 constexpr int kCols = kStrips * kStrip;   // output columns per CTA / cluster
 constexpr int kSlices = kParts * kCluster;  // k-slices: cluster rank x k-part
 constexpr int kRingBytes = 8192;      // per warp
+constexpr int kBatch = 4;             // operator layout: k-steps per ring slot (one wait, one refill per slot)
+constexpr int kSlotBytes = kBatch * 512;
+constexpr int kSlots = kRingBytes / kSlotBytes;
 constexpr int kXChunkRows = 512;      // k-rows of activations staged at a time per k-part
 constexpr int kXBytes = kXChunkRows * 16 * 2;             // 16 tokens x 512 k, bf16 = 16 KB
 constexpr int kXOffset = kWarps * kRingBytes;
@@ -144,8 +147,8 @@ __global__ void __cluster_dims__(kCluster, 1, 1) __launch_bounds__(kThreads, 1) 
   const int cg = blockIdx.x / kCluster;
   const int64_t n0 = (int64_t)cg * kCols + strip * kStrip;  // first column of this warp's strip
   constexpr int kStepRows = KP ? 64 : 16;
-  constexpr int kStageBytes = KP ? 2048 : 512;
-  constexpr int kDepth = kRingBytes / kStageBytes;  // 16 / 4 steps in flight
+  constexpr int kStageBytes = 2048;                 // KP = 1: a ring stage is one k-step
+  constexpr int kDepth = kRingBytes / kStageBytes;  // 4 steps in flight
   const int64_t rows_per_slice = p.K / kSlices;
   const int64_t k_begin = ((int64_t)crank * kParts + khalf) * rows_per_slice;
   const int steps = (int)(rows_per_slice / kStepRows);
@@ -153,7 +156,7 @@ __global__ void __cluster_dims__(kCluster, 1, 1) __launch_bounds__(kThreads, 1) 
   uint8_t* ring = smem + warp * kRingBytes;
   const uint32_t ring_u = smem_addr(ring);
 
-  // One k-step into stage s % kDepth.  KP = 0: 16 rows x 8 words, one 16-byte copy per lane (row
+  // One k-step in the ring.  KP = 0: 16 rows x 8 words, one 16-byte copy per lane (row
   // lane / 2, words 4 (lane % 2) ..); rows are stored in the order [load L = (row & 1) + 2 (row >> 3)]
   // [(row >> 1) & 3] so that load L of thread (g, q) -- word g of row 2q (+1, +8, +9) -- is
   // conflict-free.  KP = 1: 8 word-rows x 64 columns, 16-byte pieces XOR-swizzled by word-row so
@@ -168,19 +171,24 @@ __global__ void __cluster_dims__(kCluster, 1, 1) __launch_bounds__(kThreads, 1) 
   } else {
     w_src = p.qw + (k_begin / 8) * nw + n0 + (lane & 15) * 4;  // (word-row offsets are added per copy)
   }
-  auto issue = [&](int s) {
-    const uint32_t dst = ring_u + (s & (kDepth - 1)) * kStageBytes;
-    if (KP == 0) {
-      cp_async16(dst + w_dst, w_src);
-      w_src += 16 * nw;
-    } else {
+  // KP = 0: k-steps 4t .. 4t + 3 (those that exist) into slot t % kSlots, as one group -- committed
+  // even when empty, so that the number of groups that may stay pending is the same at every t
+  auto issue_batch = [&](int t) {
+    const uint32_t dst = ring_u + (t & (kSlots - 1)) * kSlotBytes + w_dst;
 #pragma unroll
-      for (int c = 0; c < 4; ++c) {
-        const int id = c * 32 + lane, w = id >> 4, piece = id & 15;
-        cp_async16(dst + w * 256 + ((piece * 16) ^ ((w & 3) * 32)), w_src + (int64_t)w * nw);
-      }
-      w_src += 8 * nw;
+    for (int j = 0; j < kBatch; ++j)
+      if (t * kBatch + j < steps) cp_async16(dst + j * 512, w_src + (int64_t)j * 16 * nw);
+    w_src += (int64_t)kBatch * 16 * nw;
+    cp_async_commit();
+  };
+  auto issue = [&](int s) {  // KP = 1: one k-step into stage s % kDepth
+    const uint32_t dst = ring_u + (s & (kDepth - 1)) * kStageBytes;
+#pragma unroll
+    for (int c = 0; c < 4; ++c) {
+      const int id = c * 32 + lane, w = id >> 4, piece = id & 15;
+      cp_async16(dst + w * 256 + ((piece * 16) ^ ((w & 3) * 32)), w_src + (int64_t)w * nw);
     }
+    w_src += 8 * nw;
     cp_async_commit();
   };
   // The activations of k-rows [k_begin + 512 c, + 512) of this k-part, copied by its 4 warps (8
@@ -214,7 +222,11 @@ __global__ void __cluster_dims__(kCluster, 1, 1) __launch_bounds__(kThreads, 1) 
 
   stage_x(0);
   int issued = 0;
-  for (; issued < steps && issued < kDepth; ++issued) issue(issued);
+  if (KP == 0) {
+    for (int t = 0; t < kSlots - 1; ++t) issue_batch(t);
+  } else {
+    for (; issued < steps && issued < kDepth; ++issued) issue(issued);
+  }
 
   float acc[4][MT][4];
 #pragma unroll
@@ -230,7 +242,9 @@ __global__ void __cluster_dims__(kCluster, 1, 1) __launch_bounds__(kThreads, 1) 
   const int steps_per_group = p.group / kStepRows;
   int to_next_group = steps_per_group - (int)((k_begin % p.group) / kStepRows) + 1;
   if (KP == 0) {
-    uint32_t sp[4], zr[4];  // {s_i, s_{i+4}}, {128 + z_i, 128 + z_{i+4}} of the thread's word column
+    // scales and 128 + zero point of the thread's 8 columns, each twice in a register: lo[i] column
+    // 8g + i, hi[i] column 8g + i + 4 (an operand register holds two k of one column)
+    uint32_t slo[4], shi[4], zlo[4], zhi[4];
     // The scales and zero points of a group are fetched one group ahead: a load that is consumed at
     // once comes back behind the cp.async traffic this warp has queued, i.e. after a full memory
     // latency, once per group.
@@ -246,59 +260,88 @@ __global__ void __cluster_dims__(kCluster, 1, 1) __launch_bounds__(kThreads, 1) 
       const uint4 sv = nsv;
       const uint32_t z = nz;
       fetch_group(grp + 1);
-      sp[0] = __byte_perm(sv.x, sv.z, 0x5410); sp[1] = __byte_perm(sv.x, sv.z, 0x7632);
-      sp[2] = __byte_perm(sv.y, sv.w, 0x5410); sp[3] = __byte_perm(sv.y, sv.w, 0x7632);
+      slo[0] = __byte_perm(sv.x, 0u, 0x1010); slo[1] = __byte_perm(sv.x, 0u, 0x3232);
+      slo[2] = __byte_perm(sv.y, 0u, 0x1010); slo[3] = __byte_perm(sv.y, 0u, 0x3232);
+      shi[0] = __byte_perm(sv.z, 0u, 0x1010); shi[1] = __byte_perm(sv.z, 0u, 0x3232);
+      shi[2] = __byte_perm(sv.w, 0u, 0x1010); shi[3] = __byte_perm(sv.w, 0u, 0x3232);
 #pragma unroll
-      for (int i = 0; i < 4; ++i) zr[i] = nib_pair(z, i);
+      for (int i = 0; i < 4; ++i) {
+        zlo[i] = (((z >> (4 * i)) & 15u) * 0x00010001u) | 0x43004300u;
+        zhi[i] = (((z >> (4 * i + 16)) & 15u) * 0x00010001u) | 0x43004300u;
+      }
+    };
+    // One k-step: the lane's four packed words (word g of k-rows 2q, 2q + 1, 2q + 8, 2q + 9) are
+    // transposed while still packed -- two byte permutes per pair of rows put the same four
+    // columns of both rows into one word -- so that a nibble pair (i, i + 4) of such a word is
+    // one column at two consecutive k: the operand register the MMA wants, with nothing to
+    // shuffle after the expansion.
+    auto k_step = [&](const uint8_t* wp, const uint8_t* xp) {
+      uint32_t b[MT][2];
+#pragma unroll
+      for (int tk = 0; tk < MT; ++tk) {
+        b[tk][0] = *reinterpret_cast<const uint32_t*>(xp + tk * 128);
+        b[tk][1] = *reinterpret_cast<const uint32_t*>(xp + 256 + tk * 128);
+      }
+      uint32_t w[4];
+#pragma unroll
+      for (int L = 0; L < 4; ++L) w[L] = *reinterpret_cast<const uint32_t*>(wp + L * 128);
+      const uint32_t m0 = __byte_perm(w[0], w[1], 0x5410), m1 = __byte_perm(w[0], w[1], 0x7632);
+      const uint32_t m2 = __byte_perm(w[2], w[3], 0x5410), m3 = __byte_perm(w[2], w[3], 0x7632);
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const uint32_t a0 = bf2_mul(bf2_sub(nib_pair(m0, i), zlo[i]), slo[i]);
+        const uint32_t a1 = bf2_mul(bf2_sub(nib_pair(m1, i), zhi[i]), shi[i]);
+        const uint32_t a2 = bf2_mul(bf2_sub(nib_pair(m2, i), zlo[i]), slo[i]);
+        const uint32_t a3 = bf2_mul(bf2_sub(nib_pair(m3, i), zhi[i]), shi[i]);
+#pragma unroll
+        for (int tk = 0; tk < MT; ++tk) mma_bf16(acc[i][tk], a0, a1, a2, a3, b[tk][0], b[tk][1]);
+      }
     };
     fetch_group(cur_grp);
     load_group(cur_grp);  // before the first wait: its latency hides under the weights'
-    for (int s = 0; s < steps; ++s) {
-      const int rest = steps - 1 - s;
-      const int pend = rest < kDepth - 1 ? rest : kDepth - 1;
-      if ((s & (kStepsPerChunk - 1)) == 0) {
+    // A ring slot holds kBatch k-steps: per slot one wait, one warp barrier (which also says that
+    // every lane is done with the slot before), one refill of that slot and one set of addresses;
+    // per k-step only 4 + 2 MT shared loads, the expansion and the MMAs (plus the group countdown
+    // in a slot that a group boundary or the end of the slice cuts).
+    constexpr int kBatchesPerChunk = kXChunkRows / (16 * kBatch);
+    const int batches = (steps + kBatch - 1) / kBatch;
+    for (int t = 0; t < batches; ++t) {
+      if ((t & (kBatchesPerChunk - 1)) == 0) {
         // a new chunk of activations: the first one was issued before the weights (it is the
         // oldest group), a later one is issued here, after every warp of the k-half is done
         // with the old chunk, and waited for at once
-        if (s > 0) {
+        if (t > 0) {
           named_bar(1 + khalf, 32 * kStrips);
-          stage_x(s / kStepsPerChunk);
+          stage_x(t / kBatchesPerChunk);
           cp_async_wait(0);
         } else {
-          cp_async_wait(issued);  // all but the weight groups: the chunk
+          asm volatile("cp.async.wait_group %0;" ::"n"(kSlots - 1) : "memory");  // all but the weights: the chunk
         }
         named_bar(1 + khalf, 32 * kStrips);
       }
-      if (pend == kDepth - 1) asm volatile("cp.async.wait_group %0;" ::"n"(kDepth - 1) : "memory");
-      else cp_async_wait(pend);
+      asm volatile("cp.async.wait_group %0;" ::"n"(kSlots - 2) : "memory");
       __syncwarp();
-      if (--to_next_group == 0) {  // (a division per step costs more than the step's arithmetic)
-        to_next_group = steps_per_group;
+      issue_batch(t + kSlots - 1);
+      const uint8_t* sl = ring + (t & (kSlots - 1)) * kSlotBytes + q * 32 + g * 4;
+      const uint8_t* xb = xs + (t & (kBatchesPerChunk - 1)) * (kBatch * 512) + g * 16 + 4 * q;
+      const int nst = steps - t * kBatch;
+      if (to_next_group == 1) {  // a group begins with this slot's first step
+        to_next_group = steps_per_group + 1;
         load_group(++cur_grp);
       }
-      uint32_t b[MT][2];
-      const uint8_t* xf = xs + (s & (kStepsPerChunk - 1)) * 512;
+      if (nst >= kBatch && to_next_group > kBatch) {  // a whole slot inside one group: nothing to test per step
+        to_next_group -= kBatch;
 #pragma unroll
-      for (int t = 0; t < MT; ++t) {
-        b[t][0] = *reinterpret_cast<const uint32_t*>(xf + (8 * t + g) * 16 + 4 * q);
-        b[t][1] = *reinterpret_cast<const uint32_t*>(xf + 256 + (8 * t + g) * 16 + 4 * q);
-      }
-      const uint8_t* st = ring + (s & (kDepth - 1)) * kStageBytes + q * 32 + g * 4;
-      uint32_t w[4];
-#pragma unroll
-      for (int L = 0; L < 4; ++L) w[L] = *reinterpret_cast<const uint32_t*>(st + L * 128);
-      __syncwarp();  // every lane has read the stage before it is refilled
-      if (issued < steps) { issue(issued); ++issued; }
-#pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const uint32_t r0 = bf2_mul(bf2_sub(nib_pair(w[0], i), zr[i]), sp[i]);
-        const uint32_t r1 = bf2_mul(bf2_sub(nib_pair(w[1], i), zr[i]), sp[i]);
-        const uint32_t r2 = bf2_mul(bf2_sub(nib_pair(w[2], i), zr[i]), sp[i]);
-        const uint32_t r3 = bf2_mul(bf2_sub(nib_pair(w[3], i), zr[i]), sp[i]);
-        const uint32_t a0 = __byte_perm(r0, r1, 0x5410), a1 = __byte_perm(r0, r1, 0x7632);
-        const uint32_t a2 = __byte_perm(r2, r3, 0x5410), a3 = __byte_perm(r2, r3, 0x7632);
-#pragma unroll
-        for (int t = 0; t < MT; ++t) mma_bf16(acc[i][t], a0, a1, a2, a3, b[t][0], b[t][1]);
+        for (int j = 0; j < kBatch; ++j) k_step(sl + j * 512, xb + j * 512);
+      } else {
+#pragma unroll 1
+        for (int j = 0; j < kBatch && j < nst; ++j) {
+          if (--to_next_group == 0) {  // (a division per step costs more than the step's arithmetic)
+            to_next_group = steps_per_group;
+            load_group(++cur_grp);
+          }
+          k_step(sl + j * 512, xb + j * 512);
+        }
       }
     }
   } else {
