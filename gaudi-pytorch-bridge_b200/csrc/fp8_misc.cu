@@ -516,19 +516,35 @@ int sum_fp8_impl(const void* in, int in_dtype, void* out, int out_dtype, int64_t
 // rows[j] <- rows[j / 4] for j in [0, n_rows), in place.  A row is a destination and, for j <
 // n_rows / 4, also a source; destinations [lo, hi) with lo > (hi - 1) / 4 have all their sources
 // below lo, so the rows are rewritten in phases from the top: [n/4, n), then [n/16, n/4), ...
-__global__ void __launch_bounds__(256) interleave_phase_kernel(uint8_t* base, int64_t row_bytes, int64_t lo, int64_t hi) {
-  const int64_t row = lo + blockIdx.y;
-  if (row >= hi) return;
-  const uint8_t* src = base + (row >> 2) * row_bytes;
-  uint8_t* dst = base + row * row_bytes;
-  if (src == dst) return;
-  const int64_t t = (int64_t)blockIdx.x * blockDim.x + threadIdx.x, stride = (int64_t)gridDim.x * blockDim.x;
-  if ((row_bytes & 15) == 0 && (reinterpret_cast<uintptr_t>(base) & 15) == 0) {
-    const uint4* s4 = reinterpret_cast<const uint4*>(src);
-    uint4* d4 = reinterpret_cast<uint4*>(dst);
-    for (int64_t i = t; i < row_bytes / 16; i += stride) d4[i] = s4[i];
-  } else {
-    for (int64_t i = t; i < row_bytes; i += stride) dst[i] = src[i];
+//
+// A phase is laid out by SOURCE row: a thread reads kIlvPieces pieces of source row s once and
+// writes them to the (up to four) destinations 4s .. 4s + 3 that lie inside the phase, all loads
+// issued before the first store.  Long rows are split over blockIdx.x; rows shorter than a block
+// share one (tpr threads per row, a power of two).
+constexpr int kIlvPieces = 4;
+
+template <typename T>
+__global__ void __launch_bounds__(256) interleave_phase_kernel(uint8_t* base, int64_t row_bytes, int64_t lo, int64_t hi,
+                                                               int64_t s_first, int64_t s_end, int tpr) {
+  const int rows_per_block = 256 / tpr;
+  const int64_t s = s_first + (int64_t)blockIdx.y * rows_per_block + threadIdx.x / tpr;
+  if (s >= s_end) return;
+  const int64_t n = row_bytes / (int64_t)sizeof(T);
+  const T* src = reinterpret_cast<const T*>(base + s * row_bytes);
+  const int64_t d0 = 4 * s > lo ? 4 * s : lo, d1 = 4 * s + 4 < hi ? 4 * s + 4 : hi;
+  const int lane = threadIdx.x % tpr;
+  for (int64_t i0 = (int64_t)blockIdx.x * tpr * kIlvPieces + lane; i0 < n; i0 += (int64_t)gridDim.x * tpr * kIlvPieces) {
+    T v[kIlvPieces];
+#pragma unroll
+    for (int k = 0; k < kIlvPieces; ++k)
+      if (i0 + (int64_t)k * tpr < n) v[k] = src[i0 + (int64_t)k * tpr];
+    for (int64_t d = d0; d < d1; ++d) {
+      if (d == s) continue;  // (row 0 is its own source)
+      T* dst = reinterpret_cast<T*>(base + d * row_bytes);
+#pragma unroll
+      for (int k = 0; k < kIlvPieces; ++k)
+        if (i0 + (int64_t)k * tpr < n) dst[i0 + (int64_t)k * tpr] = v[k];
+    }
   }
 }
 
@@ -536,19 +552,26 @@ int in_place_interleave_impl(void* data, int64_t n_rows, int64_t row_bytes, cuda
   if (n_rows < 0 || row_bytes < 0 || (n_rows % 4) != 0) return B200Q_ERR_BAD_ARGUMENT;
   if (n_rows == 0 || row_bytes == 0) return B200Q_OK;
   if (!data) return B200Q_ERR_BAD_ARGUMENT;
+  const bool wide = (row_bytes & 15) == 0 && (reinterpret_cast<uintptr_t>(data) & 15) == 0;
+  const int64_t n = wide ? row_bytes / 16 : row_bytes;  // pieces per row
+  int tpr = 256;
+  while (tpr > 1 && tpr / 2 * kIlvPieces >= n) tpr /= 2;
+  const int rows_per_block = 256 / tpr;
+  int64_t bx = (n + (int64_t)tpr * kIlvPieces - 1) / ((int64_t)tpr * kIlvPieces);
+  if (bx > 4096) bx = 4096;
   int64_t hi = n_rows;
   while (hi > 1) {
     const int64_t lo = (hi - 1) / 4 + 1;
-    int64_t bx = (row_bytes / 16 + 255) / 256;
-    if (bx < 1) bx = 1;
-    if (bx > 64) bx = 64;
-    int64_t done = lo;
-    while (done < hi) {  // grid.y is limited to 65535 rows per launch
-      const int64_t rows = (hi - done) < 65535 ? (hi - done) : 65535;
-      interleave_phase_kernel<<<dim3((unsigned)bx, (unsigned)rows), 256, 0, st>>>(static_cast<uint8_t*>(data), row_bytes, done,
-                                                                                 done + rows);
+    const int64_t s_end = (hi - 1) / 4 + 1;
+    int64_t s = lo / 4;
+    while (s < s_end) {  // grid.y is limited to 65535
+      int64_t by = (s_end - s + rows_per_block - 1) / rows_per_block;
+      if (by > 65535) by = 65535;
+      const dim3 grid((unsigned)bx, (unsigned)by);
+      if (wide) interleave_phase_kernel<uint4><<<grid, 256, 0, st>>>(static_cast<uint8_t*>(data), row_bytes, lo, hi, s, s_end, tpr);
+      else interleave_phase_kernel<uint8_t><<<grid, 256, 0, st>>>(static_cast<uint8_t*>(data), row_bytes, lo, hi, s, s_end, tpr);
       B200Q_LAUNCH_CHECK();
-      done += rows;
+      s += by * rows_per_block;
     }
     hi = lo;
   }

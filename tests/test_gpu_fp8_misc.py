@@ -228,7 +228,8 @@ def test_sum_fp8_over_an_outer_dimension(ops, dtype, shape, dim):
 # ---------------------------------------------------------------- in_place_interleave_
 @pytest.mark.gpu
 @pytest.mark.parametrize("dtype", [torch.bfloat16, E5M2, E4M3, torch.float32])
-@pytest.mark.parametrize("shape", [(8, 2, 2, 5), (4, 1, 1, 1), (64, 3, 5, 7), (1024, 2, 4, 8)])
+@pytest.mark.parametrize("shape", [(8, 2, 2, 5), (4, 1, 1, 1), (64, 3, 5, 7), (1024, 2, 4, 8), (8, 4, 512, 136), (16, 1, 1, 48),
+                                   (12, 3, 1, 37), (20, 1, 40, 1000)])
 def test_in_place_interleave(ops, dtype, shape):
     g = torch.Generator().manual_seed(shape[0])
     x = (torch.randn(shape, generator=g) * 10.0).to(torch.bfloat16).to(dtype)
