@@ -327,8 +327,8 @@ int softmax_fp8_impl(const SoftmaxParams& p, cudaStream_t st) {
 // ---------------------------------------------------------------------------- sum_fp8
 // in viewed as [outer][reduce][inner] (contiguous), fp32 accumulation in a fixed order:
 // chunk c of the reduce range is summed sequentially by one thread (inner > 1) or by one block
-// with a fixed tree (inner == 1); the chunk sums are then added in chunk order.  Same result
-// on every run.
+// with a fixed tree (inner == 1); the chunk sums are then added in chunk order (16 chunks or
+// more: eight interleaved partial orders, then those in order).  Same result on every run.
 template <int FMT>
 __device__ __forceinline__ float fp8_to_float(uint8_t b) {
   return __half2float(__half(__nv_cvt_fp8_to_halfraw(b, Fp8Fmt<FMT>::kInterp)));
@@ -351,7 +351,7 @@ __global__ void __launch_bounds__(256) sum_fp8_strided_kernel(const uint8_t* __r
 }
 
 // inner a multiple of 16, 16-byte aligned rows: a thread owns 16 neighbouring inner positions, reads
-// them with one 16-byte load per reduce row (four rows in flight) and keeps 16 fp32 sums.
+// them with one 16-byte load per reduce row (eight rows in flight) and keeps 16 fp32 sums.
 template <int FMT>
 __global__ void __launch_bounds__(256) sum_fp8_strided16_kernel(const uint8_t* __restrict__ in, float* __restrict__ partial,
                                                                 int64_t outer, int64_t reduce, int64_t inner, int chunks) {
@@ -381,10 +381,12 @@ __global__ void __launch_bounds__(256) sum_fp8_strided16_kernel(const uint8_t* _
     }
   };
   int64_t r = r0;
-  for (; r + 4 <= r1; r += 4) {  // rows in order: the sums do not depend on the unrolling
-    const uint4 a = __ldcs(src + r * stride), b = __ldcs(src + (r + 1) * stride), c = __ldcs(src + (r + 2) * stride),
-                d = __ldcs(src + (r + 3) * stride);
-    add(a); add(b); add(c); add(d);
+  for (; r + 8 <= r1; r += 8) {  // rows in order: the sums do not depend on the unrolling
+    uint4 v[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) v[j] = __ldcs(src + (r + j) * stride);
+#pragma unroll
+    for (int j = 0; j < 8; ++j) add(v[j]);
   }
   for (; r < r1; ++r) add(__ldcs(src + r * stride));
   float* dst = partial + (int64_t)chunk * (outer * inner) + o * inner + i0;
@@ -410,8 +412,7 @@ __global__ void __launch_bounds__(256) sum_fp8_rows_kernel(const uint8_t* __rest
   const int64_t nvec = (len - head) / 16;
   const uint4* v = reinterpret_cast<const uint4*>(s + head);
   float a4[4] = {0.f, 0.f, 0.f, 0.f};  // one chain per 32-bit word of the vector (fixed order all the same)
-  for (int64_t i = threadIdx.x; i < nvec; i += blockDim.x) {
-    const uint4 w = __ldcs(v + i);
+  auto add = [&](const uint4& w) {
     const uint32_t ws[4] = {w.x, w.y, w.z, w.w};
 #pragma unroll
     for (int k = 0; k < 4; ++k) {
@@ -423,19 +424,28 @@ __global__ void __launch_bounds__(256) sum_fp8_rows_kernel(const uint8_t* __rest
         a4[k] += f.y;
       }
     }
+  };
+  int64_t i = threadIdx.x;
+  for (; i + 3 * (int64_t)blockDim.x < nvec; i += 4 * (int64_t)blockDim.x) {  // four loads in flight, added in index order
+    const uint4 w0 = __ldcs(v + i), w1 = __ldcs(v + i + blockDim.x), w2 = __ldcs(v + i + 2 * (int64_t)blockDim.x),
+                w3 = __ldcs(v + i + 3 * (int64_t)blockDim.x);
+    add(w0); add(w1); add(w2); add(w3);
   }
+  for (; i < nvec; i += blockDim.x) add(__ldcs(v + i));
   acc += (a4[0] + a4[1]) + (a4[2] + a4[3]);
   const int64_t tail0 = head + nvec * 16;
   if (threadIdx.x < 16 && tail0 + (int64_t)threadIdx.x < len) acc += fp8_to_float<FMT>(s[tail0 + threadIdx.x]);
-  // fixed-order block tree
-  __shared__ float sm[256];
-  sm[threadIdx.x] = acc;
+  // fixed order: a butterfly inside each warp (no barrier), then the warp sums in warp order
+#pragma unroll
+  for (int o = 16; o; o >>= 1) acc += __shfl_xor_sync(0xffffffffu, acc, o);
+  __shared__ float sm[8];
+  if ((threadIdx.x & 31) == 0) sm[threadIdx.x >> 5] = acc;
   __syncthreads();
-  for (int o = blockDim.x >> 1; o; o >>= 1) {  // (the block size is a power of two)
-    if ((int)threadIdx.x < o) sm[threadIdx.x] += sm[threadIdx.x + o];
-    __syncthreads();
+  if (threadIdx.x == 0) {
+    float t = sm[0];
+    for (int w = 1; w < (int)(blockDim.x >> 5); ++w) t += sm[w];
+    partial[(int64_t)chunk * outer + row] = t;
   }
-  if (threadIdx.x == 0) partial[(int64_t)chunk * outer + row] = sm[0];
 }
 
 template <int FMT>
@@ -445,6 +455,39 @@ __global__ void __launch_bounds__(256) sum_fp8_finish_kernel(const float* __rest
   if (idx >= n_out) return;
   float acc = 0.f;
   for (int c = 0; c < chunks; ++c) acc += partial[(int64_t)c * n_out + idx];
+  if (out_dtype == B200Q_F32) {
+    static_cast<float*>(out)[idx] = acc;
+  } else if (out_dtype == B200Q_BF16) {
+    static_cast<__nv_bfloat16*>(out)[idx] = __float2bfloat16_rn(acc);
+  } else {
+    uint32_t b = out_dtype == B200Q_E4M3 ? (cvt_fp8x2<B200Q_E4M3>(acc, 0.f) & 0xFFu) : (cvt_fp8x2<B200Q_E5M2>(acc, 0.f) & 0xFFu);
+    if (acc != acc) b = 0x7Fu;
+    static_cast<uint8_t*>(out)[idx] = (uint8_t)b;
+  }
+}
+
+// Many chunks: a block of 32 outputs x 8 chunk lanes; lane y adds chunks y, y + 8, ... in order
+// (coalesced 128-byte loads, four in flight), the 8 lane sums are then added in lane order.
+__global__ void __launch_bounds__(256) sum_fp8_finish_wide_kernel(const float* __restrict__ partial, void* out, int out_dtype,
+                                                                  int64_t n_out, int chunks) {
+  __shared__ float sm[8][33];
+  const int x = threadIdx.x & 31, y = threadIdx.x >> 5;
+  const int64_t idx = (int64_t)blockIdx.x * 32 + x;
+  float acc = 0.f;
+  if (idx < n_out) {
+    int c = y;
+    for (; c + 24 < chunks; c += 32) {
+      const float p0 = partial[(int64_t)c * n_out + idx], p1 = partial[(int64_t)(c + 8) * n_out + idx],
+                  p2 = partial[(int64_t)(c + 16) * n_out + idx], p3 = partial[(int64_t)(c + 24) * n_out + idx];
+      acc += p0; acc += p1; acc += p2; acc += p3;
+    }
+    for (; c < chunks; c += 8) acc += partial[(int64_t)c * n_out + idx];
+  }
+  sm[y][x] = acc;
+  __syncthreads();
+  if (y != 0 || idx >= n_out) return;
+#pragma unroll
+  for (int j = 1; j < 8; ++j) acc += sm[j][x];
   if (out_dtype == B200Q_F32) {
     static_cast<float*>(out)[idx] = acc;
   } else if (out_dtype == B200Q_BF16) {
@@ -485,7 +528,9 @@ int sum_fp8_impl(const void* in, int in_dtype, void* out, int out_dtype, int64_t
   if (!out || (reduce > 0 && !in)) return B200Q_ERR_BAD_ARGUMENT;
   const int chunks = sum_fp8_chunks(outer, reduce, inner);
   if (!workspace || workspace_bytes < (size_t)chunks * n_out * sizeof(float)) return B200Q_ERR_BAD_ARGUMENT;
-  float* partial = static_cast<float*>(workspace);
+  // one chunk and fp32 output: the chunk sums are the result, written where it belongs
+  const bool direct = chunks == 1 && out_dtype == B200Q_F32;
+  float* partial = direct ? static_cast<float*>(out) : static_cast<float*>(workspace);
   const uint8_t* src = static_cast<const uint8_t*>(in);
   const int fin_blocks = (int)((n_out + 255) / 256);
   if (inner == 1) {
@@ -507,7 +552,9 @@ int sum_fp8_impl(const void* in, int in_dtype, void* out, int out_dtype, int64_t
     else sum_fp8_strided_kernel<B200Q_E5M2><<<grid, 256, 0, st>>>(src, partial, outer, reduce, inner, chunks);
   }
   B200Q_LAUNCH_CHECK();
-  sum_fp8_finish_kernel<0><<<fin_blocks, 256, 0, st>>>(partial, out, out_dtype, n_out, chunks);
+  if (direct) return B200Q_OK;
+  if (chunks >= 16) sum_fp8_finish_wide_kernel<<<(unsigned)((n_out + 31) / 32), 256, 0, st>>>(partial, out, out_dtype, n_out, chunks);
+  else sum_fp8_finish_kernel<0><<<fin_blocks, 256, 0, st>>>(partial, out, out_dtype, n_out, chunks);
   B200Q_LAUNCH_CHECK();
   return B200Q_OK;
 }
