@@ -20,6 +20,7 @@ EXPORTS = [
     "b200q_w4a16_gemm", "b200q_w4a16_workspace_bytes", "b200q_w4a16_gemm_noalloc", "b200q_swiglu_cast_fp8",
     "b200q_amax", "b200q_scale_from_amax", "b200q_amax_history_update",
     "b200q_softmax_fp8", "b200q_sum_fp8_workspace_bytes", "b200q_sum_fp8", "b200q_in_place_interleave", "b200q_im2col_fp8",
+    "b200q_nchw_to_nhwc_u8", "b200q_im2col_nhwc_fp8",
 ]
 
 DTYPE = {torch.float32: F32, torch.bfloat16: BF16, torch.float8_e4m3fn: E4M3, torch.float8_e5m2: E5M2}

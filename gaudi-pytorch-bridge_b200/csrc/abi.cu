@@ -68,6 +68,9 @@ size_t sum_fp8_workspace_bytes_impl(int64_t, int64_t, int64_t);
 int in_place_interleave_impl(void*, int64_t, int64_t, cudaStream_t);
 int im2col_u8_impl(const void*, void*, int64_t, int64_t, int64_t, int64_t, int, int, int, int, int, int, int, int, int64_t, int64_t,
                    int64_t, cudaStream_t);
+int nchw_to_nhwc_u8_impl(const void*, void*, int64_t, int64_t, int64_t, int64_t, cudaStream_t);
+int im2col_nhwc_u8_impl(const void*, void*, int64_t, int64_t, int64_t, int64_t, int, int, int, int, int, int, int, int, int64_t,
+                        int64_t, int64_t, cudaStream_t);
 int amax_impl(const void*, int, int64_t, float*, cudaStream_t);
 int scale_from_amax_impl(const float*, float*, float*, float, int, int, cudaStream_t);
 int amax_history_impl(float*, int, int, const float*, int, float*, float*, float, int, int, cudaStream_t);
@@ -230,6 +233,16 @@ int b200q_in_place_interleave(void* data, int64_t n_rows, int64_t row_bytes, voi
 int b200q_im2col_fp8(const void* in, void* out, int64_t N, int64_t C, int64_t H, int64_t W, int kh, int kw, int sh, int sw,
                      int ph, int pw, int dh, int dw, int64_t c0, int64_t cg, int64_t ld_out, void* stream) {
   return im2col_u8_impl(in, out, N, C, H, W, kh, kw, sh, sw, ph, pw, dh, dw, c0, cg, ld_out, static_cast<cudaStream_t>(stream));
+}
+
+int b200q_nchw_to_nhwc_u8(const void* in, void* out, int64_t N, int64_t C, int64_t H, int64_t W, void* stream) {
+  return nchw_to_nhwc_u8_impl(in, out, N, C, H, W, static_cast<cudaStream_t>(stream));
+}
+
+int b200q_im2col_nhwc_fp8(const void* in, void* out, int64_t N, int64_t C, int64_t H, int64_t W, int kh, int kw, int sh, int sw,
+                          int ph, int pw, int dh, int dw, int64_t c0, int64_t cg, int64_t ld_out, void* stream) {
+  return im2col_nhwc_u8_impl(in, out, N, C, H, W, kh, kw, sh, sw, ph, pw, dh, dw, c0, cg, ld_out,
+                             static_cast<cudaStream_t>(stream));
 }
 
 int b200q_amax(const void* in, int in_dtype, int64_t n, float* amax, void* stream) {

@@ -801,4 +801,145 @@ int im2col_u8_impl(const void* in, void* out, int64_t N, int64_t C, int64_t H, i
   return B200Q_OK;
 }
 
+// ---------------------------------------------------------------------------- channels-last path of conv2d_fp8
+// One-byte elements.  out[n][hw][c] = in[n][c][hw]: a block moves a tile of 64 channels x 64
+// pixels.  A thread loads four channels x four pixels as four 32-bit words (a warp reads 64
+// contiguous bytes of two channel rows per instruction), transposes the 4 x 4 bytes in registers
+// with eight byte permutes, and parks the four words -- four channels of one pixel each -- in a
+// shared-memory tile [pixel][channel]; the tile is then written out with a warp storing the 64
+// contiguous bytes of two pixels per instruction.
+constexpr int kTrTile = 64;
+constexpr int kTrPitch = kTrTile + 4;  // bytes; 17 words: the transposed writes spread over 16 banks
+
+__global__ void __launch_bounds__(256) nchw_to_nhwc_u8_kernel(const uint8_t* __restrict__ in, uint8_t* __restrict__ out, int64_t C,
+                                                              int64_t HW, int wide) {
+  __shared__ __align__(16) uint8_t tile[kTrTile * kTrPitch];
+  const int64_t n = blockIdx.z, c0 = (int64_t)blockIdx.y * kTrTile, p0 = (int64_t)blockIdx.x * kTrTile;
+  const uint8_t* src = in + n * C * HW;
+  uint8_t* dst = out + n * HW * C;
+  const int t = threadIdx.x, cb = t >> 4, pb = t & 15;
+  uint32_t r[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int64_t c = c0 + 4 * cb + i, p = p0 + 4 * pb;
+    r[i] = 0u;
+    if (c < C) {
+      if (wide && p + 3 < HW) {
+        r[i] = __ldcs(reinterpret_cast<const uint32_t*>(src + c * HW + p));
+      } else {
+#pragma unroll
+        for (int k = 0; k < 4; ++k)
+          if (p + k < HW) r[i] |= (uint32_t)src[c * HW + p + k] << (8 * k);
+      }
+    }
+  }
+  const uint32_t t0 = __byte_perm(r[0], r[1], 0x5140), t1 = __byte_perm(r[0], r[1], 0x7362);
+  const uint32_t t2 = __byte_perm(r[2], r[3], 0x5140), t3 = __byte_perm(r[2], r[3], 0x7362);
+  const uint32_t o[4] = {__byte_perm(t0, t2, 0x5410), __byte_perm(t0, t2, 0x7632), __byte_perm(t1, t3, 0x5410),
+                         __byte_perm(t1, t3, 0x7632)};
+#pragma unroll
+  for (int k = 0; k < 4; ++k) *reinterpret_cast<uint32_t*>(tile + (4 * pb + k) * kTrPitch + 4 * cb) = o[k];
+  __syncthreads();
+  // (C is a multiple of 4: a word of four channels is inside the tensor or outside it as a whole)
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    const int pl = 16 * k + (t >> 4), c4 = 4 * (t & 15);
+    const int64_t p = p0 + pl, c = c0 + c4;
+    if (p < HW && c < C)
+      *reinterpret_cast<uint32_t*>(dst + p * C + c) = *reinterpret_cast<const uint32_t*>(tile + pl * kTrPitch + c4);
+  }
+}
+
+int nchw_to_nhwc_u8_impl(const void* in, void* out, int64_t N, int64_t C, int64_t H, int64_t W, cudaStream_t st) {
+  if (N < 0 || C < 0 || H < 0 || W < 0 || (C % 4) != 0) return B200Q_ERR_BAD_ARGUMENT;
+  const int64_t HW = H * W;
+  if (N == 0 || C == 0 || HW == 0) return B200Q_OK;
+  if (!in || !out || (reinterpret_cast<uintptr_t>(out) & 3)) return B200Q_ERR_BAD_ARGUMENT;
+  const int64_t bx = (HW + kTrTile - 1) / kTrTile, by = (C + kTrTile - 1) / kTrTile;
+  if (bx > 0x7FFFFFFF || by > 65535 || N > 65535) return B200Q_ERR_TOO_LARGE;
+  const int wide = (HW % 4) == 0 && (reinterpret_cast<uintptr_t>(in) & 3) == 0;
+  nchw_to_nhwc_u8_kernel<<<dim3((unsigned)bx, (unsigned)by, (unsigned)N), 256, 0, st>>>(
+      static_cast<const uint8_t*>(in), static_cast<uint8_t*>(out), C, HW, wide);
+  B200Q_LAUNCH_CHECK();
+  return B200Q_OK;
+}
+
+// im2col from the channels-last copy: out[(n, ho, wo)][k], k = (i, j, c - c0): every window
+// position is cg contiguous bytes of one input pixel, so the matrix is built from 16-byte copies.
+// A thread owns one 16-byte column piece (i, j, 16 channels) -- its window offset is computed once
+// -- and walks kIm2Rows consecutive output rows, four loads in flight.
+constexpr int kIm2Rows = 16;
+
+struct Im2colNhwcParams {
+  const uint8_t* in;
+  uint8_t* out;
+  int64_t C, H, W, Ho, Wo, rows, ld_out;
+  int kh, kw, sh, sw, ph, pw, dh, dw;
+  int64_t c0;
+  int cg16, pieces, pieces_ld;  // 16-byte pieces per channel group, per window row (kh kw cg / 16), per output row
+};
+
+__global__ void __launch_bounds__(256) im2col_nhwc_u8_kernel(const Im2colNhwcParams p) {
+  const int64_t row0 = (int64_t)blockIdx.x * kIm2Rows;
+  const int nrows = (int)(p.rows - row0 < kIm2Rows ? p.rows - row0 : kIm2Rows);
+  // (n, ho, wo) of the block's first row
+  const int64_t hw = p.Ho * p.Wo;
+  const int64_t n0 = row0 / hw;
+  const int ho0 = (int)((row0 - n0 * hw) / p.Wo), wo0 = (int)(row0 - n0 * hw - (int64_t)ho0 * p.Wo);
+  for (int kp = threadIdx.x; kp < p.pieces_ld; kp += blockDim.x) {
+    const bool pad = kp >= p.pieces;  // columns beyond kh kw cg: zeros
+    const int ij = kp / p.cg16, c16 = kp - ij * p.cg16;
+    const int i = ij / p.kw, j = ij - i * p.kw;
+    const int dh_off = i * p.dh - p.ph, dw_off = j * p.dw - p.pw;
+    const uint8_t* src = p.in + p.c0 + 16 * (int64_t)c16;
+    uint8_t* dst = p.out + row0 * p.ld_out + 16 * (int64_t)kp;
+    int64_t n = n0;
+    int ho = ho0, wo = wo0;
+    for (int r = 0; r < nrows; r += 4) {
+      uint4 v[4];
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        v[u] = make_uint4(0u, 0u, 0u, 0u);
+        if (r + u < nrows) {
+          const int h = ho * p.sh + dh_off, w = wo * p.sw + dw_off;
+          if (!pad && h >= 0 && h < p.H && w >= 0 && w < p.W)
+            v[u] = __ldg(reinterpret_cast<const uint4*>(src + ((n * p.H + h) * p.W + w) * p.C));
+          if (++wo == p.Wo) {
+            wo = 0;
+            if (++ho == p.Ho) { ho = 0; ++n; }
+          }
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u)
+        if (r + u < nrows) __stcs(reinterpret_cast<uint4*>(dst + (int64_t)(r + u) * p.ld_out), v[u]);
+    }
+  }
+}
+
+int im2col_nhwc_u8_impl(const void* in, void* out, int64_t N, int64_t C, int64_t H, int64_t W, int kh, int kw, int sh, int sw,
+                        int ph, int pw, int dh, int dw, int64_t c0, int64_t cg, int64_t ld_out, cudaStream_t st) {
+  if (N < 0 || C <= 0 || H <= 0 || W <= 0 || kh <= 0 || kw <= 0 || sh <= 0 || sw <= 0 || ph < 0 || pw < 0 || dh <= 0 || dw <= 0 ||
+      c0 < 0 || cg <= 0 || c0 + cg > C)
+    return B200Q_ERR_BAD_ARGUMENT;
+  if ((C % 16) || (c0 % 16) || (cg % 16) || (ld_out % 16) || ld_out < cg * kh * kw) return B200Q_ERR_BAD_ARGUMENT;
+  const int64_t Ho = (H + 2 * ph - (int64_t)dh * (kh - 1) - 1) / sh + 1, Wo = (W + 2 * pw - (int64_t)dw * (kw - 1) - 1) / sw + 1;
+  if (Ho <= 0 || Wo <= 0) return B200Q_ERR_BAD_ARGUMENT;
+  if (N == 0) return B200Q_OK;
+  if (!in || !out || ((reinterpret_cast<uintptr_t>(in) | reinterpret_cast<uintptr_t>(out)) & 15)) return B200Q_ERR_BAD_ARGUMENT;
+  if (cg * kh * kw / 16 > 0x7FFFFFFF || ld_out / 16 > 0x7FFFFFFF) return B200Q_ERR_TOO_LARGE;
+  Im2colNhwcParams p;
+  p.in = static_cast<const uint8_t*>(in); p.out = static_cast<uint8_t*>(out);
+  p.C = C; p.H = H; p.W = W; p.Ho = Ho; p.Wo = Wo; p.rows = N * Ho * Wo; p.ld_out = ld_out;
+  p.kh = kh; p.kw = kw; p.sh = sh; p.sw = sw; p.ph = ph; p.pw = pw; p.dh = dh; p.dw = dw;
+  p.c0 = c0; p.cg16 = (int)(cg / 16); p.pieces = (int)(cg * kh * kw / 16); p.pieces_ld = (int)(ld_out / 16);
+  const int64_t blocks = (p.rows + kIm2Rows - 1) / kIm2Rows;
+  if (blocks > 0x7FFFFFFF) return B200Q_ERR_TOO_LARGE;
+  int threads = 32;
+  while (threads < 256 && threads < p.pieces_ld) threads += 32;
+  im2col_nhwc_u8_kernel<<<(unsigned)blocks, threads, 0, st>>>(p);
+  B200Q_LAUNCH_CHECK();
+  return B200Q_OK;
+}
+
 }  // namespace b200q

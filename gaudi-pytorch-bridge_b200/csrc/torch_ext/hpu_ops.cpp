@@ -1178,7 +1178,27 @@ at::Tensor conv2d_fp8_common(const at::Tensor& input, const at::Tensor& weight, 
   at::Tensor ts_in, ts_w;
   if (!host_scales) { ts_in = as_tensor(s_in); ts_w = as_tensor(s_w); }
   std::vector<at::Tensor> parts;
-  for (int64_t g = 0; g < groups; ++g) {
+  // Channel groups of whole 16-byte pieces: the matrix is built from a channels-last copy of the
+  // input, 16 bytes at a time, with its columns ordered (i, j, c); the weight is permuted to match.
+  const bool channels_last = (C % 16) == 0 && (Cg % 16) == 0;
+  at::Tensor nhwc;
+  if (channels_last) {
+    nhwc = at::empty({N, H, W, C}, in.options());
+    check_status(b200q_nchw_to_nhwc_u8(in.data_ptr(), nhwc.data_ptr(), N, C, H, W, current_stream()), "conv2d_fp8 (channels-last copy)");
+  }
+  for (int64_t g = 0; g < groups && channels_last; ++g) {
+    at::Tensor cols = at::empty({rows, K}, in.options());
+    check_status(b200q_im2col_nhwc_fp8(nhwc.data_ptr(), cols.data_ptr(), N, C, H, W, (int)kh, (int)kw, (int)stride[0],
+                                       (int)stride[1], (int)padding[0], (int)padding[1], (int)dilation[0], (int)dilation[1],
+                                       g * Cg, Cg, K, current_stream()),
+                 "conv2d_fp8 (im2col)");
+    at::Tensor wg = w.narrow(0, g * Cog, Cog).view(at::kByte).permute({0, 2, 3, 1}).contiguous().reshape({Cog, K}).view(w.scalar_type());
+    OptTensor bg;
+    if (bias.has_value() && bias->defined()) bg = bias->narrow(0, g * Cog, Cog).to(odt);
+    parts.push_back(host_scales ? fp8_gemm_v2_scalar(cols, false, wg, true, c10::nullopt, odt, s_in.v, s_w.v, bg, false, c10::nullopt)
+                                : fp8_gemm_v2(cols, false, wg, true, c10::nullopt, odt, ts_in, ts_w, bg, false, c10::nullopt));
+  }
+  for (int64_t g = 0; g < groups && !channels_last; ++g) {
     at::Tensor cols = at::empty({rows, Kp}, in.options());
     check_status(b200q_im2col_fp8(in.data_ptr(), cols.data_ptr(), N, C, H, W, (int)kh, (int)kw, (int)stride[0], (int)stride[1],
                                   (int)padding[0], (int)padding[1], (int)dilation[0], (int)dilation[1], g * Cg, Cg, Kp,

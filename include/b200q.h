@@ -444,6 +444,19 @@ int b200q_im2col_fp8(const void* in, void* out, int64_t N, int64_t C, int64_t H,
                      int kw, int sh, int sw, int ph, int pw, int dh, int dw, int64_t c0, int64_t cg,
                      int64_t ld_out, void* stream);
 
+/*
+ * The same matrix built from a channels-last copy of the input (same reference interface,
+ * hpu_ops/backend/fp8_ops.cpp:547-705).  b200q_nchw_to_nhwc_u8: out[n][h][w][c] = in[n][c][h][w],
+ * one-byte elements, C a multiple of 4.  b200q_im2col_nhwc_fp8: in is that copy [N][H][W][C];
+ * out: [N * Ho * Wo][ld_out] with column k = (i, j, c - c0) -- the window position first, then the
+ * channel -- so the weight operand is viewed as [C_out][kh][kw][C_g]; C, c0, cg and ld_out are
+ * multiples of 16, in and out 16-byte aligned; zero outside the image and for k >= kh * kw * cg.
+ */
+int b200q_nchw_to_nhwc_u8(const void* in, void* out, int64_t N, int64_t C, int64_t H, int64_t W, void* stream);
+int b200q_im2col_nhwc_fp8(const void* in, void* out, int64_t N, int64_t C, int64_t H, int64_t W, int kh,
+                          int kw, int sh, int sw, int ph, int pw, int dh, int dw, int64_t c0,
+                          int64_t cg, int64_t ld_out, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

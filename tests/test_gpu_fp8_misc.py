@@ -287,7 +287,13 @@ def test_conv2d_fp8_reference_case(ops, scaleA, scaleB, bias, out_dtype, fp8_dty
     dict(N=3, C=16, H=9, W=9, Co=24, k=(3, 1), stride=(1, 1), padding=(0, 0), dilation=(1, 1), groups=4),
     dict(N=1, C=64, H=14, W=14, Co=128, k=(1, 1), stride=(1, 1), padding=(0, 0), dilation=(1, 1), groups=1),
     # 512 channels x 3 rows x 66 bytes do not fit one block's shared memory: two channel chunks per output line
+    dict(N=1, C=520, H=6, W=64, Co=16, k=(3, 3), stride=(1, 1), padding=(1, 1), dilation=(1, 1), groups=1),
+    # channel groups of whole 16-byte pieces take the channels-last path (transposed copy, 16-byte gather, columns
+    # ordered window-first): many channels, groups of 16 and 48 channels, a partial 64-channel tile, odd image sizes
     dict(N=1, C=512, H=6, W=64, Co=16, k=(3, 3), stride=(1, 1), padding=(1, 1), dilation=(1, 1), groups=1),
+    dict(N=2, C=64, H=13, W=7, Co=32, k=(3, 2), stride=(2, 1), padding=(1, 1), dilation=(1, 2), groups=4),
+    dict(N=3, C=96, H=5, W=5, Co=6, k=(5, 5), stride=(1, 1), padding=(2, 2), dilation=(1, 1), groups=2),
+    dict(N=1, C=80, H=31, W=33, Co=40, k=(1, 3), stride=(3, 2), padding=(0, 1), dilation=(1, 1), groups=1),
     dict(N=2, C=6, H=11, W=23, Co=8, k=(2, 3), stride=(1, 2), padding=(1, 0), dilation=(2, 1), groups=2),
     # image rows too wide for the patch kernel's shared memory (3 channels x 3 lines x 12 KB): the fallback kernel
     dict(N=1, C=3, H=4, W=12288, Co=8, k=(3, 3), stride=(1, 1), padding=(1, 1), dilation=(1, 1), groups=1),
