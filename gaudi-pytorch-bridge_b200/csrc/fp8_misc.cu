@@ -891,9 +891,14 @@ __global__ void __launch_bounds__(256) im2col_nhwc_u8_kernel(const Im2colNhwcPar
     const int ij = kp / p.cg16, c16 = kp - ij * p.cg16;
     const int i = ij / p.kw, j = ij - i * p.kw;
     const int dh_off = i * p.dh - p.ph, dw_off = j * p.dw - p.pw;
-    const uint8_t* src = p.in + p.c0 + 16 * (int64_t)c16;
+    // the walk over the rows keeps (h, w) of the window position and the byte offset of that input
+    // pixel, stepping all three: no multiplication per row
+    const int64_t w_step = (int64_t)p.sw * p.C;                                   // wo + 1
+    const int64_t line_step = ((int64_t)p.sh * p.W - p.Wo * p.sw) * p.C;          // wo = Wo - 1 -> 0, ho + 1
+    const int64_t image_step = ((int64_t)p.H - p.Ho * p.sh) * p.W * p.C;          // ho = Ho - 1 -> 0, n + 1
+    int h = ho0 * p.sh + dh_off, w = wo0 * p.sw + dw_off;
+    const uint8_t* src = p.in + p.c0 + 16 * (int64_t)c16 + ((n0 * p.H + h) * p.W + w) * p.C;
     uint8_t* dst = p.out + row0 * p.ld_out + 16 * (int64_t)kp;
-    int64_t n = n0;
     int ho = ho0, wo = wo0;
     for (int r = 0; r < nrows; r += 4) {
       uint4 v[4];
@@ -901,12 +906,19 @@ __global__ void __launch_bounds__(256) im2col_nhwc_u8_kernel(const Im2colNhwcPar
       for (int u = 0; u < 4; ++u) {
         v[u] = make_uint4(0u, 0u, 0u, 0u);
         if (r + u < nrows) {
-          const int h = ho * p.sh + dh_off, w = wo * p.sw + dw_off;
-          if (!pad && h >= 0 && h < p.H && w >= 0 && w < p.W)
-            v[u] = __ldg(reinterpret_cast<const uint4*>(src + ((n * p.H + h) * p.W + w) * p.C));
+          if (!pad && (unsigned)h < (unsigned)p.H && (unsigned)w < (unsigned)p.W) v[u] = __ldg(reinterpret_cast<const uint4*>(src));
+          w += p.sw;
+          src += w_step;
           if (++wo == p.Wo) {
             wo = 0;
-            if (++ho == p.Ho) { ho = 0; ++n; }
+            w = dw_off;
+            h += p.sh;
+            src += line_step;
+            if (++ho == p.Ho) {
+              ho = 0;
+              h = dh_off;
+              src += image_step;
+            }
           }
         }
       }
