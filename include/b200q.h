@@ -174,7 +174,10 @@ int b200q_gptq_repack(const int32_t* qweight, int32_t* qweight_out, int64_t K, i
  * The tcgen05 path takes all four storage orders (a transposed operand is read through an
  * MN-major shared-memory descriptor); it needs batch == 1, 16-byte aligned bases and row
  * strides, and K % 16 == 0 unless both operands are stored [K][rows]; everything else runs a
- * generic CUDA kernel.
+ * generic CUDA kernel, which is two to three orders of magnitude slower on large problems.  This
+ * entry point allocates nothing: a caller with K % 16 != 0 and an operand stored [rows][K] gets
+ * the tcgen05 path by passing copies whose rows are padded with zero bytes to K rounded up to 16
+ * (fp8 0x00 is +0 and adds nothing), as the torch operator does above 2^26 multiply-adds.
  */
 typedef struct b200q_gemm_args {
   const void* A;
