@@ -19,7 +19,7 @@ The default (headline) line carries three sub-records beside the contract's keys
 
 --workload selects one member of the operator family for the same JSON contract:
   gemm (default) | gemm_m1 | gemm_m16 | gemm_m128 | cast_rne | cast_sr | uncast | cast_hybrid | cast_current |
-  softmax_fp8 | sdpa_fp8 | conv2d_fp8 | dequant | dequant_kpacked | w4a16_m2048 | w4a16_m128 | w4a16_m16 | w4a16_m16_kpacked | mlp | scaled_mm_lib
+  softmax_fp8 | sdpa_fp8 | conv2d_fp8 | dequant | dequant_kpacked | w4a16_m2048 | w4a16_m128 | w4a16_m16 | w4a16_m16_kpacked | sum_fp8_rows | sum_fp8_cols | in_place_interleave | mlp | scaled_mm_lib
 (scaled_mm_lib times torch._scaled_mm -- the vendor library -- on the headline shape, as context only).
 --impl reference times the CPU restatement of the reference semantics (the oracle; the
 reference itself has no arithmetic for these operators) on the host cores.
@@ -402,6 +402,42 @@ def build_workload(wl, args, dev, rank, world, peaks):
         w.workload = f"softmax_fp8 over the last dim of [{rows_}, {cols_}] bf16 ~N(0,2), input scale 0.125, output scale 240; 3 B/element"
         w.dtype = "bf16->e4m3 (fp32 softmax)"
         w.l2 = "3 rotating tensors"
+    elif wl in ("sum_fp8_rows", "sum_fp8_cols"):
+        # sum of an e4m3 matrix over its last / its first dimension -> fp32 (1 B/element read)
+        rows_, cols_ = 16384, 8192
+        g = torch.Generator(device=dev).manual_seed(9 + rank)
+        xs = [torch.randn(rows_, cols_, device=dev, generator=g, dtype=torch.float32).to(torch.float8_e4m3fn) for _ in range(3)]
+        outer, red, inner = (rows_, cols_, 1) if wl == "sum_fp8_rows" else (1, rows_, cols_)
+        out = torch.empty(outer * inner, device=dev, dtype=torch.float32)
+        ws_bytes = int(abi.lib.b200q_sum_fp8_workspace_bytes(outer, red, inner))
+        ws = torch.empty(max(ws_bytes, 16), device=dev, dtype=torch.uint8)
+
+        def step(i):
+            abi.check(abi.lib.b200q_sum_fp8(abi.ptr(xs[i % 3]), abi.E4M3, abi.ptr(out), abi.F32, outer, red, inner, abi.ptr(ws),
+                                            ws_bytes, abi.stream_ptr()))
+        w.step = step
+        w.launches_per_step = 1 if wl == "sum_fp8_rows" else 2
+        hbm_bound(rows_ * cols_ + 4 * outer * inner)
+        w.metric = "sum_fp8 GB/s"
+        w.workload = f"sum_fp8 e4m3 [{rows_}, {cols_}] over the {'last' if wl == 'sum_fp8_rows' else 'first'} dimension -> fp32"
+        w.dtype = "e4m3 -> fp32 (fixed-order fp32 sums)"
+        w.l2 = "3 rotating tensors"
+    elif wl == "in_place_interleave":
+        # rows[j] <- rows[j / 4] on [8, 32, 4096, 128] one-byte elements: 7 of the 8 rows (16.8 MB each) are rewritten
+        shape = (8, 32, 4096, 128)
+        g = torch.Generator(device=dev).manual_seed(11 + rank)
+        xs = [torch.randint(0, 255, shape, device=dev, generator=g, dtype=torch.uint8) for _ in range(3)]
+        row_bytes = shape[1] * shape[2] * shape[3]
+
+        def step(i):
+            abi.check(abi.lib.b200q_in_place_interleave(abi.ptr(xs[i % 3]), shape[0], row_bytes, abi.stream_ptr()))
+        w.step = step
+        w.launches_per_step = 2
+        hbm_bound(7 * row_bytes + 2 * row_bytes)  # 7 rows written, 2 distinct source rows read
+        w.metric = "in_place_interleave GB/s"
+        w.workload = "in_place_interleave_ [8, 32, 4096, 128] one-byte elements (117 MB written, 34 MB of distinct sources read)"
+        w.dtype = "u8"
+        w.l2 = "3 rotating tensors"
     elif wl == "cast_current":
         # current scaling: amax pass -> scale on the device -> cast with the device scalar scale
         n = args.elems
@@ -626,7 +662,8 @@ def family_record(args, dev, peaks):
                ("uncast", 1 << 24), ("uncast", 1 << 26), ("dequant", None), ("dequant_kpacked", None),
                ("gemm_m1", None), ("gemm_m16", None), ("gemm_m128", None), ("w4a16_m16", None), ("w4a16_m16_kpacked", None),
                ("w4a16_m2048", None), ("sdpa_fp8", None), ("softmax_fp8", None), ("cast_hybrid", None),
-               ("conv2d_fp8", None)]
+               ("conv2d_fp8", None), ("w4a16_m128", None), ("sum_fp8_rows", None), ("sum_fp8_cols", None),
+               ("in_place_interleave", None)]
     out = {}
     for name, elems in members:
         a = argparse.Namespace(**vars(args))
