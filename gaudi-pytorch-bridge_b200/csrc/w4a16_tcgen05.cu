@@ -212,6 +212,7 @@ w4a16_kernel(const __grid_constant__ CUtensorMap map_act, const __grid_constant_
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  pdl_enter();  // everything above overlaps the tail of the kernel in front; global memory is touched from here on
 
   const int num_work = p.x_tiles * p.y_tiles * p.splits;
   // work item -> (lane-side tile, column-side tile, k range).  Consecutive items (CTAs that run
@@ -844,16 +845,36 @@ static int launch_pair(const CUtensorMap& ma, const CUtensorMap& mr, const CUten
   return B200Q_OK;
 }
 
-// Sum the fp32 partial tiles of a split-K run and round once to the output dtype.
+// Sum the fp32 partial tiles of a split-K run (in split order) and round once to the output dtype.
+// VEC = 4: four neighbouring columns per thread (N and ldo multiples of 4, 16-byte aligned
+// pointers): 16-byte loads of the partials, one division per four outputs, an 8- or 16-byte
+// store.  Launched under the tail of the GEMM kernel; it waits for that grid before it reads.
+template <int VEC>
 __global__ void __launch_bounds__(256) splitk_reduce_kernel(const float* __restrict__ partial, void* out, int out_dtype,
                                                             int64_t M, int64_t N, int64_t ldo, int splits) {
-  const int64_t total = M * N;
+  pdl_enter();
+  const int64_t total = M * N / VEC;
   for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (int64_t)gridDim.x * blockDim.x) {
-    float v = 0.f;
-    for (int s = 0; s < splits; ++s) v += partial[(int64_t)s * total + i];
-    const int64_t m = i / N, n = i % N;
-    if (out_dtype == B200Q_BF16) static_cast<__nv_bfloat16*>(out)[m * ldo + n] = __float2bfloat16_rn(v);
-    else static_cast<float*>(out)[m * ldo + n] = v;
+    const int64_t e = i * VEC, m = e / N, n = e - m * N;
+    if (VEC == 4) {
+      float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+      for (int s = 0; s < splits; ++s) {
+        const float4 t = __ldcs(reinterpret_cast<const float4*>(partial + (int64_t)s * M * N + e));
+        v.x += t.x, v.y += t.y, v.z += t.z, v.w += t.w;
+      }
+      if (out_dtype == B200Q_BF16) {
+        __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
+        *reinterpret_cast<uint2*>(static_cast<__nv_bfloat16*>(out) + m * ldo + n) =
+            make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
+      } else {
+        *reinterpret_cast<float4*>(static_cast<float*>(out) + m * ldo + n) = v;
+      }
+    } else {
+      float v = 0.f;
+      for (int s = 0; s < splits; ++s) v += partial[(int64_t)s * M * N + e];
+      if (out_dtype == B200Q_BF16) static_cast<__nv_bfloat16*>(out)[m * ldo + n] = __float2bfloat16_rn(v);
+      else static_cast<float*>(out)[m * ldo + n] = v;
+    }
   }
 }
 
@@ -876,7 +897,10 @@ static int launch(const CUtensorMap& ma, const CUtensorMap& mr, const CUtensorMa
   int work = p.x_tiles * p.y_tiles * p.splits;
   int per_sm = 227 * 1024 / smem;
   int grid = work < kNumSMs * per_sm ? work : kNumSMs * per_sm;
-  kern<<<grid, C::kThreads, smem, st>>>(ma, mr, ms, mz, p);
+  if (launch_overlapped(kern, dim3((unsigned)grid), dim3(C::kThreads), (size_t)smem, st, ma, mr, ms, mz, p) != cudaSuccess) {
+    (void)cudaGetLastError();
+    kern<<<grid, C::kThreads, smem, st>>>(ma, mr, ms, mz, p);
+  }
   B200Q_LAUNCH_CHECK();
   return B200Q_OK;
 }
@@ -1036,10 +1060,18 @@ int w4a16_gemm_impl(const void* x, int64_t ldx, const int32_t* qweight, const vo
   }
   if (rc) return rc;
   if (p.splits > 1) {
-    const int64_t total = M * N;
+    const int esz = out_dtype == B200Q_BF16 ? 2 : 4;
+    const bool vec4 = (N % 4) == 0 && (ldo % 4) == 0 && (reinterpret_cast<uintptr_t>(out) % (4 * esz)) == 0 &&
+                      (reinterpret_cast<uintptr_t>(p.partial) & 15) == 0;
+    const int64_t total = vec4 ? M * N / 4 : M * N;
     int grid = (int)((total + 255) / 256);
     if (grid > kNumSMs * 8) grid = kNumSMs * 8;
-    w4::splitk_reduce_kernel<<<grid, 256, 0, st>>>(p.partial, out, out_dtype, M, N, ldo, p.splits);
+    auto kern = vec4 ? w4::splitk_reduce_kernel<4> : w4::splitk_reduce_kernel<1>;
+    if (launch_overlapped(kern, dim3((unsigned)grid), dim3(256), 0, st, (const float*)p.partial, out, out_dtype, M, N, ldo,
+                          p.splits) != cudaSuccess) {
+      (void)cudaGetLastError();
+      kern<<<grid, 256, 0, st>>>(p.partial, out, out_dtype, M, N, ldo, p.splits);
+    }
     B200Q_LAUNCH_CHECK();
   }
   return B200Q_OK;
