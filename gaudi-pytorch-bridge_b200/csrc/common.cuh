@@ -60,6 +60,15 @@ inline cudaError_t launch_overlapped(void (*kernel)(KArgs...), dim3 grid, dim3 b
   cfg.numAttrs = 1;
   return cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);
 }
+
+// launch_overlapped() with the ordinary launch as its fallback (for a driver that refuses the
+// attribute); the kernel calls pdl_enter() before its first access to global memory.
+template <typename... KArgs, typename... Args>
+inline void launch_dependent(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, Args&&... args) {
+  if (launch_overlapped(kernel, grid, block, smem, st, args...) == cudaSuccess) return;
+  (void)cudaGetLastError();
+  kernel<<<grid, block, smem, st>>>(static_cast<KArgs>(args)...);
+}
 #endif
 
 // Clears an amax word with a one-thread kernel behind which the kernel that accumulates into it

@@ -350,6 +350,7 @@ __device__ __forceinline__ float fp8_to_float(uint8_t b) {
 template <int FMT>
 __global__ void __launch_bounds__(256) sum_fp8_strided_kernel(const uint8_t* __restrict__ in, float* __restrict__ partial,
                                                               int64_t outer, int64_t reduce, int64_t inner, int chunks) {
+  pdl_enter();
   const int64_t n_out = outer * inner;
   const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= n_out) return;
@@ -368,6 +369,7 @@ __global__ void __launch_bounds__(256) sum_fp8_strided_kernel(const uint8_t* __r
 template <int FMT>
 __global__ void __launch_bounds__(256) sum_fp8_strided16_kernel(const uint8_t* __restrict__ in, float* __restrict__ partial,
                                                                 int64_t outer, int64_t reduce, int64_t inner, int chunks) {
+  pdl_enter();
   const int64_t inner16 = inner >> 4;
   const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;  // (o, 16-group)
   if (idx >= outer * inner16) return;
@@ -410,6 +412,7 @@ __global__ void __launch_bounds__(256) sum_fp8_strided16_kernel(const uint8_t* _
 template <int FMT>
 __global__ void __launch_bounds__(256) sum_fp8_rows_kernel(const uint8_t* __restrict__ in, float* __restrict__ partial,
                                                            int64_t outer, int64_t reduce, int chunks) {
+  pdl_enter();
   // grid (outer, chunks): one block sums one chunk of one row
   const int64_t row = blockIdx.x;
   const int chunk = blockIdx.y;
@@ -464,6 +467,7 @@ __global__ void __launch_bounds__(256) sum_fp8_rows_kernel(const uint8_t* __rest
 template <int FMT>
 __global__ void __launch_bounds__(256) sum_fp8_finish_kernel(const float* __restrict__ partial, void* out, int out_dtype,
                                                              int64_t n_out, int chunks) {
+  pdl_enter();
   const int64_t idx = (int64_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (idx >= n_out) return;
   float acc = 0.f;
@@ -483,6 +487,7 @@ __global__ void __launch_bounds__(256) sum_fp8_finish_kernel(const float* __rest
 // (coalesced 128-byte loads, four in flight), the 8 lane sums are then added in lane order.
 __global__ void __launch_bounds__(256) sum_fp8_finish_wide_kernel(const float* __restrict__ partial, void* out, int out_dtype,
                                                                   int64_t n_out, int chunks) {
+  pdl_enter();
   __shared__ float sm[8][33];
   const int x = threadIdx.x & 31, y = threadIdx.x >> 5;
   const int64_t idx = (int64_t)blockIdx.x * 32 + x;
@@ -553,21 +558,21 @@ int sum_fp8_impl(const void* in, int in_dtype, void* out, int out_dtype, int64_t
     const int64_t vecs = (reduce + chunks - 1) / chunks / 16;
     int threads = 32;
     while (threads < 256 && threads * 4 < vecs) threads *= 2;
-    if (in_dtype == B200Q_E4M3) sum_fp8_rows_kernel<B200Q_E4M3><<<grid, threads, 0, st>>>(src, partial, outer, reduce, chunks);
-    else sum_fp8_rows_kernel<B200Q_E5M2><<<grid, threads, 0, st>>>(src, partial, outer, reduce, chunks);
+    if (in_dtype == B200Q_E4M3) launch_dependent(sum_fp8_rows_kernel<B200Q_E4M3>, grid, dim3(threads), 0, st, src, partial, outer, reduce, chunks);
+    else launch_dependent(sum_fp8_rows_kernel<B200Q_E5M2>, grid, dim3(threads), 0, st, src, partial, outer, reduce, chunks);
   } else if ((inner % 16) == 0 && (reinterpret_cast<uintptr_t>(in) & 15) == 0) {
     dim3 grid((unsigned)((n_out / 16 + 255) / 256), (unsigned)chunks);
-    if (in_dtype == B200Q_E4M3) sum_fp8_strided16_kernel<B200Q_E4M3><<<grid, 256, 0, st>>>(src, partial, outer, reduce, inner, chunks);
-    else sum_fp8_strided16_kernel<B200Q_E5M2><<<grid, 256, 0, st>>>(src, partial, outer, reduce, inner, chunks);
+    if (in_dtype == B200Q_E4M3) launch_dependent(sum_fp8_strided16_kernel<B200Q_E4M3>, grid, dim3(256), 0, st, src, partial, outer, reduce, inner, chunks);
+    else launch_dependent(sum_fp8_strided16_kernel<B200Q_E5M2>, grid, dim3(256), 0, st, src, partial, outer, reduce, inner, chunks);
   } else {
     dim3 grid((unsigned)((n_out + 255) / 256), (unsigned)chunks);
-    if (in_dtype == B200Q_E4M3) sum_fp8_strided_kernel<B200Q_E4M3><<<grid, 256, 0, st>>>(src, partial, outer, reduce, inner, chunks);
-    else sum_fp8_strided_kernel<B200Q_E5M2><<<grid, 256, 0, st>>>(src, partial, outer, reduce, inner, chunks);
+    if (in_dtype == B200Q_E4M3) launch_dependent(sum_fp8_strided_kernel<B200Q_E4M3>, grid, dim3(256), 0, st, src, partial, outer, reduce, inner, chunks);
+    else launch_dependent(sum_fp8_strided_kernel<B200Q_E5M2>, grid, dim3(256), 0, st, src, partial, outer, reduce, inner, chunks);
   }
   B200Q_LAUNCH_CHECK();
   if (direct) return B200Q_OK;
-  if (chunks >= 16) sum_fp8_finish_wide_kernel<<<(unsigned)((n_out + 31) / 32), 256, 0, st>>>(partial, out, out_dtype, n_out, chunks);
-  else sum_fp8_finish_kernel<0><<<fin_blocks, 256, 0, st>>>(partial, out, out_dtype, n_out, chunks);
+  if (chunks >= 16) launch_dependent(sum_fp8_finish_wide_kernel, dim3((unsigned)((n_out + 31) / 32)), dim3(256), 0, st, (const float*)partial, out, out_dtype, n_out, chunks);
+  else launch_dependent(sum_fp8_finish_kernel<0>, dim3((unsigned)fin_blocks), dim3(256), 0, st, (const float*)partial, out, out_dtype, n_out, chunks);
   B200Q_LAUNCH_CHECK();
   return B200Q_OK;
 }
@@ -586,6 +591,7 @@ constexpr int kIlvPieces = 4;
 template <typename T>
 __global__ void __launch_bounds__(256) interleave_phase_kernel(uint8_t* base, int64_t row_bytes, int64_t lo, int64_t hi,
                                                                int64_t s_first, int64_t s_end, int tpr) {
+  pdl_enter();
   const int rows_per_block = 256 / tpr;
   const int64_t s = s_first + (int64_t)blockIdx.y * rows_per_block + threadIdx.x / tpr;
   if (s >= s_end) return;
@@ -628,8 +634,8 @@ int in_place_interleave_impl(void* data, int64_t n_rows, int64_t row_bytes, cuda
       int64_t by = (s_end - s + rows_per_block - 1) / rows_per_block;
       if (by > 65535) by = 65535;
       const dim3 grid((unsigned)bx, (unsigned)by);
-      if (wide) interleave_phase_kernel<uint4><<<grid, 256, 0, st>>>(static_cast<uint8_t*>(data), row_bytes, lo, hi, s, s_end, tpr);
-      else interleave_phase_kernel<uint8_t><<<grid, 256, 0, st>>>(static_cast<uint8_t*>(data), row_bytes, lo, hi, s, s_end, tpr);
+      if (wide) launch_dependent(interleave_phase_kernel<uint4>, grid, dim3(256), 0, st, static_cast<uint8_t*>(data), row_bytes, lo, hi, s, s_end, tpr);
+      else launch_dependent(interleave_phase_kernel<uint8_t>, grid, dim3(256), 0, st, static_cast<uint8_t*>(data), row_bytes, lo, hi, s, s_end, tpr);
       B200Q_LAUNCH_CHECK();
       s += by * rows_per_block;
     }
@@ -826,6 +832,7 @@ constexpr int kTrPitch = kTrTile + 4;  // bytes; 17 words: the transposed writes
 
 __global__ void __launch_bounds__(256) nchw_to_nhwc_u8_kernel(const uint8_t* __restrict__ in, uint8_t* __restrict__ out, int64_t C,
                                                               int64_t HW, int wide) {
+  pdl_enter();
   __shared__ __align__(16) uint8_t tile[kTrTile * kTrPitch];
   const int64_t n = blockIdx.z, c0 = (int64_t)blockIdx.y * kTrTile, p0 = (int64_t)blockIdx.x * kTrTile;
   const uint8_t* src = in + n * C * HW;
@@ -871,8 +878,8 @@ int nchw_to_nhwc_u8_impl(const void* in, void* out, int64_t N, int64_t C, int64_
   const int64_t bx = (HW + kTrTile - 1) / kTrTile, by = (C + kTrTile - 1) / kTrTile;
   if (bx > 0x7FFFFFFF || by > 65535 || N > 65535) return B200Q_ERR_TOO_LARGE;
   const int wide = (HW % 4) == 0 && (reinterpret_cast<uintptr_t>(in) & 3) == 0;
-  nchw_to_nhwc_u8_kernel<<<dim3((unsigned)bx, (unsigned)by, (unsigned)N), 256, 0, st>>>(
-      static_cast<const uint8_t*>(in), static_cast<uint8_t*>(out), C, HW, wide);
+  launch_dependent(nchw_to_nhwc_u8_kernel, dim3((unsigned)bx, (unsigned)by, (unsigned)N), dim3(256), 0, st,
+                   static_cast<const uint8_t*>(in), static_cast<uint8_t*>(out), C, HW, wide);
   B200Q_LAUNCH_CHECK();
   return B200Q_OK;
 }
@@ -893,6 +900,7 @@ struct Im2colNhwcParams {
 };
 
 __global__ void __launch_bounds__(256) im2col_nhwc_u8_kernel(const Im2colNhwcParams p) {
+  pdl_enter();
   const int64_t row0 = (int64_t)blockIdx.x * kIm2Rows;
   const int nrows = (int)(p.rows - row0 < kIm2Rows ? p.rows - row0 : kIm2Rows);
   // (n, ho, wo) of the block's first row
@@ -962,7 +970,7 @@ int im2col_nhwc_u8_impl(const void* in, void* out, int64_t N, int64_t C, int64_t
   if (blocks > 0x7FFFFFFF) return B200Q_ERR_TOO_LARGE;
   int threads = 32;
   while (threads < 256 && threads < p.pieces_ld) threads += 32;
-  im2col_nhwc_u8_kernel<<<(unsigned)blocks, threads, 0, st>>>(p);
+  launch_dependent(im2col_nhwc_u8_kernel, dim3((unsigned)blocks), dim3(threads), 0, st, p);
   B200Q_LAUNCH_CHECK();
   return B200Q_OK;
 }
