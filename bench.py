@@ -658,8 +658,8 @@ def time_workload(w, steps, warmup, dist, dev, use_graph, min_ms=0.0):
 # ----------------------------------------------------------------------------- sub-records
 def family_record(args, dev, peaks):
     """The other operators BASELINE.json's metric names, each timed for a few milliseconds."""
-    members = [("cast_rne", 1 << 24), ("cast_rne", 1 << 26), ("cast_sr", 1 << 24), ("cast_sr", 1 << 26),
-               ("uncast", 1 << 24), ("uncast", 1 << 26), ("dequant", None), ("dequant_kpacked", None),
+    members = [("cast_rne", 1 << 20), ("cast_rne", 1 << 24), ("cast_rne", 1 << 26), ("cast_sr", 1 << 20), ("cast_sr", 1 << 24),
+               ("cast_sr", 1 << 26), ("uncast", 1 << 20), ("uncast", 1 << 24), ("uncast", 1 << 26), ("dequant", None), ("dequant_kpacked", None),
                ("gemm_m1", None), ("gemm_m16", None), ("gemm_m128", None), ("w4a16_m16", None), ("w4a16_m16_kpacked", None),
                ("w4a16_m2048", None), ("sdpa_fp8", None), ("softmax_fp8", None), ("cast_hybrid", None),
                ("conv2d_fp8", None), ("w4a16_m128", None), ("sum_fp8_rows", None), ("sum_fp8_cols", None),
