@@ -40,6 +40,11 @@ inline void count_launch() { g_launches.fetch_add(1, std::memory_order_relaxed);
 // lets the successor be set up early in the same way.  Both parts are no-ops in an ordinary
 // launch.  Between two kernels of 10-30 us this takes 1.5-2.5 us of launch gap away.
 #ifdef __CUDACC__
+// Lets the kernel behind this one in the stream be set up now, without waiting for anything
+// itself: for a kernel that is launched behind a kernel which has already waited (the amax
+// clearing kernel) and waits on its own only before it publishes (block_amax_to_global).
+__device__ __forceinline__ void pdl_release() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 __device__ __forceinline__ void pdl_enter() {
   asm volatile("griddepcontrol.wait;" ::: "memory");
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");

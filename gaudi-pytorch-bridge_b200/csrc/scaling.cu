@@ -16,6 +16,7 @@ namespace b200q {
 // 2 (bf16) or 4 (fp32) bytes read per element, nothing written but one word: HBM-bound.
 template <typename InT>
 __global__ void __launch_bounds__(256, 8) amax_kernel(const InT* __restrict__ in, int64_t n, float* amax) {
+  pdl_release();
   constexpr int kPer16 = 16 / sizeof(InT);  // elements per 16-byte load
   const int64_t nvec = n / kPer16;
   const uint4* v = reinterpret_cast<const uint4*>(in);
