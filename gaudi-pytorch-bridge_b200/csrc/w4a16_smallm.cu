@@ -221,11 +221,13 @@ __global__ void __cluster_dims__(kCluster, 1, 1) __launch_bounds__(kThreads, 1) 
   constexpr int kStepsPerChunk = kXChunkRows / kStepRows;
 
   stage_x(0);
-  int issued = 0;
   if (KP == 0) {
     for (int t = 0; t < kSlots - 1; ++t) issue_batch(t);
   } else {
-    for (; issued < steps && issued < kDepth; ++issued) issue(issued);
+    for (int t = 0; t < kDepth - 1; ++t) {
+      if (t < steps) issue(t);
+      else cp_async_commit();
+    }
   }
 
   float acc[4][MT][4];
@@ -345,37 +347,41 @@ __global__ void __cluster_dims__(kCluster, 1, 1) __launch_bounds__(kThreads, 1) 
       }
     }
   } else {
-    uint32_t scp[4], zpk;  // scales two per register, zero points eight per register
+    // per accumulator a the two columns g + 16a and g + 16a + 8: scale and 128 + zero point, each
+    // twice in a register (an operand register holds two k of one column), set up once per group
+    uint32_t sc2[4][2], zc2[4][2];
     auto load_group = [&](int64_t grp) {
 #pragma unroll
-      for (int j = 0; j < 8; j += 2) {
-        const uint32_t lo = (uint32_t)__bfloat16_as_ushort(p.scale[grp * p.N + n0 + g + 8 * j]);
-        const uint32_t hi = (uint32_t)__bfloat16_as_ushort(p.scale[grp * p.N + n0 + g + 8 * (j + 1)]);
-        scp[j >> 1] = lo | (hi << 16);
-      }
-      zpk = 0u;  // column n0 + g + 8j is nibble g of zero-point word n0 / 8 + j
-      if (p.zp) {
-#pragma unroll
-        for (int j = 0; j < 8; ++j) zpk |= (((uint32_t)__ldg(p.zp + grp * (p.N / 8) + n0 / 8 + j) >> (4 * g)) & 15u) << (4 * j);
+      for (int j = 0; j < 8; ++j) {
+        sc2[j >> 1][j & 1] = (uint32_t)__bfloat16_as_ushort(p.scale[grp * p.N + n0 + g + 8 * j]) * 0x00010001u;
+        // column n0 + g + 8j is nibble g of zero-point word n0 / 8 + j
+        const uint32_t z = p.zp ? ((uint32_t)__ldg(p.zp + grp * (p.N / 8) + n0 / 8 + j) >> (4 * g)) & 15u : 0u;
+        zc2[j >> 1][j & 1] = (z * 0x00010001u) | 0x43004300u;
       }
     };
     load_group(cur_grp);
+    // A stage is refilled one step after it was read (after the warp barrier of the next step),
+    // so its words are loaded where they are used instead of all in front of the refill; every
+    // step commits a group, an empty one past the end, so that the wait is the same at every step.
+    auto issue_or_empty = [&](int s) {
+      if (s < steps) issue(s);
+      else cp_async_commit();
+    };
+    const uint32_t lane_off = q * 256 + g * 4, q32 = q * 32;
     for (int s = 0; s < steps; ++s) {
-      const int rest = steps - 1 - s;
-      const int pend = rest < kDepth - 1 ? rest : kDepth - 1;
       if ((s & (kStepsPerChunk - 1)) == 0) {
         if (s > 0) {
           named_bar(1 + khalf, 32 * kStrips);
           stage_x(s / kStepsPerChunk);
           cp_async_wait(0);
         } else {
-          cp_async_wait(issued);  // all but the weight groups: the chunk
+          asm volatile("cp.async.wait_group %0;" ::"n"(kDepth - 1) : "memory");  // all but the weights: the chunk
         }
         named_bar(1 + khalf, 32 * kStrips);
       }
-      if (pend == kDepth - 1) asm volatile("cp.async.wait_group %0;" ::"n"(kDepth - 1) : "memory");
-      else cp_async_wait(pend);
-      __syncwarp();
+      asm volatile("cp.async.wait_group %0;" ::"n"(kDepth - 2) : "memory");
+      __syncwarp();  // step s has landed for every lane, and every lane is done with the stage of step s - 1
+      issue_or_empty(s + kDepth - 1);
       if (--to_next_group == 0) {
         to_next_group = steps_per_group;
         load_group(++cur_grp);
@@ -395,29 +401,21 @@ __global__ void __cluster_dims__(kCluster, 1, 1) __launch_bounds__(kThreads, 1) 
           bx[t][h][3] = __byte_perm(xv.y, xv.w, 0x7632);
         }
       }
-      const uint8_t* st = ring + (s & (kDepth - 1)) * kStageBytes;
-      uint32_t wq[2][8];
-#pragma unroll
-      for (int h = 0; h < 2; ++h)
-#pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          const int wr = q + 4 * h;
-          wq[h][j] = *reinterpret_cast<const uint32_t*>(st + wr * 256 + (((g + 8 * j) * 4) ^ ((wr & 3) * 32)));
-        }
-      __syncwarp();  // every lane has read the stage before it is refilled
-      if (issued < steps) { issue(issued); ++issued; }
+      // word (word-row wr, column g + 8j) sits at wr * 256 + ((g + 8j) * 4 ^ (wr & 3) * 32); with wr = q or
+      // q + 4 that is lane_off (+ 1024) + 32 (j ^ q)
+      const uint8_t* st = ring + (s & (kDepth - 1)) * kStageBytes + lane_off;
 #pragma unroll
       for (int a = 0; a < 4; ++a) {
-        const int j0 = 2 * a, j1 = 2 * a + 1;
-        const uint32_t s0 = __byte_perm(scp[a], 0u, 0x1010), s1 = __byte_perm(scp[a], 0u, 0x3232);
-        const uint32_t z0 = (((zpk >> (4 * j0)) & 15u) * 0x00010001u) | 0x43004300u;
-        const uint32_t z1 = (((zpk >> (4 * j1)) & 15u) * 0x00010001u) | 0x43004300u;
+        const uint32_t o0 = (uint32_t)(64 * a) ^ q32, o1 = (uint32_t)(64 * a + 32) ^ q32;
+        const uint32_t w00 = *reinterpret_cast<const uint32_t*>(st + o0), w01 = *reinterpret_cast<const uint32_t*>(st + o1);
+        const uint32_t w10 = *reinterpret_cast<const uint32_t*>(st + 1024 + o0),
+                       w11 = *reinterpret_cast<const uint32_t*>(st + 1024 + o1);
 #pragma unroll
         for (int i = 0; i < 4; ++i) {
-          const uint32_t a0 = bf2_mul(bf2_sub(nib_pair(wq[0][j0], i), z0), s0);
-          const uint32_t a1 = bf2_mul(bf2_sub(nib_pair(wq[0][j1], i), z1), s1);
-          const uint32_t a2 = bf2_mul(bf2_sub(nib_pair(wq[1][j0], i), z0), s0);
-          const uint32_t a3 = bf2_mul(bf2_sub(nib_pair(wq[1][j1], i), z1), s1);
+          const uint32_t a0 = bf2_mul(bf2_sub(nib_pair(w00, i), zc2[a][0]), sc2[a][0]);
+          const uint32_t a1 = bf2_mul(bf2_sub(nib_pair(w01, i), zc2[a][1]), sc2[a][1]);
+          const uint32_t a2 = bf2_mul(bf2_sub(nib_pair(w10, i), zc2[a][0]), sc2[a][0]);
+          const uint32_t a3 = bf2_mul(bf2_sub(nib_pair(w11, i), zc2[a][1]), sc2[a][1]);
 #pragma unroll
           for (int t = 0; t < MT; ++t) mma_bf16(acc[a][t], a0, a1, a2, a3, bx[t][0][i], bx[t][1][i]);
         }
